@@ -1,0 +1,59 @@
+"""CUDA sparse kernels against the composite torch implementation run on CPU."""
+import pytest
+import torch
+
+from torchrec_b200.ops import sparse_ops as sops
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int64])
+def test_complete_cumsum(dtype):
+    x = torch.randint(0, 50, (100003,), dtype=dtype)
+    torch.testing.assert_close(sops.asynchronous_complete_cumsum(x.cuda()).cpu(), sops.asynchronous_complete_cumsum(x))
+
+
+@pytest.mark.parametrize("weighted", [False, True])
+def test_permute_2d(weighted):
+    T, B = 7, 33
+    lengths = torch.randint(0, 6, (T, B), dtype=torch.int32)
+    N = int(lengths.sum())
+    values = torch.randint(0, 1000, (N,), dtype=torch.int64)
+    w = torch.rand(N) if weighted else None
+    for perm in ([3, 0, 6, 1, 2, 5, 4], [1, 1, 4], [2, 5]):
+        p = torch.tensor(perm, dtype=torch.int32)
+        rl, rv, rw = sops.permute_2D_sparse_data(p, lengths, values, w)
+        gl, gv, gw = sops.permute_2D_sparse_data(p.cuda(), lengths.cuda(), values.cuda(), None if w is None else w.cuda())
+        assert torch.equal(gl.cpu(), rl) and torch.equal(gv.cpu(), rv)
+        if weighted:
+            assert torch.equal(gw.cpu(), rw)
+
+
+@pytest.mark.parametrize("my_size", [2, 8])
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int64])
+def test_block_bucketize(my_size, dtype):
+    F, B = 3, 41
+    rows = [1000, 77, 5000]
+    lengths = torch.randint(0, 50, (F * B,), dtype=dtype)
+    idx = torch.cat([torch.randint(0, rows[f], (int(lengths[f * B:(f + 1) * B].sum()),)) for f in range(F)]).to(dtype)
+    w = torch.rand(idx.numel())
+    blk = torch.tensor([(r + my_size - 1) // my_size for r in rows], dtype=dtype)
+    ref = sops.block_bucketize_sparse_features(lengths, idx, True, True, blk, my_size, w)
+    got = sops.block_bucketize_sparse_features(lengths.cuda(), idx.cuda(), True, True, blk.cuda(), my_size, w.cuda())
+    for r, g in zip(ref, got):
+        assert torch.equal(g.cpu(), r)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_jagged_padded_roundtrip(dtype):
+    B, L, D = 29, 12, 64
+    lengths = torch.randint(0, 20, (B,))
+    off = torch.cat([torch.zeros(1, dtype=torch.int64), lengths.cumsum(0)])
+    v = torch.randn(int(off[-1]), D).to(dtype)
+    ref = sops.jagged_to_padded_dense(v, off, L, 0.5)
+    got = sops.jagged_to_padded_dense(v.cuda(), off.cuda(), L, 0.5)
+    assert torch.equal(got.cpu(), ref)
+    lens_c = lengths.clamp(max=L)
+    off_c = torch.cat([torch.zeros(1, dtype=torch.int64), lens_c.cumsum(0)])
+    back = sops.padded_dense_to_jagged(got, off_c.cuda(), int(off_c[-1]))
+    assert torch.equal(back.cpu(), sops.padded_dense_to_jagged(ref, off_c))

@@ -1,0 +1,179 @@
+"""CUDA TBE kernels against the CPU (plain torch, fp32) implementation of the same module."""
+import copy
+
+import pytest
+import torch
+
+from torchrec_b200.modules.embedding_configs import PoolingMode
+from torchrec_b200.ops.tbe import EmbOptimType, OptimizerArgs, TableBatchedEmbeddingBags
+
+pytestmark = pytest.mark.gpu
+
+
+def _make_inputs(specs, ftm, B, max_len, weighted, seed, zipf=False, idx_dtype=torch.int64):
+    g = torch.Generator().manual_seed(seed)
+    F = len(ftm)
+    lengths = torch.randint(0, max_len + 1, (F * B,), generator=g)
+    offsets = torch.cat([torch.zeros(1, dtype=torch.int64), lengths.cumsum(0)])
+    idx = []
+    for f in range(F):
+        n = int(lengths[f * B:(f + 1) * B].sum())
+        rows = specs[ftm[f]][0]
+        if zipf:
+            r = torch.rand(n, generator=g)
+            ids = (rows ** r - 1).long().clamp(0, rows - 1)  # heavy head -> long duplicate runs
+        else:
+            ids = torch.randint(0, rows, (n,), generator=g)
+        idx.append(ids)
+    idx = torch.cat(idx)
+    psw = torch.rand(idx.numel(), generator=g) if weighted else None
+    return idx.to(idx_dtype), offsets.to(idx_dtype), psw
+
+
+def _pair(specs, ftm, pooling, opt, wdtype=torch.float32, fused=True, out_dtype=torch.float32):
+    torch.manual_seed(1)
+    cpu = TableBatchedEmbeddingBags(specs, ftm, pooling, wdtype, out_dtype, copy.deepcopy(opt), fused=fused)
+    cpu.init_embedding_weights_uniform(-0.5, 0.5)
+    gpu = TableBatchedEmbeddingBags(specs, ftm, pooling, wdtype, out_dtype, copy.deepcopy(opt), fused=fused, device="cuda")
+    with torch.no_grad():
+        gpu.weights.copy_(cpu.weights)
+    return cpu, gpu
+
+
+@pytest.mark.parametrize("pooling", [PoolingMode.SUM, PoolingMode.MEAN])
+@pytest.mark.parametrize("weighted", [False, True])
+@pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
+def test_forward_pooled(pooling, weighted, idx_dtype):
+    specs = [(1000, 128), (50, 64), (300, 256), (7, 8)]
+    ftm = [0, 1, 2, 2, 3]
+    cpu, gpu = _pair(specs, ftm, pooling, OptimizerArgs())
+    idx, off, psw = _make_inputs(specs, ftm, 37, 9, weighted, 3, idx_dtype=idx_dtype)
+    with torch.no_grad():
+        ref = cpu(idx, off, psw)
+        out = gpu(idx.cuda(), off.cuda(), None if psw is None else psw.cuda())
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-5, atol=1e-5)
+    gpu.check_error()
+
+
+@pytest.mark.parametrize("wdtype,out_dtype", [(torch.float16, torch.float16), (torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16)])
+def test_forward_low_precision(wdtype, out_dtype):
+    specs = [(500, 128), (200, 512)]
+    ftm = [0, 1]
+    cpu, gpu = _pair(specs, ftm, PoolingMode.SUM, OptimizerArgs(), wdtype, out_dtype=out_dtype)
+    idx, off, _ = _make_inputs(specs, ftm, 64, 20, False, 5)
+    with torch.no_grad():
+        ref = cpu(idx, off)
+        out = gpu(idx.cuda(), off.cuda())
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_forward_sequence():
+    specs = [(400, 64), (90, 64)]
+    ftm = [0, 1, 0]
+    cpu, gpu = _pair(specs, ftm, PoolingMode.NONE, OptimizerArgs())
+    idx, off, _ = _make_inputs(specs, ftm, 19, 40, False, 9)
+    with torch.no_grad():
+        ref = cpu(idx, off)
+        out = gpu(idx.cuda(), off.cuda())
+    torch.testing.assert_close(out.cpu(), ref)
+
+
+OPTS = [
+    OptimizerArgs(EmbOptimType.EXACT_SGD, 0.1),
+    OptimizerArgs(EmbOptimType.EXACT_ROWWISE_ADAGRAD, 0.05, eps=1e-8),
+    OptimizerArgs(EmbOptimType.EXACT_ROWWISE_ADAGRAD, 0.05, eps=1e-8, weight_decay=0.01),
+    OptimizerArgs(EmbOptimType.EXACT_ADAGRAD, 0.05, eps=1e-8),
+    OptimizerArgs(EmbOptimType.ADAM, 0.01, eps=1e-8),
+    OptimizerArgs(EmbOptimType.PARTIAL_ROWWISE_ADAM, 0.01, eps=1e-8),
+    OptimizerArgs(EmbOptimType.LAMB, 0.01, eps=1e-6, weight_decay=0.01),
+    OptimizerArgs(EmbOptimType.PARTIAL_ROWWISE_LAMB, 0.01, eps=1e-6),
+    OptimizerArgs(EmbOptimType.LARS_SGD, 0.1, eta=0.01),
+]
+
+
+@pytest.mark.parametrize("opt", OPTS, ids=lambda o: f"{o.optimizer.value}-wd{o.weight_decay}")
+@pytest.mark.parametrize("zipf", [False, True])
+def test_backward_fused_optimizers(opt, zipf):
+    """Two steps, hot rows included (zipf) so that rows spanning several 64-entry blocks are hit."""
+    specs = [(2000, 128), (64, 64), (900, 256)]
+    ftm = [0, 1, 2, 0]
+    cpu, gpu = _pair(specs, ftm, PoolingMode.SUM, opt)
+    for step in range(2):
+        idx, off, psw = _make_inputs(specs, ftm, 257, 30, step == 1, 11 + step, zipf=zipf)
+        ref = cpu(idx, off, psw)
+        out = gpu(idx.cuda(), off.cuda(), None if psw is None else psw.cuda())
+        g = torch.randn(ref.shape, generator=torch.Generator().manual_seed(step))
+        ref.backward(g)
+        out.backward(g.cuda())
+        torch.testing.assert_close(out.detach().cpu(), ref.detach(), rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(gpu.weights.detach().cpu(), cpu.weights.detach(), rtol=2e-4, atol=2e-5)
+        if cpu.momentum1.numel():
+            torch.testing.assert_close(gpu.momentum1.cpu(), cpu.momentum1, rtol=2e-4, atol=1e-6)
+        if cpu.momentum2.numel():
+            torch.testing.assert_close(gpu.momentum2.cpu(), cpu.momentum2, rtol=2e-4, atol=1e-7)
+    gpu.check_error()
+
+
+def test_backward_mean_and_bf16_grad():
+    specs = [(3000, 128)]
+    ftm = [0, 0]
+    opt = OptimizerArgs(EmbOptimType.EXACT_ROWWISE_ADAGRAD, 0.05)
+    cpu, gpu = _pair(specs, ftm, PoolingMode.MEAN, opt, out_dtype=torch.float32)
+    idx, off, _ = _make_inputs(specs, ftm, 300, 12, False, 21, zipf=True)
+    ref = cpu(idx, off)
+    out = gpu(idx.cuda(), off.cuda())
+    g = torch.randn(ref.shape).bfloat16()
+    ref.backward(g.float())
+    out.backward(g.cuda().float())
+    torch.testing.assert_close(gpu.weights.detach().cpu(), cpu.weights.detach(), rtol=2e-4, atol=2e-5)
+
+
+def test_backward_sequence_adam():
+    specs = [(500, 64), (100, 64)]
+    ftm = [0, 1]
+    opt = OptimizerArgs(EmbOptimType.ADAM, 0.01)
+    cpu, gpu = _pair(specs, ftm, PoolingMode.NONE, opt)
+    idx, off, _ = _make_inputs(specs, ftm, 33, 50, False, 31, zipf=True)
+    ref = cpu(idx, off)
+    out = gpu(idx.cuda(), off.cuda())
+    g = torch.randn(ref.shape)
+    ref.backward(g)
+    out.backward(g.cuda())
+    torch.testing.assert_close(gpu.weights.detach().cpu(), cpu.weights.detach(), rtol=2e-4, atol=2e-5)
+
+
+def test_backward_dense_grad():
+    specs = [(300, 128), (40, 32)]
+    ftm = [0, 1]
+    cpu, gpu = _pair(specs, ftm, PoolingMode.SUM, OptimizerArgs(), fused=False)
+    idx, off, _ = _make_inputs(specs, ftm, 50, 10, False, 41, zipf=True)
+    ref = cpu(idx, off)
+    out = gpu(idx.cuda(), off.cuda())
+    g = torch.randn(ref.shape)
+    ref.backward(g)
+    out.backward(g.cuda())
+    torch.testing.assert_close(gpu.weights.grad.cpu(), cpu.weights.grad, rtol=1e-4, atol=1e-5)
+
+
+def test_fp16_weights_backward():
+    specs = [(800, 256)]
+    opt = OptimizerArgs(EmbOptimType.EXACT_ROWWISE_ADAGRAD, 0.05)
+    cpu, gpu = _pair(specs, [0], PoolingMode.SUM, opt, torch.float16, out_dtype=torch.float32)
+    idx, off, _ = _make_inputs(specs, [0], 128, 20, False, 51)
+    ref = cpu(idx, off)
+    out = gpu(idx.cuda(), off.cuda())
+    g = torch.randn(ref.shape)
+    ref.backward(g)
+    out.backward(g.cuda())
+    torch.testing.assert_close(gpu.weights.detach().cpu().float(), cpu.weights.detach().float(), rtol=2e-3, atol=2e-3)
+
+
+def test_out_of_range_id_is_reported():
+    specs = [(10, 8)]
+    _, gpu = _pair(specs, [0], PoolingMode.SUM, OptimizerArgs())
+    idx = torch.tensor([1, 99], device="cuda")
+    off = torch.tensor([0, 2], device="cuda")
+    with torch.no_grad():
+        gpu(idx, off)
+    with pytest.raises(IndexError):
+        gpu.check_error()

@@ -1,0 +1,881 @@
+// Table-batched embedding (TBE) kernels for sm_100a.
+//
+//   tbe_forward          pooled lookup (sum / mean / weighted), one warp per bag, 16-byte row slices
+//                        per lane, fp32 accumulation.  The pooled bag is written straight into the
+//                        buffer of the rank that owns the sample: `out[dst_rank][b_local, col]` where
+//                        the buffers are peer-mapped (NVLink) pointers.  With one rank this is a plain
+//                        local store.  In accumulate mode (row-wise sharding) the partial sum is added
+//                        into the owner's fp32 buffer with a vector `red`, which is the reduce-scatter.
+//   tbe_sequence_forward unpooled lookup, one warp per bag writing one row per id.
+//   tbe_backward         gradient of either lookup fused with the optimizer update.  Ids are sorted by
+//                        global row (cub radix sort), the sorted list is cut into fixed blocks of
+//                        kBlk entries and one warp walks each block, summing the upstream gradient rows
+//                        of equal ids in registers.  A row whose entries lie inside one block is
+//                        updated immediately; rows that span blocks (hot ids of a Zipf distribution)
+//                        leave partial sums in scratch that a second pass combines in a fixed order,
+//                        so the update is deterministic.  No [ids, D] gradient tensor is materialised.
+//
+// The reference obtains these from an external wheel (call sites
+// torchrec/distributed/batched_embedding_kernel.py:2561-2584, :3211-3231).
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDACachingAllocator.h>
+#include <torch/library.h>
+
+#include <cub/cub.cuh>
+
+#include "common.cuh"
+
+namespace trb {
+
+// per-feature metadata rows of the int64 [kMetaRows, F] tensor
+enum MetaRow : int { M_WOFF = 0, M_HASHOFF = 1, M_ROWS = 2, M_DIM = 3, M_OUTOFF = 4, kMetaRows = 5 };
+
+enum Pooling : int { POOL_SUM = 0, POOL_MEAN = 1, POOL_NONE = 2 };
+
+enum OptType : int {
+  OPT_SGD = 0,
+  OPT_ROWWISE_ADAGRAD = 1,
+  OPT_ADAGRAD = 2,
+  OPT_ADAM = 3,
+  OPT_PARTIAL_ROWWISE_ADAM = 4,
+  OPT_LARS_SGD = 5,
+  OPT_LAMB = 6,
+  OPT_PARTIAL_ROWWISE_LAMB = 7,
+  OPT_DENSE_GRAD = 100,  // write the summed gradient into a dense buffer instead of updating
+};
+
+struct FwdParams {
+  const void* weights;
+  const int64_t* meta;  // [kMetaRows, F]
+  const void* indices;
+  const void* offsets;
+  const float* psw;  // per-sample weights or null
+  PeerPtrs out;      // output buffer on every destination rank
+  int out_dtype;
+  int64_t out_stride;  // elements per output row
+  int B;               // bags per feature handled here
+  int B_local;         // bags per feature per destination rank
+  int F;
+  int pooling;
+  int accumulate;  // 1: add fp32 partial sums into the destination (row-wise reduce-scatter)
+  int skip_empty;  // 1: do not touch the destination for an empty bag (accumulate mode)
+  int* err;
+};
+
+template <typename emb_t, typename idx_t, int kVecs>
+__global__ void __launch_bounds__(256) tbe_fwd_kernel(FwdParams p) {
+  constexpr int kUnroll = kVecs <= 2 ? 4 : (kVecs == 4 ? 2 : 1);
+  const int lane = threadIdx.x & 31;
+  const int64_t bag = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nbags = int64_t(p.F) * p.B;
+  if (bag >= nbags) return;
+  const int f = int(bag / p.B);
+  const int b = int(bag - int64_t(f) * p.B);
+  const idx_t* offsets = reinterpret_cast<const idx_t*>(p.offsets);
+  const idx_t* indices = reinterpret_cast<const idx_t*>(p.indices);
+  const int64_t start = offsets[bag], end = offsets[bag + 1];
+  const int F = p.F;
+  const int D = int(p.meta[M_DIM * F + f]);
+  const int64_t rows = p.meta[M_ROWS * F + f];
+  const emb_t* w = reinterpret_cast<const emb_t*>(p.weights) + p.meta[M_WOFF * F + f];
+  const int out_off = int(p.meta[M_OUTOFF * F + f]);
+
+  float4 acc[kVecs];
+#pragma unroll
+  for (int v = 0; v < kVecs; ++v) acc[v] = f4zero();
+
+  for (int64_t i0 = start; i0 < end; i0 += 32) {
+    const int cnt = int(min(int64_t(32), end - i0));
+    int64_t my_idx = 0;
+    float my_w = 0.f;
+    if (lane < cnt) {
+      my_idx = int64_t(indices[i0 + lane]);
+      my_w = p.psw ? p.psw[i0 + lane] : 1.f;
+      if (my_idx < 0 || my_idx >= rows) {
+        atomicExch(p.err, 1);
+        my_idx = 0;
+        my_w = 0.f;
+      }
+    }
+    for (int j = 0; j < cnt; j += kUnroll) {
+      int64_t r[kUnroll];
+      float ww[kUnroll];
+      float4 v[kUnroll][kVecs];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int src = min(j + u, cnt - 1);
+        r[u] = __shfl_sync(0xffffffffu, my_idx, src);
+        ww[u] = __shfl_sync(0xffffffffu, my_w, src);
+        if (j + u >= cnt) ww[u] = 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+#pragma unroll
+        for (int vv = 0; vv < kVecs; ++vv) {
+          const int e = vv * 128 + lane * 4;
+          v[u][vv] = (e < D) ? Vec4<emb_t>::load(w + r[u] * D + e) : f4zero();
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+#pragma unroll
+        for (int vv = 0; vv < kVecs; ++vv) {
+          acc[vv].x = fmaf(ww[u], v[u][vv].x, acc[vv].x);
+          acc[vv].y = fmaf(ww[u], v[u][vv].y, acc[vv].y);
+          acc[vv].z = fmaf(ww[u], v[u][vv].z, acc[vv].z);
+          acc[vv].w = fmaf(ww[u], v[u][vv].w, acc[vv].w);
+        }
+      }
+    }
+  }
+  if (p.pooling == POOL_MEAN && end > start) {
+    const float s = 1.f / float(end - start);
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+      acc[v].x *= s; acc[v].y *= s; acc[v].z *= s; acc[v].w *= s;
+    }
+  }
+  if (p.accumulate && p.skip_empty && end == start) return;
+  const int dst = b / p.B_local;
+  const int bl = b - dst * p.B_local;
+  void* base = p.out.p[dst];
+  const int64_t row_e = int64_t(bl) * p.out_stride + out_off;
+#pragma unroll
+  for (int v = 0; v < kVecs; ++v) {
+    const int e = v * 128 + lane * 4;
+    if (e < D) {
+      if (p.accumulate) {
+        red_add_f32x4(reinterpret_cast<float*>(base) + row_e + e, acc[v]);
+      } else {
+        store4_dyn(base, row_e + e, acc[v], p.out_dtype);
+      }
+    }
+  }
+}
+
+// unpooled: out[i, :] = W[idx_i]; one warp per bag, rows stored at the position of the id
+template <typename emb_t, typename idx_t, int kVecs>
+__global__ void __launch_bounds__(256) tbe_seq_fwd_kernel(FwdParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t bag = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nbags = int64_t(p.F) * p.B;
+  if (bag >= nbags) return;
+  const int f = int(bag / p.B);
+  const idx_t* offsets = reinterpret_cast<const idx_t*>(p.offsets);
+  const idx_t* indices = reinterpret_cast<const idx_t*>(p.indices);
+  const int64_t start = offsets[bag], end = offsets[bag + 1];
+  const int F = p.F;
+  const int D = int(p.meta[M_DIM * F + f]);
+  const int64_t rows = p.meta[M_ROWS * F + f];
+  const emb_t* w = reinterpret_cast<const emb_t*>(p.weights) + p.meta[M_WOFF * F + f];
+  void* base = p.out.p[0];
+  for (int64_t i0 = start; i0 < end; i0 += 32) {
+    const int cnt = int(min(int64_t(32), end - i0));
+    int64_t my_idx = 0;
+    bool ok = true;
+    if (lane < cnt) {
+      my_idx = int64_t(indices[i0 + lane]);
+      if (my_idx < 0 || my_idx >= rows) {
+        atomicExch(p.err, 1);
+        my_idx = 0;
+        ok = false;
+      }
+    }
+    for (int j = 0; j < cnt; ++j) {
+      const int64_t r = __shfl_sync(0xffffffffu, my_idx, j);
+      const bool rok = __shfl_sync(0xffffffffu, int(ok), j);
+#pragma unroll
+      for (int v = 0; v < kVecs; ++v) {
+        const int e = v * 128 + lane * 4;
+        if (e < D) {
+          float4 x = rok ? Vec4<emb_t>::load(w + r * D + e) : f4zero();
+          store4_dyn(base, (i0 + j) * p.out_stride + e, x, p.out_dtype);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward
+// ------------------------------------------------------------------------------------------------
+struct OptParams {
+  int type;
+  float lr, eps, beta1, beta2, weight_decay;
+  float bias_corr1, bias_corr2;  // 1 - beta^t
+  float max_grad;                // > 0: clamp the summed gradient elementwise
+};
+
+struct BwdParams {
+  void* weights;
+  float* mom1;
+  float* mom2;
+  float* dense_grad;    // OPT_DENSE_GRAD target (same layout as weights, fp32)
+  const int64_t* meta;  // [kMetaRows, F]
+  const int64_t* sorted_keys;  // [N] global row ids, ascending
+  const int32_t* sorted_src;   // [N] pooled: bag id (f*B+b); unpooled: position of the id
+  const float* sorted_w;       // [N] per-sample weights in sorted order, or null
+  const int32_t* src_feature;  // unpooled only: feature of every position (null when pooled)
+  const void* grad;            // upstream gradient rows
+  int grad_dtype;
+  int64_t grad_stride;
+  const float* bag_scale;  // mean pooling: 1/len per bag, or null
+  int64_t N;
+  int B;
+  int F;
+  int pooled;
+  float* partials;  // [2*nblocks, Dpad] fp32 scratch
+  int32_t* flags;   // [2*nblocks]  slot state, see below
+  int Dpad;
+  OptParams opt;
+};
+
+constexpr int kBlk = 64;        // sorted entries per warp
+constexpr int FLAG_USED = 1;    // slot holds a partial sum
+constexpr int FLAG_CONT = 2;    // (slot A only) the row continues into the next block
+
+template <typename emb_t, int kVecs>
+__device__ __forceinline__ void apply_update(const BwdParams& p, int64_t key, int f, float4 (&g)[kVecs], int lane) {
+  const int F = p.F;
+  const int D = int(p.meta[M_DIM * F + f]);
+  const int64_t row = key - p.meta[M_HASHOFF * F + f];
+  const int64_t woff = p.meta[M_WOFF * F + f] + row * D;
+  const OptParams& o = p.opt;
+  if (o.max_grad > 0.f) {
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+      g[v].x = fminf(fmaxf(g[v].x, -o.max_grad), o.max_grad);
+      g[v].y = fminf(fmaxf(g[v].y, -o.max_grad), o.max_grad);
+      g[v].z = fminf(fmaxf(g[v].z, -o.max_grad), o.max_grad);
+      g[v].w = fminf(fmaxf(g[v].w, -o.max_grad), o.max_grad);
+    }
+  }
+  if (o.type == OPT_DENSE_GRAD) {
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+      const int e = v * 128 + lane * 4;
+      if (e < D) Vec4<float>::store(p.dense_grad + woff + e, g[v]);
+    }
+    return;
+  }
+  emb_t* wp = reinterpret_cast<emb_t*>(p.weights) + woff;
+  float4 w[kVecs];
+#pragma unroll
+  for (int v = 0; v < kVecs; ++v) {
+    const int e = v * 128 + lane * 4;
+    w[v] = (e < D) ? Vec4<emb_t>::load_plain(wp + e) : f4zero();
+  }
+  if (o.weight_decay != 0.f && o.type != OPT_LAMB && o.type != OPT_PARTIAL_ROWWISE_LAMB) {
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+      g[v].x = fmaf(o.weight_decay, w[v].x, g[v].x);
+      g[v].y = fmaf(o.weight_decay, w[v].y, g[v].y);
+      g[v].z = fmaf(o.weight_decay, w[v].z, g[v].z);
+      g[v].w = fmaf(o.weight_decay, w[v].w, g[v].w);
+    }
+  }
+  auto sumsq = [&](float4 (&x)[kVecs]) {
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) s += x[v].x * x[v].x + x[v].y * x[v].y + x[v].z * x[v].z + x[v].w * x[v].w;
+    return warp_sum(s);
+  };
+  switch (o.type) {
+    case OPT_SGD: {
+#pragma unroll
+      for (int v = 0; v < kVecs; ++v) {
+        w[v].x -= o.lr * g[v].x; w[v].y -= o.lr * g[v].y; w[v].z -= o.lr * g[v].z; w[v].w -= o.lr * g[v].w;
+      }
+      break;
+    }
+    case OPT_LARS_SGD: {
+      const float wn = sqrtf(sumsq(w)), gn = sqrtf(sumsq(g));
+      const float trust = (wn > 0.f && gn > 0.f) ? o.eps * wn / gn : 1.f;  // eps field carries eta
+      const float s = o.lr * trust;
+#pragma unroll
+      for (int v = 0; v < kVecs; ++v) {
+        w[v].x -= s * g[v].x; w[v].y -= s * g[v].y; w[v].z -= s * g[v].z; w[v].w -= s * g[v].w;
+      }
+      break;
+    }
+    case OPT_ROWWISE_ADAGRAD: {
+      const float g2 = sumsq(g) / float(D);
+      float m = 0.f;
+      if (lane == 0) {
+        m = p.mom1[key] + g2;
+        p.mom1[key] = m;
+      }
+      m = __shfl_sync(0xffffffffu, m, 0);
+      const float s = o.lr / (sqrtf(m) + o.eps);
+#pragma unroll
+      for (int v = 0; v < kVecs; ++v) {
+        w[v].x -= s * g[v].x; w[v].y -= s * g[v].y; w[v].z -= s * g[v].z; w[v].w -= s * g[v].w;
+      }
+      break;
+    }
+    case OPT_ADAGRAD: {
+#pragma unroll
+      for (int v = 0; v < kVecs; ++v) {
+        const int e = v * 128 + lane * 4;
+        if (e < D) {
+          float4 m = Vec4<float>::load_plain(p.mom1 + woff + e);
+          m.x += g[v].x * g[v].x; m.y += g[v].y * g[v].y; m.z += g[v].z * g[v].z; m.w += g[v].w * g[v].w;
+          Vec4<float>::store(p.mom1 + woff + e, m);
+          w[v].x -= o.lr * g[v].x / (sqrtf(m.x) + o.eps);
+          w[v].y -= o.lr * g[v].y / (sqrtf(m.y) + o.eps);
+          w[v].z -= o.lr * g[v].z / (sqrtf(m.z) + o.eps);
+          w[v].w -= o.lr * g[v].w / (sqrtf(m.w) + o.eps);
+        }
+      }
+      break;
+    }
+    case OPT_ADAM:
+    case OPT_PARTIAL_ROWWISE_ADAM:
+    case OPT_LAMB:
+    case OPT_PARTIAL_ROWWISE_LAMB: {
+      const bool rowwise2 = (o.type == OPT_PARTIAL_ROWWISE_ADAM || o.type == OPT_PARTIAL_ROWWISE_LAMB);
+      const bool lamb = (o.type == OPT_LAMB || o.type == OPT_PARTIAL_ROWWISE_LAMB);
+      float m2row = 0.f;
+      if (rowwise2) {
+        const float g2 = sumsq(g) / float(D);
+        if (lane == 0) {
+          m2row = o.beta2 * p.mom2[key] + (1.f - o.beta2) * g2;
+          p.mom2[key] = m2row;
+        }
+        m2row = __shfl_sync(0xffffffffu, m2row, 0);
+      }
+      float4 upd[kVecs];
+#pragma unroll
+      for (int v = 0; v < kVecs; ++v) {
+        const int e = v * 128 + lane * 4;
+        upd[v] = f4zero();
+        if (e < D) {
+          float4 m1 = Vec4<float>::load_plain(p.mom1 + woff + e);
+          m1.x = o.beta1 * m1.x + (1.f - o.beta1) * g[v].x;
+          m1.y = o.beta1 * m1.y + (1.f - o.beta1) * g[v].y;
+          m1.z = o.beta1 * m1.z + (1.f - o.beta1) * g[v].z;
+          m1.w = o.beta1 * m1.w + (1.f - o.beta1) * g[v].w;
+          Vec4<float>::store(p.mom1 + woff + e, m1);
+          float4 m2;
+          if (rowwise2) {
+            m2 = make_float4(m2row, m2row, m2row, m2row);
+          } else {
+            m2 = Vec4<float>::load_plain(p.mom2 + woff + e);
+            m2.x = o.beta2 * m2.x + (1.f - o.beta2) * g[v].x * g[v].x;
+            m2.y = o.beta2 * m2.y + (1.f - o.beta2) * g[v].y * g[v].y;
+            m2.z = o.beta2 * m2.z + (1.f - o.beta2) * g[v].z * g[v].z;
+            m2.w = o.beta2 * m2.w + (1.f - o.beta2) * g[v].w * g[v].w;
+            Vec4<float>::store(p.mom2 + woff + e, m2);
+          }
+          const float c1 = 1.f / o.bias_corr1, c2 = 1.f / o.bias_corr2;
+          upd[v].x = (m1.x * c1) / (sqrtf(m2.x * c2) + o.eps);
+          upd[v].y = (m1.y * c1) / (sqrtf(m2.y * c2) + o.eps);
+          upd[v].z = (m1.z * c1) / (sqrtf(m2.z * c2) + o.eps);
+          upd[v].w = (m1.w * c1) / (sqrtf(m2.w * c2) + o.eps);
+          if (lamb && o.weight_decay != 0.f) {
+            upd[v].x = fmaf(o.weight_decay, w[v].x, upd[v].x);
+            upd[v].y = fmaf(o.weight_decay, w[v].y, upd[v].y);
+            upd[v].z = fmaf(o.weight_decay, w[v].z, upd[v].z);
+            upd[v].w = fmaf(o.weight_decay, w[v].w, upd[v].w);
+          }
+        }
+      }
+      float s = o.lr;
+      if (lamb) {
+        const float wn = sqrtf(sumsq(w)), un = sqrtf(sumsq(upd));
+        if (wn > 0.f && un > 0.f) s = o.lr * wn / un;
+      }
+#pragma unroll
+      for (int v = 0; v < kVecs; ++v) {
+        w[v].x -= s * upd[v].x; w[v].y -= s * upd[v].y; w[v].z -= s * upd[v].z; w[v].w -= s * upd[v].w;
+      }
+      break;
+    }
+    default:
+      break;
+  }
+#pragma unroll
+  for (int v = 0; v < kVecs; ++v) {
+    const int e = v * 128 + lane * 4;
+    if (e < D) Vec4<emb_t>::store(wp + e, w[v]);
+  }
+}
+
+template <int kVecs>
+__device__ __forceinline__ void store_partial(const BwdParams& p, int64_t slot, float4 (&g)[kVecs], int lane) {
+  float* dst = p.partials + slot * p.Dpad;
+#pragma unroll
+  for (int v = 0; v < kVecs; ++v) {
+    const int e = v * 128 + lane * 4;
+    if (e < p.Dpad) Vec4<float>::store(dst + e, g[v]);
+  }
+}
+
+// pass 1: one warp per block of kBlk sorted entries
+template <typename emb_t, int kVecs>
+__global__ void __launch_bounds__(256) tbe_bwd_block_kernel(BwdParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t blk = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t start = blk * kBlk;
+  if (start >= p.N) return;
+  const int64_t end = min(p.N, start + kBlk);
+  const int F = p.F;
+
+  if (lane == 0) {
+    p.flags[2 * blk] = 0;
+    p.flags[2 * blk + 1] = 0;
+  }
+  float4 acc[kVecs];
+#pragma unroll
+  for (int v = 0; v < kVecs; ++v) acc[v] = f4zero();
+
+  int64_t cur_key = p.sorted_keys[start];
+  bool started_before = (start > 0) && (p.sorted_keys[start - 1] == cur_key);
+  int cur_f = 0;
+
+  for (int64_t i0 = start; i0 < end; i0 += 32) {
+    const int cnt = int(min(int64_t(32), end - i0));
+    int64_t my_key = 0;
+    int my_src = 0;
+    float my_w = 1.f;
+    int my_f = 0;
+    int64_t my_goff = 0;  // element offset of this entry's gradient row slice
+    if (lane < cnt) {
+      my_key = p.sorted_keys[i0 + lane];
+      my_src = p.sorted_src[i0 + lane];
+      if (p.sorted_w) my_w = p.sorted_w[i0 + lane];
+      if (p.pooled) {
+        my_f = my_src / p.B;
+        const int b = my_src - my_f * p.B;
+        my_goff = int64_t(b) * p.grad_stride + p.meta[M_OUTOFF * F + my_f];
+        if (p.bag_scale) my_w *= p.bag_scale[my_src];
+      } else {
+        my_f = p.src_feature[my_src];
+        my_goff = int64_t(my_src) * p.grad_stride;
+      }
+    }
+    constexpr int kUnroll = kVecs <= 2 ? 4 : 1;
+    for (int j = 0; j < cnt; j += kUnroll) {
+      float4 gv[kUnroll][kVecs];
+      int64_t kk[kUnroll];
+      float ww[kUnroll];
+      int ff[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int src = min(j + u, cnt - 1);
+        kk[u] = __shfl_sync(0xffffffffu, my_key, src);
+        ww[u] = __shfl_sync(0xffffffffu, my_w, src);
+        ff[u] = __shfl_sync(0xffffffffu, my_f, src);
+        const int64_t goff = __shfl_sync(0xffffffffu, my_goff, src);
+        const int D = int(p.meta[M_DIM * F + ff[u]]);
+#pragma unroll
+        for (int v = 0; v < kVecs; ++v) {
+          const int e = v * 128 + lane * 4;
+          gv[u][v] = (e < D) ? load4_dyn(p.grad, goff + e, p.grad_dtype) : f4zero();
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (j + u < cnt) {
+          if (kk[u] != cur_key) {
+            // the current row ends here
+            if (!started_before) {
+              apply_update<emb_t, kVecs>(p, cur_key, cur_f, acc, lane);
+            } else {
+              store_partial<kVecs>(p, 2 * blk, acc, lane);
+              if (lane == 0) p.flags[2 * blk] = FLAG_USED;
+            }
+#pragma unroll
+            for (int v = 0; v < kVecs; ++v) acc[v] = f4zero();
+            cur_key = kk[u];
+            started_before = false;
+          }
+          cur_f = ff[u];
+#pragma unroll
+          for (int v = 0; v < kVecs; ++v) {
+            acc[v].x = fmaf(ww[u], gv[u][v].x, acc[v].x);
+            acc[v].y = fmaf(ww[u], gv[u][v].y, acc[v].y);
+            acc[v].z = fmaf(ww[u], gv[u][v].z, acc[v].z);
+            acc[v].w = fmaf(ww[u], gv[u][v].w, acc[v].w);
+          }
+        }
+      }
+    }
+  }
+  const bool continues = (end < p.N) && (p.sorted_keys[end] == cur_key);
+  if (!started_before && !continues) {
+    apply_update<emb_t, kVecs>(p, cur_key, cur_f, acc, lane);
+  } else if (started_before) {
+    // middle or tail of a long row: slot A
+    store_partial<kVecs>(p, 2 * blk, acc, lane);
+    if (lane == 0) p.flags[2 * blk] = FLAG_USED | (continues ? FLAG_CONT : 0);
+  } else {
+    // head of a long row: slot B; remember the feature for the second pass
+    store_partial<kVecs>(p, 2 * blk + 1, acc, lane);
+    if (lane == 0) p.flags[2 * blk + 1] = FLAG_USED | (cur_f << 8);
+  }
+}
+
+// pass 2: the head block of every row that spans blocks folds the chain of partial sums
+template <typename emb_t, int kVecs>
+__global__ void __launch_bounds__(256) tbe_bwd_long_kernel(BwdParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t blk = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nblocks = (p.N + kBlk - 1) / kBlk;
+  if (blk >= nblocks) return;
+  const int fl = p.flags[2 * blk + 1];
+  if (!(fl & FLAG_USED)) return;
+  const int f = fl >> 8;
+  const int64_t end = min(p.N, (blk + 1) * kBlk);
+  const int64_t key = p.sorted_keys[end - 1];
+  float4 acc[kVecs];
+  {
+    const float* src = p.partials + (2 * blk + 1) * p.Dpad;
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+      const int e = v * 128 + lane * 4;
+      acc[v] = (e < p.Dpad) ? Vec4<float>::load_plain(src + e) : f4zero();
+    }
+  }
+  for (int64_t j = blk + 1; j < nblocks; ++j) {
+    const int fa = p.flags[2 * j];
+    if (!(fa & FLAG_USED)) break;  // defensive: chain must exist
+    const float* src = p.partials + (2 * j) * p.Dpad;
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+      const int e = v * 128 + lane * 4;
+      if (e < p.Dpad) {
+        float4 x = Vec4<float>::load_plain(src + e);
+        acc[v].x += x.x; acc[v].y += x.y; acc[v].z += x.z; acc[v].w += x.w;
+      }
+    }
+    if (!(fa & FLAG_CONT)) break;
+  }
+  apply_update<emb_t, kVecs>(p, key, f, acc, lane);
+}
+
+// keys: global row id of every id; src: bag id (pooled) or position (unpooled)
+template <typename idx_t>
+__global__ void __launch_bounds__(256) tbe_linearize_kernel(
+    const idx_t* __restrict__ indices, const idx_t* __restrict__ offsets, const int64_t* __restrict__ meta, int F, int B,
+    int pooled, int64_t* __restrict__ keys, int32_t* __restrict__ src, int32_t* __restrict__ src_feature,
+    float* __restrict__ bag_scale, int* err) {
+  const int lane = threadIdx.x & 31;
+  const int64_t bag = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (bag >= int64_t(F) * B) return;
+  const int f = int(bag / B);
+  const int64_t start = offsets[bag], end = offsets[bag + 1];
+  const int64_t hoff = meta[M_HASHOFF * F + f];
+  const int64_t rows = meta[M_ROWS * F + f];
+  if (bag_scale && lane == 0) bag_scale[bag] = end > start ? 1.f / float(end - start) : 0.f;
+  for (int64_t i = start + lane; i < end; i += 32) {
+    int64_t r = int64_t(indices[i]);
+    if (r < 0 || r >= rows) {
+      atomicExch(err, 1);
+      r = 0;
+    }
+    keys[i] = hoff + r;
+    src[i] = pooled ? int32_t(bag) : int32_t(i);
+    if (src_feature) src_feature[i] = f;
+  }
+}
+
+__global__ void gather_sorted_weights_kernel(const float* __restrict__ psw, const int32_t* __restrict__ sorted_pos,
+                                             const int32_t* __restrict__ bag_of_pos, float* __restrict__ out_w,
+                                             int32_t* __restrict__ out_src, int64_t N) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= N) return;
+  const int32_t pos = sorted_pos[i];
+  out_w[i] = psw[pos];
+  out_src[i] = bag_of_pos ? bag_of_pos[pos] : pos;
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+static int out_dtype_code(at::ScalarType t) {
+  switch (t) {
+    case at::kFloat: return OUT_F32;
+    case at::kHalf: return OUT_F16;
+    case at::kBFloat16: return OUT_BF16;
+    default: TORCH_CHECK(false, "unsupported dtype ", t);
+  }
+}
+
+static int vecs_for_dim(int64_t max_D) {
+  TORCH_CHECK(max_D % 4 == 0, "embedding dims must be multiples of 4");
+  if (max_D <= 128) return 1;
+  if (max_D <= 256) return 2;
+  if (max_D <= 512) return 4;
+  TORCH_CHECK(max_D <= 1024, "embedding dims above 1024 are not supported");
+  return 8;
+}
+
+#define TRB_DISPATCH_EMB(TYPE, ...)                                   \
+  [&] {                                                               \
+    if (TYPE == at::kFloat) { using emb_t = float; __VA_ARGS__(); }   \
+    else if (TYPE == at::kHalf) { using emb_t = __half; __VA_ARGS__(); } \
+    else if (TYPE == at::kBFloat16) { using emb_t = __nv_bfloat16; __VA_ARGS__(); } \
+    else TORCH_CHECK(false, "unsupported weights dtype");             \
+  }()
+
+#define TRB_DISPATCH_VECS(NV, ...)                                    \
+  [&] {                                                               \
+    if (NV == 1) { constexpr int kVecs = 1; __VA_ARGS__(); }          \
+    else if (NV == 2) { constexpr int kVecs = 2; __VA_ARGS__(); }     \
+    else if (NV == 4) { constexpr int kVecs = 4; __VA_ARGS__(); }     \
+    else { constexpr int kVecs = 8; __VA_ARGS__(); }                  \
+  }()
+
+// out_ptrs: int64 CPU tensor [W] of device pointers (one per destination rank), or empty -> `out`.
+void tbe_forward_impl(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices,
+                      const at::Tensor& offsets, const c10::optional<at::Tensor>& psw, at::Tensor& out,
+                      const std::vector<int64_t>& out_ptrs, int64_t out_dtype, int64_t out_stride, int64_t B,
+                      int64_t B_local, int64_t max_D, int64_t pooling, bool accumulate, bool skip_empty,
+                      at::Tensor& err) {
+  const int F = int(meta.size(1));
+  TORCH_CHECK(meta.size(0) == kMetaRows && meta.scalar_type() == at::kLong && meta.is_contiguous());
+  TORCH_CHECK(indices.scalar_type() == offsets.scalar_type(), "indices and offsets must share a dtype");
+  TORCH_CHECK(offsets.numel() == int64_t(F) * B + 1, "offsets must have F*B+1 entries");
+  if (F == 0 || B == 0) return;
+  c10::cuda::CUDAGuard guard(weights.device());
+  FwdParams p;
+  p.weights = weights.data_ptr();
+  p.meta = meta.data_ptr<int64_t>();
+  p.indices = indices.data_ptr();
+  p.offsets = offsets.data_ptr();
+  p.psw = psw.has_value() && psw->defined() ? psw->data_ptr<float>() : nullptr;
+  if (out_ptrs.empty()) {
+    p.out.p[0] = out.data_ptr();
+    TORCH_CHECK(B_local == B);
+  } else {
+    TORCH_CHECK(out_ptrs.size() <= size_t(kMaxPeers));
+    TORCH_CHECK(int64_t(out_ptrs.size()) * B_local >= B);
+    for (size_t i = 0; i < out_ptrs.size(); ++i) p.out.p[i] = reinterpret_cast<void*>(out_ptrs[i]);
+  }
+  p.out_dtype = int(out_dtype);
+  p.out_stride = out_stride;
+  p.B = int(B);
+  p.B_local = int(B_local);
+  p.F = F;
+  p.pooling = int(pooling);
+  p.accumulate = accumulate ? 1 : 0;
+  p.skip_empty = skip_empty ? 1 : 0;
+  p.err = err.data_ptr<int>();
+  TORCH_CHECK(!accumulate || out_dtype == OUT_F32, "accumulate mode needs an fp32 destination");
+  const int64_t nbags = int64_t(F) * B;
+  const int threads = 256;
+  const int64_t blocks = (nbags * 32 + threads - 1) / threads;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int nv = vecs_for_dim(max_D);
+  const bool i64 = indices.scalar_type() == at::kLong;
+  TORCH_CHECK(i64 || indices.scalar_type() == at::kInt, "indices must be int32 or int64");
+  TRB_DISPATCH_EMB(weights.scalar_type(), [&] {
+    TRB_DISPATCH_VECS(nv, [&] {
+      if (pooling == POOL_NONE) {
+        if (i64) tbe_seq_fwd_kernel<emb_t, int64_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+        else tbe_seq_fwd_kernel<emb_t, int32_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+      } else {
+        if (i64) tbe_fwd_kernel<emb_t, int64_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+        else tbe_fwd_kernel<emb_t, int32_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+      }
+    });
+  });
+  TRB_CUDA_CHECK(cudaGetLastError());
+}
+
+at::Tensor tbe_forward(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices,
+                       const at::Tensor& offsets, const c10::optional<at::Tensor>& psw, int64_t B, int64_t total_D,
+                       int64_t max_D, int64_t pooling, int64_t out_dtype, at::Tensor err) {
+  auto dt = out_dtype == OUT_F32 ? at::kFloat : (out_dtype == OUT_F16 ? at::kHalf : at::kBFloat16);
+  at::Tensor out;
+  if (pooling == POOL_NONE) {
+    out = at::empty({indices.numel(), max_D}, weights.options().dtype(dt));
+    tbe_forward_impl(weights, meta, indices, offsets, psw, out, {}, out_dtype, max_D, B, B, max_D, pooling, false,
+                     false, err);
+  } else {
+    out = at::empty({B, total_D}, weights.options().dtype(dt));
+    tbe_forward_impl(weights, meta, indices, offsets, psw, out, {}, out_dtype, total_D, B, B, max_D, pooling, false,
+                     false, err);
+  }
+  return out;
+}
+
+// Pooled forward whose destination rows live on peer ranks (fused lookup + all-to-all / reduce-scatter).
+void tbe_forward_dist(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices,
+                      const at::Tensor& offsets, const c10::optional<at::Tensor>& psw, std::vector<int64_t> out_ptrs,
+                      int64_t out_dtype, int64_t out_stride, int64_t B, int64_t B_local, int64_t max_D,
+                      int64_t pooling, bool accumulate, bool skip_empty, at::Tensor err) {
+  at::Tensor dummy;
+  tbe_forward_impl(weights, meta, indices, offsets, psw, dummy, out_ptrs, out_dtype, out_stride, B, B_local, max_D,
+                   pooling, accumulate, skip_empty, err);
+}
+
+struct SortedPlan {
+  at::Tensor keys, src, w, src_feature, bag_scale;
+};
+
+// Build the sorted (row -> contributing bags) plan for one batch.  It depends on the ids only, so a
+// pipeline may run it on a side stream while the dense towers of the previous step are still busy.
+std::vector<at::Tensor> tbe_build_plan(const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets,
+                                       const c10::optional<at::Tensor>& psw, int64_t B, int64_t total_rows,
+                                       bool pooled, bool mean_pooling, at::Tensor err) {
+  const int F = int(meta.size(1));
+  const int64_t N = indices.numel();
+  c10::cuda::CUDAGuard guard(indices.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  auto opts_i64 = indices.options().dtype(at::kLong);
+  auto opts_i32 = indices.options().dtype(at::kInt);
+  auto opts_f32 = indices.options().dtype(at::kFloat);
+  at::Tensor keys = at::empty({N}, opts_i64), src = at::empty({N}, opts_i32);
+  at::Tensor src_feature = pooled ? at::Tensor() : at::empty({N}, opts_i32);
+  at::Tensor bag_scale = (pooled && mean_pooling) ? at::empty({int64_t(F) * B}, opts_f32) : at::Tensor();
+  const bool weighted = psw.has_value() && psw->defined();
+  at::Tensor pos;  // weighted: sort positions, then gather weights
+  if (N > 0 && F > 0 && B > 0) {
+    const int threads = 256;
+    const int64_t blocks = (int64_t(F) * B * 32 + threads - 1) / threads;
+    const bool i64 = indices.scalar_type() == at::kLong;
+    // weighted path keeps bag ids aside and sorts positions instead
+    at::Tensor bag_of_pos;
+    int32_t* src_ptr = src.data_ptr<int32_t>();
+    if (weighted && pooled) {
+      bag_of_pos = at::empty({N}, opts_i32);
+      src_ptr = bag_of_pos.data_ptr<int32_t>();
+    }
+    if (i64) {
+      tbe_linearize_kernel<int64_t><<<blocks, threads, 0, stream>>>(
+          indices.data_ptr<int64_t>(), offsets.data_ptr<int64_t>(), meta.data_ptr<int64_t>(), F, int(B), pooled ? 1 : 0,
+          keys.data_ptr<int64_t>(), src_ptr, pooled ? nullptr : src_feature.data_ptr<int32_t>(),
+          bag_scale.defined() ? bag_scale.data_ptr<float>() : nullptr, err.data_ptr<int>());
+    } else {
+      tbe_linearize_kernel<int32_t><<<blocks, threads, 0, stream>>>(
+          indices.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), meta.data_ptr<int64_t>(), F, int(B), pooled ? 1 : 0,
+          keys.data_ptr<int64_t>(), src_ptr, pooled ? nullptr : src_feature.data_ptr<int32_t>(),
+          bag_scale.defined() ? bag_scale.data_ptr<float>() : nullptr, err.data_ptr<int>());
+    }
+    TRB_CUDA_CHECK(cudaGetLastError());
+    at::Tensor vals_in = src;
+    if (weighted) {
+      vals_in = at::arange(N, opts_i32);
+    }
+    at::Tensor keys_out = at::empty({N}, opts_i64), vals_out = at::empty({N}, opts_i32);
+    int end_bit = 1;
+    while ((int64_t(1) << end_bit) < total_rows && end_bit < 63) ++end_bit;
+    size_t tmp_bytes = 0;
+    cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, keys.data_ptr<int64_t>(), keys_out.data_ptr<int64_t>(),
+                                    vals_in.data_ptr<int32_t>(), vals_out.data_ptr<int32_t>(), N, 0, end_bit, stream);
+    at::Tensor tmp = at::empty({int64_t(tmp_bytes)}, indices.options().dtype(at::kByte));
+    cub::DeviceRadixSort::SortPairs(tmp.data_ptr(), tmp_bytes, keys.data_ptr<int64_t>(), keys_out.data_ptr<int64_t>(),
+                                    vals_in.data_ptr<int32_t>(), vals_out.data_ptr<int32_t>(), N, 0, end_bit, stream);
+    keys = keys_out;
+    at::Tensor w_sorted;
+    if (weighted) {
+      w_sorted = at::empty({N}, opts_f32);
+      at::Tensor src_sorted = at::empty({N}, opts_i32);
+      const int64_t gb = (N + 255) / 256;
+      gather_sorted_weights_kernel<<<gb, 256, 0, stream>>>(
+          psw->data_ptr<float>(), vals_out.data_ptr<int32_t>(), pooled ? bag_of_pos.data_ptr<int32_t>() : nullptr,
+          w_sorted.data_ptr<float>(), src_sorted.data_ptr<int32_t>(), N);
+      TRB_CUDA_CHECK(cudaGetLastError());
+      src = src_sorted;
+    } else {
+      src = vals_out;
+    }
+    return {keys, src, w_sorted.defined() ? w_sorted : at::empty({0}, opts_f32),
+            src_feature.defined() ? src_feature : at::empty({0}, opts_i32),
+            bag_scale.defined() ? bag_scale : at::empty({0}, opts_f32)};
+  }
+  return {keys, src, at::empty({0}, opts_f32), src_feature.defined() ? src_feature : at::empty({0}, opts_i32),
+          bag_scale.defined() ? bag_scale : at::empty({0}, opts_f32)};
+}
+
+// Apply the sorted plan: segment-reduce upstream gradient rows per table row and update in place.
+void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10::optional<at::Tensor> mom2,
+                        c10::optional<at::Tensor> dense_grad, const at::Tensor& meta, const at::Tensor& sorted_keys,
+                        const at::Tensor& sorted_src, const at::Tensor& sorted_w, const at::Tensor& src_feature,
+                        const at::Tensor& bag_scale, const at::Tensor& grad, int64_t grad_stride, int64_t B,
+                        int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
+                        double beta2, double weight_decay, int64_t step, double max_grad) {
+  const int64_t N = sorted_keys.numel();
+  if (N == 0) return;
+  c10::cuda::CUDAGuard guard(weights.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int F = int(meta.size(1));
+  const int nv = vecs_for_dim(max_D);
+  const int Dpad = int(max_D);
+  const int64_t nblocks = (N + kBlk - 1) / kBlk;
+  at::Tensor partials = at::empty({2 * nblocks * Dpad}, weights.options().dtype(at::kFloat));
+  at::Tensor flags = at::empty({2 * nblocks}, weights.options().dtype(at::kInt));
+  BwdParams p;
+  p.weights = weights.data_ptr();
+  p.mom1 = mom1.has_value() && mom1->defined() ? mom1->data_ptr<float>() : nullptr;
+  p.mom2 = mom2.has_value() && mom2->defined() ? mom2->data_ptr<float>() : nullptr;
+  p.dense_grad = dense_grad.has_value() && dense_grad->defined() ? dense_grad->data_ptr<float>() : nullptr;
+  p.meta = meta.data_ptr<int64_t>();
+  p.sorted_keys = sorted_keys.data_ptr<int64_t>();
+  p.sorted_src = sorted_src.data_ptr<int32_t>();
+  p.sorted_w = sorted_w.numel() > 0 ? sorted_w.data_ptr<float>() : nullptr;
+  p.src_feature = src_feature.numel() > 0 ? src_feature.data_ptr<int32_t>() : nullptr;
+  p.grad = grad.data_ptr();
+  p.grad_dtype = out_dtype_code(grad.scalar_type());
+  p.grad_stride = grad_stride;
+  p.bag_scale = bag_scale.numel() > 0 ? bag_scale.data_ptr<float>() : nullptr;
+  p.N = N;
+  p.B = int(B);
+  p.F = F;
+  p.pooled = pooled ? 1 : 0;
+  p.partials = partials.data_ptr<float>();
+  p.flags = flags.data_ptr<int32_t>();
+  p.Dpad = Dpad;
+  p.opt.type = int(opt_type);
+  p.opt.lr = float(lr);
+  p.opt.eps = float(eps);
+  p.opt.beta1 = float(beta1);
+  p.opt.beta2 = float(beta2);
+  p.opt.weight_decay = float(weight_decay);
+  p.opt.bias_corr1 = float(1.0 - std::pow(beta1, double(std::max<int64_t>(step, 1))));
+  p.opt.bias_corr2 = float(1.0 - std::pow(beta2, double(std::max<int64_t>(step, 1))));
+  p.opt.max_grad = float(max_grad);
+  TORCH_CHECK(pooled || p.src_feature != nullptr, "unpooled backward needs src_feature");
+  if (opt_type == OPT_DENSE_GRAD) TORCH_CHECK(p.dense_grad != nullptr);
+  const int threads = 256;
+  const int64_t blocks = (nblocks * 32 + threads - 1) / threads;
+  TRB_DISPATCH_EMB(weights.scalar_type(), [&] {
+    TRB_DISPATCH_VECS(nv, [&] {
+      tbe_bwd_block_kernel<emb_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+      tbe_bwd_long_kernel<emb_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+    });
+  });
+  TRB_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace trb
+
+TORCH_LIBRARY_FRAGMENT(trb200, m) {
+  m.def(
+      "tbe_forward(Tensor weights, Tensor meta, Tensor indices, Tensor offsets, Tensor? psw, int B, int total_D, "
+      "int max_D, int pooling, int out_dtype, Tensor(a!) err) -> Tensor");
+  m.def(
+      "tbe_forward_dist(Tensor weights, Tensor meta, Tensor indices, Tensor offsets, Tensor? psw, int[] out_ptrs, "
+      "int out_dtype, int out_stride, int B, int B_local, int max_D, int pooling, bool accumulate, bool skip_empty, "
+      "Tensor(a!) err) -> ()");
+  m.def(
+      "tbe_build_plan(Tensor meta, Tensor indices, Tensor offsets, Tensor? psw, int B, int total_rows, bool pooled, "
+      "bool mean_pooling, Tensor(a!) err) -> Tensor[]");
+  m.def(
+      "tbe_backward_apply(Tensor(a!) weights, Tensor(b!)? mom1, Tensor(c!)? mom2, Tensor(d!)? dense_grad, Tensor meta, "
+      "Tensor sorted_keys, Tensor sorted_src, Tensor sorted_w, Tensor src_feature, Tensor bag_scale, Tensor grad, "
+      "int grad_stride, int B, int max_D, bool pooled, int opt_type, float lr, float eps, float beta1, float beta2, "
+      "float weight_decay, int step, float max_grad) -> ()");
+}
+
+TORCH_LIBRARY_IMPL(trb200, CUDA, m) {
+  m.impl("tbe_forward", &trb::tbe_forward);
+  m.impl("tbe_build_plan", &trb::tbe_build_plan);
+  m.impl("tbe_backward_apply", &trb::tbe_backward_apply);
+}
+
+TORCH_LIBRARY_IMPL(trb200, CompositeExplicitAutograd, m) { m.impl("tbe_forward_dist", &trb::tbe_forward_dist); }

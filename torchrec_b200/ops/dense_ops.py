@@ -1,0 +1,285 @@
+"""Dense-tower operators: fused linear+bias+activation, low-rank cross layer, dot interaction, BCE.
+
+On CUDA the GEMMs run in bf16 with fp32 accumulation through the hand-written tcgen05 kernel
+(``torchrec_b200/csrc/cuda/gemm_tcgen05.cu``); parameters stay fp32 ("master" weights) and a bf16
+copy is refreshed once per optimizer step.  On CPU (or when the compute dtype is fp32) the same
+functions fall back to plain torch math, which is also the oracle the kernels are tested against.
+
+The reference runs these layers as ``nn.Linear`` / ``torch.bmm`` library calls
+(``torchrec/modules/mlp.py:61-80``, ``torchrec/modules/crossnet.py:178-181``,
+``torchrec/models/dlrm.py:216-219``).
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional, Tuple
+
+import torch
+
+from . import _ext
+
+ACT_NONE = 0
+ACT_RELU = 1
+ACT_SIGMOID = 2
+
+_COMPUTE_DTYPE: torch.dtype = torch.float32
+_GEMM_BACKEND = os.environ.get("TRB200_GEMM", "tcgen05")  # "tcgen05" | "cublas"
+
+
+def set_dense_compute_dtype(dtype: torch.dtype) -> None:
+    """Select the dtype of dense-tower GEMM operands on CUDA (fp32 -> plain torch, bf16 -> fused kernels)."""
+    global _COMPUTE_DTYPE
+    assert dtype in (torch.float32, torch.bfloat16)
+    _COMPUTE_DTYPE = dtype
+
+
+def get_dense_compute_dtype() -> torch.dtype:
+    return _COMPUTE_DTYPE
+
+
+def set_gemm_backend(name: str) -> None:
+    global _GEMM_BACKEND
+    assert name in ("tcgen05", "cublas")
+    _GEMM_BACKEND = name
+
+
+def get_gemm_backend() -> str:
+    return _GEMM_BACKEND
+
+
+def fused_dense_enabled(x: torch.Tensor) -> bool:
+    return x.is_cuda and _COMPUTE_DTYPE == torch.bfloat16
+
+
+# --------------------------------------------------------------------------------------
+# bf16 weight cache: one cast per parameter version, shared by forward and backward
+# --------------------------------------------------------------------------------------
+class _Bf16Cache:
+    def __init__(self) -> None:
+        self._store = {}
+
+    def get(self, p: torch.Tensor, transposed: bool = False) -> torch.Tensor:
+        key = (id(p), transposed)
+        ent = self._store.get(key)
+        ver = p._version
+        if ent is not None and ent[0] == ver and ent[1].device == p.device and ent[2] is p:
+            return ent[1]
+        src = p.detach()
+        t = (src.t().contiguous() if transposed else src).to(torch.bfloat16)
+        self._store[key] = (ver, t, p)
+        return t
+
+    def clear(self) -> None:
+        self._store.clear()
+
+
+bf16_cache = _Bf16Cache()
+
+
+# --------------------------------------------------------------------------------------
+# GEMM primitive: C[M,N] = A[M,K] @ B[N,K]^T  (both operands K-major), bf16 in, fp32 accumulate
+# --------------------------------------------------------------------------------------
+def gemm_nt(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    act: int = ACT_NONE,
+    out_dtype: torch.dtype = torch.bfloat16,
+) -> torch.Tensor:
+    """``act(a @ b.T + bias)`` with ``a [M,K]``, ``b [N,K]`` bf16 row-major."""
+    if a.is_cuda and _GEMM_BACKEND == "tcgen05" and _ext.has_cuda_ext() and _tcgen05_ok(a, b):
+        return torch.ops.trb200.gemm_nt_bf16(a, b, bias, act, out_dtype == torch.float32)
+    y = torch.matmul(a, b.t())
+    if bias is not None:
+        y = y + bias.to(y.dtype)
+    if act == ACT_RELU:
+        y = torch.relu(y)
+    elif act == ACT_SIGMOID:
+        y = torch.sigmoid(y)
+    return y.to(out_dtype)
+
+
+def _tcgen05_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
+    # TMA needs 16-byte aligned row pitches: K % 8 == 0 for bf16 operands, N % 8 == 0 for the output.
+    return (
+        a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_contiguous() and b.is_contiguous()
+        and a.shape[1] % 8 == 0 and b.shape[0] % 8 == 0 and a.shape[0] > 0
+    )
+
+
+class _LinearAct(torch.autograd.Function):
+    """y = act(x W^T + b) with bf16 GEMMs; saves bf16 activations only."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, act: int):
+        w16 = bf16_cache.get(weight)
+        x16 = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        y = gemm_nt(x16, w16, bias, act, torch.bfloat16)
+        ctx.act = act
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(x16, weight, y)
+        ctx.x_dtype = x.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, weight, y = ctx.saved_tensors
+        dy = dy.contiguous()
+        if dy.dtype != torch.bfloat16:
+            dy = dy.to(torch.bfloat16)
+        if ctx.act == ACT_RELU:
+            dz = act_backward(dy, y, ACT_RELU)
+        elif ctx.act == ACT_SIGMOID:
+            dz = act_backward(dy, y, ACT_SIGMOID)
+        else:
+            dz = dy
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            wT16 = bf16_cache.get(weight, transposed=True)  # [K, N]
+            dx = gemm_nt(dz, wT16, None, ACT_NONE, torch.bfloat16).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            dw = gemm_tn(dz, x16)  # [N, K] fp32
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dz.float().sum(0) if not dz.is_cuda or not _ext.has_cuda_ext() else torch.ops.trb200.colsum_bf16(dz)
+        return dx, dw, db, None
+
+
+def act_backward(dy: torch.Tensor, y: torch.Tensor, act: int) -> torch.Tensor:
+    if dy.is_cuda and _ext.has_cuda_ext():
+        return torch.ops.trb200.act_backward_bf16(dy, y, act)
+    if act == ACT_RELU:
+        return dy * (y > 0).to(dy.dtype)
+    yf = y.float()
+    return (dy.float() * yf * (1 - yf)).to(dy.dtype)
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a.T @ b`` with ``a [M,N]``, ``b [M,K]`` bf16 -> ``[N,K]`` fp32 (weight gradient)."""
+    if a.is_cuda and _GEMM_BACKEND == "tcgen05" and _ext.has_cuda_ext() and _tcgen05_tn_ok(a, b):
+        return torch.ops.trb200.gemm_tn_bf16(a, b)
+    return torch.matmul(a.t(), b).float()
+
+
+def _tcgen05_tn_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
+    return (
+        a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_contiguous() and b.is_contiguous()
+        and a.shape[1] % 8 == 0 and b.shape[1] % 8 == 0 and a.shape[0] % 8 == 0 and a.shape[0] > 0
+    )
+
+
+def linear_act(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], act: int = ACT_NONE) -> torch.Tensor:
+    """Fused ``act(x @ weight.T + bias)``; bf16 tensor-core path on CUDA, torch math elsewhere."""
+    if fused_dense_enabled(x):
+        lead = x.shape[:-1]
+        y = _LinearAct.apply(x.reshape(-1, x.shape[-1]), weight, bias, act)
+        return y.view(*lead, weight.shape[0])
+    y = torch.nn.functional.linear(x, weight, bias)
+    if act == ACT_RELU:
+        return torch.relu(y)
+    if act == ACT_SIGMOID:
+        return torch.sigmoid(y)
+    return y
+
+
+# --------------------------------------------------------------------------------------
+# dot interaction: strict upper triangle of X X^T per sample, concatenated after the dense vector
+# --------------------------------------------------------------------------------------
+class _DotInteraction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, dense, sparse):
+        # dense [B, D], sparse [B, F, D] -> [B, D + C(F+1, 2)]
+        out = torch.ops.trb200.dot_interaction_fwd(dense, sparse)
+        ctx.save_for_backward(dense, sparse)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        dense, sparse = ctx.saved_tensors
+        dd, ds = torch.ops.trb200.dot_interaction_bwd(dout.contiguous(), dense, sparse)
+        return dd, ds
+
+
+def dot_interaction(dense: torch.Tensor, sparse: torch.Tensor) -> torch.Tensor:
+    """``cat([dense, triu(X X^T, 1)])`` with ``X = cat([dense[:,None], sparse], 1)``.
+
+    Pair order follows ``torch.triu_indices(F+1, F+1, offset=1)`` (row-major over i<j).
+    """
+    if dense.is_cuda and _ext.has_cuda_ext() and dense.dtype in (torch.float32, torch.bfloat16) and os.environ.get("TRB200_DOT", "kernel") == "kernel":
+        return _DotInteraction.apply(dense.contiguous(), sparse.contiguous().to(dense.dtype))
+    B, D = dense.shape
+    x = torch.cat((dense.unsqueeze(1), sparse.to(dense.dtype)), dim=1)
+    z = torch.bmm(x, x.transpose(1, 2))
+    n = x.shape[1]
+    iu = torch.triu_indices(n, n, offset=1, device=dense.device)
+    return torch.cat((dense, z[:, iu[0], iu[1]]), dim=1)
+
+
+# --------------------------------------------------------------------------------------
+# loss
+# --------------------------------------------------------------------------------------
+def bce_with_logits_mean(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    return torch.nn.functional.binary_cross_entropy_with_logits(logits.float(), labels.float())
+
+
+# --------------------------------------------------------------------------------------
+# DCN-v2 low-rank cross layer: y = x0 * (W (V x) + b) + x
+# --------------------------------------------------------------------------------------
+def gemm_nt_cross(v: torch.Tensor, w16: torch.Tensor, bias: torch.Tensor, x0: torch.Tensor, xl: torch.Tensor):
+    """Second GEMM of the cross layer with its epilogue: returns ``(u, y)`` where
+    ``u = v @ w16.T + bias`` and ``y = x0 * u + xl`` (both bf16)."""
+    if v.is_cuda and _GEMM_BACKEND == "tcgen05" and _ext.has_cuda_ext() and _tcgen05_ok(v, w16):
+        return torch.ops.trb200.gemm_nt_bf16_cross(v, w16, bias, x0, xl)
+    u = (torch.matmul(v, w16.t()).float() + bias.float()).to(torch.bfloat16)
+    y = (x0.float() * u.float() + xl.float()).to(torch.bfloat16)
+    return u, y
+
+
+class _LowRankCross(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x0, xl, V, W, bias):
+        # x0, xl [B, N] bf16 ; V [r, N] ; W [N, r] ; bias [N]
+        V16 = bf16_cache.get(V)
+        W16 = bf16_cache.get(W)
+        v = gemm_nt(xl, V16, None, ACT_NONE, torch.bfloat16)  # [B, r]
+        u, y = gemm_nt_cross(v, W16, bias, x0, xl)
+        ctx.save_for_backward(x0, xl, v, u, V, W)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x0, xl, v, u, V, W = ctx.saved_tensors
+        dy = dy.contiguous()
+        if dy.dtype != torch.bfloat16:
+            dy = dy.to(torch.bfloat16)
+        # du = dy * x0 ; dx0 = dy * u   (one fused elementwise pass on CUDA)
+        if dy.is_cuda and _ext.has_cuda_ext():
+            du, dx0 = torch.ops.trb200.cross_bwd_elementwise(dy, x0, u)
+        else:
+            du = (dy.float() * x0.float()).to(torch.bfloat16)
+            dx0 = (dy.float() * u.float()).to(torch.bfloat16)
+        WT16 = bf16_cache.get(W, transposed=True)  # [r, N]
+        VT16 = bf16_cache.get(V, transposed=True)  # [N, r]
+        dv = gemm_nt(du, WT16, None, ACT_NONE, torch.bfloat16)  # [B, r]
+        dW = gemm_tn(du, v)  # [N, r]
+        db = torch.ops.trb200.colsum_bf16(du) if (du.is_cuda and _ext.has_cuda_ext()) else du.float().sum(0)
+        # dxl = dy + dv @ V   (residual add in the GEMM epilogue)
+        dxl = gemm_nt_add(dv, VT16, dy)
+        dV = gemm_tn(dv, xl)  # [r, N]
+        return dx0, dxl, dV, dW, db
+
+
+def gemm_nt_add(a: torch.Tensor, b: torch.Tensor, add: torch.Tensor) -> torch.Tensor:
+    """``a @ b.T + add`` (bf16)."""
+    if a.is_cuda and _GEMM_BACKEND == "tcgen05" and _ext.has_cuda_ext() and _tcgen05_ok(a, b):
+        return torch.ops.trb200.gemm_nt_bf16_add(a, b, add)
+    return (torch.matmul(a, b.t()).float() + add.float()).to(torch.bfloat16)
+
+
+def lowrank_cross_layer(x0, xl, V, W, bias) -> torch.Tensor:
+    return _LowRankCross.apply(x0, xl, V, W, bias)
+
+
+def linear_small_out(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """Final logits layer (``out_features`` tiny, e.g. 1): a CUDA-core dot-product kernel is a
+    better fit than a tensor-core tile; plain ``F.linear`` in fp32 keeps the logits exact."""
+    return torch.nn.functional.linear(x.float(), weight, bias)
