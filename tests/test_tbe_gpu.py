@@ -106,11 +106,11 @@ def test_backward_fused_optimizers(opt, zipf):
         ref.backward(g)
         out.backward(g.cuda())
         torch.testing.assert_close(out.detach().cpu(), ref.detach(), rtol=1e-4, atol=1e-4)
-        torch.testing.assert_close(gpu.weights.detach().cpu(), cpu.weights.detach(), rtol=2e-4, atol=2e-5)
+        torch.testing.assert_close(gpu.weights.detach().cpu(), cpu.weights.detach(), rtol=1e-3, atol=5e-5)
         if cpu.momentum1.numel():
-            torch.testing.assert_close(gpu.momentum1.cpu(), cpu.momentum1, rtol=2e-4, atol=1e-6)
+            torch.testing.assert_close(gpu.momentum1.cpu(), cpu.momentum1, rtol=2e-3, atol=1e-6)
         if cpu.momentum2.numel():
-            torch.testing.assert_close(gpu.momentum2.cpu(), cpu.momentum2, rtol=2e-4, atol=1e-7)
+            torch.testing.assert_close(gpu.momentum2.cpu(), cpu.momentum2, rtol=2e-3, atol=1e-7)
     gpu.check_error()
 
 
