@@ -1,0 +1,127 @@
+"""Process-group helpers (cf. ``torchrec/distributed/comm.py:38-276``).
+
+Local (per-node) size and rank come from the launcher's environment; intra-node and
+cross-node sub-groups are built for the hierarchical shardings (TWRW / GRID) and for 2D
+parallelism.  On a single NVSwitch box every rank is "local", so the intra-node group is the
+world and the cross-node group has one member.
+"""
+from __future__ import annotations
+
+import logging
+import os
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+logger: logging.Logger = logging.getLogger(__name__)
+
+_INTRA_PG: Optional[dist.ProcessGroup] = None
+_CROSS_PG: Optional[dist.ProcessGroup] = None
+
+
+def _env2int(env_list: List[str], default: int = -1) -> int:
+    for e in env_list:
+        val = int(os.environ.get(e, -1))
+        if val >= 0:
+            return val
+    return default
+
+
+def get_local_size(world_size: Optional[int] = None) -> int:
+    if world_size is None:
+        world_size = dist.get_world_size()
+    local_size = _env2int(["LOCAL_WORLD_SIZE", "MPI_LOCALNRANKS", "OMPI_COMM_WORLD_LOCAL_SIZE", "MV2_COMM_WORLD_LOCAL_SIZE"], 8)
+    if local_size == -1 or world_size % local_size != 0:
+        logging.warning("Could not determine LOCAL_WORLD_SIZE from environment, falling back to WORLD_SIZE.")
+        local_size = world_size
+    return local_size
+
+
+def get_local_rank(world_size: Optional[int] = None, rank: Optional[int] = None) -> int:
+    my_local_rank = _env2int(["LOCAL_RANK", "MPI_LOCALRANKID", "OMPI_COMM_WORLD_LOCAL_RANK", "MV2_COMM_WORLD_LOCAL_RANK"], -1)
+    local_size = get_local_size(world_size)
+    if my_local_rank == -1 or my_local_rank >= local_size:
+        logging.warning("Could not determine LOCAL_RANK from environment, falling back to GLOBAL_RANK % LOCAL_SIZE.")
+        if rank is None:
+            rank = dist.get_rank()
+        my_local_rank = rank % local_size
+    return my_local_rank
+
+
+def get_group_rank(world_size: Optional[int] = None, rank: Optional[int] = None) -> int:
+    """Index of the node ("group") this rank belongs to."""
+    if rank is None:
+        rank = dist.get_rank()
+    return rank // get_local_size(world_size)
+
+
+def get_num_groups(world_size: Optional[int] = None) -> int:
+    if world_size is None:
+        world_size = dist.get_world_size()
+    return world_size // get_local_size(world_size)
+
+
+def intra_and_cross_node_pg(
+    device: Optional[torch.device] = None, backend: Optional[str] = None,
+) -> Tuple[Optional[dist.ProcessGroup], Optional[dist.ProcessGroup]]:
+    """Sub-groups of the ranks on this node and of the ranks with the same local index on all nodes."""
+    global _INTRA_PG, _CROSS_PG
+    my_size = dist.get_world_size()
+    my_rank = dist.get_rank()
+    my_local_size = get_local_size(my_size)
+    my_local_rank = get_local_rank(my_size, my_rank)
+    my_group_rank = get_group_rank(my_size, my_rank)
+    group_count = get_num_groups(my_size)
+    if backend is None:
+        backend = dist.get_backend()
+    if _INTRA_PG is None:
+        for group_rank in range(group_count):
+            peers = [group_rank * my_local_size + r for r in range(my_local_size)]
+            curr = dist.new_group(backend=backend, ranks=peers)
+            if my_group_rank == group_rank:
+                _INTRA_PG = curr
+        dist.barrier()
+    if _CROSS_PG is None:
+        for l_rank in range(my_local_size):
+            peers = [l_rank + g * my_local_size for g in range(group_count)]
+            curr = dist.new_group(backend=backend, ranks=peers)
+            if l_rank == my_local_rank:
+                _CROSS_PG = curr
+        dist.barrier()
+    return _INTRA_PG, _CROSS_PG
+
+
+def reset_node_process_groups() -> None:
+    global _INTRA_PG, _CROSS_PG
+    _INTRA_PG = None
+    _CROSS_PG = None
+
+
+def intra_and_cross_node_pg_2D(env, device: Optional[torch.device] = None):
+    """Intra/cross node groups inside the sharding group of a 2D environment."""
+    backend = dist.get_backend(env.sharding_pg)
+    my_rank = dist.get_rank()
+    sharding_group_size = dist.get_world_size(env.sharding_pg)
+    world_size = dist.get_world_size()
+    local_size = env.node_group_size if env.node_group_size else get_local_size(world_size)
+    num_sharding_groups = world_size // sharding_group_size
+    step = 1 if env.use_inter_host_allreduce else num_sharding_groups
+    intra_pg = cross_pg = None
+    for g in range(num_sharding_groups):
+        ranks = (
+            list(range(g * sharding_group_size, (g + 1) * sharding_group_size))
+            if env.use_inter_host_allreduce else list(range(g, world_size, step))
+        )
+        nodes = [ranks[i: i + local_size] for i in range(0, len(ranks), local_size)]
+        for node in nodes:
+            pg = dist.new_group(ranks=node, backend=backend)
+            if my_rank in node:
+                intra_pg = pg
+        for l in range(local_size):
+            peers = [node[l] for node in nodes if l < len(node)]
+            pg = dist.new_group(ranks=peers, backend=backend)
+            if my_rank in peers:
+                cross_pg = pg
+    dist.barrier()
+    return intra_pg, cross_pg

@@ -1,0 +1,687 @@
+"""Sharded ``EmbeddingBagCollection``.
+
+Tables are grouped by sharding type; each group gets an ``EmbeddingSharding`` that provides its
+input dist (KJT redistribution), lookup (TBE kernels) and output dist (pooled all-to-all or
+reduce-scatter).  The outputs of all groups are concatenated and permuted back to the table order
+of the unsharded module, so ``forward`` returns the same ``KeyedTensor`` an unsharded
+``EmbeddingBagCollection`` would.  ``state_dict`` exposes ``embedding_bags.<table>.weight`` as
+``ShardedTensor`` whose local shards are views into the kernels' memory.
+
+Counterpart of ``torchrec/distributed/embeddingbag.py`` (``ShardedEmbeddingBagCollection`` ``:454``,
+sharder ``:1933``, mean-pooling divisor ``:2253-2340``).
+"""
+from __future__ import annotations
+
+import copy
+from collections import OrderedDict, defaultdict
+from typing import Any, Dict, Iterator, List, Optional, Tuple, Type, Union
+
+import torch
+import torch.distributed as dist
+from torch import nn
+from torch.autograd.profiler import record_function
+from torch.nn.parallel import DistributedDataParallel
+
+from torchrec_b200.distributed.batched_embedding_kernel import get_state_dict
+from torchrec_b200.distributed.embedding_lookup import fused_optimizer_of_lookups
+from torchrec_b200.distributed.embedding_sharding import (
+    EmbeddingSharding,
+    EmbeddingShardingContext,
+    EmbeddingShardingInfo,
+    KJTListSplitsAwaitable,
+)
+from torchrec_b200.distributed.embedding_types import (
+    BaseEmbeddingSharder,
+    EmbeddingComputeKernel,
+    KJTList,
+    ShardedEmbeddingModule,
+)
+from torchrec_b200.distributed.sharding.cw_sharding import CwPooledEmbeddingSharding
+from torchrec_b200.distributed.sharding.dp_sharding import DpPooledEmbeddingSharding
+from torchrec_b200.distributed.sharding.grid_sharding import GridPooledEmbeddingSharding
+from torchrec_b200.distributed.sharding.rw_sharding import RwPooledEmbeddingSharding
+from torchrec_b200.distributed.sharding.tw_sharding import TwPooledEmbeddingSharding
+from torchrec_b200.distributed.sharding.twcw_sharding import TwCwPooledEmbeddingSharding
+from torchrec_b200.distributed.sharding.twrw_sharding import TwRwPooledEmbeddingSharding
+from torchrec_b200.distributed.types import (
+    Awaitable,
+    EmbeddingEvent,
+    EmbeddingModuleShardingPlan,
+    LazyAwaitable,
+    LazyGetItemMixin,
+    ParameterSharding,
+    QuantizedCommCodecs,
+    ShardedTensor,
+    ShardingEnv,
+    ShardingEnv2D,
+    ShardingType,
+)
+from torchrec_b200.distributed.utils import (
+    add_params_from_parameter_sharding,
+    append_prefix,
+    convert_to_fbgemm_types,
+    maybe_annotate_embedding_event,
+    merge_fused_params,
+    optimizer_type_to_emb_opt_type,
+)
+from torchrec_b200.modules.embedding_configs import EmbeddingBagConfig, EmbeddingTableConfig, PoolingType
+from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection, EmbeddingBagCollectionInterface
+from torchrec_b200.ops import sparse_ops as sops
+from torchrec_b200.optim.fused import EmptyFusedOptimizer, FusedOptimizerModule
+from torchrec_b200.optim.keyed import CombinedOptimizer, KeyedOptimizer
+from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor, KeyedTensor
+from torchrec_b200.streamable import Multistreamable
+
+
+def _pin_and_move(tensor: torch.Tensor, device: torch.device) -> torch.Tensor:
+    if tensor.device == device:
+        return tensor
+    if device.type == "cuda" and tensor.device.type == "cpu":
+        return tensor.pin_memory().to(device=device, non_blocking=True)
+    return tensor.to(device=device, non_blocking=True)
+
+
+def get_device_from_parameter_sharding(ps: ParameterSharding) -> str:
+    if ps.sharding_spec is None or not hasattr(ps.sharding_spec, "shards") or not ps.sharding_spec.shards:
+        return "cuda" if torch.cuda.is_available() else "cpu"
+    return ps.sharding_spec.shards[0].placement.device().type
+
+
+def replace_placement_with_meta_device(sharding_infos: List[EmbeddingShardingInfo]) -> None:
+    """Placements become ``meta`` when a module is sharded on the meta device (plan inspection without memory)."""
+    for info in sharding_infos:
+        spec = info.param_sharding.sharding_spec
+        if spec is None:
+            continue
+        for shard in spec.shards:
+            placement = shard.placement
+            if isinstance(placement, str):
+                placement = torch.distributed._remote_device(placement)
+            shard.placement = torch.distributed._remote_device(f"rank:{placement.rank()}/meta") if placement.rank() is not None else torch.distributed._remote_device("meta")
+
+
+def create_embedding_bag_sharding(
+    sharding_infos: List[EmbeddingShardingInfo], env: ShardingEnv, device: Optional[torch.device] = None,
+    permute_embeddings: bool = False, qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None,
+) -> EmbeddingSharding[EmbeddingShardingContext, KeyedJaggedTensor, torch.Tensor, torch.Tensor]:
+    sharding_type = sharding_infos[0].param_sharding.sharding_type
+    if device is not None and device.type == "meta":
+        replace_placement_with_meta_device(sharding_infos)
+    if sharding_type == ShardingType.TABLE_WISE.value:
+        return TwPooledEmbeddingSharding(sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
+    if sharding_type == ShardingType.ROW_WISE.value:
+        return RwPooledEmbeddingSharding(sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
+    if sharding_type == ShardingType.DATA_PARALLEL.value:
+        return DpPooledEmbeddingSharding(sharding_infos, env, device)
+    if sharding_type == ShardingType.TABLE_ROW_WISE.value:
+        return TwRwPooledEmbeddingSharding(sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
+    if sharding_type == ShardingType.COLUMN_WISE.value:
+        return CwPooledEmbeddingSharding(sharding_infos, env, device, permute_embeddings=permute_embeddings, qcomm_codecs_registry=qcomm_codecs_registry)
+    if sharding_type == ShardingType.TABLE_COLUMN_WISE.value:
+        return TwCwPooledEmbeddingSharding(sharding_infos, env, device, permute_embeddings=permute_embeddings, qcomm_codecs_registry=qcomm_codecs_registry)
+    if sharding_type == ShardingType.GRID_SHARD.value:
+        return GridPooledEmbeddingSharding(sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
+    raise ValueError(f"Sharding type not supported {sharding_type}")
+
+
+def construct_output_kt(embeddings: List[torch.Tensor], embedding_names: List[str], embedding_dims: List[int]) -> KeyedTensor:
+    cat_embeddings = embeddings[0] if len(embeddings) == 1 else torch.cat(embeddings, dim=1)
+    return KeyedTensor(keys=embedding_names, length_per_key=embedding_dims, values=cat_embeddings, key_dim=1)
+
+
+class VariableBatchEmbeddingBagCollectionAwaitable(LazyGetItemMixin[str, torch.Tensor], LazyAwaitable[KeyedTensor]):
+    """Output awaitable for variable batch per feature: flat per-feature outputs are expanded to the
+    full batch through the inverse indices."""
+
+    def __init__(self, awaitables: List[Awaitable[torch.Tensor]], inverse_indices: Tuple[List[str], torch.Tensor],
+                 inverse_indices_permute_indices: Optional[torch.Tensor], batch_size_per_feature_pre_a2a: List[int],
+                 uncombined_embedding_dims: List[int], embedding_names: List[str], embedding_dims: List[int],
+                 permute_op: Optional[nn.Module], module_fqn: Optional[str] = None, sharding_types: Optional[List[str]] = None) -> None:
+        super().__init__()
+        self._awaitables = awaitables
+        self._inverse_indices = inverse_indices
+        self._inverse_indices_permute_indices = inverse_indices_permute_indices
+        self._batch_size_per_feature_pre_a2a = batch_size_per_feature_pre_a2a
+        self._uncombined_embedding_dims = uncombined_embedding_dims
+        self._embedding_names = embedding_names
+        self._embedding_dims = embedding_dims
+        self._permute_op = permute_op
+
+    def _wait_impl(self) -> KeyedTensor:
+        embeddings = [w.wait() for w in self._awaitables]
+        flat = torch.cat([e.view(-1) for e in embeddings])
+        inv = self._inverse_indices[1]
+        if self._inverse_indices_permute_indices is not None:
+            inv = torch.index_select(inv, 0, self._inverse_indices_permute_indices)
+        outs, off = [], 0
+        for i, (b, d) in enumerate(zip(self._batch_size_per_feature_pre_a2a, self._uncombined_embedding_dims)):
+            block = flat[off: off + b * d].view(b, d)
+            outs.append(block.index_select(0, inv[i].to(torch.int64)))
+            off += b * d
+        values = torch.cat(outs, dim=1)
+        if self._permute_op is not None:
+            values = self._permute_op(values)
+        return KeyedTensor(keys=self._embedding_names, length_per_key=self._embedding_dims, values=values, key_dim=1)
+
+
+class EmbeddingBagCollectionAwaitable(LazyGetItemMixin[str, torch.Tensor], LazyAwaitable[KeyedTensor]):
+    def __init__(self, awaitables: List[Awaitable[torch.Tensor]], embedding_dims: List[int], embedding_names: List[str],
+                 module_fqn: Optional[str] = None, sharding_types: Optional[List[str]] = None) -> None:
+        super().__init__()
+        self._awaitables = awaitables
+        self._embedding_dims = embedding_dims
+        self._embedding_names = embedding_names
+        self._module_fqn = module_fqn
+        self._sharding_types = sharding_types
+
+    def _wait_impl(self) -> KeyedTensor:
+        embeddings = []
+        for i, w in enumerate(self._awaitables):
+            with maybe_annotate_embedding_event(EmbeddingEvent.OUTPUT_DIST_WAIT, self._module_fqn, self._sharding_types[i] if self._sharding_types else None):
+                embeddings.append(w.wait())
+        return construct_output_kt(embeddings, self._embedding_names, self._embedding_dims)
+
+
+class EmbeddingBagCollectionContext(Multistreamable):
+    def __init__(self, sharding_contexts: Optional[List[Optional[EmbeddingShardingContext]]] = None,
+                 inverse_indices: Optional[Tuple[List[str], torch.Tensor]] = None, variable_batch_per_feature: bool = False,
+                 divisor: Optional[torch.Tensor] = None) -> None:
+        super().__init__()
+        self.sharding_contexts: List[Optional[EmbeddingShardingContext]] = sharding_contexts if sharding_contexts else []
+        self.inverse_indices = inverse_indices
+        self.variable_batch_per_feature = variable_batch_per_feature
+        self.divisor = divisor
+
+    def record_stream(self, stream: torch.Stream) -> None:
+        for ctx in self.sharding_contexts:
+            if ctx:
+                ctx.record_stream(stream)
+        if self.inverse_indices is not None and self.inverse_indices[1].is_cuda:
+            self.inverse_indices[1].record_stream(stream)
+        if self.divisor is not None and self.divisor.is_cuda:
+            self.divisor.record_stream(stream)
+
+
+def _create_mean_pooling_divisor(lengths: torch.Tensor, keys: List[str], offsets: torch.Tensor, stride: int,
+                                 dim_per_key: torch.Tensor, mean_features: List[str], embedding_names: List[str],
+                                 embedding_dims: List[int], kjt_key_indices: Dict[str, int], kt_key_ordering: torch.Tensor,
+                                 weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``[B, sum(D)]`` divisor: the bag length for MEAN features of row-split tables, 1 elsewhere."""
+    with record_function("## ebc create mean pooling callback ##"):
+        batch_size = stride
+        if weights is not None:
+            lengths = sops.segment_sum_csr(1, offsets.to(torch.int64), weights)
+        lengths = lengths.clone().to(torch.float32)
+        mean_set = set(mean_features)
+        for feature in keys:
+            if feature not in mean_set:
+                i = kjt_key_indices[feature] * batch_size
+                lengths[i: i + batch_size] = 1
+        if len(embedding_names) != len(keys):
+            lengths = torch.index_select(lengths.reshape(-1, batch_size), 0, kt_key_ordering).reshape(-1)
+        lengths = lengths.reshape(-1, batch_size).T
+        divisor = torch.repeat_interleave(lengths, dim_per_key, dim=1, output_size=sum(embedding_dims))
+        return (divisor + 1e-6).detach()
+
+
+def _apply_mean_pooling(keyed_tensor: KeyedTensor, divisor: torch.Tensor) -> KeyedTensor:
+    with record_function("## ebc apply mean pooling ##"):
+        return KeyedTensor(keys=keyed_tensor.keys(), values=keyed_tensor.values() / divisor.to(keyed_tensor.values().dtype),
+                           length_per_key=keyed_tensor.length_per_key(), key_dim=1)
+
+
+class ShardedEmbeddingBagCollection(
+    ShardedEmbeddingModule[KJTList, List[torch.Tensor], KeyedTensor, EmbeddingBagCollectionContext],
+    FusedOptimizerModule,
+):
+    """Sharded counterpart of ``EmbeddingBagCollection``; built by ``EmbeddingBagCollectionSharder``."""
+
+    def __init__(
+        self,
+        module: EmbeddingBagCollectionInterface,
+        table_name_to_parameter_sharding: Dict[str, ParameterSharding],
+        env: ShardingEnv,
+        fused_params: Optional[Dict[str, Any]] = None,
+        device: Optional[torch.device] = None,
+        qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None,
+        module_fqn: Optional[str] = None,
+    ) -> None:
+        super().__init__(qcomm_codecs_registry=qcomm_codecs_registry)
+        self._module_fqn = module_fqn
+        self._embedding_bag_configs: List[EmbeddingBagConfig] = module.embedding_bag_configs()
+        self._table_names: List[str] = [c.name for c in self._embedding_bag_configs]
+        self._table_name_to_config: Dict[str, EmbeddingBagConfig] = {c.name: c for c in self._embedding_bag_configs}
+        self.module_sharding_plan: EmbeddingModuleShardingPlan = EmbeddingModuleShardingPlan(
+            {t: ps for t, ps in table_name_to_parameter_sharding.items() if t in self._table_names}
+        )
+        self._env = env
+        self._output_dtensor: bool = env.output_dtensor
+        self.sharding_type_to_sharding_infos = self.create_grouped_sharding_infos(module, table_name_to_parameter_sharding, "embedding_bags.", fused_params)
+        self._sharding_types: List[str] = list(self.sharding_type_to_sharding_infos.keys())
+        self._embedding_shardings: List[EmbeddingSharding] = [
+            create_embedding_bag_sharding(infos, env, device, permute_embeddings=True, qcomm_codecs_registry=self.qcomm_codecs_registry)
+            for infos in self.sharding_type_to_sharding_infos.values()
+        ]
+        self._is_weighted: bool = module.is_weighted()
+        self._device = device
+        self._input_dists: List[nn.Module] = []
+        self._lookups: List[nn.Module] = []
+        self._create_lookups()
+        self._output_dists: List[nn.Module] = []
+        self._embedding_names: List[str] = []
+        self._embedding_dims: List[int] = []
+        self._feature_splits: List[int] = []
+        self._features_order: List[int] = []
+        self._uncombined_embedding_names: List[str] = []
+        self._uncombined_embedding_dims: List[int] = []
+        self._inverse_indices_permute_indices: Optional[torch.Tensor] = None
+        # output order: embeddings come out grouped by sharding type; permute back to table order
+        self._permute_op: Optional[nn.Module] = None
+        self._has_uninitialized_input_dist: bool = True
+        self._has_features_permute: bool = True
+        # lookups that hold data-parallel tables are wrapped in DDP so their dense gradient is all-reduced
+        for i, (sharding, lookup) in enumerate(zip(self._embedding_shardings, self._lookups)):
+            if isinstance(sharding, DpPooledEmbeddingSharding) and env.process_group is not None and dist.get_world_size(env.process_group) >= 1:
+                if dist.get_backend(env.process_group) != "fake":
+                    self._lookups[i] = DistributedDataParallel(
+                        module=lookup, device_ids=[device] if device is not None and device.type == "cuda" else None,
+                        process_group=env.process_group, gradient_as_bucket_view=True, broadcast_buffers=True, static_graph=True,
+                    )
+        self._initialize_torch_state()
+        # optimizer
+        optims = []
+        for lookup in self._lookups:
+            lk = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
+            for _, tbe_module in lk.named_modules():
+                if isinstance(tbe_module, FusedOptimizerModule):
+                    # keys of the fused optimizer are "<table>.weight"; make them "embedding_bags.<table>.weight"
+                    params: Dict[str, Union[torch.Tensor, ShardedTensor]] = {}
+                    for param_key, weight in tbe_module.fused_optimizer.params.items():
+                        params["embedding_bags." + param_key] = weight
+                    tbe_module.fused_optimizer.params = params
+                    optims.append(("", tbe_module.fused_optimizer))
+        self._optim: CombinedOptimizer = CombinedOptimizer(optims)
+        # mean pooling for row-split tables is applied after the reduction
+        self._has_mean_pooling_callback: bool = PoolingType.MEAN.value in self._pooling_type_to_rs_features()
+        self._dim_per_key: Optional[torch.Tensor] = None
+        self._kjt_key_indices: Dict[str, int] = {}
+        self._kt_key_ordering: Optional[torch.Tensor] = None
+
+    # ---- plan -> sharding infos ------------------------------------------------------------------
+    @classmethod
+    def create_grouped_sharding_infos(cls, module, table_name_to_parameter_sharding: Dict[str, ParameterSharding], prefix: str,
+                                      fused_params: Optional[Dict[str, Any]], suffix: Optional[str] = "weight") -> Dict[str, List[EmbeddingShardingInfo]]:
+        if fused_params is None:
+            fused_params = {}
+        shared_feature: Dict[str, bool] = {}
+        for cfg in module.embedding_bag_configs():
+            if not cfg.feature_names:
+                cfg.feature_names = [cfg.name]
+            for f in cfg.feature_names:
+                shared_feature[f] = f in shared_feature
+        out: Dict[str, List[EmbeddingShardingInfo]] = defaultdict(list)
+        parameter_by_name = dict(module.named_parameters())
+        state_dict = module.state_dict()
+        for config in module.embedding_bag_configs():
+            table_name = config.name
+            assert table_name in table_name_to_parameter_sharding, f"{table_name} not in table_name_to_parameter_sharding"
+            ps = table_name_to_parameter_sharding[table_name]
+            if ps.compute_kernel not in [k.value for k in EmbeddingComputeKernel]:
+                raise ValueError(f"Compute kernel not supported {ps.compute_kernel}")
+            embedding_names = [f + "@" + config.name if shared_feature[f] else f for f in config.feature_names]
+            param_name = prefix + table_name + (f".{suffix}" if suffix is not None else "")
+            assert param_name in parameter_by_name or param_name in state_dict
+            param = parameter_by_name.get(param_name, state_dict.get(param_name))
+            optimizer_params = getattr(param, "_optimizer_kwargs", [{}])
+            optimizer_classes = getattr(param, "_optimizer_classes", [None])
+            assert len(optimizer_classes) == 1 and len(optimizer_params) == 1, "Only support 1 optimizer per table"
+            optimizer_class = optimizer_classes[0]
+            optimizer_params = copy.deepcopy(optimizer_params[0])
+            if optimizer_class:
+                optimizer_params["optimizer"] = optimizer_type_to_emb_opt_type(optimizer_class)
+            per_table = merge_fused_params(fused_params, optimizer_params)
+            per_table = add_params_from_parameter_sharding(per_table, ps)
+            per_table = convert_to_fbgemm_types(per_table)
+            out[ps.sharding_type].append(
+                EmbeddingShardingInfo(
+                    embedding_config=EmbeddingTableConfig(
+                        num_embeddings=config.num_embeddings, embedding_dim=config.embedding_dim, name=config.name,
+                        data_type=config.data_type, feature_names=copy.deepcopy(config.feature_names), pooling=config.pooling,
+                        is_weighted=module.is_weighted(), has_feature_processor=False, embedding_names=embedding_names,
+                        weight_init_max=config.weight_init_max, weight_init_min=config.weight_init_min, init_fn=config.init_fn,
+                        num_embeddings_post_pruning=getattr(config, "num_embeddings_post_pruning", None),
+                        total_num_buckets=getattr(config, "total_num_buckets", None),
+                        use_virtual_table=getattr(config, "use_virtual_table", False),
+                    ),
+                    param_sharding=ps, param=param, fused_params=per_table,
+                )
+            )
+        return out
+
+    def _pooling_type_to_rs_features(self) -> Dict[str, List[str]]:
+        out: Dict[str, List[str]] = defaultdict(list)
+        for sharding_type, infos in self.sharding_type_to_sharding_infos.items():
+            if sharding_type in (ShardingType.ROW_WISE.value, ShardingType.TABLE_ROW_WISE.value, ShardingType.GRID_SHARD.value):
+                for info in infos:
+                    out[info.embedding_config.pooling.value].extend(info.embedding_config.feature_names)
+        return out
+
+    # ---- torch state: parameters and state dict -----------------------------------------------------
+    def _initialize_torch_state(self) -> None:
+        """Register ``embedding_bags.<table>.weight`` and build the ShardedTensor view of every table."""
+        self._model_parallel_name_to_local_shards: Dict[str, List[Any]] = OrderedDict()
+        self._model_parallel_name_to_sharded_tensor: Dict[str, Any] = OrderedDict()
+        self._name_to_table_size: Dict[str, Tuple[int, int]] = {}
+        model_parallel_name_to_compute_kernel: Dict[str, str] = {}
+        for table_name, ps in self.module_sharding_plan.items():
+            if ps.sharding_type == ShardingType.DATA_PARALLEL.value:
+                continue
+            self._model_parallel_name_to_local_shards[table_name] = []
+            model_parallel_name_to_compute_kernel[table_name] = ps.compute_kernel
+        for cfg in self._embedding_bag_configs:
+            self._name_to_table_size[cfg.name] = (cfg.num_embeddings, cfg.embedding_dim)
+        self.embedding_bags: nn.ModuleDict = nn.ModuleDict()
+        tables_by_name: Dict[str, List[Tuple[Any, torch.Tensor]]] = defaultdict(list)
+        for sharding_type, lookup in zip(self._sharding_types, self._lookups):
+            lk = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
+            if sharding_type == ShardingType.DATA_PARALLEL.value:
+                # data-parallel tables are ordinary parameters (views into the dense TBE buffer)
+                for emb in lk.emb_modules:
+                    w = emb.emb_module.weights
+                    offs = emb.emb_module.weights_offsets
+                    for i, t in enumerate(emb.config.embedding_tables):
+                        m = nn.Module()
+                        from torchrec_b200.distributed.batched_embedding_kernel import TableBatchedEmbeddingSlice
+
+                        m.register_parameter("weight", TableBatchedEmbeddingSlice(w, offs[i], offs[i + 1], t.local_rows, t.local_cols))
+                        self.embedding_bags[t.name] = m
+                continue
+            for emb in lk.emb_modules:
+                for t, w in zip(emb.config.embedding_tables, emb.split_embedding_weights()):
+                    tables_by_name[t.name].append((t, w))
+        pg = self._env.sharding_pg if isinstance(self._env, ShardingEnv2D) else self._env.process_group
+        for table_name in self._model_parallel_name_to_local_shards.keys():
+            local = tables_by_name.get(table_name, [])
+            self._model_parallel_name_to_local_shards[table_name] = local
+            m = nn.Module()
+            self.embedding_bags[table_name] = m
+            # a rank may hold no shard of a table (table-wise on another rank): expose an empty parameter
+            if local:
+                if len(local) == 1:
+                    view = local[0][1]
+                else:
+                    view = torch.cat([w for _, w in local], dim=1) if all(w.shape[0] == local[0][1].shape[0] for _, w in local) else local[0][1]
+                m.register_parameter("weight", nn.Parameter(view, requires_grad=False) if len(local) > 1 else _ViewParameter(view))
+            else:
+                dev = self._device if self._device is not None else torch.device("cpu")
+                m.register_parameter("weight", nn.Parameter(torch.empty(0, device=dev), requires_grad=False))
+            if pg is not None and local:
+                sd = get_state_dict([t for t, _ in local], [w for _, w in local], pg=pg)
+                self._model_parallel_name_to_sharded_tensor[table_name] = sd[f"{table_name}.weight"]
+            elif pg is not None:
+                # no local shard: still a participant of the ShardedTensor
+                ps = self.module_sharding_plan[table_name]
+                from torchrec_b200.distributed.types import ShardedTensorMetadata, TensorProperties
+
+                rows, cols = self._name_to_table_size[table_name]
+                meta = ShardedTensorMetadata(
+                    shards_metadata=copy.deepcopy(ps.sharding_spec.shards), size=torch.Size([rows, cols]),
+                    tensor_properties=TensorProperties(dtype=torch.float32),
+                )
+                try:
+                    self._model_parallel_name_to_sharded_tensor[table_name] = ShardedTensor._init_from_local_shards_and_global_metadata(
+                        local_shards=[], sharded_tensor_metadata=meta, process_group=pg,
+                    )
+                except Exception:
+                    self._model_parallel_name_to_sharded_tensor[table_name] = None
+
+        def post_state_dict_hook(module, destination, prefix, _local_metadata) -> None:
+            for name, st in module._model_parallel_name_to_sharded_tensor.items():
+                key = f"{prefix}embedding_bags.{name}.weight"
+                if st is not None:
+                    destination[key] = st
+                elif key in destination and not module._model_parallel_name_to_local_shards.get(name):
+                    destination.pop(key)
+
+        self._register_state_dict_hook(post_state_dict_hook)
+        self._register_load_state_dict_pre_hook(self._pre_load_state_dict_hook, with_module=True)
+        self.reset_parameters()
+
+    @staticmethod
+    def _pre_load_state_dict_hook(self, state_dict, prefix, *args) -> None:
+        """Copy incoming (sharded or full) tensors into the local shard views, then hand nn.Module the
+        local parameter itself so that its own copy is a no-op."""
+        for name in list(self._model_parallel_name_to_local_shards.keys()):
+            key = f"{prefix}embedding_bags.{name}.weight"
+            if key not in state_dict:
+                continue
+            src = state_dict[key]
+            local = self._model_parallel_name_to_local_shards[name]
+            if isinstance(src, ShardedTensor):
+                src_shards = src.local_shards()
+                for t, w in local:
+                    for s in src_shards:
+                        if list(s.metadata.shard_offsets) == list(t.local_metadata.shard_offsets) and list(s.metadata.shard_sizes) == list(t.local_metadata.shard_sizes):
+                            w.detach().copy_(s.tensor)
+                            break
+                    else:
+                        raise RuntimeError(f"no matching shard for {name} at offsets {t.local_metadata.shard_offsets}")
+            elif isinstance(src, torch.Tensor):
+                rows, cols = self._name_to_table_size[name]
+                if tuple(src.shape) == (rows, cols):
+                    for t, w in local:
+                        ro, co = t.local_metadata.shard_offsets
+                        rs, cs = t.local_metadata.shard_sizes
+                        w.detach().copy_(src[ro: ro + rs, co: co + cs])
+                elif local and tuple(src.shape) == tuple(local[0][1].shape):
+                    local[0][1].detach().copy_(src)
+            state_dict[key] = self.embedding_bags[name].weight.detach()
+
+    def reset_parameters(self) -> None:
+        if self._device is not None and self._device.type == "meta":
+            return
+        # data-parallel tables start identical on every rank: DDP broadcasts rank 0's parameters at construction
+        return
+
+    # ---- parameters / optimizer ---------------------------------------------------------------------
+    def named_parameters(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True) -> Iterator[Tuple[str, nn.Parameter]]:
+        for name, m in self.embedding_bags.items():
+            yield append_prefix(prefix, f"embedding_bags.{name}.weight"), m.weight
+
+    def sharded_parameter_names(self, prefix: str = "") -> Iterator[str]:
+        for name in self._model_parallel_name_to_local_shards.keys():
+            yield append_prefix(prefix, f"embedding_bags.{name}.weight")
+
+    @property
+    def fused_optimizer(self) -> KeyedOptimizer:
+        return self._optim
+
+    @property
+    def shardings(self) -> Dict[str, EmbeddingSharding]:
+        return dict(zip(self._sharding_types, self._embedding_shardings))
+
+    @property
+    def unsharded_module_type(self) -> Type[EmbeddingBagCollection]:
+        return EmbeddingBagCollection
+
+    def create_context(self) -> EmbeddingBagCollectionContext:
+        return EmbeddingBagCollectionContext()
+
+    # ---- building the three stages --------------------------------------------------------------------
+    def _create_lookups(self) -> None:
+        for sharding in self._embedding_shardings:
+            self._lookups.append(sharding.create_lookup())
+
+    def _create_input_dist(self, input_feature_names: List[str]) -> None:
+        feature_names: List[str] = []
+        for sharding in self._embedding_shardings:
+            self._input_dists.append(sharding.create_input_dist())
+            feature_names.extend(sharding.feature_names())
+            self._feature_splits.append(len(sharding.feature_names()))
+        if feature_names == input_feature_names:
+            self._has_features_permute = False
+        else:
+            for f in feature_names:
+                self._features_order.append(input_feature_names.index(f))
+            dev = self._device if self._device is not None and self._device.type != "meta" else torch.device("cpu")
+            self.register_buffer("_features_order_tensor", torch.tensor(self._features_order, device=dev, dtype=torch.int32), persistent=False)
+
+    def _create_output_dist(self) -> None:
+        embedding_shard_metadata = []
+        for sharding in self._embedding_shardings:
+            self._output_dists.append(sharding.create_output_dist(device=self._device))
+            self._embedding_names.extend(sharding.embedding_names())
+            self._embedding_dims.extend(sharding.embedding_dims())
+            self._uncombined_embedding_names.extend(sharding.uncombined_embedding_names())
+            self._uncombined_embedding_dims.extend(sharding.uncombined_embedding_dims())
+            embedding_shard_metadata.extend(sharding.embedding_shard_metadata())
+        # restore the embedding order of the unsharded module
+        wanted = [n for names in _embedding_names_by_table(self._embedding_bag_configs) for n in names]
+        if wanted != self._embedding_names:
+            from torchrec_b200.distributed.sharding.cw_sharding import PermutePooledEmbeddingsSplit
+
+            order = [self._embedding_names.index(n) for n in wanted]
+            self._permute_op = PermutePooledEmbeddingsSplit(self._embedding_dims, order, device=self._device)
+            self._embedding_names = wanted
+            self._embedding_dims = [self._embedding_dims[i] for i in order]
+
+    def _init_mean_pooling_callback(self, input_feature_names: List[str]) -> None:
+        keys = [input_feature_names[i] for i in self._features_order] if self._features_order else list(input_feature_names)
+        self._kjt_key_indices = {k: i for i, k in enumerate(keys)}
+        dev = self._device if self._device is not None else torch.device("cpu")
+        self._dim_per_key = torch.tensor(self._embedding_dims, device=dev)
+        # embedding name -> feature name ("f@table" -> "f")
+        feat_of = [n.split("@")[0] for n in self._embedding_names]
+        self._kt_key_ordering = torch.tensor([self._kjt_key_indices[f] for f in feat_of], device=dev)
+
+    # ---- the three stages -------------------------------------------------------------------------------
+    def input_dist(self, ctx: EmbeddingBagCollectionContext, features: KeyedJaggedTensor) -> Awaitable[Awaitable[KJTList]]:
+        ctx.variable_batch_per_feature = features.variable_stride_per_key()
+        ctx.inverse_indices = features.inverse_indices_or_none()
+        if self._has_uninitialized_input_dist:
+            self._create_input_dist(features.keys())
+            self._has_uninitialized_input_dist = False
+            if not self._output_dists:
+                self._create_output_dist()
+            if ctx.variable_batch_per_feature and ctx.inverse_indices is not None:
+                self._create_inverse_indices_permute_indices(ctx.inverse_indices)
+            if self._has_mean_pooling_callback:
+                self._init_mean_pooling_callback(features.keys())
+        with torch.no_grad():
+            if self._has_features_permute:
+                features = features.permute(self._features_order, self._features_order_tensor)
+            if self._has_mean_pooling_callback:
+                ctx.divisor = _create_mean_pooling_divisor(
+                    lengths=features.lengths(), keys=features.keys(), offsets=features.offsets(), stride=features.stride(),
+                    dim_per_key=self._dim_per_key, mean_features=self._pooling_type_to_rs_features()[PoolingType.MEAN.value],
+                    embedding_names=self._embedding_names, embedding_dims=self._embedding_dims,
+                    kjt_key_indices=self._kjt_key_indices, kt_key_ordering=self._kt_key_ordering,
+                    weights=features.weights_or_none() if self._is_weighted else None,
+                )
+            features_by_shards = features.split(self._feature_splits)
+            awaitables = []
+            for input_dist, features_by_shard, sharding_type in zip(self._input_dists, features_by_shards, self._sharding_types):
+                with maybe_annotate_embedding_event(EmbeddingEvent.KJT_SPLITS_DIST, self._module_fqn, sharding_type):
+                    awaitables.append(input_dist(features_by_shard))
+                ctx.sharding_contexts.append(
+                    EmbeddingShardingContext(
+                        batch_size_per_feature_pre_a2a=features_by_shard.stride_per_key(),
+                        variable_batch_per_feature=features_by_shard.variable_stride_per_key(),
+                    )
+                )
+            return KJTListSplitsAwaitable(awaitables, ctx, self._module_fqn, self._sharding_types)
+
+    def _create_inverse_indices_permute_indices(self, inverse_indices: Optional[Tuple[List[str], torch.Tensor]]) -> None:
+        assert inverse_indices is not None, "inverse indices must be provided from KJT if using variable batch size per feature."
+        index_per_name = {name: i for i, name in enumerate(inverse_indices[0])}
+        permute_indices = [index_per_name[n.split("@")[0]] for n in self._uncombined_embedding_names]
+        if len(permute_indices) != len(index_per_name) or permute_indices != sorted(permute_indices):
+            self._inverse_indices_permute_indices = _pin_and_move(torch.tensor(permute_indices), inverse_indices[1].device)
+
+    def compute(self, ctx: EmbeddingBagCollectionContext, dist_input: KJTList) -> List[torch.Tensor]:
+        return [lookup(features) for lookup, features in zip(self._lookups, dist_input)]
+
+    def output_dist(self, ctx: EmbeddingBagCollectionContext, output: List[torch.Tensor]) -> LazyAwaitable[KeyedTensor]:
+        if not self._output_dists:
+            self._create_output_dist()
+        awaitables = [d(embs, sctx) for d, sctx, embs in zip(self._output_dists, ctx.sharding_contexts, output)]
+        return self._finish_output(ctx, awaitables)
+
+    def compute_and_output_dist(self, ctx: EmbeddingBagCollectionContext, input: KJTList) -> LazyAwaitable[KeyedTensor]:
+        if not self._output_dists:
+            self._create_output_dist()
+        awaitables = []
+        for lookup, d, sctx, features, sharding_type in zip(self._lookups, self._output_dists, ctx.sharding_contexts, input, self._sharding_types):
+            with maybe_annotate_embedding_event(EmbeddingEvent.LOOKUP, self._module_fqn, sharding_type):
+                embs = lookup(features)
+            with maybe_annotate_embedding_event(EmbeddingEvent.OUTPUT_DIST, self._module_fqn, sharding_type):
+                awaitables.append(d(embs, sctx))
+            if self.post_lookup_tracker_fn is not None:
+                self.post_lookup_tracker_fn(features, embs, self, None)
+        return self._finish_output(ctx, awaitables)
+
+    def _finish_output(self, ctx: EmbeddingBagCollectionContext, awaitables: List[Awaitable[torch.Tensor]]) -> LazyAwaitable[KeyedTensor]:
+        if ctx.variable_batch_per_feature:
+            assert ctx.inverse_indices is not None, "inverse indices must be provided from KJT if using variable batch size per feature."
+            return VariableBatchEmbeddingBagCollectionAwaitable(
+                awaitables=awaitables, inverse_indices=ctx.inverse_indices,
+                inverse_indices_permute_indices=self._inverse_indices_permute_indices,
+                batch_size_per_feature_pre_a2a=[b for s in ctx.sharding_contexts for b in s.batch_size_per_feature_pre_a2a],
+                uncombined_embedding_dims=self._uncombined_embedding_dims, embedding_names=self._embedding_names,
+                embedding_dims=self._embedding_dims, permute_op=self._permute_op,
+            )
+        awaitable = EmbeddingBagCollectionAwaitable(
+            awaitables=awaitables, embedding_dims=self._pre_permute_dims(), embedding_names=self._pre_permute_names(),
+            module_fqn=self._module_fqn, sharding_types=self._sharding_types,
+        )
+        if self._permute_op is not None:
+            permute_op, names, dims = self._permute_op, self._embedding_names, self._embedding_dims
+            awaitable.callbacks.append(lambda kt: KeyedTensor(keys=names, length_per_key=dims, values=permute_op(kt.values()), key_dim=1))
+        if self._has_mean_pooling_callback and ctx.divisor is not None:
+            divisor = ctx.divisor
+            awaitable.callbacks.append(lambda kt: _apply_mean_pooling(kt, divisor))
+        return awaitable
+
+    def _pre_permute_names(self) -> List[str]:
+        if self._permute_op is None:
+            return self._embedding_names
+        return [n for s in self._embedding_shardings for n in s.embedding_names()]
+
+    def _pre_permute_dims(self) -> List[int]:
+        if self._permute_op is None:
+            return self._embedding_dims
+        return [d for s in self._embedding_shardings for d in s.embedding_dims()]
+
+
+class _ViewParameter(nn.Parameter):
+    """Parameter object sharing storage with a TBE table view; it never receives an autograd gradient
+    (the kernel updates the table in backward) but keeps ``requires_grad`` semantics out of DDP's way."""
+
+    def __new__(cls, data: torch.Tensor):
+        return torch.Tensor._make_subclass(cls, data.detach(), False)
+
+
+def _embedding_names_by_table(tables) -> List[List[str]]:
+    shared: Dict[str, bool] = {}
+    for cfg in tables:
+        for f in cfg.feature_names:
+            shared[f] = f in shared
+    return [[f + "@" + cfg.name if shared[f] else f for f in cfg.feature_names] for cfg in tables]
+
+
+class EmbeddingBagCollectionSharder(BaseEmbeddingSharder[EmbeddingBagCollection]):
+    """Shards an ``EmbeddingBagCollection`` according to a module sharding plan."""
+
+    def shard(self, module: EmbeddingBagCollection, params: Dict[str, ParameterSharding], env: ShardingEnv,
+              device: Optional[torch.device] = None, module_fqn: Optional[str] = None) -> ShardedEmbeddingBagCollection:
+        return ShardedEmbeddingBagCollection(
+            module=module, table_name_to_parameter_sharding=params, env=env, fused_params=self.fused_params, device=device,
+            qcomm_codecs_registry=self.qcomm_codecs_registry, module_fqn=module_fqn,
+        )
+
+    def shardable_parameters(self, module: EmbeddingBagCollection) -> Dict[str, nn.Parameter]:
+        return {name.split(".")[0]: param for name, param in module.embedding_bags.named_parameters()}
+
+    @property
+    def module_type(self) -> Type[EmbeddingBagCollection]:
+        return EmbeddingBagCollection

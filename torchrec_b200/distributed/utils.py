@@ -1,0 +1,241 @@
+"""Utilities of the sharding runtime (cf. ``torchrec/distributed/utils.py``)."""
+from __future__ import annotations
+
+import copy
+import logging
+import pdb
+import sys
+from collections import OrderedDict
+from contextlib import nullcontext
+from typing import Any, Dict, List, Optional, Set, Type, TypeVar, Union
+
+import torch
+from torch import nn
+from torch.autograd.profiler import record_function
+
+from torchrec_b200 import optim as trec_optim
+from torchrec_b200.distributed.embedding_types import EmbeddingComputeKernel
+from torchrec_b200.distributed.types import DataType, EmbeddingEvent, ParameterSharding, ShardedModule, ShardingType
+from torchrec_b200.ops.tbe import EmbOptimType
+from torchrec_b200.types import CopyMixIn
+
+logger: logging.Logger = logging.getLogger(__name__)
+_T = TypeVar("_T")
+
+
+def none_throws(optional: Optional[_T], message: str = "Unexpected `None`") -> _T:
+    if optional is None:
+        raise AssertionError(message)
+    return optional
+
+
+def append_prefix(prefix: str, name: str) -> str:
+    """``"a." + "b" -> "a.b"``; empty parts are skipped."""
+    if prefix != "" and name != "":
+        return prefix + "." + name
+    return prefix + name
+
+
+def filter_state_dict(state_dict: "OrderedDict[str, torch.Tensor]", name: str) -> "OrderedDict[str, torch.Tensor]":
+    """Entries whose key starts with ``name.``, with that prefix removed."""
+    filtered = OrderedDict()
+    for key, value in state_dict.items():
+        if key.startswith(name + "."):
+            filtered[key[len(name) + 1:]] = value
+    return filtered
+
+
+def add_prefix_to_state_dict(state_dict: Dict[str, Any], prefix: str) -> None:
+    keys = sorted(state_dict.keys())
+    for key in keys:
+        state_dict[prefix + key] = state_dict.pop(key)
+    if "_metadata" in state_dict:
+        metadata = state_dict["_metadata"]
+        for key in list(metadata.keys()):
+            if len(key) == 0:
+                continue
+            metadata[prefix + key] = metadata.pop(key)
+
+
+def _get_unsharded_module_names_helper(model: nn.Module, path: str, unsharded_module_names: Set[str]) -> bool:
+    sharded_children = set()
+    for name, child in model.named_children():
+        curr_path = path + name
+        if isinstance(child, ShardedModule):
+            sharded_children.add(name)
+        else:
+            if _get_unsharded_module_names_helper(child, curr_path + ".", unsharded_module_names):
+                sharded_children.add(name)
+    if len(sharded_children) > 0:
+        for name, _ in model.named_children():
+            if name not in sharded_children:
+                unsharded_module_names.add(path + name)
+    return len(sharded_children) > 0
+
+
+def get_unsharded_module_names(model: nn.Module) -> List[str]:
+    """Minimal set of module paths that contain no sharded submodule."""
+    unsharded: Set[str] = set()
+    _get_unsharded_module_names_helper(model, "", unsharded)
+    return list(unsharded)
+
+
+class sharded_model_copy:
+    """Context manager: ``copy.deepcopy`` of a sharded model keeps sharded tensors on ``device``
+    (e.g. ``with sharded_model_copy("cpu"): m_cpu = copy.deepcopy(m)``)."""
+
+    def __init__(self, device: Optional[Union[str, int, torch.device]]) -> None:
+        self.device = device
+
+    def __enter__(self) -> None:
+        self.t_copy_save_ = torch.Tensor.__deepcopy__
+        self.p_copy_save_ = torch.nn.Parameter.__deepcopy__
+        device = self.device
+
+        def _tensor_copy(tensor, memo):
+            if tensor.device != device:
+                return tensor.detach().to(device)
+            return tensor.detach().clone()
+
+        def _param_copy(param, memo):
+            return torch.nn.Parameter(_tensor_copy(param, memo), requires_grad=param.requires_grad)
+
+        torch.Tensor.__deepcopy__ = _tensor_copy
+        torch.nn.Parameter.__deepcopy__ = _param_copy
+
+    def __exit__(self, exc_type, exc_val, exc_tb) -> None:
+        torch.Tensor.__deepcopy__ = self.t_copy_save_
+        torch.nn.Parameter.__deepcopy__ = self.p_copy_save_
+
+
+def copy_to_device(module: nn.Module, current_device: torch.device, to_device: torch.device) -> nn.Module:
+    with sharded_model_copy(device=None):
+        copy_module = copy.deepcopy(module)
+
+    def _copy_if_device_match(tensor: torch.Tensor) -> torch.Tensor:
+        if tensor.device == current_device:
+            return tensor.to(to_device)
+        return tensor
+
+    if isinstance(copy_module, CopyMixIn):
+        return copy_module.copy(to_device)
+    copied_param = {name: torch.nn.Parameter(_copy_if_device_match(p.data), requires_grad=p.requires_grad) for name, p in copy_module.named_parameters(recurse=False)}
+    copied_buffer = {name: _copy_if_device_match(b) for name, b in copy_module.named_buffers(recurse=False)}
+    for name, param in copied_param.items():
+        copy_module.register_parameter(name, param)
+    for name, buffer in copied_buffer.items():
+        copy_module.register_buffer(name, buffer)
+    for child_name, child in copy_module.named_children():
+        if not any(p.device == current_device for p in child.parameters()) and not isinstance(child, CopyMixIn):
+            continue
+        setattr(copy_module, child_name, copy_to_device(child, current_device, to_device))
+    return copy_module
+
+
+def optimizer_type_to_emb_opt_type(optimizer_class: Type[torch.optim.Optimizer]) -> Optional[EmbOptimType]:
+    """Which fused kernel update an optimizer class selects."""
+    from torchrec_b200.optim import optimizers as marker
+    from torchrec_b200.optim.rowwise_adagrad import RowWiseAdagrad
+
+    lookup = {
+        torch.optim.SGD: EmbOptimType.EXACT_SGD,
+        torch.optim.Adagrad: EmbOptimType.EXACT_ADAGRAD,
+        torch.optim.Adam: EmbOptimType.ADAM,
+        marker.SGD: EmbOptimType.EXACT_SGD,
+        marker.LarsSGD: EmbOptimType.LARS_SGD,
+        marker.LAMB: EmbOptimType.LAMB,
+        marker.PartialRowWiseLAMB: EmbOptimType.PARTIAL_ROWWISE_LAMB,
+        marker.Adam: EmbOptimType.ADAM,
+        marker.PartialRowWiseAdam: EmbOptimType.PARTIAL_ROWWISE_ADAM,
+        marker.Adagrad: EmbOptimType.EXACT_ADAGRAD,
+        RowWiseAdagrad: EmbOptimType.EXACT_ROWWISE_ADAGRAD,
+    }
+    if optimizer_class not in lookup:
+        raise ValueError(f"Cannot cast {optimizer_class} to an EmbOptimType")
+    return lookup[optimizer_class]
+
+
+def merge_fused_params(fused_params: Optional[Dict[str, Any]] = None, param_fused_params: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
+    """Sharder-level fused params overridden by the per-parameter optimizer kwargs (``lr`` -> ``learning_rate``)."""
+    if fused_params is None:
+        fused_params = {}
+    if param_fused_params is None:
+        param_fused_params = {}
+    if "lr" in param_fused_params:
+        param_fused_params["learning_rate"] = param_fused_params.pop("lr")
+    _fused_params = copy.deepcopy(fused_params)
+    _fused_params.update(param_fused_params)
+    return _fused_params
+
+
+def add_params_from_parameter_sharding(fused_params: Optional[Dict[str, Any]], parameter_sharding: ParameterSharding) -> Dict[str, Any]:
+    if fused_params is None:
+        fused_params = {}
+    if parameter_sharding.cache_params is not None:
+        cp = parameter_sharding.cache_params
+        for name in ("algorithm", "load_factor", "reserved_memory", "precision", "prefetch_pipeline", "multipass_prefetch_config"):
+            v = getattr(cp, name)
+            if v is not None:
+                fused_params[{"algorithm": "cache_algorithm", "load_factor": "cache_load_factor", "reserved_memory": "cache_reserved_memory", "precision": "cache_precision"}.get(name, name)] = v
+    for name in ("enforce_hbm", "stochastic_rounding", "bounds_check_mode", "output_dtype"):
+        v = getattr(parameter_sharding, name)
+        if v is not None:
+            fused_params[name] = v
+    if parameter_sharding.compute_kernel in {EmbeddingComputeKernel.KEY_VALUE.value, EmbeddingComputeKernel.SSD_VIRTUAL_TABLE.value, EmbeddingComputeKernel.DRAM_VIRTUAL_TABLE.value}:
+        kv = parameter_sharding.key_value_params
+        if kv is not None:
+            for k, v in kv.__dict__.items():
+                if v is not None:
+                    fused_params[k] = v
+    return fused_params
+
+
+def convert_to_fbgemm_types(fused_params: Dict[str, Any]) -> Dict[str, Any]:
+    """Kept for API parity: kernel-side enums are native to this package, nothing to convert."""
+    return fused_params
+
+
+def init_parameters(module: nn.Module, device: torch.device) -> None:
+    """Materialise ``meta`` parameters on ``device`` and run ``reset_parameters`` where defined."""
+    with torch.no_grad():
+        has_meta_param = any(isinstance(p, torch.Tensor) and p.device.type == "meta" for p in module._parameters.values())
+        for key, buf in list(module._buffers.items()):
+            if isinstance(buf, torch.Tensor) and buf.device.type == "meta":
+                module._buffers[key] = torch.zeros_like(buf, device=device)
+        if has_meta_param:
+            for key, param in list(module._parameters.items()):
+                if isinstance(param, torch.Tensor) and param.device.type == "meta":
+                    module._parameters[key] = nn.Parameter(torch.empty_like(param, device=device), requires_grad=param.requires_grad)
+
+        def maybe_reset(m: nn.Module) -> None:
+            if has_meta_param and hasattr(m, "reset_parameters"):
+                m.reset_parameters()
+
+        maybe_reset(module)
+
+
+def maybe_annotate_embedding_event(event: EmbeddingEvent, module_fqn: Optional[str], sharding_type: Optional[str]):
+    """Profiler range ``## <event>: [<module>, <sharding>] ##`` when both names are known."""
+    if module_fqn and sharding_type:
+        return record_function(f"## {event.value}: [{module_fqn}, {sharding_type}] ##")
+    return nullcontext()
+
+
+class ForkedPdb(pdb.Pdb):
+    """pdb usable inside a spawned rank (re-opens stdin)."""
+
+    def interaction(self, *args, **kwargs) -> None:
+        _stdin = sys.stdin
+        try:
+            sys.stdin = open("/dev/stdin")
+            pdb.Pdb.interaction(self, *args, **kwargs)
+        finally:
+            sys.stdin = _stdin
+
+
+def modify_input_for_feature_processor(features, feature_processors, is_collection: bool) -> None:
+    """Give unweighted features unit weights so that position-weighted processors can scale them."""
+    with torch.no_grad():
+        if features.weights_or_none() is None:
+            cat_weights = torch.ones(features.values().numel(), dtype=torch.float32, device=features.device())
+            features._weights = cat_weights
