@@ -1,0 +1,312 @@
+"""``EmbeddingShardingPlanner``: reserve -> enumerate -> (propose -> partition -> rate)* -> best plan.
+
+``collective_plan`` runs the search on rank 0 and broadcasts the result so that every rank uses the
+same plan.  Counterpart of ``torchrec/distributed/planner/planners.py:343-708``.
+"""
+from __future__ import annotations
+
+import copy
+import logging
+import time
+from functools import reduce
+from typing import Callable, Dict, List, Optional, Tuple, Union, cast
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from torchrec_b200.distributed.collective_utils import invoke_on_rank_and_broadcast_result
+from torchrec_b200.distributed.comm import get_local_size
+from torchrec_b200.distributed.planner.constants import BATCH_SIZE, MAX_SIZE
+from torchrec_b200.distributed.planner.enumerators import EmbeddingEnumerator
+from torchrec_b200.distributed.planner.partitioners import GreedyPerfPartitioner, MemoryBalancedPartitioner
+from torchrec_b200.distributed.planner.perf_models import NoopPerfModel
+from torchrec_b200.distributed.planner.proposers import GreedyProposer, GridSearchProposer, UniformProposer
+from torchrec_b200.distributed.planner.storage_reservations import HeuristicalStorageReservation
+from torchrec_b200.distributed.planner.types import (
+    Enumerator,
+    ParameterConstraints,
+    Partitioner,
+    PerfModel,
+    PlannerError,
+    PlannerErrorType,
+    Proposer,
+    ShardingOption,
+    Stats,
+    Storage,
+    StorageReservation,
+    Topology,
+    hash_planner_context_inputs,
+)
+from torchrec_b200.distributed.planner.utils import bytes_to_gb, reset_shard_rank, storage_repr_in_gb
+from torchrec_b200.distributed.sharding_plan import get_default_sharders, placement
+from torchrec_b200.distributed.types import (
+    EmbeddingModuleShardingPlan,
+    EnumerableShardingSpec,
+    ModuleSharder,
+    ParameterSharding,
+    ShardingPlan,
+    ShardingPlanner,
+    ShardingType,
+    ShardMetadata,
+)
+
+logger: logging.Logger = logging.getLogger(__name__)
+
+
+def to_sharding_plan(sharding_options: List[ShardingOption], topology: Topology) -> ShardingPlan:
+    """Convert placed sharding options into the runtime's ``ShardingPlan``."""
+    compute_device = topology.compute_device
+    local_size = topology.local_world_size
+    plan: Dict[str, EmbeddingModuleShardingPlan] = {}
+    for so in sharding_options:
+        shards = so.shards
+        sharding_type = so.sharding_type
+        module_plan = plan.get(so.path, EmbeddingModuleShardingPlan())
+        module_plan[so.name] = ParameterSharding(
+            sharding_spec=(
+                None if sharding_type == ShardingType.DATA_PARALLEL.value
+                else EnumerableShardingSpec(
+                    [
+                        ShardMetadata(shard_sizes=s.size, shard_offsets=s.offset, placement=placement(compute_device, cast(int, s.rank), local_size))
+                        for s in shards
+                    ]
+                )
+            ),
+            sharding_type=sharding_type,
+            compute_kernel=so.compute_kernel,
+            ranks=[cast(int, s.rank) for s in shards],
+            cache_params=so.cache_params,
+            enforce_hbm=so.enforce_hbm,
+            stochastic_rounding=so.stochastic_rounding,
+            bounds_check_mode=so.bounds_check_mode,
+            output_dtype=so.output_dtype,
+            key_value_params=so.key_value_params,
+        )
+        plan[so.path] = module_plan
+    return ShardingPlan(plan)
+
+
+def _merge_plans(best_plans: List[ShardingPlan]) -> ShardingPlan:
+    if len(best_plans) == 1:
+        return best_plans[0]
+    merged = ShardingPlan(plan={})
+    for p in best_plans:
+        for name, ps in p.plan.items():
+            merged.plan.setdefault(name, EmbeddingModuleShardingPlan()).update(ps)  # type: ignore[union-attr]
+    return merged
+
+
+class EmbeddingShardingPlanner(ShardingPlanner):
+    """Searches for the sharding plan with the lowest estimated step time that fits in memory.
+
+    Args:
+        topology: devices to plan for (default: the current world, 180 GB HBM each).
+        batch_size: per-rank batch size the estimators assume.
+        enumerator / storage_reservation / proposer / partitioner / performance_model / stats: plug-ins.
+        constraints: per-table restrictions and input statistics.
+        debug: print the full plan report.
+    """
+
+    def __init__(
+        self,
+        topology: Optional[Topology] = None,
+        batch_size: Optional[int] = None,
+        enumerator: Optional[Enumerator] = None,
+        storage_reservation: Optional[StorageReservation] = None,
+        proposer: Optional[Union[Proposer, List[Proposer]]] = None,
+        partitioner: Optional[Partitioner] = None,
+        performance_model: Optional[PerfModel] = None,
+        stats: Optional[Union[Stats, List[Stats]]] = None,
+        constraints: Optional[Dict[str, ParameterConstraints]] = None,
+        debug: bool = True,
+        callbacks: Optional[List[Callable[[List[ShardingOption]], List[ShardingOption]]]] = None,
+        timeout_seconds: Optional[int] = None,
+    ) -> None:
+        if topology is None:
+            world = dist.get_world_size() if dist.is_initialized() else 1
+            topology = Topology(local_world_size=get_local_size(world) if dist.is_initialized() else 1, world_size=world,
+                                compute_device="cuda" if torch.cuda.is_available() else "cpu")
+        self._topology: Topology = topology
+        self._batch_size: int = batch_size if batch_size else BATCH_SIZE
+        self._constraints = constraints
+        self._enumerator: Enumerator = enumerator if enumerator else EmbeddingEnumerator(topology=topology, batch_size=self._batch_size, constraints=constraints)
+        self._storage_reservation: StorageReservation = storage_reservation if storage_reservation else HeuristicalStorageReservation(percentage=0.15)
+        self._partitioner: Partitioner = partitioner if partitioner else GreedyPerfPartitioner()
+        if proposer:
+            self._proposers: List[Proposer] = [proposer] if not isinstance(proposer, list) else proposer
+        else:
+            self._proposers = [GridSearchProposer(), GreedyProposer(), GreedyProposer(use_depth=False), UniformProposer()]
+        self._perf_model: PerfModel = performance_model if performance_model else NoopPerfModel(topology=topology)
+        if stats is not None:
+            self._stats: List[Stats] = [stats] if not isinstance(stats, list) else stats
+        else:
+            from torchrec_b200.distributed.planner.stats import EmbeddingStats
+
+            self._stats = [EmbeddingStats()]
+        self._debug = debug
+        self._callbacks = [] if callbacks is None else callbacks
+        if timeout_seconds is not None:
+            assert timeout_seconds > 0, "Timeout must be positive"
+        self._timeout_seconds = timeout_seconds
+        self._num_proposals: int = 0
+        self._num_plans: int = 0
+        self._best_plan: Optional[List[ShardingOption]] = None
+
+    def collective_plan(self, module: nn.Module, sharders: Optional[List[ModuleSharder[nn.Module]]] = None,
+                        pg: Optional[dist.ProcessGroup] = None) -> ShardingPlan:
+        """Plan on rank 0 and broadcast."""
+        if pg is None:
+            assert dist.is_initialized(), "The default process group is not yet initialized. Call torch.distributed.init_process_group first."
+            pg = dist.GroupMember.WORLD
+        if sharders is None:
+            sharders = get_default_sharders()
+        return invoke_on_rank_and_broadcast_result(pg, 0, self.plan, module, sharders)
+
+    def hash_planner_context_inputs(self) -> int:
+        return hash_planner_context_inputs(self._topology, self._batch_size, self._enumerator, self._storage_reservation, self._constraints)
+
+    def plan(self, module: nn.Module, sharders: Optional[List[ModuleSharder[nn.Module]]] = None) -> ShardingPlan:
+        if sharders is None:
+            sharders = get_default_sharders()
+        self._num_proposals = 0
+        self._num_plans = 0
+        start_time = time.perf_counter()
+        best_plan = None
+        lowest_storage = Storage(MAX_SIZE, MAX_SIZE)
+        last_planner_error: Optional[PlannerError] = None
+        last_proposal: List[ShardingOption] = []
+        best_perf_rating = MAX_SIZE
+
+        storage_constraint: Topology = self._storage_reservation.reserve(
+            topology=self._topology, batch_size=self._batch_size, module=module, sharders=sharders, constraints=self._constraints,
+        )
+        search_space = self._enumerator.enumerate(module=module, sharders=sharders)
+        if not search_space:
+            return ShardingPlan({})
+
+        proposal_cache: Dict[Tuple[int, ...], Tuple[bool, Optional[List[ShardingOption]], Optional[float]]] = {}
+        for proposer in self._proposers:
+            proposer.load(search_space=search_space, enumerator=self._enumerator)
+
+        timed_out = False
+        for proposer in self._proposers:
+            proposal = proposer.propose()
+            while proposal:
+                if self._timeout_seconds is not None and time.perf_counter() - start_time > self._timeout_seconds:
+                    timed_out = True
+                    break
+                proposal_key = tuple(sorted(map(hash, proposal)))
+                if proposal_key in proposal_cache:
+                    partitionable, plan, perf_rating = proposal_cache[proposal_key]
+                    proposer.feedback(partitionable=partitionable, plan=plan, perf_rating=perf_rating, storage_constraint=storage_constraint)
+                    proposal = proposer.propose()
+                    continue
+                self._num_proposals += 1
+                try:
+                    plan = self._partitioner.partition(proposal=proposal, storage_constraint=storage_constraint)
+                    self._num_plans += 1
+                    perf_rating = self._perf_model.rate(plan=plan)
+                    if perf_rating < best_perf_rating:
+                        best_perf_rating = perf_rating
+                        best_plan = copy.deepcopy(plan)
+                    proposal_cache[proposal_key] = (True, plan, perf_rating)
+                    proposer.feedback(partitionable=True, plan=plan, perf_rating=perf_rating, storage_constraint=storage_constraint)
+                except PlannerError as planner_error:
+                    last_planner_error = planner_error
+                    current_storage = cast(Storage, reduce(lambda x, y: x + y, [shard.storage for option in proposal for shard in option.shards]))
+                    if current_storage < lowest_storage:
+                        lowest_storage = current_storage
+                    proposal_cache[proposal_key] = (False, proposal, None)
+                    proposer.feedback(partitionable=False, plan=proposal, storage_constraint=storage_constraint)
+                last_proposal = copy.deepcopy(proposal)
+                reset_shard_rank(proposal)
+                proposal = proposer.propose()
+            if timed_out:
+                break
+
+        if best_plan:
+            for callback in self._callbacks:
+                best_plan = callback(best_plan)
+            self._best_plan = best_plan
+            sharding_plan = to_sharding_plan(best_plan, self._topology)
+            end_time = time.perf_counter()
+            for stats in self._stats:
+                stats.log(
+                    sharding_plan=sharding_plan, topology=self._topology, batch_size=self._batch_size,
+                    storage_reservation=self._storage_reservation, num_proposals=self._num_proposals, num_plans=self._num_plans,
+                    run_time=end_time - start_time, best_plan=best_plan, constraints=self._constraints, sharders=sharders,
+                    enumerator=self._enumerator, debug=self._debug,
+                )
+            return sharding_plan
+
+        global_storage_capacity = reduce(lambda x, y: x + y, [device.storage for device in self._topology.devices])
+        global_storage_constraints = reduce(lambda x, y: x + y, [device.storage for device in storage_constraint.devices])
+        storage_reservation_solution = (
+            f"\n\t  Storage reservation percentage: {self._storage_reservation._percentage}, "  # type: ignore[attr-defined]
+            f"\n\t  Per rank reservation for dense storage: {storage_repr_in_gb(self._storage_reservation._dense_storage)}, "  # type: ignore[attr-defined]
+            f"\n\t  Per rank reservation for kjt storage: {storage_repr_in_gb(self._storage_reservation._kjt_storage)}, "  # type: ignore[attr-defined]
+            if isinstance(self._storage_reservation, HeuristicalStorageReservation) else "\n"
+        )
+        no_plan_solution = (
+            f"Planner evaluated {self._num_proposals} proposals."
+            "\nPossible solutions:"
+            f"\n  1) Increase the number of devices ({self._topology.world_size})"
+            f"\n  2) Reduce the model size ("
+            f"\n\t  Global storage: {round(bytes_to_gb(global_storage_capacity.hbm), 3)} GB, "
+            f"\n\t  Per rank hardware memory: {storage_repr_in_gb(self._topology.devices[0].storage)}, "
+            f"\n\t  Available for model parallel: {round(bytes_to_gb(global_storage_constraints.hbm), 3)} GB, "
+            f"\n\t  Requirement for model parallel: {round(bytes_to_gb(lowest_storage.hbm), 3)} GB)"
+            f"\n  3) Reduce local batch size ({self._batch_size})"
+            "\n  4) Remove planner constraints that might be reducing search space or available storage\n"
+        )
+        last_planner_error_info = f"Last planner error: \n\t{last_planner_error}\n"
+        sharding_plan = to_sharding_plan(last_proposal, self._topology) if last_proposal and all(s.rank is not None for so in last_proposal for s in so.shards) else None
+        if not lowest_storage.fits_in(global_storage_constraints):
+            raise PlannerError(
+                error_type=PlannerErrorType.INSUFFICIENT_STORAGE,
+                message="Unable to find a plan for this model because of insufficient storage. \n" + no_plan_solution + storage_reservation_solution + last_planner_error_info,
+            )
+        raise PlannerError(
+            error_type=PlannerErrorType.STRICT_CONSTRAINTS,
+            message="Unable to find a plan for this model because of the strict constraints. \n" + no_plan_solution + last_planner_error_info,
+        )
+
+
+class HeteroEmbeddingShardingPlanner(ShardingPlanner):
+    """Plans over several device groups (e.g. ``cuda`` and ``cpu``) with one planner per group; a table's
+    ``ParameterConstraints.device_group`` selects the group it may be placed on."""
+
+    def __init__(self, topology_groups: Optional[Dict[str, Topology]] = None, batch_size: Optional[int] = None,
+                 enumerators: Optional[Dict[str, Enumerator]] = None, storage_reservations: Optional[Dict[str, StorageReservation]] = None,
+                 proposers: Optional[Dict[str, Union[Proposer, List[Proposer]]]] = None, partitioners: Optional[Dict[str, Partitioner]] = None,
+                 performance_models: Optional[Dict[str, PerfModel]] = None, stats: Optional[Dict[str, Union[Stats, List[Stats]]]] = None,
+                 constraints: Optional[Dict[str, ParameterConstraints]] = None, debug: bool = True,
+                 callbacks: Optional[List[Callable[[List[ShardingOption]], List[ShardingOption]]]] = None) -> None:
+        default_device = "cuda" if torch.cuda.is_available() else "cpu"
+        if topology_groups is None:
+            world = dist.get_world_size() if dist.is_initialized() else 1
+            topology_groups = {default_device: Topology(local_world_size=get_local_size(world) if dist.is_initialized() else 1, world_size=world, compute_device=default_device)}
+        self._topology_groups = topology_groups
+        self._planners: Dict[str, EmbeddingShardingPlanner] = {}
+        for group, topology in topology_groups.items():
+            self._planners[group] = EmbeddingShardingPlanner(
+                topology=topology, batch_size=batch_size, enumerator=enumerators.get(group) if enumerators else None,
+                storage_reservation=storage_reservations.get(group) if storage_reservations else None,
+                proposer=proposers.get(group) if proposers else None, partitioner=partitioners.get(group) if partitioners else None,
+                performance_model=performance_models.get(group) if performance_models else None, stats=stats.get(group) if stats else None,
+                constraints=constraints, debug=debug, callbacks=callbacks,
+            )
+
+    def collective_plan(self, module: nn.Module, sharders: Optional[List[ModuleSharder[nn.Module]]] = None,
+                        pg: Optional[dist.ProcessGroup] = None) -> ShardingPlan:
+        if pg is None:
+            pg = dist.GroupMember.WORLD
+        if sharders is None:
+            sharders = get_default_sharders()
+        return invoke_on_rank_and_broadcast_result(pg, 0, self.plan, module, sharders)
+
+    def plan(self, module: nn.Module, sharders: Optional[List[ModuleSharder[nn.Module]]] = None) -> ShardingPlan:
+        if sharders is None:
+            sharders = get_default_sharders()
+        return _merge_plans([p.plan(module, sharders) for p in self._planners.values()])
