@@ -151,7 +151,8 @@ class KJTAllToAllSplitsAwaitable(Awaitable[KJTAllToAllTensorsAwaitable]):
     """First stage: exchange split sizes so that every rank can size its receive buffers."""
 
     def __init__(self, pg: dist.ProcessGroup, input: KeyedJaggedTensor, splits: List[int], labels: List[str],
-                 tensor_splits: List[List[int]], input_tensors: List[torch.Tensor], keys: List[str], device: torch.device, stagger: int) -> None:
+                 tensor_splits: List[List[int]], input_tensors: List[torch.Tensor], keys: List[str], device: torch.device, stagger: int,
+                 defer_splits_exchange: bool = False) -> None:
         super().__init__()
         self._workers = pg.size()
         self._pg = pg
@@ -165,15 +166,22 @@ class KJTAllToAllSplitsAwaitable(Awaitable[KJTAllToAllTensorsAwaitable]):
         self._stagger = stagger
         self._output_splits: List[List[int]] = self._input_splits
         self._stride_per_rank: Optional[List[int]] = None if self._input.variable_stride_per_key() else [self._input.stride()] * self._workers
-        if self._workers == 1:
+        self._splits_awaitable: Optional[SplitsAllToAllAwaitable] = None
+        # a train pipeline exchanges the split sizes of all its modules in one fused collective instead
+        if self._workers == 1 or defer_splits_exchange:
             return
-        input_tensors_ = [torch.tensor(s, device=device) for s in self._input_splits]
+        self._launch_splits_exchange()
+
+    def _launch_splits_exchange(self) -> None:
+        input_tensors_ = [torch.tensor(s, device=self._device) for s in self._input_splits]
         if not self._input.variable_stride_per_key():
-            input_tensors_.append(torch.tensor([input.stride()] * self._workers, device=device))
+            input_tensors_.append(torch.tensor([self._input.stride()] * self._workers, device=self._device))
         self._splits_awaitable = SplitsAllToAllAwaitable(input_tensors_, self._pg)
 
     def _wait_impl(self) -> KJTAllToAllTensorsAwaitable:
         if self._workers > 1:
+            if self._splits_awaitable is None:
+                self._launch_splits_exchange()
             output_list = self._splits_awaitable.wait()
             if self._input.variable_stride_per_key():
                 self._output_splits = output_list
@@ -200,6 +208,7 @@ class KJTAllToAll(nn.Module):
         self._splits = splits
         self._splits_cumsum = [0] + list(itertools.accumulate(splits))
         self._stagger = stagger
+        self.defer_splits_exchange: bool = False  # set by train pipelines that fuse the split exchange
 
     def forward(self, input: KeyedJaggedTensor) -> Awaitable[KJTAllToAllTensorsAwaitable]:
         with torch.no_grad():
@@ -210,6 +219,7 @@ class KJTAllToAll(nn.Module):
                 pg=self._pg, input=input, splits=self._splits, labels=input.dist_labels(),
                 tensor_splits=input.dist_splits(self._splits), input_tensors=input.dist_tensors(),
                 keys=local_keys, device=input.device(), stagger=self._stagger,
+                defer_splits_exchange=self.defer_splits_exchange,
             )
 
 

@@ -415,6 +415,9 @@ class ShardedEmbeddingBagCollection(
             else:
                 dev = self._device if self._device is not None else torch.device("cpu")
                 m.register_parameter("weight", nn.Parameter(torch.empty(0, device=dev), requires_grad=False))
+            if model_parallel_name_to_compute_kernel[table_name] != EmbeddingComputeKernel.DENSE.value:
+                # updated inside the kernel's backward: dense optimizers must skip it
+                m.weight._in_backward_optimizers = [EmptyFusedOptimizer()]
             if pg is not None and local:
                 sd = get_state_dict([t for t, _ in local], [w for _, w in local], pg=pg)
                 self._model_parallel_name_to_sharded_tensor[table_name] = sd[f"{table_name}.weight"]
