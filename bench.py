@@ -53,6 +53,7 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--pool", type=int, default=4, help="number of distinct synthetic batches that are cycled")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--breakdown", action="store_true", help="print a per-phase device-time breakdown to stderr")
+    p.add_argument("--kernel-table", action="store_true", help="print per-kernel device time of one step to stderr (diagnostic)")
     return p.parse_args()
 
 
@@ -245,6 +246,17 @@ def main() -> None:
             torch.cuda.synchronize()
         own = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and ("trb::" in e.name or "trb_" in e.name)]
         launches = len(own) * args.steps
+        if args.kernel_table and rank == 0:
+            agg: Dict[str, List[float]] = {}
+            for e in prof.events():
+                if e.device_type == torch.autograd.DeviceType.CUDA:
+                    a = agg.setdefault(e.name[:110], [0.0, 0])
+                    a[0] += e.device_time_total if hasattr(e, "device_time_total") else e.cuda_time_total
+                    a[1] += 1
+            tot = sum(v[0] for v in agg.values())
+            print(f"kernel table (one step, {tot / 1e3:.3f} ms of device time):", file=sys.stderr)
+            for name, (t, n) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:45]:
+                print(f"  {t / 1e3:8.3f} ms  x{n:<3d} {name}", file=sys.stderr)
     except Exception:
         launches = None
 

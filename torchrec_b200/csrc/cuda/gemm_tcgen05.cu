@@ -29,7 +29,7 @@ namespace trb {
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;  // 64 bf16 = 128 bytes = one swizzle span
 constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr long long kWaitCycles = 2000000000LL;  // about one second
 
 enum GemmErr : int { ERR_NONE = 0, ERR_FULL_WAIT = 1, ERR_EMPTY_WAIT = 2, ERR_TMEM_FULL_WAIT = 3, ERR_TMEM_EMPTY_WAIT = 4 };
@@ -108,8 +108,9 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
       : "memory");
 }
 
-// 32 lanes x 32 columns of fp32: thread `lane` receives row `lane`, columns [c, c+32)
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+// 32 lanes x 32 columns of fp32: thread `lane` receives row `lane`, columns [c, c+32).  The load is asynchronous;
+// tmem_ld_wait names the destination registers as in/out operands so that no use of them can be scheduled above the wait.
+__device__ __forceinline__ void tmem_ld_32x32_issue(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -119,7 +120,15 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
 }
 
 // shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100)
@@ -153,10 +162,101 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   return v;
 }
 
+enum Epi : int { EPI_PLAIN = 0, EPI_BIAS = 1, EPI_BIAS_RELU = 2, EPI_BIAS_SIGMOID = 3, EPI_CROSS = 4, EPI_ADD = 5, EPI_F32 = 6, EPI_F32_ATOMIC = 7 };
+
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
+  uint4 pk;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+  return pk;
+}
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& pk, float (&v)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(h[j]);
+    v[2 * j] = f.x;
+    v[2 * j + 1] = f.y;
+  }
+}
+
+// One 32-row x 32-column piece of the accumulator: thread `lane` owns row `lane`, r[] are its 32 columns.
+// All global loads of the piece are issued before any arithmetic so that their latencies overlap.
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&r)[32], int64_t row_off, int col0) {
+  constexpr bool kBias = EPI == EPI_BIAS || EPI == EPI_BIAS_RELU || EPI == EPI_BIAS_SIGMOID || EPI == EPI_CROSS;
+  constexpr bool kMul = EPI == EPI_CROSS;
+  constexpr bool kAdd = EPI == EPI_CROSS || EPI == EPI_ADD;
+  float4 bias[8];
+  uint4 mulv[4], addv[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int col = col0 + g * 8;
+    if (col < p.N) {
+      if constexpr (kBias) {
+        bias[2 * g] = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+        bias[2 * g + 1] = __ldg(reinterpret_cast<const float4*>(p.bias + col + 4));
+      }
+      if constexpr (kMul) mulv[g] = *reinterpret_cast<const uint4*>(p.mul + row_off + col);
+      if constexpr (kAdd) addv[g] = *reinterpret_cast<const uint4*>(p.add + row_off + col);
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int col = col0 + g * 8;
+    if (col >= p.N) continue;  // N % 8 == 0: a group of 8 columns is fully inside or outside
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
+    if constexpr (kBias) {
+      v[0] += bias[2 * g].x; v[1] += bias[2 * g].y; v[2] += bias[2 * g].z; v[3] += bias[2 * g].w;
+      v[4] += bias[2 * g + 1].x; v[5] += bias[2 * g + 1].y; v[6] += bias[2 * g + 1].z; v[7] += bias[2 * g + 1].w;
+    }
+    if constexpr (EPI == EPI_BIAS_RELU) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.f);
+    }
+    if constexpr (EPI == EPI_BIAS_SIGMOID) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 1.f / (1.f + __expf(-v[j]));
+    }
+    if constexpr (EPI == EPI_CROSS) {
+      // u = acc + bias is stored in bf16 and y is computed from the rounded u, so that y == x0 * u + x exactly as saved
+      const uint4 upk = pack_bf16x8(v);
+      *reinterpret_cast<uint4*>(p.u_out + row_off + col) = upk;
+      unpack_bf16x8(upk, v);
+      float m[8];
+      unpack_bf16x8(mulv[g], m);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] *= m[j];
+    }
+    if constexpr (kAdd) {
+      float a[8];
+      unpack_bf16x8(addv[g], a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += a[j];
+    }
+    if constexpr (EPI == EPI_F32 || EPI == EPI_F32_ATOMIC) {
+      float* o = reinterpret_cast<float*>(p.out) + row_off + col;
+      if constexpr (EPI == EPI_F32_ATOMIC) {
+        red_add_f32x4(o, make_float4(v[0], v[1], v[2], v[3]));
+        red_add_f32x4(o + 4, make_float4(v[4], v[5], v[6], v[7]));
+      } else {
+        *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    } else {
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + row_off + col) = pack_bf16x8(v);
+    }
+  }
+}
+
 // MN_MAJOR = false: A[M,K], B[N,K] row-major (K contiguous).  tmapA box {64 k, 128 rows}, tmapB box {64 k, BLOCK_N rows}.
 // MN_MAJOR = true : A[Kc,M], B[Kc,N] row-major (output dims contiguous, contraction along rows).
 //                   tmap boxes are {64 cols, 64 rows}; a stage holds M/64 (resp. N/64) such boxes.
-template <int BLOCK_N, bool MN_MAJOR>
+template <int BLOCK_N, bool MN_MAJOR, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, GemmParams p) {
   using L = SmemLayout<BLOCK_N>;
@@ -185,7 +285,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);  // one arrival per epilogue warp
+      mbar_init(&tmem_empty[a], 8);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -278,8 +378,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // ---------------- epilogue (warps 2..9) ----------------
+    // Two warps share each TMEM lane quarter (warp % 4) and split the tile's columns in halves.  The TMEM load of
+    // the next 32-column piece is in flight while the current one is processed.
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int kPieces = BLOCK_N / 64;  // 32-column pieces per warp
     uint32_t tile_it = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++tile_it) {
@@ -292,80 +396,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       const int row = m_blk * kBlockM + q * 32 + lane;
       const bool row_ok = row < p.M;
       const int64_t row_off = int64_t(row) * p.ldc;
-#pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        const int col0 = n_blk * BLOCK_N + c * 32;
-        if (col0 >= p.N) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BLOCK_N + c * 32, r);
-        if (row_ok) {
+      const int colbase = n_blk * BLOCK_N + half * (BLOCK_N / 2);
+      const uint32_t tbase = tmem_base + (uint32_t(q * 32) << 16) + acc * BLOCK_N + half * (BLOCK_N / 2);
+      uint32_t r[2][32];
+      tmem_ld_32x32_issue(tbase, r[0]);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {  // 8 columns per group
-            const int col = col0 + g * 8;
-            if (col < p.N) {             // N % 8 == 0, so a group is fully in or out
-              float v[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
-              if (p.bias) {
-                const float4 b0 = *reinterpret_cast<const float4*>(p.bias + col);
-                const float4 b1 = *reinterpret_cast<const float4*>(p.bias + col + 4);
-                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-              }
-              if (p.act) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], p.act);
-              }
-              if (p.u_out) {
-                uint4 pk;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                *reinterpret_cast<uint4*>(p.u_out + row_off + col) = pk;
-                // keep the rounded value so that y matches x0 * bf16(u) + x exactly as saved
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float2 f = __bfloat1622float2(h[j]);
-                  v[2 * j] = f.x; v[2 * j + 1] = f.y;
-                }
-              }
-              if (p.mul) {
-                const uint4 mk = *reinterpret_cast<const uint4*>(p.mul + row_off + col);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&mk);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float2 f = __bfloat1622float2(h[j]);
-                  v[2 * j] *= f.x; v[2 * j + 1] *= f.y;
-                }
-              }
-              if (p.add) {
-                const uint4 ak = *reinterpret_cast<const uint4*>(p.add + row_off + col);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&ak);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float2 f = __bfloat1622float2(h[j]);
-                  v[2 * j] += f.x; v[2 * j + 1] += f.y;
-                }
-              }
-              if (p.out_fp32) {
-                float* o = reinterpret_cast<float*>(p.out) + row_off + col;
-                if (p.atomic_out) {
-                  red_add_f32x4(o, make_float4(v[0], v[1], v[2], v[3]));
-                  red_add_f32x4(o + 4, make_float4(v[4], v[5], v[6], v[7]));
-                } else {
-                  *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
-                  *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
-                }
-              } else {
-                uint4 pk;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + row_off + col) = pk;
-              }
-            }
-          }
-        }
+      for (int c = 0; c < kPieces; ++c) {
+        tmem_ld_wait(r[c & 1]);
+        if (c + 1 < kPieces) tmem_ld_32x32_issue(tbase + (c + 1) * 32, r[(c + 1) & 1]);
+        const int col0 = colbase + c * 32;
+        if (row_ok && col0 < p.N) epilogue_chunk<EPI>(p, r[c & 1], row_off, col0);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -452,23 +492,43 @@ static void launch_gemm(const at::Tensor& a, const at::Tensor& b, GemmParams p) 
   const int m_tiles = (p.M + kBlockM - 1) / kBlockM, n_tiles = (p.N + BN - 1) / BN;
   const int work = m_tiles * n_tiles * p.k_splits;
   const int grid = std::min(work, num_sms());
-  if (wide) {
-    constexpr int smem = SmemLayout<256>::kTotal;
-    static bool set = false;
-    if (!set) {
-      TRB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<256, MN_MAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      set = true;
+  int epi;
+  if (p.out_fp32) epi = p.atomic_out ? EPI_F32_ATOMIC : EPI_F32;
+  else if (p.u_out) epi = EPI_CROSS;
+  else if (p.add) epi = EPI_ADD;
+  else if (p.bias) epi = p.act == 1 ? EPI_BIAS_RELU : (p.act == 2 ? EPI_BIAS_SIGMOID : EPI_BIAS);
+  else epi = EPI_PLAIN;
+  TORCH_CHECK(!(p.out_fp32 && (p.bias || p.act || p.add || p.mul)), "fp32 output supports the plain product only");
+  TORCH_CHECK(p.bias || p.act == 0, "an activation needs a bias operand (pass zeros)");
+  auto launch = [&](auto kernel, int smem) {
+    // the attribute is per kernel instantiation; setting it is cheap and idempotent
+    TRB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kernel<<<grid, kThreads, smem, stream>>>(ta, tb, p);
+  };
+#define TRB_GEMM_CASE(E)                                                                              \
+  case E:                                                                                             \
+    if (wide) launch(gemm_bf16_kernel<256, MN_MAJOR, E>, SmemLayout<256>::kTotal);                    \
+    else launch(gemm_bf16_kernel<128, MN_MAJOR, E>, SmemLayout<128>::kTotal);                         \
+    break;
+  if constexpr (MN_MAJOR) {
+    switch (epi) {
+      TRB_GEMM_CASE(EPI_F32)
+      TRB_GEMM_CASE(EPI_F32_ATOMIC)
+      default: TORCH_CHECK(false, "unsupported epilogue for the TN product");
     }
-    gemm_bf16_kernel<256, MN_MAJOR><<<grid, kThreads, smem, stream>>>(ta, tb, p);
   } else {
-    constexpr int smem = SmemLayout<128>::kTotal;
-    static bool set = false;
-    if (!set) {
-      TRB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<128, MN_MAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      set = true;
+    switch (epi) {
+      TRB_GEMM_CASE(EPI_PLAIN)
+      TRB_GEMM_CASE(EPI_BIAS)
+      TRB_GEMM_CASE(EPI_BIAS_RELU)
+      TRB_GEMM_CASE(EPI_BIAS_SIGMOID)
+      TRB_GEMM_CASE(EPI_CROSS)
+      TRB_GEMM_CASE(EPI_ADD)
+      TRB_GEMM_CASE(EPI_F32)
+      default: TORCH_CHECK(false, "unsupported epilogue for the NT product");
     }
-    gemm_bf16_kernel<128, MN_MAJOR><<<grid, kThreads, smem, stream>>>(ta, tb, p);
   }
+#undef TRB_GEMM_CASE
   TRB_CUDA_CHECK(cudaGetLastError());
 }
 

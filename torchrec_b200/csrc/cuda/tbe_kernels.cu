@@ -228,6 +228,8 @@ struct BwdParams {
   int pooled;
   float* partials;  // [2*nblocks, Dpad] fp32 scratch
   int32_t* flags;   // [2*nblocks]  slot state, see below
+  int64_t* long_list;  // [2*cap] (head block, last block) of chains left to pass 3
+  int* long_count;
   int Dpad;
   OptParams opt;
 };
@@ -518,7 +520,20 @@ __global__ void __launch_bounds__(256) tbe_bwd_block_kernel(BwdParams p) {
   }
 }
 
-// pass 2: the head block of every row that spans blocks folds the chain of partial sums
+constexpr int kSerialChain = 16;  // chains of at most this many slots are folded by one warp
+
+__device__ __forceinline__ int64_t upper_bound_key(const int64_t* __restrict__ keys, int64_t lo, int64_t hi, int64_t key) {
+  // first position in [lo, hi) whose key is greater than `key` (keys ascending)
+  while (lo < hi) {
+    const int64_t mid = lo + ((hi - lo) >> 1);
+    if (keys[mid] <= key) lo = mid + 1;
+    else hi = mid;
+  }
+  return lo;
+}
+
+// pass 2: the head block of every row that spans blocks folds the chain of partial sums.  Short chains are folded
+// by the head's warp; long chains (hot rows of a skewed id distribution) are queued for pass 3.
 template <typename emb_t, int kVecs>
 __global__ void __launch_bounds__(256) tbe_bwd_long_kernel(BwdParams p) {
   const int lane = threadIdx.x & 31;
@@ -530,6 +545,17 @@ __global__ void __launch_bounds__(256) tbe_bwd_long_kernel(BwdParams p) {
   const int f = fl >> 8;
   const int64_t end = min(p.N, (blk + 1) * kBlk);
   const int64_t key = p.sorted_keys[end - 1];
+  int64_t last_blk = 0;
+  if (lane == 0) last_blk = (upper_bound_key(p.sorted_keys, end, p.N, key) - 1) / kBlk;
+  last_blk = __shfl_sync(0xffffffffu, last_blk, 0);
+  if (last_blk - blk > kSerialChain) {
+    if (lane == 0) {
+      const int slot = atomicAdd(p.long_count, 1);
+      p.long_list[2 * slot] = blk;
+      p.long_list[2 * slot + 1] = last_blk;
+    }
+    return;
+  }
   float4 acc[kVecs];
   {
     const float* src = p.partials + (2 * blk + 1) * p.Dpad;
@@ -539,9 +565,7 @@ __global__ void __launch_bounds__(256) tbe_bwd_long_kernel(BwdParams p) {
       acc[v] = (e < p.Dpad) ? Vec4<float>::load_plain(src + e) : f4zero();
     }
   }
-  for (int64_t j = blk + 1; j < nblocks; ++j) {
-    const int fa = p.flags[2 * j];
-    if (!(fa & FLAG_USED)) break;  // defensive: chain must exist
+  for (int64_t j = blk + 1; j <= last_blk; ++j) {
     const float* src = p.partials + (2 * j) * p.Dpad;
 #pragma unroll
     for (int v = 0; v < kVecs; ++v) {
@@ -551,9 +575,64 @@ __global__ void __launch_bounds__(256) tbe_bwd_long_kernel(BwdParams p) {
         acc[v].x += x.x; acc[v].y += x.y; acc[v].z += x.z; acc[v].w += x.w;
       }
     }
-    if (!(fa & FLAG_CONT)) break;
   }
   apply_update<emb_t, kVecs>(p, key, f, acc, lane);
+}
+
+// pass 3: one CTA per queued long chain.  Warp w sums slots blk+1+w, blk+1+w+8, ... (fixed assignment, so the result
+// is deterministic), the eight sums are combined in shared memory in warp order, and warp 0 applies the update.
+template <typename emb_t, int kVecs>
+__global__ void __launch_bounds__(256) tbe_bwd_verylong_kernel(BwdParams p) {
+  __shared__ float4 red[8][kVecs][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int count = *p.long_count;
+  for (int i = blockIdx.x; i < count; i += gridDim.x) {
+    const int64_t blk = p.long_list[2 * i], last_blk = p.long_list[2 * i + 1];
+    float4 acc[kVecs];
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) acc[v] = f4zero();
+    for (int64_t j0 = blk + 1 + warp; j0 <= last_blk; j0 += 32) {
+      float4 x[4][kVecs];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t j = j0 + 8 * u;
+        const float* src = p.partials + (2 * min(j, last_blk)) * p.Dpad;
+#pragma unroll
+        for (int v = 0; v < kVecs; ++v) {
+          const int e = v * 128 + lane * 4;
+          x[u][v] = (j <= last_blk && e < p.Dpad) ? Vec4<float>::load_plain(src + e) : f4zero();
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+#pragma unroll
+        for (int v = 0; v < kVecs; ++v) {
+          acc[v].x += x[u][v].x; acc[v].y += x[u][v].y; acc[v].z += x[u][v].z; acc[v].w += x[u][v].w;
+        }
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) red[warp][v][lane] = acc[v];
+    __syncthreads();
+    if (warp == 0) {
+      const float* src = p.partials + (2 * blk + 1) * p.Dpad;  // the head's own partial
+#pragma unroll
+      for (int v = 0; v < kVecs; ++v) {
+        const int e = v * 128 + lane * 4;
+        float4 t = (e < p.Dpad) ? Vec4<float>::load_plain(src + e) : f4zero();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float4 y = red[k][v][lane];
+          t.x += y.x; t.y += y.y; t.z += y.z; t.w += y.w;
+        }
+        acc[v] = t;
+      }
+      const int f = p.flags[2 * blk + 1] >> 8;
+      const int64_t end = min(p.N, (blk + 1) * kBlk);
+      apply_update<emb_t, kVecs>(p, p.sorted_keys[end - 1], f, acc, lane);
+    }
+    __syncthreads();
+  }
 }
 
 // keys: global row id of every id; src: bag id (pooled) or position (unpooled)
@@ -809,6 +888,8 @@ void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10:
   const int64_t nblocks = (N + kBlk - 1) / kBlk;
   at::Tensor partials = at::empty({2 * nblocks * Dpad}, weights.options().dtype(at::kFloat));
   at::Tensor flags = at::empty({2 * nblocks}, weights.options().dtype(at::kInt));
+  at::Tensor long_list = at::empty({2 * (nblocks / kSerialChain + 1)}, weights.options().dtype(at::kLong));
+  at::Tensor long_count = at::zeros({1}, weights.options().dtype(at::kInt));
   BwdParams p;
   p.weights = weights.data_ptr();
   p.mom1 = mom1.has_value() && mom1->defined() ? mom1->data_ptr<float>() : nullptr;
@@ -829,6 +910,8 @@ void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10:
   p.pooled = pooled ? 1 : 0;
   p.partials = partials.data_ptr<float>();
   p.flags = flags.data_ptr<int32_t>();
+  p.long_list = long_list.data_ptr<int64_t>();
+  p.long_count = long_count.data_ptr<int>();
   p.Dpad = Dpad;
   p.opt.type = int(opt_type);
   p.opt.lr = float(lr);
@@ -847,6 +930,7 @@ void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10:
     TRB_DISPATCH_VECS(nv, [&] {
       tbe_bwd_block_kernel<emb_t, kVecs><<<blocks, threads, 0, stream>>>(p);
       tbe_bwd_long_kernel<emb_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+      tbe_bwd_verylong_kernel<emb_t, kVecs><<<296, 256, 0, stream>>>(p);
     });
   });
   TRB_CUDA_CHECK(cudaGetLastError());

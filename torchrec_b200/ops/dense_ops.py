@@ -87,7 +87,11 @@ def gemm_nt(
     out_dtype: torch.dtype = torch.bfloat16,
 ) -> torch.Tensor:
     """``act(a @ b.T + bias)`` with ``a [M,K]``, ``b [N,K]`` bf16 row-major."""
-    if a.is_cuda and _GEMM_BACKEND == "tcgen05" and _ext.has_cuda_ext() and _tcgen05_ok(a, b):
+    if a.is_cuda and _GEMM_BACKEND == "tcgen05" and _ext.has_cuda_ext() and _tcgen05_ok(a, b) and not (
+        out_dtype == torch.float32 and (bias is not None or act != ACT_NONE)
+    ):
+        if bias is None and act != ACT_NONE:
+            bias = torch.zeros(b.shape[0], dtype=torch.float32, device=a.device)  # the fused epilogues are bias+act
         return torch.ops.trb200.gemm_nt_bf16(a, b, bias, act, out_dtype == torch.float32)
     y = torch.matmul(a, b.t())
     if bias is not None:
