@@ -938,6 +938,153 @@ void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10:
 
 }  // namespace trb
 
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free C entry point (declared and documented in tbe_noalloc.h).  The scratch that the operator above
+// takes from the caching allocator lives here in a fixed device array; the host reaches it through the address
+// that cudaGetSymbolAddress reports, looked up once per device.
+// ---------------------------------------------------------------------------------------------------------------
+#include "tbe_noalloc.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+namespace {
+
+constexpr size_t kNaMaxBlocks = TRB_NOALLOC_MAX_ENTRIES / trb::kBlk;                               // 4096
+constexpr size_t kNaPartialBytes = size_t(2) * TRB_NOALLOC_MAX_BLOCK_DIM * sizeof(float);          // 4 MiB
+constexpr size_t kNaFlagBytes = size_t(2) * kNaMaxBlocks * sizeof(int32_t);                        // 32 KiB
+constexpr size_t kNaLongListBytes = ((2 * (kNaMaxBlocks / trb::kSerialChain + 1) * sizeof(int64_t)) + 255) / 256 * 256;
+constexpr size_t kNaCountBytes = 256;
+constexpr size_t kNaOffFlags = kNaPartialBytes;
+constexpr size_t kNaOffLongList = kNaOffFlags + kNaFlagBytes;
+constexpr size_t kNaOffCount = kNaOffLongList + kNaLongListBytes;
+constexpr size_t kNaScratchBytes = kNaOffCount + kNaCountBytes;
+
+static __device__ __align__(256) unsigned char g_tbe_noalloc_scratch[kNaScratchBytes];
+
+constexpr int kNaMaxDevices = 64;
+std::mutex g_na_mutex;
+unsigned char* g_na_scratch_ptr[kNaMaxDevices] = {};  // device address of the array, per device
+
+int na_fail(int code, char* errbuf, size_t errbuf_len, const char* fmt, ...) {
+  if (errbuf != nullptr && errbuf_len > 0) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(errbuf, errbuf_len, fmt, ap);
+    va_end(ap);
+  }
+  return code;
+}
+
+template <typename emb_t>
+void na_launch(int nv, int64_t blocks, int threads, cudaStream_t stream, const trb::BwdParams& p) {
+  TRB_DISPATCH_VECS(nv, [&] {
+    trb::tbe_bwd_block_kernel<emb_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+    trb::tbe_bwd_long_kernel<emb_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+    trb::tbe_bwd_verylong_kernel<emb_t, kVecs><<<296, 256, 0, stream>>>(p);
+  });
+}
+
+}  // namespace
+
+extern "C" int trb_tbe_backward_apply_noalloc(const trb_tbe_bwd_noalloc_args* a, void* stream_v, char* errbuf,
+                                              size_t errbuf_len) {
+  if (a == nullptr) return na_fail(TRB_NOALLOC_E_BAD_ARG, errbuf, errbuf_len, "args is null");
+  if (a->N == 0) return TRB_NOALLOC_OK;
+  if (a->N < 0 || a->weights == nullptr || a->meta == nullptr || a->sorted_keys == nullptr || a->sorted_src == nullptr ||
+      a->grad == nullptr)
+    return na_fail(TRB_NOALLOC_E_BAD_ARG, errbuf, errbuf_len, "weights, meta, sorted_keys, sorted_src and grad must be set and N >= 0");
+  if (a->weights_dtype < 0 || a->weights_dtype > 2 || a->grad_dtype < 0 || a->grad_dtype > 2)
+    return na_fail(TRB_NOALLOC_E_BAD_ARG, errbuf, errbuf_len, "dtype codes are 0 (fp32), 1 (fp16), 2 (bf16)");
+  if (a->max_D <= 0 || a->max_D % 4 != 0 || a->max_D > 1024)
+    return na_fail(TRB_NOALLOC_E_BAD_ARG, errbuf, errbuf_len, "max_D=%d must be a positive multiple of 4, at most 1024", a->max_D);
+  if (a->F <= 0 || a->B <= 0) return na_fail(TRB_NOALLOC_E_BAD_ARG, errbuf, errbuf_len, "F and B must be positive");
+  if (!a->pooled && a->src_feature == nullptr)
+    return na_fail(TRB_NOALLOC_E_BAD_ARG, errbuf, errbuf_len, "the unpooled backward needs src_feature");
+  if (a->opt_type == trb::OPT_DENSE_GRAD && a->dense_grad == nullptr)
+    return na_fail(TRB_NOALLOC_E_BAD_ARG, errbuf, errbuf_len, "opt_type 100 needs dense_grad");
+  const int64_t nblocks = (a->N + trb::kBlk - 1) / trb::kBlk;
+  if (a->N > TRB_NOALLOC_MAX_ENTRIES || nblocks * int64_t(a->max_D) > TRB_NOALLOC_MAX_BLOCK_DIM)
+    return na_fail(TRB_NOALLOC_E_TOO_LARGE, errbuf, errbuf_len,
+                   "N=%lld entries with max_D=%d is beyond the fixed scratch: N <= %d and ceil(N/64)*max_D <= %d; "
+                   "use trb200::tbe_backward_apply for larger batches",
+                   (long long)a->N, a->max_D, TRB_NOALLOC_MAX_ENTRIES, TRB_NOALLOC_MAX_BLOCK_DIM);
+
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return na_fail(TRB_NOALLOC_E_CUDA, errbuf, errbuf_len, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kNaMaxDevices) return na_fail(TRB_NOALLOC_E_DEVICE, errbuf, errbuf_len, "device %d out of range", dev);
+  cudaPointerAttributes attr;
+  e = cudaPointerGetAttributes(&attr, a->weights);
+  if (e != cudaSuccess) return na_fail(TRB_NOALLOC_E_CUDA, errbuf, errbuf_len, "cudaPointerGetAttributes: %s", cudaGetErrorString(e));
+  if (attr.type != cudaMemoryTypeDevice || attr.device != dev)
+    return na_fail(TRB_NOALLOC_E_DEVICE, errbuf, errbuf_len, "weights are not device memory of the current device %d", dev);
+
+  // set-up, once per device with that device current: the device address of the scratch array
+  unsigned char* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_na_mutex);
+    if (g_na_scratch_ptr[dev] == nullptr) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress((void**)&ptr, g_tbe_noalloc_scratch);
+      if (e != cudaSuccess || ptr == nullptr)
+        return na_fail(TRB_NOALLOC_E_CUDA, errbuf, errbuf_len, "cudaGetSymbolAddress(scratch) on device %d: %s", dev,
+                       cudaGetErrorString(e));
+      g_na_scratch_ptr[dev] = static_cast<unsigned char*>(ptr);
+    }
+    scratch = g_na_scratch_ptr[dev];
+  }
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  trb::BwdParams p;
+  p.weights = a->weights;
+  p.mom1 = a->mom1;
+  p.mom2 = a->mom2;
+  p.dense_grad = a->dense_grad;
+  p.meta = a->meta;
+  p.sorted_keys = a->sorted_keys;
+  p.sorted_src = a->sorted_src;
+  p.sorted_w = a->sorted_w;
+  p.src_feature = a->src_feature;
+  p.grad = a->grad;
+  p.grad_dtype = a->grad_dtype;
+  p.grad_stride = a->grad_stride;
+  p.bag_scale = a->bag_scale;
+  p.N = a->N;
+  p.B = a->B;
+  p.F = a->F;
+  p.pooled = a->pooled ? 1 : 0;
+  p.partials = reinterpret_cast<float*>(scratch);
+  p.flags = reinterpret_cast<int32_t*>(scratch + kNaOffFlags);
+  p.long_list = reinterpret_cast<int64_t*>(scratch + kNaOffLongList);
+  p.long_count = reinterpret_cast<int*>(scratch + kNaOffCount);
+  p.Dpad = a->max_D;
+  p.opt.type = a->opt_type;
+  p.opt.lr = a->lr;
+  p.opt.eps = a->eps;
+  p.opt.beta1 = a->beta1;
+  p.opt.beta2 = a->beta2;
+  p.opt.weight_decay = a->weight_decay;
+  const int64_t step = a->step > 1 ? a->step : 1;
+  p.opt.bias_corr1 = float(1.0 - std::pow(double(a->beta1), double(step)));
+  p.opt.bias_corr2 = float(1.0 - std::pow(double(a->beta2), double(step)));
+  p.opt.max_grad = a->max_grad;
+
+  // the only word that must start at zero: the queue length of long chains (pass 1 writes every flag it covers)
+  e = cudaMemsetAsync(p.long_count, 0, sizeof(int), stream);
+  if (e != cudaSuccess) return na_fail(TRB_NOALLOC_E_CUDA, errbuf, errbuf_len, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  const int nv = a->max_D <= 128 ? 1 : (a->max_D <= 256 ? 2 : (a->max_D <= 512 ? 4 : 8));
+  const int threads = 256;
+  const int64_t blocks = (nblocks * 32 + threads - 1) / threads;
+  if (a->weights_dtype == trb::OUT_F32) na_launch<float>(nv, blocks, threads, stream, p);
+  else if (a->weights_dtype == trb::OUT_F16) na_launch<__half>(nv, blocks, threads, stream, p);
+  else na_launch<__nv_bfloat16>(nv, blocks, threads, stream, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return na_fail(TRB_NOALLOC_E_CUDA, errbuf, errbuf_len, "kernel launch: %s", cudaGetErrorString(e));
+  return TRB_NOALLOC_OK;
+}
+
 TORCH_LIBRARY_FRAGMENT(trb200, m) {
   m.def(
       "tbe_forward(Tensor weights, Tensor meta, Tensor indices, Tensor offsets, Tensor? psw, int B, int total_D, "
