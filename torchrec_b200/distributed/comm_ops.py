@@ -335,21 +335,24 @@ class All2All_Seq_Req(Function):
         qctx = None
         if forward_recat is not None and lengths.numel() > 0 and not a2ai.variable_batch_size:
             # reorder (feature, source rank) -> (source rank, feature) so that each peer's rows are contiguous
-            _, sharded_input_embeddings, _ = sops.permute_2D_sparse_data(
-                forward_recat, lengths.view(forward_recat.numel(), -1) if lengths.dim() == 1 else lengths,
+            plen, sharded_input_embeddings, _ = sops.permute_2D_sparse_data(
+                forward_recat, lengths.reshape(forward_recat.numel(), -1),
                 sharded_input_embeddings.reshape(-1), None, sharded_input_embeddings.numel(),
             )
+            a2ai.permuted_lengths_after_sparse_data_all2all = plen
         elif forward_recat is not None and lengths.numel() > 0:
-            _, sharded_input_embeddings, _ = sops.permute_1D_sparse_data(
+            plen, sharded_input_embeddings, _ = sops.permute_1D_sparse_data(
                 forward_recat, lengths.view(-1), sharded_input_embeddings.reshape(-1), None, sharded_input_embeddings.numel()
             )
+            a2ai.permuted_lengths_after_sparse_data_all2all = plen
         del local_T
         sharded_input_embeddings = sharded_input_embeddings.reshape(-1)
         if a2ai.codecs is not None:
             qctx = a2ai.codecs.forward.create_context()
             sharded_input_embeddings = a2ai.codecs.forward.encode(sharded_input_embeddings, qctx)
-        out_splits = [s * D for s in a2ai.output_splits]
-        in_splits = [s * D for s in a2ai.input_splits]
+        # rows travel the routes of the ids in reverse: what the id all-to-all received from a peer is sent back to it
+        out_splits = [s * D for s in a2ai.input_splits]
+        in_splits = [s * D for s in a2ai.output_splits]
         sharded_output = torch.empty(sum(out_splits), dtype=sharded_input_embeddings.dtype, device=sharded_input_embeddings.device)
         with record_function("## alltoall_seq_embedding_fwd_single ##"):
             req = _all_to_all_single(sharded_output, sharded_input_embeddings, out_splits, in_splits, pg, async_op=True)
@@ -374,11 +377,12 @@ class All2All_Seq_Req(Function):
         backward_recat = a2ai.backward_recat_tensor
         lengths = (a2ai.permuted_lengths_after_sparse_data_all2all if a2ai.permuted_lengths_after_sparse_data_all2all is not None else a2ai.lengths_after_sparse_data_all2all)
         if backward_recat is not None and lengths.numel() > 0:
-            plen = lengths * D
+            # the permuted lengths saved by forward are already in elements (rows * D)
+            plen = lengths if a2ai.permuted_lengths_after_sparse_data_all2all is not None else lengths * D
             if a2ai.variable_batch_size:
                 _, grad, _ = sops.permute_1D_sparse_data(backward_recat, plen.view(-1), grad.reshape(-1), None, grad.numel())
             else:
-                _, grad, _ = sops.permute_2D_sparse_data(backward_recat, plen.view(backward_recat.numel(), -1), grad.reshape(-1), None, grad.numel())
+                _, grad, _ = sops.permute_2D_sparse_data(backward_recat, plen.reshape(backward_recat.numel(), -1), grad.reshape(-1), None, grad.numel())
         grad_input = grad.view(-1, D)
         if GRADIENT_DIVISION:
             grad_input = grad_input / dist.get_world_size(ctx.pg)
@@ -409,8 +413,8 @@ class All2All_Seq_Req_Wait(Function):
         if a2ai.codecs is not None:
             qctx = a2ai.codecs.backward.create_context()
             g = a2ai.codecs.backward.encode(g, qctx)
-        out_splits = [s * D for s in a2ai.input_splits]
-        in_splits = [s * D for s in a2ai.output_splits]
+        out_splits = [s * D for s in a2ai.output_splits]
+        in_splits = [s * D for s in a2ai.input_splits]
         grad_input = torch.empty(sum(out_splits), device=g.device, dtype=g.dtype)
         with record_function("## alltoall_seq_embedding_bwd_single ##"):
             req = _all_to_all_single(grad_input, g, out_splits, in_splits, ctx.pg, async_op=True)

@@ -156,3 +156,294 @@ class EmbeddingCollectionAwaitable(LazyAwaitable[Dict[str, JaggedTensor]]):
                 )
             )
         return jt_dict
+
+
+def _dedup_indices(ctx: EmbeddingCollectionContext, features: KeyedJaggedTensor, hash_offsets: torch.Tensor) -> KeyedJaggedTensor:
+    """Replace ``features`` by its per-feature unique ids (one id per bag, lengths all 1 where kept) and
+    remember in ``ctx`` how to expand looked-up rows back: rows for the original ids are
+    ``unique_rows[reverse_indices]``.  Ids of different features never merge (offset by ``hash_offsets``)."""
+    with record_function("## dedup_ec_indices ##"):
+        lpk = features.length_per_key()
+        F = len(lpk)
+        values = features.values()
+        feat_of = torch.repeat_interleave(
+            torch.arange(F, device=values.device), torch.tensor(lpk, device=values.device), output_size=int(sum(lpk))
+        )
+        keyed = values.to(torch.int64) + hash_offsets[feat_of]
+        uniq, reverse = torch.unique(keyed, sorted=True, return_inverse=True)
+        # sorted by (feature, id): unique ids stay key-major
+        ufeat = torch.searchsorted(hash_offsets, uniq, right=True) - 1
+        counts = torch.bincount(ufeat, minlength=F)
+        stride = features.stride()
+        # spread each feature's unique ids over its `stride` bags: first bags get ceil, rest floor (any split works,
+        # the rows are re-expanded by `reverse` and the original lengths afterwards)
+        base = torch.div(counts, stride, rounding_mode="floor")
+        rem = counts - base * stride
+        ar = torch.arange(stride, device=values.device)
+        lengths = (base.unsqueeze(1) + (ar.unsqueeze(0) < rem.unsqueeze(1)).to(base.dtype)).reshape(-1)
+        ctx.input_features.append(features)
+        ctx.reverse_indices.append(reverse)
+        return KeyedJaggedTensor(
+            keys=features.keys(), values=(uniq - hash_offsets[ufeat]).to(values.dtype), lengths=lengths.to(features.lengths().dtype),
+            stride=stride,
+        )
+
+
+class ShardedEmbeddingCollection(
+    ShardedEmbeddingModule[KJTList, List[torch.Tensor], Dict[str, JaggedTensor], EmbeddingCollectionContext],
+    FusedOptimizerModule,
+):
+    """Sharded counterpart of ``EmbeddingCollection``; built by ``EmbeddingCollectionSharder``.
+    Table-wise, row-wise, column-wise and data-parallel placements (``torchrec/distributed/embedding.py:397``)."""
+
+    _TABLE_ATTR: str = "embeddings"
+
+    def _table_configs(self):
+        return self._embedding_configs
+
+    def __init__(self, module: EmbeddingCollection, table_name_to_parameter_sharding: Dict[str, ParameterSharding], env: ShardingEnv,
+                 fused_params: Optional[Dict[str, Any]] = None, device: Optional[torch.device] = None,
+                 qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None, use_index_dedup: bool = False,
+                 module_fqn: Optional[str] = None) -> None:
+        super().__init__(qcomm_codecs_registry=qcomm_codecs_registry)
+        self._module_fqn = module_fqn
+        self._embedding_configs: List[EmbeddingConfig] = module.embedding_configs()
+        self._table_names: List[str] = [c.name for c in self._embedding_configs]
+        self._table_name_to_config: Dict[str, EmbeddingConfig] = {c.name: c for c in self._embedding_configs}
+        self.module_sharding_plan: EmbeddingModuleShardingPlan = EmbeddingModuleShardingPlan(
+            {t: ps for t, ps in table_name_to_parameter_sharding.items() if t in self._table_names}
+        )
+        self._env = env
+        self._device = device
+        self._embedding_dim: int = module.embedding_dim()
+        self._need_indices: bool = module.need_indices()
+        self._use_index_dedup: bool = use_index_dedup or get_ec_index_dedup()
+        self.sharding_type_to_sharding_infos = self.create_grouped_sharding_infos(module, table_name_to_parameter_sharding, fused_params)
+        self._sharding_types: List[str] = list(self.sharding_type_to_sharding_infos.keys())
+        self._embedding_shardings = [
+            create_embedding_sharding(st, infos, env, device, qcomm_codecs_registry=self.qcomm_codecs_registry)
+            for st, infos in self.sharding_type_to_sharding_infos.items()
+        ]
+        self._sharding_type_to_sharding = dict(zip(self._sharding_types, self._embedding_shardings))
+        self._input_dists: List[nn.Module] = []
+        self._lookups: List[nn.Module] = [s.create_lookup() for s in self._embedding_shardings]
+        self._output_dists: List[nn.Module] = [s.create_output_dist() for s in self._embedding_shardings]
+        self._feature_splits: List[int] = []
+        self._features_order: List[int] = []
+        self._has_uninitialized_input_dist: bool = True
+        self._has_features_permute: bool = True
+        self._embedding_names_per_sharding: List[List[str]] = [s.embedding_names() for s in self._embedding_shardings]
+        self._features_to_permute_indices: Dict[str, List[int]] = self._column_shard_order()
+        for i, (sharding, lookup) in enumerate(zip(self._embedding_shardings, self._lookups)):
+            if isinstance(sharding, DpSequenceEmbeddingSharding) and env.process_group is not None and dist.get_backend(env.process_group) != "fake":
+                self._lookups[i] = DistributedDataParallel(
+                    module=lookup, device_ids=[device] if device is not None and device.type == "cuda" else None,
+                    process_group=env.process_group, gradient_as_bucket_view=True, broadcast_buffers=True, static_graph=True,
+                )
+        # parameters / ShardedTensor state: same layout logic as the pooled module, under "embeddings."
+        from torchrec_b200.distributed.embeddingbag import ShardedEmbeddingBagCollection as _EBC
+
+        _EBC._initialize_torch_state(self)
+        optims = []
+        for lookup in self._lookups:
+            lk = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
+            for _, m in lk.named_modules():
+                if isinstance(m, FusedOptimizerModule):
+                    m.fused_optimizer.params = {"embeddings." + k: w for k, w in m.fused_optimizer.params.items()}
+                    optims.append(("", m.fused_optimizer))
+        self._optim: CombinedOptimizer = CombinedOptimizer(optims)
+        self._hash_offsets_per_sharding: List[Optional[torch.Tensor]] = []
+
+    # ---- plan -> sharding infos ---------------------------------------------------------------------
+    @classmethod
+    def create_grouped_sharding_infos(cls, module: EmbeddingCollection, table_name_to_parameter_sharding: Dict[str, ParameterSharding],
+                                      fused_params: Optional[Dict[str, Any]]) -> Dict[str, List[EmbeddingShardingInfo]]:
+        fused_params = fused_params or {}
+        shared_feature: Dict[str, bool] = {}
+        for cfg in module.embedding_configs():
+            if not cfg.feature_names:
+                cfg.feature_names = [cfg.name]
+            for f in cfg.feature_names:
+                shared_feature[f] = f in shared_feature
+        out: Dict[str, List[EmbeddingShardingInfo]] = defaultdict(list)
+        parameter_by_name = dict(module.named_parameters())
+        state_dict = module.state_dict()
+        for config in module.embedding_configs():
+            table_name = config.name
+            assert table_name in table_name_to_parameter_sharding, f"{table_name} not in table_name_to_parameter_sharding"
+            ps = table_name_to_parameter_sharding[table_name]
+            if ps.compute_kernel not in [k.value for k in EmbeddingComputeKernel]:
+                raise ValueError(f"Compute kernel not supported {ps.compute_kernel}")
+            param_name = "embeddings." + table_name + ".weight"
+            assert param_name in parameter_by_name or param_name in state_dict
+            param = parameter_by_name.get(param_name, state_dict.get(param_name))
+            optimizer_params = getattr(param, "_optimizer_kwargs", [{}])
+            optimizer_classes = getattr(param, "_optimizer_classes", [None])
+            assert len(optimizer_classes) == 1 and len(optimizer_params) == 1, "Only support 1 optimizer per table"
+            optimizer_params = copy.deepcopy(optimizer_params[0])
+            if optimizer_classes[0]:
+                optimizer_params["optimizer"] = optimizer_type_to_emb_opt_type(optimizer_classes[0])
+            per_table = convert_to_fbgemm_types(add_params_from_parameter_sharding(merge_fused_params(fused_params, optimizer_params), ps))
+            out[ps.sharding_type].append(
+                EmbeddingShardingInfo(
+                    embedding_config=EmbeddingTableConfig(
+                        num_embeddings=config.num_embeddings, embedding_dim=config.embedding_dim, name=config.name,
+                        data_type=config.data_type, feature_names=copy.deepcopy(config.feature_names), pooling=PoolingType.NONE,
+                        is_weighted=False, has_feature_processor=False,
+                        embedding_names=[f + "@" + config.name if shared_feature[f] else f for f in config.feature_names],
+                        weight_init_max=config.weight_init_max, weight_init_min=config.weight_init_min, init_fn=config.init_fn,
+                        total_num_buckets=getattr(config, "total_num_buckets", None),
+                        use_virtual_table=getattr(config, "use_virtual_table", False),
+                    ),
+                    param_sharding=ps, param=param, fused_params=per_table,
+                )
+            )
+        return out
+
+    def _column_shard_order(self) -> Dict[str, List[int]]:
+        """For every embedding name split column-wise: the order in which its pieces (as they appear in the
+        sharding's embedding names, i.e. by rank) must be concatenated to restore ascending columns."""
+        out: Dict[str, List[int]] = {}
+        sharding = self._sharding_type_to_sharding.get(ShardingType.COLUMN_WISE.value)
+        if sharding is None:
+            return out
+        col_offsets: Dict[str, List[int]] = defaultdict(list)
+        for table in sharding.embedding_tables():
+            off = table.local_metadata.shard_offsets[1] if table.local_metadata is not None else 0
+            for name in table.embedding_names:
+                col_offsets[name].append(off)
+        for name, offs in col_offsets.items():
+            order = sorted(range(len(offs)), key=lambda i: offs[i])
+            if order != list(range(len(offs))):
+                out[name] = order
+        return out
+
+    # ---- parameters / optimizer ---------------------------------------------------------------------
+    def reset_parameters(self) -> None:
+        return
+
+    def named_parameters(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True) -> Iterator[Tuple[str, nn.Parameter]]:
+        for name, m in self.embeddings.items():
+            yield append_prefix(prefix, f"embeddings.{name}.weight"), m.weight
+
+    def sharded_parameter_names(self, prefix: str = "") -> Iterator[str]:
+        for name in self._model_parallel_name_to_local_shards.keys():
+            yield append_prefix(prefix, f"embeddings.{name}.weight")
+
+    @staticmethod
+    def _pre_load_state_dict_hook(self, state_dict, prefix, *args) -> None:
+        from torchrec_b200.distributed.embeddingbag import ShardedEmbeddingBagCollection as _EBC
+
+        _EBC._pre_load_state_dict_hook(self, state_dict, prefix, *args)
+
+    @property
+    def fused_optimizer(self) -> KeyedOptimizer:
+        return self._optim
+
+    @property
+    def shardings(self) -> Dict[str, EmbeddingSharding]:
+        return dict(zip(self._sharding_types, self._embedding_shardings))
+
+    @property
+    def unsharded_module_type(self) -> Type[EmbeddingCollection]:
+        return EmbeddingCollection
+
+    def create_context(self) -> EmbeddingCollectionContext:
+        return EmbeddingCollectionContext(sharding_contexts=[])
+
+    # ---- the three stages ---------------------------------------------------------------------------
+    def _create_input_dist(self, input_feature_names: List[str]) -> None:
+        feature_names: List[str] = []
+        for sharding in self._embedding_shardings:
+            self._input_dists.append(sharding.create_input_dist())
+            feature_names.extend(sharding.feature_names())
+            self._feature_splits.append(len(sharding.feature_names()))
+            hash_sizes = [0]
+            for t in sharding.embedding_tables():
+                for _ in t.feature_names:
+                    hash_sizes.append(hash_sizes[-1] + t.num_embeddings)
+            dev = self._device if self._device is not None and self._device.type != "meta" else torch.device("cpu")
+            self._hash_offsets_per_sharding.append(torch.tensor(hash_sizes, dtype=torch.int64, device=dev))
+        if feature_names == input_feature_names:
+            self._has_features_permute = False
+        else:
+            self._features_order = [input_feature_names.index(f) for f in feature_names]
+            dev = self._device if self._device is not None and self._device.type != "meta" else torch.device("cpu")
+            self.register_buffer("_features_order_tensor", torch.tensor(self._features_order, device=dev, dtype=torch.int32), persistent=False)
+
+    def input_dist(self, ctx: EmbeddingCollectionContext, features: KeyedJaggedTensor) -> Awaitable[Awaitable[KJTList]]:
+        assert not features.variable_stride_per_key(), "variable batch per feature is not supported for sequence embeddings"
+        if self._has_uninitialized_input_dist:
+            self._create_input_dist(features.keys())
+            self._has_uninitialized_input_dist = False
+        with torch.no_grad():
+            if self._has_features_permute:
+                features = features.permute(self._features_order, self._features_order_tensor)
+            features_by_shards = features.split(self._feature_splits)
+            awaitables = []
+            for i, (input_dist, feats) in enumerate(zip(self._input_dists, features_by_shards)):
+                if self._use_index_dedup and feats.values().numel() > 0:
+                    feats = _dedup_indices(ctx, feats, self._hash_offsets_per_sharding[i])
+                elif self._use_index_dedup:
+                    ctx.input_features.append(feats)
+                    ctx.reverse_indices.append(torch.empty(0, dtype=torch.int64, device=feats.values().device))
+                awaitables.append(input_dist(feats))
+                ctx.sharding_contexts.append(
+                    SequenceShardingContext(
+                        features_before_input_dist=feats,
+                        unbucketize_permute_tensor=input_dist.unbucketize_permute_tensor if isinstance(input_dist, RwSparseFeaturesDist) else None,
+                    )
+                )
+            return KJTListSplitsAwaitable(awaitables, ctx, self._module_fqn, self._sharding_types)
+
+    def compute(self, ctx: EmbeddingCollectionContext, dist_input: KJTList) -> List[torch.Tensor]:
+        ret: List[torch.Tensor] = []
+        for lookup, features, sctx, sharding in zip(self._lookups, dist_input, ctx.sharding_contexts, self._embedding_shardings):
+            sctx.lengths_after_input_dist = features.lengths().view(-1, features.stride())
+            embs = lookup(features)
+            if embs.dim() == 1:  # this rank holds no table of the sharding: keep the row width for the all-to-all
+                # (requires_grad so that this rank still takes part in the backward all-to-all)
+                embs = torch.empty((0, sharding.embedding_dims()[0]), dtype=embs.dtype, device=embs.device, requires_grad=True)
+            ret.append(embs)
+        return ret
+
+    def output_dist(self, ctx: EmbeddingCollectionContext, output: List[torch.Tensor]) -> LazyAwaitable[Dict[str, JaggedTensor]]:
+        awaitables: List[Awaitable[torch.Tensor]] = []
+        features_before: List[KeyedJaggedTensor] = []
+        for odist, embeddings, sctx in zip(self._output_dists, output, ctx.sharding_contexts):
+            awaitables.append(odist(embeddings, sctx))
+            features_before.append(sctx.features_before_input_dist)
+        return EmbeddingCollectionAwaitable(
+            awaitables_per_sharding=awaitables, features_per_sharding=features_before,
+            embedding_names_per_sharding=self._embedding_names_per_sharding, need_indices=self._need_indices,
+            features_to_permute_indices=self._features_to_permute_indices, ctx=ctx,
+        )
+
+    def compute_and_output_dist(self, ctx: EmbeddingCollectionContext, input: KJTList) -> LazyAwaitable[Dict[str, JaggedTensor]]:
+        return self.output_dist(ctx, self.compute(ctx, input))
+
+
+class EmbeddingCollectionSharder(BaseEmbeddingSharder[EmbeddingCollection]):
+    """Shards an ``EmbeddingCollection`` (``torchrec/distributed/embedding.py:1675``)."""
+
+    def __init__(self, fused_params: Optional[Dict[str, Any]] = None, qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None,
+                 use_index_dedup: bool = False) -> None:
+        super().__init__(fused_params, qcomm_codecs_registry)
+        self._use_index_dedup = use_index_dedup
+
+    def shard(self, module: EmbeddingCollection, params: Dict[str, ParameterSharding], env: ShardingEnv,
+              device: Optional[torch.device] = None, module_fqn: Optional[str] = None) -> ShardedEmbeddingCollection:
+        return ShardedEmbeddingCollection(
+            module, params, env, self.fused_params, device, qcomm_codecs_registry=self.qcomm_codecs_registry,
+            use_index_dedup=self._use_index_dedup, module_fqn=module_fqn,
+        )
+
+    def shardable_parameters(self, module: EmbeddingCollection) -> Dict[str, nn.Parameter]:
+        return {name.split(".")[0]: param for name, param in module.embeddings.named_parameters()}
+
+    def sharding_types(self, compute_device_type: str) -> List[str]:
+        return [ShardingType.DATA_PARALLEL.value, ShardingType.TABLE_WISE.value, ShardingType.COLUMN_WISE.value, ShardingType.ROW_WISE.value]
+
+    @property
+    def module_type(self) -> Type[EmbeddingCollection]:
+        return EmbeddingCollection

@@ -236,6 +236,11 @@ class ShardedEmbeddingBagCollection(
 ):
     """Sharded counterpart of ``EmbeddingBagCollection``; built by ``EmbeddingBagCollectionSharder``."""
 
+    _TABLE_ATTR: str = "embedding_bags"  # name of the ModuleDict that holds ``<table>.weight``
+
+    def _table_configs(self):
+        return self._embedding_bag_configs
+
     def __init__(
         self,
         module: EmbeddingBagCollectionInterface,
@@ -378,9 +383,10 @@ class ShardedEmbeddingBagCollection(
                 continue
             self._model_parallel_name_to_local_shards[table_name] = []
             model_parallel_name_to_compute_kernel[table_name] = ps.compute_kernel
-        for cfg in self._embedding_bag_configs:
+        for cfg in self._table_configs():
             self._name_to_table_size[cfg.name] = (cfg.num_embeddings, cfg.embedding_dim)
-        self.embedding_bags: nn.ModuleDict = nn.ModuleDict()
+        setattr(self, self._TABLE_ATTR, nn.ModuleDict())
+        table_modules: nn.ModuleDict = getattr(self, self._TABLE_ATTR)
         tables_by_name: Dict[str, List[Tuple[Any, torch.Tensor]]] = defaultdict(list)
         for sharding_type, lookup in zip(self._sharding_types, self._lookups):
             lk = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
@@ -394,7 +400,7 @@ class ShardedEmbeddingBagCollection(
                         from torchrec_b200.distributed.batched_embedding_kernel import TableBatchedEmbeddingSlice
 
                         m.register_parameter("weight", TableBatchedEmbeddingSlice(w, offs[i], offs[i + 1], t.local_rows, t.local_cols))
-                        self.embedding_bags[t.name] = m
+                        table_modules[t.name] = m
                 continue
             for emb in lk.emb_modules:
                 for t, w in zip(emb.config.embedding_tables, emb.split_embedding_weights()):
@@ -404,7 +410,7 @@ class ShardedEmbeddingBagCollection(
             local = tables_by_name.get(table_name, [])
             self._model_parallel_name_to_local_shards[table_name] = local
             m = nn.Module()
-            self.embedding_bags[table_name] = m
+            table_modules[table_name] = m
             # a rank may hold no shard of a table (table-wise on another rank): expose an empty parameter
             if local:
                 if len(local) == 1:
@@ -440,7 +446,7 @@ class ShardedEmbeddingBagCollection(
 
         def post_state_dict_hook(module, destination, prefix, _local_metadata) -> None:
             for name, st in module._model_parallel_name_to_sharded_tensor.items():
-                key = f"{prefix}embedding_bags.{name}.weight"
+                key = f"{prefix}{module._TABLE_ATTR}.{name}.weight"
                 if st is not None:
                     destination[key] = st
                 elif key in destination and not module._model_parallel_name_to_local_shards.get(name):
@@ -455,7 +461,7 @@ class ShardedEmbeddingBagCollection(
         """Copy incoming (sharded or full) tensors into the local shard views, then hand nn.Module the
         local parameter itself so that its own copy is a no-op."""
         for name in list(self._model_parallel_name_to_local_shards.keys()):
-            key = f"{prefix}embedding_bags.{name}.weight"
+            key = f"{prefix}{self._TABLE_ATTR}.{name}.weight"
             if key not in state_dict:
                 continue
             src = state_dict[key]
@@ -478,7 +484,7 @@ class ShardedEmbeddingBagCollection(
                         w.detach().copy_(src[ro: ro + rs, co: co + cs])
                 elif local and tuple(src.shape) == tuple(local[0][1].shape):
                     local[0][1].detach().copy_(src)
-            state_dict[key] = self.embedding_bags[name].weight.detach()
+            state_dict[key] = getattr(self, self._TABLE_ATTR)[name].weight.detach()
 
     def reset_parameters(self) -> None:
         if self._device is not None and self._device.type == "meta":
@@ -488,12 +494,12 @@ class ShardedEmbeddingBagCollection(
 
     # ---- parameters / optimizer ---------------------------------------------------------------------
     def named_parameters(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True) -> Iterator[Tuple[str, nn.Parameter]]:
-        for name, m in self.embedding_bags.items():
-            yield append_prefix(prefix, f"embedding_bags.{name}.weight"), m.weight
+        for name, m in getattr(self, self._TABLE_ATTR).items():
+            yield append_prefix(prefix, f"{self._TABLE_ATTR}.{name}.weight"), m.weight
 
     def sharded_parameter_names(self, prefix: str = "") -> Iterator[str]:
         for name in self._model_parallel_name_to_local_shards.keys():
-            yield append_prefix(prefix, f"embedding_bags.{name}.weight")
+            yield append_prefix(prefix, f"{self._TABLE_ATTR}.{name}.weight")
 
     @property
     def fused_optimizer(self) -> KeyedOptimizer:
