@@ -217,7 +217,8 @@ def _create_mean_pooling_divisor(lengths: torch.Tensor, keys: List[str], offsets
             if feature not in mean_set:
                 i = kjt_key_indices[feature] * batch_size
                 lengths[i: i + batch_size] = 1
-        if len(embedding_names) != len(keys):
+        # rows of `lengths` follow the (permuted) input keys; the divisor must follow the output embedding order
+        if len(embedding_names) != len(keys) or [n.split("@")[0] for n in embedding_names] != list(keys):
             lengths = torch.index_select(lengths.reshape(-1, batch_size), 0, kt_key_ordering).reshape(-1)
         lengths = lengths.reshape(-1, batch_size).T
         divisor = torch.repeat_interleave(lengths, dim_per_key, dim=1, output_size=sum(embedding_dims))
