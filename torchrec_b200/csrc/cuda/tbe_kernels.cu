@@ -238,12 +238,12 @@ constexpr int kBlk = 64;        // sorted entries per warp
 constexpr int FLAG_USED = 1;    // slot holds a partial sum
 constexpr int FLAG_CONT = 2;    // (slot A only) the row continues into the next block
 
+// Optimizer update of one table row.  `g` is the summed gradient of the row, `w` the row's current weights and
+// `mpre` (lane 0) its row-wise Adagrad state, both already loaded by the caller so that their latency overlaps
+// with the gradient gather.
 template <typename emb_t, int kVecs>
-__device__ __forceinline__ void apply_update(const BwdParams& p, int64_t key, int f, float4 (&g)[kVecs], int lane) {
-  const int F = p.F;
-  const int D = int(p.meta[M_DIM * F + f]);
-  const int64_t row = key - p.meta[M_HASHOFF * F + f];
-  const int64_t woff = p.meta[M_WOFF * F + f] + row * D;
+__device__ __forceinline__ void apply_update_core(const BwdParams& p, int64_t key, int64_t woff, int D, float4 (&g)[kVecs],
+                                                  float4 (&w)[kVecs], float mpre, int lane) {
   const OptParams& o = p.opt;
   if (o.max_grad > 0.f) {
 #pragma unroll
@@ -263,12 +263,6 @@ __device__ __forceinline__ void apply_update(const BwdParams& p, int64_t key, in
     return;
   }
   emb_t* wp = reinterpret_cast<emb_t*>(p.weights) + woff;
-  float4 w[kVecs];
-#pragma unroll
-  for (int v = 0; v < kVecs; ++v) {
-    const int e = v * 128 + lane * 4;
-    w[v] = (e < D) ? Vec4<emb_t>::load_plain(wp + e) : f4zero();
-  }
   if (o.weight_decay != 0.f && o.type != OPT_LAMB && o.type != OPT_PARTIAL_ROWWISE_LAMB) {
 #pragma unroll
     for (int v = 0; v < kVecs; ++v) {
@@ -306,7 +300,7 @@ __device__ __forceinline__ void apply_update(const BwdParams& p, int64_t key, in
       const float g2 = sumsq(g) / float(D);
       float m = 0.f;
       if (lane == 0) {
-        m = p.mom1[key] + g2;
+        m = mpre + g2;
         p.mom1[key] = m;
       }
       m = __shfl_sync(0xffffffffu, m, 0);
@@ -405,6 +399,31 @@ __device__ __forceinline__ void apply_update(const BwdParams& p, int64_t key, in
   }
 }
 
+// Loads the row state of the row at element offset `woff` and applies the update.
+template <typename emb_t, int kVecs>
+__device__ __forceinline__ void apply_update_at(const BwdParams& p, int64_t key, int64_t woff, int D, float4 (&g)[kVecs], int lane) {
+  float4 w[kVecs];
+  float mpre = 0.f;
+  if (p.opt.type != OPT_DENSE_GRAD) {
+    const emb_t* wp = reinterpret_cast<const emb_t*>(p.weights) + woff;
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+      const int e = v * 128 + lane * 4;
+      w[v] = (e < D) ? Vec4<emb_t>::load_plain(wp + e) : f4zero();
+    }
+    if (p.opt.type == OPT_ROWWISE_ADAGRAD && lane == 0) mpre = p.mom1[key];
+  }
+  apply_update_core<emb_t, kVecs>(p, key, woff, D, g, w, mpre, lane);
+}
+
+template <typename emb_t, int kVecs>
+__device__ __forceinline__ void apply_update(const BwdParams& p, int64_t key, int f, float4 (&g)[kVecs], int lane) {
+  const int F = p.F;
+  const int D = int(p.meta[M_DIM * F + f]);
+  const int64_t woff = p.meta[M_WOFF * F + f] + (key - p.meta[M_HASHOFF * F + f]) * D;
+  apply_update_at<emb_t, kVecs>(p, key, woff, D, g, lane);
+}
+
 template <int kVecs>
 __device__ __forceinline__ void store_partial(const BwdParams& p, int64_t slot, float4 (&g)[kVecs], int lane) {
   float* dst = p.partials + slot * p.Dpad;
@@ -415,104 +434,143 @@ __device__ __forceinline__ void store_partial(const BwdParams& p, int64_t slot, 
   }
 }
 
-// pass 1: one warp per block of kBlk sorted entries
-template <typename emb_t, int kVecs>
+constexpr int kSmemF = 256;  // per-feature metadata is staged in shared memory up to this many features
+
+__device__ __forceinline__ void prefetch_l2_range(const void* ptr, int bytes) {
+  const uintptr_t lo = reinterpret_cast<uintptr_t>(ptr) & ~uintptr_t(127);
+  const uintptr_t hi = reinterpret_cast<uintptr_t>(ptr) + bytes;
+  for (uintptr_t a = lo; a < hi; a += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+}
+
+// pass 1: one warp per block of kBlk sorted entries.
+//
+// Preamble, one or two entries per lane: everything that depends on one entry only (feature, address of its
+// gradient row slice, weight row offset, whether the table row ends at this entry) is computed once and parked in
+// shared memory, and the gradient row of every entry plus the weight row (and row-wise state) of every row that
+// ends in the block are requested into L2 with prefetches.  That puts the whole block's DRAM traffic in flight at
+// once without holding registers.  The walk itself then costs per entry one 16-byte shared-memory broadcast, the
+// gradient load (an L2 hit by then) and the multiply-adds.
+template <typename emb_t, typename grad_t, int kVecs>
 __global__ void __launch_bounds__(256) tbe_bwd_block_kernel(BwdParams p) {
+  __shared__ int64_t s_meta[kMetaRows * kSmemF];
+  __shared__ uint4 s_rec[8][kBlk];     // {gradient byte offset lo, hi, weight bits, ctl}; ctl = end | D << 1 | f << 16
+  __shared__ int64_t s_woff[8][kBlk];  // element offset of the entry's table row in the weights
+  __shared__ int64_t s_key[8][kBlk];
+  const int F = p.F;
+  const int64_t* __restrict__ meta = p.meta;
+  if (F <= kSmemF) {
+    for (int i = threadIdx.x; i < kMetaRows * F; i += blockDim.x) s_meta[i] = p.meta[i];
+    __syncthreads();
+    meta = s_meta;
+  }
   const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
   const int64_t blk = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t start = blk * kBlk;
   if (start >= p.N) return;
-  const int64_t end = min(p.N, start + kBlk);
-  const int F = p.F;
+  const int n = int(min(int64_t(kBlk), p.N - start));
+  const int opt_type = p.opt.type;
+  const char* __restrict__ gbase = reinterpret_cast<const char*>(p.grad);
 
   if (lane == 0) {
     p.flags[2 * blk] = 0;
     p.flags[2 * blk + 1] = 0;
   }
+#pragma unroll
+  for (int t = 0; t < kBlk / 32; ++t) {
+    const int k = t * 32 + lane;
+    if (k < n) {
+      const int64_t i = start + k;
+      const int64_t key = p.sorted_keys[i];
+      const int64_t nxt = (i + 1 < p.N) ? p.sorted_keys[i + 1] : int64_t(-1);
+      const int src = p.sorted_src[i];
+      float w = p.sorted_w ? p.sorted_w[i] : 1.f;
+      int f;
+      int64_t goff;
+      if (p.pooled) {
+        f = src / p.B;
+        const int b = src - f * p.B;
+        goff = int64_t(b) * p.grad_stride + meta[M_OUTOFF * F + f];
+        if (p.bag_scale) w *= p.bag_scale[src];
+      } else {
+        f = p.src_feature[src];
+        goff = int64_t(src) * p.grad_stride;
+      }
+      const int D = int(meta[M_DIM * F + f]);
+      const int64_t woff = meta[M_WOFF * F + f] + (key - meta[M_HASHOFF * F + f]) * D;
+      const bool is_end = key != nxt;
+      const int64_t gbyte = goff * int64_t(sizeof(grad_t));
+      s_rec[wib][k] = make_uint4(uint32_t(uint64_t(gbyte)), uint32_t(uint64_t(gbyte) >> 32), __float_as_uint(w),
+                                 uint32_t(is_end ? 1 : 0) | (uint32_t(D) << 1) | (uint32_t(f) << 16));
+      s_woff[wib][k] = woff;
+      s_key[wib][k] = key;
+      prefetch_l2_range(gbase + gbyte, D * int(sizeof(grad_t)));
+      if (is_end && opt_type != OPT_DENSE_GRAD) {
+        prefetch_l2_range(reinterpret_cast<const emb_t*>(p.weights) + woff, D * int(sizeof(emb_t)));
+        if (opt_type == OPT_ROWWISE_ADAGRAD) prefetch_l2_range(p.mom1 + key, 4);
+      }
+    }
+  }
+  __syncwarp();
+
   float4 acc[kVecs];
 #pragma unroll
   for (int v = 0; v < kVecs; ++v) acc[v] = f4zero();
-
-  int64_t cur_key = p.sorted_keys[start];
-  bool started_before = (start > 0) && (p.sorted_keys[start - 1] == cur_key);
+  // does the first row of this block begin in an earlier block?
+  bool started_before = (start > 0) && (p.sorted_keys[start - 1] == s_key[wib][0]);
+  bool open = false;  // entries accumulated since the last row end
   int cur_f = 0;
 
-  for (int64_t i0 = start; i0 < end; i0 += 32) {
-    const int cnt = int(min(int64_t(32), end - i0));
-    int64_t my_key = 0;
-    int my_src = 0;
-    float my_w = 1.f;
-    int my_f = 0;
-    int64_t my_goff = 0;  // element offset of this entry's gradient row slice
-    if (lane < cnt) {
-      my_key = p.sorted_keys[i0 + lane];
-      my_src = p.sorted_src[i0 + lane];
-      if (p.sorted_w) my_w = p.sorted_w[i0 + lane];
-      if (p.pooled) {
-        my_f = my_src / p.B;
-        const int b = my_src - my_f * p.B;
-        my_goff = int64_t(b) * p.grad_stride + p.meta[M_OUTOFF * F + my_f];
-        if (p.bag_scale) my_w *= p.bag_scale[my_src];
-      } else {
-        my_f = p.src_feature[my_src];
-        my_goff = int64_t(my_src) * p.grad_stride;
+  constexpr int kUnroll = kVecs == 1 ? 4 : (kVecs == 2 ? 2 : 1);
+  for (int j = 0; j < n; j += kUnroll) {
+    uint4 r[kUnroll];
+    float4 gv[kUnroll][kVecs];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      r[u] = s_rec[wib][min(j + u, n - 1)];
+      const grad_t* gp = reinterpret_cast<const grad_t*>(gbase + (uint64_t(r[u].x) | (uint64_t(r[u].y) << 32)));
+      const int D = int(r[u].w >> 1) & 0x7fff;
+#pragma unroll
+      for (int v = 0; v < kVecs; ++v) {
+        const int e = v * 128 + lane * 4;
+        gv[u][v] = (e < D) ? Vec4<grad_t>::load_plain(gp + e) : f4zero();
       }
     }
-    constexpr int kUnroll = kVecs <= 2 ? 4 : 1;
-    for (int j = 0; j < cnt; j += kUnroll) {
-      float4 gv[kUnroll][kVecs];
-      int64_t kk[kUnroll];
-      float ww[kUnroll];
-      int ff[kUnroll];
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int src = min(j + u, cnt - 1);
-        kk[u] = __shfl_sync(0xffffffffu, my_key, src);
-        ww[u] = __shfl_sync(0xffffffffu, my_w, src);
-        ff[u] = __shfl_sync(0xffffffffu, my_f, src);
-        const int64_t goff = __shfl_sync(0xffffffffu, my_goff, src);
-        const int D = int(p.meta[M_DIM * F + ff[u]]);
+    for (int u = 0; u < kUnroll; ++u) {
+      if (j + u < n) {
+        const float ww = __uint_as_float(r[u].z);
 #pragma unroll
         for (int v = 0; v < kVecs; ++v) {
-          const int e = v * 128 + lane * 4;
-          gv[u][v] = (e < D) ? load4_dyn(p.grad, goff + e, p.grad_dtype) : f4zero();
+          acc[v].x = fmaf(ww, gv[u][v].x, acc[v].x);
+          acc[v].y = fmaf(ww, gv[u][v].y, acc[v].y);
+          acc[v].z = fmaf(ww, gv[u][v].z, acc[v].z);
+          acc[v].w = fmaf(ww, gv[u][v].w, acc[v].w);
         }
-      }
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if (j + u < cnt) {
-          if (kk[u] != cur_key) {
-            // the current row ends here
-            if (!started_before) {
-              apply_update<emb_t, kVecs>(p, cur_key, cur_f, acc, lane);
-            } else {
-              store_partial<kVecs>(p, 2 * blk, acc, lane);
-              if (lane == 0) p.flags[2 * blk] = FLAG_USED;
-            }
-#pragma unroll
-            for (int v = 0; v < kVecs; ++v) acc[v] = f4zero();
-            cur_key = kk[u];
-            started_before = false;
+        open = true;
+        cur_f = int(r[u].w >> 16);
+        if (r[u].w & 1u) {
+          // the row ends here
+          if (!started_before) {
+            apply_update_at<emb_t, kVecs>(p, s_key[wib][j + u], s_woff[wib][j + u], int(r[u].w >> 1) & 0x7fff, acc, lane);
+          } else {
+            store_partial<kVecs>(p, 2 * blk, acc, lane);
+            if (lane == 0) p.flags[2 * blk] = FLAG_USED;
           }
-          cur_f = ff[u];
 #pragma unroll
-          for (int v = 0; v < kVecs; ++v) {
-            acc[v].x = fmaf(ww[u], gv[u][v].x, acc[v].x);
-            acc[v].y = fmaf(ww[u], gv[u][v].y, acc[v].y);
-            acc[v].z = fmaf(ww[u], gv[u][v].z, acc[v].z);
-            acc[v].w = fmaf(ww[u], gv[u][v].w, acc[v].w);
-          }
+          for (int v = 0; v < kVecs; ++v) acc[v] = f4zero();
+          started_before = false;
+          open = false;
         }
       }
     }
   }
-  const bool continues = (end < p.N) && (p.sorted_keys[end] == cur_key);
-  if (!started_before && !continues) {
-    apply_update<emb_t, kVecs>(p, cur_key, cur_f, acc, lane);
-  } else if (started_before) {
-    // middle or tail of a long row: slot A
+  if (!open) return;
+  // the last row continues in the next block
+  if (started_before) {
+    // middle of a long row: slot A
     store_partial<kVecs>(p, 2 * blk, acc, lane);
-    if (lane == 0) p.flags[2 * blk] = FLAG_USED | (continues ? FLAG_CONT : 0);
+    if (lane == 0) p.flags[2 * blk] = FLAG_USED | FLAG_CONT;
   } else {
     // head of a long row: slot B; remember the feature for the second pass
     store_partial<kVecs>(p, 2 * blk + 1, acc, lane);
@@ -928,7 +986,9 @@ void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10:
   const int64_t blocks = (nblocks * 32 + threads - 1) / threads;
   TRB_DISPATCH_EMB(weights.scalar_type(), [&] {
     TRB_DISPATCH_VECS(nv, [&] {
-      tbe_bwd_block_kernel<emb_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+      if (p.grad_dtype == OUT_F32) tbe_bwd_block_kernel<emb_t, float, kVecs><<<blocks, threads, 0, stream>>>(p);
+      else if (p.grad_dtype == OUT_F16) tbe_bwd_block_kernel<emb_t, __half, kVecs><<<blocks, threads, 0, stream>>>(p);
+      else tbe_bwd_block_kernel<emb_t, __nv_bfloat16, kVecs><<<blocks, threads, 0, stream>>>(p);
       tbe_bwd_long_kernel<emb_t, kVecs><<<blocks, threads, 0, stream>>>(p);
       tbe_bwd_verylong_kernel<emb_t, kVecs><<<296, 256, 0, stream>>>(p);
     });
@@ -980,7 +1040,9 @@ int na_fail(int code, char* errbuf, size_t errbuf_len, const char* fmt, ...) {
 template <typename emb_t>
 void na_launch(int nv, int64_t blocks, int threads, cudaStream_t stream, const trb::BwdParams& p) {
   TRB_DISPATCH_VECS(nv, [&] {
-    trb::tbe_bwd_block_kernel<emb_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+    if (p.grad_dtype == trb::OUT_F32) trb::tbe_bwd_block_kernel<emb_t, float, kVecs><<<blocks, threads, 0, stream>>>(p);
+    else if (p.grad_dtype == trb::OUT_F16) trb::tbe_bwd_block_kernel<emb_t, __half, kVecs><<<blocks, threads, 0, stream>>>(p);
+    else trb::tbe_bwd_block_kernel<emb_t, __nv_bfloat16, kVecs><<<blocks, threads, 0, stream>>>(p);
     trb::tbe_bwd_long_kernel<emb_t, kVecs><<<blocks, threads, 0, stream>>>(p);
     trb::tbe_bwd_verylong_kernel<emb_t, kVecs><<<296, 256, 0, stream>>>(p);
   });
