@@ -28,11 +28,10 @@ namespace trb {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;  // 64 bf16 = 128 bytes = one swizzle span
-constexpr int kStages = 4;
 constexpr int kThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr long long kWaitCycles = 2000000000LL;  // about one second
 
-enum GemmErr : int { ERR_NONE = 0, ERR_FULL_WAIT = 1, ERR_EMPTY_WAIT = 2, ERR_TMEM_FULL_WAIT = 3, ERR_TMEM_EMPTY_WAIT = 4 };
+enum GemmErr : int { ERR_NONE = 0, ERR_FULL_WAIT = 1, ERR_EMPTY_WAIT = 2, ERR_TMEM_FULL_WAIT = 3, ERR_TMEM_EMPTY_WAIT = 4, ERR_EPI_LOAD_WAIT = 5 };
 
 struct GemmParams {
   int M, N, K;        // output rows, output cols, contraction length
@@ -93,6 +92,21 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tmap, 
       ::"r"(smem_u32(dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tmap), "r"(smem_u32(src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tmap, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the shared-memory sources of all committed stores have been read (the buffers may be overwritten)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all committed stores are complete
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// make generic-proxy writes to shared memory visible to the async proxy (TMA)
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -148,12 +162,24 @@ __host__ __device__ constexpr uint32_t make_idesc(int n, bool a_mn, bool b_mn) {
          (uint32_t(n >> 3) << 17) | (uint32_t(kBlockM >> 4) << 24);
 }
 
-template <int BLOCK_N>
+enum Epi : int { EPI_PLAIN = 0, EPI_BIAS = 1, EPI_BIAS_RELU = 2, EPI_BIAS_SIGMOID = 3, EPI_CROSS = 4, EPI_ADD = 5, EPI_F32 = 6, EPI_F32_ATOMIC = 7 };
+
+constexpr int kEpiWarps = 8;
+constexpr int kEpiBufBytes = 32 * 128;  // 32 rows x 64 bf16 columns, one TMA box
+
+// bf16 epilogues stage their tiles in shared memory and move them with TMA; the fp32 ones write registers directly
+__host__ __device__ constexpr bool epi_uses_tma(int epi) { return epi != EPI_F32 && epi != EPI_F32_ATOMIC; }
+
+template <int BLOCK_N, int EPI>
 struct SmemLayout {
   static constexpr int kABytes = kBlockM * kBlockK * 2;   // 16 KB
   static constexpr int kBBytes = BLOCK_N * kBlockK * 2;   // 16 / 32 KB
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kTotal = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  // the cross epilogue needs two staging buffers per warp (x0 -> u, x -> y); it gives up one pipeline stage for them
+  static constexpr int kEpiBufs = !epi_uses_tma(EPI) ? 0 : (EPI == EPI_CROSS ? 2 : 1);
+  static constexpr int kStages = (EPI == EPI_CROSS && BLOCK_N == 256) ? 3 : 4;
+  static constexpr int kEpiBytes = kEpiWarps * kEpiBufs * kEpiBufBytes;
+  static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ float apply_act(float v, int act) {
@@ -161,8 +187,6 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   if (act == 2) return 1.f / (1.f + __expf(-v));
   return v;
 }
-
-enum Epi : int { EPI_PLAIN = 0, EPI_BIAS = 1, EPI_BIAS_RELU = 2, EPI_BIAS_SIGMOID = 3, EPI_CROSS = 4, EPI_ADD = 5, EPI_F32 = 6, EPI_F32_ATOMIC = 7 };
 
 __device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
   uint4 pk;
@@ -258,16 +282,21 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
 //                   tmap boxes are {64 cols, 64 rows}; a stage holds M/64 (resp. N/64) such boxes.
 template <int BLOCK_N, bool MN_MAJOR, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, GemmParams p) {
-  using L = SmemLayout<BLOCK_N>;
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+                 const __grid_constant__ CUtensorMap tmapOut, const __grid_constant__ CUtensorMap tmapU,
+                 const __grid_constant__ CUtensorMap tmapMul, const __grid_constant__ CUtensorMap tmapAdd, GemmParams p) {
+  using L = SmemLayout<BLOCK_N, EPI>;
+  constexpr int kStages = L::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * L::kStageBytes);
+  uint8_t* epi_smem = smem + kStages * L::kStageBytes;  // 1024-byte aligned: stage sizes are multiples of 1024
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + L::kEpiBytes);
   uint64_t* full = bars;                       // [kStages]
   uint64_t* empty = bars + kStages;            // [kStages]
   uint64_t* tmem_full = bars + 2 * kStages;    // [2]
   uint64_t* tmem_empty = bars + 2 * kStages + 2;  // [2]
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  uint64_t* in_bars = bars + 2 * kStages + 4;  // [kEpiWarps] epilogue operand tiles have landed
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4 + kEpiWarps);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -285,8 +314,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 8);  // one arrival per epilogue warp
+      mbar_init(&tmem_empty[a], kEpiWarps);  // one arrival per epilogue warp
     }
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(&in_bars[w], 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -386,30 +416,185 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     constexpr int kPieces = BLOCK_N / 64;  // 32-column pieces per warp
     uint32_t tile_it = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++tile_it) {
-      const int tile = w / p.k_splits;
-      const int m_blk = tile / n_tiles, n_blk = tile - m_blk * n_tiles;
-      const int acc = tile_it & 1;
-      const uint32_t acc_ph = (tile_it >> 1) & 1;
-      if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag, p.err, ERR_TMEM_FULL_WAIT)) { ok = false; break; }
-      tcgen05_fence_after();
-      const int row = m_blk * kBlockM + q * 32 + lane;
-      const bool row_ok = row < p.M;
-      const int64_t row_off = int64_t(row) * p.ldc;
-      const int colbase = n_blk * BLOCK_N + half * (BLOCK_N / 2);
-      const uint32_t tbase = tmem_base + (uint32_t(q * 32) << 16) + acc * BLOCK_N + half * (BLOCK_N / 2);
-      uint32_t r[2][32];
-      tmem_ld_32x32_issue(tbase, r[0]);
+    if constexpr (epi_uses_tma(EPI)) {
+      // bf16 output through shared memory and TMA.  A warp owns 32 rows x 64 columns at a time ("box": two TMEM
+      // pieces).  Operand tiles of the fused epilogue (x0 and x of the cross layer, the residual) arrive by TMA load
+      // into the same buffers the results leave from: lane `l` reads the 16-byte chunks of its row, computes, and
+      // writes the result over them; one lane then issues the TMA store.  Chunk c of row l sits at c ^ (l & 7),
+      // the 128-byte swizzle of the tensor maps, which also keeps the 16-byte accesses free of bank conflicts.
+      constexpr bool kBias = EPI == EPI_BIAS || EPI == EPI_BIAS_RELU || EPI == EPI_BIAS_SIGMOID || EPI == EPI_CROSS;
+      constexpr bool kMul = EPI == EPI_CROSS;
+      constexpr bool kAdd = EPI == EPI_CROSS || EPI == EPI_ADD;
+      constexpr bool kIn = kMul || kAdd;
+      constexpr int kBoxes = BLOCK_N / 128;  // boxes per warp per tile
+      const int ew = warp - 2;
+      uint8_t* bufA = epi_smem + ew * L::kEpiBufs * kEpiBufBytes;  // cross: x0 -> u.  otherwise: (residual ->) out
+      uint8_t* bufB = bufA + (L::kEpiBufs > 1 ? kEpiBufBytes : 0);  // cross: x -> y
+      uint8_t* bufOut = EPI == EPI_CROSS ? bufB : bufA;
+      uint64_t* in_bar = &in_bars[ew];
+      uint32_t in_uses = 0;
+      bool in_flight = false;
+      const uint32_t sw = uint32_t(lane & 7);
+      auto load_operands = [&](int row0, int col0) {
+        // previous stores must have read the buffers before new data may land in them
+        if (lane == 0) {
+          tma_store_wait_read();
+          mbar_expect_tx(in_bar, (int(kMul) + int(kAdd)) * kEpiBufBytes);
+          if constexpr (kMul) tma_load_2d(bufA, &tmapMul, in_bar, col0, row0);
+          if constexpr (kAdd) tma_load_2d(bufOut, &tmapAdd, in_bar, col0, row0);
+        }
+        in_flight = true;
+      };
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++tile_it) {
+        const int tile = w / p.k_splits;
+        const int m_blk = tile / n_tiles, n_blk = tile - m_blk * n_tiles;
+        const int acc = tile_it & 1;
+        const uint32_t acc_ph = (tile_it >> 1) & 1;
+        const int row0 = m_blk * kBlockM + q * 32;
+        const int colbase = n_blk * BLOCK_N + half * (BLOCK_N / 2);
+        const bool rows_ok = row0 < p.M;
+        if constexpr (kIn) {
+          // operands of the first box travel while the MMAs of this tile may still be running
+          if (rows_ok && colbase < p.N) load_operands(row0, colbase);
+          if constexpr (kBoxes > 1) {
+            if (lane == 0 && rows_ok && colbase + 64 < p.N) {
+              if constexpr (kMul) tma_prefetch_2d(&tmapMul, colbase + 64, row0);
+              if constexpr (kAdd) tma_prefetch_2d(&tmapAdd, colbase + 64, row0);
+            }
+          }
+        }
+        if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag, p.err, ERR_TMEM_FULL_WAIT)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t tbase = tmem_base + (uint32_t(q * 32) << 16) + acc * BLOCK_N + half * (BLOCK_N / 2);
+        uint32_t r[2][32];
+        tmem_ld_32x32_issue(tbase, r[0]);
 #pragma unroll
-      for (int c = 0; c < kPieces; ++c) {
-        tmem_ld_wait(r[c & 1]);
-        if (c + 1 < kPieces) tmem_ld_32x32_issue(tbase + (c + 1) * 32, r[(c + 1) & 1]);
-        const int col0 = colbase + c * 32;
-        if (row_ok && col0 < p.N) epilogue_chunk<EPI>(p, r[c & 1], row_off, col0);
+        for (int c = 0; c < kPieces; ++c) {
+          const int box = c >> 1, h = c & 1;
+          const int col0 = colbase + box * 64;
+          const bool active = rows_ok && col0 < p.N;
+          tmem_ld_wait(r[c & 1]);
+          if (c + 1 < kPieces) {
+            tmem_ld_32x32_issue(tbase + (c + 1) * 32, r[(c + 1) & 1]);
+          } else {
+            // every TMEM read of this tile has completed: hand the accumulator back to the MMA warp
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          }
+          if (h == 0) {
+            if constexpr (kIn) {
+              if (active && box > 0) load_operands(row0, col0);
+              if (in_flight) {
+                const bool landed = mbar_wait(in_bar, in_uses & 1, abort_flag, p.err, ERR_EPI_LOAD_WAIT);
+                if (__all_sync(0xffffffffu, landed)) {
+                  ++in_uses;
+                  in_flight = false;
+                } else {
+                  ok = false;
+                }
+              }
+            } else {
+              if (active && lane == 0) tma_store_wait_read();
+              __syncwarp();
+            }
+          }
+          if (!ok) {
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            break;
+          }
+          if (active) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int chunk = h * 4 + g;
+              const int col = col0 + chunk * 8;
+              const uint32_t off = uint32_t(lane) * 128u + ((uint32_t(chunk) ^ sw) << 4);
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[c & 1][g * 8 + j]);
+              if constexpr (kBias) {
+                if (col < p.N) {
+                  const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+                  const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + col + 4));
+                  v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                  v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                }
+              }
+              if constexpr (EPI == EPI_BIAS_RELU) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.f);
+              }
+              if constexpr (EPI == EPI_BIAS_SIGMOID) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = 1.f / (1.f + __expf(-v[j]));
+              }
+              if constexpr (EPI == EPI_CROSS) {
+                // u = acc + bias is stored in bf16 and y is computed from the rounded u, so that y == x0 * u + x as saved
+                uint4* pa = reinterpret_cast<uint4*>(bufA + off);
+                const uint4 upk = pack_bf16x8(v);
+                float m[8];
+                unpack_bf16x8(*pa, m);
+                *pa = upk;
+                unpack_bf16x8(upk, v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] *= m[j];
+              }
+              uint4* po = reinterpret_cast<uint4*>(bufOut + off);
+              if constexpr (kAdd) {
+                float a[8];
+                unpack_bf16x8(*po, a);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += a[j];
+              }
+              *po = pack_bf16x8(v);
+            }
+            if (h == 1) {
+              fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) {
+                if constexpr (EPI == EPI_CROSS) tma_store_2d(&tmapU, bufA, col0, row0);
+                tma_store_2d(&tmapOut, bufOut, col0, row0);
+                tma_store_commit();
+              }
+            }
+          }
+        }
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+        if (!ok && in_flight) {
+          // operand tiles may still be on their way into shared memory: give them a bounded time to land
+          const long long t0 = clock64();
+          while (!mbar_try_wait(in_bar, in_uses & 1) && clock64() - t0 < kWaitCycles) {
+          }
+        }
+        tma_store_wait_all();
+      }
+    } else {
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++tile_it) {
+        const int tile = w / p.k_splits;
+        const int m_blk = tile / n_tiles, n_blk = tile - m_blk * n_tiles;
+        const int acc = tile_it & 1;
+        const uint32_t acc_ph = (tile_it >> 1) & 1;
+        if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag, p.err, ERR_TMEM_FULL_WAIT)) { ok = false; break; }
+        tcgen05_fence_after();
+        const int row = m_blk * kBlockM + q * 32 + lane;
+        const bool row_ok = row < p.M;
+        const int64_t row_off = int64_t(row) * p.ldc;
+        const int colbase = n_blk * BLOCK_N + half * (BLOCK_N / 2);
+        const uint32_t tbase = tmem_base + (uint32_t(q * 32) << 16) + acc * BLOCK_N + half * (BLOCK_N / 2);
+        uint32_t r[2][32];
+        tmem_ld_32x32_issue(tbase, r[0]);
+#pragma unroll
+        for (int c = 0; c < kPieces; ++c) {
+          tmem_ld_wait(r[c & 1]);
+          if (c + 1 < kPieces) tmem_ld_32x32_issue(tbase + (c + 1) * 32, r[(c + 1) & 1]);
+          const int col0 = colbase + c * 32;
+          if (row_ok && col0 < p.N) epilogue_chunk<EPI>(p, r[c & 1], row_off, col0);
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      }
     }
   }
 
@@ -500,15 +685,23 @@ static void launch_gemm(const at::Tensor& a, const at::Tensor& b, GemmParams p) 
   else epi = EPI_PLAIN;
   TORCH_CHECK(!(p.out_fp32 && (p.bias || p.act || p.add || p.mul)), "fp32 output supports the plain product only");
   TORCH_CHECK(p.bias || p.act == 0, "an activation needs a bias operand (pass zeros)");
+  // bf16 epilogues move 32-row x 64-column boxes of the output (and of the fused operands) by TMA
+  CUtensorMap t_out = ta, t_u = ta, t_mul = ta, t_add = ta;
+  if (epi_uses_tma(epi)) {
+    t_out = make_tmap(p.out, p.M, p.N, p.ldc, 64, 32);
+    t_u = p.u_out ? make_tmap(p.u_out, p.M, p.N, p.ldc, 64, 32) : t_out;
+    t_mul = p.mul ? make_tmap(p.mul, p.M, p.N, p.ldc, 64, 32) : t_out;
+    t_add = p.add ? make_tmap(p.add, p.M, p.N, p.ldc, 64, 32) : t_out;
+  }
   auto launch = [&](auto kernel, int smem) {
     // the attribute is per kernel instantiation; setting it is cheap and idempotent
     TRB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kernel<<<grid, kThreads, smem, stream>>>(ta, tb, p);
+    kernel<<<grid, kThreads, smem, stream>>>(ta, tb, t_out, t_u, t_mul, t_add, p);
   };
 #define TRB_GEMM_CASE(E)                                                                              \
   case E:                                                                                             \
-    if (wide) launch(gemm_bf16_kernel<256, MN_MAJOR, E>, SmemLayout<256>::kTotal);                    \
-    else launch(gemm_bf16_kernel<128, MN_MAJOR, E>, SmemLayout<128>::kTotal);                         \
+    if (wide) launch(gemm_bf16_kernel<256, MN_MAJOR, E>, SmemLayout<256, E>::kTotal);                 \
+    else launch(gemm_bf16_kernel<128, MN_MAJOR, E>, SmemLayout<128, E>::kTotal);                      \
     break;
   if constexpr (MN_MAJOR) {
     switch (epi) {

@@ -451,7 +451,7 @@ __device__ __forceinline__ void prefetch_l2_range(const void* ptr, int bytes) {
 // once without holding registers.  The walk itself then costs per entry one 16-byte shared-memory broadcast, the
 // gradient load (an L2 hit by then) and the multiply-adds.
 template <typename emb_t, typename grad_t, int kVecs>
-__global__ void __launch_bounds__(256) tbe_bwd_block_kernel(BwdParams p) {
+__global__ void __launch_bounds__(256, kVecs == 1 ? 4 : 2) tbe_bwd_block_kernel(BwdParams p) {
   __shared__ int64_t s_meta[kMetaRows * kSmemF];
   __shared__ uint4 s_rec[8][kBlk];     // {gradient byte offset lo, hi, weight bits, ctl}; ctl = end | D << 1 | f << 16
   __shared__ int64_t s_woff[8][kBlk];  // element offset of the entry's table row in the weights
