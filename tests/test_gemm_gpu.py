@@ -118,3 +118,41 @@ def test_fused_linear_autograd_matches_fp32():
         assert _ops().gemm_error_status() == 0
     finally:
         dense_ops.set_dense_compute_dtype(torch.float32)
+
+
+def test_lowrank_cross_stack_autograd_matches_fp32():
+    """Three-layer low-rank cross network as one autograd node (running dx0, fused bias gradient) against fp32
+    autograd of the same math."""
+    from torchrec_b200.ops import dense_ops
+    torch.manual_seed(5)
+    dense_ops.set_dense_compute_dtype(torch.bfloat16)
+    try:
+        B, N, r, L = 777, 384, 64, 3   # B not a multiple of the tile sizes
+        Vs = [torch.nn.Parameter(torch.randn(r, N, device="cuda") / N ** 0.5) for _ in range(L)]
+        Ws = [torch.nn.Parameter(torch.randn(N, r, device="cuda") / r ** 0.5) for _ in range(L)]
+        bs = [torch.nn.Parameter(torch.randn(N, device="cuda") * 0.1) for _ in range(L)]
+        x0 = torch.randn(B, N, device="cuda").bfloat16().requires_grad_(True)
+        y = dense_ops.lowrank_cross_stack(x0, Vs, Ws, bs)
+        g = torch.randn(B, N, device="cuda")
+        y.float().backward(g)
+        Vr = [t.detach().clone().requires_grad_(True) for t in Vs]
+        Wr = [t.detach().clone().requires_grad_(True) for t in Ws]
+        br = [t.detach().clone().requires_grad_(True) for t in bs]
+        x0r = x0.detach().float().requires_grad_(True)
+        xl = x0r
+        for l in range(L):
+            xl = x0r * (torch.nn.functional.linear(torch.nn.functional.linear(xl, Vr[l]), Wr[l]) + br[l]) + xl
+        xl.backward(g)
+
+        def rel(a, b):
+            return ((a.float() - b.float()).norm() / b.float().norm()).item()
+
+        assert rel(y, xl) < 2e-2
+        assert rel(x0.grad, x0r.grad) < 3e-2
+        for l in range(L):
+            assert rel(Vs[l].grad, Vr[l].grad) < 4e-2, l
+            assert rel(Ws[l].grad, Wr[l].grad) < 4e-2, l
+            assert rel(bs[l].grad, br[l].grad) < 4e-2, l
+        assert _ops().gemm_error_status() == 0
+    finally:
+        dense_ops.set_dense_compute_dtype(torch.float32)

@@ -87,6 +87,100 @@ std::tuple<at::Tensor, at::Tensor> cross_bwd_elementwise(const at::Tensor& dy, c
   return {du, dx0};
 }
 
+// ---- cross layer backward, fused over the layer stack ---------------------------------------------
+//   du      = dy * x0
+//   dx0_out = dy * u (+ dx0_in) (+ dy)        running gradient of x0 over the layers (the "+ dy" closes layer 0,
+//                                            whose x input is x0 itself)
+//   db     += column sums of du               bias gradient, fp32 atomics
+// A warp covers 256 consecutive columns of a row (16 bytes per lane), the 8 warps of a CTA walk rows 8 apart.
+__global__ void __launch_bounds__(256) cross_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x0,
+                                                              const __nv_bfloat16* __restrict__ u, const __nv_bfloat16* dx0_in,
+                                                              __nv_bfloat16* __restrict__ du, __nv_bfloat16* dx0_out,
+                                                              float* __restrict__ db, int64_t M, int N, int rows_per_cta, int add_dy) {
+  __shared__ float red[8][256];
+  const int lane = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + lane * 8;
+  const int64_t r0 = int64_t(blockIdx.y) * rows_per_cta;
+  const int64_t r1 = min(M, r0 + rows_per_cta);
+  float cs[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) cs[k] = 0.f;
+  if (col < N) {
+    for (int64_t r = r0 + rg; r < r1; r += 8) {
+      const int64_t i = r * N + col;
+      const bf16x8 a = *reinterpret_cast<const bf16x8*>(dy + i);
+      const bf16x8 b = *reinterpret_cast<const bf16x8*>(x0 + i);
+      const bf16x8 c = *reinterpret_cast<const bf16x8*>(u + i);
+      bf16x8 acc;
+      if (dx0_in) acc = *reinterpret_cast<const bf16x8*>(dx0_in + i);
+      bf16x8 o1, o2;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 fa = __bfloat1622float2(a.v[k]), fb = __bfloat1622float2(b.v[k]), fc = __bfloat1622float2(c.v[k]);
+        o1.v[k] = __floats2bfloat162_rn(fa.x * fb.x, fa.y * fb.y);
+        // the bias gradient sums the values that the weight-gradient GEMM will read, i.e. the rounded ones
+        const float2 fo = __bfloat1622float2(o1.v[k]);
+        cs[2 * k] += fo.x;
+        cs[2 * k + 1] += fo.y;
+        float gx = fa.x * fc.x, gy = fa.y * fc.y;
+        if (dx0_in) {
+          const float2 fd = __bfloat1622float2(acc.v[k]);
+          gx += fd.x;
+          gy += fd.y;
+        }
+        if (add_dy) {
+          gx += fa.x;
+          gy += fa.y;
+        }
+        o2.v[k] = __floats2bfloat162_rn(gx, gy);
+      }
+      *reinterpret_cast<bf16x8*>(du + i) = o1;
+      *reinterpret_cast<bf16x8*>(dx0_out + i) = o2;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[rg][lane * 8 + k] = cs[k];
+  __syncthreads();
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s += red[k][threadIdx.x];
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < N) atomicAdd(db + c, s);
+}
+
+// returns (du, dx0_out, db); dx0_out aliases dx0_in when that is given
+std::tuple<at::Tensor, at::Tensor, at::Tensor> cross_bwd_fused(const at::Tensor& dy, const at::Tensor& x0, const at::Tensor& u,
+                                                               const c10::optional<at::Tensor>& dx0_in, bool add_dy) {
+  TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && x0.scalar_type() == at::kBFloat16 && u.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(dy.dim() == 2 && dy.is_contiguous() && x0.is_contiguous() && u.is_contiguous() && dy.size(1) % 8 == 0);
+  TORCH_CHECK(x0.sizes() == dy.sizes() && u.sizes() == dy.sizes());
+  c10::cuda::CUDAGuard guard(dy.device());
+  const int64_t M = dy.size(0);
+  const int N = int(dy.size(1));
+  at::Tensor du = at::empty_like(dy);
+  at::Tensor dx0_out;
+  const __nv_bfloat16* in_ptr = nullptr;
+  if (dx0_in.has_value() && dx0_in->defined()) {
+    TORCH_CHECK(dx0_in->scalar_type() == at::kBFloat16 && dx0_in->is_contiguous() && dx0_in->sizes() == dy.sizes());
+    dx0_out = *dx0_in;
+    in_ptr = reinterpret_cast<const __nv_bfloat16*>(dx0_in->data_ptr());
+  } else {
+    dx0_out = at::empty_like(dy);
+  }
+  at::Tensor db = at::zeros({N}, dy.options().dtype(at::kFloat));
+  if (M == 0) return {du, dx0_out, db};
+  const int col_tiles = (N + 255) / 256;
+  const int row_splits = int(std::max<int64_t>(1, std::min<int64_t>((M + 63) / 64, (148 * 8 + col_tiles - 1) / col_tiles)));
+  const int rows_per_cta = int((M + row_splits - 1) / row_splits);
+  dim3 grid(col_tiles, row_splits);
+  cross_bwd_fused_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dy.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(x0.data_ptr()),
+      reinterpret_cast<const __nv_bfloat16*>(u.data_ptr()), in_ptr, reinterpret_cast<__nv_bfloat16*>(du.data_ptr()),
+      reinterpret_cast<__nv_bfloat16*>(dx0_out.data_ptr()), db.data_ptr<float>(), M, N, rows_per_cta, add_dy ? 1 : 0);
+  TRB_CUDA_CHECK(cudaGetLastError());
+  return {du, dx0_out, db};
+}
+
 // ---- column sum of a bf16 [M, N] matrix -> fp32 [N] (bias gradient) --------------------------------
 // grid.x tiles columns (64 per CTA), grid.y splits rows; partial sums are combined with fp32 atomics.
 __global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
@@ -270,6 +364,7 @@ std::tuple<at::Tensor, at::Tensor> dot_interaction_bwd(const at::Tensor& dout, c
 TORCH_LIBRARY_FRAGMENT(trb200, m) {
   m.def("act_backward_bf16(Tensor dy, Tensor y, int act) -> Tensor");
   m.def("cross_bwd_elementwise(Tensor dy, Tensor x0, Tensor u) -> (Tensor, Tensor)");
+  m.def("cross_bwd_fused(Tensor dy, Tensor x0, Tensor u, Tensor(a!)? dx0_in, bool add_dy) -> (Tensor, Tensor(a!), Tensor)");
   m.def("colsum_bf16(Tensor x) -> Tensor");
   m.def("dot_interaction_fwd(Tensor dense, Tensor sparse) -> Tensor");
   m.def("dot_interaction_bwd(Tensor dout, Tensor dense, Tensor sparse) -> (Tensor, Tensor)");
@@ -278,6 +373,7 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
 TORCH_LIBRARY_IMPL(trb200, CUDA, m) {
   m.impl("act_backward_bf16", &trb::act_backward_bf16);
   m.impl("cross_bwd_elementwise", &trb::cross_bwd_elementwise);
+  m.impl("cross_bwd_fused", &trb::cross_bwd_fused);
   m.impl("colsum_bf16", &trb::colsum_bf16);
   m.impl("dot_interaction_fwd", &trb::dot_interaction_fwd);
   m.impl("dot_interaction_bwd", &trb::dot_interaction_bwd);

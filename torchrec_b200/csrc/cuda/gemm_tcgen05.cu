@@ -170,6 +170,12 @@ constexpr int kEpiBufBytes = 32 * 128;  // 32 rows x 64 bf16 columns, one TMA bo
 // bf16 epilogues stage their tiles in shared memory and move them with TMA; the fp32 ones write registers directly
 __host__ __device__ constexpr bool epi_uses_tma(int epi) { return epi != EPI_F32 && epi != EPI_F32_ATOMIC; }
 
+// Work item -> (output tile, contraction split).  The split is the slow index: the CTAs that run at the same time
+// then work on the same slice of the contraction for different output tiles, so every operand slice is fetched
+// from DRAM once and re-read from L2 by the other tiles of its row or column.
+__device__ __forceinline__ int work_tile(int w, int k_splits, int tiles) { return k_splits == 1 ? w : w % tiles; }
+__device__ __forceinline__ int work_split(int w, int k_splits, int tiles) { return k_splits == 1 ? 0 : w / tiles; }
+
 template <int BLOCK_N, int EPI>
 struct SmemLayout {
   static constexpr int kABytes = kBlockM * kBlockK * 2;   // 16 KB
@@ -304,7 +310,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   const int n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int kb_total = (p.K + kBlockK - 1) / kBlockK;
   const int kb_per_split = p.kb_per_split;
-  const int num_work = m_tiles * n_tiles * p.k_splits;
+  const int tiles_total = m_tiles * n_tiles;
+  const int num_work = tiles_total * p.k_splits;
   constexpr uint32_t kTmemCols = 2 * BLOCK_N;  // two accumulators
 
   if (threadIdx.x == 0) {
@@ -335,7 +342,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       uint32_t it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-        const int tile = w / p.k_splits, ks = w - tile * p.k_splits;
+        const int tile = work_tile(w, p.k_splits, tiles_total), ks = work_split(w, p.k_splits, tiles_total);
         const int m_blk = tile / n_tiles, n_blk = tile - m_blk * n_tiles;
         const int kb0 = ks * kb_per_split, kb1 = min(kb_total, kb0 + kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -376,7 +383,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++tile_it) {
-        const int ks = w % p.k_splits;
+        const int ks = work_split(w, p.k_splits, tiles_total);
         const int kb0 = ks * kb_per_split, kb1 = min(kb_total, kb0 + kb_per_split);
         const int acc = tile_it & 1;
         const uint32_t acc_ph = (tile_it >> 1) & 1;
@@ -446,7 +453,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         in_flight = true;
       };
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++tile_it) {
-        const int tile = w / p.k_splits;
+        const int tile = work_tile(w, p.k_splits, tiles_total);
         const int m_blk = tile / n_tiles, n_blk = tile - m_blk * n_tiles;
         const int acc = tile_it & 1;
         const uint32_t acc_ph = (tile_it >> 1) & 1;
@@ -571,7 +578,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       }
     } else {
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++tile_it) {
-        const int tile = w / p.k_splits;
+        const int tile = work_tile(w, p.k_splits, tiles_total);
         const int m_blk = tile / n_tiles, n_blk = tile - m_blk * n_tiles;
         const int acc = tile_it & 1;
         const uint32_t acc_ph = (tile_it >> 1) & 1;
@@ -806,7 +813,21 @@ at::Tensor gemm_tn_bf16(const at::Tensor& a, const at::Tensor& b) {
   const int BN = p.N > 128 ? 256 : 128;
   const int tiles = ((p.M + kBlockM - 1) / kBlockM) * ((p.N + BN - 1) / BN);
   const int kb_total = int((Mc + kBlockK - 1) / kBlockK);
-  int splits = std::max(1, std::min(kb_total / 8, (2 * num_sms() + tiles - 1) / tiles));
+  // split the contraction so that the work items fill whole waves of the persistent grid: estimate
+  // rounds x (k-blocks per item + epilogue) for every candidate and keep the cheapest
+  int splits = 1;
+  {
+    const int sms = num_sms();
+    const int max_splits = std::max(1, std::min(kb_total / 4, 64));
+    double best = 1e30;
+    for (int s = 1; s <= max_splits; ++s) {
+      const int kbps = (kb_total + s - 1) / s;
+      const int s_eff = (kb_total + kbps - 1) / kbps;
+      const int rounds = (tiles * s_eff + sms - 1) / sms;
+      const double cost = double(rounds) * (kbps + 4.0) + 0.25 * s_eff;  // mild penalty on atomic traffic
+      if (cost < best) { best = cost; splits = s_eff; }
+    }
+  }
   at::Tensor out = splits > 1 ? at::zeros({N, K}, a.options().dtype(at::kFloat)) : at::empty({N, K}, a.options().dtype(at::kFloat));
   if (Mc == 0) return out.zero_();
   p.out = out.data_ptr(); p.out_fp32 = 1; p.atomic_out = splits > 1 ? 1 : 0; p.ldc = K;

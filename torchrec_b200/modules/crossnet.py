@@ -59,12 +59,7 @@ class LowRankCrossNet(torch.nn.Module):
         x_l = x_0
         if dense_ops.fused_dense_enabled(input) and input.shape[1] % 8 == 0 and self._low_rank % 8 == 0:
             x_0 = x_0 if x_0.dtype == torch.bfloat16 else x_0.to(torch.bfloat16)
-            x_l = x_0
-            for layer in range(self._num_layers):
-                x_l = dense_ops.lowrank_cross_layer(
-                    x_0, x_l, self.V_kernels[layer], self.W_kernels[layer], self.bias[layer]
-                )
-            return x_l
+            return dense_ops.lowrank_cross_stack(x_0, list(self.V_kernels), list(self.W_kernels), list(self.bias))
         for layer in range(self._num_layers):
             x_l_v = torch.nn.functional.linear(x_l, self.V_kernels[layer])
             x_l_w = torch.nn.functional.linear(x_l_v, self.W_kernels[layer])

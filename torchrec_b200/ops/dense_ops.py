@@ -283,6 +283,74 @@ def lowrank_cross_layer(x0, xl, V, W, bias) -> torch.Tensor:
     return _LowRankCross.apply(x0, xl, V, W, bias)
 
 
+def _cross_bwd_fused(dy, x0, u, dx0_acc, add_dy):
+    """``du = dy*x0``, running ``dx0 (+)= dy*u (+ dy)``, ``db = colsum(du)`` in one pass."""
+    if dy.is_cuda and _ext.has_cuda_ext():
+        return torch.ops.trb200.cross_bwd_fused(dy, x0, u, dx0_acc, add_dy)
+    du = (dy.float() * x0.float()).to(torch.bfloat16)
+    g = dy.float() * u.float()
+    if dx0_acc is not None:
+        g = g + dx0_acc.float()
+    if add_dy:
+        g = g + dy.float()
+    return du, g.to(torch.bfloat16), du.float().sum(0)
+
+
+class _LowRankCrossStack(torch.autograd.Function):
+    """All layers of a low-rank cross network ``x_{l+1} = x0 * (W_l (V_l x_l) + b_l) + x_l`` as one autograd node.
+
+    Keeping the stack in one node lets the backward carry the gradient of ``x0`` (which every layer multiplies by)
+    as a running sum inside the fused elementwise kernel instead of leaving one ``[B, N]`` addition per layer to
+    autograd; the bias gradient comes out of the same pass.  Per layer the backward is then one elementwise pass
+    and four GEMMs (two with fused epilogues)."""
+
+    @staticmethod
+    def forward(ctx, x0, num_layers, *params):
+        Vs, Ws, bs = params[:num_layers], params[num_layers: 2 * num_layers], params[2 * num_layers:]
+        saved = [x0]
+        xl = x0
+        for V, W, b in zip(Vs, Ws, bs):
+            v = gemm_nt(xl, bf16_cache.get(V), None, ACT_NONE, torch.bfloat16)
+            u, y = gemm_nt_cross(v, bf16_cache.get(W), b, x0, xl)
+            saved += [xl, v, u]
+            xl = y
+        ctx.num_layers = num_layers
+        ctx.save_for_backward(*saved, *Vs, *Ws)
+        return xl
+
+    @staticmethod
+    def backward(ctx, dy):
+        L = ctx.num_layers
+        t = ctx.saved_tensors
+        x0 = t[0]
+        per_layer = t[1: 1 + 3 * L]
+        Vs, Ws = t[1 + 3 * L: 1 + 4 * L], t[1 + 4 * L: 1 + 5 * L]
+        dy = dy.contiguous()
+        if dy.dtype != torch.bfloat16:
+            dy = dy.to(torch.bfloat16)
+        dVs, dWs, dbs = [None] * L, [None] * L, [None] * L
+        dx0_acc = None
+        dx0 = None
+        for l in reversed(range(L)):
+            xl, v, u = per_layer[3 * l: 3 * l + 3]
+            last = l == 0
+            du, dx0_acc, dbs[l] = _cross_bwd_fused(dy, x0, u, dx0_acc, last)
+            dv = gemm_nt(du, bf16_cache.get(Ws[l], transposed=True), None, ACT_NONE, torch.bfloat16)  # [B, r]
+            dWs[l] = gemm_tn(du, v)
+            dVs[l] = gemm_tn(dv, xl)
+            VT16 = bf16_cache.get(Vs[l], transposed=True)
+            if last:
+                dx0 = gemm_nt_add(dv, VT16, dx0_acc)  # x_0 is also the x input of layer 0
+            else:
+                dy = gemm_nt_add(dv, VT16, dy)
+        return (dx0, None, *dVs, *dWs, *dbs)
+
+
+def lowrank_cross_stack(x0, Vs, Ws, biases) -> torch.Tensor:
+    """Run a whole low-rank cross network (lists of per-layer ``V [r, N]``, ``W [N, r]``, ``bias [N]``)."""
+    return _LowRankCrossStack.apply(x0, len(Vs), *Vs, *Ws, *biases)
+
+
 def linear_small_out(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
     """Final logits layer (``out_features`` tiny, e.g. 1): a CUDA-core dot-product kernel is a
     better fit than a tensor-core tile; plain ``F.linear`` in fp32 keeps the logits exact."""
