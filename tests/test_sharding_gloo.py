@@ -78,7 +78,10 @@ class _Model(torch.nn.Module):
         return self.over(kt.values() if hasattr(kt, "values") else kt), kt
 
 
-def _parity(rank, world_size, sharding, pooling_name, opt_name, weighted=False):
+def _parity(rank, world_size, sharding, pooling_name, opt_name, weighted=False, tables=None):
+    if tables is not None:
+        global TABLES
+        TABLES = tables
     from torchrec_b200.distributed.model_parallel import DistributedModelParallel
     from torchrec_b200.distributed.types import ShardingEnv, ShardingPlan
     from torchrec_b200.modules.embedding_configs import PoolingType
@@ -170,3 +173,9 @@ def test_sharding_parity_mean_rowwise_adagrad(sharding):
 
 def test_sharding_parity_weighted():
     run_multi_process(_parity, world_size=2, sharding="mixed", pooling_name="SUM", opt_name="sgd", weighted=True)
+
+
+def test_sharding_rw_more_ranks_than_rows():
+    """Row-wise tables with fewer rows than ranks leave some ranks with empty shards (weights and row-wise state)."""
+    tables = [(3, 16, ["f0"]), (60, 16, ["f1", "f2"]), (2, 16, ["f3"]), (50, 16, ["f4"])]
+    run_multi_process(_parity, world_size=4, sharding="rw", pooling_name="SUM", opt_name="rowwise_adagrad", tables=tables)

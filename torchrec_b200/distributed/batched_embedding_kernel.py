@@ -145,9 +145,16 @@ class EmbeddingFusedOptimizer(FusedOptimizer):
             # one value per row: shard along rows exactly like the table; column shards of the same rows hold replicas,
             # of which the first (column offset 0 if present on this rank, else the lowest) represents the row block.
             seen_rows = set()
-            row_blocks: Dict[Tuple[int, int], ShardMetadata] = {}
+
+            def row_key(sm: ShardMetadata) -> Tuple[Any, ...]:
+                # empty shards (more ranks than rows) all start at the same row: keep one entry per placement
+                if sm.shard_sizes[0] == 0:
+                    return (sm.shard_offsets[0], 0, str(sm.placement))
+                return (sm.shard_offsets[0], sm.shard_sizes[0], "")
+
+            row_blocks: Dict[Tuple[Any, ...], ShardMetadata] = {}
             for sm in gm.shards_metadata:
-                rk = (sm.shard_offsets[0], sm.shard_sizes[0])
+                rk = row_key(sm)
                 if rk not in row_blocks or sm.shard_offsets[1] < row_blocks[rk].shard_offsets[1]:
                     row_blocks[rk] = sm
             metas = [
@@ -156,7 +163,7 @@ class EmbeddingFusedOptimizer(FusedOptimizer):
             ]
             for t, x in zip(tables, local):
                 lm = t.local_metadata
-                rk = (lm.shard_offsets[0], lm.shard_sizes[0])
+                rk = row_key(lm)
                 owner = row_blocks[rk]
                 if rk in seen_rows or list(owner.shard_offsets) != list(lm.shard_offsets):
                     continue
