@@ -148,7 +148,10 @@ def main() -> None:
             s.bind(("127.0.0.1", 0))
             os.environ["MASTER_PORT"] = str(s.getsockname()[1])
     os.environ.setdefault("LOCAL_WORLD_SIZE", str(world))
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    import datetime
+
+    # a short collective timeout: a rank that falls out of step ends the job in minutes, not after the 10-minute default
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device, timeout=datetime.timedelta(seconds=120))
 
     from torchrec_b200.datasets.random import RandomRecDataset
     from torchrec_b200.distributed.embeddingbag import EmbeddingBagCollectionSharder
@@ -284,8 +287,8 @@ def main() -> None:
         e2e = {"value": args.global_batch / (e2e_ms / args.steps / 1e3), "unit": "samples/s", "ms_per_step": e2e_ms / args.steps,
                "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": 4, "api": "TrainPipelineSparseDist.progress"}
 
-    if args.breakdown and rank == 0:
-        _breakdown(torch, dmp, optimizer, dev_batches[0])
+    if args.breakdown:
+        _breakdown(torch, dmp, optimizer, dev_batches[0], rank)  # a training step: every rank takes part
 
     if rank == 0:
         res = {
@@ -305,7 +308,7 @@ def main() -> None:
     dist.destroy_process_group()
 
 
-def _breakdown(torch, dmp, optimizer, batch) -> None:
+def _breakdown(torch, dmp, optimizer, batch, rank: int = 0) -> None:
     """Device time of forward / backward / optimizer of one step (stderr; diagnostic only)."""
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     torch.cuda.synchronize()
@@ -318,7 +321,8 @@ def _breakdown(torch, dmp, optimizer, batch) -> None:
     optimizer.step()
     ev[3].record()
     torch.cuda.synchronize()
-    print(f"breakdown ms: fwd {ev[0].elapsed_time(ev[1]):.3f} bwd {ev[1].elapsed_time(ev[2]):.3f} opt {ev[2].elapsed_time(ev[3]):.3f}", file=sys.stderr)
+    if rank == 0:
+        print(f"breakdown ms: fwd {ev[0].elapsed_time(ev[1]):.3f} bwd {ev[1].elapsed_time(ev[2]):.3f} opt {ev[2].elapsed_time(ev[3]):.3f}", file=sys.stderr)
 
 
 if __name__ == "__main__":
