@@ -68,6 +68,10 @@ def _extract_comm_data_type_size(sharder: Optional[ModuleSharder[nn.Module]], sh
     return float(fwd_a2a), float(bwd_a2a), float(fwd_rs), float(bwd_rs)
 
 
+# True when the row-wise output dist is the fused lookup + push kernel that skips empty bags (see _get_rw_sharding_perf)
+RW_SPARSE_REDUCE_SCATTER: bool = False
+
+
 class EmbeddingPerfEstimator(ShardEstimator):
     """Wall-time estimate of every shard of every option (fills ``shard.perf``)."""
 
@@ -193,12 +197,16 @@ class EmbeddingPerfEstimator(ShardEstimator):
                               fwd_comm, bwd_comm, num_poolings, device_bw, comms_bandwidths, bwd_compute_multiplier,
                               weighted_feature_bwd_compute_multiplier, is_pooled, shards, is_weighted=False, is_inference=False,
                               hierarchical=False, fwd_a2a=0.0, bwd_a2a=0.0) -> Perf:
-        """Every shard looks up ``1/shards`` of the ids of the global batch and contributes a partial sum for
-        every bag it touched; a bag of ``P`` ids touches at most ``min(P, shards)`` shards, which bounds the
-        bytes the fused reduce-scatter puts on the wire."""
+        """Every shard looks up ``1/shards`` of the ids of the global batch and contributes a partial sum for every
+        bag of the global batch.  The library reduce-scatter moves the dense ``[B_global, D]`` partials of every
+        shard.  A lookup kernel that pushes only the bags it touched straight into the owner's buffer moves less: a
+        bag of ``P`` ids touches at most ``min(P, shards)`` shards; ``RW_SPARSE_REDUCE_SCATTER`` selects that
+        model."""
         batch_inputs = sum(x * y * z for x, y, z in zip(input_lengths, num_poolings, batch_sizes)) / shards
         if is_pooled:
-            touched = sum(min(1.0, x / shards) if x < shards else 1.0 for x in input_lengths) / max(len(input_lengths), 1)
+            touched = 1.0
+            if RW_SPARSE_REDUCE_SCATTER:
+                touched = sum(min(1.0, x / shards) if x < shards else 1.0 for x in input_lengths) / max(len(input_lengths), 1)
             batch_outputs = sum(x * y for x, y in zip(num_poolings, batch_sizes)) * max(touched, 1.0 / shards)
         else:
             batch_outputs = batch_inputs
