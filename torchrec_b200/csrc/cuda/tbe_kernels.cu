@@ -231,6 +231,11 @@ struct BwdParams {
   int64_t* long_list;  // [2*cap] (head block, last block) of chains left to pass 3
   int* long_count;
   int Dpad;
+  // pooled gradients that live on peer ranks (fused exchange): bag b of the global batch is row b % B_local of
+  // rank b / B_local.  B_local == 0: all gradient rows are in `grad`.
+  PeerPtrs grad_peers;
+  int B_local;
+  float grad_scale;  // factor on every gradient row (1 / world size when gradients are averaged over ranks)
   OptParams opt;
 };
 
@@ -487,24 +492,34 @@ __global__ void __launch_bounds__(256, kVecs == 1 ? 4 : 2) tbe_bwd_block_kernel(
       float w = p.sorted_w ? p.sorted_w[i] : 1.f;
       int f;
       int64_t goff;
+      const char* gsrc = gbase;
+      bool local_grad = true;
       if (p.pooled) {
         f = src / p.B;
-        const int b = src - f * p.B;
+        int b = src - f * p.B;
+        if (p.B_local > 0) {
+          const int owner = b / p.B_local;
+          b -= owner * p.B_local;
+          gsrc = reinterpret_cast<const char*>(p.grad_peers.p[owner]);
+          local_grad = gsrc == gbase;
+        }
         goff = int64_t(b) * p.grad_stride + meta[M_OUTOFF * F + f];
         if (p.bag_scale) w *= p.bag_scale[src];
       } else {
         f = p.src_feature[src];
         goff = int64_t(src) * p.grad_stride;
       }
+      w *= p.grad_scale;
       const int D = int(meta[M_DIM * F + f]);
       const int64_t woff = meta[M_WOFF * F + f] + (key - meta[M_HASHOFF * F + f]) * D;
       const bool is_end = key != nxt;
-      const int64_t gbyte = goff * int64_t(sizeof(grad_t));
+      // the record holds the address of the row slice relative to the local gradient base (peer bases included)
+      const int64_t gbyte = (gsrc - gbase) + goff * int64_t(sizeof(grad_t));
       s_rec[wib][k] = make_uint4(uint32_t(uint64_t(gbyte)), uint32_t(uint64_t(gbyte) >> 32), __float_as_uint(w),
                                  uint32_t(is_end ? 1 : 0) | (uint32_t(D) << 1) | (uint32_t(f) << 16));
       s_woff[wib][k] = woff;
       s_key[wib][k] = key;
-      prefetch_l2_range(gbase + gbyte, D * int(sizeof(grad_t)));
+      if (local_grad) prefetch_l2_range(gbase + gbyte, D * int(sizeof(grad_t)));
       if (is_end && opt_type != OPT_DENSE_GRAD) {
         prefetch_l2_range(reinterpret_cast<const emb_t*>(p.weights) + woff, D * int(sizeof(emb_t)));
         if (opt_type == OPT_ROWWISE_ADAGRAD) prefetch_l2_range(p.mom1 + key, 4);
@@ -930,12 +945,13 @@ std::vector<at::Tensor> tbe_build_plan(const at::Tensor& meta, const at::Tensor&
 }
 
 // Apply the sorted plan: segment-reduce upstream gradient rows per table row and update in place.
-void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10::optional<at::Tensor> mom2,
-                        c10::optional<at::Tensor> dense_grad, const at::Tensor& meta, const at::Tensor& sorted_keys,
-                        const at::Tensor& sorted_src, const at::Tensor& sorted_w, const at::Tensor& src_feature,
-                        const at::Tensor& bag_scale, const at::Tensor& grad, int64_t grad_stride, int64_t B,
-                        int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
-                        double beta2, double weight_decay, int64_t step, double max_grad) {
+static void tbe_backward_apply_impl(at::Tensor weights, c10::optional<at::Tensor> mom1, c10::optional<at::Tensor> mom2,
+                                    c10::optional<at::Tensor> dense_grad, const at::Tensor& meta, const at::Tensor& sorted_keys,
+                                    const at::Tensor& sorted_src, const at::Tensor& sorted_w, const at::Tensor& src_feature,
+                                    const at::Tensor& bag_scale, const at::Tensor& grad, int64_t grad_stride, int64_t B,
+                                    int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
+                                    double beta2, double weight_decay, int64_t step, double max_grad,
+                                    const std::vector<int64_t>& grad_ptrs, int64_t B_local, double grad_scale) {
   const int64_t N = sorted_keys.numel();
   if (N == 0) return;
   c10::cuda::CUDAGuard guard(weights.device());
@@ -971,6 +987,20 @@ void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10:
   p.long_list = long_list.data_ptr<int64_t>();
   p.long_count = long_count.data_ptr<int>();
   p.Dpad = Dpad;
+  p.B_local = 0;
+  p.grad_scale = float(grad_scale);
+  for (int i = 0; i < kMaxPeers; ++i) p.grad_peers.p[i] = nullptr;
+  if (!grad_ptrs.empty()) {
+    TORCH_CHECK(pooled && B_local > 0 && int64_t(grad_ptrs.size()) * B_local == B && grad_ptrs.size() <= size_t(kMaxPeers),
+                "peer gradients: B must be world * B_local");
+    p.B_local = int(B_local);
+    bool has_local = false;
+    for (size_t i = 0; i < grad_ptrs.size(); ++i) {
+      p.grad_peers.p[i] = reinterpret_cast<void*>(grad_ptrs[i]);
+      has_local = has_local || p.grad_peers.p[i] == grad.data_ptr();
+    }
+    TORCH_CHECK(has_local, "grad must be this rank's own buffer among grad_ptrs");
+  }
   p.opt.type = int(opt_type);
   p.opt.lr = float(lr);
   p.opt.eps = float(eps);
@@ -994,6 +1024,30 @@ void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10:
     });
   });
   TRB_CUDA_CHECK(cudaGetLastError());
+}
+
+void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10::optional<at::Tensor> mom2,
+                        c10::optional<at::Tensor> dense_grad, const at::Tensor& meta, const at::Tensor& sorted_keys,
+                        const at::Tensor& sorted_src, const at::Tensor& sorted_w, const at::Tensor& src_feature,
+                        const at::Tensor& bag_scale, const at::Tensor& grad, int64_t grad_stride, int64_t B,
+                        int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
+                        double beta2, double weight_decay, int64_t step, double max_grad) {
+  tbe_backward_apply_impl(weights, mom1, mom2, dense_grad, meta, sorted_keys, sorted_src, sorted_w, src_feature, bag_scale, grad,
+                          grad_stride, B, max_D, pooled, opt_type, lr, eps, beta1, beta2, weight_decay, step, max_grad, {}, 0, 1.0);
+}
+
+// Backward of the fused lookup + exchange: the pooled gradient of bag b (of the global batch) is read from the
+// buffer of the rank that owns sample b (`grad_ptrs[b / B_local]`, peer-mapped), scaled by `grad_scale`.
+void tbe_backward_apply_dist(at::Tensor weights, c10::optional<at::Tensor> mom1, c10::optional<at::Tensor> mom2,
+                             c10::optional<at::Tensor> dense_grad, const at::Tensor& meta, const at::Tensor& sorted_keys,
+                             const at::Tensor& sorted_src, const at::Tensor& sorted_w, const at::Tensor& src_feature,
+                             const at::Tensor& bag_scale, const at::Tensor& grad, int64_t grad_stride, int64_t B,
+                             int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
+                             double beta2, double weight_decay, int64_t step, double max_grad,
+                             std::vector<int64_t> grad_ptrs, int64_t B_local, double grad_scale) {
+  tbe_backward_apply_impl(weights, mom1, mom2, dense_grad, meta, sorted_keys, sorted_src, sorted_w, src_feature, bag_scale, grad,
+                          grad_stride, B, max_D, pooled, opt_type, lr, eps, beta1, beta2, weight_decay, step, max_grad, grad_ptrs,
+                          B_local, grad_scale);
 }
 
 }  // namespace trb
@@ -1122,6 +1176,9 @@ extern "C" int trb_tbe_backward_apply_noalloc(const trb_tbe_bwd_noalloc_args* a,
   p.long_list = reinterpret_cast<int64_t*>(scratch + kNaOffLongList);
   p.long_count = reinterpret_cast<int*>(scratch + kNaOffCount);
   p.Dpad = a->max_D;
+  p.B_local = 0;
+  p.grad_scale = 1.f;
+  for (int i = 0; i < trb::kMaxPeers; ++i) p.grad_peers.p[i] = nullptr;
   p.opt.type = a->opt_type;
   p.opt.lr = a->lr;
   p.opt.eps = a->eps;
@@ -1163,12 +1220,18 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
       "Tensor sorted_keys, Tensor sorted_src, Tensor sorted_w, Tensor src_feature, Tensor bag_scale, Tensor grad, "
       "int grad_stride, int B, int max_D, bool pooled, int opt_type, float lr, float eps, float beta1, float beta2, "
       "float weight_decay, int step, float max_grad) -> ()");
+  m.def(
+      "tbe_backward_apply_dist(Tensor(a!) weights, Tensor(b!)? mom1, Tensor(c!)? mom2, Tensor(d!)? dense_grad, Tensor meta, "
+      "Tensor sorted_keys, Tensor sorted_src, Tensor sorted_w, Tensor src_feature, Tensor bag_scale, Tensor grad, "
+      "int grad_stride, int B, int max_D, bool pooled, int opt_type, float lr, float eps, float beta1, float beta2, "
+      "float weight_decay, int step, float max_grad, int[] grad_ptrs, int B_local, float grad_scale) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(trb200, CUDA, m) {
   m.impl("tbe_forward", &trb::tbe_forward);
   m.impl("tbe_build_plan", &trb::tbe_build_plan);
   m.impl("tbe_backward_apply", &trb::tbe_backward_apply);
+  m.impl("tbe_backward_apply_dist", &trb::tbe_backward_apply_dist);
 }
 
 TORCH_LIBRARY_IMPL(trb200, CompositeExplicitAutograd, m) { m.impl("tbe_forward_dist", &trb::tbe_forward_dist); }

@@ -364,6 +364,50 @@ class TableBatchedEmbeddingBags(nn.Module):
             return None if self.fused else dense_grad.to(w.dtype)
         return self._backward_cpu(w, grad_out, indices, offsets, psw, B)
 
+    # ---- fused lookup + exchange over peer-mapped buffers (one node, NVLink) ---------------------------
+    def _meta_tensor_at(self, device: torch.device, col_base: int) -> torch.Tensor:
+        """Metadata whose output column offsets start at ``col_base`` (this rank's block of the exchanged row)."""
+        cache = self.__dict__.setdefault("_meta_at", {})
+        key = (str(device), int(col_base))
+        if key not in cache:
+            m = self._meta_tensor(device).clone()
+            m[4] += int(col_base)
+            cache[key] = m
+        return cache[key]
+
+    def forward_push(self, indices: torch.Tensor, offsets: torch.Tensor, psw: Optional[torch.Tensor], B: int, B_local: int,
+                     out_ptrs: List[int], out_stride: int, col_base: int, out_dtype: torch.dtype) -> None:
+        """Pooled lookup of the global batch (``B`` bags per feature) whose result rows are stored directly into the
+        ``[B_local, out_stride]`` buffers of the ranks that own the samples (``out_ptrs[b // B_local]``), at column
+        ``col_base`` + the table's offset.  No output tensor: the caller synchronises with a peer barrier."""
+        _ext.require_cuda_ext("tbe_forward_dist")
+        w = self.weights.detach()
+        if indices.dtype != offsets.dtype:
+            offsets = offsets.to(indices.dtype)
+        torch.ops.trb200.tbe_forward_dist(
+            w, self._meta_tensor_at(w.device, col_base), indices.contiguous(), offsets.contiguous(), psw, out_ptrs,
+            _OUT_CODE[out_dtype], out_stride, B, B_local, self.max_D, int(self.pooling_mode), False, False, self._err,
+        )
+
+    def backward_pull(self, grad_local: torch.Tensor, grad_ptrs: List[int], grad_stride: int, indices: torch.Tensor, offsets: torch.Tensor,
+                      psw: Optional[torch.Tensor], B: int, B_local: int, col_base: int, grad_scale: float, plan: Optional[TBEPlan] = None) -> None:
+        """Backward + fused optimizer of ``forward_push``: the gradient row of bag ``b`` is read from
+        ``grad_ptrs[b // B_local]`` (``grad_local`` is this rank's own buffer among them)."""
+        assert self.fused, "the fused exchange is for tables with an in-backward optimizer"
+        _ext.require_cuda_ext("tbe_backward_apply_dist")
+        w = self.weights.detach()
+        self.step += 1
+        if plan is None:
+            plan = self.build_plan(indices, offsets, psw, B)
+        o = self.optimizer_args
+        eps = o.eta if o.optimizer == EmbOptimType.LARS_SGD else o.eps
+        torch.ops.trb200.tbe_backward_apply_dist(
+            w, self.momentum1 if self.momentum1.numel() else None, self.momentum2 if self.momentum2.numel() else None, None,
+            self._meta_tensor_at(w.device, col_base), plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale, grad_local,
+            grad_stride, B, self.max_D, True, _OPT_CODE[o.optimizer], o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay,
+            self.step, o.max_gradient, grad_ptrs, B_local, grad_scale,
+        )
+
     def _backward_cpu(self, w, grad_out, indices, offsets, psw, B) -> Optional[torch.Tensor]:
         F = len(self.feature_table_map)
         off = offsets.to(torch.int64)
