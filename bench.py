@@ -45,7 +45,7 @@ ZIPF_S = 1.05
 def parse_args() -> argparse.Namespace:
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--steps", type=int, default=50)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference", "baseline"])
     p.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
@@ -72,25 +72,38 @@ def reference_arm(args: argparse.Namespace) -> None:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi.  Started before the warm-up so that the tool is already
+    running when the timed region begins; ``mark_begin`` / ``mark_end`` bracket the timed region and only samples taken
+    between the marks are used.  A region shorter than the sampling period may hold no sample: then the samples taken
+    during the warm-up (the same steps, the same load) are used and ``window`` says so."""
 
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int) -> None:
         self.gpu_index = gpu_index
         self.path = tempfile.mktemp(prefix="trb200_clocks_", suffix=".csv")
         self.proc: Optional[subprocess.Popen] = None
+        self.t_begin: Optional[float] = None
+        self.t_end: Optional[float] = None
 
     def start(self) -> None:
         try:
             self.f = open(self.path, "w")
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu_index)],
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.gpu_index)],
                                          stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
+    def mark_begin(self) -> None:
+        self.t_begin = time.time()
+
+    def mark_end(self) -> None:
+        self.t_end = time.time()
+
     def stop(self) -> Dict[str, Any]:
+        import datetime
+
         out: Dict[str, Any] = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if self.proc is None:
             return out
@@ -100,29 +113,32 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         self.f.close()
-        sm, mx, reasons = [], [], set()
+        rows = []
         try:
             for line in open(self.path):
                 parts = [x.strip() for x in line.split(",")]
-                if len(parts) < 9:
+                if len(parts) < 10:
                     continue
                 try:
-                    sm.append(float(parts[1]))
-                    mx.append(float(parts[2]))
+                    ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    rows.append((ts, float(parts[2]), float(parts[3]), [v.lower().startswith("active") for v in parts[6:10]]))
                 except ValueError:
                     continue
-                for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], parts[5:9]):
-                    if v.lower().startswith("active"):
-                        reasons.add(name)
             os.remove(self.path)
         except Exception:
             pass
-        if sm:
-            sm.sort()
+        inside = [r for r in rows if self.t_begin is not None and self.t_end is not None and self.t_begin <= r[0] <= self.t_end]
+        window = "timed region"
+        if not inside:
+            inside, window = rows, "warm-up + timed region (timed region shorter than the sampling period)"
+        if inside:
+            sm = sorted(r[1] for r in inside)
             out["sm_mhz"] = sm[len(sm) // 2]
-            out["sm_max_mhz"] = max(mx)
-            out["samples"] = len(sm)
-        out["reasons"] = sorted(reasons)
+            out["sm_max_mhz"] = max(r[2] for r in inside)
+            out["samples"] = len(inside)
+            out["window"] = window
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            out["reasons"] = sorted({n for r in inside for n, a in zip(names, r[3]) if a})
         return out
 
 
@@ -229,12 +245,14 @@ def main() -> None:
 
     # ---- device-timed steps (inputs resident on the device; 4 distinct batches of ~60 MB ids each are cycled and the
     #      embedding tables (>100 GB) are far larger than L2, so no step re-reads cached inputs) -----------------
-    for i in range(args.warmup):
-        step(dev_batches[i % len(dev_batches)])
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for i in range(args.warmup):
+        step(dev_batches[i % len(dev_batches)])
+    sampler.mark_begin()
     total_ms = timed(lambda i: step(dev_batches[i % len(dev_batches)]), args.steps)
+    sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else {}
     ms_per_step = total_ms / args.steps
     value = args.global_batch / (ms_per_step / 1e3)
