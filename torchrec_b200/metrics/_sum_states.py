@@ -40,6 +40,9 @@ class SumStatesComputation(RecMetricComputation):
         if weights is None:
             weights = torch.ones_like(labels, dtype=torch.float32)
         n = labels.shape[-1]
+        # states are double sums: promote the per-example inputs once so that no partial sum is taken in float32
+        weights = weights.double()
+        labels = labels.double()
         for name, value in self._states(labels, predictions, weights, **kwargs).items():
             state = getattr(self, name)
             value = value.to(state.dtype)
