@@ -98,3 +98,12 @@ def cpu_ops():
     if not has_cpu_ext():
         raise RuntimeError(f"torchrec_b200: CPU native library unavailable: {_cpu_err}")
     return torch.ops.trb200_cpu
+
+
+def cpu_error() -> Optional[str]:
+    """Why the native CPU library did not load (None when it did or was not tried yet)."""
+    return _cpu_err
+
+
+def cuda_error() -> Optional[str]:
+    return _cuda_err
