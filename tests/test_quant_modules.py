@@ -1,0 +1,100 @@
+"""Quantized embedding modules against the float modules they were converted from (cf. ``torchrec/quant/tests``)."""
+import pytest
+import torch
+
+from torchrec_b200.modules.embedding_configs import DataType, EmbeddingBagConfig, EmbeddingConfig, PoolingType, QuantConfig
+from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection, EmbeddingCollection
+from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+
+def _qconfig(dtype):
+    import torch.ao.quantization as q
+
+    return QuantConfig(activation=q.PlaceholderObserver.with_args(dtype=torch.float), weight=q.PlaceholderObserver.with_args(dtype=dtype))
+
+
+def _kjt(keys, rows, B=9, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    lens, vals = [], []
+    for r in rows:
+        l = torch.randint(0, 5, (B,), generator=g)
+        lens.append(l); vals.append(torch.randint(0, r, (int(l.sum()),), generator=g))
+    return KeyedJaggedTensor.from_lengths_sync(keys=keys, values=torch.cat(vals), lengths=torch.cat(lens))
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.quint8, 0.05), (torch.quint4x2, 0.6), (torch.float16, 5e-3)])
+def test_quant_ebc_matches_float(dtype, tol):
+    from torchrec_b200.quant.embedding_modules import EmbeddingBagCollection as QEBC
+
+    tables = [EmbeddingBagConfig(name="t0", num_embeddings=40, embedding_dim=16, feature_names=["f0", "f1"], pooling=PoolingType.SUM),
+              EmbeddingBagConfig(name="t1", num_embeddings=30, embedding_dim=32, feature_names=["f2"], pooling=PoolingType.MEAN),
+              EmbeddingBagConfig(name="t2", num_embeddings=20, embedding_dim=16, feature_names=["f3"], pooling=PoolingType.SUM)]
+    ebc = EmbeddingBagCollection(tables)
+    ebc.qconfig = _qconfig(dtype)
+    q = QEBC.from_float(ebc)
+    kjt = _kjt(["f0", "f1", "f2", "f3"], [40, 40, 30, 20])
+    ref, out = ebc(kjt), q(kjt)
+    assert out.keys() == ref.keys() and out.length_per_key() == ref.length_per_key()
+    torch.testing.assert_close(out.values(), ref.values().detach(), rtol=0, atol=tol)
+    # state dict: packed tables under the float module's keys; optional split into payload + scale/bias
+    sd = q.state_dict()
+    assert set(sd) == {"embedding_bags.t0.weight", "embedding_bags.t1.weight", "embedding_bags.t2.weight"}
+    assert sd["embedding_bags.t0.weight"].dtype == torch.uint8
+    q2 = QEBC(q.embedding_bag_configs(), False, torch.device("cpu"))
+    q2.load_state_dict(sd)
+    torch.testing.assert_close(q2(kjt).values(), out.values())
+
+
+def test_quant_state_dict_split_scale_bias():
+    from torchrec_b200.quant.embedding_modules import EmbeddingBagCollection as QEBC, quant_prep_enable_quant_state_dict_split_scale_bias
+
+    ebc = EmbeddingBagCollection([EmbeddingBagConfig(name="t0", num_embeddings=10, embedding_dim=8, feature_names=["f0"])])
+    ebc.qconfig = _qconfig(torch.quint8)
+    quant_prep_enable_quant_state_dict_split_scale_bias(ebc)
+    sd = QEBC.from_float(ebc).state_dict()
+    assert sd["embedding_bags.t0.weight"].shape == (10, 8)
+    assert sd["embedding_bags.t0.weight_qscale"].shape == (10,) and sd["embedding_bags.t0.weight_qbias"].dtype == torch.float16
+    recon = sd["embedding_bags.t0.weight"].float() * sd["embedding_bags.t0.weight_qscale"].float().unsqueeze(1) + sd["embedding_bags.t0.weight_qbias"].float().unsqueeze(1)
+    torch.testing.assert_close(recon, ebc.embedding_bags["t0"].weight.detach(), rtol=0, atol=0.02)
+
+
+def test_quant_ec_matches_float():
+    from torchrec_b200.quant.embedding_modules import EmbeddingCollection as QEC
+
+    tables = [EmbeddingConfig(name="t0", num_embeddings=40, embedding_dim=16, feature_names=["f0"]),
+              EmbeddingConfig(name="t1", num_embeddings=30, embedding_dim=16, feature_names=["f1", "f2"])]
+    ec = EmbeddingCollection(tables, need_indices=True)
+    ec.qconfig = _qconfig(torch.quint8)
+    q = QEC.from_float(ec)
+    kjt = _kjt(["f0", "f1", "f2"], [40, 30, 30])
+    ref, out = ec(kjt), q(kjt)
+    assert out.keys() == ref.keys()
+    for k in ref:
+        torch.testing.assert_close(out[k].values(), ref[k].values().detach(), rtol=0, atol=0.02)
+        assert torch.equal(out[k].lengths(), ref[k].lengths())
+        assert torch.equal(out[k].weights(), ref[k].weights())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [32, 16, 8, 4, 2])
+@pytest.mark.parametrize("pooling", [0, 1, 2])
+def test_qtbe_kernel_matches_cpu(bits, pooling):
+    from torchrec_b200.modules.embedding_configs import PoolingMode
+    from torchrec_b200.ops.qtbe import QuantTableBatchedEmbeddingBags
+    from torchrec_b200.ops.quant_ops import quantize_rowwise_nbit
+
+    torch.manual_seed(bits + pooling)
+    D = 256 if pooling != 2 else 64
+    specs = [(300, D if pooling == 2 else 64, bits), (50, D, bits)]
+    ftm = [0, 1, 1]
+    cpu = QuantTableBatchedEmbeddingBags(specs, ftm, PoolingMode(pooling), torch.float32)
+    for t, (r, d, b) in enumerate(specs):
+        cpu.table_view(t).copy_(quantize_rowwise_nbit(torch.randn(r, d), b))
+    gpu = QuantTableBatchedEmbeddingBags(specs, ftm, PoolingMode(pooling), torch.float32, device="cuda")
+    gpu.weights.copy_(cpu.weights)
+    kjt = _kjt(["a", "b", "c"], [300, 50, 50], B=33, seed=5)
+    psw = torch.rand(kjt.values().numel()) if pooling == 0 else None
+    ref = cpu(kjt.values(), kjt.offsets(), psw)
+    out = gpu(kjt.values().cuda(), kjt.offsets().cuda(), None if psw is None else psw.cuda())
+    gpu.check_error()
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-4)

@@ -1,0 +1,172 @@
+// Quantized table-batched embedding lookup for inference (int8 / int4 / int2 rows, fp16 or fp32 rows too).
+//
+// Row format (row-wise N-bit quantization): D * bits / 8 payload bytes, then an fp16 scale and an fp16 bias:
+//   value[j] = scale * q[j] + bias.    Rows of one table are contiguous; different tables may use different bits.
+// One warp per bag; lane l owns elements [4l, 4l+4) (+128 per extra vector).  For int8 that is one 4-byte load per
+// row, for int4 a 2-byte load, for int2 a 1-byte load; accumulation in fp32; output fp16 / bf16 / fp32 written
+// straight into the [B, total_D] result.  The same kernel serves pooled (sum / mean / per-sample weights) and
+// unpooled lookups (pooling = 2: one output row per id).
+//
+// The reference gets this from an external kernel wheel (IntNBitTableBatchedEmbeddingBagsCodegen, call sites
+// torchrec/quant/embedding_modules.py:332-560).
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include "common.cuh"
+
+namespace trb {
+
+// per-feature metadata rows of the int64 [kQMetaRows, F] tensor
+enum QMetaRow : int { QM_WOFF = 0 /*byte offset of the table*/, QM_ROWS = 1, QM_DIM = 2, QM_OUTOFF = 3, QM_BITS = 4 /*32,16,8,4,2*/, kQMetaRows = 5 };
+
+struct QFwdParams {
+  const uint8_t* weights;
+  const int64_t* meta;
+  const void* indices;
+  const void* offsets;
+  const float* psw;
+  void* out;
+  int out_dtype;
+  int64_t out_stride;
+  int B, F, pooling;  // 0 sum, 1 mean, 2 none
+  int* err;
+};
+
+__device__ __forceinline__ int64_t qrow_bytes(int D, int bits) { return bits >= 16 ? int64_t(D) * bits / 8 : int64_t(D) * bits / 8 + 4; }
+
+// elements [e, e+4) of one row as fp32
+__device__ __forceinline__ float4 qload4(const uint8_t* row, int D, int bits, int e) {
+  if (bits == 32) return *reinterpret_cast<const float4*>(row + int64_t(e) * 4);
+  if (bits == 16) return Vec4<__half>::load_plain(reinterpret_cast<const __half*>(row) + e);
+  const __half2 sb = *reinterpret_cast<const __half2*>(row + int64_t(D) * bits / 8);
+  const float scale = __low2float(sb), bias = __high2float(sb);
+  uint32_t q0, q1, q2, q3;
+  if (bits == 8) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(row + e);
+    q0 = w & 0xff; q1 = (w >> 8) & 0xff; q2 = (w >> 16) & 0xff; q3 = w >> 24;
+  } else if (bits == 4) {
+    const uint32_t w = *reinterpret_cast<const uint16_t*>(row + e / 2);
+    q0 = w & 0xf; q1 = (w >> 4) & 0xf; q2 = (w >> 8) & 0xf; q3 = (w >> 12) & 0xf;
+  } else {  // 2 bits
+    const uint32_t w = row[e / 4];
+    q0 = w & 3; q1 = (w >> 2) & 3; q2 = (w >> 4) & 3; q3 = (w >> 6) & 3;
+  }
+  return make_float4(fmaf(scale, float(q0), bias), fmaf(scale, float(q1), bias), fmaf(scale, float(q2), bias), fmaf(scale, float(q3), bias));
+}
+
+template <typename idx_t, int kVecs>
+__global__ void __launch_bounds__(256) qtbe_fwd_kernel(QFwdParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t bag = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (bag >= int64_t(p.F) * p.B) return;
+  const int f = int(bag / p.B), b = int(bag - int64_t(f) * p.B);
+  const int F = p.F;
+  const idx_t* offsets = reinterpret_cast<const idx_t*>(p.offsets);
+  const idx_t* indices = reinterpret_cast<const idx_t*>(p.indices);
+  const int64_t start = offsets[bag], end = offsets[bag + 1];
+  const int D = int(p.meta[QM_DIM * F + f]), bits = int(p.meta[QM_BITS * F + f]);
+  const int64_t rows = p.meta[QM_ROWS * F + f];
+  const uint8_t* table = p.weights + p.meta[QM_WOFF * F + f];
+  const int64_t rb = qrow_bytes(D, bits);
+  const int out_off = int(p.meta[QM_OUTOFF * F + f]);
+  float4 acc[kVecs];
+#pragma unroll
+  for (int v = 0; v < kVecs; ++v) acc[v] = f4zero();
+  for (int64_t i = start; i < end; ++i) {
+    int64_t r = int64_t(indices[i]);
+    float w = p.psw ? p.psw[i] : 1.f;
+    if (r < 0 || r >= rows) {
+      if (lane == 0) atomicExch(p.err, 1);
+      r = 0;
+      w = 0.f;
+    }
+    const uint8_t* row = table + r * rb;
+    if (p.pooling == 2) {
+#pragma unroll
+      for (int v = 0; v < kVecs; ++v) {
+        const int e = v * 128 + lane * 4;
+        if (e < D) store4_dyn(p.out, i * p.out_stride + e, qload4(row, D, bits, e), p.out_dtype);
+      }
+      continue;
+    }
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+      const int e = v * 128 + lane * 4;
+      if (e < D) {
+        const float4 x = qload4(row, D, bits, e);
+        acc[v].x = fmaf(w, x.x, acc[v].x); acc[v].y = fmaf(w, x.y, acc[v].y);
+        acc[v].z = fmaf(w, x.z, acc[v].z); acc[v].w = fmaf(w, x.w, acc[v].w);
+      }
+    }
+  }
+  if (p.pooling == 2) return;
+  if (p.pooling == 1 && end > start) {
+    const float s = 1.f / float(end - start);
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) { acc[v].x *= s; acc[v].y *= s; acc[v].z *= s; acc[v].w *= s; }
+  }
+#pragma unroll
+  for (int v = 0; v < kVecs; ++v) {
+    const int e = v * 128 + lane * 4;
+    if (e < D) store4_dyn(p.out, int64_t(b) * p.out_stride + out_off + e, acc[v], p.out_dtype);
+  }
+}
+
+at::Tensor qtbe_forward(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets,
+                        const c10::optional<at::Tensor>& psw, int64_t B, int64_t total_D, int64_t max_D, int64_t pooling,
+                        int64_t out_dtype, at::Tensor err) {
+  TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == at::kByte && weights.is_contiguous());
+  TORCH_CHECK(meta.size(0) == kQMetaRows && meta.scalar_type() == at::kLong && meta.is_contiguous());
+  TORCH_CHECK(indices.scalar_type() == offsets.scalar_type(), "indices and offsets must share a dtype");
+  TORCH_CHECK(max_D % 4 == 0 && max_D <= 1024, "embedding dims must be multiples of 4, at most 1024");
+  const int F = int(meta.size(1));
+  c10::cuda::CUDAGuard guard(weights.device());
+  auto dt = out_dtype == OUT_F32 ? at::kFloat : (out_dtype == OUT_F16 ? at::kHalf : at::kBFloat16);
+  at::Tensor out;
+  int64_t stride;
+  if (pooling == 2) {
+    out = at::empty({indices.numel(), max_D}, weights.options().dtype(dt));
+    stride = max_D;
+  } else {
+    out = at::empty({B, total_D}, weights.options().dtype(dt));
+    stride = total_D;
+  }
+  if (F == 0 || B == 0) return out;
+  QFwdParams p;
+  p.weights = weights.data_ptr<uint8_t>();
+  p.meta = meta.data_ptr<int64_t>();
+  p.indices = indices.data_ptr();
+  p.offsets = offsets.data_ptr();
+  p.psw = psw.has_value() && psw->defined() ? psw->data_ptr<float>() : nullptr;
+  p.out = out.data_ptr();
+  p.out_dtype = int(out_dtype);
+  p.out_stride = stride;
+  p.B = int(B);
+  p.F = F;
+  p.pooling = int(pooling);
+  p.err = err.data_ptr<int>();
+  const int64_t nbags = int64_t(F) * B;
+  const int64_t blocks = (nbags * 32 + 255) / 256;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const bool i64 = indices.scalar_type() == at::kLong;
+  const int nv = max_D <= 128 ? 1 : (max_D <= 256 ? 2 : (max_D <= 512 ? 4 : 8));
+#define TRB_Q_LAUNCH(NV)                                                                          \
+  if (i64) qtbe_fwd_kernel<int64_t, NV><<<blocks, 256, 0, stream>>>(p);                             \
+  else qtbe_fwd_kernel<int32_t, NV><<<blocks, 256, 0, stream>>>(p);
+  if (nv == 1) { TRB_Q_LAUNCH(1) } else if (nv == 2) { TRB_Q_LAUNCH(2) } else if (nv == 4) { TRB_Q_LAUNCH(4) } else { TRB_Q_LAUNCH(8) }
+#undef TRB_Q_LAUNCH
+  TRB_CUDA_CHECK(cudaGetLastError());
+  return out;
+}
+
+}  // namespace trb
+
+TORCH_LIBRARY_FRAGMENT(trb200, m) {
+  m.def(
+      "qtbe_forward(Tensor weights, Tensor meta, Tensor indices, Tensor offsets, Tensor? psw, int B, int total_D, int max_D, "
+      "int pooling, int out_dtype, Tensor(a!) err) -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(trb200, CUDA, m) { m.impl("qtbe_forward", &trb::qtbe_forward); }
