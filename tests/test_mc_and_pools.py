@@ -1,0 +1,73 @@
+"""Managed collision (admission, eviction, remap stability), object pools, feature processors (cf. the reference's
+``torchrec/modules/tests/test_mc_modules.py``, ``test_tensor_pool.py``, ``test_kjt_pool_lookup.py``)."""
+import torch
+
+from torchrec_b200.modules.embedding_configs import EmbeddingBagConfig
+from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
+from torchrec_b200.modules.mc_embedding_modules import ManagedCollisionEmbeddingBagCollection
+from torchrec_b200.modules.mc_modules import DistanceLFU_EvictionPolicy, LFU_EvictionPolicy, LRU_EvictionPolicy, ManagedCollisionCollection, MCHManagedCollisionModule
+from torchrec_b200.sparse.jagged_tensor import JaggedTensor, KeyedJaggedTensor
+
+
+def _jt(ids):
+    ids = torch.tensor(ids, dtype=torch.int64)
+    return {"f": JaggedTensor(values=ids, lengths=torch.ones(ids.numel(), dtype=torch.int64))}
+
+
+def test_mch_lfu_admits_frequent_ids_and_keeps_slots():
+    mc = MCHManagedCollisionModule(zch_size=3, device=torch.device("cpu"), eviction_policy=LFU_EvictionPolicy(), eviction_interval=2)
+    mc.train()
+    mc(_jt([1000, 1000, 1000, 2000, 2000, 3000]))
+    out = mc(_jt([4000, 1000]))["f"].values()  # second batch triggers the rebuild after profiling
+    # 4 candidates for 3 slots: 1000 (4x), 2000 (2x) and one of the singletons are admitted
+    members = set(mc._mch_sorted_raw_ids[mc._mch_sorted_raw_ids != torch.iinfo(torch.int64).max].tolist())
+    assert {1000, 2000} <= members and len(members) == 3
+    a = mc.remap(_jt([1000, 2000]))["f"].values().tolist()
+    assert len(set(a)) == 2 and all(0 <= x < 3 for x in a)
+    # stable: the same ids keep their slots over later rebuilds as long as they stay popular
+    for _ in range(4):
+        mc(_jt([1000, 2000, 1000]))
+    assert mc.remap(_jt([1000, 2000]))["f"].values().tolist() == a
+    assert int(mc.open_slots()) == 0
+
+
+def test_mch_lru_evicts_stale_ids_and_reports_rows():
+    mc = MCHManagedCollisionModule(zch_size=2, device=torch.device("cpu"), eviction_policy=LRU_EvictionPolicy(), eviction_interval=1)
+    mc.train()
+    mc(_jt([10, 20]))
+    slots = dict(zip([10, 20], mc.remap(_jt([10, 20]))["f"].values().tolist()))
+    assert mc.evict() is None
+    mc(_jt([20]))          # refresh 20
+    mc(_jt([30]))          # 30 enters, 10 is the stalest member
+    ev = mc.evict()
+    assert ev is not None and ev.tolist() == [slots[10]]
+    assert mc.remap(_jt([30]))["f"].values().tolist() == [slots[10]]
+    assert mc.remap(_jt([20]))["f"].values().tolist() == [slots[20]]
+    # eval mode does not profile
+    mc.eval()
+    mc(_jt([40, 40, 40]))
+    assert 40 not in mc._mch_sorted_raw_ids.tolist()
+
+
+def test_distance_lfu_score_prefers_recent_over_old_frequent():
+    p = DistanceLFU_EvictionPolicy(decay_exponent=2.0)
+    s = p.score(torch.tensor([10, 3]), torch.tensor([0, 9]), 10)
+    assert s[1] > s[0]
+
+
+def test_mc_ebc_resets_rows_of_evicted_ids():
+    cfg = EmbeddingBagConfig(name="t", num_embeddings=2, embedding_dim=4, feature_names=["f"])
+    ebc = EmbeddingBagCollection([cfg])
+    mcc = ManagedCollisionCollection({"t": MCHManagedCollisionModule(zch_size=2, device=torch.device("cpu"), eviction_policy=LRU_EvictionPolicy(), eviction_interval=1)}, [cfg])
+    m = ManagedCollisionEmbeddingBagCollection(ebc, mcc, return_remapped_features=True)
+    m.train()
+    kjt = lambda ids: KeyedJaggedTensor.from_lengths_sync(keys=["f"], values=torch.tensor(ids), lengths=torch.ones(len(ids), dtype=torch.int64))
+    m(kjt([111, 222]))
+    with torch.no_grad():
+        ebc.embedding_bags["t"].weight.fill_(7.0)
+    m(kjt([222]))
+    out, remapped = m(kjt([333]))   # 333 takes 111's slot: that row is re-initialised, 222's row is untouched
+    w = ebc.embedding_bags["t"].weight.detach()
+    slot_333 = int(remapped.values()[0])
+    assert (w[slot_333].abs() < 7.0).all() and (w[1 - slot_333] == 7.0).all()
+    torch.testing.assert_close(out.values()[0], w[slot_333])
