@@ -176,3 +176,57 @@ def test_experimental_warns_once():
         warnings.simplefilter("always")
         f(); f()
     assert len(w) == 1
+
+
+def test_cmd_conf_builds_flags_from_dataclasses(tmp_path):
+    import dataclasses
+    import sys
+
+    from torchrec_b200.distributed.benchmark.benchmark_base import cmd_conf
+
+    @dataclasses.dataclass
+    class Opt:
+        steps: int = 3
+        name: str = "a"
+        flag: bool = False
+
+    seen = {}
+
+    @cmd_conf
+    def main(opt: Opt) -> None:
+        seen["opt"] = opt
+
+    cfg = tmp_path / "c.yml"
+    cfg.write_text("steps: 7\nname: from_yaml\n")
+    old = sys.argv
+    try:
+        sys.argv = ["prog", "--yaml_config", str(cfg), "--name", "cli"]
+        main()
+    finally:
+        sys.argv = old
+    assert seen["opt"].steps == 7 and seen["opt"].name == "cli" and seen["opt"].flag is False
+
+
+def test_bert4rec_forward_backward():
+    from torchrec_b200.models.bert4rec import BERT4Rec
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    torch.manual_seed(0)
+    m = BERT4Rec(vocab_size=50, max_len=6, emb_dim=16, nhead=2, num_layers=1, dropout=0.0)
+    lengths = torch.tensor([3, 6, 1])
+    kjt = KeyedJaggedTensor(keys=["item"], values=torch.randint(0, 50, (10,)), lengths=lengths)
+    out = m(kjt)
+    assert out.shape == (3, 6, 50)
+    out.sum().backward()
+    assert m.history.ec.embeddings["item_embedding"].weight.grad is not None
+    # padded positions do not influence valid ones: changing nothing but the padding mask input length keeps row 1 identical
+    m.eval()
+    with torch.no_grad():
+        a = m(kjt)[1]
+        kjt2 = KeyedJaggedTensor(keys=["item"], values=kjt.values()[3:9], lengths=torch.tensor([6]))
+        b = m(kjt2)[0]
+    torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)
+    pos = torch.tensor([0, 7])
+    sl = m.sampled_logits(kjt, pos, torch.tensor([4, 5]), torch.tensor([1, 2, 3]))
+    assert sl.shape == (2, 4)
+    torch.testing.assert_close(sl[:, 0], m(kjt).reshape(-1, 50)[pos, torch.tensor([4, 5])], rtol=1e-4, atol=1e-5)
