@@ -1,5 +1,6 @@
 """Managed collision (admission, eviction, remap stability), object pools, feature processors (cf. the reference's
 ``torchrec/modules/tests/test_mc_modules.py``, ``test_tensor_pool.py``, ``test_kjt_pool_lookup.py``)."""
+import pytest
 import torch
 
 from torchrec_b200.modules.embedding_configs import EmbeddingBagConfig
@@ -71,3 +72,41 @@ def test_mc_ebc_resets_rows_of_evicted_ids():
     slot_333 = int(remapped.values()[0])
     assert (w[slot_333].abs() < 7.0).all() and (w[1 - slot_333] == 7.0).all()
     torch.testing.assert_close(out.values()[0], w[slot_333])
+
+
+def test_hash_zch_module_train_eval_evict_and_rebuild():
+    from torchrec_b200.modules.hash_mc_evictions import HashZchEvictionConfig, HashZchEvictionPolicyName
+    from torchrec_b200.modules.hash_mc_modules import HashZchManagedCollisionModule
+    from torchrec_b200.sparse.jagged_tensor import JaggedTensor
+
+    m = HashZchManagedCollisionModule(zch_size=64, device=torch.device("cpu"), total_num_buckets=4, max_probe=16, name="t", tb_logging_frequency=1,
+                                      eviction_policy_name=HashZchEvictionPolicyName.SINGLE_TTL_EVICTION, eviction_config=HashZchEvictionConfig(features=["f"], single_ttl=24))
+    ids = torch.tensor([10**10 + 3, 7, 7, 123456789, 42])
+    jt = JaggedTensor(values=ids, lengths=torch.tensor([2, 0, 3]))
+    out = m({"f": jt})["f"]
+    v = out.values()
+    assert v[1] == v[2] and len(set(v.tolist())) == 4 and (v < 64).all() and (v >= 0).all()
+    assert torch.equal(out.lengths(), jt.lengths())
+    assert int(m.open_slots()) == 60
+    m.validate_state()
+    assert m._scalar_logger.last_report["t/train/insert_rate"] == 1.0
+    assert m.evict() is None
+    sd = m.state_dict()
+    assert "_hash_zch_identities" in sd and "_hash_zch_metadata" in sd
+    # eval: read-only, known ids keep their rows
+    m.eval()
+    again = m({"f": JaggedTensor(values=torch.tensor([42, 7, 999]), lengths=torch.tensor([3]))})["f"].values()
+    assert again[0] == v[4] and again[1] == v[1] and int(m.open_slots()) == 60
+    # a shard of buckets [2, 4) keeps global row numbers
+    shard = m.rebuild_with_output_id_range((32, 64))
+    shard.train()
+    o = shard({"f": JaggedTensor(values=torch.tensor([2, 6, 10, 3]), lengths=torch.tensor([4]))})["f"].values()
+    assert ((o >= 32) & (o < 64)).all() and (o[:3] < 48).all() and o[3] >= 48
+    with pytest.raises(RuntimeError):
+        m.rebuild_with_output_id_range((5, 64))
+    # disable_fallback drops unknown ids from their bags in eval
+    m2 = HashZchManagedCollisionModule(zch_size=8, device=torch.device("cpu"), total_num_buckets=1, max_probe=8, disable_fallback=True)
+    m2({"f": JaggedTensor(values=torch.tensor([1, 2]), lengths=torch.tensor([2]))})
+    m2.eval()
+    r = m2({"f": JaggedTensor(values=torch.tensor([1, 55, 2, 66]), lengths=torch.tensor([2, 2]))})["f"]
+    assert r.lengths().tolist() == [1, 1] and r.values().numel() == 2

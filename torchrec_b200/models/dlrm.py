@@ -255,7 +255,10 @@ class DLRMTrain(nn.Module):
     def forward(self, batch: Batch) -> Tuple[torch.Tensor, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]:
         logits = self.model(batch.dense_features, batch.sparse_features)
         logits = logits.squeeze(-1)
-        loss = self.loss_fn(logits.float(), batch.labels.float())
+        if logits.is_cuda and type(self.loss_fn) is nn.BCEWithLogitsLoss and self.loss_fn.weight is None and self.loss_fn.pos_weight is None and self.loss_fn.reduction == "mean":
+            loss = dense_ops.bce_with_logits_mean(logits, batch.labels)  # loss and its gradient in one kernel
+        else:
+            loss = self.loss_fn(logits.float(), batch.labels.float())
         return loss, (loss.detach(), logits.detach(), batch.labels.detach())
 
 

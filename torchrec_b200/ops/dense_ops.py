@@ -221,8 +221,27 @@ def dot_interaction(dense: torch.Tensor, sparse: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------
 # loss
 # --------------------------------------------------------------------------------------
-def bce_with_logits_mean(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
-    return torch.nn.functional.binary_cross_entropy_with_logits(logits.float(), labels.float())
+class _BCEWithLogits(torch.autograd.Function):
+    """Mean binary cross entropy whose forward kernel also writes d(loss)/d(logit): backward is one scale."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, weights):
+        loss, grad = torch.ops.trb200.bce_with_logits_fwd_bwd(logits.contiguous(), labels.float().contiguous(), None if weights is None else weights.float().contiguous())
+        ctx.save_for_backward(grad)
+        ctx.in_dtype = logits.dtype
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        (grad,) = ctx.saved_tensors
+        return (grad * g).to(ctx.in_dtype), None, None
+
+
+def bce_with_logits_mean(logits: torch.Tensor, labels: torch.Tensor, weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``mean(w * BCE(sigmoid(logits), labels))``; on a CUDA device one fused kernel computes loss and gradient."""
+    if logits.is_cuda and logits.dtype in (torch.float32, torch.float16, torch.bfloat16) and _ext.use_cuda_kernel(logits, "bce_with_logits"):
+        return _BCEWithLogits.apply(logits, labels, weights)
+    return torch.nn.functional.binary_cross_entropy_with_logits(logits.float(), labels.float(), weight=None if weights is None else weights.float())
 
 
 # --------------------------------------------------------------------------------------

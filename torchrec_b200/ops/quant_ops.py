@@ -20,7 +20,7 @@ def row_bytes(dim: int, bits: int) -> int:
 
 
 def quantize_rowwise_nbit(weight: torch.Tensor, bits: int) -> torch.Tensor:
-    """fp32 ``[R, D]`` -> uint8 ``[R, row_bytes]``."""
+    """``[R, D]`` -> uint8 ``[R, row_bytes]`` (one kernel on a CUDA device: a warp per row finds min/max and packs)."""
     assert weight.dim() == 2
     R, D = weight.shape
     w = weight.detach().float()
@@ -29,6 +29,14 @@ def quantize_rowwise_nbit(weight: torch.Tensor, bits: int) -> torch.Tensor:
     if bits == 16:
         return w.half().contiguous().view(torch.uint8).view(R, D * 2)
     assert bits in (8, 4, 2) and (D * bits) % 8 == 0
+    if weight.is_cuda and R > 0:
+        from . import _ext
+
+        _ext.require_cuda_ext("rowwise_quantize_nbit")
+        src = weight.detach()
+        if src.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            src = src.float()
+        return torch.ops.trb200.rowwise_quantize_nbit(src.contiguous(), bits)
     qmax = float(2 ** bits - 1)
     lo = w.min(dim=1, keepdim=True).values if R else w.new_zeros(0, 1)
     hi = w.max(dim=1, keepdim=True).values if R else w.new_zeros(0, 1)

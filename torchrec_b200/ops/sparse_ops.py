@@ -32,6 +32,17 @@ def _kern(t: torch.Tensor, name: str) -> bool:
     return _ext.use_cuda_kernel(t, name)
 
 
+def _cpu_native(name: str, *tensors: Optional[torch.Tensor]) -> bool:
+    """Host tensors that take no part in autograd go to the C++ implementation (``csrc/cpu/sparse_cpu.cpp``) when the host
+    library is built; the composite implementation stays the oracle and the differentiable path."""
+    if name in _COMPOSITE_ONLY or os.environ.get("TRB200_CPU_NATIVE", "1") == "0":
+        return False
+    for t in tensors:
+        if t is not None and (t.device.type != "cpu" or t.requires_grad):
+            return False
+    return _ext.has_cpu_ext()
+
+
 # --------------------------------------------------------------------------------------
 # scans
 # --------------------------------------------------------------------------------------
@@ -139,6 +150,8 @@ def permute_2D_sparse_data(
         return torch.ops.trb200.permute_2d_sparse_data(
             permute, lengths, values, weights, -1 if permuted_lengths_sum is None else int(permuted_lengths_sum)
         )
+    if values.numel() > 0 and lengths.dtype in (torch.int32, torch.int64) and _cpu_native("permute_2D_sparse_data", values, weights, lengths):
+        return _ext.cpu_ops().permute_2d_sparse_data(permute, lengths, values, weights)
     T, B = lengths.shape
     p = permute.to(torch.int64)
     out_lengths = lengths.index_select(0, p)
@@ -250,6 +263,13 @@ def block_bucketize_sparse_features(
         return torch.ops.trb200.block_bucketize(
             lengths, indices, bucketize_pos, sequence, block_sizes, my_size, weights, keep_orig_idx
         )
+    if (
+        batch_size_per_feature is None and block_bucketize_pos is None and total_num_blocks is None and block_sizes.numel() > 0
+        and lengths.dtype in (torch.int32, torch.int64) and indices.dtype in (torch.int32, torch.int64)
+        and (weights is None or weights.dtype == torch.float32)
+        and _cpu_native("block_bucketize_sparse_features", indices, lengths, weights)
+    ):
+        return _ext.cpu_ops().block_bucketize(lengths, indices, bucketize_pos, sequence, block_sizes, my_size, weights, keep_orig_idx)
     n_bags = lengths.numel()
     F = block_sizes.numel()
     N = indices.numel()
@@ -396,14 +416,78 @@ def permute_pooled_embs(pooled: torch.Tensor, dims: List[int], permute: List[int
     return pooled.index_select(1, cols)
 
 
+class RegroupPlan:
+    """Descriptor tables of one regroup (which column block of which input feeds which block of which group) for the one-launch
+    kernel, forward and backward, kept on the device."""
+
+    def __init__(self, in_lengths: List[List[int]], in_keys: List[List[str]], groups: List[List[str]], device: torch.device) -> None:
+        loc = {}
+        for ti, (keys, lens) in enumerate(zip(in_keys, in_lengths)):
+            o = 0
+            for k, l in zip(keys, lens):
+                if k not in loc:
+                    loc[k] = (ti, o, l)
+                o += l
+        self.in_widths = [sum(l) for l in in_lengths]
+        self.out_widths = [sum(loc[k][2] for k in g) for g in groups]
+        fwd_desc, fwd_src = [], []
+        readers = {}  # (in tensor, in offset, len) -> [(group, offset in group)]
+        for gi, g in enumerate(groups):
+            o = 0
+            for k in g:
+                ti, io, l = loc[k]
+                fwd_desc.append([gi, o, l, len(fwd_src), 1])
+                fwd_src.append([ti, io])
+                readers.setdefault((ti, io, l), []).append((gi, o))
+                o += l
+        bwd_desc, bwd_src = [], []
+        for ti, (keys, lens) in enumerate(zip(in_keys, in_lengths)):
+            o = 0
+            for k, l in zip(keys, lens):
+                rs = readers.get((ti, o, l), []) if loc[k] == (ti, o, l) else []
+                bwd_desc.append([ti, o, l, len(bwd_src), len(rs)])
+                bwd_src.extend([list(r) for r in rs])
+                o += l
+        mk = lambda rows, w: torch.tensor(rows if rows else [[0] * w][:0], dtype=torch.int32, device=device).reshape(-1, w)
+        self.fwd_desc, self.fwd_src = mk(fwd_desc, 5), mk(fwd_src, 2)
+        self.bwd_desc, self.bwd_src = mk(bwd_desc, 5), mk(bwd_src, 2)
+
+
+class _KTRegroup(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, plan: RegroupPlan, *values: torch.Tensor):
+        ctx.plan = plan
+        outs = torch.ops.trb200.kt_regroup([v if v.stride(1) == 1 else v.contiguous() for v in values], plan.out_widths, plan.fwd_desc, plan.fwd_src)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads: torch.Tensor):
+        plan = ctx.plan
+        B = next(g.shape[0] for g in grads if g is not None)
+        ref = next(g for g in grads if g is not None)
+        gs = [g if g is not None else ref.new_zeros(B, w) for g, w in zip(grads, plan.out_widths)]
+        gs = [g if g.stride(1) == 1 else g.contiguous() for g in gs]
+        return (None, *torch.ops.trb200.kt_regroup(gs, plan.in_widths, plan.bwd_desc, plan.bwd_src))
+
+
+_REGROUP_PLANS = {}
+
+
 def permute_multi_embedding(
     values: List[torch.Tensor], in_lengths: List[List[int]], in_keys: List[List[str]], groups: List[List[str]]
 ) -> List[torch.Tensor]:
     """Gather key-blocks from several ``[B, sum(D)]`` tensors into grouped outputs.
 
-    Differentiable (built from ``narrow``/``cat``); duplicates across groups are allowed
-    and their gradients are summed by autograd.
+    Differentiable; a key may appear in several groups (its gradients are summed).  On a CUDA device the whole regroup is one
+    kernel launch forward and one backward (``kt_regroup``); elsewhere it is built from ``narrow``/``cat``.
     """
+    v0 = values[0]
+    if v0.is_cuda and len(values) <= 32 and len(groups) <= 32 and all(v.dtype == v0.dtype and v.dim() == 2 for v in values) and _kern(v0, "kt_regroup"):
+        key = (tuple(tuple(l) for l in in_lengths), tuple(tuple(k) for k in in_keys), tuple(tuple(g) for g in groups), v0.device)
+        plan = _REGROUP_PLANS.get(key)
+        if plan is None:
+            plan = _REGROUP_PLANS[key] = RegroupPlan(in_lengths, in_keys, groups, v0.device)
+        return list(_KTRegroup.apply(plan, *values))
     loc = {}
     for ti, (keys, lens) in enumerate(zip(in_keys, in_lengths)):
         o = 0
@@ -416,3 +500,60 @@ def permute_multi_embedding(
         parts = [values[loc[k][0]].narrow(1, loc[k][1], loc[k][2]) for k in g]
         outs.append(torch.cat(parts, dim=1) if len(parts) > 1 else parts[0].contiguous())
     return outs
+
+
+# --------------------------------------------------------------------------------------
+# managed-collision hash and pruning remap
+# --------------------------------------------------------------------------------------
+ZCH_NO_EVICT, ZCH_TTL, ZCH_LRU = 0, 1, 2
+ZCH_EMPTY_SCORE = 2**31 - 1
+
+
+def zch_probe(
+    ids: torch.Tensor,
+    identities: torch.Tensor,
+    metadata: Optional[torch.Tensor],
+    segments: torch.Tensor,
+    input_hash_size: int = 0,
+    out_offset: int = 0,
+    max_probe: int = 128,
+    readonly: bool = False,
+    disable_fallback: bool = False,
+    input_metadata: Optional[torch.Tensor] = None,
+    eviction_threshold: int = -1,
+    eviction_policy: int = ZCH_NO_EVICT,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Multi-probe zero-collision hash: ``ids -> (slot, evicted_slot)`` against the slot table ``identities`` (-1 = empty),
+    updated in place unless ``readonly``.  ``segments`` are the global boundaries of the hash buckets, the table covers the slots
+    ``[out_offset, out_offset + len(identities))``.  A miss claims an empty slot among the ``max_probe`` slots after its hash
+    position inside its bucket, or evicts one whose score in ``metadata`` expired (TTL) / is the oldest (LRU); with no slot free it
+    shares the row at its hash position, or gets -1 with ``disable_fallback``.  Duplicate ids are resolved once.
+    CUDA: ``misc_kernels.cu`` (lookup and insert launches); CPU: ``csrc/cpu/sparse_cpu.cpp``."""
+    ids = ids.to(torch.int64).contiguous()
+    args = (identities, metadata, segments.to(device=ids.device, dtype=torch.int64), int(input_hash_size), int(out_offset), int(max_probe), bool(readonly),
+            bool(disable_fallback), None if input_metadata is None else input_metadata.to(torch.int32).contiguous(), int(eviction_threshold), int(eviction_policy))
+    op = torch.ops.trb200.zch_probe if _kern(ids, "zch_probe") else _ext.cpu_ops().zch_probe
+    if readonly or ids.numel() == 0:
+        return op(ids, *args)
+    # one probe per distinct id: two copies of a new id must not race for two slots
+    uniq, inverse = torch.unique(ids, return_inverse=True)
+    um = None
+    if args[8] is not None:
+        um = torch.zeros(uniq.numel(), dtype=torch.int32, device=ids.device).scatter_reduce_(0, inverse, args[8], reduce="amax", include_self=False)
+    slots, evicted = op(uniq, *args[:8], um, *args[9:])
+    ev = torch.full_like(ids, -1)
+    first = torch.full((uniq.numel(),), ids.numel(), dtype=torch.int64, device=ids.device).scatter_reduce_(
+        0, inverse, torch.arange(ids.numel(), device=ids.device), reduce="amin", include_self=True)
+    ev[first] = evicted
+    return slots.index_select(0, inverse), ev
+
+
+def itep_remap(values: torch.Tensor, feature_offsets: torch.Tensor, feature_buffer: torch.Tensor, address_lookup: torch.Tensor, row_util: torch.Tensor,
+               buffer_offsets: torch.Tensor, update_util: bool) -> torch.Tensor:
+    """Remap the ids of pruned tables through ``address_lookup`` (entry ``v >= 0``: own row ``v``; ``v < 0``: shared row
+    ``-(v+1)``) and, when ``update_util``, add one to ``row_util`` of every id seen.  ``feature_offsets [F+1]`` cuts ``values`` into
+    features, ``feature_buffer [F]`` (int32) names each feature's buffer or -1."""
+    v = values.to(torch.int64).contiguous()
+    op = torch.ops.trb200.itep_remap if _kern(v, "itep_remap") else _ext.cpu_ops().itep_remap
+    return op(v, feature_offsets.to(device=v.device, dtype=torch.int64), feature_buffer.to(device=v.device, dtype=torch.int32), address_lookup, row_util,
+              buffer_offsets.to(device=v.device, dtype=torch.int64), bool(update_util)).to(values.dtype)
