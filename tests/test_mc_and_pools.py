@@ -110,3 +110,46 @@ def test_hash_zch_module_train_eval_evict_and_rebuild():
     m2.eval()
     r = m2({"f": JaggedTensor(values=torch.tensor([1, 55, 2, 66]), lengths=torch.tensor([2, 2]))})["f"]
     assert r.lengths().tolist() == [1, 1] and r.values().numel() == 2
+
+
+def test_itep_unsharded_prunes_and_remaps():
+    from torchrec_b200.modules.itep_embedding_modules import ITEPEmbeddingBagCollection
+    from torchrec_b200.modules.itep_modules import GenericITEPModule
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    torch.manual_seed(0)
+    ebc = EmbeddingBagCollection(tables=[EmbeddingBagConfig(name="t0", embedding_dim=4, num_embeddings=4, feature_names=["f0"]),
+                                         EmbeddingBagConfig(name="t1", embedding_dim=4, num_embeddings=10, feature_names=["f1"])])
+    itep = GenericITEPModule({"t0": 12}, lookups=[ebc], pruning_interval=1001)
+    m = ITEPEmbeddingBagCollection(ebc, itep)
+    assert itep.address_lookup.tolist() == [0, 1, 2, 3, -1, -2, -3, -4, -1, -2, -3, -4]
+    sd = m.state_dict()
+    assert "_itep_module.t0_itp_address_lookup" in sd and "_itep_module.t0_itp_row_util" in sd and "_iter" in sd
+
+    def batch(ids0):
+        return KeyedJaggedTensor(keys=["f0", "f1"], values=torch.tensor(ids0 + [9, 3]), lengths=torch.tensor([len(ids0), 0, 1, 1]))
+
+    w0 = ebc.embedding_bags["t0"].weight.detach().clone()
+    # iterations 0 and 1: id 9 (a sharer of row 1) is hot, owners 1..3 are never seen
+    out = m(batch([9, 9, 9, 0]))
+    torch.testing.assert_close(out["f0"][0], 3 * w0[1] + w0[0])
+    m(batch([9, 9, 0, 0]))
+    # iteration 2 prunes before its lookup: id 9 takes the row of the least used owner (id 1 -> row 1, first among the unused)
+    m(batch([9, 0]))
+    assert itep.last_pruned_iter == 2
+    al = itep.address_lookup.tolist()
+    assert al[9] >= 0 and al[0] == 0 and sum(1 for v in al if v >= 0) == 4
+    lost = [i for i in (1, 2, 3) if al[i] < 0]
+    assert len(lost) == 1
+    # the handed-over row was re-initialised, the others were not
+    w1 = ebc.embedding_bags["t0"].weight.detach()
+    assert not torch.equal(w1[al[9]], w0[al[9]]) and torch.equal(w1[0], w0[0])
+    assert int(m._iter) == 3
+    # state round trip keeps the views live
+    m2 = ITEPEmbeddingBagCollection(EmbeddingBagCollection(tables=ebc.embedding_bag_configs()), GenericITEPModule({"t0": 12}, lookups=[ebc]))
+    m2.load_state_dict(m.state_dict())
+    assert m2._itep_module.address_lookup.tolist() == al
+    m.eval()
+    before = itep.row_util.clone()
+    m(batch([9, 5]))
+    assert torch.equal(before, itep.row_util)

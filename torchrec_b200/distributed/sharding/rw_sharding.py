@@ -75,6 +75,10 @@ class BaseRwEmbeddingSharding(BaseSharding[C, F, T, W]):
         return sum(g.num_features() for g in self._grouped_embedding_configs)
 
     def _get_feature_hash_sizes(self) -> List[int]:
+        # in-training pruning routes by the unpruned id space (set by the sharded pruning collection before the first batch)
+        override = getattr(self, "_table_hash_size_override", None)
+        if override:
+            return [override.get(t.name, t.num_embeddings) for g in self._grouped_embedding_configs for t in g.embedding_tables for _ in range(t.num_features())]
         return [h for g in self._grouped_embedding_configs for h in g.feature_hash_sizes()]
 
     def _get_feature_total_num_buckets(self) -> Optional[List[int]]:

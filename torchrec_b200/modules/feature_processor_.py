@@ -81,7 +81,9 @@ class PositionWeightedModuleCollection(FeatureProcessorsCollection):
         for k in keys:
             starts.append(acc)
             acc += self.max_feature_lengths[k]
-        seq = offsets_to_range_traceble(features.offsets(), features.values())
+        # after a row-wise input distribution the bags are split and the position of every id inside its original bag travels
+        # in the weights (torchrec/modules/feature_processor_.py:163 does the same)
+        seq = offsets_to_range_traceble(features.offsets(), features.values()) if features.weights_or_none() is None else features.weights().long()
         lpk = torch.tensor(features.length_per_key(), device=features.values().device)
         base = torch.repeat_interleave(torch.tensor(starts, device=features.values().device), lpk, output_size=features.values().numel())
         weights = torch.gather(cat_w, 0, (seq.long() + base))

@@ -143,8 +143,10 @@ class _TBEFunction(torch.autograd.Function):
     def backward(ctx, grad_out):
         indices, offsets, psw = ctx.saved_tensors
         m = ctx.module
+        # the gradient of the per-sample weights reads the rows as the forward saw them: before the fused update
+        psw_grad = m._psw_grad(grad_out, indices, offsets, ctx.B) if ctx.has_psw and ctx.needs_input_grad[4] else None
         dense_grad = m._backward_impl(grad_out, indices, offsets, psw if ctx.has_psw else None, ctx.B, ctx.plan)
-        return dense_grad, None, None, None, None, None, None
+        return dense_grad, None, None, None, psw_grad, None, None
 
 
 class TableBatchedEmbeddingBags(nn.Module):
@@ -407,6 +409,37 @@ class TableBatchedEmbeddingBags(nn.Module):
             grad_stride, B, self.max_D, True, _OPT_CODE[o.optimizer], o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay,
             self.step, o.max_gradient, grad_ptrs, B_local, grad_scale,
         )
+
+    def _psw_grad(self, grad_out: torch.Tensor, indices: torch.Tensor, offsets: torch.Tensor, B: int) -> torch.Tensor:
+        """``d loss / d per_sample_weights[i] = <grad of the bag of i, row of i>`` (learned position weights of feature
+        processors); composite, one gather per feature."""
+        w = self.weights.detach()
+        F = len(self.feature_table_map)
+        off = offsets.to(torch.int64)
+        idx = indices.to(torch.int64)
+        N = idx.numel()
+        out = torch.zeros(N, dtype=torch.float32, device=w.device)
+        if N == 0:
+            return out
+        bounds = off[:: max(B, 1)][: F + 1].tolist() if B > 0 else [0] * (F + 1)
+        lens = off[1:] - off[:-1]
+        bag = torch.repeat_interleave(torch.arange(F * B, device=w.device), lens, output_size=N)
+        g_out = grad_out.float()
+        for f in range(F):
+            s, e = bounds[f], bounds[f + 1]
+            if e == s:
+                continue
+            t = self.feature_table_map[f]
+            r, d = self.embedding_specs[t]
+            rows = w[self.weights_offsets[t]: self.weights_offsets[t + 1]].view(r, d).index_select(0, idx[s:e]).float()
+            if self.pooling_mode == PoolingMode.NONE:
+                g = g_out[s:e, :d]
+            else:
+                g = g_out[bag[s:e] - f * B, self.D_offsets[f]: self.D_offsets[f + 1]]
+                if self.pooling_mode == PoolingMode.MEAN:
+                    g = g / lens[bag[s:e]].clamp(min=1).unsqueeze(1).float()
+            out[s:e] = (rows * g).sum(dim=1)
+        return out
 
     def _backward_cpu(self, w, grad_out, indices, offsets, psw, B) -> Optional[torch.Tensor]:
         F = len(self.feature_table_map)
