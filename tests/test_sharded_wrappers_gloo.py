@@ -155,3 +155,125 @@ def _itep_run(rank, world_size, sharding):
 @pytest.mark.parametrize("sharding", ["tw", "rw"])
 def test_sharded_itep_ebc(sharding):
     run_multi_process(_itep_run, world_size=2, sharding=sharding)
+
+
+def _mc_models(device):
+    from torchrec_b200.modules.embedding_configs import EmbeddingBagConfig
+    from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
+    from torchrec_b200.modules.hash_mc_modules import HashZchManagedCollisionModule
+    from torchrec_b200.modules.mc_embedding_modules import ManagedCollisionEmbeddingBagCollection
+    from torchrec_b200.modules.mc_modules import LFU_EvictionPolicy, ManagedCollisionCollection, MCHManagedCollisionModule
+
+    cfgs = [EmbeddingBagConfig(name="t0", embedding_dim=8, num_embeddings=64, feature_names=["f0", "f1"]),
+            EmbeddingBagConfig(name="t1", embedding_dim=8, num_embeddings=32, feature_names=["f2"])]
+    ebc = EmbeddingBagCollection(tables=cfgs)
+    mcc = ManagedCollisionCollection({
+        "t0": HashZchManagedCollisionModule(zch_size=64, device=device, total_num_buckets=2, max_probe=32),
+        "t1": MCHManagedCollisionModule(zch_size=32, device=device, eviction_policy=LFU_EvictionPolicy(), eviction_interval=2, input_hash_size=4000),
+    }, cfgs)
+    return ManagedCollisionEmbeddingBagCollection(ebc, mcc, return_remapped_features=True)
+
+
+def _mc_run(rank, world_size):
+    from torchrec_b200.distributed import sharding_plan as sp
+    from torchrec_b200.distributed.mc_embeddingbag import ManagedCollisionEmbeddingBagCollectionSharder
+    from torchrec_b200.distributed.model_parallel import DistributedModelParallel
+    from torchrec_b200.distributed.sharding_plan import get_default_sharders
+    from torchrec_b200.distributed.types import ShardingEnv, ShardingPlan
+    from torchrec_b200.optim.apply_optimizer_in_backward import apply_optimizer_in_backward
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    with MultiProcessContext(rank, world_size, "gloo") as ctx:
+        torch.manual_seed(0)
+        dev = torch.device("cpu")
+        global_model = torch.nn.Module()
+        global_model.mc = _mc_models(dev)
+        local_model = copy.deepcopy(global_model)
+        apply_optimizer_in_backward(torch.optim.SGD, local_model.mc._embedding_module.parameters(), {"lr": 0.1})
+        sharder = ManagedCollisionEmbeddingBagCollectionSharder()
+        mplan = sp.construct_module_sharding_plan(local_model.mc._embedding_module, {"t0": sp.row_wise(), "t1": sp.row_wise()}, sharder=sharder._e_sharder,
+                                                  world_size=world_size, local_size=world_size, device_type="cpu")
+        dmp = DistributedModelParallel(local_model, env=ShardingEnv.from_process_group(ctx.pg), device=dev, plan=ShardingPlan({"mc": mplan}),
+                                       sharders=get_default_sharders() + [sharder])
+        sd = {k: v for k, v in global_model.state_dict().items() if "_embedding_module" in k}
+        dmp.load_state_dict(sd, strict=False)
+        B = 4
+        gen = torch.Generator().manual_seed(11)
+        per_rank = []
+        for r in range(world_size):
+            lens = torch.randint(1, 4, (3 * B,), generator=gen)
+            n = int(lens.sum())
+            vals = torch.randint(0, 10**9, (n,), generator=gen)
+            n2 = int(lens[2 * B:].sum())
+            vals[n - n2:] = torch.randint(0, 4000, (n2,), generator=gen)  # the sort-based module has a bounded input space
+            per_rank.append((vals, lens))
+        mk = lambda v, l: KeyedJaggedTensor.from_lengths_sync(keys=["f0", "f1", "f2"], values=v, lengths=l)
+        keys = ["f0", "f1", "f2"]
+        gv, gl = [], []
+        for k in range(3):
+            for v, l in per_rank:
+                kj = mk(v, l)[keys[k]]
+                gv.append(kj.values()); gl.append(kj.lengths())
+        global_kjt = mk(torch.cat(gv), torch.cat(gl))
+        g_out, g_remapped = global_model.mc(global_kjt)
+        l_out_aw, l_remapped = dmp.module.mc(mk(*per_rank[rank]))
+        l_out = l_out_aw.wait()
+        # the hash-based table gives the same rows sharded and unsharded -> identical pooled values
+        for f in ("f0", "f1"):
+            torch.testing.assert_close(l_out[f], g_out[f][rank * B:(rank + 1) * B], rtol=1e-5, atol=1e-6)
+        assert l_out["f2"].shape == (B, 8)
+        rk = l_remapped.wait()
+        lo0, lo1 = 32 * rank, 16 * rank
+        assert ((rk["f0"].values() >= lo0) & (rk["f0"].values() < lo0 + 32)).all()
+        assert ((rk["f2"].values() >= lo1) & (rk["f2"].values() < lo1 + 16)).all()
+        l_out.values().sum().backward()
+        # checkpoint: slot tables come out as shards of the global table and load back
+        full = dmp.state_dict()
+        key = "mc._managed_collision_collection._managed_collision_modules.t0._hash_zch_identities"
+        assert hasattr(full[key], "local_shards") and tuple(full[key].size()) == (64, 1)
+        g_ident = global_model.mc._managed_collision_collection._managed_collision_modules["t0"]._hash_zch_identities
+        assert torch.equal(full[key].local_shards()[0].tensor, g_ident[32 * rank:32 * rank + 32])
+        dmp.load_state_dict(full)
+        dmp.load_state_dict({k: v for k, v in global_model.state_dict().items()}, strict=False)
+
+
+def test_sharded_mc_ebc():
+    run_multi_process(_mc_run, world_size=2)
+
+
+def _fused_run(rank, world_size):
+    from torchrec_b200.distributed import sharding_plan as sp
+    from torchrec_b200.distributed.model_parallel import DistributedModelParallel
+    from torchrec_b200.distributed.types import ShardingEnv, ShardingPlan
+    from torchrec_b200.modules.embedding_configs import EmbeddingBagConfig
+    from torchrec_b200.modules.fused_embedding_modules import FusedEmbeddingBagCollection
+
+    with MultiProcessContext(rank, world_size, "gloo") as ctx:
+        torch.manual_seed(0)
+        cfgs = [EmbeddingBagConfig(name=f"t{i}", num_embeddings=r, embedding_dim=d, feature_names=list(f)) for i, (r, d, f) in enumerate(T.TABLES)]
+        g = torch.nn.Module()
+        g.ebc = FusedEmbeddingBagCollection(cfgs, torch.optim.SGD, {"lr": 0.1})
+        l = torch.nn.Module()
+        l.ebc = FusedEmbeddingBagCollection(copy.deepcopy(cfgs), torch.optim.SGD, {"lr": 0.1})
+        l.ebc.load_state_dict(g.ebc.state_dict())
+        sharders = sp.get_default_sharders()
+        fs = next(s for s in sharders if s.module_type is FusedEmbeddingBagCollection)
+        gens = {c.name: [sp.table_wise(rank=0), sp.row_wise(), sp.column_wise(ranks=[1, 0]), sp.table_wise(rank=1)][i] for i, c in enumerate(cfgs)}
+        mplan = sp.construct_module_sharding_plan(l.ebc, gens, sharder=fs, world_size=world_size, local_size=world_size, device_type="cpu")
+        dmp = DistributedModelParallel(l, env=ShardingEnv.from_process_group(ctx.pg), device=torch.device("cpu"), plan=ShardingPlan({"ebc": mplan}), sharders=sharders)
+        B = 6
+        kjts = [T._make_kjt(B, 100 + r) for r in range(world_size)]
+        for step in range(2):
+            outs = []
+            for r in range(world_size):
+                o = g.ebc(kjts[r])
+                outs.append(o)
+            # the single-device module sees both batches; gradients of a mean over the global batch
+            (sum(o.values().sum() for o in outs) / world_size).backward()
+            lo = dmp.module.ebc(kjts[rank]).wait()
+            torch.testing.assert_close(lo.values(), outs[rank].values().detach(), rtol=1e-5, atol=1e-6)
+            lo.values().sum().backward()
+
+
+def test_sharded_fused_ebc_matches_single_device():
+    run_multi_process(_fused_run, world_size=2)

@@ -1,0 +1,142 @@
+"""Sharded embedding collections behind managed collision (pooled and sequence form share this base).
+Counterpart of ``torchrec/distributed/mc_embedding_modules.py:62``, ``mc_embeddingbag.py:52``, ``mc_embedding.py:67``."""
+from __future__ import annotations
+
+from typing import Any, Dict, Iterator, List, Optional, Tuple, Type
+
+import torch
+from torch import nn
+from torch.nn.parallel import DistributedDataParallel
+
+from torchrec_b200.distributed.embedding import EmbeddingCollectionSharder, ShardedEmbeddingCollection
+from torchrec_b200.distributed.embedding_types import BaseEmbeddingSharder, KJTList, ShardedEmbeddingModule
+from torchrec_b200.distributed.embeddingbag import EmbeddingBagCollectionSharder, ShardedEmbeddingBagCollection
+from torchrec_b200.distributed.mc_modules import ShardedManagedCollisionCollection
+from torchrec_b200.distributed.types import Awaitable, LazyAwaitable, NoWait, ParameterSharding, QuantizedCommCodecs, ShardingEnv, ShardingType
+from torchrec_b200.modules.mc_embedding_modules import ManagedCollisionEmbeddingBagCollection, ManagedCollisionEmbeddingCollection
+from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+
+class BaseShardedManagedCollisionEmbeddingCollection(ShardedEmbeddingModule):
+    def __init__(self, module: nn.Module, table_name_to_parameter_sharding: Dict[str, ParameterSharding], e_sharder: BaseEmbeddingSharder, env: ShardingEnv,
+                 device: torch.device, module_fqn: Optional[str] = None) -> None:
+        super().__init__()
+        self._device, self._env = device, env
+        self._return_remapped_features = module._return_remapped_features
+        self._embedding_module = e_sharder.shard(module._embedding_module, table_name_to_parameter_sharding, env=env, device=device,
+                                                 module_fqn=(module_fqn + "._embedding_module") if module_fqn else None)
+        self._managed_collision_collection = ShardedManagedCollisionCollection(module._managed_collision_collection, table_name_to_parameter_sharding, env, device)
+        sizes = self._managed_collision_collection.table_input_sizes()
+        buckets = self._managed_collision_collection.table_total_num_buckets()
+        for sharding in self._embedding_module._embedding_shardings:
+            sharding._table_hash_size_override = sizes      # row blocks follow the collision module's input id space
+            sharding._keep_original_indices = True         # the owning rank remaps the raw id
+            if buckets is not None:
+                sharding._table_total_num_buckets_override = buckets
+        self._lookups = self._embedding_module._lookups
+        self._init_bounds = {c.name: (c.get_weight_init_min(), c.get_weight_init_max()) for c in self._managed_collision_collection._embedding_configs}
+
+    def input_dist(self, ctx, features: KeyedJaggedTensor) -> Awaitable[Awaitable[KJTList]]:
+        return self._embedding_module.input_dist(ctx, self._managed_collision_collection.preprocess(features))
+
+    @torch.no_grad()
+    def _reset_rows(self, evictions: Dict[str, Optional[torch.Tensor]]) -> None:
+        for table, rows in evictions.items():
+            if rows is None or rows.numel() == 0:
+                continue
+            lo, hi = self._init_bounds[table]
+            for _, w in self._embedding_module._model_parallel_name_to_local_shards.get(table, []):
+                r = rows.to(w.device)
+                w[r] = torch.empty(r.numel(), w.shape[1], device=w.device, dtype=torch.float32).uniform_(lo, hi).to(w.dtype)
+
+    def _remap_list(self, ctx, dist_input: KJTList) -> KJTList:
+        local, glob = [], []
+        for features in dist_input:
+            l, g = self._managed_collision_collection.remap(features)
+            local.append(l)
+            glob.append(g)
+        self._reset_rows(self._managed_collision_collection.evict())
+        ctx.remapped_kjt = glob
+        return KJTList(local)
+
+    def compute(self, ctx, dist_input: KJTList):
+        return self._embedding_module.compute(ctx, self._remap_list(ctx, dist_input))
+
+    def output_dist(self, ctx, output):
+        return self._finish(ctx, self._embedding_module.output_dist(ctx, output))
+
+    def compute_and_output_dist(self, ctx, input: KJTList):
+        return self._finish(ctx, self._embedding_module.compute_and_output_dist(ctx, self._remap_list(ctx, input)))
+
+    def _finish(self, ctx, lazy):
+        if not self._return_remapped_features:
+            return lazy, None
+        # the remapped ids stay on the rank that owns their rows (global row numbers, one KJT per sharding group)
+        return lazy, NoWait(ctx.remapped_kjt[0] if len(ctx.remapped_kjt) == 1 else ctx.remapped_kjt)
+
+    def create_context(self):
+        ctx = self._embedding_module.create_context()
+        ctx.remapped_kjt = None
+        return ctx
+
+    def sharded_parameter_names(self, prefix: str = "") -> Iterator[str]:
+        yield from self._embedding_module.sharded_parameter_names((prefix + "." if prefix else "") + "_embedding_module")
+
+    def evict(self) -> Dict[str, Optional[torch.Tensor]]:
+        return self._managed_collision_collection.evict()
+
+    def open_slots(self) -> Dict[str, torch.Tensor]:
+        return self._managed_collision_collection.open_slots()
+
+
+class ShardedManagedCollisionEmbeddingBagCollection(BaseShardedManagedCollisionEmbeddingCollection):
+    @property
+    def unsharded_module_type(self) -> Type[ManagedCollisionEmbeddingBagCollection]:
+        return ManagedCollisionEmbeddingBagCollection
+
+
+class ShardedManagedCollisionEmbeddingCollection(BaseShardedManagedCollisionEmbeddingCollection):
+    @property
+    def unsharded_module_type(self) -> Type[ManagedCollisionEmbeddingCollection]:
+        return ManagedCollisionEmbeddingCollection
+
+
+class _BaseMCSharder(BaseEmbeddingSharder):
+    _inner_sharder_type: Type[BaseEmbeddingSharder]
+    _sharded_type: Type[BaseShardedManagedCollisionEmbeddingCollection]
+
+    def __init__(self, e_sharder: Optional[BaseEmbeddingSharder] = None, qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None) -> None:
+        super().__init__(qcomm_codecs_registry=qcomm_codecs_registry)
+        self._e_sharder = e_sharder or self._inner_sharder_type(qcomm_codecs_registry=self.qcomm_codecs_registry)
+
+    def shard(self, module, params: Dict[str, ParameterSharding], env: ShardingEnv, device: Optional[torch.device] = None, module_fqn: Optional[str] = None):
+        device = device if device is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        return self._sharded_type(module, params, self._e_sharder, env, device, module_fqn)
+
+    @property
+    def fused_params(self) -> Optional[Dict[str, Any]]:
+        return self._e_sharder.fused_params
+
+    def shardable_parameters(self, module) -> Dict[str, nn.Parameter]:
+        return self._e_sharder.shardable_parameters(module._embedding_module)
+
+    def sharding_types(self, compute_device_type: str) -> List[str]:
+        return [ShardingType.ROW_WISE.value]
+
+
+class ManagedCollisionEmbeddingBagCollectionSharder(_BaseMCSharder):
+    _inner_sharder_type = EmbeddingBagCollectionSharder
+    _sharded_type = ShardedManagedCollisionEmbeddingBagCollection
+
+    @property
+    def module_type(self) -> Type[ManagedCollisionEmbeddingBagCollection]:
+        return ManagedCollisionEmbeddingBagCollection
+
+
+class ManagedCollisionEmbeddingCollectionSharder(_BaseMCSharder):
+    _inner_sharder_type = EmbeddingCollectionSharder
+    _sharded_type = ShardedManagedCollisionEmbeddingCollection
+
+    @property
+    def module_type(self) -> Type[ManagedCollisionEmbeddingCollection]:
+        return ManagedCollisionEmbeddingCollection

@@ -80,7 +80,8 @@ class DefaultDataParallelWrapper(DataParallelWrapper):
         pg = env.process_group
         if pg is None:
             raise RuntimeError("Can only init DDP for ProcessGroup-based ShardingEnv")
-        all_parameter_names = set(dict(dmp.named_parameters()).keys())
+        # parameters that take no gradient (slot tables of collision modules) need no all-reduce either
+        all_parameter_names = {n for n, p in dmp.named_parameters() if p.requires_grad}
         if len(all_parameter_names - ddp_ignore_param_names) == 0:
             return
         DistributedDataParallel._set_params_and_buffers_to_ignore_for_model(module=dmp._dmp_wrapped_module, params_and_buffers_to_ignore=ddp_ignore_param_names)

@@ -44,6 +44,7 @@ class RwSequenceEmbeddingSharding(BaseRwEmbeddingSharding[SequenceShardingContex
             pg=self._pg, num_features=self._get_num_features(), feature_hash_sizes=self._get_feature_hash_sizes(),
             feature_total_num_buckets=self._get_feature_total_num_buckets(), device=device if device is not None else self._device,
             is_sequence=True, has_feature_processor=self._has_feature_processor, need_pos=False,
+            keep_original_indices=getattr(self, "_keep_original_indices", False),
         )
 
     def create_lookup(self, device: Optional[torch.device] = None, fused_params: Optional[Dict[str, Any]] = None, feature_processor=None) -> BaseEmbeddingLookup:

@@ -82,6 +82,9 @@ class BaseRwEmbeddingSharding(BaseSharding[C, F, T, W]):
         return [h for g in self._grouped_embedding_configs for h in g.feature_hash_sizes()]
 
     def _get_feature_total_num_buckets(self) -> Optional[List[int]]:
+        override = getattr(self, "_table_total_num_buckets_override", None)
+        if override:
+            return [override[t.name] for g in self._grouped_embedding_configs for t in g.embedding_tables for _ in range(t.num_features())]
         out: List[int] = []
         for g in self._grouped_embedding_configs:
             for t in g.embedding_tables:
@@ -160,6 +163,7 @@ class RwPooledEmbeddingSharding(BaseRwEmbeddingSharding[EmbeddingShardingContext
             pg=self._pg, num_features=self._get_num_features(), feature_hash_sizes=self._get_feature_hash_sizes(),
             feature_total_num_buckets=self._get_feature_total_num_buckets(), device=device if device is not None else self._device,
             is_sequence=False, has_feature_processor=self._has_feature_processor, need_pos=self._need_pos,
+            keep_original_indices=getattr(self, "_keep_original_indices", False),
         )
 
     def create_lookup(self, device: Optional[torch.device] = None, fused_params: Optional[Dict[str, Any]] = None, feature_processor=None) -> BaseEmbeddingLookup:

@@ -38,11 +38,13 @@ def get_default_sharders() -> List[ModuleSharder[nn.Module]]:
         ("torchrec_b200.distributed.embedding", "EmbeddingCollectionSharder"),
         ("torchrec_b200.distributed.fp_embeddingbag", "FeatureProcessedEmbeddingBagCollectionSharder"),
         ("torchrec_b200.distributed.fused_embeddingbag", "FusedEmbeddingBagCollectionSharder"),
+        ("torchrec_b200.distributed.fused_embeddingbag", "FusedEmbeddingCollectionSharder"),
         ("torchrec_b200.distributed.quant_embeddingbag", "QuantEmbeddingBagCollectionSharder"),
         ("torchrec_b200.distributed.quant_embedding", "QuantEmbeddingCollectionSharder"),
         ("torchrec_b200.distributed.mc_embeddingbag", "ManagedCollisionEmbeddingBagCollectionSharder"),
         ("torchrec_b200.distributed.mc_embedding", "ManagedCollisionEmbeddingCollectionSharder"),
         ("torchrec_b200.distributed.itep_embeddingbag", "ITEPEmbeddingBagCollectionSharder"),
+        ("torchrec_b200.distributed.itep_embeddingbag", "ITEPEmbeddingCollectionSharder"),
     ):
         try:
             mod = __import__(modname, fromlist=[clsname])
