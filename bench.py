@@ -262,7 +262,8 @@ def main() -> None:
     try:
         from torch.profiler import ProfilerActivity, profile
 
-        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        acts = [ProfilerActivity.CUDA] + ([ProfilerActivity.CPU] if args.kernel_table else [])
+        with profile(activities=acts, record_shapes=bool(args.kernel_table)) as prof:
             step(dev_batches[0])
             torch.cuda.synchronize()
         own = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and ("trb::" in e.name or "trb_" in e.name)]
@@ -278,6 +279,10 @@ def main() -> None:
             print(f"kernel table (one step, {tot / 1e3:.3f} ms of device time):", file=sys.stderr)
             for name, (t, n) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:45]:
                 print(f"  {t / 1e3:8.3f} ms  x{n:<3d} {name}", file=sys.stderr)
+            print("operators by own device time (with input shapes):", file=sys.stderr)
+            rows = sorted(prof.key_averages(group_by_input_shape=True), key=lambda r: -getattr(r, "self_device_time_total", 0.0))
+            for r in rows[:30]:
+                print(f"  {getattr(r, 'self_device_time_total', 0.0) / 1e3:8.3f} ms  x{r.count:<3d} {r.key[:50]:50s} {str(r.input_shapes)[:150]}", file=sys.stderr)
     except Exception:
         launches = None
 

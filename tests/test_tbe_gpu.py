@@ -177,3 +177,53 @@ def test_out_of_range_id_is_reported():
         gpu(idx, off)
     with pytest.raises(IndexError):
         gpu.check_error()
+
+
+@pytest.mark.parametrize("gdtype", [torch.float32, torch.bfloat16])
+def test_backward_reads_a_column_slice_without_copy(gdtype):
+    """The gradient of a concat arrives as a column slice of a wider tensor (row stride > width)."""
+    specs = [(2000, 128), (500, 128)]
+    ftm = [0, 1, 0]
+    opt = OptimizerArgs(EmbOptimType.EXACT_ROWWISE_ADAGRAD, 0.05)
+    cpu, gpu = _pair(specs, ftm, PoolingMode.SUM, opt, out_dtype=gdtype)
+    idx, off, _ = _make_inputs(specs, ftm, 300, 12, False, 31, zipf=True)
+    ref = cpu(idx, off)
+    out = gpu(idx.cuda(), off.cuda())
+    wide = torch.randn(300, 64 + 384, generator=torch.Generator().manual_seed(3)).to(gdtype)
+    g = wide[:, 64:]
+    assert not g.is_contiguous()
+    ref.backward(g.contiguous())
+    out.backward(wide.cuda()[:, 64:])
+    torch.testing.assert_close(gpu.weights.detach().cpu(), cpu.weights.detach(), rtol=2e-3 if gdtype == torch.bfloat16 else 2e-4, atol=2e-5)
+    gpu.check_error()
+
+
+@pytest.mark.parametrize("pooling", [PoolingMode.SUM, PoolingMode.MEAN])
+def test_per_sample_weight_gradient(pooling):
+    specs = [(400, 64), (300, 32)]
+    ftm = [0, 1, 1]
+    opt = OptimizerArgs(EmbOptimType.EXACT_SGD, 0.1)
+    cpu, gpu = _pair(specs, ftm, pooling, opt)
+    idx, off, psw = _make_inputs(specs, ftm, 50, 6, True, 41)
+    w0 = [t.clone() for t in cpu.split_embedding_weights()]
+    pc = psw.clone().requires_grad_(True)
+    pg = psw.cuda().requires_grad_(True)
+    ref = cpu(idx, off, pc)
+    out = gpu(idx.cuda(), off.cuda(), pg)
+    g = torch.randn(ref.shape, generator=torch.Generator().manual_seed(5))
+    ref.backward(g)
+    out.backward(g.cuda())
+    torch.testing.assert_close(pg.grad.cpu(), pc.grad, rtol=1e-4, atol=1e-5)
+    # oracle: autograd through plain embedding bags on the weights as they were before the update
+    po = psw.clone().requires_grad_(True)
+    cols, outs = 0, []
+    B = 50
+    for f, t in enumerate(ftm):
+        o = off[f * B:(f + 1) * B + 1]
+        s, e = int(o[0]), int(o[-1])
+        r = torch.nn.functional.embedding_bag(idx[s:e], w0[t], o[:-1] - s, mode="sum", per_sample_weights=po[s:e])
+        if pooling == PoolingMode.MEAN:
+            r = r / (o[1:] - o[:-1]).clamp(min=1).unsqueeze(1).float()
+        outs.append(r)
+    torch.cat(outs, 1).backward(g)
+    torch.testing.assert_close(pc.grad, po.grad, rtol=1e-4, atol=1e-5)

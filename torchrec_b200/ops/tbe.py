@@ -350,7 +350,11 @@ class TableBatchedEmbeddingBags(nn.Module):
             _ext.require_cuda_ext("tbe_backward")
             if plan is None:
                 plan = self.build_plan(indices, offsets, psw, B)
-            grad_out = grad_out.contiguous()
+            # the kernel reads gradient rows through a row stride: a column slice of a wider tensor (the gradient of a concat)
+            # needs no copy as long as rows are dense and 16-byte aligned
+            esz = grad_out.element_size()
+            if grad_out.dim() != 2 or grad_out.stride(1) != 1 or grad_out.data_ptr() % 16 != 0 or (grad_out.stride(0) * esz) % 16 != 0:
+                grad_out = grad_out.contiguous()
             o = self.optimizer_args
             dense_grad = None
             if not self.fused:
