@@ -257,8 +257,14 @@ def _jt_unflatten(values, context) -> JaggedTensor:
     return JaggedTensor(*values)
 
 
+def _jt_flatten_with_keys(t: JaggedTensor):
+    values, context = _jt_flatten(t)
+    return [(pytree.GetAttrKey(k), v) for k, v in zip(JaggedTensor._fields, values)], context
+
+
 pytree.register_pytree_node(
-    JaggedTensor, _jt_flatten, _jt_unflatten, serialized_type_name="torchrec_b200.sparse.jagged_tensor.JaggedTensor"
+    JaggedTensor, _jt_flatten, _jt_unflatten, flatten_with_keys_fn=_jt_flatten_with_keys,
+    serialized_type_name="torchrec_b200.sparse.jagged_tensor.JaggedTensor"
 )
 
 
@@ -894,8 +900,13 @@ def _kjt_unflatten(values, context) -> KeyedJaggedTensor:
     return KeyedJaggedTensor(keys, *values, stride_per_key_per_rank=spkpr)
 
 
+def _kjt_flatten_with_keys(t: KeyedJaggedTensor):
+    values, context = _kjt_flatten(t)
+    return [(pytree.GetAttrKey(k), v) for k, v in zip(KeyedJaggedTensor._fields, values)], context
+
+
 pytree.register_pytree_node(
-    KeyedJaggedTensor, _kjt_flatten, _kjt_unflatten,
+    KeyedJaggedTensor, _kjt_flatten, _kjt_unflatten, flatten_with_keys_fn=_kjt_flatten_with_keys,
     serialized_type_name="torchrec_b200.sparse.jagged_tensor.KeyedJaggedTensor",
 )
 
@@ -1043,8 +1054,14 @@ def _kt_unflatten(values, context) -> KeyedTensor:
     return KeyedTensor(keys, lpk, values[0], key_dim)
 
 
+def _kt_flatten_with_keys(kt: KeyedTensor):
+    values, context = _kt_flatten(kt)
+    return [(pytree.GetAttrKey("_values"), values[0])], context
+
+
 pytree.register_pytree_node(
-    KeyedTensor, _kt_flatten, _kt_unflatten, serialized_type_name="torchrec_b200.sparse.jagged_tensor.KeyedTensor"
+    KeyedTensor, _kt_flatten, _kt_unflatten, flatten_with_keys_fn=_kt_flatten_with_keys,
+    serialized_type_name="torchrec_b200.sparse.jagged_tensor.KeyedTensor"
 )
 
 
