@@ -1,0 +1,151 @@
+"""Planner: search space, constraints, memory feasibility, balance, determinism (cf. ``torchrec/distributed/planner/tests``)."""
+import pytest
+import torch
+from torch import nn
+
+from torchrec_b200.distributed.embedding_types import EmbeddingComputeKernel
+from torchrec_b200.distributed.embeddingbag import EmbeddingBagCollectionSharder
+from torchrec_b200.distributed.planner import EmbeddingShardingPlanner, ParameterConstraints, Topology
+from torchrec_b200.distributed.planner.enumerators import EmbeddingEnumerator
+from torchrec_b200.distributed.planner.partitioners import GreedyPerfPartitioner, MemoryBalancedPartitioner
+from torchrec_b200.distributed.planner.proposers import DynamicProgrammingProposer, GreedyProposer, GridSearchProposer, UniformProposer, proposers_to_proposals_list
+from torchrec_b200.distributed.planner.storage_reservations import FixedPercentageStorageReservation, HeuristicalStorageReservation
+from torchrec_b200.distributed.planner.types import PlannerError, PlannerErrorType
+from torchrec_b200.distributed.types import ShardingType
+from torchrec_b200.modules.embedding_configs import EmbeddingBagConfig
+from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
+
+GB = 1024 ** 3
+
+
+class _Model(nn.Module):
+    def __init__(self, tables):
+        super().__init__()
+        self.sparse = EmbeddingBagCollection(tables=tables, device=torch.device("meta"))
+        self.dense = nn.Linear(8, 8)
+
+
+def _tables(n=4, rows=1000, dim=64):
+    return [EmbeddingBagConfig(name=f"t{i}", embedding_dim=dim, num_embeddings=rows * (i + 1), feature_names=[f"f{i}"]) for i in range(n)]
+
+
+def _topo(world=2, hbm=8 * GB, local=None):
+    return Topology(world_size=world, compute_device="cuda", hbm_cap=hbm, local_world_size=local)
+
+
+def test_enumerator_covers_sharding_types_and_respects_constraints():
+    model = _Model(_tables(2))
+    topo = _topo(4, local=2)
+    opts = EmbeddingEnumerator(topology=topo, batch_size=128).enumerate(model, [EmbeddingBagCollectionSharder()])
+    kinds = {(o.name, o.sharding_type) for o in opts}
+    for st in (ShardingType.TABLE_WISE, ShardingType.ROW_WISE, ShardingType.COLUMN_WISE, ShardingType.DATA_PARALLEL, ShardingType.TABLE_ROW_WISE):
+        assert ("t0", st.value) in kinds, st
+    for o in opts:
+        assert o.total_storage.hbm > 0 and o.total_perf > 0, (o.name, o.sharding_type)
+        rows = sum(s.size[0] for s in o.shards) if o.sharding_type in (ShardingType.ROW_WISE.value, ShardingType.TABLE_ROW_WISE.value) else None
+        if rows is not None:
+            assert rows == o.tensor.shape[0]
+        if o.sharding_type == ShardingType.COLUMN_WISE.value:
+            assert sum(s.size[1] for s in o.shards) == o.tensor.shape[1]
+    cons = {"t0": ParameterConstraints(sharding_types=[ShardingType.ROW_WISE.value], compute_kernels=[EmbeddingComputeKernel.FUSED.value]),
+            "t1": ParameterConstraints(sharding_types=[ShardingType.COLUMN_WISE.value], min_partition=32)}
+    opts = EmbeddingEnumerator(topology=topo, batch_size=128, constraints=cons).enumerate(model, [EmbeddingBagCollectionSharder()])
+    assert {o.sharding_type for o in opts if o.name == "t0"} == {ShardingType.ROW_WISE.value}
+    assert {o.compute_kernel for o in opts if o.name == "t0"} == {EmbeddingComputeKernel.FUSED.value}
+    t1 = [o for o in opts if o.name == "t1"]
+    assert t1 and all(o.sharding_type == ShardingType.COLUMN_WISE.value and all(s.size[1] >= 32 for s in o.shards) for o in t1)
+
+
+def test_plan_places_every_shard_within_memory_and_is_deterministic():
+    model = _Model(_tables(6, rows=200_000, dim=128))
+    topo = _topo(4)
+    plans = []
+    for _ in range(2):
+        planner = EmbeddingShardingPlanner(topology=_topo(4), batch_size=512, debug=False)
+        plans.append(planner.plan(model, [EmbeddingBagCollectionSharder()]))
+    a, b = (p.plan["sparse"] for p in plans)
+    assert set(a.keys()) == {f"t{i}" for i in range(6)}
+    for name in a:
+        assert a[name].sharding_type == b[name].sharding_type and a[name].ranks == b[name].ranks
+        spec = a[name].sharding_spec
+        if spec is not None:
+            rows, dim = 200_000 * (int(name[1:]) + 1), 128
+            assert sum(s.shard_sizes[0] * s.shard_sizes[1] for s in spec.shards) == rows * dim
+    used = [0] * 4
+    for name, ps in a.items():
+        if ps.sharding_spec is None:
+            continue
+        for s in ps.sharding_spec.shards:
+            r = int(str(s.placement).split("/")[0].split(":")[1])
+            used[r] += s.shard_sizes[0] * s.shard_sizes[1] * 4
+    assert max(used) < 8 * GB and min(used) > 0
+
+
+def test_plan_fails_with_a_storage_error_when_nothing_fits():
+    model = _Model(_tables(3, rows=4_000_000, dim=128))  # ~2 GB, 4 GB, 6 GB tables (+ optimizer/IO) on 2 x 1 GB
+    hbm_only = {f"t{i}": ParameterConstraints(compute_kernels=[EmbeddingComputeKernel.FUSED.value]) for i in range(3)}  # no spill-over to host memory
+    planner = EmbeddingShardingPlanner(topology=_topo(2, hbm=1 * GB), batch_size=512, debug=False, constraints=hbm_only)
+    with pytest.raises(PlannerError) as e:
+        planner.plan(model, [EmbeddingBagCollectionSharder()])
+    assert e.value.error_type in (PlannerErrorType.INSUFFICIENT_STORAGE, PlannerErrorType.PARTITION)
+
+
+def test_big_table_is_split_when_it_does_not_fit_on_one_device():
+    tables = [EmbeddingBagConfig(name="big", embedding_dim=128, num_embeddings=6_000_000, feature_names=["f"])]  # 3 GB of weights
+    planner = EmbeddingShardingPlanner(topology=_topo(4, hbm=2 * GB), batch_size=512, debug=False, storage_reservation=FixedPercentageStorageReservation(0.1),
+                                       constraints={"big": ParameterConstraints(compute_kernels=[EmbeddingComputeKernel.FUSED.value])})
+    ps = planner.plan(_Model(tables), [EmbeddingBagCollectionSharder()]).plan["sparse"]["big"]
+    assert ps.sharding_type in (ShardingType.ROW_WISE.value, ShardingType.COLUMN_WISE.value, ShardingType.TABLE_ROW_WISE.value, ShardingType.GRID_SHARD.value)
+    assert len(ps.ranks) >= 2
+
+
+def test_proposers_and_partitioners():
+    model = _Model(_tables(3))
+    topo = _topo(2)
+    space = EmbeddingEnumerator(topology=topo, batch_size=128).enumerate(model, [EmbeddingBagCollectionSharder()])
+    for proposer in (GreedyProposer(), UniformProposer(), GridSearchProposer(), DynamicProgrammingProposer()):
+        proposer.load(space)
+        first = proposer.propose()
+        assert first is not None and sorted(o.name for o in first) == ["t0", "t1", "t2"], type(proposer).__name__
+        proposer.feedback(partitionable=True, plan=first, perf_rating=1.0, storage_constraint=topo)
+    uni = UniformProposer()
+    uni.load(space)
+    seen = set()
+    while (p := uni.propose()) is not None:
+        kinds = {o.sharding_type for o in p}
+        assert len(kinds) == 1
+        seen |= kinds
+        uni.feedback(True)
+    assert ShardingType.TABLE_WISE.value in seen and ShardingType.ROW_WISE.value in seen
+    assert len(proposers_to_proposals_list([GreedyProposer(), UniformProposer()], space)) >= 2
+    greedy = GreedyProposer()
+    greedy.load(space)
+    proposal = greedy.propose()
+    for part in (GreedyPerfPartitioner(), MemoryBalancedPartitioner()):
+        placed = part.partition([o for o in __import__("copy").deepcopy(proposal)], _topo(2))
+        for o in placed:
+            assert all(s.rank is not None and 0 <= s.rank < 2 for s in o.shards)
+    with pytest.raises(PlannerError):
+        GreedyPerfPartitioner().partition(__import__("copy").deepcopy(proposal), _topo(2, hbm=1024))
+
+
+def test_storage_reservations_shrink_the_topology():
+    model = _Model(_tables(2))
+    topo = _topo(2, hbm=10 * GB)
+    fixed = FixedPercentageStorageReservation(0.2).reserve(topo, 512, model, [EmbeddingBagCollectionSharder()])
+    assert fixed.devices[0].storage.hbm == int(10 * GB * 0.8)
+    heur = HeuristicalStorageReservation(percentage=0.15).reserve(_topo(2, hbm=10 * GB), 512, model, [EmbeddingBagCollectionSharder()])
+    assert heur.devices[0].storage.hbm < int(10 * GB * 0.85)
+    assert topo.devices[0].storage.hbm == 10 * GB  # the input topology is untouched
+
+
+def test_plan_report_lists_every_table():
+    from torchrec_b200.distributed.planner.stats import EmbeddingStats
+
+    stats = EmbeddingStats()
+    planner = EmbeddingShardingPlanner(topology=_topo(2), batch_size=256, debug=True, stats=stats)
+    planner.plan(_Model(_tables(3)), [EmbeddingBagCollectionSharder()])
+    report = stats.report()
+    for t in ("t0", "t1", "t2"):
+        assert t in report
+    assert "Rank" in report or "rank" in report

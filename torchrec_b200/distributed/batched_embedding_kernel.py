@@ -142,34 +142,24 @@ class EmbeddingFusedOptimizer(FusedOptimizer):
             return local[0] if len(local) == 1 else torch.cat([x.reshape(x.shape[0], -1) for x in local], dim=-1)
         local_shards: List[Shard] = []
         if rowwise:
-            # one value per row: shard along rows exactly like the table; column shards of the same rows hold replicas,
-            # of which the first (column offset 0 if present on this rank, else the lowest) represents the row block.
-            seen_rows = set()
-
-            def row_key(sm: ShardMetadata) -> Tuple[Any, ...]:
-                # empty shards (more ranks than rows) all start at the same row: keep one entry per placement
-                if sm.shard_sizes[0] == 0:
-                    return (sm.shard_offsets[0], 0, str(sm.placement))
-                return (sm.shard_offsets[0], sm.shard_sizes[0], "")
-
-            row_blocks: Dict[Tuple[Any, ...], ShardMetadata] = {}
-            for sm in gm.shards_metadata:
-                rk = row_key(sm)
-                if rk not in row_blocks or sm.shard_offsets[1] < row_blocks[rk].shard_offsets[1]:
-                    row_blocks[rk] = sm
-            metas = [
-                ShardMetadata(shard_offsets=[rk[0]], shard_sizes=[rk[1]], placement=copy.deepcopy(sm.placement))
-                for rk, sm in sorted(row_blocks.items())
-            ]
+            # one value per row of every shard.  Column shards of the same rows keep independent values (each is computed from
+            # its own columns), so the state tensor stacks the shards along dim 0 in (column offset, row offset) order:
+            # row-wise tables give [rows], column-wise ones [rows * column shards]
+            # (same layout as torchrec/distributed/batched_embedding_kernel.py:1132-1190).
+            ordered = sorted(gm.shards_metadata, key=lambda sm: (sm.shard_offsets[1], sm.shard_offsets[0], str(sm.placement)))
+            offset_of: Dict[Tuple[Any, ...], int] = {}
+            metas = []
+            rolling = 0
+            for sm in ordered:
+                k = (sm.shard_offsets[0], sm.shard_offsets[1], sm.shard_sizes[0], sm.shard_sizes[1], str(sm.placement))
+                offset_of[k] = rolling
+                metas.append(ShardMetadata(shard_offsets=[rolling], shard_sizes=[sm.shard_sizes[0]], placement=copy.deepcopy(sm.placement)))
+                rolling += sm.shard_sizes[0]
             for t, x in zip(tables, local):
                 lm = t.local_metadata
-                rk = row_key(lm)
-                owner = row_blocks[rk]
-                if rk in seen_rows or list(owner.shard_offsets) != list(lm.shard_offsets):
-                    continue
-                seen_rows.add(rk)
-                local_shards.append(Shard(x, ShardMetadata(shard_offsets=[rk[0]], shard_sizes=[rk[1]], placement=copy.deepcopy(lm.placement))))
-            size = torch.Size([gm.size[0]])
+                k = (lm.shard_offsets[0], lm.shard_offsets[1], lm.shard_sizes[0], lm.shard_sizes[1], str(lm.placement))
+                local_shards.append(Shard(x, ShardMetadata(shard_offsets=[offset_of[k]], shard_sizes=[lm.shard_sizes[0]], placement=copy.deepcopy(lm.placement))))
+            size = torch.Size([rolling])
         else:
             metas = [copy.deepcopy(sm) for sm in gm.shards_metadata]
             for t, x in zip(tables, local):
