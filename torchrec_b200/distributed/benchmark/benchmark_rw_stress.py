@@ -1,0 +1,137 @@
+"""Row-wise sharding stress: an ``EmbeddingBagCollection`` of 64 tables x 10M rows x dim 256 in fp16 with a fixed pooling factor
+of 20 (sum pooling, uniform ids), batch 16384 per rank; one step is forward + backward with the fused row-wise Adagrad.  Besides
+the step time the three exchanges of a row-wise step are timed on their own with the step's shapes and reported as achieved GB/s
+per rank and as a fraction of the NVLink peer-copy bandwidth: the input-dist all-to-all (ids and lengths after bucketization), the
+pooled reduce-scatter and the gradient all-gather.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 4 --master-addr 127.0.0.1 --master-port 29512 \\
+        -m torchrec_b200.distributed.benchmark.benchmark_rw_stress --steps 10 --warmup 3
+"""
+from __future__ import annotations
+
+import argparse
+import datetime
+import json
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU
+
+
+def _time(fn, iters: int, device: torch.device) -> float:
+    for _ in range(3):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device=device)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms)
+
+
+def main() -> None:
+    p = argparse.ArgumentParser()
+    p.add_argument("--steps", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--tables", type=int, default=64)
+    p.add_argument("--rows", type=int, default=10_000_000)
+    p.add_argument("--dim", type=int, default=256)
+    p.add_argument("--pooling", type=int, default=20)
+    p.add_argument("--batch-per-rank", type=int, default=16384)
+    a = p.parse_args()
+    rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    device = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(device)
+    if "MASTER_ADDR" not in os.environ:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            os.environ["MASTER_PORT"] = str(s.getsockname()[1])
+    os.environ.setdefault("LOCAL_WORLD_SIZE", str(world))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device, timeout=datetime.timedelta(seconds=120))
+
+    from torchrec_b200.distributed import sharding_plan as sp
+    from torchrec_b200.distributed.embeddingbag import EmbeddingBagCollectionSharder
+    from torchrec_b200.distributed.model_parallel import DistributedModelParallel
+    from torchrec_b200.distributed.types import ShardingEnv, ShardingPlan
+    from torchrec_b200.modules.embedding_configs import DataType, EmbeddingBagConfig
+    from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
+    from torchrec_b200.ops import _ext
+    from torchrec_b200.optim.apply_optimizer_in_backward import apply_optimizer_in_backward
+    from torchrec_b200.optim.rowwise_adagrad import RowWiseAdagrad
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    _ext.require_cuda_ext("benchmark_rw_stress")
+    weight_bytes = a.tables * a.rows * a.dim * 2 / world
+    free, total = torch.cuda.mem_get_info(device)
+    if weight_bytes * 1.1 > free:
+        raise SystemExit(f"{weight_bytes / 2**30:.0f} GiB of table shards per rank do not fit in {free / 2**30:.0f} GiB: use more ranks")
+    keys = [f"f{i}" for i in range(a.tables)]
+    tables = [EmbeddingBagConfig(name=f"t{i}", embedding_dim=a.dim, num_embeddings=a.rows, feature_names=[k], data_type=DataType.FP16) for i, k in enumerate(keys)]
+    ebc = EmbeddingBagCollection(tables=tables, device=torch.device("meta"))
+    model = torch.nn.Module()
+    model.ebc = ebc
+    apply_optimizer_in_backward(RowWiseAdagrad, ebc.parameters(), {"lr": 0.01, "eps": 1e-8})
+    sharder = EmbeddingBagCollectionSharder(fused_params={"output_dtype": DataType.FP16})
+    mplan = sp.construct_module_sharding_plan(ebc, {t.name: sp.row_wise() for t in tables}, sharder=sharder, world_size=world, local_size=world, device_type="cuda")
+    dmp = DistributedModelParallel(model, env=ShardingEnv.from_process_group(dist.group.WORLD), device=device, plan=ShardingPlan({"ebc": mplan}), sharders=[sharder])
+    sebc = dmp.module.ebc
+    B = a.batch_per_rank
+    gen = torch.Generator(device=device).manual_seed(10 + rank)
+    batches = []
+    for _ in range(2):
+        values = torch.randint(0, a.rows, (a.tables * B * a.pooling,), generator=gen, device=device, dtype=torch.int64)
+        lengths = torch.full((a.tables * B,), a.pooling, dtype=torch.int32, device=device)
+        batches.append(KeyedJaggedTensor(keys=keys, values=values, lengths=lengths, stride=B))
+
+    def step(i: int) -> None:
+        out = sebc(batches[i % 2]).wait()
+        out.values().backward(torch.ones_like(out.values()))
+
+    for i in range(a.warmup):
+        step(i)
+    step_ms = _time(lambda: step(0), a.steps, device)
+
+    # ---- the three exchanges on their own, with the step's shapes ------------------------------------------------
+    ids_per_rank = a.tables * B * a.pooling
+    id_send = torch.empty(ids_per_rank, dtype=torch.int64, device=device)
+    id_recv = torch.empty_like(id_send)
+    len_send = torch.empty(a.tables * B * world, dtype=torch.int32, device=device)
+    len_recv = torch.empty_like(len_send)
+
+    def input_dist() -> None:
+        dist.all_to_all_single(len_recv, len_send)
+        dist.all_to_all_single(id_recv, id_send)
+
+    t_in = _time(input_dist, 10, device)
+    in_bytes = (id_send.numel() * 8 + len_send.numel() * 4) * (world - 1) / world
+    pooled = torch.empty(B * world, a.tables * a.dim, dtype=torch.float16, device=device)
+    rs_out = torch.empty(B, a.tables * a.dim, dtype=torch.float16, device=device)
+    t_rs = _time(lambda: dist.reduce_scatter_tensor(rs_out, pooled), 10, device)
+    rs_bytes = pooled.numel() * 2 * (world - 1) / world
+    t_ag = _time(lambda: dist.all_gather_into_tensor(pooled, rs_out), 10, device)
+    ag_bytes = rs_bytes
+    if rank == 0:
+        gbs = lambda b, ms: b / (ms / 1e3) / 1e9
+        print(json.dumps({
+            "metric": "row-wise EBC step (forward + backward, fused row-wise Adagrad)", "n_gpus": world, "ms_per_step": step_ms,
+            "samples_per_s": B * world / (step_ms / 1e3), "lookups_per_s": ids_per_rank * world / (step_ms / 1e3),
+            "input_dist_a2a": {"ms": t_in, "GBps_per_rank": gbs(in_bytes, t_in), "fraction_of_nvlink": gbs(in_bytes, t_in) / NVLINK_GBS},
+            "pooled_reduce_scatter": {"ms": t_rs, "GBps_per_rank": gbs(rs_bytes, t_rs), "fraction_of_nvlink": gbs(rs_bytes, t_rs) / NVLINK_GBS},
+            "grad_all_gather": {"ms": t_ag, "GBps_per_rank": gbs(ag_bytes, t_ag), "fraction_of_nvlink": gbs(ag_bytes, t_ag) / NVLINK_GBS},
+            "exchange_share_of_step": (t_in + t_rs + t_ag) / step_ms,
+            "config": {"tables": a.tables, "rows": a.rows, "dim": a.dim, "dtype": "fp16", "pooling": a.pooling, "batch_per_rank": B, "data": "synthetic uniform ids",
+                       "exchange_timing": "library collectives with the step's shapes, device-timed, max over ranks"}}))
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -52,7 +52,7 @@ def trim_torch_package_prefix_from_typename(typename: str) -> str:
 
 
 def _qdtype(dtype: torch.dtype) -> torch.dtype:
-    return {torch.int8: torch.quint8, torch.uint8: torch.quint8, torch.quint8: torch.quint8, torch.quint4x2: torch.quint4x2,
+    return {torch.int8: torch.quint8, torch.qint8: torch.quint8, torch.uint8: torch.quint8, torch.quint8: torch.quint8, torch.quint4x2: torch.quint4x2,
             torch.quint2x4: torch.quint2x4, torch.float16: torch.float16, torch.float32: torch.float32}[dtype]
 
 
