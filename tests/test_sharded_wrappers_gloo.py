@@ -277,3 +277,105 @@ def _fused_run(rank, world_size):
 
 def test_sharded_fused_ebc_matches_single_device():
     run_multi_process(_fused_run, world_size=2)
+
+
+class _TowerInteraction(torch.nn.Module):
+    def __init__(self, in_dim):
+        super().__init__()
+        self.lin = torch.nn.Linear(in_dim, 4)
+
+    def forward(self, kt):
+        return torch.relu(self.lin(kt.values()))
+
+
+def _tower_run(rank, world_size):
+    from torchrec_b200.distributed import sharding_plan as sp
+    from torchrec_b200.distributed.embedding_tower_sharding import EmbeddingTowerSharder
+    from torchrec_b200.distributed.model_parallel import DistributedModelParallel
+    from torchrec_b200.distributed.types import ShardingEnv, ShardingPlan
+    from torchrec_b200.modules.embedding_configs import PoolingType
+    from torchrec_b200.modules.embedding_tower import EmbeddingTower
+    from torchrec_b200.optim.apply_optimizer_in_backward import apply_optimizer_in_backward
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    with MultiProcessContext(rank, world_size, "gloo") as ctx:
+        torch.manual_seed(0)
+        B, lr = 6, 0.1
+        g = torch.nn.Module()
+        g.tower = EmbeddingTower(T._make_ebc(PoolingType.SUM), _TowerInteraction(5 * 16))
+        g.head = torch.nn.Linear(4, 1)
+        l = copy.deepcopy(g)
+        apply_optimizer_in_backward(torch.optim.SGD, l.tower.embedding.parameters(), {"lr": lr})
+        sharder = EmbeddingTowerSharder()
+        mplan = sp.construct_module_sharding_plan(l.tower.embedding, {f"t{i}": sp.table_wise(rank=1) for i in range(4)}, sharder=sharder._embedding_sharder,
+                                                  world_size=world_size, local_size=world_size, device_type="cpu")
+        dmp = DistributedModelParallel(l, env=ShardingEnv.from_process_group(ctx.pg), device=torch.device("cpu"), plan=ShardingPlan({"tower": mplan}),
+                                       sharders=sp.get_default_sharders() + [sharder])
+        dmp.load_state_dict(copy.deepcopy(g.state_dict()))
+        assert dmp.module.tower.owner_rank == 1
+        dense_params = [p for n, p in dmp.named_parameters() if "embedding" not in n]
+        opt = torch.optim.SGD(dense_params, lr=lr)
+        g_opt = torch.optim.SGD(g.parameters(), lr=lr)
+        kjts = [T._make_kjt(B, 100 + r) for r in range(world_size)]
+        keys = kjts[0].keys()
+        vals, lens = [], []
+        for k in keys:
+            for kj in kjts:
+                vals.append(kj[k].values()); lens.append(kj[k].lengths())
+        global_kjt = KeyedJaggedTensor.from_lengths_sync(keys=keys, values=torch.cat(vals), lengths=torch.cat(lens))
+        for step in range(2):
+            g_opt.zero_grad()
+            g_pred = g.head(g.tower(global_kjt))
+            g_pred.mean().backward()
+            g_opt.step()
+            opt.zero_grad()
+            out = dmp.module.tower(kjts[rank]).wait()
+            assert out.shape == (B, 4)
+            l_pred = dmp.module.head(out)
+            l_pred.mean().backward()
+            # the head is replicated: average its gradient by hand (the bare submodule call bypasses the wrapper's hooks)
+            for p in dmp.module.head.parameters():
+                dist.all_reduce(p.grad)
+                p.grad /= world_size
+            opt.step()
+            torch.testing.assert_close(l_pred.detach(), g_pred.detach()[rank * B:(rank + 1) * B], rtol=1e-4, atol=1e-5)
+        if rank == 1:  # the interaction was trained where the tower lives
+            torch.testing.assert_close(dmp.module.tower.interaction.lin.weight, g.tower.interaction.lin.weight, rtol=1e-4, atol=1e-5)
+
+
+def test_sharded_embedding_tower_matches_unsharded():
+    run_multi_process(_tower_run, world_size=2)
+
+
+def _pool_run(rank, world_size):
+    from torchrec_b200.distributed.object_pool import KeyedJaggedTensorPoolSharder, TensorPoolSharder
+    from torchrec_b200.distributed.types import ObjectPoolShardingPlan, ObjectPoolShardingType, ShardingEnv
+    from torchrec_b200.modules.keyed_jagged_tensor_pool import KeyedJaggedTensorPool
+    from torchrec_b200.modules.tensor_pool import TensorPool
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    with MultiProcessContext(rank, world_size, "gloo") as ctx:
+        env = ShardingEnv.from_process_group(ctx.pg)
+        plan = ObjectPoolShardingPlan(sharding_type=ObjectPoolShardingType.ROW_WISE)
+        pool = TensorPoolSharder().shard(TensorPool(pool_size=11, dim=3, dtype=torch.float32), plan, env, torch.device("cpu"))
+        assert pool._pool.shape[0] == (4 if rank < 2 else 3)
+        ids = torch.tensor([[0, 5, 9], [10, 4, 1], [8, 2, 6]][rank])
+        pool.update(ids, ids.float().unsqueeze(1).repeat(1, 3) + 0.5)
+        want = torch.tensor([1, 9, 10, 0, 2, 8, 3])  # 3 was never written
+        got = pool(want)
+        expect = (want.float().unsqueeze(1).repeat(1, 3) + 0.5) * (want != 3).float().unsqueeze(1)
+        torch.testing.assert_close(got, expect)
+        rep = TensorPoolSharder().shard(TensorPool(pool_size=6, dim=2, dtype=torch.float32), ObjectPoolShardingPlan(sharding_type=ObjectPoolShardingType.REPLICATED_ROW_WISE), env, torch.device("cpu"))
+        rep.update(torch.tensor([rank]), torch.full((1, 2), float(rank + 1)))
+        torch.testing.assert_close(rep(torch.tensor([0, 1, 2]))[:, 0], torch.tensor([1.0, 2.0, 3.0]))
+        kp = KeyedJaggedTensorPoolSharder().shard(KeyedJaggedTensorPool(pool_size=9, feature_max_lengths={"a": 2, "b": 3}), plan, env, torch.device("cpu"))
+        my_ids = torch.tensor([[0, 4], [8, 3], [6, 1]][rank])
+        kjt = KeyedJaggedTensor(keys=["a", "b"], values=torch.tensor([10, 11, 12, 20, 21, 22, 23]) + 100 * rank, lengths=torch.tensor([2, 1, 1, 3]))
+        kp.update(my_ids, kjt)
+        out = kp(torch.tensor([3, 0, 7]))  # written by rank 1 (second sample), rank 0 (first sample), never
+        assert out.lengths().tolist() == [1, 2, 0, 3, 1, 0]
+        assert out["a"].values().tolist() == [112, 10, 11] and out["b"].values().tolist() == [121, 122, 123, 20]
+
+
+def test_sharded_object_pools():
+    run_multi_process(_pool_run, world_size=3)
