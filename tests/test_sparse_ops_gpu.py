@@ -57,3 +57,34 @@ def test_jagged_padded_roundtrip(dtype):
     off_c = torch.cat([torch.zeros(1, dtype=torch.int64), lens_c.cumsum(0)])
     back = sops.padded_dense_to_jagged(got, off_c.cuda(), int(off_c[-1]))
     assert torch.equal(back.cpu(), sops.padded_dense_to_jagged(ref, off_c))
+
+
+def test_jagged_padded_kernels_are_differentiable():
+    import os
+
+    from torchrec_b200.ops import sparse_ops as sops
+
+    torch.manual_seed(0)
+    lengths = torch.tensor([3, 0, 7, 2, 5])
+    offsets = torch.cat([torch.zeros(1, dtype=torch.long), lengths.cumsum(0)]).cuda()
+    v = torch.randn(int(lengths.sum()), 16, device="cuda", requires_grad=True)
+    w = torch.randn(5, 4, 16, device="cuda")
+    out = sops.jagged_to_padded_dense(v, offsets, 4, 0.0)  # bag 2 and 4 are truncated
+    (out * w).sum().backward()
+    vr = v.detach().clone().requires_grad_(True)
+    sops._COMPOSITE_ONLY.add("jagged_to_padded_dense")
+    try:
+        ref = sops.jagged_to_padded_dense(vr, offsets, 4, 0.0)
+    finally:
+        sops._COMPOSITE_ONLY.discard("jagged_to_padded_dense")
+    (ref * w).sum().backward()
+    torch.testing.assert_close(out, ref)
+    torch.testing.assert_close(v.grad, vr.grad)
+    d = torch.randn(5, 8, 16, device="cuda", requires_grad=True)
+    j = sops.padded_dense_to_jagged(d, offsets, int(lengths.sum()))
+    wj = torch.randn_like(j)
+    (j * wj).sum().backward()
+    dr = d.detach().clone().requires_grad_(True)
+    mask = torch.arange(8, device="cuda").unsqueeze(0) < lengths.cuda().unsqueeze(1)
+    (dr[mask] * wj).sum().backward()
+    torch.testing.assert_close(d.grad, dr.grad)

@@ -51,6 +51,7 @@ def main() -> None:
     p.add_argument("--negatives", type=int, default=8192)
     p.add_argument("--pool", type=int, default=4, help="distinct batches cycled")
     p.add_argument("--cpu", action="store_true", help="plumbing check on the host (gloo); not a benchmark")
+    p.add_argument("--kernel-table", action="store_true", help="print the device time per kernel of one untimed step to stderr")
     a = p.parse_args()
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     device = torch.device("cpu") if a.cpu else torch.device(f"cuda:{local_rank}")
@@ -133,11 +134,28 @@ def main() -> None:
     tok = torch.tensor([tokens_per_step], device=device)
     dist.all_reduce(tok)
     ms_per_step = float(ms) / a.steps
+    if a.kernel_table and rank == 0 and not a.cpu:
+        import sys
+
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step(0)
+            torch.cuda.synchronize()
+        agg = {}
+        for e in prof.events():
+            if e.device_type == torch.autograd.DeviceType.CUDA:
+                r = agg.setdefault(e.name[:100], [0.0, 0])
+                r[0] += e.device_time_total
+                r[1] += 1
+        print(f"kernel table ({sum(v[0] for v in agg.values()) / 1e3:.2f} ms of device time):", file=sys.stderr)
+        for name, (t, n) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:30]:
+            print(f"  {t / 1e3:8.3f} ms  x{n:<4d} {name}", file=sys.stderr)
     if rank == 0:
         print(json.dumps({
             "metric": "BERT4Rec train sequences/sec", "value": a.batch_per_rank * world / (ms_per_step / 1e3), "unit": "sequences/s",
             "tokens_per_s": float(tok) / (ms_per_step / 1e3), "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
-            "loss": float(loss), "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic (Zipf(1.1) items, lengths U[20,200], 15% masked)",
+            "loss": float(loss.detach()), "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic (Zipf(1.1) items, lengths U[20,200], 15% masked)",
             "config": {"model": "BERT4Rec 2 layers, 4 heads, hidden 256, FFN 1024, sampled softmax 8192 negatives", "item_tables": f"input and output embeddings, each {a.vocab} x {a.dim} bf16",
                        "parallelism": f"column-wise x{n_col} EmbeddingCollection + dense DDP x{world}", "batch_per_rank": a.batch_per_rank,
                        "l2_policy": f"{a.pool} distinct batches cycled, two tables of {a.vocab * a.dim * 2 / 2**30:.1f} GiB"}}))

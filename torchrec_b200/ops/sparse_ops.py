@@ -327,11 +327,41 @@ def block_bucketize_sparse_features(
 # --------------------------------------------------------------------------------------
 # jagged <-> dense
 # --------------------------------------------------------------------------------------
+class _JaggedToPadded(torch.autograd.Function):
+    """The kernels are each other's adjoint: padding positions receive no gradient, truncated rows get zero."""
+
+    @staticmethod
+    def forward(ctx, values, offsets, max_length, padding_value):
+        ctx.save_for_backward(offsets)
+        ctx.total = values.shape[0]
+        return torch.ops.trb200.jagged_to_padded_dense(values, offsets, max_length, padding_value)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (offsets,) = ctx.saved_tensors
+        return torch.ops.trb200.padded_dense_to_jagged(grad.contiguous(), offsets, ctx.total), None, None, None
+
+
+class _PaddedToJagged(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, dense, offsets, total):
+        ctx.save_for_backward(offsets)
+        ctx.max_length = dense.shape[1]
+        return torch.ops.trb200.padded_dense_to_jagged(dense, offsets, total)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (offsets,) = ctx.saved_tensors
+        return torch.ops.trb200.jagged_to_padded_dense(grad.contiguous(), offsets, ctx.max_length, 0.0), None, None
+
+
 def jagged_to_padded_dense(
     values: torch.Tensor, offsets: torch.Tensor, max_length: int, padding_value: float = 0.0
 ) -> torch.Tensor:
     """``values [N(, D)]`` + ``offsets [B+1]`` -> ``[B, max_length(, D)]`` (truncating long bags)."""
     if values.is_cuda and values.numel() > 0 and values.dim() == 2 and _kern(values, "jagged_to_padded_dense"):
+        if values.requires_grad and torch.is_grad_enabled():
+            return _JaggedToPadded.apply(values, offsets, max_length, float(padding_value))
         return torch.ops.trb200.jagged_to_padded_dense(values, offsets, max_length, float(padding_value))
     B = offsets.numel() - 1
     off = offsets.to(torch.int64)
@@ -351,6 +381,8 @@ def padded_dense_to_jagged(dense: torch.Tensor, offsets: torch.Tensor, total: Op
     if dense.is_cuda and dense.dim() == 3 and dense.numel() > 0 and _kern(dense, "padded_dense_to_jagged"):
         if total is None:
             total = int(offsets[-1].item())
+        if dense.requires_grad and torch.is_grad_enabled():
+            return _PaddedToJagged.apply(dense, offsets, total)
         return torch.ops.trb200.padded_dense_to_jagged(dense, offsets, total)
     B, L = dense.shape[0], dense.shape[1]
     off = offsets.to(torch.int64)
