@@ -155,44 +155,47 @@ __global__ void __launch_bounds__(256) tbe_fwd_kernel(FwdParams p) {
   }
 }
 
-// unpooled: out[i, :] = W[idx_i]; one warp per bag, rows stored at the position of the id
+// unpooled: out[i, :] = W[idx_i].  One warp per group of kSeqPer consecutive ids, independent of how the ids are cut into
+// bags (a single bag may hold most of a batch); the feature of an id is found by a search over the F+1 feature boundaries.
+constexpr int kSeqPer = 8;
 template <typename emb_t, typename idx_t, int kVecs>
-__global__ void __launch_bounds__(256) tbe_seq_fwd_kernel(FwdParams p) {
+__global__ void __launch_bounds__(256) tbe_seq_fwd_kernel(FwdParams p, int64_t N) {
   const int lane = threadIdx.x & 31;
-  const int64_t bag = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nbags = int64_t(p.F) * p.B;
-  if (bag >= nbags) return;
-  const int f = int(bag / p.B);
+  const int64_t i0 = ((int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * kSeqPer;
+  if (i0 >= N) return;
   const idx_t* offsets = reinterpret_cast<const idx_t*>(p.offsets);
   const idx_t* indices = reinterpret_cast<const idx_t*>(p.indices);
-  const int64_t start = offsets[bag], end = offsets[bag + 1];
   const int F = p.F;
-  const int D = int(p.meta[M_DIM * F + f]);
-  const int64_t rows = p.meta[M_ROWS * F + f];
-  const emb_t* w = reinterpret_cast<const emb_t*>(p.weights) + p.meta[M_WOFF * F + f];
+  const int64_t B = p.B;
+  const int cnt = int(min(int64_t(kSeqPer), N - i0));
+  int64_t my_idx = lane < cnt ? int64_t(indices[i0 + lane]) : 0;
+  // last feature whose first id is <= i0 (features may be empty)
+  int lo = 0, hi = F;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (int64_t(offsets[int64_t(mid) * B]) <= i0) lo = mid; else hi = mid;
+  }
+  int f = lo;
+  int64_t f_end = int64_t(offsets[int64_t(f + 1) * B]);
   void* base = p.out.p[0];
-  for (int64_t i0 = start; i0 < end; i0 += 32) {
-    const int cnt = int(min(int64_t(32), end - i0));
-    int64_t my_idx = 0;
-    bool ok = true;
-    if (lane < cnt) {
-      my_idx = int64_t(indices[i0 + lane]);
-      if (my_idx < 0 || my_idx >= rows) {
-        atomicExch(p.err, 1);
-        my_idx = 0;
-        ok = false;
-      }
+  for (int j = 0; j < cnt; ++j) {
+    const int64_t i = i0 + j;
+    while (i >= f_end && f + 1 < F) {
+      ++f;
+      f_end = int64_t(offsets[int64_t(f + 1) * B]);
     }
-    for (int j = 0; j < cnt; ++j) {
-      const int64_t r = __shfl_sync(0xffffffffu, my_idx, j);
-      const bool rok = __shfl_sync(0xffffffffu, int(ok), j);
+    const int D = int(p.meta[M_DIM * F + f]);
+    const int64_t rows = p.meta[M_ROWS * F + f];
+    const emb_t* w = reinterpret_cast<const emb_t*>(p.weights) + p.meta[M_WOFF * F + f];
+    const int64_t r = __shfl_sync(0xffffffffu, my_idx, j);
+    const bool rok = r >= 0 && r < rows;
+    if (!rok && lane == 0) atomicExch(p.err, 1);
 #pragma unroll
-      for (int v = 0; v < kVecs; ++v) {
-        const int e = v * 128 + lane * 4;
-        if (e < D) {
-          float4 x = rok ? Vec4<emb_t>::load(w + r * D + e) : f4zero();
-          store4_dyn(base, (i0 + j) * p.out_stride + e, x, p.out_dtype);
-        }
+    for (int v = 0; v < kVecs; ++v) {
+      const int e = v * 128 + lane * 4;
+      if (e < D) {
+        float4 x = rok ? Vec4<emb_t>::load(w + r * D + e) : f4zero();
+        store4_dyn(base, i * p.out_stride + e, x, p.out_dtype);
       }
     }
   }
@@ -827,8 +830,11 @@ void tbe_forward_impl(const at::Tensor& weights, const at::Tensor& meta, const a
   TRB_DISPATCH_EMB(weights.scalar_type(), [&] {
     TRB_DISPATCH_VECS(nv, [&] {
       if (pooling == POOL_NONE) {
-        if (i64) tbe_seq_fwd_kernel<emb_t, int64_t, kVecs><<<blocks, threads, 0, stream>>>(p);
-        else tbe_seq_fwd_kernel<emb_t, int32_t, kVecs><<<blocks, threads, 0, stream>>>(p);
+        const int64_t n_ids = indices.numel();
+        const int64_t seq_blocks = ((n_ids + kSeqPer - 1) / kSeqPer * 32 + threads - 1) / threads;
+        if (n_ids == 0) return;
+        if (i64) tbe_seq_fwd_kernel<emb_t, int64_t, kVecs><<<seq_blocks, threads, 0, stream>>>(p, n_ids);
+        else tbe_seq_fwd_kernel<emb_t, int32_t, kVecs><<<seq_blocks, threads, 0, stream>>>(p, n_ids);
       } else {
         if (i64) tbe_fwd_kernel<emb_t, int64_t, kVecs><<<blocks, threads, 0, stream>>>(p);
         else tbe_fwd_kernel<emb_t, int32_t, kVecs><<<blocks, threads, 0, stream>>>(p);
