@@ -231,8 +231,8 @@ def test_per_sample_weight_gradient(pooling):
 
 @pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
 def test_forward_sequence_one_huge_bag_and_empty_feature(idx_dtype):
-    """Unpooled lookups are spread over ids, not bags: one bag with most of the batch, a feature without ids, mixed widths."""
-    specs = [(400, 64), (90, 128), (50, 64)]
+    """Unpooled lookups are spread over ids, not bags: one bag with most of the batch and a feature without ids."""
+    specs = [(400, 64), (90, 64), (50, 64)]
     ftm = [0, 1, 2, 0]
     B = 7
     g = torch.Generator().manual_seed(3)
@@ -242,9 +242,6 @@ def test_forward_sequence_one_huge_bag_and_empty_feature(idx_dtype):
     lengths[3 * B:] = torch.randint(0, 5, (B,), generator=g)  # feature 3; feature 2 stays empty
     offsets = torch.cat([torch.zeros(1, dtype=torch.int64), lengths.cumsum(0)])
     idx = torch.cat([torch.randint(0, 400, (5000,), generator=g), torch.randint(0, 90, (13,), generator=g), torch.randint(0, 400, (int(lengths[3 * B:].sum()),), generator=g)])
-    cpu = TableBatchedEmbeddingBags(specs, ftm, PoolingMode.NONE, torch.float32, torch.float32, OptimizerArgs())
-    # unpooled tables share one width in the module: use the common width case and the mixed case through max_D padding
-    specs = [(400, 64), (90, 64), (50, 64)]
     cpu, gpu = _pair(specs, ftm, PoolingMode.NONE, OptimizerArgs())
     with torch.no_grad():
         ref = cpu(idx.to(idx_dtype), offsets.to(idx_dtype))

@@ -25,6 +25,15 @@ def _time(fn, iters: int, device: torch.device) -> float:
     for _ in range(3):
         fn()
     dist.barrier()
+    if device.type == "cpu":
+        import time
+
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            fn()
+        ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / iters])
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -46,17 +55,22 @@ def main() -> None:
     p.add_argument("--dim", type=int, default=256)
     p.add_argument("--pooling", type=int, default=20)
     p.add_argument("--batch-per-rank", type=int, default=16384)
+    p.add_argument("--cpu", action="store_true", help="plumbing check on the host (gloo); not a benchmark")
     a = p.parse_args()
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
-    device = torch.device(f"cuda:{local_rank}")
-    torch.cuda.set_device(device)
+    device = torch.device("cpu") if a.cpu else torch.device(f"cuda:{local_rank}")
+    if not a.cpu:
+        torch.cuda.set_device(device)
     if "MASTER_ADDR" not in os.environ:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         with socket.socket() as s:
             s.bind(("127.0.0.1", 0))
             os.environ["MASTER_PORT"] = str(s.getsockname()[1])
     os.environ.setdefault("LOCAL_WORLD_SIZE", str(world))
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device, timeout=datetime.timedelta(seconds=120))
+    if a.cpu:
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
+    else:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device, timeout=datetime.timedelta(seconds=120))
 
     from torchrec_b200.distributed import sharding_plan as sp
     from torchrec_b200.distributed.embeddingbag import EmbeddingBagCollectionSharder
@@ -69,9 +83,10 @@ def main() -> None:
     from torchrec_b200.optim.rowwise_adagrad import RowWiseAdagrad
     from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
 
-    _ext.require_cuda_ext("benchmark_rw_stress")
+    if not a.cpu:
+        _ext.require_cuda_ext("benchmark_rw_stress")
     weight_bytes = a.tables * a.rows * a.dim * 2 / world
-    free, total = torch.cuda.mem_get_info(device)
+    free = torch.cuda.mem_get_info(device)[0] if not a.cpu else 1 << 60
     if weight_bytes * 1.1 > free:
         raise SystemExit(f"{weight_bytes / 2**30:.0f} GiB of table shards per rank do not fit in {free / 2**30:.0f} GiB: use more ranks")
     keys = [f"f{i}" for i in range(a.tables)]
@@ -81,11 +96,11 @@ def main() -> None:
     model.ebc = ebc
     apply_optimizer_in_backward(RowWiseAdagrad, ebc.parameters(), {"lr": 0.01, "eps": 1e-8})
     sharder = EmbeddingBagCollectionSharder(fused_params={"output_dtype": DataType.FP16})
-    mplan = sp.construct_module_sharding_plan(ebc, {t.name: sp.row_wise() for t in tables}, sharder=sharder, world_size=world, local_size=world, device_type="cuda")
+    mplan = sp.construct_module_sharding_plan(ebc, {t.name: sp.row_wise() for t in tables}, sharder=sharder, world_size=world, local_size=world, device_type=device.type)
     dmp = DistributedModelParallel(model, env=ShardingEnv.from_process_group(dist.group.WORLD), device=device, plan=ShardingPlan({"ebc": mplan}), sharders=[sharder])
     sebc = dmp.module.ebc
     B = a.batch_per_rank
-    gen = torch.Generator(device=device).manual_seed(10 + rank)
+    gen = torch.Generator(device=device).manual_seed(10 + rank) if not a.cpu else torch.Generator().manual_seed(10 + rank)
     batches = []
     for _ in range(2):
         values = torch.randint(0, a.rows, (a.tables * B * a.pooling,), generator=gen, device=device, dtype=torch.int64)
