@@ -145,9 +145,29 @@ def build_cpu(verbose: bool = False, force: bool = False) -> str:
     return out
 
 
+def build_plugins(verbose: bool = False, force: bool = False) -> List[str]:
+    """Run-time plugins of the dynamic-embedding library (``cpu/plugins/<name>.cpp`` -> ``torchrec_b200/_tde_<name>.so``); they
+    depend on the plugin ABI header only, not on the tensor library."""
+    outs = []
+    hdrs = sorted(glob.glob(os.path.join(HERE, "cpu", "*.h")))
+    for src in sorted(glob.glob(os.path.join(HERE, "cpu", "plugins", "*.cpp"))):
+        name = os.path.splitext(os.path.basename(src))[0]
+        out = os.path.join(PKG, f"_tde_{name}.so")
+        tag = _hash([src] + hdrs, "plugin")
+        stamp = os.path.join(OBJ, f"plugin_{name}.stamp")
+        os.makedirs(OBJ, exist_ok=True)
+        if force or not os.path.exists(out) or not os.path.exists(stamp) or open(stamp).read() != tag:
+            _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", out, src], verbose)
+            with open(stamp, "w") as f:
+                f.write(tag)
+        outs.append(out)
+    return outs
+
+
 def build_all(verbose: bool = False, force: bool = False) -> None:
     build_cuda(verbose=verbose, force=force)
     build_cpu(verbose=verbose, force=force)
+    build_plugins(verbose=verbose, force=force)
 
 
 if __name__ == "__main__":
