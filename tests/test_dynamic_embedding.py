@@ -79,7 +79,7 @@ def test_ps_evict_fetch_round_trip(col_shards):
 def test_unknown_io_type_raises():
     shards = torch.classes.trb_tde.LocalShardList()
     with pytest.raises(RuntimeError, match="no IO provider"):
-        torch.classes.trb_tde.PS("t", shards, 8, 0, "redis://127.0.0.1:6379", 10)
+        torch.classes.trb_tde.PS("t", shards, 8, 0, "nosuchstore://127.0.0.1:6379", 10)
 
 
 def test_id_transformer_collection_keeps_rows_across_eviction():
