@@ -257,6 +257,15 @@ def main() -> None:
     ms_per_step = total_ms / args.steps
     value = args.global_batch / (ms_per_step / 1e3)
 
+    # ---- diagnostic: how long the host needs to issue a step (no synchronisation inside); close to ms_per_step = host-bound ------
+    torch.cuda.synchronize()
+    dist.barrier()
+    t_issue0 = time.perf_counter()
+    for i in range(5):
+        step(dev_batches[i % len(dev_batches)])
+    host_issue_ms = (time.perf_counter() - t_issue0) * 1e3 / 5
+    torch.cuda.synchronize()
+
     # ---- count this package's kernel launches in one (untimed) step ----------------------------------------------
     launches = None
     try:
@@ -325,6 +334,7 @@ def main() -> None:
                        "qcomm": "fp16 fwd / bf16 bwd", "gemm": dense_ops.get_gemm_backend(), "rows": "full" if not args.row_cap else f"capped at {args.row_cap}",
                        "l2_policy": f"inputs larger than L2: {args.pool} distinct batches cycled, tables > 100 GB"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "diagnostics": {"host_issue_ms_per_step": host_issue_ms},
         }
         print(json.dumps(res))
     dist.barrier()
