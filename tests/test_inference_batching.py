@@ -81,3 +81,62 @@ def test_timeout_flushes_partial_batch_and_threads():
     q.stop()
     with pytest.raises(RuntimeError):
         q.wait_result(12345, 10)
+
+
+def test_resource_manager_bounds_in_flight_batches():
+    rm = torch.classes.trb_inference.ResourceManager(2, 2)
+    assert rm.occupy(0, 10) and rm.occupy(0, 10)
+    assert not rm.occupy(0, 20)  # third batch on device 0 is refused after the wait
+    assert rm.occupy(1, 10)
+    assert rm.outstanding(0) == 2 and rm.peak(0) == 2 and rm.rejected() == 1
+    t = threading.Timer(0.05, lambda: rm.release(0))
+    t.start()
+    assert rm.occupy(0, 2000)  # a slot frees up while waiting
+    t.join()
+    rm.release(0); rm.release(0); rm.release(1)
+    with pytest.raises(RuntimeError):
+        rm.release(1)
+
+
+def test_batching_executor_merges_concurrent_clients():
+    from torchrec_b200.inference.executor import BatchingExecutor
+    from torchrec_b200.modules.embedding_configs import EmbeddingBagConfig
+    from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    torch.manual_seed(0)
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ebc = EmbeddingBagCollection(tables=[EmbeddingBagConfig(name="t", embedding_dim=4, num_embeddings=50, feature_names=["a", "b"])])
+            self.lin = torch.nn.Linear(3 + 8, 2)
+
+        def forward(self, dense, kjt):
+            return self.lin(torch.cat([dense, self.ebc(kjt).values()], dim=1))
+
+    m = M().eval()
+    ex = BatchingExecutor(m, ["a", "b"], [torch.device("cpu")], max_batch_size=16, batching_timeout_ms=20)
+    results = {}
+
+    def client(i):
+        g = torch.Generator().manual_seed(i)
+        b = 1 + i % 3
+        lengths = torch.randint(0, 3, (2 * b,), generator=g)
+        kjt = KeyedJaggedTensor(keys=["a", "b"], values=torch.randint(0, 50, (int(lengths.sum()),), generator=g), lengths=lengths)
+        dense = torch.randn(b, 3, generator=g)
+        got = ex.predict(dense, kjt)
+        with torch.no_grad():
+            results[i] = (got, m(dense, kjt))
+
+    threads = [threading.Thread(target=client, args=(i,)) for i in range(12)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    ex.shutdown()
+    assert len(results) == 12
+    for got, want in results.values():
+        torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
+    assert ex.batches_formed < 12  # requests were merged
+    assert ex.peak_outstanding[0] >= 1 and ex.rejected_batches == 0

@@ -50,7 +50,8 @@ class BatchingQueue : public torch::CustomClassHolder {
     const int64_t b = dense.size(0);
     TORCH_CHECK(lengths.numel() == num_features_ * b, "lengths must hold num_features * b entries (feature-major)");
     TORCH_CHECK(lengths.sum().item<int64_t>() == values.numel(), "values must hold sum(lengths) ids");
-    Request r{next_id_++, dense.contiguous(), lengths.contiguous().view({num_features_, b}), values.contiguous(), b,
+    const int64_t id = next_id_.fetch_add(1);  // the id this call returns: concurrent callers must not read the counter again
+    Request r{id, dense.contiguous(), lengths.contiguous().view({num_features_, b}), values.contiguous(), b,
               std::chrono::steady_clock::now()};
     {
       std::lock_guard<std::mutex> lock(mu_);
@@ -59,7 +60,7 @@ class BatchingQueue : public torch::CustomClassHolder {
       pending_samples_ += b;
     }
     cv_.notify_all();
-    return next_id_ - 1;
+    return id;
   }
 
   // (dense, lengths, values, request_ids, request_sizes); all empty when nothing arrived within the timeout
