@@ -181,7 +181,8 @@ class _PeerPushLookup(torch.autograd.Function):
             if psw is not None and psw.dtype != torch.float32:
                 psw = psw.float()
             tbe.forward_push(f.values(), f.offsets(), psw, B, B_local, out_ptrs, total_D, col, out.dtype)
-            saved.append((f.values(), f.offsets(), psw))
+            # the id sort of the backward starts now, on the side stream, under the dense towers
+            saved.append((f.values(), f.offsets(), psw, tbe.build_plan_ahead(f.values(), f.offsets(), psw, B) if torch.is_grad_enabled() else None))
             col += tbe.total_D
         peer.barrier()
         ctx.lookup = lookup
@@ -201,9 +202,9 @@ class _PeerPushLookup(torch.autograd.Function):
         peer.barrier()
         scale = 1.0 / peer.world if comm_ops.get_gradient_division() else 1.0
         col = lookup._peer_col_base
-        for emb_op, (idx, off, psw) in zip(lookup._emb_modules, ctx.saved):
+        for emb_op, (idx, off, psw, plan) in zip(lookup._emb_modules, ctx.saved):
             tbe = emb_op.emb_module
-            tbe.backward_pull(g, g_ptrs, lookup._peer_total_D, idx, off, psw, ctx.B, ctx.B_local, col, scale)
+            tbe.backward_pull(g, g_ptrs, lookup._peer_total_D, idx, off, psw, ctx.B, ctx.B_local, col, scale, plan)
             col += tbe.total_D
         ctx.saved = None
         return None, None, None

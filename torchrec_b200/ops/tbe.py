@@ -14,6 +14,7 @@ and ``torch.optim`` for the others.
 from __future__ import annotations
 
 import enum
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -78,12 +79,33 @@ class OptimizerArgs:
 
 
 class TBEPlan:
-    """Sorted (row -> contributing bags) plan of one batch; built from ids only."""
+    """Sorted (row -> contributing bags) plan of one batch; built from ids only.  ``ready`` is set when the plan was built on a
+    side stream: the consumer's stream waits for it before the backward kernels read the plan."""
 
-    __slots__ = ("keys", "src", "w", "src_feature", "bag_scale")
+    __slots__ = ("keys", "src", "w", "src_feature", "bag_scale", "ready")
 
     def __init__(self, tensors: List[torch.Tensor]) -> None:
         self.keys, self.src, self.w, self.src_feature, self.bag_scale = tensors
+        self.ready = None
+
+    def wait(self) -> None:
+        if self.ready is not None:
+            torch.cuda.current_stream().wait_event(self.ready)
+            self.ready = None
+
+
+# The id sort of the backward depends on the ids only.  It is memory-bound while the dense towers that run between an embedding
+# forward and its backward are tensor-core-bound, so it is issued on a side stream right after the forward lookup and overlaps them.
+_PLAN_AHEAD = os.environ.get("TRB200_PLAN_AHEAD", "1") != "0"
+_plan_streams: Dict[int, "torch.cuda.Stream"] = {}
+
+
+def _plan_stream(device: torch.device) -> "torch.cuda.Stream":
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    s = _plan_streams.get(idx)
+    if s is None:
+        s = _plan_streams[idx] = torch.cuda.Stream(device=device)
+    return s
 
 
 def _apply_rows_cpu(
@@ -132,6 +154,8 @@ class _TBEFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, dummy, module, indices, offsets, psw, B, plan):
         out = module._forward_impl(indices, offsets, psw, B)
+        if plan is None:
+            plan = module.build_plan_ahead(indices, offsets, psw, B)
         ctx.module = module
         ctx.B = B
         ctx.plan = plan
@@ -342,6 +366,26 @@ class TableBatchedEmbeddingBags(nn.Module):
             )
         )
 
+    def build_plan_ahead(self, indices: torch.Tensor, offsets: torch.Tensor, psw: Optional[torch.Tensor], B: int) -> Optional[TBEPlan]:
+        """:meth:`build_plan` issued on the side stream, ordered after everything already queued on the current stream.  The
+        plan's tensors are marked as used by the current stream so that their memory is not recycled under the backward."""
+        if not (_PLAN_AHEAD and self.weights.is_cuda and indices.numel() > 0):
+            return None
+        cur = torch.cuda.current_stream()
+        side = _plan_stream(self.weights.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            plan = self.build_plan(indices, offsets, psw, B)
+            plan.ready = torch.cuda.Event()
+            plan.ready.record(side)
+        for t in (plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale):
+            if t is not None and t.numel() > 0:
+                t.record_stream(cur)
+        for t in (indices, offsets, psw):
+            if t is not None and t.is_cuda:
+                t.record_stream(side)
+        return plan
+
     def _backward_impl(self, grad_out, indices, offsets, psw, B, plan) -> Optional[torch.Tensor]:
         w = self.weights.detach()
         if self.fused:
@@ -350,6 +394,8 @@ class TableBatchedEmbeddingBags(nn.Module):
             _ext.require_cuda_ext("tbe_backward")
             if plan is None:
                 plan = self.build_plan(indices, offsets, psw, B)
+            else:
+                plan.wait()
             # the kernel reads gradient rows through a row stride: a column slice of a wider tensor (the gradient of a concat)
             # needs no copy as long as rows are dense and 16-byte aligned
             esz = grad_out.element_size()
@@ -405,6 +451,8 @@ class TableBatchedEmbeddingBags(nn.Module):
         self.step += 1
         if plan is None:
             plan = self.build_plan(indices, offsets, psw, B)
+        else:
+            plan.wait()
         o = self.optimizer_args
         eps = o.eta if o.optimizer == EmbOptimType.LARS_SGD else o.eps
         torch.ops.trb200.tbe_backward_apply_dist(
