@@ -96,3 +96,69 @@ def _run(rank, world_size, pipeline_name):
 @pytest.mark.parametrize("pipeline_name", ["base", "sparse", "fused", "semisync", "prefetch"])
 def test_pipeline_matches_plain_loop(pipeline_name):
     run_multi_process(_run, world_size=2, pipeline_name=pipeline_name)
+
+
+def _run_eval_and_staged(rank, world_size):
+    from torchrec_b200.distributed.train_pipeline import EvalPipelineSparseDist, StagedTrainPipeline, TrainPipelinePT2
+    from torchrec_b200.distributed.train_pipeline.pipeline_stage import PipelineStage, SparseDataDistUtil
+    from torchrec_b200.optim.keyed import CombinedOptimizer, KeyedOptimizerWrapper
+    from torchrec_b200.optim.optimizers import in_backward_optimizer_filter
+
+    with MultiProcessContext(rank, world_size, "gloo") as ctx:
+        batches = _batches(rank, 5)
+        dmp = _build(rank, world_size, ctx)
+        dense = KeyedOptimizerWrapper(dict(in_backward_optimizer_filter(dmp.named_parameters())), lambda p: torch.optim.SGD(p, lr=0.05))
+        opt = CombinedOptimizer([dmp.fused_optimizer, dense])
+        before = {k: (v.local_shards()[0].tensor.clone() if hasattr(v, "local_shards") and v.local_shards() else None) for k, v in dmp.state_dict().items()}
+        # evaluation pipeline: same outputs as plain eval forwards, nothing is updated
+        dmp.eval()
+        with torch.no_grad():
+            want = [dmp(b)[0].clone() for b in batches]
+        pipe = EvalPipelineSparseDist(dmp, opt, torch.device("cpu"))
+        it = iter(batches)
+        got = [pipe.progress(it)[0] for _ in range(5)]
+        with pytest.raises(StopIteration):
+            pipe.progress(it)
+        for a, b in zip(got, want):
+            torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+        for k, v in dmp.state_dict().items():
+            if before[k] is not None:
+                assert torch.equal(v.local_shards()[0].tensor, before[k])
+        # staged pipeline: a transform stage and the sparse data dist stage run ahead of the model
+        dmp.train()
+        seen = []
+
+        def tag(batch):
+            seen.append(float(batch.dense_features.sum()))
+            return batch
+
+        util = SparseDataDistUtil(model=dmp, data_dist_stream=None)
+        staged = StagedTrainPipeline(pipeline_stages=[
+            PipelineStage(name="tag", runnable=tag, stream=None),
+            PipelineStage(name="start_sparse_data_dist", runnable=util.start_sparse_data_dist, stream=None),
+        ])
+        it = iter(batches)
+        losses = []
+        while True:
+            batch = staged.progress(it)
+            if batch is None:
+                break
+            batch = util.wait_sparse_data_dist(batch)
+            opt.zero_grad()
+            loss, _ = dmp(batch)
+            loss.backward()
+            opt.step()
+            losses.append(float(loss))
+        assert len(losses) == 5 and len(seen) == 5
+        assert all(l == l for l in losses)
+        # the PT2 pipeline runs the uncompiled path when no compile config is given
+        util.detach()
+        pt2 = TrainPipelinePT2(dmp, opt, torch.device("cpu"))
+        it = iter(batches[:2])
+        assert pt2.progress(it) is not None and pt2.progress(it) is not None
+        with pytest.raises(StopIteration):
+            pt2.progress(it)
+
+
+def test_eval_staged_and_pt2_pipelines():
+    run_multi_process(_run_eval_and_staged, world_size=2)
