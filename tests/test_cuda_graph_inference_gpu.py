@@ -34,6 +34,7 @@ def test_graph_replay_matches_eager():
 
     d0, k0 = request(6)
     graphed = CudaGraphDenseSparseModule(model, d0, k0, values_capacity=int(k0.values().numel() * 2))
+    assert graphed.captured, graphed.capture_error
     for max_len in (6, 2, 9, 0):
         d, k = request(max_len)
         with torch.no_grad():

@@ -44,7 +44,8 @@ class CudaGraphDenseSparseModule(nn.Module):
         self._weights = torch.zeros(self._capacity, dtype=torch.float32, device=sample_dense.device) if self._weighted else None
         if self._weighted:
             self._weights[:n].copy_(sample_kjt.weights())
-        self._graph = torch.cuda.CUDAGraph()
+        self._graph: Optional[torch.cuda.CUDAGraph] = torch.cuda.CUDAGraph()
+        self.capture_error: Optional[str] = None
         side = torch.cuda.Stream(device=sample_dense.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side), torch.no_grad():
@@ -52,10 +53,19 @@ class CudaGraphDenseSparseModule(nn.Module):
                 self._run_static()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        with torch.no_grad(), torch.cuda.graph(self._graph):
-            self._out = self._run_static()
+        try:
+            with torch.no_grad(), torch.cuda.graph(self._graph):
+                self._out = self._run_static()
+        except Exception as e:  # a module that synchronises with the host cannot be captured: serve it eagerly
+            self._graph = None
+            self.capture_error = f"{type(e).__name__}: {e}"
+            torch.cuda.synchronize()
         self.replays = 0
         self.fallbacks = 0
+
+    @property
+    def captured(self) -> bool:
+        return self._graph is not None
 
     def _run_static(self) -> torch.Tensor:
         kjt = KeyedJaggedTensor(keys=self._keys, values=self._values, lengths=self._lengths, weights=self._weights, stride=self._B)
@@ -68,9 +78,10 @@ class CudaGraphDenseSparseModule(nn.Module):
     @torch.no_grad()
     def forward(self, dense: torch.Tensor, kjt: KeyedJaggedTensor) -> torch.Tensor:
         """Returns the static output buffer: it is overwritten by the next call, copy it if it must live longer."""
-        if not self._fits(dense, kjt):
+        if self._graph is None or not self._fits(dense, kjt):
             self.fallbacks += 1
-            return self.module(dense, kjt)
+            dev = self._dense.device
+            return self.module(dense.to(dev, non_blocking=True), kjt.to(dev, non_blocking=True))
         n = kjt.values().numel()
         self._dense.copy_(dense, non_blocking=True)
         self._values[:n].copy_(kjt.values(), non_blocking=True)
