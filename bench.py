@@ -211,8 +211,17 @@ def main() -> None:
     dense_opt = KeyedOptimizerWrapper(dict(in_backward_optimizer_filter(dmp.named_parameters())), lambda p: torch.optim.Adagrad(p, lr=0.01, foreach=True))
     optimizer = CombinedOptimizer([dmp.fused_optimizer, dense_opt])
     shard_types: Dict[str, int] = {}
+    # algorithmic bytes of the embedding exchange per rank and step: pooled rows of the samples other ranks own (forward, 2 bytes
+    # per element) and the same volume of gradient rows (backward); a row-wise table moves its partial sums through a reduce-scatter
+    cols_on_rank = [0] * world
     for ps in plan.plan["model.sparse_arch.embedding_bag_collection"].values():
         shard_types[ps.sharding_type] = shard_types.get(ps.sharding_type, 0) + 1
+        if ps.sharding_spec is None:
+            continue
+        for sh in ps.sharding_spec.shards:
+            r = int(str(sh.placement).split("/")[0].split(":")[1])
+            cols_on_rank[r] += sh.shard_sizes[1]
+    exchange_bytes = max(cols_on_rank) * args.global_batch * (world - 1) // max(world, 1) * 2
 
     ds = RandomRecDataset(keys=keys, batch_size=B_local, hash_sizes=rows, ids_per_features=POOLING, min_ids_per_features=POOLING,
                           num_dense=DENSE_IN, manual_seed=1234 + rank, num_generated_batches=args.pool, zipf_s=ZIPF_S,
@@ -335,6 +344,9 @@ def main() -> None:
                        "l2_policy": f"inputs larger than L2: {args.pool} distinct batches cycled, tables > 100 GB"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "diagnostics": {"host_issue_ms_per_step": host_issue_ms},
+            "emb_a2a": {"fwd_bytes_per_step_busiest_rank": exchange_bytes, "bwd_bytes_per_step_busiest_rank": exchange_bytes,
+                        "GBps_lower_bound": (2 * exchange_bytes / (ms_per_step / 1e3) / 1e9) if world > 1 else 0.0,
+                        "note": "algorithmic bytes of the embedding exchange over the whole step time; the exchange is fused into the lookup kernels, so it has no time of its own"},
         }
         print(json.dumps(res))
     dist.barrier()
