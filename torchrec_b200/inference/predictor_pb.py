@@ -1,5 +1,16 @@
-"""Message classes of ``protos/predictor.proto`` built at import time from a descriptor written in code, so that no protobuf
-compiler is needed at build or run time.  ``SERVICE = "predictor.Predictor"``, method ``Predict``."""
+"""Messages of the prediction service, built at import time from a descriptor written in code (no protobuf compiler at build or
+run time).  Package ``predictor``; service ``Predictor`` with one unary method ``Predict(PredictionRequest) -> PredictionResponse``.
+
+Wire format (field numbers in brackets; the same numbers as the reference's ``torchrec/inference/protos/predictor.proto``, so
+clients of either server interoperate).  Tensors travel as raw little-endian bytes.
+
+* ``PredictionRequest``: batch_size [1] int32; float_features [2] ``FloatFeatures``; id_list_features [3], id_score_list_features [4]
+  and unary_features [6] ``SparseFeatures``; embedding_features [5] ``FloatFeatures``.
+* ``FloatFeatures``: num_features [1] int32; values [2] bytes = fp32 ``[batch, num_features]``.
+* ``SparseFeatures``: num_features [1] int32; lengths [2] bytes = int32 ``[num_features, batch]``; values [3] bytes = int32 ids,
+  jagged, feature-major; weights [4] bytes = fp32, one per id (score lists only).
+* ``PredictionResponse``: predictions [1] map from task name to ``FloatVec`` (data [1] repeated float).
+"""
 from __future__ import annotations
 
 from google.protobuf import descriptor_pb2, descriptor_pool, message_factory

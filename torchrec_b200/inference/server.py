@@ -1,6 +1,6 @@
 """Prediction server: ``Predict(PredictionRequest) -> PredictionResponse`` over gRPC.
 
-A request carries raw tensor bytes (see ``protos/predictor.proto``); the server rebuilds ``float_features [B, n]`` and the
+A request carries raw tensor bytes (wire format: ``predictor_pb.py``); the server rebuilds ``float_features [B, n]`` and the
 ``id_list_features`` / ``id_score_list_features`` jagged inputs, moves them to the serving device from pinned staging buffers, runs
 the predict module and returns ``{"default": scores}`` (or every entry of a dict result).  Requests arriving together are merged
 into one forward by the native batching queue (``torch.classes.trb_inference.BatchingQueue``) when ``max_batch_size`` allows.
