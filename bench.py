@@ -54,6 +54,7 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--breakdown", action="store_true", help="print a per-phase device-time breakdown to stderr")
     p.add_argument("--kernel-table", action="store_true", help="print per-kernel device time of one step to stderr (diagnostic)")
+    p.add_argument("--host-profile", action="store_true", help="print the host-side profile (cProfile) of 10 untimed steps to stderr (diagnostic)")
     return p.parse_args()
 
 
@@ -167,6 +168,7 @@ def main() -> None:
     import datetime
 
     # a short collective timeout: a rank that falls out of step ends the job in minutes, not after the 10-minute default
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # the library's banner must not land in front of the JSON line on stdout
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device, timeout=datetime.timedelta(seconds=120))
 
     from torchrec_b200.datasets.random import RandomRecDataset
@@ -274,6 +276,25 @@ def main() -> None:
         step(dev_batches[i % len(dev_batches)])
     host_issue_ms = (time.perf_counter() - t_issue0) * 1e3 / 5
     torch.cuda.synchronize()
+
+    if args.host_profile and rank == 0:
+        import cProfile
+        import io
+        import pstats
+
+        pr = cProfile.Profile()
+        pr.enable()
+        for i in range(10):
+            step(dev_batches[i % len(dev_batches)])
+        pr.disable()
+        torch.cuda.synchronize()
+        for key in ("tottime", "cumulative"):
+            buf = io.StringIO()
+            pstats.Stats(pr, stream=buf).sort_stats(key).print_stats(45)
+            print(f"host profile of 10 steps by {key}:\n" + buf.getvalue()[:9000], file=sys.stderr)
+    elif args.host_profile:
+        for i in range(10):
+            step(dev_batches[i % len(dev_batches)])
 
     # ---- count this package's kernel launches in one (untimed) step ----------------------------------------------
     launches = None
