@@ -52,6 +52,8 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--row-cap", type=int, default=0, help="cap table rows (smoke runs on small memory); 0 = full size")
     p.add_argument("--pool", type=int, default=4, help="number of distinct synthetic batches that are cycled")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--loop", choices=["pipeline", "plain"], default="pipeline",
+                   help="timed loop: TrainPipelineSparseDist over device-resident batches (input distribution of the next batch on side streams) or a plain forward/backward/step loop")
     p.add_argument("--breakdown", action="store_true", help="print a per-phase device-time breakdown to stderr")
     p.add_argument("--kernel-table", action="store_true", help="print per-kernel device time of one step to stderr (diagnostic)")
     p.add_argument("--host-profile", action="store_true", help="print the host-side profile (cProfile) of 10 untimed steps to stderr (diagnostic)")
@@ -148,6 +150,11 @@ def main() -> None:
     if args.impl == "reference":
         reference_arm(args)
         return
+
+    # libraries print banners on stdout (the collective library's version line): everything goes to stderr until the result line
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
 
     import torch
     import torch.distributed as dist
@@ -261,12 +268,14 @@ def main() -> None:
         sampler.start()
     for i in range(args.warmup):
         step(dev_batches[i % len(dev_batches)])
-    sampler.mark_begin()
-    total_ms = timed(lambda i: step(dev_batches[i % len(dev_batches)]), args.steps)
-    sampler.mark_end()
-    clocks = sampler.stop() if rank == 0 else {}
-    ms_per_step = total_ms / args.steps
-    value = args.global_batch / (ms_per_step / 1e3)
+    plain_ms = None
+    if args.loop == "plain":
+        sampler.mark_begin()
+        total_ms = timed(lambda i: step(dev_batches[i % len(dev_batches)]), args.steps)
+        sampler.mark_end()
+        clocks = sampler.stop() if rank == 0 else {}
+        ms_per_step = total_ms / args.steps
+        value = args.global_batch / (ms_per_step / 1e3)
 
     # ---- diagnostic: how long the host needs to issue a step (no synchronisation inside); close to ms_per_step = host-bound ------
     torch.cuda.synchronize()
@@ -325,29 +334,62 @@ def main() -> None:
     except Exception:
         launches = None
 
-    # ---- end to end through the public pipeline API: H2D from pinned memory + loss read-back every step ------------
+    # ---- the training pipeline: one instance serves the device-timed loop (device-resident batches) and the end-to-end loop
+    #      (pinned host batches + loss read-back); the feed switches its source between the two phases ------------------------
     e2e = None
-    if not args.no_e2e:
-        pipe = TrainPipelineSparseDist(dmp, optimizer, device)
+    feed_mode = {"host": False}
 
-        def endless():
-            i = 0
-            while True:
-                yield host_batches[i % len(host_batches)]
-                i += 1
+    def feed():
+        i = 0
+        while True:
+            src = host_batches if feed_mode["host"] else dev_batches
+            yield src[i % len(src)]
+            i += 1
 
-        it = endless()
-        sink = []
-
-        def e2e_step(_i):
-            out = pipe.progress(it)
-            sink.append(float(out[0].item()))  # device-to-host read of the step's loss
+    it = feed()
+    pipe = TrainPipelineSparseDist(dmp, optimizer, device) if (args.loop == "pipeline" or not args.no_e2e) else None
+    if args.loop == "pipeline":
+        def pstep(_i):
+            return pipe.progress(it)
 
         for i in range(max(args.warmup, 3)):
+            pstep(i)
+        sampler.mark_begin()
+        total_ms = timed(pstep, args.steps)
+        sampler.mark_end()
+        clocks = sampler.stop() if rank == 0 else {}
+        ms_per_step = total_ms / args.steps
+        value = args.global_batch / (ms_per_step / 1e3)
+    if not args.no_e2e:
+        feed_mode["host"] = True
+        # the loss of every step is copied to pinned host memory inside the step and consumed two steps later, so that the read-back
+        # does not drain the device after every step
+        loss_bufs = [torch.empty((), dtype=torch.float32).pin_memory() for _ in range(2)]
+        loss_events: List[Optional[torch.cuda.Event]] = [None, None]
+        sink: List[float] = []
+
+        def e2e_step(i):
+            out = pipe.progress(it)
+            k = i % 2
+            if loss_events[k] is not None:
+                loss_events[k].synchronize()
+                sink.append(float(loss_bufs[k]))
+            loss_bufs[k].copy_(out[0].detach().float().reshape(()), non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            loss_events[k] = ev
+
+        for i in range(max(args.warmup, 3) + 2):  # + the two device-resident batches still in flight from the first phase
             e2e_step(i)
         e2e_ms = timed(e2e_step, args.steps)
+        for ev, buf in zip(loss_events, loss_bufs):
+            if ev is not None:
+                ev.synchronize()
+                sink.append(float(buf))
+        assert all(v == v for v in sink), "non-finite loss"
         e2e = {"value": args.global_batch / (e2e_ms / args.steps / 1e3), "unit": "samples/s", "ms_per_step": e2e_ms / args.steps,
-               "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": 4, "api": "TrainPipelineSparseDist.progress"}
+               "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": 4, "api": "TrainPipelineSparseDist.progress",
+               "read_back": "loss copied to pinned memory every step, consumed on the host two steps later"}
 
     if args.breakdown:
         _breakdown(torch, dmp, optimizer, dev_batches[0], rank)  # a training step: every rank takes part
@@ -362,14 +404,17 @@ def main() -> None:
                        "global_batch": args.global_batch, "seq_len": None, "parallelism": f"planner: {shard_types} + dense DDP x{world}",
                        "embedding_optimizer": "fused rowwise Adagrad lr 0.005", "dense_optimizer": "Adagrad",
                        "qcomm": "fp16 fwd / bf16 bwd", "gemm": dense_ops.get_gemm_backend(), "rows": "full" if not args.row_cap else f"capped at {args.row_cap}",
-                       "l2_policy": f"inputs larger than L2: {args.pool} distinct batches cycled, tables > 100 GB"},
+                       "l2_policy": f"inputs larger than L2: {args.pool} distinct batches cycled, tables > 100 GB",
+                       "timed_loop": "TrainPipelineSparseDist.progress over device-resident batches" if args.loop == "pipeline" else "plain forward/backward/optimizer loop"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "diagnostics": {"host_issue_ms_per_step": host_issue_ms},
             "emb_a2a": {"fwd_bytes_per_step_busiest_rank": exchange_bytes, "bwd_bytes_per_step_busiest_rank": exchange_bytes,
                         "GBps_lower_bound": (2 * exchange_bytes / (ms_per_step / 1e3) / 1e9) if world > 1 else 0.0,
                         "note": "algorithmic bytes of the embedding exchange over the whole step time; the exchange is fused into the lookup kernels, so it has no time of its own"},
         }
-        print(json.dumps(res))
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps(res), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -14,7 +14,7 @@ Counterpart of ``torchrec/distributed/dist_data.py`` (splits ``:220-291``, tenso
 from __future__ import annotations
 
 import itertools
-from typing import Callable, Dict, List, Optional
+from typing import Any, Callable, Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -49,6 +49,24 @@ def _get_recat(
     """
     if local_split == 0:
         return None
+    vb_key = tuple(batch_size_per_rank) if batch_size_per_rank is not None and any(bs != batch_size_per_rank[0] for bs in batch_size_per_rank) else None
+    cache_key = (local_split, num_splits, stagger, str(device), vb_key)
+    cached = _RECAT_CACHE.get(cache_key)
+    if cached is not None:
+        return cached
+    out = _build_recat(local_split, num_splits, stagger, device, batch_size_per_rank)
+    if len(_RECAT_CACHE) >= 256:
+        _RECAT_CACHE.clear()
+    _RECAT_CACHE[cache_key] = out
+    return out
+
+
+# Building the permutation on the device is a host-to-device copy from pageable memory, which stalls the host until the stream
+# has drained; the permutation only depends on the layout of the exchange, so it is built once per layout.
+_RECAT_CACHE: Dict[Tuple[Any, ...], torch.Tensor] = {}
+
+
+def _build_recat(local_split: int, num_splits: int, stagger: int, device: Optional[torch.device], batch_size_per_rank: Optional[List[int]]) -> torch.Tensor:
     feature_order = [x + num_splits // stagger * y for x in range(num_splits // stagger) for y in range(stagger)]
     recat = [i + j * local_split for i in range(local_split) for j in feature_order]
     vb = batch_size_per_rank is not None and any(bs != batch_size_per_rank[0] for bs in batch_size_per_rank)
