@@ -105,6 +105,8 @@ def _run(rank, world_size, pooling_name):
         torch.cuda.synchronize()
         for m in lookups:
             m._peer.check_error()
+        # the tables were placed out of order, so the exchange stored them at their final columns instead of permuting afterwards
+        assert all(m._peer_feature_columns is not None for m in lookups)
         sd_r, sd_f = ref.state_dict(), fused.state_dict()
         for name, vr in sd_r.items():
             vf = sd_f[name]

@@ -172,15 +172,16 @@ class _PeerPushLookup(torch.autograd.Function):
         total_D = lookup._peer_total_D
         groups = features.split(lookup._feature_splits) if len(lookup._emb_modules) > 1 else [features]
         col = lookup._peer_col_base
+        layout = lookup._peer_feature_columns  # per module: the final column of every feature, or None (rank-major blocks)
         saved = []
-        for config, emb_op, f in zip(lookup.grouped_configs, lookup._emb_modules, groups):
+        for gi, (config, emb_op, f) in enumerate(zip(lookup.grouped_configs, lookup._emb_modules, groups)):
             tbe = emb_op.emb_module
             psw = f.weights_or_none() if config.is_weighted else None
             if psw is not None and not torch.is_floating_point(psw):
                 psw = None
             if psw is not None and psw.dtype != torch.float32:
                 psw = psw.float()
-            tbe.forward_push(f.values(), f.offsets(), psw, B, B_local, out_ptrs, total_D, col, out.dtype)
+            tbe.forward_push(f.values(), f.offsets(), psw, B, B_local, out_ptrs, total_D, col if layout is None else layout[gi], out.dtype)
             # the id sort of the backward starts now, on the side stream, under the dense towers
             saved.append((f.values(), f.offsets(), psw, tbe.build_plan_ahead(f.values(), f.offsets(), psw, B) if torch.is_grad_enabled() else None))
             col += tbe.total_D
@@ -189,6 +190,7 @@ class _PeerPushLookup(torch.autograd.Function):
         ctx.saved = saved
         ctx.B = B
         ctx.B_local = B_local
+        ctx.layout = layout
         return out
 
     @staticmethod
@@ -202,9 +204,9 @@ class _PeerPushLookup(torch.autograd.Function):
         peer.barrier()
         scale = 1.0 / peer.world if comm_ops.get_gradient_division() else 1.0
         col = lookup._peer_col_base
-        for emb_op, (idx, off, psw, plan) in zip(lookup._emb_modules, ctx.saved):
+        for gi, (emb_op, (idx, off, psw, plan)) in enumerate(zip(lookup._emb_modules, ctx.saved)):
             tbe = emb_op.emb_module
-            tbe.backward_pull(g, g_ptrs, lookup._peer_total_D, idx, off, psw, ctx.B, ctx.B_local, col, scale, plan)
+            tbe.backward_pull(g, g_ptrs, lookup._peer_total_D, idx, off, psw, ctx.B, ctx.B_local, col if ctx.layout is None else ctx.layout[gi], scale, plan)
             col += tbe.total_D
         ctx.saved = None
         return None, None, None
@@ -229,6 +231,7 @@ class GroupedPooledEmbeddingsLookup(_GroupedLookupBase):
         self._peer = None  # PeerGroup when the fused lookup + exchange is on
         self._peer_total_D = 0
         self._peer_col_base = 0
+        self._peer_feature_columns: Optional[List[List[int]]] = None
         self._peer_dtype = torch.float32
         self._peer_bufs: Dict[str, Any] = {}
         self._peer_step = 0
@@ -243,6 +246,21 @@ class GroupedPooledEmbeddingsLookup(_GroupedLookupBase):
         self._peer_col_base = int(sum(dim_sum_per_rank[: peer.rank]))
         self._peer_dtype = dtype
         self._peer_anchor = torch.zeros(1, requires_grad=True)
+
+    def set_peer_output_layout(self, column_of_embedding: Dict[str, int]) -> bool:
+        """Store every table's pooled columns at their final place of the exchanged row (``column_of_embedding``: embedding name ->
+        first column in the unsharded module's output) instead of in rank-major blocks, which saves the column permute (a full copy
+        of the output forward and of its gradient backward).  Returns whether the layout was taken."""
+        if self._peer is None:
+            return False
+        cols: List[List[int]] = []
+        for config in self.grouped_configs:
+            names = config.embedding_names()
+            if any(n not in column_of_embedding for n in names):
+                return False
+            cols.append([int(column_of_embedding[n]) for n in names])
+        self._peer_feature_columns = cols
+        return True
 
     def _peer_out_buffer(self, B_local: int):
         key = f"out{self._peer_step % 2}"
@@ -276,6 +294,7 @@ class GroupedPooledEmbeddingsLookup(_GroupedLookupBase):
         if self._can_push(sparse_features):
             out = _PeerPushLookup.apply(self._peer_anchor, self, sparse_features)
             out._trb_exchanged = True  # tells the output dist that the rows are already where they belong
+            out._trb_final_layout = self._peer_feature_columns is not None  # ... and the columns in the unsharded module's order
             return out
         if len(self._emb_modules) == 0:
             return self._dummy_embs_tensor.view(sparse_features.stride(), 0) if sparse_features.stride() else self._dummy_embs_tensor

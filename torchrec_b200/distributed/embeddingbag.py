@@ -551,9 +551,19 @@ class ShardedEmbeddingBagCollection(
             from torchrec_b200.distributed.sharding.cw_sharding import PermutePooledEmbeddingsSplit
 
             order = [self._embedding_names.index(n) for n in wanted]
+            self._pre_names, self._pre_dims = list(self._embedding_names), list(self._embedding_dims)
             self._permute_op = PermutePooledEmbeddingsSplit(self._embedding_dims, order, device=self._device)
             self._embedding_names = wanted
             self._embedding_dims = [self._embedding_dims[i] for i in order]
+            # a single table-wise sharding on the fused exchange path can store every table at its final column right away
+            if len(self._embedding_shardings) == 1 and len(set(self._pre_names)) == len(self._pre_names):
+                column, acc = {}, 0
+                for n, d in zip(self._embedding_names, self._embedding_dims):
+                    column[n] = acc
+                    acc += d
+                lk = self._lookups[0].module if isinstance(self._lookups[0], DistributedDataParallel) else self._lookups[0]
+                if hasattr(lk, "set_peer_output_layout"):
+                    lk.set_peer_output_layout(column)
 
     def _init_mean_pooling_callback(self, input_feature_names: List[str]) -> None:
         keys = [input_feature_names[i] for i in self._features_order] if self._features_order else list(input_feature_names)
@@ -646,7 +656,13 @@ class ShardedEmbeddingBagCollection(
         )
         if self._permute_op is not None:
             permute_op, names, dims = self._permute_op, self._embedding_names, self._embedding_dims
-            awaitable.callbacks.append(lambda kt: KeyedTensor(keys=names, length_per_key=dims, values=permute_op(kt.values()), key_dim=1))
+
+            def to_module_order(kt: KeyedTensor) -> KeyedTensor:
+                v = kt.values()
+                # the fused exchange may already have stored the columns in the module's order
+                return KeyedTensor(keys=names, length_per_key=dims, values=v if getattr(v, "_trb_final_layout", False) else permute_op(v), key_dim=1)
+
+            awaitable.callbacks.append(to_module_order)
         if self._has_mean_pooling_callback and ctx.divisor is not None:
             divisor = ctx.divisor
             awaitable.callbacks.append(lambda kt: _apply_mean_pooling(kt, divisor))

@@ -417,18 +417,24 @@ class TableBatchedEmbeddingBags(nn.Module):
         return self._backward_cpu(w, grad_out, indices, offsets, psw, B)
 
     # ---- fused lookup + exchange over peer-mapped buffers (one node, NVLink) ---------------------------
-    def _meta_tensor_at(self, device: torch.device, col_base: int) -> torch.Tensor:
-        """Metadata whose output column offsets start at ``col_base`` (this rank's block of the exchanged row)."""
+    def _meta_tensor_at(self, device: torch.device, col_base) -> torch.Tensor:
+        """Metadata whose output column offsets start at ``col_base`` (this rank's block of the exchanged row), or, when
+        ``col_base`` is a sequence, are exactly those per-feature columns (tables stored at their final place in the row)."""
         cache = self.__dict__.setdefault("_meta_at", {})
-        key = (str(device), int(col_base))
+        absolute = not isinstance(col_base, int)
+        key = (str(device), tuple(int(c) for c in col_base) if absolute else int(col_base))
         if key not in cache:
             m = self._meta_tensor(device).clone()
-            m[4] += int(col_base)
+            if absolute:
+                assert len(col_base) == m.shape[1], "one output column per feature"
+                m[4] = torch.tensor([int(c) for c in col_base], dtype=m.dtype, device=m.device)
+            else:
+                m[4] += int(col_base)
             cache[key] = m
         return cache[key]
 
     def forward_push(self, indices: torch.Tensor, offsets: torch.Tensor, psw: Optional[torch.Tensor], B: int, B_local: int,
-                     out_ptrs: List[int], out_stride: int, col_base: int, out_dtype: torch.dtype) -> None:
+                     out_ptrs: List[int], out_stride: int, col_base, out_dtype: torch.dtype) -> None:
         """Pooled lookup of the global batch (``B`` bags per feature) whose result rows are stored directly into the
         ``[B_local, out_stride]`` buffers of the ranks that own the samples (``out_ptrs[b // B_local]``), at column
         ``col_base`` + the table's offset.  No output tensor: the caller synchronises with a peer barrier."""
@@ -442,7 +448,7 @@ class TableBatchedEmbeddingBags(nn.Module):
         )
 
     def backward_pull(self, grad_local: torch.Tensor, grad_ptrs: List[int], grad_stride: int, indices: torch.Tensor, offsets: torch.Tensor,
-                      psw: Optional[torch.Tensor], B: int, B_local: int, col_base: int, grad_scale: float, plan: Optional[TBEPlan] = None) -> None:
+                      psw: Optional[torch.Tensor], B: int, B_local: int, col_base, grad_scale: float, plan: Optional[TBEPlan] = None) -> None:
         """Backward + fused optimizer of ``forward_push``: the gradient row of bag ``b`` is read from
         ``grad_ptrs[b // B_local]`` (``grad_local`` is this rank's own buffer among them)."""
         assert self.fused, "the fused exchange is for tables with an in-backward optimizer"
