@@ -87,14 +87,21 @@ def _build_recat(local_split: int, num_splits: int, stagger: int, device: Option
 class SplitsAllToAllAwaitable(Awaitable[List[List[int]]]):
     """All-to-all of the per-destination split sizes; ``wait()`` returns them as Python lists."""
 
-    def __init__(self, input_tensors: List[torch.Tensor], pg: dist.ProcessGroup) -> None:
+    def __init__(self, input_tensors, pg: dist.ProcessGroup, device: Optional[torch.device] = None) -> None:
+        """``input_tensors``: one ``[world]`` tensor per quantity, or (cheaper) one Python list per quantity together with ``device``:
+        the lists are interleaved on the host and cross to the device in a single copy."""
         super().__init__()
         self.num_workers: int = pg.size()
         with record_function("## all2all_data:kjt splits ##"):
-            self._output_tensor = torch.empty(
-                [self.num_workers * len(input_tensors)], device=input_tensors[0].device, dtype=input_tensors[0].dtype
-            )
-            input_tensor = torch.stack(input_tensors, dim=1).flatten()
+            if len(input_tensors) > 0 and not isinstance(input_tensors[0], torch.Tensor):
+                flat = [int(s[w]) for w in range(self.num_workers) for s in input_tensors]
+                input_tensor = torch.tensor(flat, dtype=torch.int64, device=device)
+                self._output_tensor = torch.empty_like(input_tensor)
+            else:
+                self._output_tensor = torch.empty(
+                    [self.num_workers * len(input_tensors)], device=input_tensors[0].device, dtype=input_tensors[0].dtype
+                )
+                input_tensor = torch.stack(input_tensors, dim=1).flatten()
             self._splits_awaitable = dist.all_to_all_single(output=self._output_tensor, input=input_tensor, group=pg, async_op=True)
 
     def _wait_impl(self) -> List[List[int]]:
@@ -191,10 +198,10 @@ class KJTAllToAllSplitsAwaitable(Awaitable[KJTAllToAllTensorsAwaitable]):
         self._launch_splits_exchange()
 
     def _launch_splits_exchange(self) -> None:
-        input_tensors_ = [torch.tensor(s, device=self._device) for s in self._input_splits]
+        lists = [list(s) for s in self._input_splits]
         if not self._input.variable_stride_per_key():
-            input_tensors_.append(torch.tensor([self._input.stride()] * self._workers, device=self._device))
-        self._splits_awaitable = SplitsAllToAllAwaitable(input_tensors_, self._pg)
+            lists.append([self._input.stride()] * self._workers)
+        self._splits_awaitable = SplitsAllToAllAwaitable(lists, self._pg, device=self._device)
 
     def _wait_impl(self) -> KJTAllToAllTensorsAwaitable:
         if self._workers > 1:

@@ -272,7 +272,7 @@ class FusedKJTListSplitsAwaitable(Awaitable[List[KJTListAwaitable]]):
             device = w._device
         self._splits_awaitable = None
         if splits and pg is not None and pg.size() > 1:
-            self._splits_awaitable = SplitsAllToAllAwaitable([torch.tensor(s, device=device) for s in splits], pg)
+            self._splits_awaitable = SplitsAllToAllAwaitable([list(s) for s in splits], pg, device=device)
         self._flat_splits = splits
 
     def _wait_impl(self) -> List[KJTListAwaitable]:
