@@ -1,0 +1,76 @@
+"""fused_params keys, the width bucketer, inference introspection helpers and the package version."""
+import torch
+from torch import nn
+
+from torchrec_b200.distributed import fused_params as fp
+from torchrec_b200.distributed.embedding_dim_bucketer import EmbDimBucketer, EmbDimBucketerPolicy
+from torchrec_b200.distributed.infer_utils import get_all_torchrec_modules, get_non_scriptable_trec_module, get_path_device_tuples
+from torchrec_b200.modules.embedding_configs import DataType, EmbeddingBagConfig
+from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
+
+
+def test_version():
+    import torchrec_b200.version as v
+
+    assert v.__version__.count(".") == 2
+
+
+def test_fused_params_helpers():
+    params = {fp.FUSED_PARAM_REGISTER_TBE_BOOL: True, fp.FUSED_PARAM_TBE_ROW_ALIGNMENT: 16, fp.FUSED_PARAM_LENGTHS_TO_OFFSETS_LOOKUP: True,
+              fp.FUSED_PARAM_SSD_TABLE_LIST: ["t"], "learning_rate": 0.1, "cache_load_factor": 0.2}
+    assert fp.is_fused_param_register_tbe(params) and not fp.is_fused_param_register_tbe(None) and not fp.is_fused_param_register_tbe({})
+    assert fp.get_fused_param_tbe_row_alignment(params) == 16 and fp.get_fused_param_tbe_row_alignment({}) is None
+    assert fp.fused_param_lengths_to_offsets_lookup(params) and not fp.fused_param_lengths_to_offsets_lookup(None)
+    assert fp.fused_param_bounds_check_mode(params) is None
+    assert not fp.is_fused_param_quant_state_dict_split_scale_bias(params)
+    assert fp.tbe_fused_params(params) == {"learning_rate": 0.1, "cache_load_factor": 0.2}
+    assert fp.tbe_fused_params(None) is None and fp.tbe_fused_params({}) is None
+
+    class Lookup(nn.Module, fp.TBEToRegisterMixIn):
+        def __init__(self):
+            super().__init__()
+            self.k = nn.Identity()
+
+        def get_tbes_to_register(self):
+            return {self.k: "cfg"}
+
+    lk = Lookup()
+    assert fp.get_tbes_to_register_from_iterable([nn.Linear(1, 1), lk]) == {lk.k: "cfg"}
+
+
+class _T:
+    def __init__(self, cols, dt=DataType.FP32):
+        self.local_cols, self.data_type = cols, dt
+
+
+def test_dim_bucketer_policies():
+    tables = [_T(16), _T(32), _T(48), _T(64), _T(32), _T(64, DataType.FP16), _T(256)]
+    one = EmbDimBucketer(tables, EmbDimBucketerPolicy.SINGLE_BUCKET)
+    assert one.bucket_count() == 1 and one.get_bucket(256, DataType.FP32) == 0
+    every = EmbDimBucketer(tables, EmbDimBucketerPolicy.ALL_BUCKETS)
+    # byte widths: 64, 128, 192, 256, 128, 128, 1024 -> 5 distinct
+    assert every.bucket_count() == 5
+    assert every.get_bucket(32, DataType.FP32) == every.get_bucket(64, DataType.FP16)
+    line = EmbDimBucketer(tables, EmbDimBucketerPolicy.CACHELINE_BUCKETS)
+    # 128-byte line counts: 0, 1, 1, 2, 1, 1, 8 -> 4 groups
+    assert line.bucket_count() == 4
+    assert line.get_bucket(32, DataType.FP32) == line.get_bucket(48, DataType.FP32) != line.get_bucket(64, DataType.FP32)
+
+
+def test_infer_utils_module_search_and_devices():
+    ebc = EmbeddingBagCollection(tables=[EmbeddingBagConfig(name="t", embedding_dim=8, num_embeddings=10, feature_names=["f"])])
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.sparse = nn.Sequential(ebc)
+            self.dense = nn.Linear(4, 2)
+            self.extra = [torch.zeros(2)]
+
+    net = Net()
+    found = get_all_torchrec_modules(net)
+    assert list(found) == ["sparse.0"] and found["sparse.0"] is ebc
+    assert get_non_scriptable_trec_module(net) == {}
+    paths = dict(get_path_device_tuples(net))
+    assert paths["dense.weight"] == "cpu" and paths["extra[0]"] == "cpu"
+    assert any(p.startswith("sparse.0.embedding_bags.t") for p in paths)
