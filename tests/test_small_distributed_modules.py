@@ -74,3 +74,26 @@ def test_infer_utils_module_search_and_devices():
     paths = dict(get_path_device_tuples(net))
     assert paths["dense.weight"] == "cpu" and paths["extra[0]"] == "cpu"
     assert any(p.startswith("sparse.0.embedding_bags.t") for p in paths)
+
+
+def test_quant_utils_fx_names_and_meta_to_cpu():
+    from torchrec_b200.modules.embedding_configs import DataType as DT
+    from torchrec_b200.quant.embedding_modules import EmbeddingBagCollection as QEBC
+    from torchrec_b200.quant.utils import meta_to_cpu_placement, recursive_populate_fx_names
+
+    tables = [EmbeddingBagConfig(name="a", embedding_dim=8, num_embeddings=10, feature_names=["fa"], data_type=DT.INT8),
+              EmbeddingBagConfig(name="b", embedding_dim=8, num_embeddings=10, feature_names=["fb"], data_type=DT.INT8)]
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q = QEBC(tables, is_weighted=False, device=torch.device("meta"))
+            self.keep = QEBC(tables, is_weighted=False, device=torch.device("cpu"))
+
+    net = Net()
+    old_q, old_keep = net.q, net.keep
+    recursive_populate_fx_names(net)
+    assert old_q._emb_modules[0]._fx_path == "emb_module.a,b"
+    meta_to_cpu_placement(net)
+    assert net.q is not old_q and net.keep is old_keep
+    assert net.q.device.type == "cpu" and [c.name for c in net.q.embedding_bag_configs()] == ["a", "b"]
