@@ -39,6 +39,7 @@ from torchrec_b200.distributed.train_pipeline.runtime_forwards import (
 from torchrec_b200.distributed.train_pipeline.types import CallArgs, PipelineState
 from torchrec_b200.distributed.train_pipeline.utils import (
     ArgRecorder,
+    find_postproc_candidates,
     DataLoadingThread,
     In,
     Out,
@@ -210,6 +211,7 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
         self._pipelined_forwards: Dict[str, Any] = {}
         self._call_args: Dict[str, CallArgs] = {}
         self._recorder: Optional[ArgRecorder] = None
+        self._pipelined_postprocs: Dict[str, Any] = {}
         self._batch_i: Optional[In] = None
         self._batch_ip1: Optional[In] = None
         self._batch_ip2: Optional[In] = None
@@ -271,6 +273,8 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
     def _set_module_context(self, context: TrainPipelineContext) -> None:
         for fwd in self._pipelined_forwards.values():
             fwd.set_context(context)
+        for pp in self._pipelined_postprocs.values():
+            pp.set_context(context)
 
     # ---- pipelining the model --------------------------------------------------------------------------
     def _make_forward(self, name: str, module: ShardedModule, call_args: CallArgs, context: TrainPipelineContext):
@@ -278,7 +282,8 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
 
     def _install_recorder(self) -> None:
         self._all_sharded = find_sharded_modules(self._model)
-        self._recorder = ArgRecorder(self._all_sharded)
+        candidates = find_postproc_candidates(self._model, self._all_sharded) if self._pipeline_postproc else None
+        self._recorder = ArgRecorder(self._all_sharded, candidates)
 
     def _pipeline_model(self, batch: In, context: TrainPipelineContext) -> None:
         """After the first (unpipelined) forward: resolve where every sharded module's inputs live in the
@@ -286,7 +291,11 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
         assert self._recorder is not None
         self._call_args = self._recorder.resolve(batch)
         self._recorder.remove()
+        self._pipelined_postprocs = dict(self._recorder.postprocs)
         self._recorder = None
+        self._swap_postprocs(install=True)
+        for pp in self._pipelined_postprocs.values():
+            pp.set_context(context)
         for name, ca in self._call_args.items():
             module = self._all_sharded[name]
             self._pipelined_modules[name] = module
@@ -299,9 +308,17 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
                     m.defer_splits_exchange = True
         self._pipelined = True
 
+    def _swap_postprocs(self, install: bool) -> None:
+        """Put the pipelined post-processing wrappers into the model in place of the modules they wrap, or take them out."""
+        for fqn, pp in self._pipelined_postprocs.items():
+            parent_name, _, child = fqn.rpartition(".")
+            parent = self._model.get_submodule(parent_name) if parent_name else self._model
+            setattr(parent, child, pp if install else pp.postproc_module)
+
     def detach(self) -> torch.nn.Module:
         """Restore the original forwards so the model can be used outside the pipeline."""
         if self._pipelined:
+            self._swap_postprocs(install=False)
             for name, module in self._pipelined_modules.items():
                 module.forward = self._original_forwards[name]  # type: ignore[assignment]
                 for m in module.modules():
@@ -316,6 +333,7 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
             self._model = model
         self._model_attached = True
         if self._pipelined_forwards and not self._pipelined:
+            self._swap_postprocs(install=True)
             for name, module in self._pipelined_modules.items():
                 module.forward = self._pipelined_forwards[name]  # type: ignore[assignment]
                 for m in module.modules():

@@ -99,14 +99,37 @@ def _find_path(root: Any, target: Any, max_depth: int = 4) -> Optional[ArgInfo]:
     return rec(root, [], [], 0)
 
 
-class ArgRecorder:
-    """Pre-forward hooks on the sharded modules that remember the first call's arguments."""
+def find_postproc_candidates(model: torch.nn.Module, sharded: Dict[str, ShardedModule]) -> Dict[str, torch.nn.Module]:
+    """Modules that may run ahead of the model forward as input post-processing: not the root, not a sharded module nor inside
+    one, not a container of one, and without trainable parameters (running a trained module a batch early would read stale
+    weights)."""
+    out: Dict[str, torch.nn.Module] = {}
+    sharded_names = list(sharded.keys())
+    for name, m in model.named_modules():
+        if name == "" or isinstance(m, ShardedModule):
+            continue
+        if any(s == name or s.startswith(name + ".") or name.startswith(s + ".") for s in sharded_names):
+            continue
+        if any(p.requires_grad for p in m.parameters()):
+            continue
+        out[name] = m
+    return out
 
-    def __init__(self, modules: Dict[str, ShardedModule]) -> None:
+
+class ArgRecorder:
+    """Hooks that remember the first call of every sharded module (its arguments) and, when post-processing modules are to be
+    pipelined too, of every candidate post-processing module (arguments and output)."""
+
+    def __init__(self, modules: Dict[str, ShardedModule], postproc_candidates: Optional[Dict[str, torch.nn.Module]] = None) -> None:
         self.calls: Dict[str, Tuple[Tuple[Any, ...], Dict[str, Any]]] = {}
+        self.postproc_calls: Dict[str, Tuple[Tuple[Any, ...], Dict[str, Any], Any]] = {}
+        self.postproc_modules: Dict[str, torch.nn.Module] = dict(postproc_candidates or {})
+        self.postprocs: Dict[str, Any] = {}  # fqn -> PipelinedPostproc, filled by resolve()
         self._handles = []
         for name, m in modules.items():
             self._handles.append(m.register_forward_pre_hook(self._make_hook(name), with_kwargs=True))
+        for name, m in self.postproc_modules.items():
+            self._handles.append(m.register_forward_hook(self._make_postproc_hook(name), with_kwargs=True))
 
     def _make_hook(self, name: str):
         def hook(module, args, kwargs):
@@ -116,30 +139,65 @@ class ArgRecorder:
 
         return hook
 
+    def _make_postproc_hook(self, name: str):
+        def hook(module, args, kwargs, output):
+            if name not in self.postproc_calls:
+                self.postproc_calls[name] = (args, dict(kwargs), output)
+            return None
+
+        return hook
+
     def remove(self) -> None:
         for h in self._handles:
             h.remove()
         self._handles = []
 
+    def _locate(self, batch: Any, value: Any, depth: int = 0) -> Optional[ArgInfo]:
+        """Where ``value`` comes from: a literal, the batch, or the output of a post-processing module whose own inputs can be
+        located the same way."""
+        if isinstance(value, (int, float, str, bool, type(None))):
+            return ArgInfo(constant=(value,))
+        found = _find_path(batch, value)
+        if found is not None or depth > 4:
+            return found
+        from torchrec_b200.distributed.train_pipeline.postproc import PipelinedPostproc
+
+        for name, (args, kwargs, output) in self.postproc_calls.items():
+            inside = _find_path(output, value)
+            if inside is None:
+                continue
+            pp = self.postprocs.get(name)
+            if pp is None:
+                call = self._locate_all(batch, args, kwargs, depth + 1)
+                if call is None:
+                    continue
+                pp = PipelinedPostproc(self.postproc_modules[name], name, call)
+                self.postprocs[name] = pp
+            inside.postproc = pp
+            return inside
+        return None
+
+    def _locate_all(self, batch: Any, args: Tuple[Any, ...], kwargs: Dict[str, Any], depth: int = 0) -> Optional[CallArgs]:
+        ca = CallArgs()
+        for a in args:
+            p = self._locate(batch, a, depth)
+            if p is None:
+                return None
+            ca.args.append(p)
+        for k, a in kwargs.items():
+            p = self._locate(batch, a, depth)
+            if p is None:
+                return None
+            ca.kwargs[k] = p
+        return ca
+
     def resolve(self, batch: Any) -> Dict[str, CallArgs]:
-        """Accessor paths for every recorded module whose arguments all come straight from the batch."""
+        """Accessor paths for every recorded sharded module whose arguments all come from the batch, directly or through
+        post-processing modules."""
         out: Dict[str, CallArgs] = {}
         for name, (args, kwargs) in self.calls.items():
-            ok = True
-            ca = CallArgs()
-            for a in args:
-                p = _find_path(batch, a)
-                if p is None:
-                    ok = False
-                    break
-                ca.args.append(p)
-            for k, a in kwargs.items():
-                p = _find_path(batch, a)
-                if p is None:
-                    ok = False
-                    break
-                ca.kwargs[k] = p
-            if ok:
+            ca = self._locate_all(batch, args, kwargs)
+            if ca is not None:
                 out[name] = ca
             else:
                 logger.warning(f"train pipeline: inputs of sharded module '{name}' are computed inside the model; it will not be pipelined")
@@ -158,7 +216,7 @@ def _start_data_dist(pipelined_modules: Dict[str, ShardedModule], call_args: Dic
         ca = call_args.get(name)
         if ca is None:
             continue
-        args, kwargs = ca.build_args_kwargs(batch)
+        args, kwargs = ca.build_args_kwargs(batch, context)
         module_ctx = module.create_context()
         if context.version == 0:
             context.module_contexts_next_batch[name] = module_ctx
@@ -269,7 +327,9 @@ class DataLoadingThread(threading.Thread, Generic[In]):
 
 
 def use_context_for_postprocs(module: torch.nn.Module, context: TrainPipelineContext) -> None:
-    """Point every pipelined post-processing module at the context of the batch about to be processed."""
+    """Point every pipelined post-processing module at the context of the batch whose forward is about to run."""
+    from torchrec_b200.distributed.train_pipeline.postproc import PipelinedPostproc
+
     for m in module.modules():
-        if hasattr(m, "set_context") and type(m).__name__ == "PipelinedPostproc":
+        if isinstance(m, PipelinedPostproc):
             m.set_context(context)
