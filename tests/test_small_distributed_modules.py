@@ -97,3 +97,33 @@ def test_quant_utils_fx_names_and_meta_to_cpu():
     meta_to_cpu_placement(net)
     assert net.q is not old_q and net.keep is old_keep
     assert net.q.device.type == "cpu" and [c.name for c in net.q.embedding_bag_configs()] == ["a", "b"]
+
+
+def test_grouped_position_weighted_module():
+    from torchrec_b200.distributed.grouped_position_weighted import GroupedPositionWeightedModule
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    m = GroupedPositionWeightedModule({"a": 3, "c": 2})
+    with torch.no_grad():
+        m.position_weights["a"].copy_(torch.tensor([1.0, 2.0, 3.0]))
+        m.position_weights["c"].copy_(torch.tensor([10.0, 20.0]))
+    kjt = KeyedJaggedTensor.from_lengths_sync(keys=["a", "b", "c"], values=torch.arange(10), lengths=torch.tensor([3, 1, 2, 0, 1, 3]))
+    out = m(kjt)
+    # a: bags [0,1,2],[0]; b: [0,1],[]; c: [0],[0,1,2 -> clamped to 1]
+    torch.testing.assert_close(out.weights(), torch.tensor([1.0, 2.0, 3.0, 1.0, 1.0, 1.0, 10.0, 10.0, 20.0, 20.0]))
+    out.weights().sum().backward()
+    torch.testing.assert_close(m.position_weights["a"].grad, torch.tensor([2.0, 1.0, 1.0]))
+    torch.testing.assert_close(m.position_weights["c"].grad, torch.tensor([2.0, 2.0]))
+    assert sorted(m.state_dict()) == ["position_weights.a", "position_weights.c"]
+    assert [n for n, _ in m.named_parameters("fp")] == ["fp.position_weights.a", "fp.position_weights.c"]
+    # positions carried as weights (as after a row-wise input dist) are used instead of the offsets
+    carried = KeyedJaggedTensor.from_lengths_sync(keys=["a"], values=torch.arange(2), lengths=torch.tensor([2]), weights=torch.tensor([2.0, 0.0]))
+    torch.testing.assert_close(m(carried).weights(), torch.tensor([3.0, 1.0]))
+
+
+def test_alias_import_paths():
+    from torchrec_b200.distributed.batched_embedding_kernel import TableBatchedEmbeddingSlice as A
+    from torchrec_b200.distributed.composable.table_batched_embedding_slice import TableBatchedEmbeddingSlice as B
+    from torchrec_b200.distributed.embedding_kernel import BaseEmbedding, get_state_dict  # noqa: F401
+
+    assert A is B
