@@ -127,3 +127,25 @@ def test_alias_import_paths():
     from torchrec_b200.distributed.embedding_kernel import BaseEmbedding, get_state_dict  # noqa: F401
 
     assert A is B
+
+
+def test_sharded_tbes_weights_spec():
+    from torchrec_b200.distributed.quant_embeddingbag import ShardedQuantEmbeddingBagCollection
+    from torchrec_b200.distributed.quant_state import WeightSpec, get_param_id_from_type, sharded_tbes_weights_spec
+    from torchrec_b200.distributed.types import ParameterSharding, ShardingEnv
+    from torchrec_b200.modules.embedding_configs import DataType as DT
+    from torchrec_b200.quant.embedding_modules import EmbeddingBagCollection as QEBC
+
+    tables = [EmbeddingBagConfig(name="a", embedding_dim=8, num_embeddings=10, feature_names=["fa"], data_type=DT.INT8),
+              EmbeddingBagConfig(name="b", embedding_dim=16, num_embeddings=20, feature_names=["fb"], data_type=DT.INT4)]
+    q = QEBC(tables, is_weighted=False, device=torch.device("cpu"))
+    sharding = {"a": ParameterSharding(sharding_type="table_wise", compute_kernel="quant", ranks=[0]),
+                "b": ParameterSharding(sharding_type="table_wise", compute_kernel="quant", ranks=[1])}
+    sharded = ShardedQuantEmbeddingBagCollection(q, sharding, ShardingEnv.from_local(world_size=2, rank=0), device=torch.device("cpu"))
+    net = nn.Sequential(sharded)
+    spec = sharded_tbes_weights_spec(net)
+    assert spec["0.tbes.0.0.a.weight"] == WeightSpec("0.embedding_bags.a.weight", [0, 0], [10, 8], "table_wise")
+    assert spec["0.tbes.1.0.b.weight"].shard_sizes == [20, 8]
+    assert spec["0.tbes.1.0.b.weight_qscale"].fqn == "0.embedding_bags.b.weight_qscale" and spec["0.tbes.1.0.b.weight_qbias"].shard_sizes == [20, 2]
+    assert len(spec) == 6
+    assert get_param_id_from_type(True, False, False) == "embedding_bags" and get_param_id_from_type(False, False, False) == "embeddings"
