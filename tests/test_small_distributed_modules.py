@@ -149,3 +149,19 @@ def test_sharded_tbes_weights_spec():
     assert spec["0.tbes.1.0.b.weight_qscale"].fqn == "0.embedding_bags.b.weight_qscale" and spec["0.tbes.1.0.b.weight_qbias"].shard_sizes == [20, 2]
     assert len(spec) == 6
     assert get_param_id_from_type(True, False, False) == "embedding_bags" and get_param_id_from_type(False, False, False) == "embeddings"
+
+
+def test_infer_pool_sharding_single_process():
+    from torchrec_b200.distributed.sharding.rw_tensor_pool_sharding import InferRwTensorPoolSharding
+    from torchrec_b200.distributed.types import ShardingEnv
+
+    sharding = InferRwTensorPoolSharding(pool_size=10, env=ShardingEnv.from_local(world_size=3, rank=0), device=torch.device("cpu"))
+    assert sharding.local_pool_size_per_rank == [4, 4, 2]
+    pool = torch.arange(10.0).unsqueeze(1).repeat(1, 2)
+    shards = [pool[0:4], pool[4:8], pool[8:10]]
+    ids_dist = sharding.create_lookup_ids_dist()
+    ids = torch.tensor([9, 0, 5, 4, 3, 8])
+    parts = ids_dist(ids)
+    assert [p.tolist() for p in parts] == [[0, 3], [1, 0], [1, 0]]
+    out = sharding.create_lookup_values_dist()([s.index_select(0, p) for s, p in zip(shards, parts)], ids_dist.unbucketize_permute)
+    assert torch.equal(out, pool.index_select(0, ids))

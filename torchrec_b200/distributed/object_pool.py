@@ -16,48 +16,28 @@ from torchrec_b200.modules.tensor_pool import TensorPool
 from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
 
 
-class _RwRouter:
-    """Id routing shared by the pools: block size, per-rank counts and the permutation that groups ids by owner."""
-
-    def __init__(self, pool_size: int, env: ShardingEnv) -> None:
-        self.world, self.rank, self.pg = env.world_size, env.rank, env.process_group
-        self.block = (pool_size + self.world - 1) // self.world
-        self.local_rows = max(0, min(self.block, pool_size - self.rank * self.block))
-
-    def route(self, ids: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, List[int], List[int]]:
-        """``(order, local ids received here, send counts, receive counts)``; ``ids[order]`` is grouped by owner."""
-        ids = ids.long()
-        owner = torch.div(ids, self.block, rounding_mode="floor").clamp(max=self.world - 1)
-        order = torch.argsort(owner, stable=True)
-        send = torch.bincount(owner, minlength=self.world)
-        recv = torch.empty_like(send)
-        dist.all_to_all_single(recv, send, group=self.pg)
-        send_l, recv_l = send.tolist(), recv.tolist()
-        got = torch.empty(sum(recv_l), dtype=torch.int64, device=ids.device)
-        dist.all_to_all_single(got, ids.index_select(0, order).contiguous(), output_split_sizes=recv_l, input_split_sizes=send_l, group=self.pg)
-        return order, got - self.rank * self.block, send_l, recv_l
-
-    def exchange(self, payload: torch.Tensor, in_splits: List[int], out_splits: List[int]) -> torch.Tensor:
-        out = torch.empty((sum(out_splits),) + tuple(payload.shape[1:]), dtype=payload.dtype, device=payload.device)
-        dist.all_to_all_single(out, payload.contiguous(), output_split_sizes=out_splits, input_split_sizes=in_splits, group=self.pg)
-        return out
-
-
 class ShardedTensorPool(nn.Module):
+    """``TensorPool`` whose rows live on their owning rank (row-wise) or on every rank (replicated).  ``update`` / ``lookup`` run
+    the id exchange and then the value exchange built by the pool's sharding object."""
+
     def __init__(self, module: TensorPool, plan: ObjectPoolShardingPlan, env: ShardingEnv, device: Optional[torch.device] = None) -> None:
+        from torchrec_b200.distributed.sharding.rw_tensor_pool_sharding import TensorPoolRwReplicatedSharding, TensorPoolRwSharding
+
         super().__init__()
         self._plan, self._env = plan, env
         self._pool_size, self._dim, self._dtype = module.pool_size, module.dim, module.dtype
         device = device if device is not None else module.device
-        if plan.sharding_type == ObjectPoolShardingType.ROW_WISE:
-            self._router: Optional[_RwRouter] = _RwRouter(self._pool_size, env)
-            rows = self._router.local_rows
-            lo = env.rank * self._router.block
-        else:
-            self._router, rows, lo = None, self._pool_size, 0
+        self._replicated = plan.sharding_type != ObjectPoolShardingType.ROW_WISE
+        cls = TensorPoolRwReplicatedSharding if self._replicated else TensorPoolRwSharding
+        self._sharding = cls(self._pool_size, self._dim, env, device)
+        rows, lo = self._sharding.local_pool_size, self._sharding.row_offset
         self.register_buffer("_pool", torch.zeros(rows, self._dim, dtype=self._dtype, device=device))
         if module.device.type != "meta" and rows > 0:
             self._pool.copy_(module.pool[lo: lo + rows])
+        self._update_ids_dist = self._sharding.create_update_ids_dist()
+        self._update_values_dist = self._sharding.create_update_values_dist()
+        self._lookup_ids_dist = self._sharding.create_lookup_ids_dist()
+        self._lookup_values_dist = self._sharding.create_lookup_values_dist()
 
     @property
     def pool_size(self) -> int:
@@ -68,33 +48,19 @@ class ShardedTensorPool(nn.Module):
         return self._dim
 
     def update(self, ids: torch.Tensor, values: torch.Tensor) -> None:
-        ids = ids.to(self._pool.device)
-        values = values.to(self._pool.device)
-        if self._router is None:
-            # replicated: every rank applies every rank's updates
-            all_ids = [torch.empty(0)] * self._env.world_size
-            gathered_i: List[Optional[torch.Tensor]] = [None] * self._env.world_size
-            gathered_v: List[Optional[torch.Tensor]] = [None] * self._env.world_size
-            dist.all_gather_object(gathered_i, ids.cpu(), group=self._env.process_group)
-            dist.all_gather_object(gathered_v, values.cpu(), group=self._env.process_group)
-            for i, v in zip(gathered_i, gathered_v):
-                self._pool.index_copy_(0, i.to(self._pool.device).long(), v.to(self._pool.device))
-            del all_ids
-            return
-        order, local_ids, send, recv = self._router.route(ids)
-        got = self._router.exchange(values.index_select(0, order), send, recv)
-        self._pool.index_copy_(0, local_ids, got)
+        ctx = self._sharding.create_context()
+        local_ids = self._update_ids_dist(ctx, ids.to(self._pool.device))
+        rows = self._update_values_dist(ctx, values.to(self._pool.device))
+        if local_ids.numel():
+            self._pool.index_copy_(0, local_ids, rows.to(self._pool.dtype))
 
     def lookup(self, ids: torch.Tensor) -> torch.Tensor:
         ids = ids.to(self._pool.device)
-        if self._router is None:
+        if self._replicated:
             return self._pool.index_select(0, ids.long())
-        order, local_ids, send, recv = self._router.route(ids)
-        rows = self._pool.index_select(0, local_ids)
-        back = self._router.exchange(rows, recv, send)
-        out = torch.empty_like(back)
-        out[order] = back
-        return out
+        ctx = self._sharding.create_context()
+        local_ids = self._lookup_ids_dist(ctx, ids)
+        return self._lookup_values_dist(ctx, self._pool.index_select(0, local_ids))
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         return self.lookup(ids)
@@ -106,9 +72,15 @@ class ShardedKeyedJaggedTensorPool(nn.Module):
     def __init__(self, module: KeyedJaggedTensorPool, plan: ObjectPoolShardingPlan, env: ShardingEnv, device: Optional[torch.device] = None) -> None:
         super().__init__()
         assert plan.sharding_type == ObjectPoolShardingType.ROW_WISE, "KJT pools are row-wise sharded"
-        self._router = _RwRouter(module.pool_size, env)
+        from torchrec_b200.distributed.sharding.rw_kjt_pool_sharding import KeyedJaggedTensorPoolRwSharding
+
         dev = device if device is not None else module._values.device
-        self._local = KeyedJaggedTensorPool(max(self._router.local_rows, 1), module.feature_max_lengths, values_dtype=module._values.dtype, is_weighted=module._is_weighted, device=dev)
+        self._sharding = KeyedJaggedTensorPoolRwSharding(module.pool_size, env, dev, num_features=len(module.feature_max_lengths))
+        self._update_ids_dist = self._sharding.create_update_ids_dist()
+        self._update_values_dist = self._sharding.create_update_values_dist()
+        self._lookup_ids_dist = self._sharding.create_lookup_ids_dist()
+        self._lookup_values_dist = self._sharding.create_lookup_values_dist()
+        self._local = KeyedJaggedTensorPool(max(self._sharding.local_pool_size, 1), module.feature_max_lengths, values_dtype=module._values.dtype, is_weighted=module._is_weighted, device=dev)
         self._keys = list(module.feature_max_lengths.keys())
         self._caps = [module.feature_max_lengths[k] for k in self._keys]
         self._is_weighted = module._is_weighted
@@ -119,13 +91,13 @@ class ShardedKeyedJaggedTensorPool(nn.Module):
         dev = self._local._values.device
         ids = ids.to(dev)
         B = ids.numel()
-        order, local_ids, send, recv = self._router.route(ids)
+        ctx = self._sharding.create_context()
+        local_ids = self._update_ids_dist(ctx, ids)
         lens = values.lengths().view(len(self._keys), B).t().to(dev)  # [B, F]
         jt = values.to_dict()
         dense = torch.cat([sops.jagged_to_padded_dense(jt[k].values().to(dev), jt[k].offsets().to(dev), cap, 0) if jt[k].values().numel() else
                            torch.zeros(B, cap, dtype=values.values().dtype, device=dev) for k, cap in zip(self._keys, self._caps)], dim=1)
-        got_v = self._router.exchange(dense.index_select(0, order), send, recv)
-        got_l = self._router.exchange(lens.index_select(0, order), send, recv)
+        got_v, got_l = self._update_values_dist(ctx, dense, lens)
         if local_ids.numel() == 0:
             return
         self._local._values[local_ids] = got_v.to(self._local._values.dtype)
@@ -135,12 +107,9 @@ class ShardedKeyedJaggedTensorPool(nn.Module):
         dev = self._local._values.device
         ids = ids.to(dev)
         B = ids.numel()
-        order, local_ids, send, recv = self._router.route(ids)
-        rows = self._router.exchange(self._local._values.index_select(0, local_ids), recv, send)
-        lens = self._router.exchange(self._local._lengths.index_select(0, local_ids), recv, send)
-        v = torch.empty_like(rows)
-        l = torch.empty_like(lens)
-        v[order], l[order] = rows, lens
+        ctx = self._sharding.create_context()
+        local_ids = self._lookup_ids_dist(ctx, ids)
+        v, l = self._lookup_values_dist(ctx, self._local._values.index_select(0, local_ids), self._local._lengths.index_select(0, local_ids))
         vals, start = [], 0
         for f, cap in enumerate(self._caps):
             block = v[:, start: start + cap]
