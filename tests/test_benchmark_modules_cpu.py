@@ -1,0 +1,41 @@
+"""CPU smoke runs of the module / operator benchmarks (tiny shapes)."""
+import torch
+
+
+def test_benchmark_inference_forms():
+    from torchrec_b200.distributed.benchmark.benchmark_inference import main
+
+    res = main(["--module", "both", "--forms", "float,quant,quant_sharded", "--world_size", "2", "--row_cap", "500", "--num_tables", "3",
+                "--batch_size", "8", "--iters", "2", "--warmup", "1", "--device", "cpu"])
+    assert [r.short_name for r in res] == ["ebc-float", "ebc-quant", "ebc-quant_sharded", "ec-float", "ec-quant", "ec-quant_sharded"]
+    assert all(r.gpu_elapsed_time.numel() == 2 for r in res)
+
+
+def test_benchmark_tbe_operator_and_wrappers():
+    from torchrec_b200.distributed.benchmark.benchmark_split_table_batched_embeddings import TBEBenchConfig, op_bench
+    from torchrec_b200.distributed.benchmark.embedding_collection_wrappers import ModuleForm, benchmark_ebc_module, get_tables
+
+    res = op_bench(TBEBenchConfig(num_tables=2, num_embeddings=200, embedding_dim=8, batch_size=16, pooling=2, num_iters=2, warmup_iters=1, device="cpu"))
+    assert res.gpu_elapsed_time.numel() == 2
+    res = op_bench(TBEBenchConfig(num_tables=2, num_embeddings=200, embedding_dim=8, batch_size=16, pooling=2, train=False, num_iters=2, warmup_iters=1, device="cpu"))
+    assert "fwd" in res.short_name
+    tables = get_tables([(100, 8), (50, 8)], is_pooled=True)
+    r = benchmark_ebc_module(tables, ModuleForm.FLOAT, batch_size=8, pooling=2, num_iters=2, warmup_iters=1, device=torch.device("cpu"), train=True)
+    assert r.short_name == "ebc-float-train"
+
+
+def test_benchmark_post_a2a_variants_agree():
+    from torchrec_b200.distributed.benchmark import benchmark_set_sharding_context_post_a2a as m
+    from torchrec_b200.distributed.embedding import EmbeddingCollectionContext
+    from torchrec_b200.distributed.embedding_sharding import _set_sharding_context_post_a2a
+    from torchrec_b200.distributed.sharding.sequence_sharding import SequenceShardingContext
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    kjt = KeyedJaggedTensor(keys=["a", "b"], values=torch.arange(5), lengths=torch.tensor([1, 1, 1, 2]), stride_per_key_per_rank=[[1, 1], [2, 0]])
+    out = []
+    for fn in (_set_sharding_context_post_a2a, m._set_sharding_context_post_a2a_zip):
+        ctx = EmbeddingCollectionContext(sharding_contexts=[SequenceShardingContext(batch_size_per_rank_per_feature=[])])
+        fn([kjt], ctx)
+        out.append(ctx.sharding_contexts[0].batch_size_per_rank_per_feature)
+    assert out[0] == out[1] == [[1, 2], [1, 0]]
+    m.main(["--num_list", "5", "--num_keys", "4"])
