@@ -49,3 +49,21 @@ def _rank(rank, world_size, sharding_type):
 @pytest.mark.parametrize("sharding_type", ["table_wise", "row_wise"])
 def test_sharding_single_rank_harness(sharding_type):
     run_multi_process(_rank, world_size=2, sharding_type=sharding_type)
+
+
+def test_tables_config_and_td_input():
+    from torchrec_b200.distributed.test_utils.test_input import TdModelInput
+    from torchrec_b200.distributed.test_utils.test_tables import EmbeddingTablesConfig
+
+    cfg = EmbeddingTablesConfig(num_unweighted_features=3, num_weighted_features=2, embedding_feature_dim=16,
+                                additional_tables=[[{"name": "extra", "embedding_dim": 16, "num_embeddings": 77, "feature_names": ["fx"]}], [], [
+                                    {"name": "own_group", "embedding_dim": 8, "num_embeddings": 5, "feature_names": ["fo"]}]])
+    unweighted, weighted, third = cfg.generate_tables()
+    assert [t.name for t in unweighted] == ["table_0", "table_1", "table_2", "extra"] and unweighted[0].num_embeddings == 100_000
+    assert [t.feature_names[0] for t in weighted] == ["weighted_feature_0", "weighted_feature_1"] and third[0].embedding_dim == 8
+
+    tables, _ = _tables()
+    whole, parts = TdModelInput.generate(batch_size=2, world_size=2, num_float_features=4, tables=tables, weighted_tables=[], pooling_avg=2, random_seed=3)
+    assert isinstance(whole.idlist_features, dict) and len(parts) == 2
+    kjt = parts[0].to_kjt()
+    assert kjt.keys() == [f"feature_{i}" for i in range(4)] and kjt.stride() == 2
