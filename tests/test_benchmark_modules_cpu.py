@@ -39,3 +39,16 @@ def test_benchmark_post_a2a_variants_agree():
         out.append(ctx.sharding_contexts[0].batch_size_per_rank_per_feature)
     assert out[0] == out[1] == [[1, 2], [1, 0]]
     m.main(["--num_list", "5", "--num_keys", "4"])
+
+
+def test_benchmark_zch_collision_rates():
+    from torchrec_b200.distributed.benchmark.benchmark_zch.benchmark_zch import main
+
+    common = ["--num_tables", "2", "--zch_size", "1000", "--distinct_ids", "700", "--batch_size", "128", "--train_batches", "6", "--eval_batches", "2",
+              "--embedding_dim", "8", "--pooling", "2", "--device", "cpu", "--warmup_batches", "1"]
+    zch = main(["--zch_method", "mpzch"] + common)
+    mod = main(["--zch_method", "none"] + common)
+    assert zch["distinct_lookups"] == mod["distinct_lookups"] > 0
+    # zero-collision hashing keeps distinct ids apart where a plain modulo does not
+    assert zch["collision_rate"] < 0.02 < mod["collision_rate"]
+    assert 0.0 <= zch["auc"] <= 1.0 and zch["train_qps"] > 0
