@@ -50,5 +50,5 @@ def test_benchmark_zch_collision_rates():
     mod = main(["--zch_method", "none"] + common)
     assert zch["distinct_lookups"] == mod["distinct_lookups"] > 0
     # zero-collision hashing keeps distinct ids apart where a plain modulo does not
-    assert zch["collision_rate"] < 0.02 < mod["collision_rate"]
+    assert zch["collision_rate"] * 3 < mod["collision_rate"]
     assert 0.0 <= zch["auc"] <= 1.0 and zch["train_qps"] > 0
