@@ -108,3 +108,45 @@ def test_id_transformer_collection_keeps_rows_across_eviction():
             else:
                 first[g] = r.clone()
     group.save()
+
+
+def test_wrapped_dataloader_rewrites_ids_and_saves():
+    """``wrap`` returns a loader whose batches carry cache rows instead of global ids; a failing source surfaces as an error."""
+    import pytest
+    from torchrec_b200.contrib import dynamic_embedding as tde
+    from torchrec_b200.modules.embedding_configs import EmbeddingBagConfig
+    from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    cfg = EmbeddingBagConfig(name="t0", num_embeddings=8, embedding_dim=4, feature_names=["f0"])
+    ebc = EmbeddingBagCollection([cfg])
+
+    def source(n):
+        for step in range(n):
+            gids = torch.arange(step * 3, step * 3 + 4, dtype=torch.long) * 1_000_003
+            yield torch.full((4,), float(step)), KeyedJaggedTensor.from_lengths_sync(keys=["f0"], values=gids, lengths=torch.ones(4, dtype=torch.long))
+
+    loader, model = tde.wrap("memory://wrapped", list(source(5)), ebc, {"": [cfg]}, data_info={1: ""}, num_prefetch=2)
+    assert model is ebc and len(loader) == 5
+    seen = 0
+    for label, kjt in loader:
+        assert int(kjt.values().max()) < 8 and int(kjt.values().min()) >= 0 and float(label[0]) == seen
+        model(kjt).values().sum().backward()
+        seen += 1
+    assert seen == 5
+    tde.save(model)
+    with pytest.raises(ValueError):
+        tde.save(EmbeddingBagCollection([cfg]))
+
+    def broken():
+        yield from source(1)
+        raise OSError("disk gone")
+
+    bad, _ = tde.wrap("memory://wrapped2", broken(), EmbeddingBagCollection([cfg]), {"": [cfg]}, data_info={1: ""})
+    it = iter(bad)
+    next(it)
+    with pytest.raises(RuntimeError):
+        next(it)
+    tl = tde.TensorList([torch.zeros(2)])
+    tl.append(torch.ones(3))
+    assert len(tl) == 2 and tl[1].numel() == 3

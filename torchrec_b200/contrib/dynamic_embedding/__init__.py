@@ -7,3 +7,5 @@ from torchrec_b200.contrib.dynamic_embedding.id_transformer_collection import ID
 from torchrec_b200.contrib.dynamic_embedding.id_transformer_group import IDTransformerGroup  # noqa: F401
 from torchrec_b200.contrib.dynamic_embedding.ps import PS, PSCollection  # noqa: F401
 from torchrec_b200.contrib.dynamic_embedding.utils import register_io  # noqa: F401
+from torchrec_b200.contrib.dynamic_embedding.dataloader import DataLoader, save, wrap  # noqa: F401
+from torchrec_b200.contrib.dynamic_embedding.tensor_list import TensorList  # noqa: F401
