@@ -1,0 +1,79 @@
+"""Row-wise and column-wise placement of quantized pooled tables must reproduce the unsharded quantized module exactly (the shards
+hold the very same quantized bytes)."""
+import pytest
+import torch
+
+from torchrec_b200.distributed.quant_embeddingbag import ShardedQuantEmbeddingBagCollection
+from torchrec_b200.distributed.types import ParameterSharding, ShardingEnv
+from torchrec_b200.modules.embedding_configs import DataType, EmbeddingBagConfig, PoolingType
+from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
+from torchrec_b200.quant.embedding_modules import EmbeddingBagCollection as QEBC
+from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+
+def _quantized(dtype: DataType, weighted: bool):
+    torch.manual_seed(0)
+    tables = [
+        EmbeddingBagConfig(name="tw", embedding_dim=16, num_embeddings=30, feature_names=["f_tw"], pooling=PoolingType.SUM),
+        EmbeddingBagConfig(name="rw_sum", embedding_dim=16, num_embeddings=37, feature_names=["f_rs", "f_rs2"], pooling=PoolingType.SUM),
+        EmbeddingBagConfig(name="rw_mean", embedding_dim=16, num_embeddings=10, feature_names=["f_rm"], pooling=PoolingType.SUM if weighted else PoolingType.MEAN),
+        EmbeddingBagConfig(name="cw", embedding_dim=48, num_embeddings=25, feature_names=["f_cw"], pooling=PoolingType.SUM),
+    ]
+    ebc = EmbeddingBagCollection(tables=tables, is_weighted=weighted)
+    for t in tables:
+        t.data_type = dtype
+    return QEBC.from_float(_with_qconfig(ebc, dtype)), tables
+
+
+def _with_qconfig(ebc, dtype):
+    import torch.ao.quantization as tq
+
+    from torchrec_b200.quant.embedding_modules import QuantConfig
+
+    qd = {DataType.INT8: torch.qint8, DataType.INT4: torch.quint4x2}[dtype]
+    ebc.qconfig = QuantConfig(activation=tq.PlaceholderObserver.with_args(dtype=torch.float), weight=tq.PlaceholderObserver.with_args(dtype=qd))
+    return ebc
+
+
+def _kjt(tables, B, weighted, seed):
+    g = torch.Generator().manual_seed(seed)
+    keys, lens, vals = [], [], []
+    for t in tables:
+        for f in t.feature_names:
+            l = torch.randint(0, 5, (B,), generator=g)
+            keys.append(f)
+            lens.append(l)
+            vals.append(torch.randint(0, t.num_embeddings, (int(l.sum()),), generator=g))
+    v = torch.cat(vals)
+    return KeyedJaggedTensor(keys=keys, values=v, lengths=torch.cat(lens), weights=torch.rand(v.numel(), generator=g) if weighted else None)
+
+
+@pytest.mark.parametrize("dtype", [DataType.INT8, DataType.INT4])
+@pytest.mark.parametrize("weighted", [False, True])
+def test_rw_cw_match_unsharded(dtype, weighted):
+    q, tables = _quantized(dtype, weighted)
+    W = 3
+    plan = {
+        "tw": ParameterSharding(sharding_type="table_wise", compute_kernel="quant", ranks=[1]),
+        "rw_sum": ParameterSharding(sharding_type="row_wise", compute_kernel="quant", ranks=list(range(W))),
+        "rw_mean": ParameterSharding(sharding_type="row_wise", compute_kernel="quant", ranks=list(range(W))),
+        "cw": ParameterSharding(sharding_type="column_wise", compute_kernel="quant", ranks=[2, 0, 1]),
+    }
+    sharded = ShardedQuantEmbeddingBagCollection(q, plan, ShardingEnv.from_local(world_size=W, rank=0), device=torch.device("cpu"))
+    for seed in range(3):
+        kjt = _kjt(tables, 6, weighted, seed)
+        # key order of the request differs from table order
+        kjt = kjt.permute([4, 0, 3, 1, 2])
+        want, got = q(kjt), sharded(kjt)
+        assert want.keys() == got.keys() and want.length_per_key() == got.length_per_key()
+        torch.testing.assert_close(got.values(), want.values(), rtol=1e-5, atol=1e-6)
+    names = list(sharded.sharded_parameter_names())
+    assert "_rw_shards.2.embedding_bags.rw_sum.weight" in names and "_cw_shards.0.embedding_bags.cw.weight" in names and "_shards.1.embedding_bags.tw.weight" in names
+
+
+def test_cw_on_one_device_twice_is_rejected():
+    q, _ = _quantized(DataType.INT8, False)
+    plan = {n: ParameterSharding(sharding_type="table_wise", compute_kernel="quant", ranks=[0]) for n in ("tw", "rw_sum", "rw_mean")}
+    plan["cw"] = ParameterSharding(sharding_type="column_wise", compute_kernel="quant", ranks=[0, 0])
+    with pytest.raises(ValueError):
+        ShardedQuantEmbeddingBagCollection(q, plan, ShardingEnv.from_local(world_size=2, rank=0), device=torch.device("cpu"))

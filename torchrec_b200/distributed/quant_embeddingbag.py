@@ -1,9 +1,10 @@
 """Sharded quantized ``EmbeddingBagCollection`` for inference: ONE process drives all devices.
 
-Tables are placed table-wise (whole table on one device) following the module sharding plan; the request KJT is split
-by feature and copied to the owning devices, each device runs one quantized lookup, and the pooled outputs are
-concatenated on the output device in the key order of the unsharded module.  Synchronous ``forward`` (no awaitables),
-as serving code expects.  Counterpart of ``torchrec/distributed/quant_embeddingbag.py:165-470`` (table-wise path).
+Tables are placed table-wise, row-wise or column-wise following the module sharding plan; the request KJT is split by feature
+(row-wise tables: also by row block) and copied to the owning devices, each device runs its quantized lookups, and the pooled
+outputs are assembled on the output device in the key order of the unsharded module.  Synchronous ``forward`` (no awaitables),
+as serving code expects.  Counterpart of ``torchrec/distributed/quant_embeddingbag.py:165-470`` and the inference dists of
+``sharding/{tw,rw,cw}_sharding.py``.
 """
 from __future__ import annotations
 
@@ -26,57 +27,144 @@ def _device_for(rank: int, device_type: str) -> torch.device:
 
 
 class ShardedQuantEmbeddingBagCollection(nn.Module):
+    """Placement per table: ``table_wise`` (whole table on ``ranks[0]``), ``row_wise`` (equal row blocks over all devices; ids are
+    bucketized by block, every device pools its part, the parts are summed) or ``column_wise`` (one column range per entry of
+    ``ranks``, all on distinct devices; every device pools its columns, the ranges are concatenated).  Quantized rows are cut
+    without requantizing: a row block keeps whole rows, a column range keeps its payload bytes and a copy of the row's scale and
+    bias."""
+
     def __init__(self, module: QuantEmbeddingBagCollection, table_name_to_parameter_sharding: Dict[str, ParameterSharding], env: ShardingEnv,
                  fused_params: Optional[Dict[str, Any]] = None, device: Optional[torch.device] = None) -> None:
         super().__init__()
+        from torchrec_b200.ops.quant_ops import BITS
+
         self._configs = module.embedding_bag_configs()
         self._is_weighted = module.is_weighted()
         self._world_size = env.world_size
         self._device_type = (device.type if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
         self._out_device = device if device is not None else _device_for(0, self._device_type)
-        by_rank: List[List[Any]] = [[] for _ in range(self._world_size)]
+        W = self._world_size
+        tw: List[List[Any]] = [[] for _ in range(W)]
+        rw: List[List[Any]] = [[] for _ in range(W)]
+        cw: List[List[Any]] = [[] for _ in range(W)]
+        slices: Dict[Any, torch.Tensor] = {}  # (kind, rank, table) -> packed rows of that shard
+        self._rw_tables: List[Any] = []
+        self._rw_mean_features: List[str] = []
+        self._cw_order: Dict[str, List[int]] = {}  # table -> ranks in column order
         for cfg in self._configs:
             ps = table_name_to_parameter_sharding[cfg.name]
-            if ps.sharding_type != ShardingType.TABLE_WISE.value:
-                raise ValueError(f"quantized inference sharding supports table_wise placement, got {ps.sharding_type} for {cfg.name}")
-            by_rank[ps.ranks[0]].append(cfg)
-        self._shards = nn.ModuleList()
-        self._feature_names_per_rank: List[List[str]] = []
-        self._names_per_rank: List[List[str]] = []
-        for rank, cfgs in enumerate(by_rank):
-            if not cfgs:
-                self._shards.append(nn.Identity())
-                self._feature_names_per_rank.append([])
-                self._names_per_rank.append([])
-                continue
-            dev = _device_for(rank, self._device_type)
-            shard = QuantEmbeddingBagCollection(copy.deepcopy(cfgs), self._is_weighted, dev, output_dtype=module.output_dtype())
-            for cfg in cfgs:
-                shard.embedding_bags[cfg.name].weight.copy_(module.embedding_bags[cfg.name].weight.to(dev))
-            self._shards.append(shard)
-            self._feature_names_per_rank.append([f for c in cfgs for f in c.feature_names])
+            packed = module.embedding_bags[cfg.name].weight
+            bits = BITS[cfg.data_type]
+            if ps.sharding_type == ShardingType.TABLE_WISE.value:
+                tw[ps.ranks[0]].append(cfg)
+                slices[("tw", ps.ranks[0], cfg.name)] = packed
+            elif ps.sharding_type == ShardingType.ROW_WISE.value:
+                block = (cfg.num_embeddings + W - 1) // W
+                self._rw_tables.append((cfg, block))
+                if cfg.pooling == PoolingType.MEAN:
+                    self._rw_mean_features.extend(cfg.feature_names)
+                for r in range(W):
+                    rows = max(0, min(block, cfg.num_embeddings - r * block))
+                    local = copy.deepcopy(cfg)
+                    local.num_embeddings = max(rows, 1)  # an empty block keeps one unused row so the kernel has a table
+                    local.pooling = PoolingType.SUM  # the divisor of a mean needs the whole bag: applied after the sum over devices
+                    rw[r].append(local)
+                    part = packed[r * block: r * block + rows]
+                    slices[("rw", r, cfg.name)] = part if rows > 0 else packed.new_zeros(1, packed.shape[1])
+            elif ps.sharding_type == ShardingType.COLUMN_WISE.value:
+                ranks = list(ps.ranks)
+                if len(set(ranks)) != len(ranks):
+                    raise ValueError(f"column-wise shards of {cfg.name} must sit on distinct devices, got ranks {ranks}")
+                if cfg.embedding_dim % len(ranks):
+                    raise ValueError(f"{cfg.name}: embedding_dim {cfg.embedding_dim} is not divisible into {len(ranks)} column shards")
+                width = cfg.embedding_dim // len(ranks)
+                payload = cfg.embedding_dim * bits // 8
+                self._cw_order[cfg.name] = ranks
+                for j, r in enumerate(ranks):
+                    local = copy.deepcopy(cfg)
+                    local.embedding_dim = width
+                    cw[r].append(local)
+                    cols = packed[:, j * width * bits // 8: (j + 1) * width * bits // 8]
+                    slices[("cw", r, cfg.name)] = torch.cat([cols, packed[:, payload:]], dim=1) if bits < 16 else cols
+            else:
+                raise ValueError(f"quantized inference sharding supports table_wise, row_wise and column_wise placement, got {ps.sharding_type} for {cfg.name}")
+
+        def build(kind: str, per_rank: List[List[Any]]) -> nn.ModuleList:
+            out = nn.ModuleList()
+            for rank, cfgs in enumerate(per_rank):
+                if not cfgs:
+                    out.append(nn.Identity())
+                    continue
+                dev = _device_for(rank, self._device_type)
+                shard = QuantEmbeddingBagCollection(copy.deepcopy(cfgs), self._is_weighted, dev, output_dtype=module.output_dtype())
+                for cfg in cfgs:
+                    shard.embedding_bags[cfg.name].weight.copy_(slices[(kind, rank, cfg.name)].to(dev))
+                out.append(shard)
+            return out
+
+        self._shards = build("tw", tw)
+        self._rw_shards = build("rw", rw)
+        self._cw_shards = build("cw", cw)
+        self._feature_names_per_rank: List[List[str]] = [[f for c in cfgs for f in c.feature_names] for cfgs in tw]
+        self._cw_feature_names_per_rank: List[List[str]] = [[f for c in cfgs for f in c.feature_names] for cfgs in cw]
+        self._rw_feature_names: List[str] = [f for cfg, _ in self._rw_tables for f in cfg.feature_names]
+        self.register_buffer("_rw_block_sizes", torch.tensor([b for cfg, b in self._rw_tables for _ in cfg.feature_names], dtype=torch.int64), persistent=False)
+        # embedding name (feature, or feature@table when a feature feeds several tables) -> how its output is assembled
         self._embedding_names = module._embedding_names
         self._length_per_key = module._length_per_key
+        self._name_kind: Dict[str, str] = {}
+        self._name_table: Dict[str, str] = {}
+        i = 0
+        for cfg in self._configs:
+            kind = {ShardingType.TABLE_WISE.value: "tw", ShardingType.ROW_WISE.value: "rw", ShardingType.COLUMN_WISE.value: "cw"}[table_name_to_parameter_sharding[cfg.name].sharding_type]
+            for _ in cfg.feature_names:
+                self._name_kind[self._embedding_names[i]] = kind
+                self._name_table[self._embedding_names[i]] = cfg.name
+                i += 1
+
+    def _local(self, features: KeyedJaggedTensor, keys: List[str], names: List[str], rank: int) -> KeyedJaggedTensor:
+        return features.permute([keys.index(f) for f in names]).to(_device_for(rank, self._device_type), non_blocking=True)
 
     def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
+        from torchrec_b200.distributed.embedding_sharding import bucketize_kjt_before_all2all
+
         keys = features.keys()
         pieces: Dict[str, torch.Tensor] = {}
         for rank, (shard, fnames) in enumerate(zip(self._shards, self._feature_names_per_rank)):
-            if not fnames:
-                continue
-            dev = _device_for(rank, self._device_type)
-            local = features.permute([keys.index(f) for f in fnames]).to(dev, non_blocking=True)
-            kt = shard(local)
-            for k, v in kt.to_dict().items():
-                pieces[k] = v.to(self._out_device, non_blocking=True)
+            if fnames:
+                for k, v in shard(self._local(features, keys, fnames, rank)).to_dict().items():
+                    pieces[k] = v.to(self._out_device, non_blocking=True)
+        if self._rw_feature_names:
+            rw_in = features.permute([keys.index(f) for f in self._rw_feature_names])
+            bucketized, _ = bucketize_kjt_before_all2all(rw_in, num_buckets=self._world_size, block_sizes=self._rw_block_sizes.to(rw_in.values().device))
+            for rank, part in enumerate(bucketized.split([len(self._rw_feature_names)] * self._world_size)):
+                local = KeyedJaggedTensor(keys=self._rw_feature_names, values=part.values(), weights=part.weights_or_none(), lengths=part.lengths(), stride=features.stride())
+                out = self._rw_shards[rank](local.to(_device_for(rank, self._device_type), non_blocking=True)).to_dict()
+                for k, v in out.items():
+                    v = v.to(self._out_device, non_blocking=True)
+                    pieces[k] = v if k not in pieces or rank == 0 else pieces[k] + v
+            if self._rw_mean_features:
+                lens = rw_in.lengths().view(len(self._rw_feature_names), -1).to(self._out_device)
+                for name in self._embedding_names:
+                    f = name.split("@")[0]
+                    if self._name_kind.get(name) == "rw" and f in self._rw_mean_features:
+                        pieces[name] = pieces[name] / lens[self._rw_feature_names.index(f)].clamp(min=1).unsqueeze(1).to(pieces[name].dtype)
+        cw_parts: Dict[str, Dict[int, torch.Tensor]] = {}
+        for rank, (shard, fnames) in enumerate(zip(self._cw_shards, self._cw_feature_names_per_rank)):
+            if fnames:
+                for k, v in shard(self._local(features, keys, fnames, rank)).to_dict().items():
+                    cw_parts.setdefault(k, {})[rank] = v.to(self._out_device, non_blocking=True)
+        for name, by_rank in cw_parts.items():
+            pieces[name] = torch.cat([by_rank[r] for r in self._cw_order[self._name_table[name]]], dim=1)
         values = torch.cat([pieces[n] for n in self._embedding_names], dim=1)
         return KeyedTensor(keys=self._embedding_names, values=values, length_per_key=self._length_per_key)
 
     def sharded_parameter_names(self, prefix: str = ""):
-        for rank, shard in enumerate(self._shards):
-            if isinstance(shard, QuantEmbeddingBagCollection):
-                for name in shard.embedding_bags.keys():
-                    yield f"{prefix}_shards.{rank}.embedding_bags.{name}.weight"
+        for attr in ("_shards", "_rw_shards", "_cw_shards"):
+            for rank, shard in enumerate(getattr(self, attr)):
+                if isinstance(shard, QuantEmbeddingBagCollection):
+                    for name in shard.embedding_bags.keys():
+                        yield f"{prefix}{attr}.{rank}.embedding_bags.{name}.weight"
 
 
 class QuantEmbeddingBagCollectionSharder(BaseQuantEmbeddingSharder[QuantEmbeddingBagCollection]):
@@ -88,7 +176,7 @@ class QuantEmbeddingBagCollectionSharder(BaseQuantEmbeddingSharder[QuantEmbeddin
         return {name: m.weight for name, m in module.embedding_bags.items()}
 
     def sharding_types(self, compute_device_type: str) -> List[str]:
-        return [ShardingType.TABLE_WISE.value]
+        return [ShardingType.TABLE_WISE.value, ShardingType.ROW_WISE.value, ShardingType.COLUMN_WISE.value]
 
     @property
     def module_type(self) -> Type[QuantEmbeddingBagCollection]:
