@@ -77,3 +77,34 @@ def test_cw_on_one_device_twice_is_rejected():
     plan["cw"] = ParameterSharding(sharding_type="column_wise", compute_kernel="quant", ranks=[0, 0])
     with pytest.raises(ValueError):
         ShardedQuantEmbeddingBagCollection(q, plan, ShardingEnv.from_local(world_size=2, rank=0), device=torch.device("cpu"))
+
+
+@pytest.mark.parametrize("need_indices", [False, True])
+def test_sequence_rw_cw_match_unsharded(need_indices):
+    from torchrec_b200.distributed.quant_embedding import ShardedQuantEmbeddingCollection
+    from torchrec_b200.modules.embedding_configs import EmbeddingConfig
+    from torchrec_b200.modules.embedding_modules import EmbeddingCollection
+    from torchrec_b200.quant.embedding_modules import EmbeddingCollection as QEC
+
+    torch.manual_seed(1)
+    tables = [EmbeddingConfig(name="tw", embedding_dim=24, num_embeddings=30, feature_names=["f_tw"]),
+              EmbeddingConfig(name="rw", embedding_dim=24, num_embeddings=41, feature_names=["f_r1", "f_r2"]),
+              EmbeddingConfig(name="cw3", embedding_dim=24, num_embeddings=25, feature_names=["f_c3"]),
+              EmbeddingConfig(name="cw2", embedding_dim=24, num_embeddings=19, feature_names=["f_c2"])]
+    ec = EmbeddingCollection(tables=tables, need_indices=need_indices)
+    q = QEC.from_float(_with_qconfig(ec, DataType.INT8))
+    W = 3
+    plan = {"tw": ParameterSharding(sharding_type="table_wise", compute_kernel="quant", ranks=[2]),
+            "rw": ParameterSharding(sharding_type="row_wise", compute_kernel="quant", ranks=list(range(W))),
+            "cw3": ParameterSharding(sharding_type="column_wise", compute_kernel="quant", ranks=[1, 2, 0]),
+            "cw2": ParameterSharding(sharding_type="column_wise", compute_kernel="quant", ranks=[0, 2])}
+    sharded = ShardedQuantEmbeddingCollection(q, plan, ShardingEnv.from_local(world_size=W, rank=0), device=torch.device("cpu"))
+    for seed in range(3):
+        kjt = _kjt(tables, 5, False, seed).permute([3, 0, 4, 2, 1])
+        want, got = q(kjt), sharded(kjt)
+        assert sorted(want) == sorted(got)
+        for k in want:
+            torch.testing.assert_close(got[k].values(), want[k].values(), rtol=1e-5, atol=1e-6)
+            assert torch.equal(got[k].lengths(), want[k].lengths())
+            if need_indices:
+                assert torch.equal(got[k].weights(), want[k].weights())
