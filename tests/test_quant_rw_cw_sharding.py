@@ -108,3 +108,25 @@ def test_sequence_rw_cw_match_unsharded(need_indices):
             assert torch.equal(got[k].lengths(), want[k].lengths())
             if need_indices:
                 assert torch.equal(got[k].weights(), want[k].weights())
+
+
+def test_weight_specs_of_rw_and_cw_shards():
+    from torchrec_b200.distributed.quant_state import sharded_tbes_weights_spec
+
+    q, _ = _quantized(DataType.INT8, False)
+    W = 3
+    plan = {"tw": ParameterSharding(sharding_type="table_wise", compute_kernel="quant", ranks=[1]),
+            "rw_sum": ParameterSharding(sharding_type="row_wise", compute_kernel="quant", ranks=list(range(W))),
+            "rw_mean": ParameterSharding(sharding_type="table_wise", compute_kernel="quant", ranks=[0]),
+            "cw": ParameterSharding(sharding_type="column_wise", compute_kernel="quant", ranks=[2, 0, 1])}
+    sharded = ShardedQuantEmbeddingBagCollection(q, plan, ShardingEnv.from_local(world_size=W, rank=0), device=torch.device("cpu"))
+    spec = sharded_tbes_weights_spec(torch.nn.ModuleDict({"ebc": sharded}))
+    by_fqn = {}
+    for k, v in spec.items():
+        if k.endswith(".weight"):
+            by_fqn.setdefault(v.fqn, []).append(v)
+    rw = sorted(by_fqn["ebc.embedding_bags.rw_sum.weight"], key=lambda w: w.shard_offsets[0])
+    assert [(w.shard_offsets, w.shard_sizes) for w in rw] == [([0, 0], [13, 16]), ([13, 0], [13, 16]), ([26, 0], [11, 16])] and rw[0].sharding_type == "row_wise"
+    cw = sorted(by_fqn["ebc.embedding_bags.cw.weight"], key=lambda w: w.shard_offsets[1])
+    assert [(w.shard_offsets, w.shard_sizes) for w in cw] == [([0, 0], [25, 16]), ([0, 16], [25, 16]), ([0, 32], [25, 16])] and cw[0].sharding_type == "column_wise"
+    assert by_fqn["ebc.embedding_bags.tw.weight"][0].shard_sizes == [30, 16]

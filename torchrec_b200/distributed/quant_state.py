@@ -3,7 +3,8 @@ unsharded tensor it holds.  Model publishing uses the map to cut an unsharded qu
 
 Keys are ``<module path>.tbes.<kernel index>.<slot in kernel>.<table>.weight`` plus ``_qscale`` / ``_qbias`` for sub-16-bit tables
 (payload bytes and the two fp16 row parameters are reported separately); values name the unsharded tensor, the shard's offsets
-and sizes, and the sharding type.  Counterpart of ``torchrec/distributed/quant_state.py:383-520``."""
+and sizes (column offsets and widths in payload bytes), and the sharding type.  Kernels are numbered over the table-wise
+shards by device, then the row-wise shards, then the column-wise shards.  Counterpart of ``torchrec/distributed/quant_state.py:383-520``."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -36,8 +37,7 @@ def get_param_id_from_type(is_sqebc: bool, is_sqmcec: bool, is_sfpebc: bool) -> 
 
 
 def sharded_tbes_weights_spec(sharded_model: torch.nn.Module, virtual_table_name_to_bucket_lengths: Optional[Dict[str, List[int]]] = None) -> Dict[str, WeightSpec]:
-    """Walk ``sharded_model`` for sharded quantized collections and describe every table shard of every kernel.  Kernel indices
-    count over the devices in order, then over the pooling groups of a device."""
+    """Walk ``sharded_model`` for sharded quantized collections and describe every table shard of every kernel."""
     from torchrec_b200.distributed.quant_embedding import ShardedQuantEmbeddingCollection
     from torchrec_b200.distributed.quant_embeddingbag import ShardedQuantEmbeddingBagCollection
 
@@ -48,7 +48,16 @@ def sharded_tbes_weights_spec(sharded_model: torch.nn.Module, virtual_table_name
         container = get_param_id_from_type(isinstance(module, ShardedQuantEmbeddingBagCollection), False, False)
         prefix = f"{module_fqn}." if module_fqn else ""
         kernel = 0
-        for shard in module._shards:
+        rw_block = {cfg.name: block for cfg, block in getattr(module, "_rw_tables", [])}
+        full = {cfg.name: cfg for cfg in module._configs}
+        if isinstance(module, ShardedQuantEmbeddingBagCollection):
+            cw_ranks = dict(module._cw_order)
+            cw_shards = [(r, s) for r, s in enumerate(module._cw_shards)]
+        else:
+            cw_ranks = {cfg.name: ranks for cfg, ranks, _ in module._cw_tables}
+            cw_shards = [(int(key.split("_")[0]), s) for key, s in module._cw_shards.items()]
+        groups = [("tw", r, s) for r, s in enumerate(module._shards)] + [("rw", r, s) for r, s in enumerate(module._rw_shards)] + [("cw", r, s) for r, s in cw_shards]
+        for kind, rank, shard in groups:
             if not hasattr(shard, "_group_tables"):
                 continue
             for group in shard._group_tables:
@@ -56,12 +65,17 @@ def sharded_tbes_weights_spec(sharded_model: torch.nn.Module, virtual_table_name
                     bits = BITS[table.data_type]
                     rows = table.num_embeddings
                     payload = table.embedding_dim * bits // 8
+                    row_off, col_off, stype = 0, 0, ShardingType.TABLE_WISE.value
+                    if kind == "rw":
+                        row_off, stype = rank * rw_block[table.name], ShardingType.ROW_WISE.value
+                        rows = max(0, min(rw_block[table.name], full[table.name].num_embeddings - row_off))
+                    elif kind == "cw":
+                        col_off, stype = cw_ranks[table.name].index(rank) * payload, ShardingType.COLUMN_WISE.value
                     unsharded = f"{prefix}{container}.{table.name}.weight"
                     key = f"{prefix}tbes.{kernel}.{slot}.{table.name}.weight"
-                    # table-wise placement: the shard is the whole table
-                    out[key] = WeightSpec(unsharded, [0, 0], [rows, payload], ShardingType.TABLE_WISE.value)
+                    out[key] = WeightSpec(unsharded, [row_off, col_off], [rows, payload], stype)
                     if bits < 16:
                         for suffix in ("_qscale", "_qbias"):
-                            out[key + suffix] = WeightSpec(unsharded + suffix, [0, 0], [rows, 2], ShardingType.TABLE_WISE.value)
+                            out[key + suffix] = WeightSpec(unsharded + suffix, [row_off, 0], [rows, 2], stype)
                 kernel += 1
     return out
