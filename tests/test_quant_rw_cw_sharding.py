@@ -130,3 +130,19 @@ def test_weight_specs_of_rw_and_cw_shards():
     cw = sorted(by_fqn["ebc.embedding_bags.cw.weight"], key=lambda w: w.shard_offsets[1])
     assert [(w.shard_offsets, w.shard_sizes) for w in cw] == [([0, 0], [25, 16]), ([0, 16], [25, 16]), ([0, 32], [25, 16])] and cw[0].sharding_type == "column_wise"
     assert by_fqn["ebc.embedding_bags.tw.weight"][0].shard_sizes == [30, 16]
+
+
+def test_shard_quant_model_honours_constraints():
+    from torchrec_b200.distributed.planner import ParameterConstraints
+    from torchrec_b200.inference.modules import shard_quant_model
+
+    q, tables = _quantized(DataType.INT8, False)
+    holder = torch.nn.Sequential(q)
+    kjt = _kjt(tables, 4, False, 5)
+    want = q(kjt).values().clone()
+    sharded, plan = shard_quant_model(holder, world_size=3, compute_device="cpu",
+                                      constraints={"rw_sum": ParameterConstraints(sharding_types=["row_wise"]), "cw": ParameterConstraints(sharding_types=["column_wise"])})
+    p = plan.plan["0"]
+    assert p["rw_sum"].sharding_type == "row_wise" and p["rw_sum"].ranks == [0, 1, 2]
+    assert p["cw"].sharding_type == "column_wise" and len(p["cw"].ranks) == 3 and p["tw"].sharding_type == "table_wise"
+    torch.testing.assert_close(sharded(kjt).values(), want, rtol=1e-5, atol=1e-6)

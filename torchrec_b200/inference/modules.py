@@ -207,8 +207,9 @@ def quantize_inference_model(model: nn.Module, quantization_mapping: Optional[Di
 
 def shard_quant_model(model: nn.Module, world_size: int = 1, compute_device: str = "cuda", sharding_device: str = "meta", sharders: Optional[List[Any]] = None,
                       device_memory_size: Optional[int] = None, constraints: Optional[Dict[str, Any]] = None, ddr_cap: Optional[int] = None) -> Tuple[nn.Module, ShardingPlan]:
-    """Place the quantized tables of ``model`` table-wise on ``world_size`` devices of this host, balancing bytes per device
-    (largest table first onto the lightest device), and swap the quantized modules for their sharded form."""
+    """Place the quantized tables of ``model`` on ``world_size`` devices of this host and swap the quantized modules for their sharded
+    form.  Default: table-wise, largest table first onto the lightest device.  A table whose entry in ``constraints`` (an object with
+    ``sharding_types``, e.g. ``ParameterConstraints``) asks for ``row_wise`` or ``column_wise`` first is placed that way."""
     env = ShardingEnv.from_local(world_size=world_size, rank=0)
     device = torch.device(compute_device)
     plan: Dict[str, Dict[str, ParameterSharding]] = {}
@@ -222,7 +223,27 @@ def shard_quant_model(model: nn.Module, world_size: int = 1, compute_device: str
         container = m.embedding_bags if isinstance(m, QuantEmbeddingBagCollection) else m.embeddings
         for name, holder in container.items():
             sized.append((holder.weight.numel(), path, name))
+    dims = {}
+    for path, m in targets:
+        for cfg in (m.embedding_bag_configs() if isinstance(m, QuantEmbeddingBagCollection) else m.embedding_configs()):
+            dims[(path, cfg.name)] = cfg.embedding_dim
     for nbytes, path, name in sorted(sized, reverse=True):
+        wanted = getattr((constraints or {}).get(name), "sharding_types", None) or [ShardingType.TABLE_WISE.value]
+        if wanted[0] == ShardingType.ROW_WISE.value and world_size > 1:
+            # equal row blocks on every device
+            for i in range(world_size):
+                load[i] += nbytes // world_size
+            plan.setdefault(path, {})[name] = ParameterSharding(sharding_type=ShardingType.ROW_WISE.value, compute_kernel="quant", ranks=list(range(world_size)))
+            continue
+        if wanted[0] == ShardingType.COLUMN_WISE.value and world_size > 1:
+            # as many equal column ranges as divide the width in multiples of 16, on the lightest devices
+            n = max((k for k in range(1, world_size + 1) if dims[(path, name)] % (16 * k) == 0), default=1)
+            ranks = sorted(range(world_size), key=lambda i: load[i])[:n]
+            for i in ranks:
+                load[i] += nbytes // n
+            plan.setdefault(path, {})[name] = ParameterSharding(sharding_type=ShardingType.COLUMN_WISE.value if n > 1 else ShardingType.TABLE_WISE.value,
+                                                                compute_kernel="quant", ranks=ranks)
+            continue
         r = min(range(world_size), key=lambda i: load[i])
         load[r] += nbytes
         plan.setdefault(path, {})[name] = ParameterSharding(sharding_type=ShardingType.TABLE_WISE.value, compute_kernel="quant", ranks=[r])
