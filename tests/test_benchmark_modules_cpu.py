@@ -52,3 +52,16 @@ def test_benchmark_zch_collision_rates():
     # zero-collision hashing keeps distinct ids apart where a plain modulo does not
     assert zch["collision_rate"] * 3 < mod["collision_rate"]
     assert 0.0 <= zch["auc"] <= 1.0 and zch["train_qps"] > 0
+
+
+def test_top_level_ebc_benchmark_runs():
+    import importlib.util
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "ebc_benchmarks.py")
+    spec = importlib.util.spec_from_file_location("ebc_benchmarks_main", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.get_shrunk_dlrm_num_embeddings(128)[0] == 45833188 // 128 and mod.get_shrunk_dlrm_num_embeddings(128)[1] == 36746
+    e, es, f, fs, speedup = mod.get_ebc_comparison(mod._tables([50, 20], dim=8), torch.device("cpu"), epochs=2, batch_size=8, num_batches=2)
+    assert e > 0 and f > 0 and speedup > 0
