@@ -146,3 +146,22 @@ def test_shard_quant_model_honours_constraints():
     assert p["rw_sum"].sharding_type == "row_wise" and p["rw_sum"].ranks == [0, 1, 2]
     assert p["cw"].sharding_type == "column_wise" and len(p["cw"].ranks) == 3 and p["tw"].sharding_type == "table_wise"
     torch.testing.assert_close(sharded(kjt).values(), want, rtol=1e-5, atol=1e-6)
+
+
+def test_shard_quant_model_splits_tables_that_do_not_fit():
+    from torchrec_b200.inference.modules import shard_quant_model
+
+    q, tables = _quantized(DataType.INT8, False)
+    kjt = _kjt(tables, 4, False, 9)
+    want = q(kjt).values().clone()
+    sizes = {n: h.weight.numel() for n, h in q.embedding_bags.items()}
+    # room for the largest table's half only: it must be split, the small ones still go whole
+    sharded, plan = shard_quant_model(torch.nn.Sequential(q), world_size=2, compute_device="cpu", device_memory_size=max(sizes.values()) - 1)
+    kinds = {n: ps.sharding_type for n, ps in plan.plan["0"].items()}
+    biggest = max(sizes, key=sizes.get)
+    assert kinds[biggest] == "row_wise"
+    torch.testing.assert_close(sharded(kjt).values(), want, rtol=1e-5, atol=1e-6)
+    # with room to spare everything stays table-wise
+    q2, _ = _quantized(DataType.INT8, False)
+    _, roomy = shard_quant_model(torch.nn.Sequential(q2), world_size=2, compute_device="cpu", device_memory_size=10 * sum(sizes.values()))
+    assert {ps.sharding_type for ps in roomy.plan["0"].values()} == {"table_wise"}

@@ -209,7 +209,8 @@ def shard_quant_model(model: nn.Module, world_size: int = 1, compute_device: str
                       device_memory_size: Optional[int] = None, constraints: Optional[Dict[str, Any]] = None, ddr_cap: Optional[int] = None) -> Tuple[nn.Module, ShardingPlan]:
     """Place the quantized tables of ``model`` on ``world_size`` devices of this host and swap the quantized modules for their sharded
     form.  Default: table-wise, largest table first onto the lightest device.  A table whose entry in ``constraints`` (an object with
-    ``sharding_types``, e.g. ``ParameterConstraints``) asks for ``row_wise`` or ``column_wise`` first is placed that way."""
+    ``sharding_types``, e.g. ``ParameterConstraints``) asks for ``row_wise`` or ``column_wise`` first is placed that way; with ``device_memory_size`` (bytes per device) a table that does not fit on the
+    lightest device is split row-wise over all devices."""
     env = ShardingEnv.from_local(world_size=world_size, rank=0)
     device = torch.device(compute_device)
     plan: Dict[str, Dict[str, ParameterSharding]] = {}
@@ -229,6 +230,8 @@ def shard_quant_model(model: nn.Module, world_size: int = 1, compute_device: str
             dims[(path, cfg.name)] = cfg.embedding_dim
     for nbytes, path, name in sorted(sized, reverse=True):
         wanted = getattr((constraints or {}).get(name), "sharding_types", None) or [ShardingType.TABLE_WISE.value]
+        if device_memory_size is not None and wanted[0] == ShardingType.TABLE_WISE.value and min(load) + nbytes > device_memory_size:
+            wanted = [ShardingType.ROW_WISE.value]  # does not fit on any single device next to what is already there: split its rows
         if wanted[0] == ShardingType.ROW_WISE.value and world_size > 1:
             # equal row blocks on every device
             for i in range(world_size):
