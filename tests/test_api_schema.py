@@ -66,3 +66,16 @@ def test_signature_is_call_compatible(name):
     for p in params:
         if p.name not in [e[0] for e in expected] and p.kind in (p.POSITIONAL_OR_KEYWORD, p.KEYWORD_ONLY):
             assert p.default is not inspect.Parameter.empty, f"{name}: extra parameter {p.name} has no default"
+
+
+def test_package_level_exports():
+    import torchrec_b200 as t
+    import torchrec_b200.distributed as d
+
+    for name in ("DataType", "EmbeddingBagConfig", "EmbeddingConfig", "PoolingType", "EmbeddingBagCollection", "EmbeddingBagCollectionInterface", "EmbeddingCollection",
+                 "JaggedTensor", "KeyedJaggedTensor", "KeyedTensor", "Multistreamable", "Pipelineable", "__version__", "distributed", "quant", "tracer"):
+        assert getattr(t, name) is not None, name
+    for name in ("get_local_rank", "get_local_size", "DistributedModelParallel", "DataLoadingThread", "EvalPipelineSparseDist", "PrefetchTrainPipelineSparseDist",
+                 "TrainPipeline", "TrainPipelineBase", "TrainPipelineSparseDist", "Awaitable", "ModuleSharder", "NoWait", "ParameterSharding", "ShardedModule",
+                 "ShardedTensor", "ShardingEnv", "ShardingPlanner", "get_unsharded_module_names", "sharded_model_copy"):
+        assert getattr(d, name) is not None, name

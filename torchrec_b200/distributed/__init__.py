@@ -25,9 +25,8 @@ def __getattr__(name):
         from torchrec_b200.distributed import model_parallel
 
         return getattr(model_parallel, name)
-    if name in ("TrainPipelineBase", "TrainPipelineSparseDist", "TrainPipelineFusedSparseDist", "TrainPipelineSemiSync",
-                "PrefetchTrainPipelineSparseDist", "EvalPipelineSparseDist", "StagedTrainPipeline"):
-        from torchrec_b200.distributed.train_pipeline import train_pipelines
-
-        return getattr(train_pipelines, name)
+    if name in ("TrainPipeline", "TrainPipelineBase", "TrainPipelineSparseDist", "TrainPipelineFusedSparseDist", "TrainPipelineSemiSync",
+                "PrefetchTrainPipelineSparseDist", "EvalPipelineSparseDist", "StagedTrainPipeline", "DataLoadingThread", "PipelinedPostproc"):
+        from torchrec_b200.distributed import train_pipeline
+        return getattr(train_pipeline, name)
     raise AttributeError(name)
