@@ -65,3 +65,14 @@ def test_top_level_ebc_benchmark_runs():
     assert mod.get_shrunk_dlrm_num_embeddings(128)[0] == 45833188 // 128 and mod.get_shrunk_dlrm_num_embeddings(128)[1] == 36746
     e, es, f, fs, speedup = mod.get_ebc_comparison(mod._tables([50, 20], dim=8), torch.device("cpu"), epochs=2, batch_size=8, num_batches=2)
     assert e > 0 and f > 0 and speedup > 0
+
+
+def test_count_dataset_distributions():
+    from torchrec_b200.distributed.benchmark.benchmark_zch.count_dataset_distributions import count_distributions, main
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    kjt = KeyedJaggedTensor(keys=["a"], values=torch.tensor([7, 7, 7, 7, 7, 7, 1, 2, 3, 4]), lengths=torch.tensor([10]))
+    r = count_distributions([kjt], top_k=1)["a"]
+    assert r["lookups"] == 10 and r["distinct_ids"] == 5 and abs(r["top_1_share"] - 0.6) < 1e-9 and r["ids_for_50pct"] == 1 and r["ids_for_90pct"] == 4
+    res = main(["--num_batches", "2", "--batch_size", "64", "--distinct_ids", "50"])
+    assert set(res) == {"f0", "f1"} and res["f0"]["lookups"] == 128
