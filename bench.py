@@ -11,11 +11,17 @@ lookup backward, Adagrad on dense parameters, planner-chosen sharding, fp16 forw
 Synthetic data, random-init weights.
 
 Prints ONE JSON line on rank 0.  ``value`` is device-timed (CUDA events, max over ranks) over steps whose inputs
-already sit on the device; ``e2e`` runs the same steps through ``TrainPipelineSparseDist.progress`` from pinned
-host memory, including the host-to-device copy of every batch and a device-to-host read of the loss.
+already sit on the device; ``e2e`` runs the same steps through the public pipeline API (``TrainPipelineGraphed.progress``)
+from pinned host memory, including the host-to-device copy of every batch and a device-to-host read of the loss.
 
-``--impl reference`` is the arm that would run the unmodified reference package; it needs ``fbgemm_gpu``, which
-is not installable offline, so it reports ``unavailable``.
+Arms (``--impl``):
+  ours        fused sparse engine over peer memory, tcgen05 GEMMs, peer-memory gradient averaging, one-launch dense
+              optimizer, the whole step replayed as one CUDA graph.  After its own measurement it also times the
+              ``nccl_torch`` arm for a few steps in the same process and reports ``vs_baseline`` against it.
+  nccl_torch  the same model on library code only: NCCL collectives for every exchange, cuBLAS GEMMs, the embedding
+              lookup / backward / row-wise Adagrad composed from torch ops, DistributedDataParallel, torch.optim.Adagrad.
+  reference   the unmodified reference package; it needs ``fbgemm_gpu``, which is not installable offline, so this arm
+              reports ``unavailable``.
 """
 from __future__ import annotations
 
@@ -47,13 +53,15 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=50)
     p.add_argument("--warmup", type=int, default=5)
-    p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference", "baseline"])
+    p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference", "nccl_torch"])
+    p.add_argument("--baseline-steps", type=int, default=4, help="timed steps of the nccl_torch arm inside an 'ours' run (0 = skip)")
+    p.add_argument("--no-parity", action="store_true", help="skip the bf16-vs-fp32 loss parity check")
     p.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
     p.add_argument("--row-cap", type=int, default=0, help="cap table rows (smoke runs on small memory); 0 = full size")
     p.add_argument("--pool", type=int, default=4, help="number of distinct synthetic batches that are cycled")
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--loop", choices=["pipeline", "plain"], default="pipeline",
-                   help="timed loop: TrainPipelineSparseDist over device-resident batches (input distribution of the next batch on side streams) or a plain forward/backward/step loop")
+    p.add_argument("--loop", choices=["graph", "pipeline", "plain"], default="graph",
+                   help="timed loop: TrainPipelineGraphed (whole step replayed as one CUDA graph), TrainPipelineSparseDist, or a plain forward/backward/step loop")
     p.add_argument("--breakdown", action="store_true", help="print a per-phase device-time breakdown to stderr")
     p.add_argument("--kernel-table", action="store_true", help="print per-kernel device time of one step to stderr (diagnostic)")
     p.add_argument("--host-profile", action="store_true", help="print the host-side profile (cProfile) of 10 untimed steps to stderr (diagnostic)")
@@ -145,6 +153,275 @@ class ClockSampler:
         return out
 
 
+def _set_arm(arm: str) -> None:
+    """Process-wide switches of an arm (read at call time by the package)."""
+    from torchrec_b200.ops import dense_ops, tbe
+
+    ours = arm == "ours"
+    os.environ["TRB200_PEER_EXCHANGE"] = "1" if ours else "0"
+    dense_ops.set_gemm_backend("tcgen05" if ours else "cublas")
+    tbe.set_tbe_backend("kernel" if ours else "torch")
+    dense_ops.set_dense_compute_dtype(__import__("torch").bfloat16)
+
+
+def _build(args, arm: str, device, world: int):
+    import torch
+    import torch.distributed as dist
+
+    from torchrec_b200.distributed.embeddingbag import EmbeddingBagCollectionSharder
+    from torchrec_b200.distributed.fbgemm_qcomm_codec import CommType, QCommsConfig, get_qcomm_codecs_registry
+    from torchrec_b200.distributed.model_parallel import DefaultDataParallelWrapper, DistributedModelParallel
+    from torchrec_b200.distributed.peer_data_parallel import PeerDataParallelWrapper
+    from torchrec_b200.distributed.planner import EmbeddingShardingPlanner, ParameterConstraints, Topology
+    from torchrec_b200.distributed.planner.stats import NoopEmbeddingStats
+    from torchrec_b200.distributed.types import ShardingEnv
+    from torchrec_b200.models.dlrm import DLRM_DCN, DLRMTrain
+    from torchrec_b200.modules.embedding_configs import DataType, EmbeddingBagConfig
+    from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
+    from torchrec_b200.optim.apply_optimizer_in_backward import apply_optimizer_in_backward
+    from torchrec_b200.optim.fused_dense import FusedDenseOptimizer
+    from torchrec_b200.optim.keyed import CombinedOptimizer, KeyedOptimizerWrapper
+    from torchrec_b200.optim.optimizers import in_backward_optimizer_filter
+    from torchrec_b200.optim.rowwise_adagrad import RowWiseAdagrad
+
+    _set_arm(arm)
+    rows = [min(r, args.row_cap) if args.row_cap else r for r in ROWS]
+    B_local = args.global_batch // world
+    keys = [f"cat_{i}" for i in range(len(rows))]
+    tables = [EmbeddingBagConfig(name=f"t_{k}", embedding_dim=EMB_DIM, num_embeddings=r, feature_names=[k]) for k, r in zip(keys, rows)]
+    ebc = EmbeddingBagCollection(tables=tables, device=torch.device("meta"))
+    torch.manual_seed(4321)
+    model = DLRMTrain(DLRM_DCN(ebc, dense_in_features=DENSE_IN, dense_arch_layer_sizes=DENSE_ARCH, over_arch_layer_sizes=OVER_ARCH,
+                               dcn_num_layers=DCN_LAYERS, dcn_low_rank_dim=DCN_RANK, dense_device=device))
+    apply_optimizer_in_backward(RowWiseAdagrad, model.model.sparse_arch.parameters(), {"lr": 0.005, "eps": 1e-8})
+    qcomm = get_qcomm_codecs_registry(QCommsConfig(forward_precision=CommType.FP16, backward_precision=CommType.BF16), device=device)
+    sharders = [EmbeddingBagCollectionSharder(fused_params={"output_dtype": DataType.BF16}, qcomm_codecs_registry=qcomm)]
+    constraints = {f"t_{k}": ParameterConstraints(pooling_factors=[float(p)]) for k, p in zip(keys, POOLING)}
+    planner = EmbeddingShardingPlanner(topology=Topology(world_size=world, local_world_size=world, compute_device="cuda"),
+                                       batch_size=B_local, constraints=constraints, stats=NoopEmbeddingStats())
+    plan = planner.collective_plan(model, sharders, dist.group.WORLD)
+    wrapper = PeerDataParallelWrapper() if arm == "ours" else DefaultDataParallelWrapper()
+    dmp = DistributedModelParallel(model, env=ShardingEnv.from_process_group(dist.group.WORLD), device=device, plan=plan, sharders=sharders,
+                                   data_parallel_wrapper=wrapper)
+    dense_params = dict(in_backward_optimizer_filter(dmp.named_parameters()))
+    if arm == "ours":
+        dense_opt = KeyedOptimizerWrapper(dense_params, lambda p: FusedDenseOptimizer(p, "adagrad", lr=0.01))
+    else:
+        dense_opt = KeyedOptimizerWrapper(dense_params, lambda p: torch.optim.Adagrad(p, lr=0.01, foreach=True))
+    optimizer = CombinedOptimizer([dmp.fused_optimizer, dense_opt])
+    shard_types: Dict[str, int] = {}
+    cols_on_rank = [0] * world
+    for ps in plan.plan["model.sparse_arch.embedding_bag_collection"].values():
+        shard_types[ps.sharding_type] = shard_types.get(ps.sharding_type, 0) + 1
+        if ps.sharding_spec is None:
+            continue
+        for sh in ps.sharding_spec.shards:
+            r = int(str(sh.placement).split("/")[0].split(":")[1])
+            cols_on_rank[r] += sh.shard_sizes[1]
+    return dmp, optimizer, shard_types, cols_on_rank, keys, rows
+
+
+def _timed(torch, dist, device, fn, n_steps: int) -> float:
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n_steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+def run_arm(args, arm: str, device, rank: int, world: int, local_rank: int, host_batches, steps: int, warmup: int, full: bool) -> Dict[str, Any]:
+    """Build the model of ``arm``, run ``warmup`` untimed and ``steps`` timed steps; ``full`` adds the end-to-end loop and diagnostics."""
+    import torch
+    import torch.distributed as dist
+
+    from torchrec_b200.distributed.train_pipeline import TrainPipelineGraphed, TrainPipelineSparseDist
+
+    dmp, optimizer, shard_types, cols_on_rank, keys, rows = _build(args, arm, device, world)
+    dev_batches = [b.to(device) for b in host_batches]
+    torch.cuda.synchronize()
+    loop = args.loop if arm == "ours" else "pipeline"
+    feed_mode = {"host": False}
+
+    def feed():
+        i = 0
+        while True:
+            src = host_batches if feed_mode["host"] else dev_batches
+            yield src[i % len(src)]
+            i += 1
+
+    it = feed()
+
+    def plain_step(batch):
+        optimizer.zero_grad()
+        loss, _ = dmp(batch)
+        loss.backward()
+        optimizer.step()
+        return loss
+
+    if loop == "graph":
+        pipe = TrainPipelineGraphed(dmp, optimizer, device, warmup_steps=3)
+    elif loop == "pipeline":
+        pipe = TrainPipelineSparseDist(dmp, optimizer, device)
+    else:
+        pipe = None
+
+    def pstep(_i):
+        if pipe is None:
+            out = plain_step(dev_batches[_i % len(dev_batches)])
+            return (out,)
+        return pipe.progress(it)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0 and full:
+        sampler.start()
+    for i in range(max(warmup, 3) + 2):
+        pstep(i)
+    torch.cuda.synchronize()
+    sampler.mark_begin()
+    total_ms = _timed(torch, dist, device, pstep, steps)
+    sampler.mark_end()
+    clocks = sampler.stop() if (rank == 0 and full) else {}
+    ms_per_step = total_ms / steps
+    res: Dict[str, Any] = {"ms_per_step": ms_per_step, "value": args.global_batch / (ms_per_step / 1e3), "clocks": clocks, "shard_types": shard_types,
+                           "cols_on_rank": cols_on_rank, "loop": loop}
+    if loop == "graph":
+        res["graph_captured"] = bool(pipe.captured)
+        res["eager_steps_after_capture"] = int(pipe.eager_steps)
+    if not full:
+        del pipe, dmp, optimizer, dev_batches
+        return res
+
+    # ---- diagnostic: how long the host needs to issue a step (no synchronisation inside) -------------------------------------
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(2):
+        pstep(i)
+    res["host_issue_ms"] = (time.perf_counter() - t0) * 1e3 / 2
+    torch.cuda.synchronize()
+
+    # ---- this package's kernel launches in one (untimed) step --------------------------------------------------------------------
+    launches = None
+    try:
+        from torch.profiler import ProfilerActivity, profile
+
+        acts = [ProfilerActivity.CUDA] + ([ProfilerActivity.CPU] if args.kernel_table else [])
+        with profile(activities=acts) as prof:
+            pstep(0)
+            torch.cuda.synchronize()
+        kernels = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+        own = [e for e in kernels if ("trb::" in e.name or "trb_" in e.name)]
+        launches = len(own) * steps
+        res["kernels_per_step"] = {"own": len(own), "all": len(kernels)}
+        if args.kernel_table and rank == 0:
+            agg: Dict[str, List[float]] = {}
+            for e in kernels:
+                a = agg.setdefault(e.name[:110], [0.0, 0])
+                a[0] += e.device_time_total if hasattr(e, "device_time_total") else e.cuda_time_total
+                a[1] += 1
+            tot = sum(v[0] for v in agg.values())
+            print(f"kernel table (one step, {tot / 1e3:.3f} ms of device time):", file=sys.stderr)
+            for name, (t, n) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:50]:
+                print(f"  {t / 1e3:8.3f} ms  x{n:<3d} {name}", file=sys.stderr)
+    except Exception as e:  # the profiler is a diagnostic: never fail the run on it
+        print(f"profiler pass failed: {type(e).__name__}: {e}", file=sys.stderr)
+    res["gpu_launches"] = launches
+
+    # ---- end to end: pinned host batches in, loss out, through the public pipeline API -----------------------------------------
+    if not args.no_e2e:
+        feed_mode["host"] = True
+        b0 = host_batches[0]
+        h2d_bytes = sum(t.numel() * t.element_size() for t in (b0.dense_features, b0.labels, b0.sparse_features.values(), b0.sparse_features.lengths()))
+        loss_bufs = [torch.empty((), dtype=torch.float32).pin_memory() for _ in range(2)]
+        loss_events: List[Optional[torch.cuda.Event]] = [None, None]
+        sink: List[float] = []
+
+        def e2e_step(i):
+            out = pstep(i)
+            k = i % 2
+            if loss_events[k] is not None:
+                loss_events[k].synchronize()
+                sink.append(float(loss_bufs[k]))
+            loss_bufs[k].copy_(out[0].detach().float().reshape(()), non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            loss_events[k] = ev
+
+        for i in range(max(warmup, 3) + 3):  # + the device-resident batches still in flight from the first phase
+            e2e_step(i)
+        e2e_ms = _timed(torch, dist, device, e2e_step, steps)
+        for ev, buf in zip(loss_events, loss_bufs):
+            if ev is not None:
+                ev.synchronize()
+                sink.append(float(buf))
+        assert all(v == v for v in sink), "non-finite loss"
+        api = {"graph": "TrainPipelineGraphed.progress", "pipeline": "TrainPipelineSparseDist.progress", "plain": "forward/backward/step"}[loop]
+        res["e2e"] = {"value": args.global_batch / (e2e_ms / steps / 1e3), "unit": "samples/s", "ms_per_step": e2e_ms / steps,
+                      "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": 4, "api": api, "last_loss": sink[-1] if sink else None,
+                      "read_back": "loss copied to pinned memory every step, consumed on the host two steps later"}
+    # ---- balance of the plan: ids every rank's lookup receives per step ---------------------------------------------------------
+    try:
+        from torchrec_b200.distributed.embeddingbag import ShardedEmbeddingBagCollection
+
+        for m in dmp.modules():
+            if isinstance(m, ShardedEmbeddingBagCollection) and getattr(m, "_engine", None) is not None and m._engine.recv_counts:
+                rc = m._engine.recv_counts
+                res["lookup_ids_per_rank"] = {"max": max(rc), "mean": sum(rc) / len(rc), "max_over_mean": max(rc) / max(sum(rc) / len(rc), 1)}
+    except Exception:
+        pass
+    from torchrec_b200.distributed import peer_memory
+
+    peer_memory.check_all()
+    del pipe, dmp, optimizer, dev_batches
+    return res
+
+
+def loss_parity(device) -> Dict[str, Any]:
+    """Loss after 50 steps with bf16 towers and with fp32 towers, same seed, same data (small tables, batch 8192, one GPU)."""
+    import torch
+
+    from torchrec_b200.datasets.random import RandomRecDataset
+    from torchrec_b200.models.dlrm import DLRM_DCN, DLRMTrain
+    from torchrec_b200.modules.embedding_configs import EmbeddingBagConfig
+    from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
+    from torchrec_b200.ops import dense_ops
+
+    rows = [min(r, 20000) for r in ROWS]
+    keys = [f"cat_{i}" for i in range(len(rows))]
+    ds = RandomRecDataset(keys=keys, batch_size=8192, hash_sizes=rows, ids_per_features=POOLING, min_ids_per_features=POOLING, num_dense=DENSE_IN,
+                          manual_seed=99, num_generated_batches=4, zipf_s=ZIPF_S, idx_dtype=torch.int64, label_positive_rate=0.25, dense_log_transform=True)
+    batches = [b.to(device) for b in ds.batch_generator._generated_batches]
+    out = {}
+    for name, dt in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        dense_ops.set_dense_compute_dtype(dt)
+        torch.manual_seed(7)
+        tables = [EmbeddingBagConfig(name=f"t_{k}", embedding_dim=EMB_DIM, num_embeddings=r, feature_names=[k]) for k, r in zip(keys, rows)]
+        model = DLRMTrain(DLRM_DCN(EmbeddingBagCollection(tables=tables, device=device), dense_in_features=DENSE_IN, dense_arch_layer_sizes=DENSE_ARCH,
+                                   over_arch_layer_sizes=OVER_ARCH, dcn_num_layers=DCN_LAYERS, dcn_low_rank_dim=DCN_RANK, dense_device=device))
+        opt = torch.optim.Adagrad(model.parameters(), lr=0.01)
+        losses = []
+        for i in range(50):
+            opt.zero_grad()
+            loss, _ = model(batches[i % len(batches)])
+            loss.backward()
+            opt.step()
+            losses.append(loss.detach())
+        out[name] = float(torch.stack(losses[-4:]).float().mean())
+        out[name + "_first"] = float(losses[0])
+        del model, opt
+    dense_ops.set_dense_compute_dtype(torch.bfloat16)
+    out["rel_diff"] = abs(out["bf16"] - out["fp32"]) / max(abs(out["fp32"]), 1e-12)
+    out["what"] = "mean loss of steps 47-50 of 50, DLRM-DCNv2 towers, tables capped at 20000 rows, batch 8192, Adagrad lr 0.01, same seed and data"
+    return out
+
+
 def main() -> None:
     args = parse_args()
     if args.impl == "reference":
@@ -155,6 +432,9 @@ def main() -> None:
     sys.stdout.flush()
     real_stdout = os.dup(1)
     os.dup2(2, 1)
+
+    import datetime
+    import gc
 
     import torch
     import torch.distributed as dist
@@ -172,244 +452,71 @@ def main() -> None:
             s.bind(("127.0.0.1", 0))
             os.environ["MASTER_PORT"] = str(s.getsockname()[1])
     os.environ.setdefault("LOCAL_WORLD_SIZE", str(world))
-    import datetime
-
-    # a short collective timeout: a rank that falls out of step ends the job in minutes, not after the 10-minute default
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # the library's banner must not land in front of the JSON line on stdout
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device, timeout=datetime.timedelta(seconds=120))
+    # a short collective timeout: a rank that falls out of step ends the job in minutes, not after the 10-minute default
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device, timeout=datetime.timedelta(seconds=180))
 
     from torchrec_b200.datasets.random import RandomRecDataset
-    from torchrec_b200.distributed.embeddingbag import EmbeddingBagCollectionSharder
-    from torchrec_b200.distributed.fbgemm_qcomm_codec import CommType, QCommsConfig, get_qcomm_codecs_registry
-    from torchrec_b200.distributed.model_parallel import DistributedModelParallel
-    from torchrec_b200.distributed.planner import EmbeddingShardingPlanner, ParameterConstraints, Topology
-    from torchrec_b200.distributed.planner.stats import NoopEmbeddingStats
-    from torchrec_b200.distributed.train_pipeline import TrainPipelineSparseDist
-    from torchrec_b200.distributed.types import ShardingEnv
-    from torchrec_b200.models.dlrm import DLRM_DCN, DLRMTrain
-    from torchrec_b200.modules.embedding_configs import DataType, EmbeddingBagConfig
-    from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
     from torchrec_b200.ops import _ext, dense_ops
-    from torchrec_b200.optim.apply_optimizer_in_backward import apply_optimizer_in_backward
-    from torchrec_b200.optim.keyed import CombinedOptimizer, KeyedOptimizerWrapper
-    from torchrec_b200.optim.optimizers import in_backward_optimizer_filter
-    from torchrec_b200.optim.rowwise_adagrad import RowWiseAdagrad
 
     _ext.require_cuda_ext("bench")
-    baseline = args.impl == "baseline"
-    if baseline:
-        dense_ops.set_gemm_backend("cublas")
-    dense_ops.set_dense_compute_dtype(torch.bfloat16)
-
     rows = [min(r, args.row_cap) if args.row_cap else r for r in ROWS]
     B_local = args.global_batch // world
     keys = [f"cat_{i}" for i in range(len(rows))]
-    tables = [EmbeddingBagConfig(name=f"t_{k}", embedding_dim=EMB_DIM, num_embeddings=r, feature_names=[k]) for k, r in zip(keys, rows)]
-    ebc = EmbeddingBagCollection(tables=tables, device=torch.device("meta"))
-    model = DLRMTrain(DLRM_DCN(ebc, dense_in_features=DENSE_IN, dense_arch_layer_sizes=DENSE_ARCH, over_arch_layer_sizes=OVER_ARCH,
-                               dcn_num_layers=DCN_LAYERS, dcn_low_rank_dim=DCN_RANK, dense_device=device))
-    apply_optimizer_in_backward(RowWiseAdagrad, model.model.sparse_arch.parameters(), {"lr": 0.005, "eps": 1e-8})
-
-    qcomm = get_qcomm_codecs_registry(QCommsConfig(forward_precision=CommType.FP16, backward_precision=CommType.BF16), device=device)
-    sharders = [EmbeddingBagCollectionSharder(fused_params={"output_dtype": DataType.BF16}, qcomm_codecs_registry=qcomm)]
-    constraints = {f"t_{k}": ParameterConstraints(pooling_factors=[float(p)]) for k, p in zip(keys, POOLING)}
-    planner = EmbeddingShardingPlanner(topology=Topology(world_size=world, local_world_size=world, compute_device="cuda"),
-                                       batch_size=B_local, constraints=constraints, stats=NoopEmbeddingStats())
-    plan = planner.collective_plan(model, sharders, dist.group.WORLD)
-    dmp = DistributedModelParallel(model, env=ShardingEnv.from_process_group(dist.group.WORLD), device=device, plan=plan, sharders=sharders)
-    dense_opt = KeyedOptimizerWrapper(dict(in_backward_optimizer_filter(dmp.named_parameters())), lambda p: torch.optim.Adagrad(p, lr=0.01, foreach=True))
-    optimizer = CombinedOptimizer([dmp.fused_optimizer, dense_opt])
-    shard_types: Dict[str, int] = {}
-    # algorithmic bytes of the embedding exchange per rank and step: pooled rows of the samples other ranks own (forward, 2 bytes
-    # per element) and the same volume of gradient rows (backward); a row-wise table moves its partial sums through a reduce-scatter
-    cols_on_rank = [0] * world
-    for ps in plan.plan["model.sparse_arch.embedding_bag_collection"].values():
-        shard_types[ps.sharding_type] = shard_types.get(ps.sharding_type, 0) + 1
-        if ps.sharding_spec is None:
-            continue
-        for sh in ps.sharding_spec.shards:
-            r = int(str(sh.placement).split("/")[0].split(":")[1])
-            cols_on_rank[r] += sh.shard_sizes[1]
-    exchange_bytes = max(cols_on_rank) * args.global_batch * (world - 1) // max(world, 1) * 2
-
     ds = RandomRecDataset(keys=keys, batch_size=B_local, hash_sizes=rows, ids_per_features=POOLING, min_ids_per_features=POOLING,
                           num_dense=DENSE_IN, manual_seed=1234 + rank, num_generated_batches=args.pool, zipf_s=ZIPF_S,
                           idx_dtype=torch.int32, label_positive_rate=0.25, dense_log_transform=True)
     host_batches = [b.pin_memory() for b in ds.batch_generator._generated_batches]
-    dev_batches = [b.to(device) for b in host_batches]
-    h2d_bytes = sum(t.numel() * t.element_size() for t in (host_batches[0].dense_features, host_batches[0].labels,
-                                                            host_batches[0].sparse_features.values(), host_batches[0].sparse_features.lengths()))
 
-    def step(batch):
-        optimizer.zero_grad()
-        loss, _ = dmp(batch)
-        loss.backward()
-        optimizer.step()
-        return loss
+    main_res = run_arm(args, args.impl, device, rank, world, local_rank, host_batches, args.steps, args.warmup, full=True)
+    gc.collect()
+    torch.cuda.empty_cache()
 
-    def timed(fn, n_steps: int) -> float:
+    baseline = None
+    if args.impl == "ours" and args.baseline_steps > 0:
+        try:
+            b = run_arm(args, "nccl_torch", device, rank, world, local_rank, host_batches, args.baseline_steps, 3, full=False)
+            baseline = {"impl": "nccl_torch", "value": b["value"], "ms_per_step": b["ms_per_step"], "steps": args.baseline_steps, "warmup": 5,
+                        "what": "same model, data and plan on library code only: NCCL collectives, cuBLAS GEMMs, embedding lookup/backward/row-wise Adagrad "
+                                "composed from torch ops, DistributedDataParallel, torch.optim.Adagrad, TrainPipelineSparseDist; timed in this process after the main arm"}
+        except Exception as e:
+            baseline = {"impl": "nccl_torch", "failed": f"{type(e).__name__}: {e}"[:300]}
+        gc.collect()
+        torch.cuda.empty_cache()
+    parity = None
+    if args.impl == "ours" and not args.no_parity:
+        if rank == 0:
+            try:
+                parity = loss_parity(device)
+            except Exception as e:
+                parity = {"failed": f"{type(e).__name__}: {e}"[:300]}
         dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(n_steps):
-            fn(i)
-        e1.record()
-        torch.cuda.synchronize()
-        dist.barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
-    # ---- device-timed steps (inputs resident on the device; 4 distinct batches of ~60 MB ids each are cycled and the
-    #      embedding tables (>100 GB) are far larger than L2, so no step re-reads cached inputs) -----------------
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    for i in range(args.warmup):
-        step(dev_batches[i % len(dev_batches)])
-    plain_ms = None
-    if args.loop == "plain":
-        sampler.mark_begin()
-        total_ms = timed(lambda i: step(dev_batches[i % len(dev_batches)]), args.steps)
-        sampler.mark_end()
-        clocks = sampler.stop() if rank == 0 else {}
-        ms_per_step = total_ms / args.steps
-        value = args.global_batch / (ms_per_step / 1e3)
-
-    # ---- diagnostic: how long the host needs to issue a step (no synchronisation inside); close to ms_per_step = host-bound ------
-    torch.cuda.synchronize()
-    dist.barrier()
-    t_issue0 = time.perf_counter()
-    for i in range(2):  # two steps stay well below the depth of the launch queue, so the host never waits for the device here
-        step(dev_batches[i % len(dev_batches)])
-    host_issue_ms = (time.perf_counter() - t_issue0) * 1e3 / 2
-    torch.cuda.synchronize()
-
-    if args.host_profile and rank == 0:
-        import cProfile
-        import io
-        import pstats
-
-        pr = cProfile.Profile()
-        pr.enable()
-        for i in range(10):
-            step(dev_batches[i % len(dev_batches)])
-        pr.disable()
-        torch.cuda.synchronize()
-        for key in ("tottime", "cumulative"):
-            buf = io.StringIO()
-            pstats.Stats(pr, stream=buf).sort_stats(key).print_stats(45)
-            print(f"host profile of 10 steps by {key}:\n" + buf.getvalue()[:9000], file=sys.stderr)
-    elif args.host_profile:
-        for i in range(10):
-            step(dev_batches[i % len(dev_batches)])
-
-    # ---- count this package's kernel launches in one (untimed) step ----------------------------------------------
-    launches = None
-    try:
-        from torch.profiler import ProfilerActivity, profile
-
-        acts = [ProfilerActivity.CUDA] + ([ProfilerActivity.CPU] if args.kernel_table else [])
-        with profile(activities=acts, record_shapes=bool(args.kernel_table)) as prof:
-            step(dev_batches[0])
-            torch.cuda.synchronize()
-        own = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and ("trb::" in e.name or "trb_" in e.name)]
-        launches = len(own) * args.steps
-        if args.kernel_table and rank == 0:
-            agg: Dict[str, List[float]] = {}
-            for e in prof.events():
-                if e.device_type == torch.autograd.DeviceType.CUDA:
-                    a = agg.setdefault(e.name[:110], [0.0, 0])
-                    a[0] += e.device_time_total if hasattr(e, "device_time_total") else e.cuda_time_total
-                    a[1] += 1
-            tot = sum(v[0] for v in agg.values())
-            print(f"kernel table (one step, {tot / 1e3:.3f} ms of device time):", file=sys.stderr)
-            for name, (t, n) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:45]:
-                print(f"  {t / 1e3:8.3f} ms  x{n:<3d} {name}", file=sys.stderr)
-            print("operators by own device time (with input shapes):", file=sys.stderr)
-            rows = sorted(prof.key_averages(group_by_input_shape=True), key=lambda r: -getattr(r, "self_device_time_total", 0.0))
-            for r in rows[:30]:
-                print(f"  {getattr(r, 'self_device_time_total', 0.0) / 1e3:8.3f} ms  x{r.count:<3d} {r.key[:50]:50s} {str(r.input_shapes)[:150]}", file=sys.stderr)
-    except Exception:
-        launches = None
-
-    # ---- the training pipeline: one instance serves the device-timed loop (device-resident batches) and the end-to-end loop
-    #      (pinned host batches + loss read-back); the feed switches its source between the two phases ------------------------
-    e2e = None
-    feed_mode = {"host": False}
-
-    def feed():
-        i = 0
-        while True:
-            src = host_batches if feed_mode["host"] else dev_batches
-            yield src[i % len(src)]
-            i += 1
-
-    it = feed()
-    pipe = TrainPipelineSparseDist(dmp, optimizer, device) if (args.loop == "pipeline" or not args.no_e2e) else None
-    if args.loop == "pipeline":
-        def pstep(_i):
-            return pipe.progress(it)
-
-        for i in range(max(args.warmup, 3)):
-            pstep(i)
-        sampler.mark_begin()
-        total_ms = timed(pstep, args.steps)
-        sampler.mark_end()
-        clocks = sampler.stop() if rank == 0 else {}
-        ms_per_step = total_ms / args.steps
-        value = args.global_batch / (ms_per_step / 1e3)
-    if not args.no_e2e:
-        feed_mode["host"] = True
-        # the loss of every step is copied to pinned host memory inside the step and consumed two steps later, so that the read-back
-        # does not drain the device after every step
-        loss_bufs = [torch.empty((), dtype=torch.float32).pin_memory() for _ in range(2)]
-        loss_events: List[Optional[torch.cuda.Event]] = [None, None]
-        sink: List[float] = []
-
-        def e2e_step(i):
-            out = pipe.progress(it)
-            k = i % 2
-            if loss_events[k] is not None:
-                loss_events[k].synchronize()
-                sink.append(float(loss_bufs[k]))
-            loss_bufs[k].copy_(out[0].detach().float().reshape(()), non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record()
-            loss_events[k] = ev
-
-        for i in range(max(args.warmup, 3) + 2):  # + the two device-resident batches still in flight from the first phase
-            e2e_step(i)
-        e2e_ms = timed(e2e_step, args.steps)
-        for ev, buf in zip(loss_events, loss_bufs):
-            if ev is not None:
-                ev.synchronize()
-                sink.append(float(buf))
-        assert all(v == v for v in sink), "non-finite loss"
-        e2e = {"value": args.global_batch / (e2e_ms / args.steps / 1e3), "unit": "samples/s", "ms_per_step": e2e_ms / args.steps,
-               "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": 4, "api": "TrainPipelineSparseDist.progress",
-               "read_back": "loss copied to pinned memory every step, consumed on the host two steps later"}
-
-    if args.breakdown:
-        _breakdown(torch, dmp, optimizer, dev_batches[0], rank)  # a training step: every rank takes part
 
     if rank == 0:
+        r = main_res
+        exchange_bytes = max(r["cols_on_rank"]) * args.global_batch * (world - 1) // max(world, 1) * 2
         res = {
-            "metric": "DLRM-DCNv2 train samples/sec", "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "metric": "DLRM-DCNv2 train samples/sec", "value": r["value"], "unit": "samples/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": (r["value"] / baseline["value"]) if (baseline and "value" in baseline) else None,
             "dtype": "bf16", "data": "synthetic (Zipf(1.05) ids hashed over each table, fixed pooling factors, random-init weights)",
-            "impl": "ours" if not baseline else "baseline(cublas gemm)",
+            "impl": args.impl,
             "config": {"model": "DLRM-DCNv2 (26 tables dim 128 fp32, bottom 512-256-128, 3x low-rank cross r512, top 1024-1024-512-256-1)",
-                       "global_batch": args.global_batch, "seq_len": None, "parallelism": f"planner: {shard_types} + dense DDP x{world}",
-                       "embedding_optimizer": "fused rowwise Adagrad lr 0.005", "dense_optimizer": "Adagrad",
-                       "qcomm": "fp16 fwd / bf16 bwd", "gemm": dense_ops.get_gemm_backend(), "rows": "full" if not args.row_cap else f"capped at {args.row_cap}",
+                       "global_batch": args.global_batch, "seq_len": None, "parallelism": f"planner: {r['shard_types']} + dense data parallel x{world}",
+                       "embedding_optimizer": "fused rowwise Adagrad lr 0.005", "dense_optimizer": "Adagrad lr 0.01",
+                       "qcomm": "fp16 fwd / bf16 bwd", "gemm": "tcgen05" if args.impl == "ours" else "cublas", "rows": "full" if not args.row_cap else f"capped at {args.row_cap}",
                        "l2_policy": f"inputs larger than L2: {args.pool} distinct batches cycled, tables > 100 GB",
-                       "timed_loop": "TrainPipelineSparseDist.progress over device-resident batches" if args.loop == "pipeline" else "plain forward/backward/optimizer loop"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
-            "diagnostics": {"host_issue_ms_per_step": host_issue_ms},
+                       "timed_loop": {"graph": "TrainPipelineGraphed.progress (whole step replayed as one CUDA graph) over device-resident batches",
+                                      "pipeline": "TrainPipelineSparseDist.progress over device-resident batches",
+                                      "plain": "plain forward/backward/optimizer loop"}[r["loop"]]},
+            "clocks": r["clocks"], "e2e": r.get("e2e"), "gpu_launches": r.get("gpu_launches"),
+            "baseline": baseline, "vs_baseline_is": "value / the nccl_torch arm timed in this run (the reference itself cannot be installed offline; it publishes no number for this metric)",
+            "loss_parity": parity,
+            "diagnostics": {"host_issue_ms_per_step": r.get("host_issue_ms"), "kernels_per_step": r.get("kernels_per_step"),
+                            "graph_captured": r.get("graph_captured"), "eager_steps_after_capture": r.get("eager_steps_after_capture"),
+                            "lookup_ids_per_rank": r.get("lookup_ids_per_rank")},
             "emb_a2a": {"fwd_bytes_per_step_busiest_rank": exchange_bytes, "bwd_bytes_per_step_busiest_rank": exchange_bytes,
-                        "GBps_lower_bound": (2 * exchange_bytes / (ms_per_step / 1e3) / 1e9) if world > 1 else 0.0,
+                        "GBps_lower_bound": (2 * exchange_bytes / (r["ms_per_step"] / 1e3) / 1e9) if world > 1 else 0.0,
                         "note": "algorithmic bytes of the embedding exchange over the whole step time; the exchange is fused into the lookup kernels, so it has no time of its own"},
         }
         sys.stdout.flush()
@@ -417,23 +524,6 @@ def main() -> None:
         print(json.dumps(res), flush=True)
     dist.barrier()
     dist.destroy_process_group()
-
-
-def _breakdown(torch, dmp, optimizer, batch, rank: int = 0) -> None:
-    """Device time of forward / backward / optimizer of one step (stderr; diagnostic only)."""
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-    torch.cuda.synchronize()
-    optimizer.zero_grad()
-    ev[0].record()
-    loss, _ = dmp(batch)
-    ev[1].record()
-    loss.backward()
-    ev[2].record()
-    optimizer.step()
-    ev[3].record()
-    torch.cuda.synchronize()
-    if rank == 0:
-        print(f"breakdown ms: fwd {ev[0].elapsed_time(ev[1]):.3f} bwd {ev[1].elapsed_time(ev[2]):.3f} opt {ev[2].elapsed_time(ev[3]):.3f}", file=sys.stderr)
 
 
 if __name__ == "__main__":

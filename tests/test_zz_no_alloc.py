@@ -71,7 +71,7 @@ def _call_regular(tbe, plan, grad, B, step):
         w, tbe.momentum1 if tbe.momentum1.numel() else None, tbe.momentum2 if tbe.momentum2.numel() else None, None,
         tbe._meta_tensor(w.device), plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale, grad, grad.stride(0), B,
         tbe.max_D, tbe.pooling_mode != PoolingMode.NONE, _OPT_CODE[o.optimizer], o.learning_rate,
-        o.eta if o.optimizer == EmbOptimType.LARS_SGD else o.eps, o.beta1, o.beta2, o.weight_decay, step, o.max_gradient,
+        o.eta if o.optimizer == EmbOptimType.LARS_SGD else o.eps, o.beta1, o.beta2, o.weight_decay, step, o.max_gradient, None,
     )
 
 

@@ -1,13 +1,19 @@
-// Cross-GPU synchronisation over peer-mapped memory (NVLink / NVSwitch) for the fused lookup + exchange path.
+// Cross-GPU synchronisation over peer-mapped memory (NVLink / NVSwitch) for the fused exchange paths.
 //
-// Every rank owns an int32 flag array `flags[world]` in its own memory, mapped into all peers.  Barrier number `e`
-// (e grows by one per call, the same on all ranks): rank r publishes everything it has written to peer memory
-// (`__threadfence_system`), stores `e` into flags[r] of every peer, then waits until its own flags[p] >= e for
-// every peer p.  A stream that runs "push kernel, barrier" therefore sees the pushes of all peers after the
-// barrier.  The wait is bounded (about one second of SM clock): on expiry the kernel records an error code and
-// returns, it never traps and never spins for ever.  One kernel per rank and GPU; ranks never share a GPU.
+// Every rank owns an int32 flag array `flags[nslots][world]` in its own memory, mapped into all peers, and a local
+// (unshared) counter `epochs[nslots]`.  A slot is one synchronisation point of a step (split sizes published, ids
+// delivered, pooled rows delivered, gradients published, ...).  Signalling slot s: the rank takes the next epoch
+// e = epochs[s] + 1, publishes everything it wrote to peer memory (`__threadfence_system`), raises flags[s][rank]
+// of every peer to e with a system-scope atomic max (so a flag never moves backwards, whatever the order in which
+// two signals land) and stores e back.  Waiting on slot s: spin until flags[s][p] >= epochs[s] for every peer p.
+// Epochs live on the device, so the same launches can be replayed from a CUDA graph: the host passes no counter.
+// All ranks run the same sequence of signals, hence agree on the epoch numbers without talking.
 //
-// The reference has no counterpart: it exchanges pooled embeddings with library all-to-all / reduce-scatter calls
+// Waits are bounded by a caller-given number of SM clock cycles: on expiry the kernel stores an error code
+// (100 + peer for a plain wait) in `err` and returns; it never traps and never spins for ever.  The host reads `err`
+// (PeerGroup.poll_error) and raises.  One waiting kernel per rank and GPU at a time; ranks never share a GPU.
+//
+// The reference has no counterpart: it synchronises through library collectives
 // (torchrec/distributed/comm_ops.py:574-1073).
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
@@ -17,37 +23,35 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "peer_sync.cuh"
 
 namespace trb {
 
-constexpr long long kBarrierWaitCycles = 2000000000LL;
-
-__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int* err) {
+__global__ void peer_sync_kernel(PeerPtrs flags, int rank, int world, int slot, int* epochs, int do_signal, int do_wait,
+                                 long long wait_cycles, int* err) {
   const int p = threadIdx.x;
-  if (p >= world) return;
-  __threadfence_system();
-  volatile int* remote = reinterpret_cast<volatile int*>(flags.p[p]) + rank;
-  *remote = epoch;
-  __threadfence_system();
-  volatile int* mine = reinterpret_cast<volatile int*>(flags.p[rank]) + p;
-  const long long t0 = clock64();
-  while (*mine < epoch) {
-    if (clock64() - t0 > kBarrierWaitCycles) {
-      atomicCAS(err, 0, 100 + p);  // which peer never arrived
-      return;
-    }
-  }
-  __threadfence_system();
+  __shared__ int s_epoch;
+  if (p == 0) s_epoch = epochs[slot] + (do_signal ? 1 : 0);
+  __syncthreads();
+  const int epoch = s_epoch;
+  if (do_signal && p < world) peer_signal_one(flags, p, rank, world, slot, epoch);
+  if (do_wait && p < world) peer_wait_one(flags, p, rank, world, slot, epoch, wait_cycles, err, 100);
+  __syncthreads();
+  if (do_signal && p == 0) epochs[slot] = epoch;
 }
 
-void peer_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t epoch, at::Tensor err) {
+void peer_sync(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t slot, at::Tensor epochs, bool signal, bool wait,
+               int64_t wait_cycles, at::Tensor err) {
   const int world = int(flag_ptrs.size());
-  TORCH_CHECK(world >= 1 && world <= kMaxPeers, "peer_barrier supports up to ", kMaxPeers, " ranks");
+  TORCH_CHECK(world >= 1 && world <= kMaxPeers, "peer_sync supports up to ", kMaxPeers, " ranks");
   TORCH_CHECK(err.is_cuda() && err.scalar_type() == at::kInt && err.numel() >= 1);
+  TORCH_CHECK(epochs.is_cuda() && epochs.scalar_type() == at::kInt && slot >= 0 && slot < epochs.numel());
   c10::cuda::CUDAGuard guard(err.device());
   PeerPtrs f;
   for (int i = 0; i < kMaxPeers; ++i) f.p[i] = i < world ? reinterpret_cast<void*>(flag_ptrs[i]) : nullptr;
-  peer_barrier_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(f, int(rank), world, int(epoch), err.data_ptr<int>());
+  peer_sync_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(f, int(rank), world, int(slot), epochs.data_ptr<int>(),
+                                                                   signal ? 1 : 0, wait ? 1 : 0, (long long)wait_cycles,
+                                                                   err.data_ptr<int>());
   TRB_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -110,7 +114,7 @@ at::Tensor peer_read(int64_t ptr, int64_t nbytes, at::Device device) {
 }  // namespace trb
 
 TORCH_LIBRARY_FRAGMENT(trb200, m) {
-  m.def("peer_barrier(int[] flag_ptrs, int rank, int epoch, Tensor(a!) err) -> ()");
+  m.def("peer_sync(int[] flag_ptrs, int rank, int slot, Tensor(a!) epochs, bool signal, bool wait, int wait_cycles, Tensor(b!) err) -> ()");
   m.def("peer_alloc(int nbytes, Device device) -> Tensor");
   m.def("peer_handle(Tensor buf) -> Tensor");
   m.def("peer_open(Tensor handle, Device device) -> int");
@@ -119,7 +123,7 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
 }
 
 TORCH_LIBRARY_IMPL(trb200, CompositeExplicitAutograd, m) {
-  m.impl("peer_barrier", &trb::peer_barrier);
+  m.impl("peer_sync", &trb::peer_sync);
   m.impl("peer_alloc", &trb::peer_alloc);
   m.impl("peer_handle", &trb::peer_handle);
   m.impl("peer_open", &trb::peer_open);

@@ -226,6 +226,7 @@ struct BwdParams {
   int64_t grad_stride;
   const float* bag_scale;  // mean pooling: 1/len per bag, or null
   int64_t N;
+  const int64_t* n_valid;  // device-side count of valid sorted entries (the tail holds padding keys), or null: all N are valid
   int B;
   int F;
   int pooled;
@@ -460,6 +461,7 @@ __device__ __forceinline__ void prefetch_l2_range(const void* ptr, int bytes) {
 // gradient load (an L2 hit by then) and the multiply-adds.
 template <typename emb_t, typename grad_t, int kVecs>
 __global__ void __launch_bounds__(256, kVecs == 1 ? 4 : 2) tbe_bwd_block_kernel(BwdParams p) {
+  const int64_t N_ = p.n_valid ? min(p.N, *p.n_valid) : p.N;
   __shared__ int64_t s_meta[kMetaRows * kSmemF];
   __shared__ uint4 s_rec[8][kBlk];     // {gradient byte offset lo, hi, weight bits, ctl}; ctl = end | D << 1 | f << 16
   __shared__ int64_t s_woff[8][kBlk];  // element offset of the entry's table row in the weights
@@ -475,8 +477,8 @@ __global__ void __launch_bounds__(256, kVecs == 1 ? 4 : 2) tbe_bwd_block_kernel(
   const int wib = threadIdx.x >> 5;
   const int64_t blk = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t start = blk * kBlk;
-  if (start >= p.N) return;
-  const int n = int(min(int64_t(kBlk), p.N - start));
+  if (start >= N_) return;
+  const int n = int(min(int64_t(kBlk), N_ - start));
   const int opt_type = p.opt.type;
   const char* __restrict__ gbase = reinterpret_cast<const char*>(p.grad);
 
@@ -490,7 +492,7 @@ __global__ void __launch_bounds__(256, kVecs == 1 ? 4 : 2) tbe_bwd_block_kernel(
     if (k < n) {
       const int64_t i = start + k;
       const int64_t key = p.sorted_keys[i];
-      const int64_t nxt = (i + 1 < p.N) ? p.sorted_keys[i + 1] : int64_t(-1);
+      const int64_t nxt = (i + 1 < N_) ? p.sorted_keys[i + 1] : int64_t(-1);
       const int src = p.sorted_src[i];
       float w = p.sorted_w ? p.sorted_w[i] : 1.f;
       int f;
@@ -612,17 +614,18 @@ __device__ __forceinline__ int64_t upper_bound_key(const int64_t* __restrict__ k
 // by the head's warp; long chains (hot rows of a skewed id distribution) are queued for pass 3.
 template <typename emb_t, int kVecs>
 __global__ void __launch_bounds__(256) tbe_bwd_long_kernel(BwdParams p) {
+  const int64_t N_ = p.n_valid ? min(p.N, *p.n_valid) : p.N;
   const int lane = threadIdx.x & 31;
   const int64_t blk = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nblocks = (p.N + kBlk - 1) / kBlk;
+  const int64_t nblocks = (N_ + kBlk - 1) / kBlk;
   if (blk >= nblocks) return;
   const int fl = p.flags[2 * blk + 1];
   if (!(fl & FLAG_USED)) return;
   const int f = fl >> 8;
-  const int64_t end = min(p.N, (blk + 1) * kBlk);
+  const int64_t end = min(N_, (blk + 1) * kBlk);
   const int64_t key = p.sorted_keys[end - 1];
   int64_t last_blk = 0;
-  if (lane == 0) last_blk = (upper_bound_key(p.sorted_keys, end, p.N, key) - 1) / kBlk;
+  if (lane == 0) last_blk = (upper_bound_key(p.sorted_keys, end, N_, key) - 1) / kBlk;
   last_blk = __shfl_sync(0xffffffffu, last_blk, 0);
   if (last_blk - blk > kSerialChain) {
     if (lane == 0) {
@@ -659,6 +662,7 @@ __global__ void __launch_bounds__(256) tbe_bwd_long_kernel(BwdParams p) {
 // is deterministic), the eight sums are combined in shared memory in warp order, and warp 0 applies the update.
 template <typename emb_t, int kVecs>
 __global__ void __launch_bounds__(256) tbe_bwd_verylong_kernel(BwdParams p) {
+  const int64_t N_ = p.n_valid ? min(p.N, *p.n_valid) : p.N;
   __shared__ float4 red[8][kVecs][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int count = *p.long_count;
@@ -704,7 +708,7 @@ __global__ void __launch_bounds__(256) tbe_bwd_verylong_kernel(BwdParams p) {
         acc[v] = t;
       }
       const int f = p.flags[2 * blk + 1] >> 8;
-      const int64_t end = min(p.N, (blk + 1) * kBlk);
+      const int64_t end = min(N_, (blk + 1) * kBlk);
       apply_update<emb_t, kVecs>(p, p.sorted_keys[end - 1], f, acc, lane);
     }
     __syncthreads();
@@ -735,6 +739,11 @@ __global__ void __launch_bounds__(256) tbe_linearize_kernel(
     src[i] = pooled ? int32_t(bag) : int32_t(i);
     if (src_feature) src_feature[i] = f;
   }
+}
+
+template <typename idx_t>
+__global__ void tbe_count_valid_kernel(const idx_t* __restrict__ offsets, int64_t nbags, int64_t* __restrict__ out) {
+  out[0] = int64_t(offsets[nbags]) - int64_t(offsets[0]);
 }
 
 __global__ void gather_sorted_weights_kernel(const float* __restrict__ psw, const int32_t* __restrict__ sorted_pos,
@@ -879,7 +888,7 @@ struct SortedPlan {
 // pipeline may run it on a side stream while the dense towers of the previous step are still busy.
 std::vector<at::Tensor> tbe_build_plan(const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets,
                                        const c10::optional<at::Tensor>& psw, int64_t B, int64_t total_rows,
-                                       bool pooled, bool mean_pooling, at::Tensor err) {
+                                       bool pooled, bool mean_pooling, bool padded, at::Tensor err) {
   const int F = int(meta.size(1));
   const int64_t N = indices.numel();
   c10::cuda::CUDAGuard guard(indices.device());
@@ -887,7 +896,11 @@ std::vector<at::Tensor> tbe_build_plan(const at::Tensor& meta, const at::Tensor&
   auto opts_i64 = indices.options().dtype(at::kLong);
   auto opts_i32 = indices.options().dtype(at::kInt);
   auto opts_f32 = indices.options().dtype(at::kFloat);
-  at::Tensor keys = at::empty({N}, opts_i64), src = at::empty({N}, opts_i32);
+  // padded: `indices` is a buffer of fixed capacity of which only [offsets[0], offsets[F*B]) holds ids of these tables.
+  // Every other position gets a key past the last table row, sorts to the tail and is skipped by the backward kernels,
+  // which read the number of real entries from `n_valid` on the device: no size ever travels to the host.
+  at::Tensor keys = padded ? at::full({N}, total_rows, opts_i64) : at::empty({N}, opts_i64), src = at::empty({N}, opts_i32);
+  at::Tensor n_valid = padded ? at::empty({1}, opts_i64) : at::Tensor();
   at::Tensor src_feature = pooled ? at::Tensor() : at::empty({N}, opts_i32);
   at::Tensor bag_scale = (pooled && mean_pooling) ? at::empty({int64_t(F) * B}, opts_f32) : at::Tensor();
   const bool weighted = psw.has_value() && psw->defined();
@@ -914,6 +927,10 @@ std::vector<at::Tensor> tbe_build_plan(const at::Tensor& meta, const at::Tensor&
           keys.data_ptr<int64_t>(), src_ptr, pooled ? nullptr : src_feature.data_ptr<int32_t>(),
           bag_scale.defined() ? bag_scale.data_ptr<float>() : nullptr, err.data_ptr<int>());
     }
+    if (padded) {
+      if (i64) tbe_count_valid_kernel<int64_t><<<1, 1, 0, stream>>>(offsets.data_ptr<int64_t>(), int64_t(F) * B, n_valid.data_ptr<int64_t>());
+      else tbe_count_valid_kernel<int32_t><<<1, 1, 0, stream>>>(offsets.data_ptr<int32_t>(), int64_t(F) * B, n_valid.data_ptr<int64_t>());
+    }
     TRB_CUDA_CHECK(cudaGetLastError());
     at::Tensor vals_in = src;
     if (weighted) {
@@ -921,7 +938,7 @@ std::vector<at::Tensor> tbe_build_plan(const at::Tensor& meta, const at::Tensor&
     }
     at::Tensor keys_out = at::empty({N}, opts_i64), vals_out = at::empty({N}, opts_i32);
     int end_bit = 1;
-    while ((int64_t(1) << end_bit) < total_rows && end_bit < 63) ++end_bit;
+    while ((int64_t(1) << end_bit) < total_rows + (padded ? 1 : 0) && end_bit < 63) ++end_bit;
     size_t tmp_bytes = 0;
     cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, keys.data_ptr<int64_t>(), keys_out.data_ptr<int64_t>(),
                                     vals_in.data_ptr<int32_t>(), vals_out.data_ptr<int32_t>(), N, 0, end_bit, stream);
@@ -942,12 +959,16 @@ std::vector<at::Tensor> tbe_build_plan(const at::Tensor& meta, const at::Tensor&
     } else {
       src = vals_out;
     }
-    return {keys, src, w_sorted.defined() ? w_sorted : at::empty({0}, opts_f32),
-            src_feature.defined() ? src_feature : at::empty({0}, opts_i32),
-            bag_scale.defined() ? bag_scale : at::empty({0}, opts_f32)};
+    std::vector<at::Tensor> res = {keys, src, w_sorted.defined() ? w_sorted : at::empty({0}, opts_f32),
+                                   src_feature.defined() ? src_feature : at::empty({0}, opts_i32),
+                                   bag_scale.defined() ? bag_scale : at::empty({0}, opts_f32)};
+    if (padded) res.push_back(n_valid);
+    return res;
   }
-  return {keys, src, at::empty({0}, opts_f32), src_feature.defined() ? src_feature : at::empty({0}, opts_i32),
-          bag_scale.defined() ? bag_scale : at::empty({0}, opts_f32)};
+  std::vector<at::Tensor> res = {keys, src, at::empty({0}, opts_f32), src_feature.defined() ? src_feature : at::empty({0}, opts_i32),
+                                 bag_scale.defined() ? bag_scale : at::empty({0}, opts_f32)};
+  if (padded) res.push_back(at::zeros({1}, opts_i64));
+  return res;
 }
 
 // Apply the sorted plan: segment-reduce upstream gradient rows per table row and update in place.
@@ -957,7 +978,8 @@ static void tbe_backward_apply_impl(at::Tensor weights, c10::optional<at::Tensor
                                     const at::Tensor& bag_scale, const at::Tensor& grad, int64_t grad_stride, int64_t B,
                                     int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
                                     double beta2, double weight_decay, int64_t step, double max_grad,
-                                    const std::vector<int64_t>& grad_ptrs, int64_t B_local, double grad_scale) {
+                                    const std::vector<int64_t>& grad_ptrs, int64_t B_local, double grad_scale,
+                                    const c10::optional<at::Tensor>& n_valid = c10::nullopt) {
   const int64_t N = sorted_keys.numel();
   if (N == 0) return;
   c10::cuda::CUDAGuard guard(weights.device());
@@ -985,6 +1007,7 @@ static void tbe_backward_apply_impl(at::Tensor weights, c10::optional<at::Tensor
   p.grad_stride = grad_stride;
   p.bag_scale = bag_scale.numel() > 0 ? bag_scale.data_ptr<float>() : nullptr;
   p.N = N;
+  p.n_valid = n_valid.has_value() && n_valid->defined() ? n_valid->data_ptr<int64_t>() : nullptr;
   p.B = int(B);
   p.F = F;
   p.pooled = pooled ? 1 : 0;
@@ -1037,9 +1060,10 @@ void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10:
                         const at::Tensor& sorted_src, const at::Tensor& sorted_w, const at::Tensor& src_feature,
                         const at::Tensor& bag_scale, const at::Tensor& grad, int64_t grad_stride, int64_t B,
                         int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
-                        double beta2, double weight_decay, int64_t step, double max_grad) {
+                        double beta2, double weight_decay, int64_t step, double max_grad, c10::optional<at::Tensor> n_valid) {
   tbe_backward_apply_impl(weights, mom1, mom2, dense_grad, meta, sorted_keys, sorted_src, sorted_w, src_feature, bag_scale, grad,
-                          grad_stride, B, max_D, pooled, opt_type, lr, eps, beta1, beta2, weight_decay, step, max_grad, {}, 0, 1.0);
+                          grad_stride, B, max_D, pooled, opt_type, lr, eps, beta1, beta2, weight_decay, step, max_grad, {}, 0, 1.0,
+                          n_valid);
 }
 
 // Backward of the fused lookup + exchange: the pooled gradient of bag b (of the global batch) is read from the
@@ -1050,10 +1074,11 @@ void tbe_backward_apply_dist(at::Tensor weights, c10::optional<at::Tensor> mom1,
                              const at::Tensor& bag_scale, const at::Tensor& grad, int64_t grad_stride, int64_t B,
                              int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
                              double beta2, double weight_decay, int64_t step, double max_grad,
-                             std::vector<int64_t> grad_ptrs, int64_t B_local, double grad_scale) {
+                             std::vector<int64_t> grad_ptrs, int64_t B_local, double grad_scale,
+                             c10::optional<at::Tensor> n_valid) {
   tbe_backward_apply_impl(weights, mom1, mom2, dense_grad, meta, sorted_keys, sorted_src, sorted_w, src_feature, bag_scale, grad,
                           grad_stride, B, max_D, pooled, opt_type, lr, eps, beta1, beta2, weight_decay, step, max_grad, grad_ptrs,
-                          B_local, grad_scale);
+                          B_local, grad_scale, n_valid);
 }
 
 }  // namespace trb
@@ -1174,6 +1199,7 @@ extern "C" int trb_tbe_backward_apply_noalloc(const trb_tbe_bwd_noalloc_args* a,
   p.grad_stride = a->grad_stride;
   p.bag_scale = a->bag_scale;
   p.N = a->N;
+  p.n_valid = nullptr;
   p.B = a->B;
   p.F = a->F;
   p.pooled = a->pooled ? 1 : 0;
@@ -1220,17 +1246,17 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
       "Tensor(a!) err) -> ()");
   m.def(
       "tbe_build_plan(Tensor meta, Tensor indices, Tensor offsets, Tensor? psw, int B, int total_rows, bool pooled, "
-      "bool mean_pooling, Tensor(a!) err) -> Tensor[]");
+      "bool mean_pooling, bool padded, Tensor(a!) err) -> Tensor[]");
   m.def(
       "tbe_backward_apply(Tensor(a!) weights, Tensor(b!)? mom1, Tensor(c!)? mom2, Tensor(d!)? dense_grad, Tensor meta, "
       "Tensor sorted_keys, Tensor sorted_src, Tensor sorted_w, Tensor src_feature, Tensor bag_scale, Tensor grad, "
       "int grad_stride, int B, int max_D, bool pooled, int opt_type, float lr, float eps, float beta1, float beta2, "
-      "float weight_decay, int step, float max_grad) -> ()");
+      "float weight_decay, int step, float max_grad, Tensor? n_valid) -> ()");
   m.def(
       "tbe_backward_apply_dist(Tensor(a!) weights, Tensor(b!)? mom1, Tensor(c!)? mom2, Tensor(d!)? dense_grad, Tensor meta, "
       "Tensor sorted_keys, Tensor sorted_src, Tensor sorted_w, Tensor src_feature, Tensor bag_scale, Tensor grad, "
       "int grad_stride, int B, int max_D, bool pooled, int opt_type, float lr, float eps, float beta1, float beta2, "
-      "float weight_decay, int step, float max_grad, int[] grad_ptrs, int B_local, float grad_scale) -> ()");
+      "float weight_decay, int step, float max_grad, int[] grad_ptrs, int B_local, float grad_scale, Tensor? n_valid) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(trb200, CUDA, m) {

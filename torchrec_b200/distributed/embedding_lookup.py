@@ -157,61 +157,6 @@ class GroupedEmbeddingsLookup(_GroupedLookupBase):
         return torch.cat(embeddings).view(-1, dim)
 
 
-class _PeerPushLookup(torch.autograd.Function):
-    """Pooled lookup fused with its exchange: every rank's kernel stores the pooled rows of its tables into the
-    ``[B_local, D_total]`` buffer of the rank that owns each sample (peer-mapped, NVLink), a device-side barrier
-    closes the step, and the local buffer is the result.  Backward: gradients go into a peer-mapped buffer, barrier,
-    and each rank's backward kernel pulls the rows it needs from the owners while applying the fused optimizer."""
-
-    @staticmethod
-    def forward(ctx, anchor, lookup, features):
-        peer = lookup._peer
-        B = features.stride()
-        B_local = B // peer.world
-        out, out_ptrs = lookup._peer_out_buffer(B_local)
-        total_D = lookup._peer_total_D
-        groups = features.split(lookup._feature_splits) if len(lookup._emb_modules) > 1 else [features]
-        col = lookup._peer_col_base
-        layout = lookup._peer_feature_columns  # per module: the final column of every feature, or None (rank-major blocks)
-        saved = []
-        for gi, (config, emb_op, f) in enumerate(zip(lookup.grouped_configs, lookup._emb_modules, groups)):
-            tbe = emb_op.emb_module
-            psw = f.weights_or_none() if config.is_weighted else None
-            if psw is not None and not torch.is_floating_point(psw):
-                psw = None
-            if psw is not None and psw.dtype != torch.float32:
-                psw = psw.float()
-            tbe.forward_push(f.values(), f.offsets(), psw, B, B_local, out_ptrs, total_D, col if layout is None else layout[gi], out.dtype)
-            # the id sort of the backward starts now, on the side stream, under the dense towers
-            saved.append((f.values(), f.offsets(), psw, tbe.build_plan_ahead(f.values(), f.offsets(), psw, B) if torch.is_grad_enabled() else None))
-            col += tbe.total_D
-        peer.barrier()
-        ctx.lookup = lookup
-        ctx.saved = saved
-        ctx.B = B
-        ctx.B_local = B_local
-        ctx.layout = layout
-        return out
-
-    @staticmethod
-    def backward(ctx, grad):
-        from torchrec_b200.distributed import comm_ops
-
-        lookup = ctx.lookup
-        peer = lookup._peer
-        g, g_ptrs = lookup._peer_grad_buffer(ctx.B_local)
-        g.copy_(grad)
-        peer.barrier()
-        scale = 1.0 / peer.world if comm_ops.get_gradient_division() else 1.0
-        col = lookup._peer_col_base
-        for gi, (emb_op, (idx, off, psw, plan)) in enumerate(zip(lookup._emb_modules, ctx.saved)):
-            tbe = emb_op.emb_module
-            tbe.backward_pull(g, g_ptrs, lookup._peer_total_D, idx, off, psw, ctx.B, ctx.B_local, col if ctx.layout is None else ctx.layout[gi], scale, plan)
-            col += tbe.total_D
-        ctx.saved = None
-        return None, None, None
-
-
 class GroupedPooledEmbeddingsLookup(_GroupedLookupBase):
     """Pooled lookup over the TBE groups of one rank -> ``[B, sum(D)]``."""
 
@@ -228,59 +173,6 @@ class GroupedPooledEmbeddingsLookup(_GroupedLookupBase):
         self._world_size: int = dist.get_world_size(pg) if pg is not None else 1
         self._scale_gradient_factor: int = self._world_size if scale_weight_gradients else 1
         self._finish_init(device)
-        self._peer = None  # PeerGroup when the fused lookup + exchange is on
-        self._peer_total_D = 0
-        self._peer_col_base = 0
-        self._peer_feature_columns: Optional[List[List[int]]] = None
-        self._peer_dtype = torch.float32
-        self._peer_bufs: Dict[str, Any] = {}
-        self._peer_step = 0
-
-    # ---- fused lookup + exchange (table-wise / column-wise shardings on one node) ------------------------
-    def enable_peer_exchange(self, peer, dim_sum_per_rank: List[int], dtype: torch.dtype) -> None:
-        """Switch ``forward`` to the kernel that writes pooled rows straight into the owners' buffers.  ``dim_sum_per_rank``
-        fixes the column block of every rank in the exchanged ``[B_local, sum(D)]`` row; the caller has made sure that
-        every table of the sharding uses a fused (in-backward) optimizer and no feature processor."""
-        self._peer = peer
-        self._peer_total_D = int(sum(dim_sum_per_rank))
-        self._peer_col_base = int(sum(dim_sum_per_rank[: peer.rank]))
-        self._peer_dtype = dtype
-        self._peer_anchor = torch.zeros(1, requires_grad=True)
-
-    def set_peer_output_layout(self, column_of_embedding: Dict[str, int]) -> bool:
-        """Store every table's pooled columns at their final place of the exchanged row (``column_of_embedding``: embedding name ->
-        first column in the unsharded module's output) instead of in rank-major blocks, which saves the column permute (a full copy
-        of the output forward and of its gradient backward).  Returns whether the layout was taken."""
-        if self._peer is None:
-            return False
-        cols: List[List[int]] = []
-        for config in self.grouped_configs:
-            names = config.embedding_names()
-            if any(n not in column_of_embedding for n in names):
-                return False
-            cols.append([int(column_of_embedding[n]) for n in names])
-        self._peer_feature_columns = cols
-        return True
-
-    def _peer_out_buffer(self, B_local: int):
-        key = f"out{self._peer_step % 2}"
-        self._peer_step += 1
-        return self._peer_buffer(key, B_local)
-
-    def _peer_grad_buffer(self, B_local: int):
-        return self._peer_buffer("grad", B_local)
-
-    def _peer_buffer(self, key: str, B_local: int):
-        ent = self._peer_bufs.get(key)
-        if ent is None or ent[0].shape[0] != B_local:
-            # collective: every rank allocates and shares at the same point of its step
-            ent = self._peer.alloc_shared((B_local, self._peer_total_D), self._peer_dtype)
-            self._peer_bufs[key] = ent
-        return ent
-
-    def _can_push(self, features: KeyedJaggedTensor) -> bool:
-        return (self._peer is not None and not features.variable_stride_per_key() and features.stride() > 0
-                and features.stride() % self._peer.world == 0)
 
     @staticmethod
     def _create_embedding_kernel(config: GroupedEmbeddingConfig, device, pg, sharding_type) -> BaseEmbedding:
@@ -291,11 +183,6 @@ class GroupedPooledEmbeddingsLookup(_GroupedLookupBase):
         raise ValueError(f"Compute kernel not supported {config.compute_kernel}")
 
     def forward(self, sparse_features: KeyedJaggedTensor) -> torch.Tensor:
-        if self._can_push(sparse_features):
-            out = _PeerPushLookup.apply(self._peer_anchor, self, sparse_features)
-            out._trb_exchanged = True  # tells the output dist that the rows are already where they belong
-            out._trb_final_layout = self._peer_feature_columns is not None  # ... and the columns in the unsharded module's order
-            return out
         if len(self._emb_modules) == 0:
             return self._dummy_embs_tensor.view(sparse_features.stride(), 0) if sparse_features.stride() else self._dummy_embs_tensor
         embeddings: List[torch.Tensor] = []

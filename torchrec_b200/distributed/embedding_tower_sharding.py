@@ -50,6 +50,8 @@ class ShardedEmbeddingTower(ShardedEmbeddingModule):
         self._active = self._rank == self._owner
         self.embedding: ShardedEmbeddingBagCollection = embedding_sharder.shard(module.embedding, table_name_to_parameter_sharding, env=env, device=device,
                                                                               module_fqn=(module_fqn + ".embedding") if module_fqn else None)
+        if hasattr(self.embedding, "disable_fused_engine"):
+            self.embedding.disable_fused_engine()  # the tower consumes the owner-side lookup before any exchange
         self._lookups = self.embedding._lookups
         self.interaction = module.interaction.to(device) if device.type != "meta" else module.interaction
         self._out_dim: Optional[int] = None

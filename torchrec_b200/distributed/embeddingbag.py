@@ -45,6 +45,7 @@ from torchrec_b200.distributed.sharding.twcw_sharding import TwCwPooledEmbedding
 from torchrec_b200.distributed.sharding.twrw_sharding import TwRwPooledEmbeddingSharding
 from torchrec_b200.distributed.types import (
     Awaitable,
+    NoWait,
     EmbeddingEvent,
     EmbeddingModuleShardingPlan,
     LazyAwaitable,
@@ -191,8 +192,11 @@ class EmbeddingBagCollectionContext(Multistreamable):
         self.inverse_indices = inverse_indices
         self.variable_batch_per_feature = variable_batch_per_feature
         self.divisor = divisor
+        self.engine_handle = None  # set when the fused sparse engine distributed this batch
 
     def record_stream(self, stream: torch.Stream) -> None:
+        if self.engine_handle is not None:
+            self.engine_handle.record_stream(stream)
         for ctx in self.sharding_contexts:
             if ctx:
                 ctx.record_stream(stream)
@@ -309,6 +313,9 @@ class ShardedEmbeddingBagCollection(
         self._optim: CombinedOptimizer = CombinedOptimizer(optims)
         # mean pooling for row-split tables is applied after the reduction
         self._has_mean_pooling_callback: bool = PoolingType.MEAN.value in self._pooling_type_to_rs_features()
+        # fused sparse engine (peer-memory input dist + lookup + output hand-over): built on the first batch, collectively
+        self._engine_state: str = "auto"  # "auto" -> "on" | "off"
+        self._engine = None
         self._dim_per_key: Optional[torch.Tensor] = None
         self._kjt_key_indices: Dict[str, int] = {}
         self._kt_key_ordering: Optional[torch.Tensor] = None
@@ -555,15 +562,6 @@ class ShardedEmbeddingBagCollection(
             self._permute_op = PermutePooledEmbeddingsSplit(self._embedding_dims, order, device=self._device)
             self._embedding_names = wanted
             self._embedding_dims = [self._embedding_dims[i] for i in order]
-            # a single table-wise sharding on the fused exchange path can store every table at its final column right away
-            if len(self._embedding_shardings) == 1 and len(set(self._pre_names)) == len(self._pre_names):
-                column, acc = {}, 0
-                for n, d in zip(self._embedding_names, self._embedding_dims):
-                    column[n] = acc
-                    acc += d
-                lk = self._lookups[0].module if isinstance(self._lookups[0], DistributedDataParallel) else self._lookups[0]
-                if hasattr(lk, "set_peer_output_layout"):
-                    lk.set_peer_output_layout(column)
 
     def _init_mean_pooling_callback(self, input_feature_names: List[str]) -> None:
         keys = [input_feature_names[i] for i in self._features_order] if self._features_order else list(input_feature_names)
@@ -575,9 +573,87 @@ class ShardedEmbeddingBagCollection(
         self._kt_key_ordering = torch.tensor([self._kjt_key_indices[f] for f in feat_of], device=dev)
 
     # ---- the three stages -------------------------------------------------------------------------------
+    # ---- fused sparse engine ---------------------------------------------------------------------------
+    def disable_fused_engine(self) -> None:
+        """Wrappers that transform the distributed KJT between input dist and lookup (feature processors, managed
+        collision, pruning) need the classic three-stage path."""
+        self._engine_state, self._engine = "off", None
+
+    def _fused_engine(self):
+        if self._engine_state == "auto":
+            self._engine = self._build_fused_engine()
+            self._engine_state = "on" if self._engine is not None else "off"
+        return self._engine
+
+    def _build_fused_engine(self):
+        """All ranks take the same decision: it depends on the plan, the environment and one collective agreement."""
+        from torchrec_b200.distributed.fbgemm_qcomm_codec import CastCodec
+        from torchrec_b200.distributed.fused_sparse_engine import FusedSparseEngine
+        from torchrec_b200.distributed.peer_memory import PeerGroup
+        from torchrec_b200.distributed.types import CommOp
+
+        dev = self._device
+        if dev is None or dev.type != "cuda" or isinstance(self._env, ShardingEnv2D):
+            return None
+        allowed = {ShardingType.TABLE_WISE.value, ShardingType.COLUMN_WISE.value, ShardingType.TABLE_COLUMN_WISE.value,
+                   ShardingType.ROW_WISE.value, ShardingType.TABLE_ROW_WISE.value, ShardingType.GRID_SHARD.value}
+        if not self._sharding_types or any(t not in allowed for t in self._sharding_types):
+            return None
+        fused = (EmbeddingComputeKernel.FUSED, EmbeddingComputeKernel.FUSED_UVM, EmbeddingComputeKernel.FUSED_UVM_CACHING)
+        out_dtypes = set()
+        for sh, lk in zip(self._embedding_shardings, self._lookups):
+            if isinstance(lk, DistributedDataParallel) or getattr(lk, "_feature_processor", None) is not None:
+                return None
+            for groups in sh._grouped_embedding_configs_per_rank:
+                for g in groups:
+                    if g.compute_kernel not in fused or g.has_feature_processor:
+                        return None
+                    if g.is_weighted and g.pooling.value == PoolingType.MEAN.value:
+                        return None
+            for emb in lk.emb_modules:
+                out_dtypes.add(emb.emb_module.output_dtype)
+        if len(out_dtypes) > 1:
+            return None
+        out_dtype = out_dtypes.pop() if out_dtypes else torch.float32
+        stage_dtype, grad_dtype = out_dtype, torch.float32
+        reg = self.qcomm_codecs_registry or {}
+        for op in (CommOp.POOLED_EMBEDDINGS_ALL_TO_ALL.name, CommOp.POOLED_EMBEDDINGS_REDUCE_SCATTER.name):
+            codecs = reg.get(op)
+            if codecs is None:
+                continue
+            fwd, bwd = codecs.forward, codecs.backward
+            stage_dtype = fwd.quantized_dtype if isinstance(fwd, CastCodec) and fwd.quantized_dtype != torch.float32 else (torch.float16 if not isinstance(fwd, CastCodec) else stage_dtype)
+            grad_dtype = bwd.quantized_dtype if isinstance(bwd, CastCodec) and bwd.quantized_dtype != torch.float32 else (torch.bfloat16 if not isinstance(bwd, CastCodec) else grad_dtype)
+        pg = self._env.process_group
+        peer = PeerGroup.get(pg, dev)
+        if peer is None:
+            return None
+        try:
+            return FusedSparseEngine(peer, self._embedding_bag_configs, self._embedding_shardings, self._lookups, out_dtype, stage_dtype, grad_dtype)
+        except AssertionError as e:
+            import warnings
+
+            warnings.warn(f"fused sparse engine not used for this module: {e}")
+            return None
+
+    def _engine_names_dims(self) -> Tuple[List[str], List[int]]:
+        names = [n for ns in _embedding_names_by_table(self._embedding_bag_configs) for n in ns]
+        dims = [cfg.embedding_dim for cfg in self._embedding_bag_configs for _ in cfg.feature_names]
+        return names, dims
+
+    def _engine_output(self, ctx: EmbeddingBagCollectionContext) -> LazyAwaitable[KeyedTensor]:
+        out = self._engine.lookup(ctx.engine_handle)
+        names, dims = self._engine_names_dims()
+        return EmbeddingBagCollectionAwaitable(awaitables=[NoWait(out)], embedding_dims=dims, embedding_names=names,
+                                               module_fqn=self._module_fqn, sharding_types=None)
+
     def input_dist(self, ctx: EmbeddingBagCollectionContext, features: KeyedJaggedTensor) -> Awaitable[Awaitable[KJTList]]:
         ctx.variable_batch_per_feature = features.variable_stride_per_key()
         ctx.inverse_indices = features.inverse_indices_or_none()
+        engine = self._fused_engine() if self._engine_state != "off" else None
+        if engine is not None and engine.accepts(features):
+            ctx.engine_handle = engine.input_dist(features)
+            return NoWait(NoWait(EngineDistInput(ctx.engine_handle)))
         if self._has_uninitialized_input_dist:
             self._create_input_dist(features.keys())
             self._has_uninitialized_input_dist = False
@@ -619,15 +695,23 @@ class ShardedEmbeddingBagCollection(
             self._inverse_indices_permute_indices = _pin_and_move(torch.tensor(permute_indices), inverse_indices[1].device)
 
     def compute(self, ctx: EmbeddingBagCollectionContext, dist_input: KJTList) -> List[torch.Tensor]:
+        if isinstance(dist_input, EngineDistInput):
+            return [self._engine.lookup(ctx.engine_handle)]
         return [lookup(features) for lookup, features in zip(self._lookups, dist_input)]
 
     def output_dist(self, ctx: EmbeddingBagCollectionContext, output: List[torch.Tensor]) -> LazyAwaitable[KeyedTensor]:
+        if ctx.engine_handle is not None:
+            names, dims = self._engine_names_dims()
+            return EmbeddingBagCollectionAwaitable(awaitables=[NoWait(output[0])], embedding_dims=dims, embedding_names=names,
+                                                   module_fqn=self._module_fqn, sharding_types=None)
         if not self._output_dists:
             self._create_output_dist()
         awaitables = [d(embs, sctx) for d, sctx, embs in zip(self._output_dists, ctx.sharding_contexts, output)]
         return self._finish_output(ctx, awaitables)
 
     def compute_and_output_dist(self, ctx: EmbeddingBagCollectionContext, input: KJTList) -> LazyAwaitable[KeyedTensor]:
+        if isinstance(input, EngineDistInput):
+            return self._engine_output(ctx)
         if not self._output_dists:
             self._create_output_dist()
         awaitables = []
@@ -658,9 +742,7 @@ class ShardedEmbeddingBagCollection(
             permute_op, names, dims = self._permute_op, self._embedding_names, self._embedding_dims
 
             def to_module_order(kt: KeyedTensor) -> KeyedTensor:
-                v = kt.values()
-                # the fused exchange may already have stored the columns in the module's order
-                return KeyedTensor(keys=names, length_per_key=dims, values=v if getattr(v, "_trb_final_layout", False) else permute_op(v), key_dim=1)
+                return KeyedTensor(keys=names, length_per_key=dims, values=permute_op(kt.values()), key_dim=1)
 
             awaitable.callbacks.append(to_module_order)
         if self._has_mean_pooling_callback and ctx.divisor is not None:
@@ -677,6 +759,17 @@ class ShardedEmbeddingBagCollection(
         if self._permute_op is None:
             return self._embedding_dims
         return [d for s in self._embedding_shardings for d in s.embedding_dims()]
+
+
+class EngineDistInput(Multistreamable):
+    """What ``input_dist`` hands to ``compute`` when the fused sparse engine took the batch: the ids already sit in this
+    rank's receive buffers; the handle names them."""
+
+    def __init__(self, handle) -> None:
+        self.handle = handle
+
+    def record_stream(self, stream: torch.Stream) -> None:
+        self.handle.record_stream(stream)
 
 
 class _ViewParameter(nn.Parameter):

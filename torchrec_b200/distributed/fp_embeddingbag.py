@@ -32,6 +32,7 @@ class ShardedFeatureProcessedEmbeddingBagCollection(ShardedEmbeddingModule[KJTLi
         self._embedding_bag_collection: ShardedEmbeddingBagCollection = ebc_sharder.shard(
             module._embedding_bag_collection, table_name_to_parameter_sharding, env=env, device=device,
             module_fqn=(module_fqn + "._embedding_bag_collection") if module_fqn else None)
+        self._embedding_bag_collection.disable_fused_engine()  # the processors run between input dist and lookup
         # row-wise input distributions must ship the position of every id in its bag
         for sharding in self._embedding_bag_collection._embedding_shardings:
             if hasattr(sharding, "_has_feature_processor"):

@@ -129,6 +129,7 @@ class ShardedITEPEmbeddingBagCollection(_ShardedITEPBase):
         self._embedding_bag_collection: ShardedEmbeddingBagCollection = ebc_sharder.shard(
             module._embedding_bag_collection, table_name_to_parameter_sharding, env=env, device=device,
             module_fqn=(module_fqn + "._embedding_bag_collection") if module_fqn else None)
+        self._embedding_bag_collection.disable_fused_engine()  # ids are remapped between input dist and lookup
         self._setup(self._embedding_bag_collection, module._itep_module, table_name_to_parameter_sharding, env)
 
     @property

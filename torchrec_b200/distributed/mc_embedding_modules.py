@@ -25,6 +25,8 @@ class BaseShardedManagedCollisionEmbeddingCollection(ShardedEmbeddingModule):
         self._return_remapped_features = module._return_remapped_features
         self._embedding_module = e_sharder.shard(module._embedding_module, table_name_to_parameter_sharding, env=env, device=device,
                                                  module_fqn=(module_fqn + "._embedding_module") if module_fqn else None)
+        if hasattr(self._embedding_module, "disable_fused_engine"):
+            self._embedding_module.disable_fused_engine()  # ids are remapped on the owning rank between input dist and lookup
         self._managed_collision_collection = ShardedManagedCollisionCollection(module._managed_collision_collection, table_name_to_parameter_sharding, env, device)
         sizes = self._managed_collision_collection.table_input_sizes()
         buckets = self._managed_collision_collection.table_total_num_buckets()

@@ -67,12 +67,6 @@ class TwPooledEmbeddingDist(BaseEmbeddingDist[EmbeddingShardingContext, torch.Te
         self._variable_dist: Optional[VariableBatchPooledEmbeddingsAllToAll] = None
 
     def forward(self, local_embs: torch.Tensor, sharding_ctx: Optional[EmbeddingShardingContext] = None) -> Awaitable[torch.Tensor]:
-        if getattr(local_embs, "_trb_exchanged", False):
-            # the lookup kernel already delivered the rows to their owners (fused lookup + exchange)
-            if self._callbacks:
-                for cb in self._callbacks:
-                    local_embs = cb(local_embs)
-            return NoWait(local_embs)
         if self._dist is None:
             self._create_output_dist_module(sharding_ctx)
         if sharding_ctx is None:
@@ -106,36 +100,7 @@ class TwPooledEmbeddingSharding(BaseTwEmbeddingSharding[EmbeddingShardingContext
             grouped_configs=self._grouped_embedding_configs, pg=self._pg, device=device if device is not None else self._device,
             feature_processor=feature_processor, sharding_type=ShardingType.TABLE_WISE,
         )
-        self._maybe_enable_peer_exchange(lookup, device if device is not None else self._device, feature_processor)
         return lookup
-
-    def _maybe_enable_peer_exchange(self, lookup: GroupedPooledEmbeddingsLookup, device: Optional[torch.device], feature_processor) -> None:
-        """Use the fused lookup + exchange kernel when the whole sharding qualifies: one node with peer access, every
-        table with a fused optimizer, one output dtype, no feature processor.  All ranks see the same tables, so they
-        decide alike; the peer set-up itself is agreed on with a collective."""
-        from torchrec_b200.distributed.embedding_types import EmbeddingComputeKernel
-        from torchrec_b200.distributed.peer_memory import PeerGroup, peer_exchange_enabled
-
-        if feature_processor is not None or not peer_exchange_enabled() or device is None or device.type != "cuda":
-            return
-        tables = self.embedding_tables()
-        fused = (EmbeddingComputeKernel.FUSED, EmbeddingComputeKernel.FUSED_UVM, EmbeddingComputeKernel.FUSED_UVM_CACHING)
-        if not tables or any(t.compute_kernel not in fused or t.has_feature_processor for t in tables):
-            return
-        dtypes = {(t.fused_params or {}).get("output_dtype", None) for t in tables}
-        if len(dtypes) != 1:
-            return
-        out_dtype = dtypes.pop()
-        if out_dtype is None:
-            out_dtype = torch.float32
-        elif not isinstance(out_dtype, torch.dtype):
-            from torchrec_b200.modules.embedding_configs import data_type_to_dtype
-
-            out_dtype = data_type_to_dtype(out_dtype)
-        peer = PeerGroup.get(self._pg, device)
-        if peer is None:
-            return
-        lookup.enable_peer_exchange(peer, self._dim_sum_per_rank(), out_dtype)
 
     def create_output_dist(self, device: Optional[torch.device] = None) -> BaseEmbeddingDist[EmbeddingShardingContext, torch.Tensor, torch.Tensor]:
         assert self._pg is not None

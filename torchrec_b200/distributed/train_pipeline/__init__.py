@@ -20,3 +20,4 @@ from torchrec_b200.distributed.train_pipeline.train_pipelines import (  # noqa: 
 from torchrec_b200.distributed.train_pipeline.types import ArgInfo, CallArgs, PipelineState  # noqa: F401
 from torchrec_b200.distributed.train_pipeline.utils import DataLoadingThread, In, Out, _to_device, _wait_for_batch  # noqa: F401
 from torchrec_b200.distributed.train_pipeline.postproc import PipelinedPostproc  # noqa: F401
+from torchrec_b200.distributed.train_pipeline.graphed import TrainPipelineGraphed  # noqa: F401

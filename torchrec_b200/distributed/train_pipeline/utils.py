@@ -255,6 +255,11 @@ def _wait_data_dist(context: TrainPipelineContext) -> None:
     for names, awaitable in context.fused_splits_awaitables:
         for name, request in zip(names, awaitable.wait()):
             context.input_dist_tensors_requests[name] = request
+    fused = {n for names, _ in context.fused_splits_awaitables for n in names}
+    for name, request in context.input_dist_splits_requests.items():
+        if name not in fused:
+            # a module whose input distribution has no split-size stage (the fused sparse engine keeps sizes on the device)
+            context.input_dist_tensors_requests[name] = request.wait()
     context.input_dist_splits_requests.clear()
     context.fused_splits_awaitables.clear()
 

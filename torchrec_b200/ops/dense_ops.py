@@ -55,10 +55,35 @@ def fused_dense_enabled(x: torch.Tensor) -> bool:
 # bf16 weight cache: one cast per parameter version, shared by forward and backward
 # --------------------------------------------------------------------------------------
 class _Bf16Cache:
+    """bf16 (and transposed bf16) copies of fp32 parameters.
+
+    Unmanaged parameters are re-cast when their version counter moves.  Parameters of a ``FlatParamBuffer``
+    (``optim/fused_dense.py``) are *managed*: their copies live at fixed addresses and are rewritten by the optimizer
+    kernel itself, so a forward pass launches no cast; a managed copy is only refreshed here when the parameter was
+    changed behind the optimizer's back (a checkpoint load, an in-place init)."""
+
     def __init__(self) -> None:
         self._store = {}
+        self._managed = {}
+
+    def register(self, p: torch.Tensor, w16: torch.Tensor, wT16: Optional[torch.Tensor]) -> None:
+        self._managed[id(p)] = [p._version, w16, wT16, p]
+
+    def mark_fresh(self, p: torch.Tensor) -> None:
+        ent = self._managed.get(id(p))
+        if ent is not None:
+            ent[0] = p._version
 
     def get(self, p: torch.Tensor, transposed: bool = False) -> torch.Tensor:
+        m = self._managed.get(id(p))
+        if m is not None and m[3] is p and (m[2] is not None or not transposed):
+            if m[0] != p._version:
+                with torch.no_grad():
+                    m[1].copy_(p.detach())
+                    if m[2] is not None:
+                        m[2].copy_(p.detach().reshape(m[2].shape[1], m[2].shape[0]).t())
+                m[0] = p._version
+            return m[2] if transposed else m[1]
         key = (id(p), transposed)
         ent = self._store.get(key)
         ver = p._version
@@ -71,6 +96,7 @@ class _Bf16Cache:
 
     def clear(self) -> None:
         self._store.clear()
+        self._managed.clear()
 
 
 bf16_cache = _Bf16Cache()

@@ -82,10 +82,12 @@ class TBEPlan:
     """Sorted (row -> contributing bags) plan of one batch; built from ids only.  ``ready`` is set when the plan was built on a
     side stream: the consumer's stream waits for it before the backward kernels read the plan."""
 
-    __slots__ = ("keys", "src", "w", "src_feature", "bag_scale", "ready")
+    __slots__ = ("keys", "src", "w", "src_feature", "bag_scale", "n_valid", "ready")
 
     def __init__(self, tensors: List[torch.Tensor]) -> None:
-        self.keys, self.src, self.w, self.src_feature, self.bag_scale = tensors
+        self.keys, self.src, self.w, self.src_feature, self.bag_scale = tensors[:5]
+        # padded plans (ids in a fixed-capacity buffer): number of real entries, kept on the device
+        self.n_valid: Optional[torch.Tensor] = tensors[5] if len(tensors) > 5 else None
         self.ready = None
 
     def wait(self) -> None:
@@ -97,6 +99,20 @@ class TBEPlan:
 # The id sort of the backward depends on the ids only.  It is memory-bound while the dense towers that run between an embedding
 # forward and its backward are tensor-core-bound, so it is issued on a side stream right after the forward lookup and overlaps them.
 _PLAN_AHEAD = os.environ.get("TRB200_PLAN_AHEAD", "1") != "0"
+# "kernel": the sm_100a kernels (the product).  "torch": the composite torch implementation on the device as well -- gather,
+# ``embedding_bag``, ``unique`` + ``index_add`` and the optimizer written out in torch ops -- which is what a framework without
+# its own embedding kernels runs; benchmarks use it as the plain-library baseline.
+_TBE_BACKEND = os.environ.get("TRB200_TBE", "kernel")
+
+
+def set_tbe_backend(name: str) -> None:
+    global _TBE_BACKEND
+    assert name in ("kernel", "torch")
+    _TBE_BACKEND = name
+
+
+def get_tbe_backend() -> str:
+    return _TBE_BACKEND
 _plan_streams: Dict[int, "torch.cuda.Stream"] = {}
 
 
@@ -312,7 +328,7 @@ class TableBatchedEmbeddingBags(nn.Module):
 
     def _forward_impl(self, indices, offsets, psw, B) -> torch.Tensor:
         w = self.weights.detach()
-        if w.is_cuda:
+        if w.is_cuda and _TBE_BACKEND == "kernel":
             _ext.require_cuda_ext("tbe_forward")
             meta = self._meta_tensor(w.device)
             if indices.dtype != offsets.dtype:
@@ -351,10 +367,12 @@ class TableBatchedEmbeddingBags(nn.Module):
         return out.to(self.output_dtype)
 
     # ---- backward ---------------------------------------------------------------------
-    def build_plan(self, indices: torch.Tensor, offsets: torch.Tensor, psw: Optional[torch.Tensor], B: int) -> Optional[TBEPlan]:
+    def build_plan(self, indices: torch.Tensor, offsets: torch.Tensor, psw: Optional[torch.Tensor], B: int, padded: bool = False) -> Optional[TBEPlan]:
         """Sort the ids of a batch by table row.  Depends on the ids only, so it can run ahead of
-        the backward pass (e.g. on a side stream during the dense forward)."""
-        if not self.weights.is_cuda:
+        the backward pass (e.g. on a side stream during the dense forward).  ``padded``: ``indices`` is a buffer of
+        fixed capacity and only positions ``[offsets[0], offsets[-1])`` hold ids of this module; the count of real
+        entries stays on the device (``TBEPlan.n_valid``)."""
+        if not self.weights.is_cuda or _TBE_BACKEND != "kernel":
             return None
         meta = self._meta_tensor(self.weights.device)
         if indices.dtype != offsets.dtype:
@@ -362,23 +380,23 @@ class TableBatchedEmbeddingBags(nn.Module):
         return TBEPlan(
             torch.ops.trb200.tbe_build_plan(
                 meta, indices.contiguous(), offsets.contiguous(), psw, B, max(self.total_rows, 2),
-                self.pooling_mode != PoolingMode.NONE, self.pooling_mode == PoolingMode.MEAN, self._err,
+                self.pooling_mode != PoolingMode.NONE, self.pooling_mode == PoolingMode.MEAN, padded, self._err,
             )
         )
 
-    def build_plan_ahead(self, indices: torch.Tensor, offsets: torch.Tensor, psw: Optional[torch.Tensor], B: int) -> Optional[TBEPlan]:
+    def build_plan_ahead(self, indices: torch.Tensor, offsets: torch.Tensor, psw: Optional[torch.Tensor], B: int, padded: bool = False) -> Optional[TBEPlan]:
         """:meth:`build_plan` issued on the side stream, ordered after everything already queued on the current stream.  The
         plan's tensors are marked as used by the current stream so that their memory is not recycled under the backward."""
-        if not (_PLAN_AHEAD and self.weights.is_cuda and indices.numel() > 0):
+        if not (_PLAN_AHEAD and self.weights.is_cuda and indices.numel() > 0 and _TBE_BACKEND == "kernel"):
             return None
         cur = torch.cuda.current_stream()
         side = _plan_stream(self.weights.device)
         side.wait_stream(cur)
         with torch.cuda.stream(side):
-            plan = self.build_plan(indices, offsets, psw, B)
+            plan = self.build_plan(indices, offsets, psw, B, padded)
             plan.ready = torch.cuda.Event()
             plan.ready.record(side)
-        for t in (plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale):
+        for t in (plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale, plan.n_valid):
             if t is not None and t.numel() > 0:
                 t.record_stream(cur)
         for t in (indices, offsets, psw):
@@ -390,7 +408,7 @@ class TableBatchedEmbeddingBags(nn.Module):
         w = self.weights.detach()
         if self.fused:
             self.step += 1
-        if w.is_cuda:
+        if w.is_cuda and _TBE_BACKEND == "kernel":
             _ext.require_cuda_ext("tbe_backward")
             if plan is None:
                 plan = self.build_plan(indices, offsets, psw, B)
@@ -411,7 +429,7 @@ class TableBatchedEmbeddingBags(nn.Module):
                 w, self.momentum1 if self.momentum1.numel() else None, self.momentum2 if self.momentum2.numel() else None,
                 dense_grad, self._meta_tensor(w.device), plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale,
                 grad_out, grad_out.stride(0), B, self.max_D, self.pooling_mode != PoolingMode.NONE, code,
-                o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay, self.step, o.max_gradient,
+                o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay, self.step, o.max_gradient, plan.n_valid,
             )
             return None if self.fused else dense_grad.to(w.dtype)
         return self._backward_cpu(w, grad_out, indices, offsets, psw, B)
@@ -434,7 +452,7 @@ class TableBatchedEmbeddingBags(nn.Module):
         return cache[key]
 
     def forward_push(self, indices: torch.Tensor, offsets: torch.Tensor, psw: Optional[torch.Tensor], B: int, B_local: int,
-                     out_ptrs: List[int], out_stride: int, col_base, out_dtype: torch.dtype) -> None:
+                     out_ptrs: List[int], out_stride: int, col_base, out_dtype: torch.dtype, pooling: Optional[int] = None) -> None:
         """Pooled lookup of the global batch (``B`` bags per feature) whose result rows are stored directly into the
         ``[B_local, out_stride]`` buffers of the ranks that own the samples (``out_ptrs[b // B_local]``), at column
         ``col_base`` + the table's offset.  No output tensor: the caller synchronises with a peer barrier."""
@@ -444,11 +462,12 @@ class TableBatchedEmbeddingBags(nn.Module):
             offsets = offsets.to(indices.dtype)
         torch.ops.trb200.tbe_forward_dist(
             w, self._meta_tensor_at(w.device, col_base), indices.contiguous(), offsets.contiguous(), psw, out_ptrs,
-            _OUT_CODE[out_dtype], out_stride, B, B_local, self.max_D, int(self.pooling_mode), False, False, self._err,
+            _OUT_CODE[out_dtype], out_stride, B, B_local, self.max_D, int(self.pooling_mode) if pooling is None else pooling, False, False, self._err,
         )
 
     def backward_pull(self, grad_local: torch.Tensor, grad_ptrs: List[int], grad_stride: int, indices: torch.Tensor, offsets: torch.Tensor,
-                      psw: Optional[torch.Tensor], B: int, B_local: int, col_base, grad_scale: float, plan: Optional[TBEPlan] = None) -> None:
+                      psw: Optional[torch.Tensor], B: int, B_local: int, col_base, grad_scale: float, plan: Optional[TBEPlan] = None,
+                      padded: bool = False) -> None:
         """Backward + fused optimizer of ``forward_push``: the gradient row of bag ``b`` is read from
         ``grad_ptrs[b // B_local]`` (``grad_local`` is this rank's own buffer among them)."""
         assert self.fused, "the fused exchange is for tables with an in-backward optimizer"
@@ -456,7 +475,7 @@ class TableBatchedEmbeddingBags(nn.Module):
         w = self.weights.detach()
         self.step += 1
         if plan is None:
-            plan = self.build_plan(indices, offsets, psw, B)
+            plan = self.build_plan(indices, offsets, psw, B, padded)
         else:
             plan.wait()
         o = self.optimizer_args
@@ -465,7 +484,7 @@ class TableBatchedEmbeddingBags(nn.Module):
             w, self.momentum1 if self.momentum1.numel() else None, self.momentum2 if self.momentum2.numel() else None, None,
             self._meta_tensor_at(w.device, col_base), plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale, grad_local,
             grad_stride, B, self.max_D, True, _OPT_CODE[o.optimizer], o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay,
-            self.step, o.max_gradient, grad_ptrs, B_local, grad_scale,
+            self.step, o.max_gradient, grad_ptrs, B_local, grad_scale, plan.n_valid,
         )
 
     def _psw_grad(self, grad_out: torch.Tensor, indices: torch.Tensor, offsets: torch.Tensor, B: int) -> torch.Tensor:
