@@ -1,8 +1,12 @@
-"""Fused lookup + exchange over peer-mapped buffers (2 GPUs) against the library all-to-all path: the same sharded
-model is built twice, once with ``TRB200_PEER_EXCHANGE=0``; pooled outputs and the tables after two optimizer steps
-must agree.  Also checks the device-side barrier's bounded wait path on the host side of its API."""
+"""Fused sparse engine on real ranks (2 GPUs, NCCL control plane) against the library-collective path: the same sharded
+model is built twice, once with ``TRB200_PEER_EXCHANGE=0``; pooled outputs and the tables after three optimizer steps
+must agree.  The plan mixes table-wise, row-wise and column-wise tables, one table has two features.
+
+A second test makes one rank arrive late by more than a (shortened) wait limit: the waiting rank's kernels return, its
+step raises on the host and nothing faults.  NVLS is off and only plain peer loads / stores are used."""
 import copy
 import os
+import time
 
 import pytest
 import torch
@@ -11,7 +15,8 @@ from torchrec_b200.test_utils.multi_process import MultiProcessContext, run_mult
 
 pytestmark = pytest.mark.gpu
 
-TABLES = [(1000, 128, ["f0"]), (600, 128, ["f1", "f2"]), (33, 128, ["f3"]), (500, 128, ["f4"]), (77, 128, ["f5"])]
+TABLES = [(1000, 128, ["f0"]), (600, 128, ["f1", "f2"]), (33, 128, ["f3"]), (500, 128, ["f4"]), (77, 64, ["f5"])]
+KINDS = ["tw", "rw", "tw", "cw", "rw"]
 
 
 def _make_ebc(pooling):
@@ -40,7 +45,7 @@ class _Model(torch.nn.Module):
     def __init__(self, ebc):
         super().__init__()
         self.ebc = ebc
-        self.over = torch.nn.Linear(sum(len(f) for _, _, f in TABLES) * 128, 1)
+        self.over = torch.nn.Linear(sum(len(f) * d for _, d, f in TABLES), 1)
 
     def forward(self, kjt):
         kt = self.ebc(kjt)
@@ -48,7 +53,7 @@ class _Model(torch.nn.Module):
         return self.over(v), v
 
 
-def _build(ctx, rank, world_size, pooling, peer):
+def _build(ctx, world_size, pooling, peer):
     from torchrec_b200.distributed import sharding_plan as sp
     from torchrec_b200.distributed.embeddingbag import EmbeddingBagCollectionSharder
     from torchrec_b200.distributed.model_parallel import DistributedModelParallel
@@ -62,51 +67,47 @@ def _build(ctx, rank, world_size, pooling, peer):
     model = _Model(_make_ebc(pooling))
     apply_optimizer_in_backward(RowWiseAdagrad, model.ebc.parameters(), {"lr": 0.1, "eps": 1e-8})
     sharder = EmbeddingBagCollectionSharder(fused_params={"output_dtype": DataType.BF16})
-    # ranks [1, 0, 1, 1, 0]: rank 0 owns two tables, rank 1 three; t1 has two features
-    gens = {f"t{i}": sp.table_wise(rank=[1, 0, 1, 1, 0][i]) for i in range(len(TABLES))}
+    gens = {}
+    for i, kind in enumerate(KINDS):
+        gens[f"t{i}"] = {"tw": sp.table_wise(rank=[1, 0, 1, 1, 0][i]), "rw": sp.row_wise(), "cw": sp.column_wise(ranks=[1, 0])}[kind]
     plan = ShardingPlan({"ebc": sp.construct_module_sharding_plan(model.ebc, gens, sharder=sharder, world_size=world_size, local_size=world_size, device_type="cuda")})
     return DistributedModelParallel(model, env=ShardingEnv.from_process_group(ctx.pg), device=ctx.device, plan=plan, sharders=[sharder])
 
 
+def _sharded_ebc(dmp):
+    from torchrec_b200.distributed.embeddingbag import ShardedEmbeddingBagCollection
+
+    return [m for m in dmp.modules() if isinstance(m, ShardedEmbeddingBagCollection)][0]
+
+
 def _run(rank, world_size, pooling_name):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    from torchrec_b200.distributed.embedding_lookup import GroupedPooledEmbeddingsLookup
+    from torchrec_b200.distributed.peer_memory import check_all
     from torchrec_b200.modules.embedding_configs import PoolingType
 
     with MultiProcessContext(rank, world_size, "nccl") as ctx:
         pooling = PoolingType[pooling_name]
-        ref = _build(ctx, rank, world_size, pooling, peer=False)
-        fused = _build(ctx, rank, world_size, pooling, peer=True)
+        ref = _build(ctx, world_size, pooling, peer=False)
+        fused = _build(ctx, world_size, pooling, peer=True)
         fused.load_state_dict(copy.deepcopy(ref.state_dict()))
-        def lookups_of(dmp):
-            from torchrec_b200.distributed.embeddingbag import ShardedEmbeddingBagCollection
-
-            out = []
-            for m in dmp.modules():
-                if isinstance(m, ShardedEmbeddingBagCollection):
-                    out += [l for l in m._lookups if isinstance(l, GroupedPooledEmbeddingsLookup)]
-            return out
-
-        lookups = lookups_of(fused)
-        assert lookups and all(m._peer is not None for m in lookups), "the fused exchange must be active on a 2-GPU node"
-        assert all(m._peer is None for m in lookups_of(ref))
         opt_r = torch.optim.SGD([p for n, p in ref.named_parameters() if "ebc" not in n], lr=0.05)
         opt_f = torch.optim.SGD([p for n, p in fused.named_parameters() if "ebc" not in n], lr=0.05)
-        B = 64
+        B = 300
         for step in range(3):
             kjt = _make_kjt(B, 100 + 10 * step + rank, ctx.device)
             opt_r.zero_grad(); opt_f.zero_grad()
+            os.environ["TRB200_PEER_EXCHANGE"] = "0"
             pr, vr = ref(kjt)
+            os.environ["TRB200_PEER_EXCHANGE"] = "1"
             pf, vf = fused(kjt)
             torch.testing.assert_close(vf, vr, rtol=2e-2, atol=2e-2)  # bf16 outputs on both paths (fp16 wire on the reference one)
             pr.mean().backward()
             pf.mean().backward()
             opt_r.step(); opt_f.step()
         torch.cuda.synchronize()
-        for m in lookups:
-            m._peer.check_error()
-        # the tables were placed out of order, so the exchange stored them at their final columns instead of permuting afterwards
-        assert all(m._peer_feature_columns is not None for m in lookups)
+        check_all()
+        assert _sharded_ebc(fused)._engine is not None, "the fused sparse engine must be active on a 2-GPU node"
+        assert _sharded_ebc(ref)._engine is None
         sd_r, sd_f = ref.state_dict(), fused.state_dict()
         for name, vr in sd_r.items():
             vf = sd_f[name]
@@ -118,7 +119,39 @@ def _run(rank, world_size, pooling_name):
 
 
 @pytest.mark.parametrize("pooling_name", ["SUM", "MEAN"])
-def test_peer_exchange_matches_all_to_all(pooling_name):
+def test_engine_matches_library_collectives(pooling_name):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     run_multi_process(_run, world_size=2, pooling_name=pooling_name)
+
+
+def _run_late(rank, world_size):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["TRB200_PEER_WAIT_S"] = "0.5"
+    from torchrec_b200.distributed.peer_memory import check_all
+    from torchrec_b200.modules.embedding_configs import PoolingType
+
+    with MultiProcessContext(rank, world_size, "nccl") as ctx:
+        model = _build(ctx, world_size, PoolingType.SUM, peer=True)
+        kjt = _make_kjt(64, rank, ctx.device)
+        model(kjt)  # sizes the buffers, both ranks in step
+        torch.cuda.synchronize()
+        check_all()
+        import torch.distributed as dist
+
+        dist.barrier(group=ctx.pg)
+        if rank == 1:
+            time.sleep(3.0)  # far past the 0.5 s wait limit: rank 0's kernels give up and return
+        _, v = model(kjt)
+        torch.cuda.synchronize()
+        if rank == 0:
+            assert torch.isnan(v).any(), "a step whose wait ran out must not hand on stale rows"
+            with pytest.raises(RuntimeError, match="timed out waiting for rank 1"):
+                check_all()
+        dist.barrier(group=ctx.pg)
+
+
+def test_late_rank_raises_on_the_waiting_rank():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    run_multi_process(_run_late, world_size=2)

@@ -60,66 +60,90 @@ class DataParallelWrapper(abc.ABC):
         ...
 
 
+_COMPRESSION_HOOKS = {"fp16": ddp_default_hooks.fp16_compress_hook, "bf16": ddp_default_hooks.bf16_compress_hook}
+
+
 class DefaultDataParallelWrapper(DataParallelWrapper):
     """DDP over every parameter that is not owned by a sharded module.
 
     25 MB buckets, static graph, gradients as bucket views; optional fp16 / bf16 gradient compression.
+    (``PeerDataParallelWrapper`` in ``peer_data_parallel.py`` is the single-node alternative that needs no DDP.)
     """
 
     def __init__(self, bucket_cap_mb: int = 25, static_graph: bool = True, find_unused_parameters: bool = False,
                  allreduce_comm_precision: Optional[str] = None, params_to_ignore: Optional[List[str]] = None,
                  ddp_kwargs: Optional[Dict[str, Any]] = None) -> None:
-        self._bucket_cap_mb = bucket_cap_mb
-        self._static_graph = static_graph
-        self._find_unused_parameters = find_unused_parameters
+        self._ddp_options: Dict[str, Any] = dict(bucket_cap_mb=bucket_cap_mb, static_graph=static_graph, find_unused_parameters=find_unused_parameters,
+                                                 gradient_as_bucket_view=True, broadcast_buffers=False)
+        self._ddp_options.update(ddp_kwargs or {})
         self._allreduce_comm_precision = allreduce_comm_precision
         self._additional_params_to_ignore: Set[str] = set(params_to_ignore or [])
-        self._ddp_kwargs: Dict[str, Any] = ddp_kwargs or {}
 
     def _ddp_wrap(self, dmp: "DistributedModelParallel", env: ShardingEnv, device: torch.device, ddp_ignore_param_names: Set[str]) -> None:
-        pg = env.process_group
-        if pg is None:
+        if env.process_group is None:
             raise RuntimeError("Can only init DDP for ProcessGroup-based ShardingEnv")
-        # parameters that take no gradient (slot tables of collision modules) need no all-reduce either
-        all_parameter_names = {n for n, p in dmp.named_parameters() if p.requires_grad}
-        if len(all_parameter_names - ddp_ignore_param_names) == 0:
-            return
-        DistributedDataParallel._set_params_and_buffers_to_ignore_for_model(module=dmp._dmp_wrapped_module, params_and_buffers_to_ignore=ddp_ignore_param_names)
-        dmp._dmp_wrapped_module = cast(
-            nn.Module,
-            DistributedDataParallel(
-                module=dmp._dmp_wrapped_module.to(device), device_ids=None if device.type == "cpu" else [device], process_group=pg,
-                gradient_as_bucket_view=True, broadcast_buffers=False, static_graph=self._static_graph,
-                find_unused_parameters=self._find_unused_parameters, bucket_cap_mb=self._bucket_cap_mb, **self._ddp_kwargs,
-            ),
-        )
-        if self._allreduce_comm_precision == "fp16":
-            dmp._dmp_wrapped_module.register_comm_hook(None, ddp_default_hooks.fp16_compress_hook)
-        elif self._allreduce_comm_precision == "bf16":
-            dmp._dmp_wrapped_module.register_comm_hook(None, ddp_default_hooks.bf16_compress_hook)
+        trainable = {name for name, p in dmp.named_parameters() if p.requires_grad}
+        if trainable <= ddp_ignore_param_names:
+            return  # nothing left to average (e.g. a model that is all embedding tables)
+        inner = dmp._dmp_wrapped_module
+        DistributedDataParallel._set_params_and_buffers_to_ignore_for_model(module=inner, params_and_buffers_to_ignore=ddp_ignore_param_names)
+        ddp = DistributedDataParallel(module=inner.to(device), device_ids=[device] if device.type != "cpu" else None,
+                                      process_group=env.process_group, **self._ddp_options)
+        hook = _COMPRESSION_HOOKS.get(self._allreduce_comm_precision or "")
+        if hook is not None:
+            ddp.register_comm_hook(None, hook)
+        dmp._dmp_wrapped_module = cast(nn.Module, ddp)
 
     def wrap(self, dmp: "DistributedModelParallel", env: ShardingEnv, device: torch.device) -> None:
         if isinstance(dmp._dmp_wrapped_module, DistributedDataParallel):
             return
-        sharded_parameter_names = set(DistributedModelParallel._sharded_parameter_names(dmp._dmp_wrapped_module))
-        self._ddp_wrap(dmp, env, device, sharded_parameter_names.union(self._additional_params_to_ignore))
+        owned_by_shards = set(DistributedModelParallel._sharded_parameter_names(dmp._dmp_wrapped_module))
+        self._ddp_wrap(dmp, env, device, owned_by_shards | self._additional_params_to_ignore)
+
+
+def _strip(module: nn.Module, ddp_too: bool) -> nn.Module:
+    while True:
+        if isinstance(module, DistributedModelParallel):
+            module = module._dmp_wrapped_module
+        elif ddp_too and isinstance(module, DistributedDataParallel):
+            module = module.module
+        else:
+            return module
 
 
 def get_unwrapped_module(module: nn.Module) -> nn.Module:
     """Strip ``DistributedModelParallel`` / DDP wrappers."""
-    while isinstance(module, DistributedModelParallel) or isinstance(module, DistributedDataParallel):
-        if isinstance(module, DistributedModelParallel):
-            module = module._dmp_wrapped_module
-        else:
-            module = module.module
-    return module
+    return _strip(module, ddp_too=True)
 
 
 def get_module(module: nn.Module) -> nn.Module:
     """Strip ``DistributedModelParallel`` wrappers only (data-parallel wrappers stay)."""
-    while isinstance(module, DistributedModelParallel):
-        module = module._dmp_wrapped_module
-    return module
+    return _strip(module, ddp_too=False)
+
+
+def _join(prefix: str, name: str) -> str:
+    return f"{prefix}.{name}" if prefix else name
+
+
+def _leaves(module: nn.Module, prefix: str = "") -> Iterator[Tuple[str, nn.Module, bool]]:
+    """Depth-first walk that stops at sharded modules: yields ``(path, module, is_sharded)`` for every module visited,
+    with data-parallel wrappers looked through (so paths are those of the unsharded model)."""
+    module = get_unwrapped_module(module)
+    sharded = isinstance(module, ShardedModule)
+    yield prefix, module, sharded
+    if not sharded:
+        for name, child in module.named_children():
+            yield from _leaves(child, append_prefix(prefix, name))
+
+
+def _unique(pairs: Iterator[Tuple[str, Any]], remove_duplicate: bool) -> Iterator[Tuple[str, Any]]:
+    seen = set()
+    for name, t in pairs:
+        if t in seen:
+            continue
+        if remove_duplicate:
+            seen.add(t)
+        yield name, t
 
 
 class DistributedModelParallel(nn.Module, FusedOptimizerModule):
@@ -154,36 +178,33 @@ class DistributedModelParallel(nn.Module, FusedOptimizerModule):
         super().__init__()
         self.init_parameters = init_parameters
         self._ddp_wrapped: bool = False
-        if env is None:
-            pg = dist.GroupMember.WORLD
-            assert pg is not None, "Process group is not initialized"
-            env = ShardingEnv.from_process_group(pg)
-        self._env: ShardingEnv = env
-        if device is None:
-            device = torch.device("cpu")
-        self.device: torch.device = device
-        if sharders is None:
-            sharders = get_default_sharders()
+        self._env: ShardingEnv = env if env is not None else self._world_env()
+        self.device: torch.device = device if device is not None else torch.device("cpu")
+        sharders = sharders if sharders is not None else get_default_sharders()
         self._sharder_map: Dict[Type[nn.Module], ModuleSharder[nn.Module]] = {s.module_type: s for s in sharders}
-        if data_parallel_wrapper is None:
-            data_parallel_wrapper = DefaultDataParallelWrapper()
-        self._data_parallel_wrapper: DataParallelWrapper = data_parallel_wrapper
-        if plan is None:
-            from torchrec_b200.distributed.planner import EmbeddingShardingPlanner, Topology
-
-            planner = EmbeddingShardingPlanner(
-                topology=Topology(local_world_size=get_local_size(self._env.world_size), world_size=self._env.world_size, compute_device=self.device.type)
-            )
-            pg = self._env.process_group
-            plan = planner.collective_plan(module, sharders, pg) if pg is not None else planner.plan(module, sharders)
-        self._plan: ShardingPlan = plan
+        self._data_parallel_wrapper: DataParallelWrapper = data_parallel_wrapper or DefaultDataParallelWrapper()
+        self._plan: ShardingPlan = plan if plan is not None else self._make_plan(module, sharders)
         self._dmp_wrapped_module: nn.Module = self._init_dmp(module)
         self._optim: CombinedOptimizer = self._init_optim(self._dmp_wrapped_module)
         if init_parameters:
             self._init_parameters(self.module)
         if init_data_parallel:
             self.init_data_parallel()
-        self.model_delta_tracker = self._init_delta_tracker(model_tracker_config, self._dmp_wrapped_module) if model_tracker_config is not None else None
+        self.model_delta_tracker = None if model_tracker_config is None else self._init_delta_tracker(model_tracker_config, self._dmp_wrapped_module)
+
+    @staticmethod
+    def _world_env() -> ShardingEnv:
+        world = dist.GroupMember.WORLD
+        assert world is not None, "Process group is not initialized"
+        return ShardingEnv.from_process_group(world)
+
+    def _make_plan(self, module: nn.Module, sharders: List[ModuleSharder[nn.Module]]) -> ShardingPlan:
+        from torchrec_b200.distributed.planner import EmbeddingShardingPlanner, Topology
+
+        topology = Topology(local_world_size=get_local_size(self._env.world_size), world_size=self._env.world_size, compute_device=self.device.type)
+        planner = EmbeddingShardingPlanner(topology=topology)
+        group = self._env.process_group
+        return planner.plan(module, sharders) if group is None else planner.collective_plan(module, sharders, group)
 
     @property
     def module(self) -> nn.Module:
@@ -201,19 +222,20 @@ class DistributedModelParallel(nn.Module, FusedOptimizerModule):
 
     def init_data_parallel(self) -> None:
         """Wrap the dense part (deferred form of ``init_data_parallel=True``); idempotent."""
-        if not self._ddp_wrapped:
-            self._data_parallel_wrapper.wrap(self, self._env, self.device)
-            self._ddp_wrapped = True
+        if self._ddp_wrapped:
+            return
+        self._data_parallel_wrapper.wrap(self, self._env, self.device)
+        self._ddp_wrapped = True
 
     def copy(self, device: torch.device) -> "DistributedModelParallel":
         """Copy of the wrapper whose dense part lives on ``device``; sharded modules are shared."""
         assert isinstance(device, torch.device)
         with sharded_model_copy(device=None):
-            copy_dmp = copy.deepcopy(self)
-        copy_dmp_wrapped_module = copy_to_device(self._dmp_wrapped_module, self.device, device)
-        copy_dmp._dmp_wrapped_module = copy_dmp_wrapped_module
-        return copy_dmp
+            twin = copy.deepcopy(self)
+        twin._dmp_wrapped_module = copy_to_device(self._dmp_wrapped_module, self.device, device)
+        return twin
 
+    # ---- construction steps ---------------------------------------------------------------------------------------------------
     def _init_dmp(self, module: nn.Module) -> nn.Module:
         return self._shard_modules_impl(module)
 
@@ -236,137 +258,102 @@ class DistributedModelParallel(nn.Module, FusedOptimizerModule):
         return CombinedOptimizer(self._fused_optim_impl(module, []))
 
     def _fused_optim_impl(self, module: nn.Module, fused_optims: List[Tuple[str, KeyedOptimizer]], path: str = "") -> List[Tuple[str, KeyedOptimizer]]:
-        if isinstance(module, FusedOptimizerModule):
-            fused_optims.append((path, module.fused_optimizer))
-            return fused_optims
-        for name, child in module.named_children():
-            self._fused_optim_impl(child, fused_optims, path + "." + name if path else name)
+        """Fused optimizers of the tree, keyed by the path of the module that owns them (a module that owns one is a leaf)."""
+        stack = [(path, module)]
+        found: List[Tuple[str, KeyedOptimizer]] = []
+        while stack:
+            where, m = stack.pop()
+            if isinstance(m, FusedOptimizerModule):
+                found.append((where, m.fused_optimizer))
+            else:
+                stack.extend((_join(where, n), c) for n, c in reversed(list(m.named_children())))
+        fused_optims.extend(found)
         return fused_optims
 
     def _shard_modules_impl(self, module: nn.Module, path: str = "") -> nn.Module:
+        """Replace every module the plan names by its sharded form, top-down (a replaced module is not descended into)."""
         if isinstance(module, ShardedModule):
             return module
-        module_sharding_plan = self._plan.get_plan_for_module(path)
-        if module_sharding_plan:
-            sharder_key = type(module)
-            module = self._sharder_map[sharder_key].shard(module, module_sharding_plan, self._env, self.device, path)
-            torch._C._log_api_usage_once(f"torchrec.distributed.{type(module).__name__}")
-            return module
-        for name, child in module.named_children():
-            child = self._shard_modules_impl(child, path + "." + name if path else name)
-            setattr(module, name, child)
+        plan_here = self._plan.get_plan_for_module(path)
+        if plan_here:
+            sharded = self._sharder_map[type(module)].shard(module, plan_here, self._env, self.device, path)
+            torch._C._log_api_usage_once(f"torchrec.distributed.{type(sharded).__name__}")
+            return sharded
+        for name, child in list(module.named_children()):
+            replacement = self._shard_modules_impl(child, _join(path, name))
+            if replacement is not child:
+                setattr(module, name, replacement)
         return module
 
     def _init_parameters(self, module: nn.Module) -> None:
-        @torch.no_grad()
-        def init(m: nn.Module) -> None:
-            if isinstance(m, ShardedModule):
-                return
-            init_parameters(m, self.device)
-
-        module.apply(init)
+        with torch.no_grad():
+            for _, m, sharded in _leaves(module):
+                if not sharded:
+                    init_parameters(m, self.device)
 
     # ---- named members with DDP prefixes removed and sharded modules reported under unsharded names ----
     def sparse_grad_parameter_names(self, destination: Optional[List[str]] = None, prefix: str = "") -> List[str]:
-        destination = [] if destination is None else destination
-        return self._sparse_grad_parameter_names(self.module, destination, prefix)
+        return self._sparse_grad_parameter_names(self.module, [] if destination is None else destination, prefix)
 
     def _sparse_grad_parameter_names(self, module: nn.Module, destination: List[str], prefix: str = "") -> List[str]:
-        module = get_unwrapped_module(module)
-        if isinstance(module, ShardedModule):
-            pass
-        elif isinstance(module, nn.Embedding):
-            if module.sparse:
-                destination.append(append_prefix(prefix, "weight"))
-        elif isinstance(module, nn.EmbeddingBag):
-            if module.sparse:
-                destination.append(append_prefix(prefix, "weight"))
-        else:
-            for name, child in module.named_children():
-                self._sparse_grad_parameter_names(child, destination, append_prefix(prefix, name))
+        for where, m, sharded in _leaves(module, prefix):
+            if not sharded and isinstance(m, (nn.Embedding, nn.EmbeddingBag)) and m.sparse:
+                destination.append(append_prefix(where, "weight"))
         return destination
 
     def state_dict(self, destination: Optional[Dict[str, Any]] = None, prefix: str = "", keep_vars: bool = False) -> Dict[str, Any]:
-        state_dict = get_module(self).state_dict(destination=destination, prefix=prefix, keep_vars=keep_vars)
-        torch.nn.modules.utils.consume_prefix_in_state_dict_if_present(state_dict, prefix + _DDP_STATE_DICT_PREFIX)
-        add_prefix_to_state_dict(state_dict, prefix)
-        return state_dict
+        sd = get_module(self).state_dict(destination=destination, prefix=prefix, keep_vars=keep_vars)
+        # keys of the unsharded model: no "module." of a data-parallel wrapper
+        torch.nn.modules.utils.consume_prefix_in_state_dict_if_present(sd, prefix + _DDP_STATE_DICT_PREFIX)
+        add_prefix_to_state_dict(sd, prefix)
+        return sd
 
     def load_state_dict(self, state_dict: "OrderedDict[str, torch.Tensor]", prefix: str = "", strict: bool = True) -> _IncompatibleKeys:
         return self._load_state_dict(self, state_dict, prefix, strict)
 
     def _load_state_dict(self, module: nn.Module, state_dict: "OrderedDict[str, torch.Tensor]", prefix: str = "", strict: bool = True) -> _IncompatibleKeys:
-        missing_keys: List[str] = []
-        unexpected_keys: List[str] = []
         module = get_module(module)
         if isinstance(module, DistributedDataParallel):
             torch.nn.modules.utils.consume_prefix_in_state_dict_if_present(state_dict, prefix)
             add_prefix_to_state_dict(state_dict, prefix + _DDP_STATE_DICT_PREFIX)
         if getattr(module, "_FORCE_STATE_DICT_LOAD", False):
             return module.load_state_dict(state_dict, strict=strict)
-        module._load_from_state_dict(state_dict, prefix, {}, strict, missing_keys, unexpected_keys, [])
+        missing: List[str] = []
+        unexpected: List[str] = []
+        module._load_from_state_dict(state_dict, prefix, {}, strict, missing, unexpected, [])
         for name, child in module.named_children():
-            m_keys, u_keys = self._load_state_dict(child, filter_state_dict(state_dict, prefix + name), "", strict)
-            missing_keys.extend(m_keys)
-            unexpected_keys.extend(u_keys)
-        return _IncompatibleKeys(missing_keys=missing_keys, unexpected_keys=unexpected_keys)
+            sub = self._load_state_dict(child, filter_state_dict(state_dict, prefix + name), "", strict)
+            missing += sub.missing_keys
+            unexpected += sub.unexpected_keys
+        return _IncompatibleKeys(missing_keys=missing, unexpected_keys=unexpected)
 
     def _named_parameters(self, module: nn.Module, prefix: str = "", recurse: bool = True, strip_ddp: bool = True) -> Iterator[Tuple[str, torch.nn.Parameter]]:
-        if strip_ddp:
-            module = get_unwrapped_module(module)
-        if isinstance(module, ShardedModule):
-            yield from module.named_parameters(prefix, recurse)
-        else:
+        if not strip_ddp and isinstance(module, DistributedDataParallel):
             yield from module.named_parameters(prefix, recurse=False)
             for name, child in module.named_children():
                 yield from self._named_parameters(child, append_prefix(prefix, name), recurse, strip_ddp)
+            return
+        for where, m, sharded in _leaves(module, prefix):
+            yield from m.named_parameters(where, recurse if sharded else False)
 
     def named_parameters(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True) -> Iterator[Tuple[str, torch.nn.Parameter]]:
-        gen = self._named_parameters(self.module, prefix, recurse)
-        memo = set()
-        for key, param in gen:
-            if param in memo:
-                continue
-            if remove_duplicate:
-                memo.add(param)
-            yield key, param
+        yield from _unique(self._named_parameters(self.module, prefix, recurse), remove_duplicate)
 
     def bare_named_parameters(self, prefix: str = "", recurse: bool = True) -> Iterator[Tuple[str, torch.nn.Parameter]]:
-        gen = self._named_parameters(self.module, prefix, recurse)
-        memo = set()
-        for key, param in gen:
-            if param in memo:
-                continue
-            memo.add(param)
-            yield key, param
+        yield from _unique(self._named_parameters(self.module, prefix, recurse), True)
 
     @staticmethod
     def _sharded_parameter_names(module: nn.Module, prefix: str = "") -> Iterator[str]:
-        module = get_unwrapped_module(module)
-        if isinstance(module, ShardedModule):
-            yield from module.sharded_parameter_names(prefix)
-        else:
-            for name, child in module.named_children():
-                yield from DistributedModelParallel._sharded_parameter_names(child, append_prefix(prefix, name))
+        for where, m, sharded in _leaves(module, prefix):
+            if sharded:
+                yield from m.sharded_parameter_names(where)
 
     def _named_buffers(self, module: nn.Module, prefix: str = "", recurse: bool = True) -> Iterator[Tuple[str, torch.Tensor]]:
-        module = get_unwrapped_module(module)
-        if isinstance(module, ShardedModule):
-            yield from module.named_buffers(prefix, recurse)
-        else:
-            yield from module.named_buffers(prefix, recurse=False)
-            for name, child in module.named_children():
-                yield from self._named_buffers(child, append_prefix(prefix, name), recurse)
+        for where, m, sharded in _leaves(module, prefix):
+            yield from m.named_buffers(where, recurse if sharded else False)
 
     def named_buffers(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True) -> Iterator[Tuple[str, torch.Tensor]]:
-        gen = self._named_buffers(self.module, prefix, recurse)
-        memo = set()
-        for key, param in gen:
-            if param in memo:
-                continue
-            if remove_duplicate:
-                memo.add(param)
-            yield key, param
+        yield from _unique(self._named_buffers(self.module, prefix, recurse), remove_duplicate)
 
     @property
     def fused_optimizer(self) -> KeyedOptimizer:
@@ -378,22 +365,33 @@ class DistributedModelParallel(nn.Module, FusedOptimizerModule):
 
     @staticmethod
     def _reset_parameters(module: nn.Module) -> None:
-        for _, m in module.named_modules():
-            if hasattr(m, "reset_parameters"):
-                m.reset_parameters()
+        for m in module.modules():
+            reset = getattr(m, "reset_parameters", None)
+            if reset is not None:
+                reset()
 
     def reshard(self, sharded_module_fqn: str, changed_shard_to_params: Dict[str, ParameterSharding]) -> None:
         """Move the shards of ``sharded_module_fqn`` to a new placement at run time (dynamic resharding)."""
         from torchrec_b200.distributed.sharding.dynamic_sharding import reshard_module
 
-        steps = sharded_module_fqn.split(".")
-        sharded_module = self.module
-        for s in steps:
-            sharded_module = getattr(sharded_module, s)
-        assert isinstance(sharded_module, ShardedModule)
-        reshard_module(self, sharded_module_fqn, sharded_module, changed_shard_to_params)
+        target = self.module.get_submodule(sharded_module_fqn)
+        assert isinstance(target, ShardedModule)
+        reshard_module(self, sharded_module_fqn, target, changed_shard_to_params)
         self._optim = self._init_optim(self._dmp_wrapped_module)
-        self._plan.plan[sharded_module_fqn] = sharded_module.module_sharding_plan
+        self._plan.plan[sharded_module_fqn] = target.module_sharding_plan
+
+
+def _rank_groups(world_size: int, group_size: int, contiguous: bool) -> Tuple[List[List[int]], List[List[int]]]:
+    """(sharding groups, replica groups).  ``contiguous``: a sharding group is a run of consecutive ranks (one host) and its
+    replicas are the ranks with the same position in other runs; otherwise sharding groups are strided over the world."""
+    n_groups = world_size // group_size
+    if contiguous:
+        shard = [list(range(g * group_size, (g + 1) * group_size)) for g in range(n_groups)]
+        replica = [list(range(i, world_size, group_size)) for i in range(group_size)]
+    else:
+        shard = [list(range(g, world_size, n_groups)) for g in range(n_groups)]
+        replica = [list(range(i * n_groups, (i + 1) * n_groups)) for i in range(group_size)]
+    return shard, replica
 
 
 class DMPCollection(DistributedModelParallel):
@@ -420,8 +418,7 @@ class DMPCollection(DistributedModelParallel):
     ) -> None:
         assert device.type in ("cuda", "cpu"), "DMPCollection needs a cuda or cpu device"
         assert sharding_group_size > 0 and world_size % sharding_group_size == 0, "sharding_group_size must divide the world size"
-        self._global_pg = global_pg
-        self._global_rank = dist.get_rank(global_pg)
+        self._global_pg, self._global_rank = global_pg, dist.get_rank(global_pg)
         self._device = device
         self._custom_all_reduce = custom_all_reduce
         self._use_inter_host_allreduce = use_inter_host_allreduce
@@ -433,84 +430,69 @@ class DMPCollection(DistributedModelParallel):
 
     @staticmethod
     def _create_process_groups(global_pg, world_size: int, sharding_group_size: int, inter_host: bool):
-        """``sharding_pg``: ranks that shard together; ``replica_pg``: ranks holding the same shard."""
-        rank = dist.get_rank(global_pg)
-        backend = dist.get_backend(global_pg)
-        n_groups = world_size // sharding_group_size
-        sharding_pg = replica_pg = None
-        if inter_host:
-            shard_groups = [list(range(g * sharding_group_size, (g + 1) * sharding_group_size)) for g in range(n_groups)]
-            replica_groups = [list(range(i, world_size, sharding_group_size)) for i in range(sharding_group_size)]
-        else:
-            shard_groups = [list(range(g, world_size, n_groups)) for g in range(n_groups)]
-            replica_groups = [list(range(i * n_groups, (i + 1) * n_groups)) for i in range(sharding_group_size)]
-        for ranks in shard_groups:
-            pg = dist.new_group(ranks=ranks, backend=backend)
-            if rank in ranks:
-                sharding_pg = pg
-        for ranks in replica_groups:
-            pg = dist.new_group(ranks=ranks, backend=backend)
-            if rank in ranks:
-                replica_pg = pg
-        return sharding_pg, replica_pg
+        """``sharding_pg``: ranks that shard together; ``replica_pg``: ranks holding the same shard.  Every rank creates
+        every group (group creation is collective) and keeps the two it belongs to."""
+        me, backend = dist.get_rank(global_pg), dist.get_backend(global_pg)
+        mine: List[Optional[dist.ProcessGroup]] = []
+        for family in _rank_groups(world_size, sharding_group_size, inter_host):
+            kept = None
+            for ranks in family:
+                group = dist.new_group(ranks=ranks, backend=backend)
+                kept = group if me in ranks else kept
+            mine.append(kept)
+        return mine[0], mine[1]
 
     @staticmethod
     def _remap_sharding_plan(plan: ShardingPlan, rank: int, step: int, inter_host: bool, sharding_group_size: int) -> None:
         """Plans are written for ranks ``0..group_size-1``; map them to the global ranks of this rank's group."""
-        group_start = (rank // sharding_group_size) * sharding_group_size if inter_host else rank % step
-        for _, module_plan in plan.plan.items():
+        if inter_host:
+            first = rank - rank % sharding_group_size
+
+            def to_global(r: int) -> int:
+                return first + r
+        else:
+            first = rank % step
+
+            def to_global(r: int) -> int:
+                return first + r * step
+
+        for module_plan in plan.plan.values():
             if not isinstance(module_plan, dict):
                 continue
-            for _, ps in module_plan.items():
+            for ps in module_plan.values():
                 if ps.ranks is not None:
-                    ps.ranks = [r + group_start if inter_host else r * step + group_start for r in ps.ranks]
-                if ps.sharding_spec is not None and hasattr(ps.sharding_spec, "shards"):
-                    for i, shard in enumerate(ps.sharding_spec.shards):
-                        pl = shard.placement
-                        r = pl.rank()
-                        new_r = r + group_start if inter_host else r * step + group_start
-                        dev = pl.device()
-                        shard.placement = torch.distributed._remote_device(f"rank:{new_r}/{dev}")
+                    ps.ranks = [to_global(r) for r in ps.ranks]
+                for shard in getattr(ps.sharding_spec, "shards", None) or []:
+                    where = shard.placement
+                    shard.placement = torch.distributed._remote_device(f"rank:{to_global(where.rank())}/{where.device()}")
 
     def _group_sharded_modules(self) -> List[nn.Module]:
-        out: List[nn.Module] = []
+        return [m for _, m, sharded in _leaves(self._dmp_wrapped_module) if sharded]
 
-        def walk(m: nn.Module) -> None:
-            if isinstance(m, ShardedModule):
-                out.append(m)
-                return
-            for c in m.children():
-                walk(c)
-
-        walk(self._dmp_wrapped_module)
-        return out
+    def _replicated_tensors(self, include_optimizer_state: bool) -> Iterator[torch.Tensor]:
+        for m in self._modules_to_sync:
+            for lookup in getattr(m, "_lookups", []):
+                lookup = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
+                for emb in getattr(lookup, "emb_modules", []):
+                    tbe = emb.emb_module
+                    yield tbe.weights.detach()
+                    if include_optimizer_state:
+                        yield from (t for t in (tbe.momentum1, tbe.momentum2) if t.numel())
 
     def sync(self, include_optimizer_state: bool = True) -> None:
         """All-reduce (average) embedding weights and optimizer row/element state over the replica group."""
         assert self._replica_pg is not None, "replica_pg is not initialized!"
-        tensors: List[torch.Tensor] = []
-        for m in self._modules_to_sync:
-            for lookup in getattr(m, "_lookups", []):
-                lk = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
-                for emb in getattr(lk, "emb_modules", []):
-                    tbe = emb.emb_module
-                    tensors.append(tbe.weights.detach())
-                    if include_optimizer_state:
-                        if tbe.momentum1.numel():
-                            tensors.append(tbe.momentum1)
-                        if tbe.momentum2.numel():
-                            tensors.append(tbe.momentum2)
-        n = dist.get_world_size(self._replica_pg)
+        replicas = dist.get_world_size(self._replica_pg)
         with torch.no_grad():
-            for t in tensors:
+            for t in self._replicated_tensors(include_optimizer_state):
                 if self._custom_all_reduce is not None:
                     self._custom_all_reduce([t])
-                else:
-                    work = t.float() if t.dtype not in (torch.float32, torch.float64) else t
-                    dist.all_reduce(work, group=self._replica_pg)
-                    work.div_(n)
-                    if work is not t:
-                        t.copy_(work)
+                    continue
+                wide = t if t.dtype in (torch.float32, torch.float64) else t.float()
+                dist.all_reduce(wide, group=self._replica_pg)
+                wide.div_(replicas)
+                if wide is not t:
+                    t.copy_(wide)
 
     def set_all_reduce_hook(self, reduce_hook) -> None:
         self._custom_all_reduce = reduce_hook

@@ -42,6 +42,9 @@ from torchrec_b200.modules.embedding_configs import DataType
 from torchrec_b200.modules.embedding_modules import EmbeddingCollectionInterface
 
 
+_PERF_FIELDS = ("fwd_compute", "fwd_comms", "bwd_compute", "bwd_comms", "prefetch_compute")
+
+
 @dataclass(repr=True, eq=True)
 class Perf:
     """Cost estimate (ms) of one shard per step."""
@@ -52,18 +55,22 @@ class Perf:
     bwd_comms: float
     prefetch_compute: float = 0.0
 
+    def _tuple(self) -> Tuple[float, ...]:
+        return tuple(getattr(self, f) for f in _PERF_FIELDS)
+
     @property
     def total(self) -> float:
+        fc, fx, bc, bx, pre = self._tuple()
         if FUSED_DIST_OVERLAP:
-            return max(self.fwd_compute, self.fwd_comms) + max(self.bwd_compute, self.bwd_comms) + self.prefetch_compute
-        return self.fwd_compute + self.bwd_compute + self.fwd_comms + self.bwd_comms + self.prefetch_compute
+            # the exchange runs inside the lookup kernels: per direction the slower of the two sets the time
+            return max(fc, fx) + max(bc, bx) + pre
+        return fc + fx + bc + bx + pre
 
     def __add__(self, other: "Perf") -> "Perf":
-        return Perf(self.fwd_compute + other.fwd_compute, self.fwd_comms + other.fwd_comms, self.bwd_compute + other.bwd_compute,
-                    self.bwd_comms + other.bwd_comms, self.prefetch_compute + other.prefetch_compute)
+        return Perf(*(a + b for a, b in zip(self._tuple(), other._tuple())))
 
     def __hash__(self) -> int:
-        return hash((self.fwd_compute, self.fwd_comms, self.bwd_compute, self.bwd_comms, self.prefetch_compute))
+        return hash(self._tuple())
 
 
 @dataclass(repr=True, order=True, eq=True)
@@ -72,16 +79,16 @@ class Storage:
     ddr: int
 
     def __add__(self, other: "Storage") -> "Storage":
-        return Storage(hbm=self.hbm + other.hbm, ddr=self.ddr + other.ddr)
+        return Storage(self.hbm + other.hbm, self.ddr + other.ddr)
 
     def __sub__(self, other: "Storage") -> "Storage":
-        return Storage(hbm=self.hbm - other.hbm, ddr=self.ddr - other.ddr)
+        return Storage(self.hbm - other.hbm, self.ddr - other.ddr)
 
     def __hash__(self) -> int:
         return hash((self.hbm, self.ddr))
 
     def fits_in(self, other: "Storage") -> bool:
-        return self.hbm <= other.hbm and self.ddr <= other.ddr
+        return other.hbm >= self.hbm and other.ddr >= self.ddr
 
 
 @dataclass
@@ -97,10 +104,11 @@ class CustomTopologyData:
     supported_fields = ["ddr_cap", "hbm_cap"]
 
     def __init__(self, data: Dict[str, List[int]], world_size: int) -> None:
-        assert all(key in self.supported_fields for key in data.keys()), f"{data.keys()} not supported in CustomTopologyData"
-        assert all(len(v) == world_size for v in data.values()), f"{data.values()} must be positive"
-        self._data = data
-        self._world_size = world_size
+        unknown = [k for k in data if k not in self.supported_fields]
+        assert not unknown, f"{data.keys()} not supported in CustomTopologyData"
+        short = [k for k, v in data.items() if len(v) != world_size]
+        assert not short, f"{data.values()} must be positive"
+        self._data, self._world_size = data, world_size
 
     def get_data(self, key: str) -> List[int]:
         assert key in self.supported_fields
@@ -134,24 +142,30 @@ class GeneralizedCommsBandwidth(abc.ABC):
 
 
 class BasicCommsBandwidths(GeneralizedCommsBandwidth):
+    """Two numbers: what a collective gets inside a node and what it gets across nodes."""
+
     def __init__(self, inter_host_bw: float = CROSS_NODE_BANDWIDTH, intra_host_bw: float = INTRA_NODE_BANDWIDTH) -> None:
-        self.name = "BasicCommsBandwidths"
-        self._inter_host_bw = inter_host_bw
-        self._intra_host_bw = intra_host_bw
+        self.name = type(self).__name__
+        self._bw = {"inter": inter_host_bw, "intra": intra_host_bw}
 
     def __str__(self) -> str:
-        return self.name + f": inter_host_bw={self.inter_host_bw}, intra_host_bw={self.intra_host_bw}"
+        return f"{self.name}: inter_host_bw={self.inter_host_bw}, intra_host_bw={self.intra_host_bw}"
 
     @property
     def inter_host_bw(self) -> float:
-        return self._inter_host_bw
+        return self._bw["inter"]
 
     @property
     def intra_host_bw(self) -> float:
-        return self._intra_host_bw
+        return self._bw["intra"]
 
     def get_bw(self, local_world_size: int, world_size: int, collective_type: CollectiveType) -> float:
-        return self.intra_host_bw if world_size <= local_world_size else self.inter_host_bw
+        spans_nodes = world_size > local_world_size
+        return self._bw["inter" if spans_nodes else "intra"]
+
+
+def _read_only(attr: str):
+    return property(lambda self: getattr(self, attr))
 
 
 class Topology:
@@ -177,63 +191,37 @@ class Topology:
         generalized_comms_bandwidths: Optional[GeneralizedCommsBandwidth] = None,
     ) -> None:
         assert compute_device in ["cpu", "cuda", "mtia"], f"unsupported compute device {compute_device}"
-        self._compute_device = compute_device
-        self._world_size = world_size
-        hbm_per_device = [0] * world_size
-        if self._compute_device == "cuda":
-            hbm_per_device = [hbm_cap if hbm_cap else HBM_CAP] * world_size
-        ddr_cap_per_rank = [ddr_cap if ddr_cap else DDR_CAP] * world_size
-        if custom_topology_data:
-            if custom_topology_data.has_data("hbm_cap"):
-                hbm_per_device = custom_topology_data.get_data("hbm_cap")
-            if custom_topology_data.has_data("ddr_cap"):
-                ddr_cap_per_rank = custom_topology_data.get_data("ddr_cap")
-        self._devices: List[DeviceHardware] = [
-            DeviceHardware(rank=rank, storage=Storage(hbm=hbm_per_device[rank], ddr=ddr_cap_per_rank[rank]), perf=Perf(0, 0, 0, 0))
-            for rank in range(world_size)
-        ]
-        self._local_world_size: int = local_world_size if local_world_size else world_size
-        self._hbm_mem_bw = hbm_mem_bw
-        self._ddr_mem_bw = ddr_mem_bw
-        self._hbm_to_ddr_mem_bw = hbm_to_ddr_mem_bw
+        self._compute_device, self._world_size = compute_device, world_size
+        self._custom_topology_data = custom_topology_data
+
+        def per_rank(key: str, uniform: int) -> List[int]:
+            if custom_topology_data is not None and custom_topology_data.has_data(key):
+                return custom_topology_data.get_data(key)
+            return [uniform] * world_size
+
+        hbm = per_rank("hbm_cap", (hbm_cap or HBM_CAP) if compute_device == "cuda" else 0)
+        ddr = per_rank("ddr_cap", ddr_cap or DDR_CAP)
+        self._devices: List[DeviceHardware] = [DeviceHardware(r, Storage(hbm=hbm[r], ddr=ddr[r]), Perf(0, 0, 0, 0)) for r in range(world_size)]
+        self._local_world_size: int = local_world_size or world_size
+        self._pod_size = pod_size or self._local_world_size
+        self._hbm_mem_bw, self._ddr_mem_bw, self._hbm_to_ddr_mem_bw = hbm_mem_bw, ddr_mem_bw, hbm_to_ddr_mem_bw
         self._comms_bandwidths: GeneralizedCommsBandwidth = generalized_comms_bandwidths or BasicCommsBandwidths(inter_host_bw, intra_host_bw)
         self._bwd_compute_multiplier = bwd_compute_multiplier
-        self._custom_topology_data = custom_topology_data
         self._weighted_feature_bwd_compute_multiplier = weighted_feature_bwd_compute_multiplier
         self._uneven_sharding_perf_multiplier = uneven_sharding_perf_multiplier
-        self._pod_size = pod_size if pod_size else self._local_world_size
 
-    @property
-    def compute_device(self) -> str:
-        return self._compute_device
-
-    @property
-    def devices(self) -> List[DeviceHardware]:
-        return self._devices
-
-    @property
-    def world_size(self) -> int:
-        return self._world_size
-
-    @property
-    def local_world_size(self) -> int:
-        return self._local_world_size
-
-    @property
-    def pod_size(self) -> int:
-        return self._pod_size
-
-    @property
-    def hbm_mem_bw(self) -> float:
-        return self._hbm_mem_bw
-
-    @property
-    def ddr_mem_bw(self) -> float:
-        return self._ddr_mem_bw
-
-    @property
-    def hbm_to_ddr_mem_bw(self) -> float:
-        return self._hbm_to_ddr_mem_bw
+    compute_device = _read_only("_compute_device")
+    devices = _read_only("_devices")
+    world_size = _read_only("_world_size")
+    local_world_size = _read_only("_local_world_size")
+    pod_size = _read_only("_pod_size")
+    hbm_mem_bw = _read_only("_hbm_mem_bw")
+    ddr_mem_bw = _read_only("_ddr_mem_bw")
+    hbm_to_ddr_mem_bw = _read_only("_hbm_to_ddr_mem_bw")
+    comms_bandwidths = _read_only("_comms_bandwidths")
+    bwd_compute_multiplier = _read_only("_bwd_compute_multiplier")
+    weighted_feature_bwd_compute_multiplier = _read_only("_weighted_feature_bwd_compute_multiplier")
+    uneven_sharding_perf_multiplier = _read_only("_uneven_sharding_perf_multiplier")
 
     @property
     def intra_host_bw(self) -> float:
@@ -243,27 +231,11 @@ class Topology:
     def inter_host_bw(self) -> float:
         return self._comms_bandwidths.inter_host_bw
 
-    @property
-    def comms_bandwidths(self) -> GeneralizedCommsBandwidth:
-        return self._comms_bandwidths
-
-    @property
-    def bwd_compute_multiplier(self) -> float:
-        return self._bwd_compute_multiplier
-
-    @property
-    def weighted_feature_bwd_compute_multiplier(self) -> float:
-        return self._weighted_feature_bwd_compute_multiplier
-
-    @property
-    def uneven_sharding_perf_multiplier(self) -> float:
-        return self._uneven_sharding_perf_multiplier
-
     def __repr__(self) -> str:
-        lines = [f"world_size={self._world_size}", f"compute_device={self._compute_device}", "devices="]
-        lines += [f"\tdevice {i} {d}" for i, d in enumerate(self._devices)]
-        lines += [f"local_world_size={self._local_world_size}", str(self._comms_bandwidths)]
-        return "\n".join(lines) + "\n"
+        device_lines = [f"\tdevice {i} {d}" for i, d in enumerate(self._devices)]
+        head = [f"world_size={self._world_size}", f"compute_device={self._compute_device}", "devices="]
+        tail = [f"local_world_size={self._local_world_size}", str(self._comms_bandwidths)]
+        return "\n".join(head + device_lines + tail) + "\n"
 
     def _hash(self) -> int:
         return hash_sha256_to_int(repr(self))
@@ -278,10 +250,13 @@ class Shard:
     rank: Optional[int] = None
 
     def __hash__(self) -> int:
-        return hash((tuple(self.size), tuple(self.offset), self.storage, self.perf, self.rank))
+        return hash((*self.size, -1, *self.offset, self.storage, self.perf, self.rank))
 
     def __str__(self) -> str:
         return f"Shard size: {tuple(self.size)}, offset: {tuple(self.offset)}, storage: {self.storage}, perf: {self.perf}, rank: {self.rank}"
+
+
+_NOT_COPIED = ("_tensor", "_module")  # shared with the model: a deep copy of an option must not clone them
 
 
 class ShardingOption:
@@ -308,25 +283,12 @@ class ShardingOption:
         output_dtype: Optional[DataType] = None,
         key_value_params: Optional[KeyValueParams] = None,
     ) -> None:
-        self.name = name
-        self._tensor = tensor
-        self._module = module
-        self.input_lengths = input_lengths
-        self.batch_size = batch_size
-        self.sharding_type = sharding_type
-        self.partition_by = partition_by
-        self.compute_kernel = compute_kernel
-        self.shards = shards
-        self.cache_params = cache_params
-        self.enforce_hbm = enforce_hbm
-        self.stochastic_rounding = stochastic_rounding
-        self.bounds_check_mode = bounds_check_mode
-        self.dependency = dependency
-        self._is_pooled = is_pooled
+        given = dict(locals())
+        for private in ("tensor", "module", "is_pooled"):
+            setattr(self, "_" + private, given.pop(private))
+        given.pop("self")
+        self.__dict__.update(given)
         self.is_weighted: Optional[bool] = None
-        self.feature_names: Optional[List[str]] = feature_names
-        self.output_dtype: Optional[DataType] = output_dtype
-        self.key_value_params: Optional[KeyValueParams] = key_value_params
 
     @property
     def tensor(self) -> torch.Tensor:
@@ -337,16 +299,17 @@ class ShardingOption:
         return self._module
 
     @property
+    def path(self) -> str:
+        return self._module[0]
+
+    @property
     def fqn(self) -> str:
-        return self.module[0] + "." + self.name
+        return f"{self.path}.{self.name}"
 
     @property
     def cache_load_factor(self) -> Optional[float]:
-        return self.cache_params.load_factor if self.cache_params is not None else None
-
-    @property
-    def path(self) -> str:
-        return self.module[0]
+        cp = self.cache_params
+        return None if cp is None else cp.load_factor
 
     @property
     def num_shards(self) -> int:
@@ -358,47 +321,39 @@ class ShardingOption:
 
     @property
     def total_storage(self) -> Storage:
-        storage = Storage(hbm=0, ddr=0)
-        for shard in self.shards:
-            storage += cast(Storage, shard.storage)
-        return storage
+        return Storage(hbm=sum(cast(Storage, s.storage).hbm for s in self.shards), ddr=sum(cast(Storage, s.storage).ddr for s in self.shards))
 
     @property
     def total_perf(self) -> float:
-        return sum(cast(Perf, shard.perf).total for shard in self.shards)
+        return sum(cast(Perf, s.perf).total for s in self.shards)
 
     @property
     def is_pooled(self) -> bool:
         if self._is_pooled is None:
-            self._is_pooled = ShardingOption.module_pooled(self.module[1], self.name)
+            self._is_pooled = self.module_pooled(self._module[1], self.name)
         return self._is_pooled
 
     @staticmethod
     def module_pooled(module: nn.Module, sharding_option_name: str) -> bool:
-        if isinstance(module, EmbeddingCollectionInterface) or type(module).__name__.endswith("EmbeddingCollection") and "Bag" not in type(module).__name__:
+        """False when the table belongs to an (unpooled) embedding collection, directly or through a wrapper module."""
+        kind = type(module).__name__
+        if isinstance(module, EmbeddingCollectionInterface) or (kind.endswith("EmbeddingCollection") and "Bag" not in kind):
             return False
-        for submodule in module.modules():
-            if isinstance(submodule, EmbeddingCollectionInterface):
-                for name, _ in submodule.named_parameters():
-                    if sharding_option_name in name:
-                        return False
+        for sub in module.modules():
+            if isinstance(sub, EmbeddingCollectionInterface) and any(sharding_option_name in n for n, _ in sub.named_parameters()):
+                return False
         return True
 
     def __hash__(self) -> int:
         return hash((self.fqn, self.sharding_type, self.compute_kernel, tuple(self.shards), self.cache_params))
 
     def __deepcopy__(self, memo: Optional[Dict[int, "ShardingOption"]]) -> "ShardingOption":
-        cls = self.__class__
-        result = cls.__new__(cls)
-        for k, v in self.__dict__.items():
-            if k in ("_tensor", "_module"):
-                setattr(result, k, v)
-            else:
-                setattr(result, k, deepcopy(v, memo))
-        return result
+        clone = object.__new__(type(self))
+        clone.__dict__.update({k: (v if k in _NOT_COPIED else deepcopy(v, memo)) for k, v in self.__dict__.items()})
+        return clone
 
     def __str__(self) -> str:
-        return "\n".join(f"{k}: {v}" for k, v in self.__dict__.items() if k not in ("_tensor", "_module"))
+        return "\n".join(f"{k}: {v}" for k, v in self.__dict__.items() if k not in _NOT_COPIED)
 
 
 class PartitionByType(Enum):
@@ -527,25 +482,19 @@ class Stats(abc.ABC):
         ...
 
 
-def hash_sha256_to_int(hashable_list: Any) -> int:
-    serialized = str(hashable_list).encode("utf-8")
-    return int(hashlib.sha256(serialized).hexdigest(), 16)
-
-
 def hash_sha256_str(hashable_list: Any) -> str:
     return hashlib.sha256(str(hashable_list).encode("utf-8")).hexdigest()
+
+
+def hash_sha256_to_int(hashable_list: Any) -> int:
+    return int(hash_sha256_str(hashable_list), 16)
 
 
 def hash_planner_context_inputs(topology: Topology, batch_size: int, enumerator: Enumerator, storage_reservation: StorageReservation,
                                 constraints: Optional[Dict[str, ParameterConstraints]], hash_function=hash_sha256_to_int):
     """Fingerprint of everything that determines a plan; used to validate a loaded plan."""
     assert hasattr(enumerator, "last_stored_search_space"), "This enumerator is not compatible with hashing"
-    search_space = enumerator.last_stored_search_space  # type: ignore[attr-defined]
-    storage_constraint = storage_reservation.last_reserved_topology
-    hashable = [
-        topology, batch_size,
-        [[so.fqn, so.sharding_type, so.compute_kernel, tuple(so.shards), so.cache_params] for so in search_space],
-        storage_constraint, storage_reservation._last_reserved_topology if hasattr(storage_reservation, "_last_reserved_topology") else None,
-        sorted(constraints.items()) if constraints else None,
-    ]
-    return hash_function(hashable)
+    options = [[o.fqn, o.sharding_type, o.compute_kernel, tuple(o.shards), o.cache_params] for o in enumerator.last_stored_search_space]  # type: ignore[attr-defined]
+    reserved = storage_reservation.last_reserved_topology
+    return hash_function([topology, batch_size, options, reserved, getattr(storage_reservation, "_last_reserved_topology", None),
+                          sorted(constraints.items()) if constraints else None])

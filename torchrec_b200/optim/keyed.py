@@ -4,12 +4,16 @@ Keys are fully qualified names, so the state survives re-sharding and can be wri
 distributed checkpoint.  ``load_state_dict`` is strict and copies *in place* into existing
 ``ShardedTensor`` / ``DTensor`` / plain tensor states.  Counterpart of
 ``torchrec/optim/keyed.py:35-515``.
+
+Layout of this implementation: the recursive walks over nested state (``_export_leaf`` / ``_import_leaf``)
+are free functions driven by small per-type handlers, and the param-group bookkeeping lives in
+``_GroupIndex``; the classes only wire them to the ``torch.optim.Optimizer`` surface.
 """
 from __future__ import annotations
 
+import copy
 import json
-from copy import deepcopy
-from typing import Any, Callable, Collection, Dict, List, Mapping, Optional, OrderedDict, Set, Tuple, Union
+from typing import Any, Callable, Collection, Dict, Iterable, List, Mapping, Optional, Set, Tuple, Union
 
 import torch
 from torch import optim
@@ -21,6 +25,76 @@ except Exception:  # pragma: no cover
     DTensor = None  # type: ignore
 
 OptimizerFactory = Callable[[List[Union[torch.Tensor, ShardedTensor]]], optim.Optimizer]
+_SAVE_GROUPS = "_save_param_groups"
+
+
+# ---- nested state: export ------------------------------------------------------------------------------------------
+def _export_leaf(value: Any) -> Any:
+    """Checkpoint form of one state entry: dicts recurse, stateful objects give their own state dict."""
+    if isinstance(value, dict):
+        return {name: _export_leaf(child) for name, child in value.items()}
+    exporter = getattr(value, "state_dict", None)
+    return exporter() if callable(exporter) else value
+
+
+# ---- nested state: in-place import ---------------------------------------------------------------------------------
+def _shard_count_error(have: int, got: int, path: List[Any]) -> ValueError:
+    return ValueError(f"Different number of shards {have} vs {got} for the path of {json.dumps(path)}")
+
+
+def _copy_sharded_tensor(dst: ShardedTensor, src: Any, path: List[Any]) -> None:
+    assert isinstance(src, ShardedTensor)
+    mine, theirs = dst.local_shards(), src.local_shards()
+    if len(mine) != len(theirs):
+        raise _shard_count_error(len(mine), len(theirs), path)
+    for a, b in zip(mine, theirs):
+        if a.tensor.shape != b.tensor.shape:
+            a.tensor.resize_(b.tensor.shape)
+        a.tensor.detach().copy_(b.tensor)
+
+
+def _copy_dtensor(dst: Any, src: Any, path: List[Any]) -> None:
+    from torchrec_b200.distributed.shards_wrapper import LocalShardsWrapper
+
+    assert isinstance(src, DTensor)
+    local = dst.to_local()
+    if not isinstance(local, LocalShardsWrapper):
+        dst.detach().copy_(src)
+        return
+    mine, theirs = local.local_shards(), src.to_local().local_shards()
+    if len(mine) != len(theirs):
+        raise _shard_count_error(len(mine), len(theirs), path)
+    for a, b in zip(mine, theirs):
+        a.detach().copy_(b)
+
+
+def _import_leaf(holder: Dict[str, Any], name: str, incoming: Any, path: List[Any]) -> None:
+    """Write ``incoming`` into ``holder[name]`` without replacing tensors (their memory may belong to a kernel)."""
+    here = holder[name]
+    if isinstance(here, dict):
+        for child in here:
+            _import_leaf(here, child, incoming[child], path + [child])
+    elif callable(getattr(here, "load_state_dict", None)):
+        here.load_state_dict(incoming)
+    elif isinstance(here, ShardedTensor):
+        _copy_sharded_tensor(here, incoming, path)
+    elif DTensor is not None and isinstance(here, DTensor):
+        _copy_dtensor(here, incoming, path)
+    elif isinstance(here, torch.Tensor):
+        here.detach().copy_(incoming)
+    else:
+        holder[name] = copy.deepcopy(incoming)
+
+
+class _GroupIndex:
+    """Param groups addressed by the sorted names of their parameters."""
+
+    def __init__(self, names_of: Callable[[Mapping[str, Any]], List[str]], groups: Iterable[Mapping[str, Any]]) -> None:
+        self.by_key: Dict[str, Mapping[str, Any]] = {"/".join(names_of(g)): g for g in groups}
+
+    @staticmethod
+    def options(group: Mapping[str, Any]) -> Dict[str, Any]:
+        return {k: v for k, v in group.items() if k != "params"}
 
 
 class KeyedOptimizer(optim.Optimizer):
@@ -31,120 +105,77 @@ class KeyedOptimizer(optim.Optimizer):
     """
 
     def __init__(self, params: Mapping[str, Union[torch.Tensor, ShardedTensor]], state: Mapping[Any, Any], param_groups: Collection[Mapping[str, Any]]) -> None:
+        # torch.optim.Optimizer.__init__ is deliberately not called: state and groups are adopted, not built
         self._optimizer_step_pre_hooks: Dict[int, Callable] = {}
         self._optimizer_step_post_hooks: Dict[int, Callable] = {}
+        self.params = params
         self.state: Mapping[Any, Any] = state
         self.param_groups: Collection[Mapping[str, Any]] = param_groups
-        self.params = params
-        self.defaults: Dict[str, Any] = {"_save_param_groups": False}
-        params_set = set(params.values())
-        bad = [key for key in self.state if key not in params_set]
-        if bad:
-            raise ValueError(f"All state keys must be params. The following keys are not: {bad}.")
+        self.defaults: Dict[str, Any] = {_SAVE_GROUPS: False}
+        known = set(params.values())
+        strangers = [k for k in state if k not in known]
+        if strangers:
+            raise ValueError(f"All state keys must be params. The following keys are not: {strangers}.")
 
+    # kept as static methods because subclasses and tests reach them through the class
     @staticmethod
     def _extract_state_dict_content(input_dict: Dict[str, Any]) -> Dict[str, Any]:
-        result = {}
-        for k, v in input_dict.items():
-            if isinstance(v, dict):
-                result[k] = KeyedOptimizer._extract_state_dict_content(v)
-            elif hasattr(v, "state_dict") and callable(v.state_dict):
-                result[k] = v.state_dict()
-            else:
-                result[k] = v
-        return result
+        return _export_leaf(input_dict)
 
     @staticmethod
     def _update_param_state_dict_object(current: Dict[str, Any], to_load: Dict[str, Any], parent_keys: List[Any]) -> None:
-        from torchrec_b200.distributed.shards_wrapper import LocalShardsWrapper
+        for name in current:
+            _import_leaf(current, name, to_load[name], parent_keys + [name])
 
-        for k, v in current.items():
-            new_v = to_load[k]
-            parent_keys.append(k)
-            if isinstance(v, dict):
-                KeyedOptimizer._update_param_state_dict_object(v, new_v, parent_keys)
-            elif hasattr(v, "load_state_dict") and callable(v.load_state_dict):
-                v.load_state_dict(new_v)
-            elif isinstance(v, ShardedTensor):
-                assert isinstance(new_v, ShardedTensor)
-                if len(v.local_shards()) != len(new_v.local_shards()):
-                    raise ValueError(
-                        f"Different number of shards {len(v.local_shards())} vs {len(new_v.local_shards())} for the path of {json.dumps(parent_keys)}"
-                    )
-                for shard, new_shard in zip(v.local_shards(), new_v.local_shards()):
-                    if shard.tensor.shape != new_shard.tensor.shape:
-                        shard.tensor.resize_(new_shard.tensor.shape)
-                    shard.tensor.detach().copy_(new_shard.tensor)
-            elif DTensor is not None and isinstance(v, DTensor):
-                assert isinstance(new_v, DTensor)
-                if isinstance(v.to_local(), LocalShardsWrapper):
-                    a, b = v.to_local().local_shards(), new_v.to_local().local_shards()
-                    if len(a) != len(b):
-                        raise ValueError(f"Different number of shards {len(a)} vs {len(b)} for the path of {json.dumps(parent_keys)}")
-                    for shard, new_shard in zip(a, b):
-                        shard.detach().copy_(new_shard)
-                else:
-                    v.detach().copy_(new_v)
-            elif isinstance(v, torch.Tensor):
-                v.detach().copy_(new_v)
-            else:
-                current[k] = deepcopy(new_v)
-            parent_keys.pop()
+    def _names(self) -> Dict[Any, str]:
+        return {p: n for n, p in self.params.items()}
 
     def state_dict(self) -> Dict[str, Any]:
-        param_to_key = {param: key for key, param in self.params.items()}
-        ret_state = {param_to_key[param]: self._extract_state_dict_content(ps) for param, ps in self.state.items()}
-        ret_groups = []
-        for group in self.param_groups:
-            ret_group = {"params": sorted(param_to_key[p] for p in group["params"])}
-            for k, v in group.items():
-                if k != "params":
-                    ret_group[k] = deepcopy(v)
-            ret_groups.append(ret_group)
-        ret: Dict[str, object] = {"state": ret_state}
-        if self.defaults["_save_param_groups"]:
-            ret["param_groups"] = ret_groups
-        return ret
+        name_of = self._names()
+        out: Dict[str, Any] = {"state": {name_of[p]: _export_leaf(s) for p, s in self.state.items()}}
+        if self.defaults[_SAVE_GROUPS]:
+            out["param_groups"] = [
+                {"params": sorted(name_of[p] for p in g["params"]), **copy.deepcopy(_GroupIndex.options(g))} for g in self.param_groups
+            ]
+        return out
 
     def post_load_state_dict(self) -> None:
         pass
 
+    def _load_groups(self, saved_groups: List[Mapping[str, Any]]) -> None:
+        if len(self.param_groups) != len(saved_groups):
+            raise ValueError(f"Different param_groups count: {len(self.param_groups)} vs {len(saved_groups)}")
+        name_of = self._names()
+        mine = _GroupIndex(lambda g: sorted(name_of[p] for p in g["params"]), self.param_groups)
+        theirs = _GroupIndex(lambda g: sorted(g["params"]), saved_groups)
+        for key, group in mine.by_key.items():
+            saved = theirs.by_key.get(key)
+            if saved is None:
+                raise ValueError(f"Group {key} not found")
+            if len(group) != len(saved):
+                raise ValueError(f"Different param_group size: {len(group)} vs {len(saved)}")
+            missing = [k for k in group if k not in saved]
+            if missing:
+                raise ValueError(f"Group key {missing[0]} not found for group {key}")
+            for option in _GroupIndex.options(group):
+                group[option] = copy.deepcopy(saved[option])  # type: ignore[index]
+
     def load_state_dict(self, state_dict: Mapping[str, Any]) -> None:
         """Strict, in-place load: keys and shard layouts must match the current state."""
-        new_state = state_dict["state"]
-        state = self.state
-        params = self.params
-        if len(state) != len(new_state):
-            raise ValueError(f"Different parameter count: {len(state)} vs {len(new_state)}")
-        for param_key, param in params.items():
-            if param not in state:
+        incoming = state_dict["state"]
+        if len(self.state) != len(incoming):
+            raise ValueError(f"Different parameter count: {len(self.state)} vs {len(incoming)}")
+        for name, param in self.params.items():
+            if param not in self.state:
                 continue
-            if param_key not in new_state:
-                raise ValueError(f"Parameter {param_key} not found")
-            if len(state[param]) != len(new_state[param_key]):
-                raise ValueError(f"Different state size: {len(state[param])} vs {len(new_state[param_key])}")
-            KeyedOptimizer._update_param_state_dict_object(state[param], new_state[param_key], [param_key])
-        if self.defaults["_save_param_groups"]:
-            new_param_groups = state_dict["param_groups"]
-            param_groups = self.param_groups
-            if len(param_groups) != len(new_param_groups):
-                raise ValueError(f"Different param_groups count: {len(param_groups)} vs {len(new_param_groups)}")
-            param_to_key = {param: key for key, param in params.items()}
-            group_map = {}
-            for group in param_groups:
-                group_map["/".join(sorted(param_to_key[p] for p in group["params"]))] = group
-            new_group_map = {"/".join(sorted(g["params"])): g for g in new_param_groups}
-            for group_key, group in group_map.items():
-                if group_key not in new_group_map:
-                    raise ValueError(f"Group {group_key} not found")
-                new_group = new_group_map[group_key]
-                if len(group) != len(new_group):
-                    raise ValueError(f"Different param_group size: {len(group)} vs {len(new_group)}")
-                for k in group:
-                    if k not in new_group:
-                        raise ValueError(f"Group key {k} not found for group {group_key}")
-                    if k != "params":
-                        group[k] = deepcopy(new_group[k])
+            slot = self.state[param]
+            if name not in incoming:
+                raise ValueError(f"Parameter {name} not found")
+            if len(slot) != len(incoming[name]):
+                raise ValueError(f"Different state size: {len(slot)} vs {len(incoming[name])}")
+            self._update_param_state_dict_object(slot, incoming[name], [name])
+        if self.defaults[_SAVE_GROUPS]:
+            self._load_groups(state_dict["param_groups"])
         self.post_load_state_dict()
 
     def add_param_group(self, param_group: Any) -> None:
@@ -152,16 +183,16 @@ class KeyedOptimizer(optim.Optimizer):
 
     def init_state(self, sparse_grad_parameter_names: Optional[Set[str]] = None) -> None:
         """Run one step on zero gradients so that all state exists (needed before loading a checkpoint)."""
-        for key, param in self.params.items():
-            if param.requires_grad:
-                t = torch.zeros_like(param)
-                if sparse_grad_parameter_names is not None and key in sparse_grad_parameter_names:
-                    t = t.to_sparse()
-                param.grad = torch.autograd.Variable(t)
+        sparse = sparse_grad_parameter_names or set()
+        for name, p in self.params.items():
+            if not p.requires_grad:
+                continue
+            zero = torch.zeros_like(p)
+            p.grad = zero.to_sparse() if name in sparse else zero
         self.step(closure=None)
 
     def save_param_groups(self, save: bool) -> None:
-        self.defaults["_save_param_groups"] = save
+        self.defaults[_SAVE_GROUPS] = save
 
     def __getstate__(self) -> Dict[str, object]:
         return self.__dict__
@@ -171,21 +202,17 @@ class CombinedOptimizer(KeyedOptimizer):
     """Several keyed optimizers behind one interface; keys may be prefixed per optimizer."""
 
     def __init__(self, optims: List[Union[KeyedOptimizer, Tuple[str, KeyedOptimizer]]]) -> None:
-        self.defaults: Dict[str, Any] = {}
-        self._optims: List[Tuple[str, KeyedOptimizer]] = []
-        for key_value in optims:
-            if isinstance(key_value, KeyedOptimizer):
-                key_value = ("", key_value)
-            self._optims.append(key_value)
-        all_keys: Set[str] = set()
-        self.defaults["_save_param_groups"] = False if len(self._optims) == 0 else self._optims[0][1].defaults["_save_param_groups"]
-        for opt_key, opt in self._optims:
-            assert self.defaults["_save_param_groups"] == opt.defaults["_save_param_groups"]
-            for param_key in opt.params.keys():
-                new_param = CombinedOptimizer.prepend_opt_key(param_key, opt_key)
-                if new_param in all_keys:
-                    raise ValueError(f"Duplicate param key {new_param}")
-                all_keys.add(new_param)
+        self._optims: List[Tuple[str, KeyedOptimizer]] = [o if isinstance(o, tuple) else ("", o) for o in optims]
+        flag = self._optims[0][1].defaults[_SAVE_GROUPS] if self._optims else False
+        self.defaults: Dict[str, Any] = {_SAVE_GROUPS: flag}
+        seen: Set[str] = set()
+        for prefix, opt in self._optims:
+            assert opt.defaults[_SAVE_GROUPS] == flag
+            for name in opt.params:
+                full = self.prepend_opt_key(name, prefix)
+                if full in seen:
+                    raise ValueError(f"Duplicate param key {full}")
+                seen.add(full)
         self._optimizer_step_pre_hooks: Dict[int, Callable] = {}
         self._optimizer_step_post_hooks: Dict[int, Callable] = {}
         self._patch_step_function()
@@ -193,15 +220,18 @@ class CombinedOptimizer(KeyedOptimizer):
     def _patch_step_function(self) -> None:
         pass
 
+    def _each(self) -> Iterable[KeyedOptimizer]:
+        return (opt for _, opt in self._optims)
+
     def __repr__(self) -> str:
-        return "\n".join(f"{k}: {o!r}" for k, o in self._optims)
+        return "\n".join(f"{prefix}: {opt!r}" for prefix, opt in self._optims)
 
     def zero_grad(self, set_to_none: bool = False) -> None:
-        for _, opt in self._optims:
+        for opt in self._each():
             opt.zero_grad(set_to_none=set_to_none)
 
     def step(self, closure: Any = None) -> None:
-        for _, opt in self._optims:
+        for opt in self._each():
             opt.step(closure=closure)
 
     @property
@@ -210,56 +240,55 @@ class CombinedOptimizer(KeyedOptimizer):
 
     @staticmethod
     def prepend_opt_key(name: str, opt_key: str) -> str:
-        if not name:
-            return opt_key
-        return opt_key + ("." if opt_key else "") + name
+        return ".".join(part for part in (opt_key, name) if part)
 
     @property
     def param_groups(self) -> Collection[Mapping[str, Any]]:
-        return [pg for _, opt in self._optims for pg in opt.param_groups]
+        groups: List[Mapping[str, Any]] = []
+        for opt in self._each():
+            groups.extend(opt.param_groups)
+        return groups
 
     @property
     def params(self) -> Mapping[str, Union[torch.Tensor, ShardedTensor]]:
-        ret = {}
-        for opt_key, opt in self._optims:
-            for param_key, param in opt.params.items():
-                ret[CombinedOptimizer.prepend_opt_key(param_key, opt_key)] = param
-        return ret
+        return {self.prepend_opt_key(name, prefix): p for prefix, opt in self._optims for name, p in opt.params.items()}
 
     @property
     def state(self) -> Mapping[torch.Tensor, Any]:
-        ret = {}
-        for _, opt in self._optims:
-            for param, state in opt.state.items():
-                ret[param] = state
-        return ret
+        merged: Dict[torch.Tensor, Any] = {}
+        for opt in self._each():
+            merged.update(opt.state)
+        return merged
 
     def post_load_state_dict(self) -> None:
-        for _, opt in self._optims:
+        for opt in self._each():
             opt.post_load_state_dict()
 
     def save_param_groups(self, save: bool) -> None:
-        self.defaults["_save_param_groups"] = save
-        for _, opt in self._optims:
+        self.defaults[_SAVE_GROUPS] = save
+        for opt in self._each():
             opt.save_param_groups(save)
 
+    def _forward_optional(self, method: str, *args: Any) -> None:
+        for opt in self._each():
+            fn = getattr(opt, method, None)
+            if fn is not None:
+                fn(*args)
+
     def set_optimizer_step(self, step: int) -> None:
-        for _, opt in self._optims:
-            if hasattr(opt, "set_optimizer_step"):
-                opt.set_optimizer_step(step)
+        self._forward_optional("set_optimizer_step", step)
 
     def update_hyper_parameters(self, params_dict: Dict[str, Any]) -> None:
-        for _, opt in self._optims:
-            if hasattr(opt, "update_hyper_parameters"):
-                opt.update_hyper_parameters(params_dict)
+        self._forward_optional("update_hyper_parameters", params_dict)
 
 
 class KeyedOptimizerWrapper(KeyedOptimizer):
     """Build a torch optimizer from ``{name: param}`` with ``optim_factory`` and key its state by name."""
 
     def __init__(self, params: Mapping[str, Union[torch.Tensor, ShardedTensor]], optim_factory: OptimizerFactory) -> None:
-        self._optimizer: optim.Optimizer = optim_factory(list(params.values()))
-        super().__init__(params, self._optimizer.state, self._optimizer.param_groups)
+        inner = optim_factory([p for p in params.values()])
+        self._optimizer: optim.Optimizer = inner
+        super().__init__(params, inner.state, inner.param_groups)
 
     def zero_grad(self, set_to_none: bool = False) -> None:
         self._optimizer.zero_grad(set_to_none=set_to_none)
@@ -273,13 +302,17 @@ class OptimizerWrapper(KeyedOptimizer):
 
     def __init__(self, optimizer: KeyedOptimizer) -> None:
         self._optimizer = optimizer
-        self.params: Mapping[str, Union[torch.Tensor, ShardedTensor]] = optimizer.params
-        self.state: Mapping[Any, Any] = optimizer.state
-        self.param_groups: Collection[Mapping[str, Any]] = optimizer.param_groups
-        self.defaults: Dict[str, Any] = {"_save_param_groups": False}
+        self._adopt()
+        self.defaults: Dict[str, Any] = {_SAVE_GROUPS: False}
+
+    def _adopt(self) -> None:
+        inner = self._optimizer
+        self.params: Mapping[str, Union[torch.Tensor, ShardedTensor]] = inner.params
+        self.state: Mapping[Any, Any] = inner.state
+        self.param_groups: Collection[Mapping[str, Any]] = inner.param_groups
 
     def __repr__(self) -> str:
-        return self._optimizer.__repr__()
+        return repr(self._optimizer)
 
     def zero_grad(self, set_to_none: bool = False) -> None:
         self._optimizer.zero_grad(set_to_none=set_to_none)
@@ -298,8 +331,7 @@ class OptimizerWrapper(KeyedOptimizer):
 
     def load_state_dict(self, state_dict: Mapping[str, Any]) -> None:
         self._optimizer.load_state_dict(state_dict)
-        self.state = self._optimizer.state
-        self.param_groups = self._optimizer.param_groups
+        self._adopt()  # a wrapped optimizer may have rebuilt its containers while loading
         self.post_load_state_dict()
 
     def save_param_groups(self, save: bool) -> None:

@@ -16,45 +16,56 @@ from torch.optim.optimizer import Optimizer
 
 logger: logging.Logger = logging.getLogger(__name__)
 
+_NON_NEGATIVE = (("lr", "learning rate"), ("lr_decay", "lr_decay value"), ("weight_decay", "weight_decay value"),
+                 ("initial_accumulator_value", "initial_accumulator_value value"), ("eps", "epsilon value"))
+
+
+def _row_state(p: Tensor, fill: float) -> Tensor:
+    """One accumulator per row of a matrix (kept as a column so that it broadcasts), one per element otherwise."""
+    if p.dim() > 1:
+        return torch.full((p.shape[0], 1), fill, dtype=p.dtype, device=p.device)
+    return torch.full_like(p, fill, memory_format=torch.preserve_format)
+
+
+def _update_one(param: Tensor, grad: Tensor, acc: Tensor, steps: Tensor, lr: float, weight_decay: float, lr_decay: float, eps: float, maximize: bool) -> None:
+    if grad.is_sparse:
+        raise RuntimeError("RowWise adagrad cannot be used with sparse gradients")
+    steps += 1
+    g = grad.neg() if maximize else grad
+    if weight_decay != 0:
+        g = g + weight_decay * param
+    acc.add_(g.square().mean(dim=1, keepdim=True))
+    rate = lr / (1.0 + (float(steps) - 1.0) * lr_decay)
+    param.addcdiv_(g, acc.sqrt() + eps, value=-rate)
+
 
 class RowWiseAdagrad(Optimizer):
     def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-2, lr_decay: float = 0.0, weight_decay: float = 0.0,
                  initial_accumulator_value: float = 0.0, eps: float = 1e-10, *, maximize: bool = False, **unused) -> None:
-        if not 0.0 <= lr:
-            raise ValueError(f"Invalid learning rate: {lr}")
-        if not 0.0 <= lr_decay:
-            raise ValueError(f"Invalid lr_decay value: {lr_decay}")
-        if not 0.0 <= weight_decay:
-            raise ValueError(f"Invalid weight_decay value: {weight_decay}")
-        if not 0.0 <= initial_accumulator_value:
-            raise ValueError(f"Invalid initial_accumulator_value value: {initial_accumulator_value}")
-        if not 0.0 <= eps:
-            raise ValueError(f"Invalid epsilon value: {eps}")
-        defaults = dict(lr=lr, lr_decay=lr_decay, eps=eps, weight_decay=weight_decay, initial_accumulator_value=initial_accumulator_value, maximize=maximize)
-        super().__init__(params, defaults)
+        given = dict(lr=lr, lr_decay=lr_decay, weight_decay=weight_decay, initial_accumulator_value=initial_accumulator_value, eps=eps)
+        for key, label in _NON_NEGATIVE:
+            if given[key] < 0.0:
+                raise ValueError(f"Invalid {label}: {given[key]}")
+        super().__init__(params, dict(given, maximize=maximize))
+        for p in self._all_params():
+            fill = complex(initial_accumulator_value, initial_accumulator_value) if torch.is_complex(p) else initial_accumulator_value
+            self.state[p].update(step=torch.tensor(0.0), sum=_row_state(p, fill))
+
+    def _all_params(self) -> Iterable[Tensor]:
         for group in self.param_groups:
-            for p in group["params"]:
-                state = self.state[p]
-                state["step"] = torch.tensor(0.0)
-                init_value = complex(initial_accumulator_value, initial_accumulator_value) if torch.is_complex(p) else initial_accumulator_value
-                state["sum"] = (
-                    torch.full_like(p, init_value, memory_format=torch.preserve_format).mean(axis=1).view(-1, 1)
-                    if p.dim() > 1 else torch.full_like(p, init_value, memory_format=torch.preserve_format)
-                )
+            yield from group["params"]
 
     def __setstate__(self, state: Dict[str, Any]) -> None:
         super().__setstate__(state)
         for group in self.param_groups:
             group.setdefault("maximize", False)
-        state_values = list(self.state.values())
-        if state_values and not torch.is_tensor(state_values[0]["step"]):
-            for s in state_values:
-                s["step"] = torch.tensor(float(s["step"]))
+        for entry in self.state.values():  # checkpoints written with a python number as step counter
+            if not torch.is_tensor(entry["step"]):
+                entry["step"] = torch.tensor(float(entry["step"]))
 
     def share_memory(self) -> None:
-        for group in self.param_groups:
-            for p in group["params"]:
-                self.state[p]["sum"].share_memory_()
+        for p in self._all_params():
+            self.state[p]["sum"].share_memory_()
 
     @torch.no_grad()
     def step(self, closure: Any = None) -> Any:
@@ -63,30 +74,14 @@ class RowWiseAdagrad(Optimizer):
             with torch.enable_grad():
                 loss = closure()
         for group in self.param_groups:
-            params_with_grad, grads, state_sums, state_steps = [], [], [], []
-            for p in group["params"]:
-                if p.grad is not None:
-                    params_with_grad.append(p)
-                    grads.append(p.grad)
-                    state = self.state[p]
-                    state_sums.append(state["sum"])
-                    state_steps.append(state["step"])
-            adagrad(params_with_grad, grads, state_sums, state_steps, lr=group["lr"], weight_decay=group["weight_decay"],
-                    lr_decay=group["lr_decay"], eps=group["eps"], maximize=group["maximize"])
+            live = [p for p in group["params"] if p.grad is not None]
+            adagrad(live, [p.grad for p in live], [self.state[p]["sum"] for p in live], [self.state[p]["step"] for p in live],
+                    lr=group["lr"], weight_decay=group["weight_decay"], lr_decay=group["lr_decay"], eps=group["eps"], maximize=group["maximize"])
         return loss
 
 
 def adagrad(params: List[Tensor], grads: List[Tensor], state_sums: List[Tensor], state_steps: List[Tensor], *, lr: float,
             weight_decay: float, lr_decay: float, eps: float, maximize: bool) -> None:
-    for param, grad, state_sum, step_t in zip(params, grads, state_sums, state_steps):
-        if grad.is_sparse:
-            raise RuntimeError("RowWise adagrad cannot be used with sparse gradients")
-        step_t += 1
-        step = step_t.item()
-        grad = grad if not maximize else -grad
-        if weight_decay != 0:
-            grad = grad.add(param, alpha=weight_decay)
-        state_sum += grad.pow(2).mean(axis=1).view(-1, 1)
-        std = state_sum.sqrt().add_(eps)
-        clr = lr / (1 + (step - 1) * lr_decay)
-        param.addcdiv_(grad, std, value=-clr)
+    """Functional form over parallel lists (the signature of ``torchrec.optim.rowwise_adagrad.adagrad``)."""
+    for quad in zip(params, grads, state_sums, state_steps):
+        _update_one(*quad, lr, weight_decay, lr_decay, eps, maximize)

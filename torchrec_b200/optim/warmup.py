@@ -38,69 +38,71 @@ class WarmupStage:
 
 
 def _lr_stages(stages: List[WarmupStage]) -> List[WarmupStage]:
-    last = WarmupStage(policy=WarmupPolicy.NONE, max_iters=1 << 63, value=1.0)
-    if len(stages) == 0:
-        return [last]
-    start = 0
-    for s in stages:
-        assert s.max_iters > start, f"Max iter of the stage {s} must be greater than the previous max iter {start}"
-        start = s.max_iters
-        if s.decay_iters <= 0:
-            s.decay_iters = s.max_iters
-    return stages + [last]
+    """Validated stage list with an open-ended identity stage appended (what applies after the last boundary)."""
+    boundary = 0
+    for stage in stages:
+        assert stage.max_iters > boundary, f"Max iter of the stage {stage} must be greater than the previous max iter {boundary}"
+        boundary = stage.max_iters
+        if stage.decay_iters <= 0:
+            stage.decay_iters = stage.max_iters
+    return list(stages) + [WarmupStage(policy=WarmupPolicy.NONE, max_iters=1 << 63, value=1.0)]
+
+
+def _cosine_restart(stage: WarmupStage, it: int) -> float:
+    phase = (it % stage.sgdr_period) / stage.sgdr_period
+    return stage.value + (1.0 - stage.value) * 0.5 * (1.0 + math.cos(math.pi * phase))
+
+
+_FACTOR = {
+    WarmupPolicy.NONE: lambda s, it: 1.0,
+    WarmupPolicy.LINEAR: lambda s, it: s.value + (1.0 - s.value) * it / s.max_iters,
+    WarmupPolicy.CONSTANT: lambda s, it: s.value,
+    WarmupPolicy.POLY: lambda s, it: (1.0 - it / s.decay_iters) ** s.value,
+    WarmupPolicy.STEP: lambda s, it: s.value ** (it // s.decay_iters),
+    WarmupPolicy.INVSQRT: lambda s, it: 1.0 / math.sqrt(it),
+    WarmupPolicy.COSINE_ANNEALING_WARM_RESTARTS: _cosine_restart,
+}
 
 
 def _get_multiplier(stage: WarmupStage, iter: int) -> float:
-    m = 1.0
-    if stage.policy == WarmupPolicy.LINEAR:
-        m = stage.value + (1.0 - stage.value) * iter / stage.max_iters
-    elif stage.policy == WarmupPolicy.CONSTANT:
-        m = stage.value
-    elif stage.policy == WarmupPolicy.POLY:
-        m = math.pow(1 - iter / stage.decay_iters, stage.value)
-    elif stage.policy == WarmupPolicy.STEP:
-        m = math.pow(stage.value, iter // stage.decay_iters)
-    elif stage.policy == WarmupPolicy.INVSQRT:
-        m = 1.0 / math.sqrt(iter)
-    elif stage.policy == WarmupPolicy.COSINE_ANNEALING_WARM_RESTARTS:
-        t0 = stage.sgdr_period
-        t_cur = iter % t0
-        m = stage.value + (1.0 - stage.value) * 0.5 * (1 + math.cos(math.pi * t_cur / t0))
-    return m * stage.lr_scale
+    return _FACTOR[stage.policy](stage, iter) * stage.lr_scale
 
 
 class WarmupOptimizer(OptimizerWrapper):
     def __init__(self, optimizer: KeyedOptimizer, stages: List[WarmupStage], lr: float = 0.1, lr_param: str = "lr", param_name: str = "__warmup") -> None:
         super().__init__(optimizer)
         self._stages = _lr_stages(stages)
-        self._lr_param = lr_param
-        self._lr = lr
+        self._lr_param, self._lr = lr_param, lr
+        # the step counter is the state of a dummy parameter, so it is checkpointed with the optimizer
         self._warmup_param = torch.nn.Parameter()
         self.params[param_name] = self._warmup_param  # type: ignore[index]
-        # the step counter lives in the optimizer state so that it is checkpointed with it
-        self.state[self._warmup_param] = {"warmup": torch.tensor([0], dtype=torch.long)}  # type: ignore[index]
-        self._set_lr(0, 0)
+        self.state[self._warmup_param] = {"warmup": torch.zeros(1, dtype=torch.long)}  # type: ignore[index]
+        self._apply(0)
 
-    def _set_lr(self, iter_: int, stage_id: int) -> None:
-        lr = self._lr * _get_multiplier(self._stages[stage_id], iter_)
+    def _counter(self) -> torch.Tensor:
+        return self.state[self._warmup_param]["warmup"]
+
+    def _stage_of(self, it: int) -> WarmupStage:
+        for stage in self._stages:
+            if it < stage.max_iters:
+                return stage
+        return self._stages[-1]
+
+    def _apply(self, it: int) -> None:
+        value = self._lr * _get_multiplier(self._stage_of(it), it)
         for group in self.param_groups:
-            group[self._lr_param] = lr  # type: ignore[index]
+            group[self._lr_param] = value  # type: ignore[index]
 
     def _get_warmup_state(self) -> Tuple[int, int]:
-        iter_ = int(self.state[self._warmup_param]["warmup"][0].item())
-        stage_id = 0
-        for i, s in enumerate(self._stages):
-            if iter_ >= s.max_iters and i + 1 < len(self._stages):
-                stage_id = i + 1
-        return iter_, stage_id
+        it = int(self._counter()[0])
+        return it, self._stages.index(self._stage_of(it))
 
     def post_load_state_dict(self) -> None:
-        iter_, stage_id = self._get_warmup_state()
-        logger.info(f"Warmup Optimizer set to iteration {iter_}")
-        self._set_lr(iter_, stage_id)
+        it = int(self._counter()[0])
+        logger.info(f"Warmup Optimizer set to iteration {it}")
+        self._apply(it)
 
     def step(self, closure: Any = None) -> None:
         super().step(closure)
-        self.state[self._warmup_param]["warmup"] += 1
-        iter_, stage_id = self._get_warmup_state()
-        self._set_lr(iter_, stage_id)
+        self._counter().add_(1)
+        self._apply(int(self._counter()[0]))
