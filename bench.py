@@ -472,27 +472,9 @@ def main() -> None:
     gc.collect()
     torch.cuda.empty_cache()
 
-    baseline = None
-    if args.impl == "ours" and args.baseline_steps > 0:
-        try:
-            b = run_arm(args, "nccl_torch", device, rank, world, local_rank, host_batches, args.baseline_steps, 3, full=False)
-            baseline = {"impl": "nccl_torch", "value": b["value"], "ms_per_step": b["ms_per_step"], "steps": args.baseline_steps, "warmup": 5,
-                        "what": "same model, data and plan on library code only: NCCL collectives, cuBLAS GEMMs, embedding lookup/backward/row-wise Adagrad "
-                                "composed from torch ops, DistributedDataParallel, torch.optim.Adagrad, TrainPipelineSparseDist; timed in this process after the main arm"}
-        except Exception as e:
-            baseline = {"impl": "nccl_torch", "failed": f"{type(e).__name__}: {e}"[:300]}
-        gc.collect()
-        torch.cuda.empty_cache()
-    parity = None
-    if args.impl == "ours" and not args.no_parity:
-        if rank == 0:
-            try:
-                parity = loss_parity(device)
-            except Exception as e:
-                parity = {"failed": f"{type(e).__name__}: {e}"[:300]}
-        dist.barrier()
-
-    if rank == 0:
+    def emit(baseline, parity) -> None:
+        if rank != 0:
+            return
         r = main_res
         exchange_bytes = max(r["cols_on_rank"]) * args.global_batch * (world - 1) // max(world, 1) * 2
         res = {
@@ -522,6 +504,40 @@ def main() -> None:
         sys.stdout.flush()
         os.dup2(real_stdout, 1)
         print(json.dumps(res), flush=True)
+
+    # The comparison arm and the parity check run after the measurement.  They are extras: if one of them stalls (a library
+    # collective that never completes), a timer prints the result line without them and ends the process.
+    import threading
+
+    extras: Dict[str, Any] = {"baseline": None, "parity": None}
+
+    def give_up() -> None:
+        b = extras["baseline"] or {"impl": "nccl_torch", "failed": "did not finish within the time allowed for the comparison arm"}
+        emit(b, extras["parity"])
+        os._exit(0)
+
+    timer = threading.Timer(float(os.environ.get("TRB200_BENCH_EXTRAS_TIMEOUT_S", "240")), give_up)
+    timer.daemon = True
+    timer.start()
+    if args.impl == "ours" and args.baseline_steps > 0:
+        try:
+            b = run_arm(args, "nccl_torch", device, rank, world, local_rank, host_batches, args.baseline_steps, 3, full=False)
+            extras["baseline"] = {"impl": "nccl_torch", "value": b["value"], "ms_per_step": b["ms_per_step"], "steps": args.baseline_steps, "warmup": 5,
+                                  "what": "same model, data and plan on library code only: NCCL collectives, cuBLAS GEMMs, embedding lookup/backward/row-wise Adagrad "
+                                          "composed from torch ops, DistributedDataParallel, torch.optim.Adagrad, TrainPipelineSparseDist; timed in this process after the main arm"}
+        except Exception as e:
+            extras["baseline"] = {"impl": "nccl_torch", "failed": f"{type(e).__name__}: {e}"[:300]}
+        gc.collect()
+        torch.cuda.empty_cache()
+    if args.impl == "ours" and not args.no_parity:
+        if rank == 0:
+            try:
+                extras["parity"] = loss_parity(device)
+            except Exception as e:
+                extras["parity"] = {"failed": f"{type(e).__name__}: {e}"[:300]}
+        dist.barrier()
+    timer.cancel()
+    emit(extras["baseline"], extras["parity"])
     dist.barrier()
     dist.destroy_process_group()
 

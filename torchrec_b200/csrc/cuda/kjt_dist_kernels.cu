@@ -19,8 +19,8 @@
 //   output side  pooled_finalize turns the staging rows that the lookup kernels of all ranks stored into this rank's
 //                buffer into the module's output: copies whole-shard columns, sums the W partial rows of row-split
 //                tables in a fixed order (a deterministic reduce-scatter), applies the mean divisor and casts.
-//                grad_publish is its mirror for the backward: casts/scales the output gradient into the peer-visible
-//                buffer from which the owners' backward kernels pull rows.
+//                grad_publish is its mirror for the backward: it casts / scales the output gradient and pushes every column
+//                block to the rank(s) that own the table, so the owners' backward kernels read local memory only.
 //
 // Receive buffers have a fixed capacity (ids per rank).  A step whose ids do not fit is detected from the sizes before
 // anything is written: writers skip that destination and the destination records error 300, which the host raises.
@@ -402,27 +402,34 @@ __global__ void __launch_bounds__(256) pooled_finalize_kernel(const void* __rest
   }
 }
 
-__global__ void __launch_bounds__(256) grad_publish_kernel(const void* __restrict__ grad, int g_dtype, int64_t g_stride,
-                                                           void* __restrict__ out, int out_dtype, int64_t out_stride,
-                                                           const int32_t* __restrict__ seg, int n_seg, int B,
-                                                           const void* __restrict__ kjt_offsets, int off64,
+// Gradient hand-over, the mirror of the forward: the rank that owns the samples pushes every column block of its output
+// gradient to the rank(s) whose tables produced it, into row `rank * B + b` of the owner's local gradient slab
+// [W * B, slab_stride].  The owners' backward kernels then read local memory only.  Row-split tables have several
+// owners: the block goes to each of them (an all-gather by stores).
+enum GSegCol : int { GS_SRC = 0, GS_WIDTH = 1, GS_DEST = 2, GS_DCOL = 3, GS_MEAN_FEAT = 4, kGSegCols = 5 };
+
+__global__ void __launch_bounds__(256) grad_publish_kernel(const void* __restrict__ grad, int g_dtype, int64_t g_stride, PeerPtrs slabs,
+                                                           int out_dtype, int64_t slab_stride, const int32_t* __restrict__ gseg, int n_seg,
+                                                           int B, int rank, const void* __restrict__ kjt_offsets, int off64,
                                                            const int32_t* __restrict__ feat_pos, float scale_all) {
   const int lane = threadIdx.x & 31;
   const int64_t wid = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (wid >= int64_t(B) * n_seg) return;
   const int b = int(wid / n_seg), s = int(wid - int64_t(b) * n_seg);
-  const int32_t* d = seg + s * kSegCols;
-  const int width = d[SEG_WIDTH];
+  const int32_t* d = gseg + s * kGSegCols;
+  const int width = d[GS_WIDTH];
   float scale = scale_all;
-  if (d[SEG_MEAN_FEAT] >= 0) {
-    const int f = feat_pos[d[SEG_MEAN_FEAT]];
+  if (d[GS_MEAN_FEAT] >= 0) {
+    const int f = feat_pos[d[GS_MEAN_FEAT]];
     const int64_t len = load_off(kjt_offsets, int64_t(f) * B + b + 1, off64) - load_off(kjt_offsets, int64_t(f) * B + b, off64);
     if (len > 0) scale /= float(len);
   }
+  void* out = slabs.p[d[GS_DEST]];
+  const int64_t orow = (int64_t(rank) * B + b) * slab_stride + d[GS_DCOL];
   for (int e = lane * 4; e < width; e += 128) {
-    float4 v = load4_dyn(grad, int64_t(b) * g_stride + d[SEG_OUT] + e, g_dtype);
+    float4 v = load4_dyn(grad, int64_t(b) * g_stride + d[GS_SRC] + e, g_dtype);
     v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
-    store4_dyn(out, int64_t(b) * out_stride + d[SEG_OUT] + e, v, out_dtype);
+    store4_dyn(out, orow + e, v, out_dtype);
   }
 }
 
@@ -564,21 +571,23 @@ at::Tensor pooled_finalize(const at::Tensor& staging, int64_t st_stride, const a
   return out;
 }
 
-void grad_publish(const at::Tensor& grad, at::Tensor out, const at::Tensor& seg, const at::Tensor& kjt_offsets,
-                  const at::Tensor& feat_pos, double scale) {
-  TORCH_CHECK(grad.is_cuda() && grad.dim() == 2 && grad.stride(1) == 1 && out.dim() == 2 && out.stride(1) == 1);
-  TORCH_CHECK(grad.size(0) == out.size(0) && grad.size(1) == out.size(1));
+void grad_publish(const at::Tensor& grad, std::vector<int64_t> slab_ptrs, at::ScalarType slab_dtype, int64_t slab_stride, int64_t rank,
+                  const at::Tensor& gseg, const at::Tensor& kjt_offsets, const at::Tensor& feat_pos, double scale) {
+  TORCH_CHECK(grad.is_cuda() && grad.dim() == 2 && grad.stride(1) == 1);
   TORCH_CHECK((grad.stride(0) * grad.element_size()) % 8 == 0 && reinterpret_cast<uintptr_t>(grad.data_ptr()) % 16 == 0,
               "gradient rows must be 16-byte aligned");
+  TORCH_CHECK(gseg.is_cuda() && gseg.scalar_type() == at::kInt && gseg.dim() == 2 && gseg.size(1) == kGSegCols && gseg.is_contiguous());
   c10::cuda::CUDAGuard guard(grad.device());
   const int64_t B = grad.size(0);
-  const int n_seg = int(seg.size(0));
+  const int n_seg = int(gseg.size(0));
   if (B == 0 || n_seg == 0) return;
+  PeerPtrs slabs;
+  fill_peers(slabs, slab_ptrs, int(slab_ptrs.size()));
   const int64_t blocks = (B * n_seg * 32 + 255) / 256;
   grad_publish_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
-      grad.data_ptr(), dtype_code(grad.scalar_type()), grad.stride(0), out.data_ptr(), dtype_code(out.scalar_type()), out.stride(0),
-      seg.data_ptr<int32_t>(), n_seg, int(B), kjt_offsets.data_ptr(), kjt_offsets.scalar_type() == at::kLong ? 1 : 0,
-      feat_pos.data_ptr<int32_t>(), float(scale));
+      grad.data_ptr(), dtype_code(grad.scalar_type()), grad.stride(0), slabs, dtype_code(slab_dtype), slab_stride, gseg.data_ptr<int32_t>(),
+      n_seg, int(B), int(rank), kjt_offsets.data_ptr(), kjt_offsets.scalar_type() == at::kLong ? 1 : 0, feat_pos.data_ptr<int32_t>(),
+      float(scale));
   TRB_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -595,7 +604,9 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
   m.def(
       "pooled_finalize(Tensor staging, int st_stride, Tensor seg, int B, int out_cols, ScalarType out_dtype, Tensor kjt_offsets, "
       "Tensor feat_pos, Tensor err) -> Tensor");
-  m.def("grad_publish(Tensor grad, Tensor(a!) out, Tensor seg, Tensor kjt_offsets, Tensor feat_pos, float scale) -> ()");
+  m.def(
+      "grad_publish(Tensor grad, int[] slab_ptrs, ScalarType slab_dtype, int slab_stride, int rank, Tensor gseg, Tensor kjt_offsets, "
+      "Tensor feat_pos, float scale) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(trb200, CompositeExplicitAutograd, m) {

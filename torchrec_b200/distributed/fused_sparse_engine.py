@@ -9,9 +9,9 @@ host read, one all-to-all per KJT tensor, permute, lookup, pooled all-to-all / r
                  (whole-shard tables at their final output column, row-split tables into a per-source partial slot)
     finalize     one kernel per rank sums the partial slots in a fixed order, applies mean divisors, casts, and
                  writes a fresh ``[B_local, sum(D)]`` output in the unsharded module's column order
-    backward     ``grad_publish`` puts the output gradient into a peer-visible buffer; every owner's TBE backward
-                 pulls the rows it needs from there while it applies the fused optimizer (no gradient all-to-all,
-                 no ``[ids, D]`` tensor)
+    backward     ``grad_publish`` pushes every column block of the output gradient into the local gradient slab of the
+                 rank(s) that own the table; every owner's TBE backward then segment-reduces rows of its own slab while
+                 it applies the fused optimizer (no gradient all-to-all call, no ``[ids, D]`` tensor)
 
 All sharding types whose shards are (rows x columns) blocks of a table are covered by one mechanism: table-wise,
 column-wise, table-column-wise, row-wise, table-row-wise and grid shards are just different block layouts.  Data-
@@ -72,8 +72,9 @@ class _ModuleRange:
     weighted: bool
     j0: int
     j1: int
-    fwd_cols: List[int] = field(default_factory=list)
-    bwd_cols: List[int] = field(default_factory=list)
+    fwd_cols: List[int] = field(default_factory=list)   # staging column of every feature (forward)
+    bwd_cols: List[int] = field(default_factory=list)   # column in the module's output (= in its gradient)
+    slab_cols: List[int] = field(default_factory=list)  # column in this rank's gradient slab
 
 
 class DistHandle:
@@ -88,6 +89,8 @@ class DistHandle:
         self.feat_pos = feat_pos
         self.recv_offsets: Optional[torch.Tensor] = None
         self.plans: List[Any] = []
+        self.out: Optional[torch.Tensor] = None   # one-rank shortcut: the lookups write the output directly
+        self.grad: Optional[torch.Tensor] = None  # ... and read the output gradient directly
 
     def record_stream(self, stream: torch.Stream) -> None:
         for t in (self.offsets, self.values, self.weights, self.feat_pos):
@@ -228,11 +231,29 @@ class FusedSparseEngine:
                 segs.append([final, jb.cols, final, 1, 0, mean_slot])
             else:
                 segs.append([final, jb.cols, self.total_D + self.part_col[key], W, P, mean_slot])
+        # gradient slabs: on its owner, job g reads columns [slab_col, slab_col + cols) of row (source rank * B + b)
+        gsegs: List[List[int]] = []
+        self.slab_cols = 4
+        slab_col_of: Dict[int, int] = {}
+        for d in range(W):
+            acc = 0
+            for g in range(self.dest_job_start[d], self.dest_job_start[d + 1]):
+                jb = jobs[g]
+                slab_col_of[g] = acc
+                gsegs.append([jb.out_col + jb.col_off, jb.cols, d, acc, jb.slot if jb.mean_after else -1])
+                acc += jb.cols
+            self.slab_cols = max(self.slab_cols, acc)
+        for m in self.modules:
+            m.slab_cols = [slab_col_of[g0 + j] for j in range(m.j0, m.j1)]
+        self.has_mean_after = any(jb.mean_after for jb in jobs)
+        # one rank and nothing to fix up afterwards: lookups write the output and read the gradient directly
+        self.direct = W == 1 and not self.has_mean_after
         covered = sum(s[1] for s in segs)
         assert covered == self.total_D, f"shards cover {covered} of {self.total_D} output columns"
         dev = self.device
         i32 = dict(dtype=torch.int32, device=dev)
         self.t_seg = torch.tensor(segs, **i32).reshape(-1, 6)
+        self.t_gseg = torch.tensor(gsegs, **i32).reshape(-1, 5)
         self.t_jobs = torch.tensor([[jb.dest, jb.local, jb.slot, 0 if jb.whole else 1, max(jb.shard_index, 0)] for jb in jobs], **i32).reshape(-1, 5)
         self.t_dest_job_start = torch.tensor(self.dest_job_start, **i32)
         self.t_grp = torch.tensor(self.grp, **i32).reshape(-1, 3)
@@ -319,8 +340,9 @@ class FusedSparseEngine:
             else:
                 r.w, r.w_ptrs = None, []
             b.recv.append(r)
-        b.staging, b.staging_ptrs = self.peer.alloc_shared((b.B, self.stage_cols), self.stage_dtype)
-        b.gstage, b.gstage_ptrs = self.peer.alloc_shared((b.B, self.total_D), self.grad_dtype)
+        if not self.direct:
+            b.staging, b.staging_ptrs = self.peer.alloc_shared((b.B, self.stage_cols), self.stage_dtype)
+            b.gslab, b.gslab_ptrs = self.peer.alloc_shared((self.W * b.B, self.slab_cols), self.grad_dtype)
         if pg is not None:
             import torch.distributed as dist
 
@@ -381,18 +403,27 @@ class FusedSparseEngine:
         roff = torch.ops.trb200.kjt_dist_recv_offsets(r.len, n_jobs * Bg, self.ids_dtype == torch.int64, self.flags.ptrs, self.rank,
                                                      self.flags.epochs, self.peer.wait_cycles, self.peer.err)
         h.recv_offsets = roff
-        # every rank has finished reading the staging rows of the previous step before they are overwritten
-        self.flags.wait(SLOT_FIN)
+        if self.direct:
+            h.out = torch.empty((h.B, self.total_D), dtype=self.out_dtype, device=self.device)
+            dst_ptrs, dst_stride, dst_dtype = [h.out.data_ptr()], self.total_D, self.out_dtype
+        else:
+            # every rank has finished reading the staging rows of the previous step before they are overwritten
+            self.flags.wait(SLOT_FIN)
+            dst_ptrs, dst_stride, dst_dtype = b.staging_ptrs, self.stage_cols, self.stage_dtype
         h.plans = []
         for m in self.modules:
             off = roff[m.j0 * Bg: m.j1 * Bg + 1]
             psw = r.w if (m.weighted and h.weights is not None) else None
-            m.tbe.forward_push(r.val, off, psw, Bg, h.B, b.staging_ptrs, self.stage_cols, m.fwd_cols, self.stage_dtype)
+            m.tbe.forward_push(r.val, off, psw, Bg, h.B, dst_ptrs, dst_stride, m.bwd_cols if self.direct else m.fwd_cols, dst_dtype)
             h.plans.append(m.tbe.build_plan_ahead(r.val, off, psw, Bg, padded=True) if build_plans else None)
-        self.flags.signal(SLOT_OUT)
+        if not self.direct:
+            self.flags.signal(SLOT_OUT)
 
     def phase_finalize(self, h: DistHandle) -> torch.Tensor:
         b = self._bufs[h.B]
+        if self.direct:
+            out, h.out = h.out, None
+            return out
         self.flags.wait(SLOT_OUT)
         out = torch.ops.trb200.pooled_finalize(b.staging, self.stage_cols, self.t_seg, h.B, self.total_D, self.out_dtype, h.offsets, h.feat_pos,
                                                self.peer.err)
@@ -403,18 +434,26 @@ class FusedSparseEngine:
         b = self._bufs[h.B]
         if grad.dim() != 2 or grad.stride(1) != 1 or grad.data_ptr() % 16 != 0 or (grad.stride(0) * grad.element_size()) % 16 != 0:
             grad = grad.contiguous()
-        torch.ops.trb200.grad_publish(grad, b.gstage, self.t_seg, h.offsets, h.feat_pos, scale)
+        if self.direct:
+            h.grad = grad
+            return
+        torch.ops.trb200.grad_publish(grad, b.gslab_ptrs, self.grad_dtype, self.slab_cols, self.rank, self.t_gseg, h.offsets, h.feat_pos, scale)
         self.flags.signal(SLOT_GRAD)
 
     def phase_pull(self, h: DistHandle) -> None:
         b = self._bufs[h.B]
         r = b.recv[h.parity]
         Bg = self.W * h.B
-        self.flags.wait(SLOT_GRAD)
+        if self.direct:
+            grad = h.grad
+            h.grad = None
+        else:
+            self.flags.wait(SLOT_GRAD)
+            grad = b.gslab
         for m, plan in zip(self.modules, h.plans):
             off = h.recv_offsets[m.j0 * Bg: m.j1 * Bg + 1]
             psw = r.w if (m.weighted and h.weights is not None) else None
-            m.tbe.backward_pull(b.gstage, b.gstage_ptrs, self.total_D, r.val, off, psw, Bg, h.B, m.bwd_cols, 1.0, plan, padded=True)
+            m.tbe.backward_local(grad, r.val, off, psw, Bg, m.bwd_cols if self.direct else m.slab_cols, plan, padded=True)
         if not torch.cuda.is_current_stream_capturing():
             ev = torch.cuda.Event()
             ev.record()

@@ -487,6 +487,27 @@ class TableBatchedEmbeddingBags(nn.Module):
             self.step, o.max_gradient, grad_ptrs, B_local, grad_scale, plan.n_valid,
         )
 
+    def backward_local(self, grad: torch.Tensor, indices: torch.Tensor, offsets: torch.Tensor, psw: Optional[torch.Tensor], B: int, cols,
+                       plan: Optional[TBEPlan] = None, padded: bool = False) -> None:
+        """Backward + fused optimizer reading the pooled gradient of bag ``b`` from row ``b`` of ``grad`` (a local ``[B, stride]``
+        slab), at the per-feature columns ``cols``."""
+        assert self.fused, "the fused exchange is for tables with an in-backward optimizer"
+        _ext.require_cuda_ext("tbe_backward_apply")
+        w = self.weights.detach()
+        self.step += 1
+        if plan is None:
+            plan = self.build_plan(indices, offsets, psw, B, padded)
+        else:
+            plan.wait()
+        o = self.optimizer_args
+        eps = o.eta if o.optimizer == EmbOptimType.LARS_SGD else o.eps
+        torch.ops.trb200.tbe_backward_apply(
+            w, self.momentum1 if self.momentum1.numel() else None, self.momentum2 if self.momentum2.numel() else None, None,
+            self._meta_tensor_at(w.device, cols), plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale, grad, grad.stride(0), B,
+            self.max_D, True, _OPT_CODE[o.optimizer], o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay, self.step, o.max_gradient,
+            plan.n_valid,
+        )
+
     def _psw_grad(self, grad_out: torch.Tensor, indices: torch.Tensor, offsets: torch.Tensor, B: int) -> torch.Tensor:
         """``d loss / d per_sample_weights[i] = <grad of the bag of i, row of i>`` (learned position weights of feature
         processors); composite, one gather per feature."""
