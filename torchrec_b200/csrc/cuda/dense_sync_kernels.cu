@@ -135,11 +135,18 @@ struct DenseOptParams {
 __global__ void __launch_bounds__(256) dense_optimizer_kernel(DenseOptParams p) {
   __shared__ float tile[32][33];
   __shared__ int s_t;
+  __shared__ float s_bc[2];
   // which tensor does this tile belong to (T is small: linear search by one thread)
   if (threadIdx.x == 0 && threadIdx.y == 0) {
     int t = 0;
     while (t + 1 < p.T && p.desc[(t + 1) * kDescCols + DC_TILE0] <= int64_t(blockIdx.x)) ++t;
     s_t = t;
+    if (p.opt == DOPT_ADAM) {
+      // bias corrections in double: the fast-math single-precision power is too coarse for 1 - beta^t at small t
+      const double st = double(p.step[0]);
+      s_bc[0] = float(1.0 - pow(double(p.beta1), st));
+      s_bc[1] = float(1.0 - pow(double(p.beta2), st));
+    }
   }
   __syncthreads();
   const int64_t* d = p.desc + s_t * kDescCols;
@@ -150,9 +157,8 @@ __global__ void __launch_bounds__(256) dense_optimizer_kernel(DenseOptParams p) 
   const int ty = lt / tiles_x, tx = lt - ty * tiles_x;
   float bc1 = 1.f, bc2 = 1.f;
   if (p.opt == DOPT_ADAM) {
-    const float st = float(p.step[0]);
-    bc1 = 1.f - __powf(p.beta1, st);
-    bc2 = 1.f - __powf(p.beta2, st);
+    bc1 = s_bc[0];
+    bc2 = s_bc[1];
   }
   const int c = tx * 32 + threadIdx.x;
 #pragma unroll

@@ -324,52 +324,52 @@ class ShardedEmbeddingBagCollection(
     @classmethod
     def create_grouped_sharding_infos(cls, module, table_name_to_parameter_sharding: Dict[str, ParameterSharding], prefix: str,
                                       fused_params: Optional[Dict[str, Any]], suffix: Optional[str] = "weight") -> Dict[str, List[EmbeddingShardingInfo]]:
-        if fused_params is None:
-            fused_params = {}
-        shared_feature: Dict[str, bool] = {}
-        for cfg in module.embedding_bag_configs():
-            if not cfg.feature_names:
-                cfg.feature_names = [cfg.name]
+        """``{sharding type: [one EmbeddingShardingInfo per table]}`` in the order the tables appear in the module.  A feature
+        that feeds two tables gets the embedding name ``feature@table`` so that output columns stay distinguishable."""
+        configs = list(module.embedding_bag_configs())
+        for cfg in configs:
+            cfg.feature_names = cfg.feature_names or [cfg.name]
+        uses: Dict[str, int] = defaultdict(int)
+        for cfg in configs:
             for f in cfg.feature_names:
-                shared_feature[f] = f in shared_feature
-        out: Dict[str, List[EmbeddingShardingInfo]] = defaultdict(list)
-        parameter_by_name = dict(module.named_parameters())
-        state_dict = module.state_dict()
-        for config in module.embedding_bag_configs():
-            table_name = config.name
-            assert table_name in table_name_to_parameter_sharding, f"{table_name} not in table_name_to_parameter_sharding"
-            ps = table_name_to_parameter_sharding[table_name]
-            if ps.compute_kernel not in [k.value for k in EmbeddingComputeKernel]:
+                uses[f] += 1
+        tensors: Dict[str, Any] = dict(module.state_dict())
+        tensors.update(dict(module.named_parameters()))  # parameters win: they carry the optimizer annotations
+        valid_kernels = {k.value for k in EmbeddingComputeKernel}
+        grouped: Dict[str, List[EmbeddingShardingInfo]] = defaultdict(list)
+        for cfg in configs:
+            assert cfg.name in table_name_to_parameter_sharding, f"{cfg.name} not in table_name_to_parameter_sharding"
+            ps = table_name_to_parameter_sharding[cfg.name]
+            if ps.compute_kernel not in valid_kernels:
                 raise ValueError(f"Compute kernel not supported {ps.compute_kernel}")
-            embedding_names = [f + "@" + config.name if shared_feature[f] else f for f in config.feature_names]
-            param_name = prefix + table_name + (f".{suffix}" if suffix is not None else "")
-            assert param_name in parameter_by_name or param_name in state_dict
-            param = parameter_by_name.get(param_name, state_dict.get(param_name))
-            optimizer_params = getattr(param, "_optimizer_kwargs", [{}])
-            optimizer_classes = getattr(param, "_optimizer_classes", [None])
-            assert len(optimizer_classes) == 1 and len(optimizer_params) == 1, "Only support 1 optimizer per table"
-            optimizer_class = optimizer_classes[0]
-            optimizer_params = copy.deepcopy(optimizer_params[0])
-            if optimizer_class:
-                optimizer_params["optimizer"] = optimizer_type_to_emb_opt_type(optimizer_class)
-            per_table = merge_fused_params(fused_params, optimizer_params)
-            per_table = add_params_from_parameter_sharding(per_table, ps)
-            per_table = convert_to_fbgemm_types(per_table)
-            out[ps.sharding_type].append(
-                EmbeddingShardingInfo(
-                    embedding_config=EmbeddingTableConfig(
-                        num_embeddings=config.num_embeddings, embedding_dim=config.embedding_dim, name=config.name,
-                        data_type=config.data_type, feature_names=copy.deepcopy(config.feature_names), pooling=config.pooling,
-                        is_weighted=module.is_weighted(), has_feature_processor=False, embedding_names=embedding_names,
-                        weight_init_max=config.weight_init_max, weight_init_min=config.weight_init_min, init_fn=config.init_fn,
-                        num_embeddings_post_pruning=getattr(config, "num_embeddings_post_pruning", None),
-                        total_num_buckets=getattr(config, "total_num_buckets", None),
-                        use_virtual_table=getattr(config, "use_virtual_table", False),
-                    ),
-                    param_sharding=ps, param=param, fused_params=per_table,
-                )
+            key = prefix + cfg.name + ("" if suffix is None else f".{suffix}")
+            assert key in tensors, f"{key} is neither a parameter nor a state-dict entry of the module"
+            param = tensors[key]
+            table = EmbeddingTableConfig(
+                num_embeddings=cfg.num_embeddings, embedding_dim=cfg.embedding_dim, name=cfg.name, data_type=cfg.data_type,
+                feature_names=list(cfg.feature_names), pooling=cfg.pooling, is_weighted=module.is_weighted(), has_feature_processor=False,
+                embedding_names=[f"{f}@{cfg.name}" if uses[f] > 1 else f for f in cfg.feature_names],
+                weight_init_max=cfg.weight_init_max, weight_init_min=cfg.weight_init_min, init_fn=cfg.init_fn,
+                num_embeddings_post_pruning=getattr(cfg, "num_embeddings_post_pruning", None),
+                total_num_buckets=getattr(cfg, "total_num_buckets", None), use_virtual_table=getattr(cfg, "use_virtual_table", False),
             )
-        return out
+            grouped[ps.sharding_type].append(
+                EmbeddingShardingInfo(embedding_config=table, param_sharding=ps, param=param, fused_params=cls._table_fused_params(param, ps, fused_params or {}))
+            )
+        return grouped
+
+    @staticmethod
+    def _table_fused_params(param, ps: ParameterSharding, module_fused_params: Dict[str, Any]) -> Dict[str, Any]:
+        """Kernel options of one table: module-level options, overridden by the optimizer attached to the parameter
+        (``apply_optimizer_in_backward``), then by what the plan fixed for this table."""
+        classes = getattr(param, "_optimizer_classes", [None])
+        kwargs = getattr(param, "_optimizer_kwargs", [{}])
+        assert len(classes) == 1 and len(kwargs) == 1, "Only support 1 optimizer per table"
+        from_optimizer = copy.deepcopy(kwargs[0])
+        if classes[0]:
+            from_optimizer["optimizer"] = optimizer_type_to_emb_opt_type(classes[0])
+        merged = merge_fused_params(module_fused_params, from_optimizer)
+        return convert_to_fbgemm_types(add_params_from_parameter_sharding(merged, ps))
 
     def _pooling_type_to_rs_features(self) -> Dict[str, List[str]]:
         out: Dict[str, List[str]] = defaultdict(list)
@@ -380,89 +380,118 @@ class ShardedEmbeddingBagCollection(
         return out
 
     # ---- torch state: parameters and state dict -----------------------------------------------------
-    def _initialize_torch_state(self) -> None:
-        """Register ``embedding_bags.<table>.weight`` and build the ShardedTensor view of every table."""
-        self._model_parallel_name_to_local_shards: Dict[str, List[Any]] = OrderedDict()
-        self._model_parallel_name_to_sharded_tensor: Dict[str, Any] = OrderedDict()
-        self._name_to_table_size: Dict[str, Tuple[int, int]] = {}
-        model_parallel_name_to_compute_kernel: Dict[str, str] = {}
-        for table_name, ps in self.module_sharding_plan.items():
-            if ps.sharding_type == ShardingType.DATA_PARALLEL.value:
-                continue
-            self._model_parallel_name_to_local_shards[table_name] = []
-            model_parallel_name_to_compute_kernel[table_name] = ps.compute_kernel
-        for cfg in self._table_configs():
-            self._name_to_table_size[cfg.name] = (cfg.num_embeddings, cfg.embedding_dim)
-        setattr(self, self._TABLE_ATTR, nn.ModuleDict())
-        table_modules: nn.ModuleDict = getattr(self, self._TABLE_ATTR)
-        tables_by_name: Dict[str, List[Tuple[Any, torch.Tensor]]] = defaultdict(list)
+    def _unwrapped_lookups(self):
         for sharding_type, lookup in zip(self._sharding_types, self._lookups):
-            lk = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
-            if sharding_type == ShardingType.DATA_PARALLEL.value:
-                # data-parallel tables are ordinary parameters (views into the dense TBE buffer)
-                for emb in lk.emb_modules:
-                    w = emb.emb_module.weights
-                    offs = emb.emb_module.weights_offsets
-                    for i, t in enumerate(emb.config.embedding_tables):
-                        m = nn.Module()
-                        from torchrec_b200.distributed.batched_embedding_kernel import TableBatchedEmbeddingSlice
+            yield sharding_type, (lookup.module if isinstance(lookup, DistributedDataParallel) else lookup)
 
-                        m.register_parameter("weight", TableBatchedEmbeddingSlice(w, offs[i], offs[i + 1], t.local_rows, t.local_cols))
-                        table_modules[t.name] = m
-                continue
-            for emb in lk.emb_modules:
-                for t, w in zip(emb.config.embedding_tables, emb.split_embedding_weights()):
-                    tables_by_name[t.name].append((t, w))
+    def _initialize_torch_state(self) -> None:
+        """Register ``embedding_bags.<table>.weight`` and build the checkpoint view of every model-parallel table: a
+        ``ShardedTensor``, or (``env.output_dtensor``) a ``DTensor`` whose local tensor wraps this rank's shards."""
+        holder = nn.ModuleDict()
+        setattr(self, self._TABLE_ATTR, holder)
+        self._name_to_table_size: Dict[str, Tuple[int, int]] = {c.name: (c.num_embeddings, c.embedding_dim) for c in self._table_configs()}
+        plan = self.module_sharding_plan
+        model_parallel = [t for t, ps in plan.items() if ps.sharding_type != ShardingType.DATA_PARALLEL.value]
+        self._model_parallel_name_to_local_shards: Dict[str, List[Any]] = OrderedDict((t, []) for t in model_parallel)
+        self._model_parallel_name_to_sharded_tensor: Dict[str, Any] = OrderedDict()
+        # local shards of every table, straight views into the kernels' memory
+        for sharding_type, lookup in self._unwrapped_lookups():
+            for emb in lookup.emb_modules:
+                if sharding_type == ShardingType.DATA_PARALLEL.value:
+                    self._register_data_parallel_tables(holder, emb)
+                    continue
+                for table, weight in zip(emb.config.embedding_tables, emb.split_embedding_weights()):
+                    self._model_parallel_name_to_local_shards[table.name].append((table, weight))
         pg = self._env.sharding_pg if isinstance(self._env, ShardingEnv2D) else self._env.process_group
-        for table_name in self._model_parallel_name_to_local_shards.keys():
-            local = tables_by_name.get(table_name, [])
-            self._model_parallel_name_to_local_shards[table_name] = local
-            m = nn.Module()
-            table_modules[table_name] = m
-            # a rank may hold no shard of a table (table-wise on another rank): expose an empty parameter
-            if local:
-                if len(local) == 1:
-                    view = local[0][1]
-                else:
-                    view = torch.cat([w for _, w in local], dim=1) if all(w.shape[0] == local[0][1].shape[0] for _, w in local) else local[0][1]
-                m.register_parameter("weight", nn.Parameter(view, requires_grad=False) if len(local) > 1 else _ViewParameter(view))
-            else:
-                dev = self._device if self._device is not None else torch.device("cpu")
-                m.register_parameter("weight", nn.Parameter(torch.empty(0, device=dev), requires_grad=False))
-            if model_parallel_name_to_compute_kernel[table_name] != EmbeddingComputeKernel.DENSE.value:
-                # updated inside the kernel's backward: dense optimizers must skip it
-                m.weight._in_backward_optimizers = [EmptyFusedOptimizer()]
-            if pg is not None and local:
-                sd = get_state_dict([t for t, _ in local], [w for _, w in local], pg=pg)
-                self._model_parallel_name_to_sharded_tensor[table_name] = sd[f"{table_name}.weight"]
-            elif pg is not None:
-                # no local shard: still a participant of the ShardedTensor
-                ps = self.module_sharding_plan[table_name]
-                from torchrec_b200.distributed.types import ShardedTensorMetadata, TensorProperties
-
-                rows, cols = self._name_to_table_size[table_name]
-                meta = ShardedTensorMetadata(
-                    shards_metadata=copy.deepcopy(ps.sharding_spec.shards), size=torch.Size([rows, cols]),
-                    tensor_properties=TensorProperties(dtype=torch.float32),
-                )
-                try:
-                    self._model_parallel_name_to_sharded_tensor[table_name] = ShardedTensor._init_from_local_shards_and_global_metadata(
-                        local_shards=[], sharded_tensor_metadata=meta, process_group=pg,
-                    )
-                except Exception:
-                    self._model_parallel_name_to_sharded_tensor[table_name] = None
+        for name in model_parallel:
+            local = self._model_parallel_name_to_local_shards[name]
+            slot = nn.Module()
+            holder[name] = slot
+            slot.register_parameter("weight", self._local_parameter(local))
+            if plan[name].compute_kernel != EmbeddingComputeKernel.DENSE.value:
+                slot.weight._in_backward_optimizers = [EmptyFusedOptimizer()]  # updated inside the kernel's backward: dense optimizers skip it
+            if pg is not None:
+                self._model_parallel_name_to_sharded_tensor[name] = self._checkpoint_view(name, local, pg)
 
         def post_state_dict_hook(module, destination, prefix, _local_metadata) -> None:
-            for name, st in module._model_parallel_name_to_sharded_tensor.items():
+            for name, view in module._model_parallel_name_to_sharded_tensor.items():
                 key = f"{prefix}{module._TABLE_ATTR}.{name}.weight"
-                if st is not None:
-                    destination[key] = st
-                elif key in destination and not module._model_parallel_name_to_local_shards.get(name):
-                    destination.pop(key)
+                if view is not None:
+                    destination[key] = view
+                elif not module._model_parallel_name_to_local_shards.get(name):
+                    destination.pop(key, None)
 
         self._register_state_dict_hook(post_state_dict_hook)
         self._register_load_state_dict_pre_hook(self._pre_load_state_dict_hook, with_module=True)
         self.reset_parameters()
+
+    @staticmethod
+    def _register_data_parallel_tables(holder: nn.ModuleDict, emb) -> None:
+        """Data-parallel tables are ordinary parameters: ``[rows, cols]`` views into the dense kernel's flat buffer."""
+        from torchrec_b200.distributed.batched_embedding_kernel import TableBatchedEmbeddingSlice
+
+        flat, bounds = emb.emb_module.weights, emb.emb_module.weights_offsets
+        for i, table in enumerate(emb.config.embedding_tables):
+            slot = nn.Module()
+            slot.register_parameter("weight", TableBatchedEmbeddingSlice(flat, bounds[i], bounds[i + 1], table.local_rows, table.local_cols))
+            holder[table.name] = slot
+
+    def _local_parameter(self, local: List[Tuple[Any, torch.Tensor]]) -> nn.Parameter:
+        """What ``named_parameters`` shows for a table: the shard itself when the rank holds one, the column shards side by
+        side when it holds several of equal height, an empty parameter when it holds none."""
+        if not local:
+            dev = self._device if self._device is not None else torch.device("cpu")
+            return nn.Parameter(torch.empty(0, device=dev), requires_grad=False)
+        if len(local) == 1:
+            return _ViewParameter(local[0][1])
+        heights = {w.shape[0] for _, w in local}
+        joined = torch.cat([w for _, w in local], dim=1) if len(heights) == 1 else local[0][1]
+        return nn.Parameter(joined, requires_grad=False)
+
+    def _checkpoint_view(self, name: str, local: List[Tuple[Any, torch.Tensor]], pg):
+        rows, cols = self._name_to_table_size[name]
+        if self._output_dtensor:
+            view = self._dtensor_view(name, local, pg, rows, cols)
+            if view is not None:
+                return view
+        if local:
+            return get_state_dict([t for t, _ in local], [w for _, w in local], pg=pg)[f"{name}.weight"]
+        # a rank without a shard of the table still takes part in the ShardedTensor
+        from torchrec_b200.distributed.types import ShardedTensorMetadata, TensorProperties
+
+        meta = ShardedTensorMetadata(shards_metadata=copy.deepcopy(self.module_sharding_plan[name].sharding_spec.shards), size=torch.Size([rows, cols]),
+                                     tensor_properties=TensorProperties(dtype=torch.float32))
+        try:
+            return ShardedTensor._init_from_local_shards_and_global_metadata(local_shards=[], sharded_tensor_metadata=meta, process_group=pg)
+        except Exception:
+            return None
+
+    def _dtensor_view(self, name: str, local: List[Tuple[Any, torch.Tensor]], pg, rows: int, cols: int):
+        """``DTensor`` over a 1-D mesh of the sharding group.  Its local tensor is a ``LocalShardsWrapper`` holding this rank's
+        shards with their (row, column) offsets, which is what distributed checkpointing reads; the placement names the split
+        dimension (rows for row-wise kinds, columns for column-wise kinds, replicate for table-wise)."""
+        try:
+            from torch.distributed.device_mesh import DeviceMesh
+            from torch.distributed.tensor import DTensor, Replicate, Shard
+
+            from torchrec_b200.distributed.shards_wrapper import LocalShardsWrapper
+        except Exception:
+            return None
+        mesh = getattr(self._env, "device_mesh", None)
+        if mesh is None or mesh.ndim != 1:
+            dev_type = self._device.type if self._device is not None else "cpu"
+            mesh = DeviceMesh.from_group(pg, dev_type)
+        kind = self.module_sharding_plan[name].sharding_type
+        if kind in (ShardingType.ROW_WISE.value, ShardingType.TABLE_ROW_WISE.value, ShardingType.GRID_SHARD.value):
+            placements = (Shard(0),)
+        elif kind in (ShardingType.COLUMN_WISE.value, ShardingType.TABLE_COLUMN_WISE.value):
+            placements = (Shard(1),)
+        else:
+            placements = (Replicate(),)
+        shards = [w for _, w in local]
+        offsets = [tuple(int(x) for x in t.local_metadata.shard_offsets) for t, _ in local]
+        wrapper = LocalShardsWrapper(shards, offsets)
+        return DTensor.from_local(wrapper, mesh, placements, run_check=False, shape=torch.Size([rows, cols]), stride=(cols, 1))
 
     @staticmethod
     def _pre_load_state_dict_hook(self, state_dict, prefix, *args) -> None:
@@ -483,6 +512,16 @@ class ShardedEmbeddingBagCollection(
                             break
                     else:
                         raise RuntimeError(f"no matching shard for {name} at offsets {t.local_metadata.shard_offsets}")
+            elif type(src).__name__ == "DTensor":
+                inner = src.to_local()
+                pieces = list(zip(inner.local_shards(), inner.local_offsets())) if hasattr(inner, "local_shards") else []
+                for t, w in local:
+                    want = tuple(int(x) for x in t.local_metadata.shard_offsets)
+                    match = [piece for piece, at in pieces if tuple(int(x) for x in at) == want and tuple(piece.shape) == tuple(w.shape)]
+                    if not match:
+                        raise RuntimeError(f"no matching shard for {name} at offsets {want}")
+                    if match[0].data_ptr() != w.data_ptr():
+                        w.detach().copy_(match[0])
             elif isinstance(src, torch.Tensor):
                 rows, cols = self._name_to_table_size[name]
                 if tuple(src.shape) == (rows, cols):

@@ -79,40 +79,44 @@ class TrainPipeline(abc.ABC, Generic[In, Out]):
         pass
 
 
+def _device_streams(device: torch.device, n: int) -> List[Optional[torch.Stream]]:
+    """``n`` high-priority side streams on an accelerator, ``None`` placeholders on the CPU."""
+    if device.type in ("cuda", "mtia"):
+        mod = torch.get_device_module(device)
+        return [mod.Stream(priority=-1) if device.type == "cuda" else mod.Stream() for _ in range(n)]
+    return [None] * n
+
+
+def _stream_scope(device: torch.device):
+    return torch.get_device_module(device).stream if device.type in ("cuda", "mtia") else contextlib.nullcontext
+
+
 class TrainPipelineBase(TrainPipeline[In, Out]):
     """Two-deep pipeline: host-to-device copy of the next batch overlaps the current step."""
 
     def __init__(self, model: torch.nn.Module, optimizer: torch.optim.Optimizer, device: torch.device, custom_model_fwd: Optional[Callable[[In], Tuple[torch.Tensor, Out]]] = None) -> None:
-        self._model = model
-        self._optimizer = optimizer
-        self._device = device
-        self._memcpy_stream: Optional[torch.Stream] = torch.get_device_module(device).Stream() if device.type in ["cuda", "mtia"] else None
-        self._stream_context = torch.get_device_module(self._device).stream if self._device.type in ["cuda", "mtia"] else contextlib.nullcontext
-        self._cur_batch: Optional[In] = None
-        self._connected = False
-        self._data_iter_stopped = False
-        self._model_fwd: Callable[[In], Tuple[torch.Tensor, Out]] = custom_model_fwd if custom_model_fwd else model
+        self._model, self._optimizer, self._device = model, optimizer, device
+        (self._memcpy_stream,) = _device_streams(device, 1)
+        self._stream_context = _stream_scope(device)
+        self._model_fwd: Callable[[In], Tuple[torch.Tensor, Out]] = custom_model_fwd or model
+        self._reset_data_iter()
 
     def _reset_data_iter(self) -> None:
-        self._connected = False
-        self._data_iter_stopped = False
-        self._cur_batch = None
-
-    def _connect(self, dataloader_iter: Iterator[In]) -> None:
-        cur_batch = next(dataloader_iter)
-        self._cur_batch = cur_batch
-        with self._stream_context(self._memcpy_stream):
-            self._cur_batch = _to_device(cur_batch, self._device, non_blocking=True)
-        self._connected = True
+        self._connected, self._data_iter_stopped, self._cur_batch = False, False, None
 
     def _next_batch(self, dataloader_iter: Iterator[In]) -> Optional[In]:
         with record_function("## next_batch ##"):
-            try:
-                next_batch = next(dataloader_iter)
-            except StopIteration:
-                self._data_iter_stopped = True
-                return None
-        return next_batch
+            batch = next(dataloader_iter, None)
+        self._data_iter_stopped = batch is None
+        return batch
+
+    def _copy_batch_to_gpu(self, cur_batch: In) -> None:
+        with record_function("## copy_batch_to_gpu ##"), self._stream_context(self._memcpy_stream):
+            self._cur_batch = _to_device(cur_batch, self._device, non_blocking=True)
+
+    def _connect(self, dataloader_iter: Iterator[In]) -> None:
+        self._copy_batch_to_gpu(next(dataloader_iter))
+        self._connected = True
 
     def _wait_for_batch(self, cur_batch: In) -> None:
         with record_function("## wait_for_batch ##"):
@@ -122,32 +126,27 @@ class TrainPipelineBase(TrainPipeline[In, Out]):
         with record_function("## backward ##"):
             torch.sum(losses, dim=0).backward()
 
-    def _copy_batch_to_gpu(self, cur_batch: In) -> None:
-        with record_function("## copy_batch_to_gpu ##"):
-            with self._stream_context(self._memcpy_stream):
-                self._cur_batch = _to_device(cur_batch, self._device, non_blocking=True)
-
     def progress(self, dataloader_iter: Iterator[In]) -> Out:
         if not self._connected:
             self._connect(dataloader_iter)
         if self._data_iter_stopped:
             raise StopIteration()
-        cur_batch = cast(In, self._cur_batch)
-        if self._model.training:
+        batch = cast(In, self._cur_batch)
+        training = self._model.training
+        if training:
             with record_function("## zero_grad ##"):
                 self._optimizer.zero_grad()
-        self._wait_for_batch(cur_batch)
-        # fetch the next batch while this one is being consumed
-        next_batch = self._next_batch(dataloader_iter)
+        self._wait_for_batch(batch)
+        upcoming = self._next_batch(dataloader_iter)  # fetched now so that the loader works while the device computes
         with record_function("## forward ##"):
-            (losses, output) = self._model_fwd(cur_batch)
-        if self._model.training:
+            losses, output = self._model_fwd(batch)
+        if training:
             self._backward(losses)
-        if next_batch is not None:
-            self._copy_batch_to_gpu(next_batch)
-        else:
+        if upcoming is None:
             self._cur_batch = None
-        if self._model.training:
+        else:
+            self._copy_batch_to_gpu(upcoming)
+        if training:
             with record_function("## optimizer ##"):
                 self._optimizer.step()
         return output
@@ -155,22 +154,21 @@ class TrainPipelineBase(TrainPipeline[In, Out]):
 
 class TrainPipelinePT2(TrainPipelineBase[In, Out]):
     """Kept for API parity: this framework does not use a tracing compiler, so the model runs eagerly
-    (CUDA kernels + streams); the class behaves like ``TrainPipelineBase``."""
+    (CUDA kernels + streams); the class behaves like ``TrainPipelineBase``.  The captured-step counterpart is
+    ``TrainPipelineGraphed``."""
 
     def __init__(self, model: torch.nn.Module, optimizer: torch.optim.Optimizer, device: torch.device, compile_configs: Optional[Any] = None,
                  pre_compile_fn: Optional[Callable[[torch.nn.Module], None]] = None, post_compile_fn: Optional[Callable[[torch.nn.Module], None]] = None,
                  input_transformer: Optional[Callable[[In], In]] = None) -> None:
         super().__init__(model, optimizer, device)
         self._input_transformer = input_transformer
-        if pre_compile_fn:
-            pre_compile_fn(model)
-        if post_compile_fn:
-            post_compile_fn(model)
+        for hook in (pre_compile_fn, post_compile_fn):
+            if hook is not None:
+                hook(model)
 
     def progress(self, dataloader_iter: Iterator[In]) -> Out:
-        if self._input_transformer is not None:
-            dataloader_iter = (self._input_transformer(b) for b in dataloader_iter)
-        return super().progress(dataloader_iter)
+        transform = self._input_transformer
+        return super().progress(dataloader_iter if transform is None else map(transform, dataloader_iter))
 
 
 class TrainPipelineSparseDist(TrainPipeline[In, Out]):
@@ -183,6 +181,9 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
         device: device of this rank.
         execute_all_batches: keep stepping until the in-flight batches are drained when the data ends.
         apply_jit / enqueue_batch_after_forward / context_type / custom_model_fwd / dmp_collection_sync_interval_batches: as named.
+
+    A step is a fixed sequence of small phases (``_step_*`` methods); the derived pipelines change single phases instead of
+    re-stating the loop.
     """
 
     _model_attached: bool = True
@@ -191,90 +192,77 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
                  apply_jit: bool = False, context_type: Type[TrainPipelineContext] = TrainPipelineContext,
                  pipeline_postproc: bool = False, custom_model_fwd: Optional[Callable[[Optional[In]], Tuple[torch.Tensor, Out]]] = None,
                  dmp_collection_sync_interval_batches: Optional[int] = 1, enqueue_batch_after_forward: bool = False) -> None:
-        self._model = model
-        self._optimizer = optimizer
-        self._device = device
+        self._model, self._optimizer, self._device = model, optimizer, device
         self._execute_all_batches = execute_all_batches
         self._apply_jit = apply_jit
         self._enqueue_batch_after_forward = enqueue_batch_after_forward
         self._pipeline_postproc = pipeline_postproc
         self._dmp_collection_sync_interval_batches = dmp_collection_sync_interval_batches
-        if device.type == "cuda":
-            self._memcpy_stream: Optional[torch.Stream] = torch.cuda.Stream(priority=-1)
-            self._data_dist_stream: Optional[torch.Stream] = torch.cuda.Stream(priority=-1)
-        else:
-            self._memcpy_stream = None
-            self._data_dist_stream = None
-        self._stream_context = torch.get_device_module(self._device).stream if self._device.type in ["cuda", "mtia"] else contextlib.nullcontext
+        self._memcpy_stream, self._data_dist_stream = _device_streams(device, 2) if device.type == "cuda" else (None, None)
+        self._stream_context = _stream_scope(device)
+        self._model_fwd: Callable[[Optional[In]], Tuple[torch.Tensor, Out]] = custom_model_fwd or model
+        self._context_type = context_type
+        self._context = context_type(version=0)
+        # what pipelining changed in the model, so that detach() can undo it
         self._original_forwards: Dict[str, Callable[..., Any]] = {}
         self._pipelined_modules: Dict[str, ShardedModule] = {}
         self._pipelined_forwards: Dict[str, Any] = {}
+        self._pipelined_postprocs: Dict[str, Any] = {}
         self._call_args: Dict[str, CallArgs] = {}
         self._recorder: Optional[ArgRecorder] = None
-        self._pipelined_postprocs: Dict[str, Any] = {}
-        self._batch_i: Optional[In] = None
-        self._batch_ip1: Optional[In] = None
-        self._batch_ip2: Optional[In] = None
-        self._context = context_type(version=0)
-        self._context_type = context_type
-        self._model_fwd: Callable[[Optional[In]], Tuple[torch.Tensor, Out]] = custom_model_fwd if custom_model_fwd else model
+        self._pipelined: bool = False
+        # batches in flight, oldest first, with their contexts
         self.batches: Deque[Optional[In]] = deque()
         self.contexts: Deque[TrainPipelineContext] = deque()
+        self._batch_i = self._batch_ip1 = self._batch_ip2 = None
         self._dataloader_iter: Optional[Iterator[In]] = None
         self._dataloader_exhausted: bool = False
-        self._pipelined: bool = False
         self._next_index: int = 0
         self._state: PipelineState = PipelineState.IDLE
 
     # ---- batch queue -----------------------------------------------------------------------------------
     def _create_context(self) -> TrainPipelineContext:
-        ctx = self._context_type(index=self._next_index, version=1)
-        self._next_index += 1
-        return ctx
+        index, self._next_index = self._next_index, self._next_index + 1
+        return self._context_type(index=index, version=1)
 
     def _next_batch(self, dataloader_iter: Iterator[In]) -> Optional[In]:
-        # calling next() again on an exhausted loader can hang some loaders: remember the end
-        if dataloader_iter is not self._dataloader_iter:
-            self._dataloader_iter = dataloader_iter
-            self._dataloader_exhausted = False
+        """Next batch or None; a loader that ended once is not asked again (some loaders block on that)."""
+        if self._dataloader_iter is not dataloader_iter:
+            self._dataloader_iter, self._dataloader_exhausted = dataloader_iter, False
         if self._dataloader_exhausted:
             return None
         with record_function("## next_batch ##"):
             batch = next(dataloader_iter, None)
-            if batch is None:
-                self._dataloader_exhausted = True
+        self._dataloader_exhausted = batch is None
         return batch
 
     def copy_batch_to_gpu(self, dataloader_iter: Iterator[In]) -> Tuple[Optional[In], Optional[TrainPipelineContext]]:
         context = self._create_context()
-        with record_function(f"## copy_batch_to_gpu {context.index} ##"):
-            with self._stream_context(self._memcpy_stream):
-                batch = self._next_batch(dataloader_iter)
-                if batch is not None:
-                    batch = _to_device(batch, self._device, non_blocking=True)
-                elif not self._execute_all_batches:
+        with record_function(f"## copy_batch_to_gpu {context.index} ##"), self._stream_context(self._memcpy_stream):
+            batch = self._next_batch(dataloader_iter)
+            if batch is None:
+                if not self._execute_all_batches:
                     raise StopIteration
-                return batch, context
+                return None, context
+            return _to_device(batch, self._device, non_blocking=True), context
 
     def enqueue_batch(self, dataloader_iter: Iterator[In]) -> bool:
         batch, context = self.copy_batch_to_gpu(dataloader_iter)
-        if batch is None:
-            return False
-        self.batches.append(batch)
-        self.contexts.append(cast(TrainPipelineContext, context))
-        return True
+        if batch is not None:
+            self.batches.append(batch)
+            self.contexts.append(cast(TrainPipelineContext, context))
+        return batch is not None
 
     def dequeue_batch(self) -> None:
         self.batches.popleft()
         self.contexts.popleft()
-        if len(self.contexts) > 0:
+        if self.contexts:
             self._set_module_context(self.contexts[0])
 
     def _set_module_context(self, context: TrainPipelineContext) -> None:
-        for fwd in self._pipelined_forwards.values():
-            fwd.set_context(context)
-        for pp in self._pipelined_postprocs.values():
-            pp.set_context(context)
+        for holder in (self._pipelined_forwards, self._pipelined_postprocs):
+            for item in holder.values():
+                item.set_context(context)
 
     # ---- pipelining the model --------------------------------------------------------------------------
     def _make_forward(self, name: str, module: ShardedModule, call_args: CallArgs, context: TrainPipelineContext):
@@ -285,28 +273,38 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
         candidates = find_postproc_candidates(self._model, self._all_sharded) if self._pipeline_postproc else None
         self._recorder = ArgRecorder(self._all_sharded, candidates)
 
+    @staticmethod
+    def _defer_split_exchange(module: ShardedModule, defer: bool) -> None:
+        for m in module.modules():
+            if isinstance(m, KJTAllToAll):
+                m.defer_splits_exchange = defer
+
+    def _install_forwards(self, install: bool) -> None:
+        """Put the pipelined forwards (and post-processing wrappers) into the model, or take them out again."""
+        self._swap_postprocs(install)
+        table = self._pipelined_forwards if install else self._original_forwards
+        for name, module in self._pipelined_modules.items():
+            module.forward = table[name]  # type: ignore[assignment]
+            self._defer_split_exchange(module, install)
+        self._pipelined = install
+
     def _pipeline_model(self, batch: In, context: TrainPipelineContext) -> None:
         """After the first (unpipelined) forward: resolve where every sharded module's inputs live in the
         batch and swap the modules' ``forward`` for pipelined ones."""
-        assert self._recorder is not None
-        self._call_args = self._recorder.resolve(batch)
-        self._recorder.remove()
-        self._pipelined_postprocs = dict(self._recorder.postprocs)
+        recorder = self._recorder
+        assert recorder is not None
+        self._call_args = recorder.resolve(batch)
+        recorder.remove()
+        self._pipelined_postprocs = dict(recorder.postprocs)
         self._recorder = None
-        self._swap_postprocs(install=True)
-        for pp in self._pipelined_postprocs.values():
-            pp.set_context(context)
         for name, ca in self._call_args.items():
             module = self._all_sharded[name]
             self._pipelined_modules[name] = module
             self._original_forwards[name] = module.forward
-            fwd = self._make_forward(name, module, ca, context)
-            self._pipelined_forwards[name] = fwd
-            module.forward = fwd  # type: ignore[assignment]
-            for m in module.modules():
-                if isinstance(m, KJTAllToAll):
-                    m.defer_splits_exchange = True
-        self._pipelined = True
+            self._pipelined_forwards[name] = self._make_forward(name, module, ca, context)
+        self._install_forwards(True)
+        for pp in self._pipelined_postprocs.values():
+            pp.set_context(context)
 
     def _swap_postprocs(self, install: bool) -> None:
         """Put the pipelined post-processing wrappers into the model in place of the modules they wrap, or take them out."""
@@ -318,13 +316,7 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
     def detach(self) -> torch.nn.Module:
         """Restore the original forwards so the model can be used outside the pipeline."""
         if self._pipelined:
-            self._swap_postprocs(install=False)
-            for name, module in self._pipelined_modules.items():
-                module.forward = self._original_forwards[name]  # type: ignore[assignment]
-                for m in module.modules():
-                    if isinstance(m, KJTAllToAll):
-                        m.defer_splits_exchange = False
-            self._pipelined = False
+            self._install_forwards(False)
         self._model_attached = False
         return self._model
 
@@ -332,91 +324,96 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
         if model is not None:
             self._model = model
         self._model_attached = True
-        if self._pipelined_forwards and not self._pipelined:
-            self._swap_postprocs(install=True)
-            for name, module in self._pipelined_modules.items():
-                module.forward = self._pipelined_forwards[name]  # type: ignore[assignment]
-                for m in module.modules():
-                    if isinstance(m, KJTAllToAll):
-                        m.defer_splits_exchange = True
-            self._pipelined = True
-            if sparse_dist and self.batches:
-                # in-flight batches lost their input dists on detach: start them again
-                for batch, ctx in zip(self.batches, self.contexts):
-                    if not ctx.input_dist_tensors_requests and not ctx.input_dist_splits_requests:
-                        self.start_sparse_data_dist(batch, ctx)
-                        self.wait_sparse_data_dist(ctx)
+        if not self._pipelined_forwards or self._pipelined:
+            return
+        self._install_forwards(True)
+        if sparse_dist:
+            # batches that were in flight lost their input dists on detach: run them again
+            for batch, ctx in zip(self.batches, self.contexts):
+                if not (ctx.input_dist_tensors_requests or ctx.input_dist_splits_requests):
+                    self.start_sparse_data_dist(batch, ctx)
+                    self.wait_sparse_data_dist(ctx)
 
     def start_sparse_data_dist(self, batch: Optional[In], context: TrainPipelineContext) -> None:
         """Stage 1 of the input dist of ``batch`` on the data-dist stream."""
         if batch is None or not self._pipelined:
             return
-        with record_function(f"## start_sparse_data_dist {context.index} ##"):
-            with self._stream_context(self._data_dist_stream):
-                _wait_for_batch(batch, self._memcpy_stream)
-                _start_data_dist(self._pipelined_modules, self._call_args, batch, context)
+        with record_function(f"## start_sparse_data_dist {context.index} ##"), self._stream_context(self._data_dist_stream):
+            _wait_for_batch(batch, self._memcpy_stream)
+            _start_data_dist(self._pipelined_modules, self._call_args, batch, context)
 
     def wait_sparse_data_dist(self, context: TrainPipelineContext) -> None:
         """Finish stage 1 (host learns the split sizes) and launch stage 2."""
         if not self._pipelined:
             return
-        with record_function(f"## wait_sparse_data_dist {context.index} ##"):
-            with self._stream_context(self._data_dist_stream):
-                _wait_data_dist(context)
+        with record_function(f"## wait_sparse_data_dist {context.index} ##"), self._stream_context(self._data_dist_stream):
+            _wait_data_dist(context)
 
     def _wait_for_batch(self) -> None:
-        batch_id = self.contexts[0].index
-        with record_function(f"## wait_for_batch {batch_id} ##"):
-            _wait_for_batch(cast(In, self.batches[0]), self._data_dist_stream if self._pipelined else self._memcpy_stream)
+        producer = self._data_dist_stream if self._pipelined else self._memcpy_stream
+        with record_function(f"## wait_for_batch {self.contexts[0].index} ##"):
+            _wait_for_batch(cast(In, self.batches[0]), producer)
 
     def _backward(self, losses: torch.Tensor) -> None:
         with record_function(f"## backward {self.contexts[0].index} ##"):
             torch.sum(losses, dim=0).backward()
 
     def fill_pipeline(self, dataloader_iter: Iterator[In]) -> None:
-        if len(self.batches) >= 2:
-            return
-        if self.batches and self._execute_all_batches:
-            return  # draining
+        """Bring the queue to two batches (current + next), with the current one's input dist done."""
+        have = len(self.batches)
+        if have >= 2 or (have == 1 and self._execute_all_batches):
+            return  # full, or draining the tail
         if not self.enqueue_batch(dataloader_iter):
             return
-        if not self._pipelined and self._recorder is None and not self._pipelined_forwards:
+        if not (self._pipelined or self._recorder is not None or self._pipelined_forwards):
             self._install_recorder()
         if self._pipelined:
-            self.start_sparse_data_dist(self.batches[0], self.contexts[0])
-            self.wait_sparse_data_dist(self.contexts[0])
-            self._set_module_context(self.contexts[0])
-        if not self.enqueue_batch(dataloader_iter):
-            return
+            head = self.contexts[0]
+            self.start_sparse_data_dist(self.batches[0], head)
+            self.wait_sparse_data_dist(head)
+            self._set_module_context(head)
+        self.enqueue_batch(dataloader_iter)
 
-    def progress(self, dataloader_iter: Iterator[In]) -> Out:
+    # ---- one step, phase by phase -------------------------------------------------------------------------
+    def _step_prepare(self, dataloader_iter: Iterator[In]) -> None:
         if not self._model_attached:
             self.attach(self._model)
         self.fill_pipeline(dataloader_iter)
         if not self.batches:
             raise StopIteration
+
+    def _step_before_forward(self) -> None:
+        """Hook between queue handling and the step proper (derived pipelines start look-ahead work here)."""
+
+    def _step_open(self, dataloader_iter: Iterator[In]) -> None:
         self._state = PipelineState.IDLE
         if self._model.training:
             with record_function("## zero_grad ##"):
                 self._optimizer.zero_grad()
         self._wait_for_batch()
-        if len(self.batches) >= 2 and self._pipelined:
+        if self._pipelined and len(self.batches) >= 2:
             self.start_sparse_data_dist(self.batches[1], self.contexts[1])
         if not self._enqueue_batch_after_forward:
             self.enqueue_batch(dataloader_iter)
+
+    def _step_forward(self, dataloader_iter: Iterator[In]) -> Tuple[torch.Tensor, Out]:
         self._state = PipelineState.CALL_FWD
         with record_function(f"## forward {self.contexts[0].index} ##"):
             losses, output = self._model_fwd(self.batches[0])
         if self._enqueue_batch_after_forward:
             self.enqueue_batch(dataloader_iter)
-        if not self._pipelined and self._recorder is not None:
-            # first batch ran unpipelined; from now on input dists run ahead
-            first_ctx = self.contexts[1] if len(self.contexts) > 1 else self.contexts[0]
-            self._pipeline_model(cast(In, self.batches[0]), first_ctx)
+        if self._recorder is not None and not self._pipelined:
+            # the first batch ran unpipelined; its recorded arguments tell where later batches' inputs come from
+            self._pipeline_model(cast(In, self.batches[0]), self.contexts[min(1, len(self.contexts) - 1)])
             if len(self.batches) >= 2:
                 self.start_sparse_data_dist(self.batches[1], self.contexts[1])
+        return losses, output
+
+    def _step_after_forward(self) -> None:
         if len(self.batches) >= 2:
             self.wait_sparse_data_dist(self.contexts[1])
+
+    def _step_close(self, losses: torch.Tensor) -> None:
         if self._model.training:
             self._state = PipelineState.CALL_BWD
             self._backward(losses)
@@ -424,13 +421,20 @@ class TrainPipelineSparseDist(TrainPipeline[In, Out]):
             with record_function(f"## optimizer {self.contexts[0].index} ##"):
                 self._optimizer.step()
         self.dequeue_batch()
+
+    def progress(self, dataloader_iter: Iterator[In]) -> Out:
+        self._step_prepare(dataloader_iter)
+        self._step_before_forward()
+        self._step_open(dataloader_iter)
+        losses, output = self._step_forward(dataloader_iter)
+        self._step_after_forward()
+        self._step_close(losses)
         return output
 
     def reset(self) -> None:
         self.batches.clear()
         self.contexts.clear()
-        self._dataloader_exhausted = False
-        self._dataloader_iter = None
+        self._dataloader_iter, self._dataloader_exhausted = None, False
 
 
 class TrainPipelineFusedSparseDist(TrainPipelineSparseDist[In, Out]):
@@ -470,15 +474,9 @@ class TrainPipelineFusedSparseDist(TrainPipelineSparseDist[In, Out]):
                     mctx = context.module_contexts[name]
                     context.embedding_a2a_requests[name] = module.compute_and_output_dist(mctx, data)
 
-    def progress(self, dataloader_iter: Iterator[In]) -> Out:
-        if not self._model_attached:
-            self.attach(self._model)
-        self.fill_pipeline(dataloader_iter)
-        if not self.batches:
-            raise StopIteration
+    def _step_before_forward(self) -> None:
         if self._pipelined and self.contexts[0].input_dist_tensors_requests:
             self.start_embedding_lookup(self.batches[0], cast(EmbeddingTrainPipelineContext, self.contexts[0]))
-        return super().progress(dataloader_iter)
 
 
 class TrainPipelineSemiSync(TrainPipelineFusedSparseDist[In, Out]):
@@ -499,46 +497,20 @@ class TrainPipelineSemiSync(TrainPipelineFusedSparseDist[In, Out]):
         return EmbeddingPipelinedForward(name, call_args, module, context, self._emb_lookup_stream)
 
     def is_semi_sync(self) -> bool:
-        if len(self.batches) >= 1 and self.contexts[0].index is not None:
-            return self.contexts[0].index >= self._start_batch
-        return False
+        head = self.contexts[0].index if self.batches else None
+        return head is not None and head >= self._start_batch
 
-    def progress(self, dataloader_iter: Iterator[In]) -> Out:
-        if not self._model_attached:
-            self.attach(self._model)
-        self.fill_pipeline(dataloader_iter)
-        if not self.batches:
-            raise StopIteration
-        semi = self.is_semi_sync()
-        if self._pipelined and not semi and self.contexts[0].input_dist_tensors_requests:
-            self.start_embedding_lookup(self.batches[0], cast(EmbeddingTrainPipelineContext, self.contexts[0]))
-        self._state = PipelineState.IDLE
-        if self._model.training:
-            self._optimizer.zero_grad()
-        self._wait_for_batch()
-        if len(self.batches) >= 2 and self._pipelined:
-            self.start_sparse_data_dist(self.batches[1], self.contexts[1])
-        self.enqueue_batch(dataloader_iter)
-        self._state = PipelineState.CALL_FWD
-        with record_function(f"## forward {self.contexts[0].index} ##"):
-            losses, output = self._model_fwd(self.batches[0])
-        if not self._pipelined and self._recorder is not None:
-            first_ctx = self.contexts[1] if len(self.contexts) > 1 else self.contexts[0]
-            self._pipeline_model(cast(In, self.batches[0]), first_ctx)
-            if len(self.batches) >= 2:
-                self.start_sparse_data_dist(self.batches[1], self.contexts[1])
-        if len(self.batches) >= 2:
-            self.wait_sparse_data_dist(self.contexts[1])
-            if semi and self._pipelined:
-                # the stale lookup: launched before this batch's sparse update
-                self.start_embedding_lookup(self.batches[1], cast(EmbeddingTrainPipelineContext, self.contexts[1]))
-        if self._model.training:
-            self._state = PipelineState.CALL_BWD
-            self._backward(losses)
-            self.sync_embeddings(self._model, self._dmp_collection_sync_interval_batches, self.contexts[0])
-            self._optimizer.step()
-        self.dequeue_batch()
-        return output
+    def _step_before_forward(self) -> None:
+        # from ``start_batch`` on the lookup of a batch was already launched one step earlier (see ``_step_after_forward``)
+        self._semi = self.is_semi_sync()
+        if not self._semi:
+            super()._step_before_forward()
+
+    def _step_after_forward(self) -> None:
+        super()._step_after_forward()
+        if self._semi and self._pipelined and len(self.batches) >= 2:
+            # the stale lookup: launched before this batch's sparse update is applied
+            self.start_embedding_lookup(self.batches[1], cast(EmbeddingTrainPipelineContext, self.contexts[1]))
 
 
 class PrefetchTrainPipelineSparseDist(TrainPipelineSparseDist[In, Out]):
@@ -572,15 +544,9 @@ class PrefetchTrainPipelineSparseDist(TrainPipelineSparseDist[In, Out]):
                     context.module_input_post_prefetch[name] = data
                     context.module_contexts_post_prefetch[name] = mctx
 
-    def progress(self, dataloader_iter: Iterator[In]) -> Out:
-        if not self._model_attached:
-            self.attach(self._model)
-        self.fill_pipeline(dataloader_iter)
-        if not self.batches:
-            raise StopIteration
+    def _step_before_forward(self) -> None:
         if self._pipelined and self.contexts[0].input_dist_tensors_requests:
             self._prefetch(self.batches[0], cast(PrefetchTrainPipelineContext, self.contexts[0]))
-        return super().progress(dataloader_iter)
 
 
 class EvalPipelineSparseDist(TrainPipelineSparseDist[In, Out]):
