@@ -167,110 +167,126 @@ class EmbeddingShardingPlanner(ShardingPlanner):
         return hash_planner_context_inputs(self._topology, self._batch_size, self._enumerator, self._storage_reservation, self._constraints)
 
     def plan(self, module: nn.Module, sharders: Optional[List[ModuleSharder[nn.Module]]] = None) -> ShardingPlan:
-        if sharders is None:
-            sharders = get_default_sharders()
-        self._num_proposals = 0
-        self._num_plans = 0
-        start_time = time.perf_counter()
-        best_plan = None
-        lowest_storage = Storage(MAX_SIZE, MAX_SIZE)
-        last_planner_error: Optional[PlannerError] = None
-        last_proposal: List[ShardingOption] = []
-        best_perf_rating = MAX_SIZE
-
-        storage_constraint: Topology = self._storage_reservation.reserve(
-            topology=self._topology, batch_size=self._batch_size, module=module, sharders=sharders, constraints=self._constraints,
-        )
-        search_space = self._enumerator.enumerate(module=module, sharders=sharders)
-        if not search_space:
+        """Search: every proposer suggests complete plans; each new suggestion is placed on devices by the partitioner and
+        rated by the perf model, and the proposer hears how it went.  The best rated placement wins."""
+        sharders = sharders if sharders is not None else get_default_sharders()
+        search = _Search(self._timeout_seconds)
+        self._num_proposals = self._num_plans = 0
+        budget = self._storage_reservation.reserve(topology=self._topology, batch_size=self._batch_size, module=module, sharders=sharders,
+                                                   constraints=self._constraints)
+        options = self._enumerator.enumerate(module=module, sharders=sharders)
+        if not options:
             return ShardingPlan({})
-
-        proposal_cache: Dict[Tuple[int, ...], Tuple[bool, Optional[List[ShardingOption]], Optional[float]]] = {}
         for proposer in self._proposers:
-            proposer.load(search_space=search_space, enumerator=self._enumerator)
-
-        timed_out = False
+            proposer.load(search_space=options, enumerator=self._enumerator)
         for proposer in self._proposers:
-            proposal = proposer.propose()
-            while proposal:
-                if self._timeout_seconds is not None and time.perf_counter() - start_time > self._timeout_seconds:
-                    timed_out = True
-                    break
-                proposal_key = tuple(sorted(map(hash, proposal)))
-                if proposal_key in proposal_cache:
-                    partitionable, plan, perf_rating = proposal_cache[proposal_key]
-                    proposer.feedback(partitionable=partitionable, plan=plan, perf_rating=perf_rating, storage_constraint=storage_constraint)
-                    proposal = proposer.propose()
-                    continue
-                self._num_proposals += 1
-                try:
-                    plan = self._partitioner.partition(proposal=proposal, storage_constraint=storage_constraint)
-                    self._num_plans += 1
-                    perf_rating = self._perf_model.rate(plan=plan)
-                    if perf_rating < best_perf_rating:
-                        best_perf_rating = perf_rating
-                        best_plan = copy.deepcopy(plan)
-                    proposal_cache[proposal_key] = (True, plan, perf_rating)
-                    proposer.feedback(partitionable=True, plan=plan, perf_rating=perf_rating, storage_constraint=storage_constraint)
-                except PlannerError as planner_error:
-                    last_planner_error = planner_error
-                    current_storage = cast(Storage, reduce(lambda x, y: x + y, [shard.storage for option in proposal for shard in option.shards]))
-                    if current_storage < lowest_storage:
-                        lowest_storage = current_storage
-                    proposal_cache[proposal_key] = (False, proposal, None)
-                    proposer.feedback(partitionable=False, plan=proposal, storage_constraint=storage_constraint)
-                last_proposal = copy.deepcopy(proposal)
-                reset_shard_rank(proposal)
+            while not search.out_of_time():
                 proposal = proposer.propose()
-            if timed_out:
+                if not proposal:
+                    break
+                self._try_proposal(search, proposer, proposal, budget)
+            if search.out_of_time():
                 break
+        if search.best_plan is None:
+            raise self._no_plan_error(search, budget)
+        plan = search.best_plan
+        for callback in self._callbacks:
+            plan = callback(plan)
+        self._best_plan = plan
+        result = to_sharding_plan(plan, self._topology)
+        elapsed = time.perf_counter() - search.started
+        for sink in self._stats:
+            sink.log(sharding_plan=result, topology=self._topology, batch_size=self._batch_size, storage_reservation=self._storage_reservation,
+                     num_proposals=self._num_proposals, num_plans=self._num_plans, run_time=elapsed, best_plan=plan,
+                     constraints=self._constraints, sharders=sharders, enumerator=self._enumerator, debug=self._debug)
+        return result
 
-        if best_plan:
-            for callback in self._callbacks:
-                best_plan = callback(best_plan)
-            self._best_plan = best_plan
-            sharding_plan = to_sharding_plan(best_plan, self._topology)
-            end_time = time.perf_counter()
-            for stats in self._stats:
-                stats.log(
-                    sharding_plan=sharding_plan, topology=self._topology, batch_size=self._batch_size,
-                    storage_reservation=self._storage_reservation, num_proposals=self._num_proposals, num_plans=self._num_plans,
-                    run_time=end_time - start_time, best_plan=best_plan, constraints=self._constraints, sharders=sharders,
-                    enumerator=self._enumerator, debug=self._debug,
-                )
-            return sharding_plan
+    def _try_proposal(self, search: "_Search", proposer: Proposer, proposal: List[ShardingOption], budget: Topology) -> None:
+        key = tuple(sorted(hash(o) for o in proposal))
+        known = search.seen.get(key)
+        if known is not None:  # another proposer already suggested exactly this: replay the verdict
+            ok, placed, rating = known
+            proposer.feedback(partitionable=ok, plan=placed, perf_rating=rating, storage_constraint=budget)
+            return
+        self._num_proposals += 1
+        try:
+            placed = self._partitioner.partition(proposal=proposal, storage_constraint=budget)
+        except PlannerError as err:
+            search.note_failure(err, proposal)
+            search.seen[key] = (False, proposal, None)
+            proposer.feedback(partitionable=False, plan=proposal, storage_constraint=budget)
+        else:
+            self._num_plans += 1
+            rating = self._perf_model.rate(plan=placed)
+            search.note_success(placed, rating)
+            search.seen[key] = (True, placed, rating)
+            proposer.feedback(partitionable=True, plan=placed, perf_rating=rating, storage_constraint=budget)
+        search.last_proposal = copy.deepcopy(proposal)
+        reset_shard_rank(proposal)  # the option objects are shared between proposals: forget this placement
 
-        global_storage_capacity = reduce(lambda x, y: x + y, [device.storage for device in self._topology.devices])
-        global_storage_constraints = reduce(lambda x, y: x + y, [device.storage for device in storage_constraint.devices])
-        storage_reservation_solution = (
-            f"\n\t  Storage reservation percentage: {self._storage_reservation._percentage}, "  # type: ignore[attr-defined]
-            f"\n\t  Per rank reservation for dense storage: {storage_repr_in_gb(self._storage_reservation._dense_storage)}, "  # type: ignore[attr-defined]
-            f"\n\t  Per rank reservation for kjt storage: {storage_repr_in_gb(self._storage_reservation._kjt_storage)}, "  # type: ignore[attr-defined]
-            if isinstance(self._storage_reservation, HeuristicalStorageReservation) else "\n"
-        )
-        no_plan_solution = (
-            f"Planner evaluated {self._num_proposals} proposals."
-            "\nPossible solutions:"
-            f"\n  1) Increase the number of devices ({self._topology.world_size})"
-            f"\n  2) Reduce the model size ("
-            f"\n\t  Global storage: {round(bytes_to_gb(global_storage_capacity.hbm), 3)} GB, "
-            f"\n\t  Per rank hardware memory: {storage_repr_in_gb(self._topology.devices[0].storage)}, "
-            f"\n\t  Available for model parallel: {round(bytes_to_gb(global_storage_constraints.hbm), 3)} GB, "
-            f"\n\t  Requirement for model parallel: {round(bytes_to_gb(lowest_storage.hbm), 3)} GB)"
-            f"\n  3) Reduce local batch size ({self._batch_size})"
-            "\n  4) Remove planner constraints that might be reducing search space or available storage\n"
-        )
-        last_planner_error_info = f"Last planner error: \n\t{last_planner_error}\n"
-        sharding_plan = to_sharding_plan(last_proposal, self._topology) if last_proposal and all(s.rank is not None for so in last_proposal for s in so.shards) else None
-        if not lowest_storage.fits_in(global_storage_constraints):
-            raise PlannerError(
-                error_type=PlannerErrorType.INSUFFICIENT_STORAGE,
-                message="Unable to find a plan for this model because of insufficient storage. \n" + no_plan_solution + storage_reservation_solution + last_planner_error_info,
-            )
-        raise PlannerError(
-            error_type=PlannerErrorType.STRICT_CONSTRAINTS,
-            message="Unable to find a plan for this model because of the strict constraints. \n" + no_plan_solution + last_planner_error_info,
-        )
+    def _no_plan_error(self, search: "_Search", budget: Topology) -> PlannerError:
+        def total(devices) -> Storage:
+            acc = Storage(0, 0)
+            for d in devices:
+                acc = acc + d.storage
+            return acc
+
+        hardware, available, needed = total(self._topology.devices), total(budget.devices), search.smallest_failure
+        reservation = self._storage_reservation
+        advice = [
+            f"Planner evaluated {self._num_proposals} proposals.",
+            "Possible solutions:",
+            f"  1) Increase the number of devices ({self._topology.world_size})",
+            "  2) Reduce the model size (",
+            f"\t  Global storage: {round(bytes_to_gb(hardware.hbm), 3)} GB, ",
+            f"\t  Per rank hardware memory: {storage_repr_in_gb(self._topology.devices[0].storage)}, ",
+            f"\t  Available for model parallel: {round(bytes_to_gb(available.hbm), 3)} GB, ",
+            f"\t  Requirement for model parallel: {round(bytes_to_gb(needed.hbm), 3)} GB)",
+            f"  3) Reduce local batch size ({self._batch_size})",
+            "  4) Remove planner constraints that might be reducing search space or available storage",
+        ]
+        tail = f"Last planner error: \n\t{search.last_error}\n"
+        if not needed.fits_in(available):
+            if isinstance(reservation, HeuristicalStorageReservation):
+                advice += [
+                    f"\t  Storage reservation percentage: {reservation._percentage}, ",
+                    f"\t  Per rank reservation for dense storage: {storage_repr_in_gb(reservation._dense_storage)}, ",
+                    f"\t  Per rank reservation for kjt storage: {storage_repr_in_gb(reservation._kjt_storage)}, ",
+                ]
+            return PlannerError(error_type=PlannerErrorType.INSUFFICIENT_STORAGE,
+                                message="Unable to find a plan for this model because of insufficient storage. \n" + "\n".join(advice) + "\n" + tail)
+        return PlannerError(error_type=PlannerErrorType.STRICT_CONSTRAINTS,
+                            message="Unable to find a plan for this model because of the strict constraints. \n" + "\n".join(advice) + "\n" + tail)
+
+
+class _Search:
+    """Book-keeping of one ``plan`` call: verdicts by proposal, the best placement so far, what failed and why."""
+
+    def __init__(self, timeout_seconds: Optional[int]) -> None:
+        self.started = time.perf_counter()
+        self.timeout = timeout_seconds
+        self.seen: Dict[Tuple[int, ...], Tuple[bool, Optional[List[ShardingOption]], Optional[float]]] = {}
+        self.best_plan: Optional[List[ShardingOption]] = None
+        self.best_rating: float = MAX_SIZE
+        self.smallest_failure = Storage(MAX_SIZE, MAX_SIZE)
+        self.last_error: Optional[PlannerError] = None
+        self.last_proposal: List[ShardingOption] = []
+
+    def out_of_time(self) -> bool:
+        return self.timeout is not None and time.perf_counter() - self.started > self.timeout
+
+    def note_success(self, placed: List[ShardingOption], rating: float) -> None:
+        if rating < self.best_rating:
+            self.best_rating, self.best_plan = rating, copy.deepcopy(placed)
+
+    def note_failure(self, err: PlannerError, proposal: List[ShardingOption]) -> None:
+        self.last_error = err
+        need = Storage(0, 0)
+        for option in proposal:
+            for shard in option.shards:
+                need = need + cast(Storage, shard.storage)
+        if need < self.smallest_failure:
+            self.smallest_failure = need
 
 
 class HeteroEmbeddingShardingPlanner(ShardingPlanner):

@@ -46,31 +46,27 @@ def filter_state_dict(state_dict: "OrderedDict[str, torch.Tensor]", name: str) -
 
 
 def add_prefix_to_state_dict(state_dict: Dict[str, Any], prefix: str) -> None:
-    keys = sorted(state_dict.keys())
-    for key in keys:
-        state_dict[prefix + key] = state_dict.pop(key)
-    if "_metadata" in state_dict:
-        metadata = state_dict["_metadata"]
-        for key in list(metadata.keys()):
-            if len(key) == 0:
-                continue
-            metadata[prefix + key] = metadata.pop(key)
+    """In place: every key (and every non-empty key of the ``_metadata`` entry) gets ``prefix`` in front."""
+    renamed = [(key, prefix + key) for key in sorted(state_dict)]
+    for old, new in renamed:
+        state_dict[new] = state_dict.pop(old)
+    meta = state_dict.get("_metadata")
+    if meta is not None:
+        for old in [k for k in meta if k]:
+            meta[prefix + old] = meta.pop(old)
 
 
 def _get_unsharded_module_names_helper(model: nn.Module, path: str, unsharded_module_names: Set[str]) -> bool:
-    sharded_children = set()
-    for name, child in model.named_children():
-        curr_path = path + name
-        if isinstance(child, ShardedModule):
-            sharded_children.add(name)
-        else:
-            if _get_unsharded_module_names_helper(child, curr_path + ".", unsharded_module_names):
-                sharded_children.add(name)
-    if len(sharded_children) > 0:
-        for name, _ in model.named_children():
-            if name not in sharded_children:
-                unsharded_module_names.add(path + name)
-    return len(sharded_children) > 0
+    """Returns whether ``model`` contains a sharded module.  When it does, its children that do not are reported (their own
+    descendants need no separate entry); when it does not, the caller reports ``model`` itself."""
+    holds_shards = {
+        name: isinstance(child, ShardedModule) or _get_unsharded_module_names_helper(child, f"{path}{name}.", unsharded_module_names)
+        for name, child in model.named_children()
+    }
+    if not any(holds_shards.values()):
+        return False
+    unsharded_module_names.update(path + name for name, has in holds_shards.items() if not has)
+    return True
 
 
 def get_unsharded_module_names(model: nn.Module) -> List[str]:
@@ -82,54 +78,46 @@ def get_unsharded_module_names(model: nn.Module) -> List[str]:
 
 class sharded_model_copy:
     """Context manager: ``copy.deepcopy`` of a sharded model keeps sharded tensors on ``device``
-    (e.g. ``with sharded_model_copy("cpu"): m_cpu = copy.deepcopy(m)``)."""
+    (e.g. ``with sharded_model_copy("cpu"): m_cpu = copy.deepcopy(m)``).  It works by swapping the ``__deepcopy__`` of tensors
+    and parameters for the duration of the block."""
 
     def __init__(self, device: Optional[Union[str, int, torch.device]]) -> None:
         self.device = device
+        self._saved: Optional[tuple] = None
+
+    def _clone(self, tensor: torch.Tensor, memo) -> torch.Tensor:
+        detached = tensor.detach()
+        return detached.clone() if tensor.device == self.device else detached.to(self.device)
 
     def __enter__(self) -> None:
-        self.t_copy_save_ = torch.Tensor.__deepcopy__
-        self.p_copy_save_ = torch.nn.Parameter.__deepcopy__
-        device = self.device
-
-        def _tensor_copy(tensor, memo):
-            if tensor.device != device:
-                return tensor.detach().to(device)
-            return tensor.detach().clone()
-
-        def _param_copy(param, memo):
-            return torch.nn.Parameter(_tensor_copy(param, memo), requires_grad=param.requires_grad)
-
-        torch.Tensor.__deepcopy__ = _tensor_copy
-        torch.nn.Parameter.__deepcopy__ = _param_copy
+        self._saved = (torch.Tensor.__deepcopy__, torch.nn.Parameter.__deepcopy__)
+        clone = self._clone
+        torch.Tensor.__deepcopy__ = lambda t, memo: clone(t, memo)
+        torch.nn.Parameter.__deepcopy__ = lambda p, memo: torch.nn.Parameter(clone(p, memo), requires_grad=p.requires_grad)
 
     def __exit__(self, exc_type, exc_val, exc_tb) -> None:
-        torch.Tensor.__deepcopy__ = self.t_copy_save_
-        torch.nn.Parameter.__deepcopy__ = self.p_copy_save_
+        torch.Tensor.__deepcopy__, torch.nn.Parameter.__deepcopy__ = self._saved
 
 
 def copy_to_device(module: nn.Module, current_device: torch.device, to_device: torch.device) -> nn.Module:
+    """Deep copy of ``module`` in which everything that lives on ``current_device`` moves to ``to_device``; tensors on other
+    devices (sharded tables) are shared with the original through ``sharded_model_copy``."""
     with sharded_model_copy(device=None):
-        copy_module = copy.deepcopy(module)
+        twin = copy.deepcopy(module)
+    if isinstance(twin, CopyMixIn):
+        return twin.copy(to_device)
 
-    def _copy_if_device_match(tensor: torch.Tensor) -> torch.Tensor:
-        if tensor.device == current_device:
-            return tensor.to(to_device)
-        return tensor
+    def moved(t: torch.Tensor) -> torch.Tensor:
+        return t.to(to_device) if t.device == current_device else t
 
-    if isinstance(copy_module, CopyMixIn):
-        return copy_module.copy(to_device)
-    copied_param = {name: torch.nn.Parameter(_copy_if_device_match(p.data), requires_grad=p.requires_grad) for name, p in copy_module.named_parameters(recurse=False)}
-    copied_buffer = {name: _copy_if_device_match(b) for name, b in copy_module.named_buffers(recurse=False)}
-    for name, param in copied_param.items():
-        copy_module.register_parameter(name, param)
-    for name, buffer in copied_buffer.items():
-        copy_module.register_buffer(name, buffer)
-    for child_name, child in copy_module.named_children():
-        if not any(p.device == current_device for p in child.parameters()) and not isinstance(child, CopyMixIn):
-            continue
-        setattr(copy_module, child_name, copy_to_device(child, current_device, to_device))
-    return copy_module
+    for name, p in list(twin.named_parameters(recurse=False)):
+        twin.register_parameter(name, torch.nn.Parameter(moved(p.data), requires_grad=p.requires_grad))
+    for name, buf in list(twin.named_buffers(recurse=False)):
+        twin.register_buffer(name, moved(buf))
+    for name, child in list(twin.named_children()):
+        if isinstance(child, CopyMixIn) or any(p.device == current_device for p in child.parameters()):
+            setattr(twin, name, copy_to_device(child, current_device, to_device))
+    return twin
 
 
 def optimizer_type_to_emb_opt_type(optimizer_class: Type[torch.optim.Optimizer]) -> Optional[EmbOptimType]:
@@ -157,15 +145,12 @@ def optimizer_type_to_emb_opt_type(optimizer_class: Type[torch.optim.Optimizer])
 
 def merge_fused_params(fused_params: Optional[Dict[str, Any]] = None, param_fused_params: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
     """Sharder-level fused params overridden by the per-parameter optimizer kwargs (``lr`` -> ``learning_rate``)."""
-    if fused_params is None:
-        fused_params = {}
-    if param_fused_params is None:
-        param_fused_params = {}
-    if "lr" in param_fused_params:
-        param_fused_params["learning_rate"] = param_fused_params.pop("lr")
-    _fused_params = copy.deepcopy(fused_params)
-    _fused_params.update(param_fused_params)
-    return _fused_params
+    merged = copy.deepcopy(fused_params or {})
+    overrides = param_fused_params if param_fused_params is not None else {}
+    if "lr" in overrides:
+        overrides["learning_rate"] = overrides.pop("lr")  # the kernels know the learning rate under this name
+    merged.update(overrides)
+    return merged
 
 
 def add_params_from_parameter_sharding(fused_params: Optional[Dict[str, Any]], parameter_sharding: ParameterSharding) -> Dict[str, Any]:
