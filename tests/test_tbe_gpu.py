@@ -248,3 +248,44 @@ def test_forward_sequence_one_huge_bag_and_empty_feature(idx_dtype):
         out = gpu(idx.to(idx_dtype).cuda(), offsets.to(idx_dtype).cuda())
     torch.testing.assert_close(out.cpu(), ref)
     gpu.check_error()
+
+
+def test_out_of_range_id_leaves_row_zero_alone():
+    """An id outside its table contributes nothing to the forward; the backward must not update row 0 for it either."""
+    specs = [(10, 8)]
+    _, gpu = _pair(specs, [0], PoolingMode.SUM, OptimizerArgs(EmbOptimType.EXACT_ROWWISE_ADAGRAD, 0.1))
+    before = gpu.weights.detach().clone()
+    idx = torch.tensor([3, 99, -5], device="cuda")
+    off = torch.tensor([0, 3], device="cuda")
+    out = gpu(idx, off)
+    out.backward(torch.ones_like(out))
+    after = gpu.weights.detach().view(10, 8)
+    b = before.view(10, 8)
+    assert not torch.equal(after[3], b[3]), "the valid id must be updated"
+    torch.testing.assert_close(after[0], b[0], rtol=0, atol=0)
+    assert float(gpu.momentum1[0]) == 0.0
+    with pytest.raises(IndexError):
+        gpu.check_error()
+
+
+def test_stochastic_rounding_is_unbiased_where_nearest_rounding_stalls():
+    """bf16 table, updates of a small fraction of one unit in the last place: rounding to nearest never moves the weights,
+    stochastic rounding moves them by the right amount on average."""
+    rows, D, steps, lr = 4096, 128, 50, 1.0
+    specs = [(rows, D)]
+    idx = torch.arange(rows, device="cuda")
+    off = torch.arange(rows + 1, device="cuda")
+    results = {}
+    for sr in (False, True):
+        opt = OptimizerArgs(EmbOptimType.EXACT_SGD, lr, stochastic_rounding=sr)
+        tbe = TableBatchedEmbeddingBags(specs, [0], PoolingMode.SUM, torch.bfloat16, torch.float32, opt, device="cuda")
+        with torch.no_grad():
+            tbe.weights.fill_(1.0)  # one unit in the last place of bf16 at 1.0 is 2**-7
+        g = torch.full((rows, D), 2.0 ** -7 / 16, device="cuda")  # each step moves a weight by 1/16 of that unit
+        for _ in range(steps):
+            out = tbe(idx, off)
+            out.backward(g)
+        results[sr] = float((1.0 - tbe.weights.detach().float()).mean())
+    expected = steps * 2.0 ** -7 / 16
+    assert results[False] == 0.0
+    assert abs(results[True] - expected) < 0.1 * expected, (results, expected)

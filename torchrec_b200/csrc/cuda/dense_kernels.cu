@@ -212,12 +212,19 @@ __global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __rest
   }
 }
 
-at::Tensor colsum_bf16(const at::Tensor& x) {
+// column sums of x; with `acc` they are ADDED into that fp32 [N] tensor (a bias gradient landing in a flat gradient buffer)
+static at::Tensor colsum_impl(const at::Tensor& x, c10::optional<at::Tensor> acc) {
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous() && x.size(1) % 2 == 0);
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t M = x.size(0);
   const int N = int(x.size(1));
-  at::Tensor out = at::zeros({N}, x.options().dtype(at::kFloat));
+  at::Tensor out;
+  if (acc.has_value() && acc->defined()) {
+    out = *acc;
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.numel() == N && out.is_contiguous());
+  } else {
+    out = at::zeros({N}, x.options().dtype(at::kFloat));
+  }
   if (M == 0) return out;
   const int col_tiles = (N + 63) / 64;
   int row_splits = int(std::max<int64_t>(1, std::min<int64_t>((148 * 8) / col_tiles, (M + 255) / 256)));
@@ -228,6 +235,10 @@ at::Tensor colsum_bf16(const at::Tensor& x) {
   TRB_CUDA_CHECK(cudaGetLastError());
   return out;
 }
+
+at::Tensor colsum_bf16(const at::Tensor& x) { return colsum_impl(x, c10::nullopt); }
+
+void colsum_bf16_acc(const at::Tensor& x, at::Tensor acc) { colsum_impl(x, acc); }
 
 // ---- dot interaction ------------------------------------------------------------------------------
 // One CTA per sample.  X = [dense; sparse] is staged in shared memory as fp32 with a padded pitch.
@@ -366,6 +377,7 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
   m.def("cross_bwd_elementwise(Tensor dy, Tensor x0, Tensor u) -> (Tensor, Tensor)");
   m.def("cross_bwd_fused(Tensor dy, Tensor x0, Tensor u, Tensor(a!)? dx0_in, bool add_dy) -> (Tensor, Tensor(a!), Tensor)");
   m.def("colsum_bf16(Tensor x) -> Tensor");
+  m.def("colsum_bf16_acc(Tensor x, Tensor(a!) acc) -> ()");
   m.def("dot_interaction_fwd(Tensor dense, Tensor sparse) -> Tensor");
   m.def("dot_interaction_bwd(Tensor dout, Tensor dense, Tensor sparse) -> (Tensor, Tensor)");
 }
@@ -375,6 +387,7 @@ TORCH_LIBRARY_IMPL(trb200, CUDA, m) {
   m.impl("cross_bwd_elementwise", &trb::cross_bwd_elementwise);
   m.impl("cross_bwd_fused", &trb::cross_bwd_fused);
   m.impl("colsum_bf16", &trb::colsum_bf16);
+  m.impl("colsum_bf16_acc", &trb::colsum_bf16_acc);
   m.impl("dot_interaction_fwd", &trb::dot_interaction_fwd);
   m.impl("dot_interaction_bwd", &trb::dot_interaction_bwd);
 }

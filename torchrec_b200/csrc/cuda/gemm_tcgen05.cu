@@ -801,8 +801,10 @@ at::Tensor gemm_nt_bf16_add(const at::Tensor& a, const at::Tensor& b, const at::
   return out;
 }
 
-// a^T @ b : a [Mc, N], b [Mc, K] -> [N, K] fp32 (weight gradient), split over the contraction
-at::Tensor gemm_tn_bf16(const at::Tensor& a, const at::Tensor& b) {
+// a^T @ b : a [Mc, N], b [Mc, K] -> [N, K] fp32 (weight gradient), split over the contraction.  With `acc` the product is
+// ADDED into that tensor (every work item reduces into it with red.add), which lets a weight gradient land directly in a
+// pre-zeroed flat gradient buffer: no output allocation, no zero fill, no accumulation pass afterwards.
+static at::Tensor gemm_tn_impl(const at::Tensor& a, const at::Tensor& b, c10::optional<at::Tensor> acc) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16);
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(0) == b.size(0) && a.stride(1) == 1 && b.stride(1) == 1);
   TORCH_CHECK(a.size(1) % 8 == 0 && b.size(1) % 8 == 0);
@@ -828,13 +830,26 @@ at::Tensor gemm_tn_bf16(const at::Tensor& a, const at::Tensor& b) {
       if (cost < best) { best = cost; splits = s_eff; }
     }
   }
-  at::Tensor out = splits > 1 ? at::zeros({N, K}, a.options().dtype(at::kFloat)) : at::empty({N, K}, a.options().dtype(at::kFloat));
-  if (Mc == 0) return out.zero_();
-  p.out = out.data_ptr(); p.out_fp32 = 1; p.atomic_out = splits > 1 ? 1 : 0; p.ldc = K;
+  const bool into = acc.has_value() && acc->defined();
+  at::Tensor out;
+  if (into) {
+    out = *acc;
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.dim() == 2 && out.size(0) == N && out.size(1) == K && out.is_contiguous(),
+                "accumulator must be a contiguous fp32 [N, K] tensor");
+    if (Mc == 0) return out;
+  } else {
+    out = splits > 1 ? at::zeros({N, K}, a.options().dtype(at::kFloat)) : at::empty({N, K}, a.options().dtype(at::kFloat));
+    if (Mc == 0) return out.zero_();
+  }
+  p.out = out.data_ptr(); p.out_fp32 = 1; p.atomic_out = (splits > 1 || into) ? 1 : 0; p.ldc = K;
   p.k_splits = splits;
   launch_gemm<true>(a, b, p);
   return out;
 }
+
+at::Tensor gemm_tn_bf16(const at::Tensor& a, const at::Tensor& b) { return gemm_tn_impl(a, b, c10::nullopt); }
+
+void gemm_tn_bf16_acc(const at::Tensor& a, const at::Tensor& b, at::Tensor acc) { gemm_tn_impl(a, b, acc); }
 
 // nonzero after a kernel gave up waiting (one device-to-host read; resets the flag)
 int64_t gemm_error_status() {
@@ -853,6 +868,7 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
   m.def("gemm_nt_bf16_cross(Tensor a, Tensor b, Tensor bias, Tensor x0, Tensor xl) -> (Tensor, Tensor)");
   m.def("gemm_nt_bf16_add(Tensor a, Tensor b, Tensor add) -> Tensor");
   m.def("gemm_tn_bf16(Tensor a, Tensor b) -> Tensor");
+  m.def("gemm_tn_bf16_acc(Tensor a, Tensor b, Tensor(a!) acc) -> ()");
   m.def("gemm_error_status() -> int");
 }
 
@@ -861,6 +877,7 @@ TORCH_LIBRARY_IMPL(trb200, CUDA, m) {
   m.impl("gemm_nt_bf16_cross", &trb::gemm_nt_bf16_cross);
   m.impl("gemm_nt_bf16_add", &trb::gemm_nt_bf16_add);
   m.impl("gemm_tn_bf16", &trb::gemm_tn_bf16);
+  m.impl("gemm_tn_bf16_acc", &trb::gemm_tn_bf16_acc);
 }
 
 TORCH_LIBRARY_IMPL(trb200, CompositeExplicitAutograd, m) { m.impl("gemm_error_status", &trb::gemm_error_status); }

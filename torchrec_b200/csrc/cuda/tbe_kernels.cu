@@ -206,6 +206,7 @@ __global__ void __launch_bounds__(256) tbe_seq_fwd_kernel(FwdParams p, int64_t N
 // ------------------------------------------------------------------------------------------------
 struct OptParams {
   int type;
+  int stochastic_rounding;  // fp16 / bf16 tables: round the updated weights up or down at random, unbiased in expectation
   float lr, eps, beta1, beta2, weight_decay;
   float bias_corr1, bias_corr2;  // 1 - beta^t
   float max_grad;                // > 0: clamp the summed gradient elementwise
@@ -246,6 +247,38 @@ struct BwdParams {
 constexpr int kBlk = 64;        // sorted entries per warp
 constexpr int FLAG_USED = 1;    // slot holds a partial sum
 constexpr int FLAG_CONT = 2;    // (slot A only) the row continues into the next block
+
+// ---- stochastic rounding of updated weights (16-bit tables) --------------------------------------------------------
+// Rounding to nearest loses every update smaller than half a unit in the last place, which stalls training of fp16 / bf16
+// tables with small learning rates.  Rounding up with probability equal to the discarded fraction keeps the expectation.
+// The random bits come from a hash of (row, element, the fp32 value itself): the value changes with every update, so the
+// bits do too, without a host-side seed (which a replayed CUDA graph would freeze).
+__device__ __forceinline__ uint32_t sr_hash(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ __nv_bfloat16 sr_bf16(float x, uint32_t salt) {
+  const uint32_t bits = __float_as_uint(x);
+  if ((bits & 0x7f800000u) == 0x7f800000u) return __float2bfloat16(x);  // inf / nan
+  const uint32_t r = sr_hash(bits ^ salt) & 0xffffu;
+  return __ushort_as_bfloat16((unsigned short)((bits + r) >> 16));
+}
+__device__ __forceinline__ __half sr_f16(float x, uint32_t salt) {
+  const uint32_t bits = __float_as_uint(x);
+  if ((bits & 0x7f800000u) == 0x7f800000u) return __float2half(x);
+  const uint32_t r = sr_hash(bits ^ salt) & 0x1fffu;  // fp32 keeps 13 more mantissa bits than fp16
+  return __float2half_rz(__uint_as_float(bits + r));
+}
+template <typename emb_t>
+__device__ __forceinline__ void store4_stochastic(emb_t* p, float4 v, uint32_t salt) { Vec4<emb_t>::store(p, v); }
+template <>
+__device__ __forceinline__ void store4_stochastic<__nv_bfloat16>(__nv_bfloat16* p, float4 v, uint32_t salt) {
+  p[0] = sr_bf16(v.x, salt); p[1] = sr_bf16(v.y, salt + 1); p[2] = sr_bf16(v.z, salt + 2); p[3] = sr_bf16(v.w, salt + 3);
+}
+template <>
+__device__ __forceinline__ void store4_stochastic<__half>(__half* p, float4 v, uint32_t salt) {
+  p[0] = sr_f16(v.x, salt); p[1] = sr_f16(v.y, salt + 1); p[2] = sr_f16(v.z, salt + 2); p[3] = sr_f16(v.w, salt + 3);
+}
 
 // Optimizer update of one table row.  `g` is the summed gradient of the row, `w` the row's current weights and
 // `mpre` (lane 0) its row-wise Adagrad state, both already loaded by the caller so that their latency overlaps
@@ -404,7 +437,10 @@ __device__ __forceinline__ void apply_update_core(const BwdParams& p, int64_t ke
 #pragma unroll
   for (int v = 0; v < kVecs; ++v) {
     const int e = v * 128 + lane * 4;
-    if (e < D) Vec4<emb_t>::store(wp + e, w[v]);
+    if (e < D) {
+      if (o.stochastic_rounding) store4_stochastic(wp + e, w[v], uint32_t(key) * 2654435761u + uint32_t(e));
+      else Vec4<emb_t>::store(wp + e, w[v]);
+    }
   }
 }
 
@@ -493,8 +529,12 @@ __global__ void __launch_bounds__(256, kVecs == 1 ? 4 : 2) tbe_bwd_block_kernel(
       const int64_t i = start + k;
       const int64_t key = p.sorted_keys[i];
       const int64_t nxt = (i + 1 < N_) ? p.sorted_keys[i + 1] : int64_t(-1);
-      const int src = p.sorted_src[i];
+      int src = p.sorted_src[i];
       float w = p.sorted_w ? p.sorted_w[i] : 1.f;
+      if (src < 0) {  // id outside its table: no gradient, no state change (matches the forward, which skipped it)
+        src = -src - 1;
+        w = 0.f;
+      }
       int f;
       int64_t goff;
       const char* gsrc = gbase;
@@ -731,12 +771,15 @@ __global__ void __launch_bounds__(256) tbe_linearize_kernel(
   if (bag_scale && lane == 0) bag_scale[bag] = end > start ? 1.f / float(end - start) : 0.f;
   for (int64_t i = start + lane; i < end; i += 32) {
     int64_t r = int64_t(indices[i]);
-    if (r < 0 || r >= rows) {
+    const bool bad = r < 0 || r >= rows;
+    if (bad) {
       atomicExch(err, 1);
       r = 0;
     }
     keys[i] = hoff + r;
-    src[i] = pooled ? int32_t(bag) : int32_t(i);
+    // an id outside its table contributed nothing to the forward; a negative source tells the backward to give it weight 0
+    const int32_t s = pooled ? int32_t(bag) : int32_t(i);
+    src[i] = bad ? -s - 1 : s;
     if (src_feature) src_feature[i] = f;
   }
 }
@@ -979,7 +1022,7 @@ static void tbe_backward_apply_impl(at::Tensor weights, c10::optional<at::Tensor
                                     int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
                                     double beta2, double weight_decay, int64_t step, double max_grad,
                                     const std::vector<int64_t>& grad_ptrs, int64_t B_local, double grad_scale,
-                                    const c10::optional<at::Tensor>& n_valid = c10::nullopt) {
+                                    const c10::optional<at::Tensor>& n_valid = c10::nullopt, bool stochastic_rounding = false) {
   const int64_t N = sorted_keys.numel();
   if (N == 0) return;
   c10::cuda::CUDAGuard guard(weights.device());
@@ -1039,6 +1082,7 @@ static void tbe_backward_apply_impl(at::Tensor weights, c10::optional<at::Tensor
   p.opt.bias_corr1 = float(1.0 - std::pow(beta1, double(std::max<int64_t>(step, 1))));
   p.opt.bias_corr2 = float(1.0 - std::pow(beta2, double(std::max<int64_t>(step, 1))));
   p.opt.max_grad = float(max_grad);
+  p.opt.stochastic_rounding = (stochastic_rounding && weights.scalar_type() != at::kFloat) ? 1 : 0;
   TORCH_CHECK(pooled || p.src_feature != nullptr, "unpooled backward needs src_feature");
   if (opt_type == OPT_DENSE_GRAD) TORCH_CHECK(p.dense_grad != nullptr);
   const int threads = 256;
@@ -1060,10 +1104,11 @@ void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10:
                         const at::Tensor& sorted_src, const at::Tensor& sorted_w, const at::Tensor& src_feature,
                         const at::Tensor& bag_scale, const at::Tensor& grad, int64_t grad_stride, int64_t B,
                         int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
-                        double beta2, double weight_decay, int64_t step, double max_grad, c10::optional<at::Tensor> n_valid) {
+                        double beta2, double weight_decay, int64_t step, double max_grad, c10::optional<at::Tensor> n_valid,
+                        bool stochastic_rounding) {
   tbe_backward_apply_impl(weights, mom1, mom2, dense_grad, meta, sorted_keys, sorted_src, sorted_w, src_feature, bag_scale, grad,
                           grad_stride, B, max_D, pooled, opt_type, lr, eps, beta1, beta2, weight_decay, step, max_grad, {}, 0, 1.0,
-                          n_valid);
+                          n_valid, stochastic_rounding);
 }
 
 // Backward of the fused lookup + exchange: the pooled gradient of bag b (of the global batch) is read from the
@@ -1221,6 +1266,7 @@ extern "C" int trb_tbe_backward_apply_noalloc(const trb_tbe_bwd_noalloc_args* a,
   p.opt.bias_corr1 = float(1.0 - std::pow(double(a->beta1), double(step)));
   p.opt.bias_corr2 = float(1.0 - std::pow(double(a->beta2), double(step)));
   p.opt.max_grad = a->max_grad;
+  p.opt.stochastic_rounding = 0;
 
   // the only word that must start at zero: the queue length of long chains (pass 1 writes every flag it covers)
   e = cudaMemsetAsync(p.long_count, 0, sizeof(int), stream);
@@ -1251,7 +1297,7 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
       "tbe_backward_apply(Tensor(a!) weights, Tensor(b!)? mom1, Tensor(c!)? mom2, Tensor(d!)? dense_grad, Tensor meta, "
       "Tensor sorted_keys, Tensor sorted_src, Tensor sorted_w, Tensor src_feature, Tensor bag_scale, Tensor grad, "
       "int grad_stride, int B, int max_D, bool pooled, int opt_type, float lr, float eps, float beta1, float beta2, "
-      "float weight_decay, int step, float max_grad, Tensor? n_valid) -> ()");
+      "float weight_decay, int step, float max_grad, Tensor? n_valid, bool stochastic_rounding=False) -> ()");
   m.def(
       "tbe_backward_apply_dist(Tensor(a!) weights, Tensor(b!)? mom1, Tensor(c!)? mom2, Tensor(d!)? dense_grad, Tensor meta, "
       "Tensor sorted_keys, Tensor sorted_src, Tensor sorted_w, Tensor src_feature, Tensor bag_scale, Tensor grad, "

@@ -85,6 +85,7 @@ def _optimizer_args_from_fused_params(fused_params: Optional[Dict[str, Any]]) ->
         weight_decay=float(fp.get("weight_decay", 0.0)),
         eta=float(fp.get("eta", 0.001)),
         max_gradient=float(fp.get("max_gradient", 1.0)) if fp.get("gradient_clipping", False) else 0.0,
+        stochastic_rounding=bool(fp.get("stochastic_rounding", True)),
     )
 
 

@@ -50,8 +50,9 @@ class PeerGradSync:
         self.enabled = True
         for p in self.buffer.params:
             p.register_post_accumulate_grad_hook(self._on_grad)
+        self.buffer.on_direct_write = self._on_grad  # gradients written by kernels bypass the accumulation hooks
 
-    def _on_grad(self, _p: torch.Tensor) -> None:
+    def _on_grad(self, _p: Optional[torch.Tensor] = None) -> None:
         if not self._armed and self.enabled:
             self._armed = True
             torch.autograd.Variable._execution_engine.queue_callback(self._finish_backward)

@@ -12,6 +12,7 @@ The reference runs these layers as ``nn.Linear`` / ``torch.bmm`` library calls
 from __future__ import annotations
 
 import os
+import weakref
 from typing import Optional, Tuple
 
 import torch
@@ -102,6 +103,20 @@ class _Bf16Cache:
 bf16_cache = _Bf16Cache()
 
 
+def _grad_sink(p: torch.Tensor) -> Optional[torch.Tensor]:
+    """Where the gradient of ``p`` may be accumulated directly: its view into a flat gradient buffer (``FlatParamBuffer``),
+    provided that buffer was zeroed for this step.  The weight-gradient GEMM and the bias column sum then reduce straight into
+    it, which removes an output allocation, a zero fill and an accumulation pass per parameter."""
+    buf = getattr(p, "_trb_flat", None)
+    if buf is None or not getattr(buf, "direct_grads", False):
+        return None
+    g = p.grad
+    if g is None or g.dtype != torch.float32 or not g.is_cuda or not g.is_contiguous() or not _ext.has_cuda_ext():
+        return None
+    buf.note_direct_write()
+    return g
+
+
 # --------------------------------------------------------------------------------------
 # GEMM primitive: C[M,N] = A[M,K] @ B[N,K]^T  (both operands K-major), bf16 in, fp32 accumulate
 # --------------------------------------------------------------------------------------
@@ -147,6 +162,7 @@ class _LinearAct(torch.autograd.Function):
         y = gemm_nt(x16, w16, bias, act, torch.bfloat16)
         ctx.act = act
         ctx.has_bias = bias is not None
+        ctx.bias_ref = weakref.ref(bias) if bias is not None else None
         ctx.save_for_backward(x16, weight, y)
         ctx.x_dtype = x.dtype
         return y
@@ -168,9 +184,9 @@ class _LinearAct(torch.autograd.Function):
             wT16 = bf16_cache.get(weight, transposed=True)  # [K, N]
             dx = gemm_nt(dz, wT16, None, ACT_NONE, torch.bfloat16).to(ctx.x_dtype)
         if ctx.needs_input_grad[1]:
-            dw = gemm_tn(dz, x16)  # [N, K] fp32
+            dw = gemm_tn(dz, x16, into=_grad_sink(weight))  # [N, K] fp32, or None when it went straight into weight.grad
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dz.float().sum(0) if not dz.is_cuda or not _ext.has_cuda_ext() else torch.ops.trb200.colsum_bf16(dz)
+            db = colsum(dz, into=_grad_sink(ctx.bias_ref()) if ctx.bias_ref is not None else None)
         return dx, dw, db, None
 
 
@@ -183,11 +199,33 @@ def act_backward(dy: torch.Tensor, y: torch.Tensor, act: int) -> torch.Tensor:
     return (dy.float() * yf * (1 - yf)).to(dy.dtype)
 
 
-def gemm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """``a.T @ b`` with ``a [M,N]``, ``b [M,K]`` bf16 -> ``[N,K]`` fp32 (weight gradient)."""
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, into: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``a.T @ b`` with ``a [M,N]``, ``b [M,K]`` bf16 -> ``[N,K]`` fp32 (weight gradient).  With ``into`` the product is added to
+    that tensor and ``None`` is returned."""
     if a.is_cuda and _GEMM_BACKEND == "tcgen05" and _ext.has_cuda_ext() and _tcgen05_tn_ok(a, b):
+        if into is not None:
+            torch.ops.trb200.gemm_tn_bf16_acc(a, b, into.view(a.shape[1], b.shape[1]))
+            return None
         return torch.ops.trb200.gemm_tn_bf16(a, b)
-    return torch.matmul(a.t(), b).float()
+    out = torch.matmul(a.t(), b).float()
+    if into is not None:
+        into.add_(out.view_as(into))
+        return None
+    return out
+
+
+def colsum(x: torch.Tensor, into: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """Column sums of a bf16 matrix in fp32 (bias gradient); with ``into`` they are added to that tensor and ``None`` is returned."""
+    if x.is_cuda and _ext.has_cuda_ext() and x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] % 2 == 0:
+        if into is not None:
+            torch.ops.trb200.colsum_bf16_acc(x, into)
+            return None
+        return torch.ops.trb200.colsum_bf16(x)
+    out = x.float().sum(0)
+    if into is not None:
+        into.add_(out)
+        return None
+    return out
 
 
 def _tcgen05_tn_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
@@ -381,8 +419,8 @@ class _LowRankCrossStack(torch.autograd.Function):
             last = l == 0
             du, dx0_acc, dbs[l] = _cross_bwd_fused(dy, x0, u, dx0_acc, last)
             dv = gemm_nt(du, bf16_cache.get(Ws[l], transposed=True), None, ACT_NONE, torch.bfloat16)  # [B, r]
-            dWs[l] = gemm_tn(du, v)
-            dVs[l] = gemm_tn(dv, xl)
+            dWs[l] = gemm_tn(du, v, into=_grad_sink(Ws[l]))
+            dVs[l] = gemm_tn(dv, xl, into=_grad_sink(Vs[l]))
             VT16 = bf16_cache.get(Vs[l], transposed=True)
             if last:
                 dx0 = gemm_nt_add(dv, VT16, dx0_acc)  # x_0 is also the x input of layer 0

@@ -76,6 +76,7 @@ class OptimizerArgs:
     weight_decay: float = 0.0
     eta: float = 0.001  # LARS trust coefficient
     max_gradient: float = 0.0  # > 0 clamps the summed row gradient elementwise
+    stochastic_rounding: bool = True  # fp16 / bf16 tables only: unbiased random rounding of the updated weights
 
 
 class TBEPlan:
@@ -429,7 +430,7 @@ class TableBatchedEmbeddingBags(nn.Module):
                 w, self.momentum1 if self.momentum1.numel() else None, self.momentum2 if self.momentum2.numel() else None,
                 dense_grad, self._meta_tensor(w.device), plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale,
                 grad_out, grad_out.stride(0), B, self.max_D, self.pooling_mode != PoolingMode.NONE, code,
-                o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay, self.step, o.max_gradient, plan.n_valid,
+                o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay, self.step, o.max_gradient, plan.n_valid, bool(o.stochastic_rounding),
             )
             return None if self.fused else dense_grad.to(w.dtype)
         return self._backward_cpu(w, grad_out, indices, offsets, psw, B)
@@ -505,7 +506,7 @@ class TableBatchedEmbeddingBags(nn.Module):
             w, self.momentum1 if self.momentum1.numel() else None, self.momentum2 if self.momentum2.numel() else None, None,
             self._meta_tensor_at(w.device, cols), plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale, grad, grad.stride(0), B,
             self.max_D, True, _OPT_CODE[o.optimizer], o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay, self.step, o.max_gradient,
-            plan.n_valid,
+            plan.n_valid, bool(o.stochastic_rounding),
         )
 
     def _psw_grad(self, grad_out: torch.Tensor, indices: torch.Tensor, offsets: torch.Tensor, B: int) -> torch.Tensor:

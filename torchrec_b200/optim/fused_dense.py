@@ -57,6 +57,9 @@ class FlatParamBuffer:
             rows_cols.append((rows, cols))
         self.rows_cols = rows_cols
         self.total_tiles = tile0
+        # direct gradient accumulation (ops/dense_ops.py::_grad_sink): valid while every p.grad is its view of the zeroed flat buffer
+        self.direct_grads = False
+        self.on_direct_write: Optional[Callable[[], None]] = None
         self.desc = torch.tensor(desc, dtype=torch.int64, device=dev).reshape(-1, 5)
         self._register_bf16()
         self.refresh_bf16()
@@ -105,11 +108,16 @@ class FlatParamBuffer:
                 view.copy_(g)
                 p.grad = view
 
+    def note_direct_write(self) -> None:
+        if self.on_direct_write is not None:
+            self.on_direct_write()
+
     def zero_grad(self) -> None:
         self.grad.zero_()
         for p, off in zip(self.params, self.offsets):
             if p.grad is None or p.grad.data_ptr() != self.grad.data_ptr() + 4 * off:
                 p.grad = self.grad[off: off + p.numel()].view(p.shape)
+        self.direct_grads = True  # from here to the optimizer step, gradient kernels may reduce straight into the flat buffer
 
 
 def flat_buffer_of(params: Sequence[torch.nn.Parameter]) -> Optional[FlatParamBuffer]:
@@ -164,6 +172,7 @@ class FusedDenseOptimizer(torch.optim.Optimizer):
         if not torch.cuda.is_current_stream_capturing() if b.device.type == "cuda" else True:
             b.attach_grads()
         self.step_count.add_(1)
+        b.direct_grads = False
         if b.device.type == "cuda":
             torch.ops.trb200.dense_optimizer_step(b.master, b.grad, self.s1, self.s2, b.w16, b.wT16, b.desc, b.total_tiles, _OPT_CODE[self._kind],
                                                   lr, eps, float(b1), float(b2), wd, self.step_count if self._kind == "adam" else None)
