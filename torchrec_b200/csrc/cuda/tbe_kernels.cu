@@ -207,6 +207,7 @@ __global__ void __launch_bounds__(256) tbe_seq_fwd_kernel(FwdParams p, int64_t N
 struct OptParams {
   int type;
   int stochastic_rounding;  // fp16 / bf16 tables: round the updated weights up or down at random, unbiased in expectation
+  const int64_t* sr_counter;  // device-side call counter that salts the random bits (a replayed CUDA graph keeps host values frozen)
   float lr, eps, beta1, beta2, weight_decay;
   float bias_corr1, bias_corr2;  // 1 - beta^t
   float max_grad;                // > 0: clamp the summed gradient elementwise
@@ -251,8 +252,9 @@ constexpr int FLAG_CONT = 2;    // (slot A only) the row continues into the next
 // ---- stochastic rounding of updated weights (16-bit tables) --------------------------------------------------------
 // Rounding to nearest loses every update smaller than half a unit in the last place, which stalls training of fp16 / bf16
 // tables with small learning rates.  Rounding up with probability equal to the discarded fraction keeps the expectation.
-// The random bits come from a hash of (row, element, the fp32 value itself): the value changes with every update, so the
-// bits do too, without a host-side seed (which a replayed CUDA graph would freeze).
+// The random bits come from a hash of (row, element, value, a call counter kept on the device): a host-side seed would be
+// frozen by a replayed CUDA graph, and a hash of the value alone would give a weight that was rounded back to where it
+// started the same bits again at the next step.
 __device__ __forceinline__ uint32_t sr_hash(uint32_t x) {
   x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
   return x;
@@ -438,7 +440,7 @@ __device__ __forceinline__ void apply_update_core(const BwdParams& p, int64_t ke
   for (int v = 0; v < kVecs; ++v) {
     const int e = v * 128 + lane * 4;
     if (e < D) {
-      if (o.stochastic_rounding) store4_stochastic(wp + e, w[v], uint32_t(key) * 2654435761u + uint32_t(e));
+      if (o.stochastic_rounding) store4_stochastic(wp + e, w[v], (uint32_t(key) * 2654435761u + uint32_t(e)) ^ (uint32_t(*o.sr_counter) * 0x9e3779b9u));
       else Vec4<emb_t>::store(wp + e, w[v]);
     }
   }
@@ -784,6 +786,8 @@ __global__ void __launch_bounds__(256) tbe_linearize_kernel(
   }
 }
 
+__global__ void tbe_bump_counter_kernel(int64_t* counter) { counter[0] += 1; }
+
 template <typename idx_t>
 __global__ void tbe_count_valid_kernel(const idx_t* __restrict__ offsets, int64_t nbags, int64_t* __restrict__ out) {
   out[0] = int64_t(offsets[nbags]) - int64_t(offsets[0]);
@@ -1022,7 +1026,8 @@ static void tbe_backward_apply_impl(at::Tensor weights, c10::optional<at::Tensor
                                     int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
                                     double beta2, double weight_decay, int64_t step, double max_grad,
                                     const std::vector<int64_t>& grad_ptrs, int64_t B_local, double grad_scale,
-                                    const c10::optional<at::Tensor>& n_valid = c10::nullopt, bool stochastic_rounding = false) {
+                                    const c10::optional<at::Tensor>& n_valid = c10::nullopt,
+                                    const c10::optional<at::Tensor>& sr_counter = c10::nullopt) {
   const int64_t N = sorted_keys.numel();
   if (N == 0) return;
   c10::cuda::CUDAGuard guard(weights.device());
@@ -1082,7 +1087,10 @@ static void tbe_backward_apply_impl(at::Tensor weights, c10::optional<at::Tensor
   p.opt.bias_corr1 = float(1.0 - std::pow(beta1, double(std::max<int64_t>(step, 1))));
   p.opt.bias_corr2 = float(1.0 - std::pow(beta2, double(std::max<int64_t>(step, 1))));
   p.opt.max_grad = float(max_grad);
-  p.opt.stochastic_rounding = (stochastic_rounding && weights.scalar_type() != at::kFloat) ? 1 : 0;
+  const bool sr = sr_counter.has_value() && sr_counter->defined() && weights.scalar_type() != at::kFloat;
+  if (sr) TORCH_CHECK(sr_counter->is_cuda() && sr_counter->scalar_type() == at::kLong && sr_counter->numel() >= 1);
+  p.opt.stochastic_rounding = sr ? 1 : 0;
+  p.opt.sr_counter = sr ? sr_counter->data_ptr<int64_t>() : nullptr;
   TORCH_CHECK(pooled || p.src_feature != nullptr, "unpooled backward needs src_feature");
   if (opt_type == OPT_DENSE_GRAD) TORCH_CHECK(p.dense_grad != nullptr);
   const int threads = 256;
@@ -1096,6 +1104,7 @@ static void tbe_backward_apply_impl(at::Tensor weights, c10::optional<at::Tensor
       tbe_bwd_verylong_kernel<emb_t, kVecs><<<296, 256, 0, stream>>>(p);
     });
   });
+  if (sr) tbe_bump_counter_kernel<<<1, 1, 0, stream>>>(sr_counter->data_ptr<int64_t>());
   TRB_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -1105,10 +1114,10 @@ void tbe_backward_apply(at::Tensor weights, c10::optional<at::Tensor> mom1, c10:
                         const at::Tensor& bag_scale, const at::Tensor& grad, int64_t grad_stride, int64_t B,
                         int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
                         double beta2, double weight_decay, int64_t step, double max_grad, c10::optional<at::Tensor> n_valid,
-                        bool stochastic_rounding) {
+                        c10::optional<at::Tensor> sr_counter) {
   tbe_backward_apply_impl(weights, mom1, mom2, dense_grad, meta, sorted_keys, sorted_src, sorted_w, src_feature, bag_scale, grad,
                           grad_stride, B, max_D, pooled, opt_type, lr, eps, beta1, beta2, weight_decay, step, max_grad, {}, 0, 1.0,
-                          n_valid, stochastic_rounding);
+                          n_valid, sr_counter);
 }
 
 // Backward of the fused lookup + exchange: the pooled gradient of bag b (of the global batch) is read from the
@@ -1267,6 +1276,7 @@ extern "C" int trb_tbe_backward_apply_noalloc(const trb_tbe_bwd_noalloc_args* a,
   p.opt.bias_corr2 = float(1.0 - std::pow(double(a->beta2), double(step)));
   p.opt.max_grad = a->max_grad;
   p.opt.stochastic_rounding = 0;
+  p.opt.sr_counter = nullptr;
 
   // the only word that must start at zero: the queue length of long chains (pass 1 writes every flag it covers)
   e = cudaMemsetAsync(p.long_count, 0, sizeof(int), stream);
@@ -1297,7 +1307,7 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
       "tbe_backward_apply(Tensor(a!) weights, Tensor(b!)? mom1, Tensor(c!)? mom2, Tensor(d!)? dense_grad, Tensor meta, "
       "Tensor sorted_keys, Tensor sorted_src, Tensor sorted_w, Tensor src_feature, Tensor bag_scale, Tensor grad, "
       "int grad_stride, int B, int max_D, bool pooled, int opt_type, float lr, float eps, float beta1, float beta2, "
-      "float weight_decay, int step, float max_grad, Tensor? n_valid, bool stochastic_rounding=False) -> ()");
+      "float weight_decay, int step, float max_grad, Tensor? n_valid, Tensor(e!)? sr_counter=None) -> ()");
   m.def(
       "tbe_backward_apply_dist(Tensor(a!) weights, Tensor(b!)? mom1, Tensor(c!)? mom2, Tensor(d!)? dense_grad, Tensor meta, "
       "Tensor sorted_keys, Tensor sorted_src, Tensor sorted_w, Tensor src_feature, Tensor bag_scale, Tensor grad, "

@@ -67,28 +67,25 @@ def intra_and_cross_node_pg(
 ) -> Tuple[Optional[dist.ProcessGroup], Optional[dist.ProcessGroup]]:
     """Sub-groups of the ranks on this node and of the ranks with the same local index on all nodes."""
     global _INTRA_PG, _CROSS_PG
-    my_size = dist.get_world_size()
-    my_rank = dist.get_rank()
-    my_local_size = get_local_size(my_size)
-    my_local_rank = get_local_rank(my_size, my_rank)
-    my_group_rank = get_group_rank(my_size, my_rank)
-    group_count = get_num_groups(my_size)
-    if backend is None:
-        backend = dist.get_backend()
+    world, me = dist.get_world_size(), dist.get_rank()
+    per_node = get_local_size(world)
+    nodes = get_num_groups(world)
+    backend = backend or dist.get_backend()
+
+    def make_family(groups: List[List[int]]) -> Optional[dist.ProcessGroup]:
+        # group creation is collective: every rank creates every group and keeps the one it is a member of
+        mine = None
+        for ranks in groups:
+            pg = dist.new_group(backend=backend, ranks=ranks)
+            if me in ranks:
+                mine = pg
+        dist.barrier()
+        return mine
+
     if _INTRA_PG is None:
-        for group_rank in range(group_count):
-            peers = [group_rank * my_local_size + r for r in range(my_local_size)]
-            curr = dist.new_group(backend=backend, ranks=peers)
-            if my_group_rank == group_rank:
-                _INTRA_PG = curr
-        dist.barrier()
+        _INTRA_PG = make_family([list(range(n * per_node, (n + 1) * per_node)) for n in range(nodes)])
     if _CROSS_PG is None:
-        for l_rank in range(my_local_size):
-            peers = [l_rank + g * my_local_size for g in range(group_count)]
-            curr = dist.new_group(backend=backend, ranks=peers)
-            if l_rank == my_local_rank:
-                _CROSS_PG = curr
-        dist.barrier()
+        _CROSS_PG = make_family([list(range(i, world, per_node)) for i in range(per_node)])
     return _INTRA_PG, _CROSS_PG
 
 

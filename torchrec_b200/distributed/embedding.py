@@ -22,6 +22,7 @@ from torch.nn.parallel import DistributedDataParallel
 
 from torchrec_b200.distributed.batched_embedding_kernel import TableBatchedEmbeddingSlice, get_state_dict
 from torchrec_b200.distributed.embedding_sharding import EmbeddingSharding, EmbeddingShardingInfo, KJTListSplitsAwaitable
+from torchrec_b200.distributed.embeddingbag import ShardedTableStateMixin
 from torchrec_b200.distributed.embedding_types import BaseEmbeddingSharder, EmbeddingComputeKernel, KJTList, ShardedEmbeddingModule
 from torchrec_b200.distributed.sharding.cw_sequence_sharding import CwSequenceEmbeddingSharding
 from torchrec_b200.distributed.sharding.dp_sequence_sharding import DpSequenceEmbeddingSharding
@@ -190,6 +191,7 @@ def _dedup_indices(ctx: EmbeddingCollectionContext, features: KeyedJaggedTensor,
 
 
 class ShardedEmbeddingCollection(
+    ShardedTableStateMixin,
     ShardedEmbeddingModule[KJTList, List[torch.Tensor], Dict[str, JaggedTensor], EmbeddingCollectionContext],
     FusedOptimizerModule,
 ):
@@ -241,9 +243,8 @@ class ShardedEmbeddingCollection(
                     process_group=env.process_group, gradient_as_bucket_view=True, broadcast_buffers=True, static_graph=True,
                 )
         # parameters / ShardedTensor state: same layout logic as the pooled module, under "embeddings."
-        from torchrec_b200.distributed.embeddingbag import ShardedEmbeddingBagCollection as _EBC
-
-        _EBC._initialize_torch_state(self)
+        self._output_dtensor = getattr(env, "output_dtensor", False)
+        self._initialize_torch_state()
         optims = []
         for lookup in self._lookups:
             lk = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
@@ -329,12 +330,6 @@ class ShardedEmbeddingCollection(
     def sharded_parameter_names(self, prefix: str = "") -> Iterator[str]:
         for name in self._model_parallel_name_to_local_shards.keys():
             yield append_prefix(prefix, f"embeddings.{name}.weight")
-
-    @staticmethod
-    def _pre_load_state_dict_hook(self, state_dict, prefix, *args) -> None:
-        from torchrec_b200.distributed.embeddingbag import ShardedEmbeddingBagCollection as _EBC
-
-        _EBC._pre_load_state_dict_hook(self, state_dict, prefix, *args)
 
     @property
     def fused_optimizer(self) -> KeyedOptimizer:

@@ -235,149 +235,10 @@ def _apply_mean_pooling(keyed_tensor: KeyedTensor, divisor: torch.Tensor) -> Key
                            length_per_key=keyed_tensor.length_per_key(), key_dim=1)
 
 
-class ShardedEmbeddingBagCollection(
-    ShardedEmbeddingModule[KJTList, List[torch.Tensor], KeyedTensor, EmbeddingBagCollectionContext],
-    FusedOptimizerModule,
-):
-    """Sharded counterpart of ``EmbeddingBagCollection``; built by ``EmbeddingBagCollectionSharder``."""
-
-    _TABLE_ATTR: str = "embedding_bags"  # name of the ModuleDict that holds ``<table>.weight``
-
-    def _table_configs(self):
-        return self._embedding_bag_configs
-
-    def __init__(
-        self,
-        module: EmbeddingBagCollectionInterface,
-        table_name_to_parameter_sharding: Dict[str, ParameterSharding],
-        env: ShardingEnv,
-        fused_params: Optional[Dict[str, Any]] = None,
-        device: Optional[torch.device] = None,
-        qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None,
-        module_fqn: Optional[str] = None,
-    ) -> None:
-        super().__init__(qcomm_codecs_registry=qcomm_codecs_registry)
-        self._module_fqn = module_fqn
-        self._embedding_bag_configs: List[EmbeddingBagConfig] = module.embedding_bag_configs()
-        self._table_names: List[str] = [c.name for c in self._embedding_bag_configs]
-        self._table_name_to_config: Dict[str, EmbeddingBagConfig] = {c.name: c for c in self._embedding_bag_configs}
-        self.module_sharding_plan: EmbeddingModuleShardingPlan = EmbeddingModuleShardingPlan(
-            {t: ps for t, ps in table_name_to_parameter_sharding.items() if t in self._table_names}
-        )
-        self._env = env
-        self._output_dtensor: bool = env.output_dtensor
-        self.sharding_type_to_sharding_infos = self.create_grouped_sharding_infos(module, table_name_to_parameter_sharding, "embedding_bags.", fused_params)
-        self._sharding_types: List[str] = list(self.sharding_type_to_sharding_infos.keys())
-        self._embedding_shardings: List[EmbeddingSharding] = [
-            create_embedding_bag_sharding(infos, env, device, permute_embeddings=True, qcomm_codecs_registry=self.qcomm_codecs_registry)
-            for infos in self.sharding_type_to_sharding_infos.values()
-        ]
-        self._is_weighted: bool = module.is_weighted()
-        self._device = device
-        self._input_dists: List[nn.Module] = []
-        self._lookups: List[nn.Module] = []
-        self._create_lookups()
-        self._output_dists: List[nn.Module] = []
-        self._embedding_names: List[str] = []
-        self._embedding_dims: List[int] = []
-        self._feature_splits: List[int] = []
-        self._features_order: List[int] = []
-        self._uncombined_embedding_names: List[str] = []
-        self._uncombined_embedding_dims: List[int] = []
-        self._inverse_indices_permute_indices: Optional[torch.Tensor] = None
-        # output order: embeddings come out grouped by sharding type; permute back to table order
-        self._permute_op: Optional[nn.Module] = None
-        self._has_uninitialized_input_dist: bool = True
-        self._has_features_permute: bool = True
-        # lookups that hold data-parallel tables are wrapped in DDP so their dense gradient is all-reduced
-        for i, (sharding, lookup) in enumerate(zip(self._embedding_shardings, self._lookups)):
-            if isinstance(sharding, DpPooledEmbeddingSharding) and env.process_group is not None and dist.get_world_size(env.process_group) >= 1:
-                if dist.get_backend(env.process_group) != "fake":
-                    self._lookups[i] = DistributedDataParallel(
-                        module=lookup, device_ids=[device] if device is not None and device.type == "cuda" else None,
-                        process_group=env.process_group, gradient_as_bucket_view=True, broadcast_buffers=True, static_graph=True,
-                    )
-        self._initialize_torch_state()
-        # optimizer
-        optims = []
-        for lookup in self._lookups:
-            lk = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
-            for _, tbe_module in lk.named_modules():
-                if isinstance(tbe_module, FusedOptimizerModule):
-                    # keys of the fused optimizer are "<table>.weight"; make them "embedding_bags.<table>.weight"
-                    params: Dict[str, Union[torch.Tensor, ShardedTensor]] = {}
-                    for param_key, weight in tbe_module.fused_optimizer.params.items():
-                        params["embedding_bags." + param_key] = weight
-                    tbe_module.fused_optimizer.params = params
-                    optims.append(("", tbe_module.fused_optimizer))
-        self._optim: CombinedOptimizer = CombinedOptimizer(optims)
-        # mean pooling for row-split tables is applied after the reduction
-        self._has_mean_pooling_callback: bool = PoolingType.MEAN.value in self._pooling_type_to_rs_features()
-        # fused sparse engine (peer-memory input dist + lookup + output hand-over): built on the first batch, collectively
-        self._engine_state: str = "auto"  # "auto" -> "on" | "off"
-        self._engine = None
-        self._dim_per_key: Optional[torch.Tensor] = None
-        self._kjt_key_indices: Dict[str, int] = {}
-        self._kt_key_ordering: Optional[torch.Tensor] = None
-
-    # ---- plan -> sharding infos ------------------------------------------------------------------
-    @classmethod
-    def create_grouped_sharding_infos(cls, module, table_name_to_parameter_sharding: Dict[str, ParameterSharding], prefix: str,
-                                      fused_params: Optional[Dict[str, Any]], suffix: Optional[str] = "weight") -> Dict[str, List[EmbeddingShardingInfo]]:
-        """``{sharding type: [one EmbeddingShardingInfo per table]}`` in the order the tables appear in the module.  A feature
-        that feeds two tables gets the embedding name ``feature@table`` so that output columns stay distinguishable."""
-        configs = list(module.embedding_bag_configs())
-        for cfg in configs:
-            cfg.feature_names = cfg.feature_names or [cfg.name]
-        uses: Dict[str, int] = defaultdict(int)
-        for cfg in configs:
-            for f in cfg.feature_names:
-                uses[f] += 1
-        tensors: Dict[str, Any] = dict(module.state_dict())
-        tensors.update(dict(module.named_parameters()))  # parameters win: they carry the optimizer annotations
-        valid_kernels = {k.value for k in EmbeddingComputeKernel}
-        grouped: Dict[str, List[EmbeddingShardingInfo]] = defaultdict(list)
-        for cfg in configs:
-            assert cfg.name in table_name_to_parameter_sharding, f"{cfg.name} not in table_name_to_parameter_sharding"
-            ps = table_name_to_parameter_sharding[cfg.name]
-            if ps.compute_kernel not in valid_kernels:
-                raise ValueError(f"Compute kernel not supported {ps.compute_kernel}")
-            key = prefix + cfg.name + ("" if suffix is None else f".{suffix}")
-            assert key in tensors, f"{key} is neither a parameter nor a state-dict entry of the module"
-            param = tensors[key]
-            table = EmbeddingTableConfig(
-                num_embeddings=cfg.num_embeddings, embedding_dim=cfg.embedding_dim, name=cfg.name, data_type=cfg.data_type,
-                feature_names=list(cfg.feature_names), pooling=cfg.pooling, is_weighted=module.is_weighted(), has_feature_processor=False,
-                embedding_names=[f"{f}@{cfg.name}" if uses[f] > 1 else f for f in cfg.feature_names],
-                weight_init_max=cfg.weight_init_max, weight_init_min=cfg.weight_init_min, init_fn=cfg.init_fn,
-                num_embeddings_post_pruning=getattr(cfg, "num_embeddings_post_pruning", None),
-                total_num_buckets=getattr(cfg, "total_num_buckets", None), use_virtual_table=getattr(cfg, "use_virtual_table", False),
-            )
-            grouped[ps.sharding_type].append(
-                EmbeddingShardingInfo(embedding_config=table, param_sharding=ps, param=param, fused_params=cls._table_fused_params(param, ps, fused_params or {}))
-            )
-        return grouped
-
-    @staticmethod
-    def _table_fused_params(param, ps: ParameterSharding, module_fused_params: Dict[str, Any]) -> Dict[str, Any]:
-        """Kernel options of one table: module-level options, overridden by the optimizer attached to the parameter
-        (``apply_optimizer_in_backward``), then by what the plan fixed for this table."""
-        classes = getattr(param, "_optimizer_classes", [None])
-        kwargs = getattr(param, "_optimizer_kwargs", [{}])
-        assert len(classes) == 1 and len(kwargs) == 1, "Only support 1 optimizer per table"
-        from_optimizer = copy.deepcopy(kwargs[0])
-        if classes[0]:
-            from_optimizer["optimizer"] = optimizer_type_to_emb_opt_type(classes[0])
-        merged = merge_fused_params(module_fused_params, from_optimizer)
-        return convert_to_fbgemm_types(add_params_from_parameter_sharding(merged, ps))
-
-    def _pooling_type_to_rs_features(self) -> Dict[str, List[str]]:
-        out: Dict[str, List[str]] = defaultdict(list)
-        for sharding_type, infos in self.sharding_type_to_sharding_infos.items():
-            if sharding_type in (ShardingType.ROW_WISE.value, ShardingType.TABLE_ROW_WISE.value, ShardingType.GRID_SHARD.value):
-                for info in infos:
-                    out[info.embedding_config.pooling.value].extend(info.embedding_config.feature_names)
-        return out
+class ShardedTableStateMixin:
+    """Parameters and checkpoint views of the tables of a sharded embedding module (pooled or unpooled): what
+    ``named_parameters`` / ``state_dict`` / ``load_state_dict`` see.  The module provides ``_TABLE_ATTR``, ``_table_configs()``,
+    ``_sharding_types``, ``_lookups``, ``module_sharding_plan``, ``_env``, ``_device`` and ``_output_dtensor``."""
 
     # ---- torch state: parameters and state dict -----------------------------------------------------
     def _unwrapped_lookups(self):
@@ -532,6 +393,153 @@ class ShardedEmbeddingBagCollection(
                 elif local and tuple(src.shape) == tuple(local[0][1].shape):
                     local[0][1].detach().copy_(src)
             state_dict[key] = getattr(self, self._TABLE_ATTR)[name].weight.detach()
+
+
+
+class ShardedEmbeddingBagCollection(
+    ShardedTableStateMixin,
+    ShardedEmbeddingModule[KJTList, List[torch.Tensor], KeyedTensor, EmbeddingBagCollectionContext],
+    FusedOptimizerModule,
+):
+    """Sharded counterpart of ``EmbeddingBagCollection``; built by ``EmbeddingBagCollectionSharder``."""
+
+    _TABLE_ATTR: str = "embedding_bags"  # name of the ModuleDict that holds ``<table>.weight``
+
+    def _table_configs(self):
+        return self._embedding_bag_configs
+
+    def __init__(
+        self,
+        module: EmbeddingBagCollectionInterface,
+        table_name_to_parameter_sharding: Dict[str, ParameterSharding],
+        env: ShardingEnv,
+        fused_params: Optional[Dict[str, Any]] = None,
+        device: Optional[torch.device] = None,
+        qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None,
+        module_fqn: Optional[str] = None,
+    ) -> None:
+        super().__init__(qcomm_codecs_registry=qcomm_codecs_registry)
+        self._module_fqn = module_fqn
+        self._embedding_bag_configs: List[EmbeddingBagConfig] = module.embedding_bag_configs()
+        self._table_names: List[str] = [c.name for c in self._embedding_bag_configs]
+        self._table_name_to_config: Dict[str, EmbeddingBagConfig] = {c.name: c for c in self._embedding_bag_configs}
+        self.module_sharding_plan: EmbeddingModuleShardingPlan = EmbeddingModuleShardingPlan(
+            {t: ps for t, ps in table_name_to_parameter_sharding.items() if t in self._table_names}
+        )
+        self._env = env
+        self._output_dtensor: bool = env.output_dtensor
+        self.sharding_type_to_sharding_infos = self.create_grouped_sharding_infos(module, table_name_to_parameter_sharding, "embedding_bags.", fused_params)
+        self._sharding_types: List[str] = list(self.sharding_type_to_sharding_infos.keys())
+        self._embedding_shardings: List[EmbeddingSharding] = [
+            create_embedding_bag_sharding(infos, env, device, permute_embeddings=True, qcomm_codecs_registry=self.qcomm_codecs_registry)
+            for infos in self.sharding_type_to_sharding_infos.values()
+        ]
+        self._is_weighted: bool = module.is_weighted()
+        self._device = device
+        self._input_dists: List[nn.Module] = []
+        self._lookups: List[nn.Module] = []
+        self._create_lookups()
+        self._output_dists: List[nn.Module] = []
+        self._embedding_names: List[str] = []
+        self._embedding_dims: List[int] = []
+        self._feature_splits: List[int] = []
+        self._features_order: List[int] = []
+        self._uncombined_embedding_names: List[str] = []
+        self._uncombined_embedding_dims: List[int] = []
+        self._inverse_indices_permute_indices: Optional[torch.Tensor] = None
+        # output order: embeddings come out grouped by sharding type; permute back to table order
+        self._permute_op: Optional[nn.Module] = None
+        self._has_uninitialized_input_dist: bool = True
+        self._has_features_permute: bool = True
+        # lookups that hold data-parallel tables are wrapped in DDP so their dense gradient is all-reduced
+        for i, (sharding, lookup) in enumerate(zip(self._embedding_shardings, self._lookups)):
+            if isinstance(sharding, DpPooledEmbeddingSharding) and env.process_group is not None and dist.get_world_size(env.process_group) >= 1:
+                if dist.get_backend(env.process_group) != "fake":
+                    self._lookups[i] = DistributedDataParallel(
+                        module=lookup, device_ids=[device] if device is not None and device.type == "cuda" else None,
+                        process_group=env.process_group, gradient_as_bucket_view=True, broadcast_buffers=True, static_graph=True,
+                    )
+        self._initialize_torch_state()
+        # optimizer
+        optims = []
+        for lookup in self._lookups:
+            lk = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
+            for _, tbe_module in lk.named_modules():
+                if isinstance(tbe_module, FusedOptimizerModule):
+                    # keys of the fused optimizer are "<table>.weight"; make them "embedding_bags.<table>.weight"
+                    params: Dict[str, Union[torch.Tensor, ShardedTensor]] = {}
+                    for param_key, weight in tbe_module.fused_optimizer.params.items():
+                        params["embedding_bags." + param_key] = weight
+                    tbe_module.fused_optimizer.params = params
+                    optims.append(("", tbe_module.fused_optimizer))
+        self._optim: CombinedOptimizer = CombinedOptimizer(optims)
+        # mean pooling for row-split tables is applied after the reduction
+        self._has_mean_pooling_callback: bool = PoolingType.MEAN.value in self._pooling_type_to_rs_features()
+        # fused sparse engine (peer-memory input dist + lookup + output hand-over): built on the first batch, collectively
+        self._engine_state: str = "auto"  # "auto" -> "on" | "off"
+        self._engine = None
+        self._dim_per_key: Optional[torch.Tensor] = None
+        self._kjt_key_indices: Dict[str, int] = {}
+        self._kt_key_ordering: Optional[torch.Tensor] = None
+
+    # ---- plan -> sharding infos ------------------------------------------------------------------
+    @classmethod
+    def create_grouped_sharding_infos(cls, module, table_name_to_parameter_sharding: Dict[str, ParameterSharding], prefix: str,
+                                      fused_params: Optional[Dict[str, Any]], suffix: Optional[str] = "weight") -> Dict[str, List[EmbeddingShardingInfo]]:
+        """``{sharding type: [one EmbeddingShardingInfo per table]}`` in the order the tables appear in the module.  A feature
+        that feeds two tables gets the embedding name ``feature@table`` so that output columns stay distinguishable."""
+        configs = list(module.embedding_bag_configs())
+        for cfg in configs:
+            cfg.feature_names = cfg.feature_names or [cfg.name]
+        uses: Dict[str, int] = defaultdict(int)
+        for cfg in configs:
+            for f in cfg.feature_names:
+                uses[f] += 1
+        tensors: Dict[str, Any] = dict(module.state_dict())
+        tensors.update(dict(module.named_parameters()))  # parameters win: they carry the optimizer annotations
+        valid_kernels = {k.value for k in EmbeddingComputeKernel}
+        grouped: Dict[str, List[EmbeddingShardingInfo]] = defaultdict(list)
+        for cfg in configs:
+            assert cfg.name in table_name_to_parameter_sharding, f"{cfg.name} not in table_name_to_parameter_sharding"
+            ps = table_name_to_parameter_sharding[cfg.name]
+            if ps.compute_kernel not in valid_kernels:
+                raise ValueError(f"Compute kernel not supported {ps.compute_kernel}")
+            key = prefix + cfg.name + ("" if suffix is None else f".{suffix}")
+            assert key in tensors, f"{key} is neither a parameter nor a state-dict entry of the module"
+            param = tensors[key]
+            table = EmbeddingTableConfig(
+                num_embeddings=cfg.num_embeddings, embedding_dim=cfg.embedding_dim, name=cfg.name, data_type=cfg.data_type,
+                feature_names=list(cfg.feature_names), pooling=cfg.pooling, is_weighted=module.is_weighted(), has_feature_processor=False,
+                embedding_names=[f"{f}@{cfg.name}" if uses[f] > 1 else f for f in cfg.feature_names],
+                weight_init_max=cfg.weight_init_max, weight_init_min=cfg.weight_init_min, init_fn=cfg.init_fn,
+                num_embeddings_post_pruning=getattr(cfg, "num_embeddings_post_pruning", None),
+                total_num_buckets=getattr(cfg, "total_num_buckets", None), use_virtual_table=getattr(cfg, "use_virtual_table", False),
+            )
+            grouped[ps.sharding_type].append(
+                EmbeddingShardingInfo(embedding_config=table, param_sharding=ps, param=param, fused_params=cls._table_fused_params(param, ps, fused_params or {}))
+            )
+        return grouped
+
+    @staticmethod
+    def _table_fused_params(param, ps: ParameterSharding, module_fused_params: Dict[str, Any]) -> Dict[str, Any]:
+        """Kernel options of one table: module-level options, overridden by the optimizer attached to the parameter
+        (``apply_optimizer_in_backward``), then by what the plan fixed for this table."""
+        classes = getattr(param, "_optimizer_classes", [None])
+        kwargs = getattr(param, "_optimizer_kwargs", [{}])
+        assert len(classes) == 1 and len(kwargs) == 1, "Only support 1 optimizer per table"
+        from_optimizer = copy.deepcopy(kwargs[0])
+        if classes[0]:
+            from_optimizer["optimizer"] = optimizer_type_to_emb_opt_type(classes[0])
+        merged = merge_fused_params(module_fused_params, from_optimizer)
+        return convert_to_fbgemm_types(add_params_from_parameter_sharding(merged, ps))
+
+    def _pooling_type_to_rs_features(self) -> Dict[str, List[str]]:
+        out: Dict[str, List[str]] = defaultdict(list)
+        for sharding_type, infos in self.sharding_type_to_sharding_infos.items():
+            if sharding_type in (ShardingType.ROW_WISE.value, ShardingType.TABLE_ROW_WISE.value, ShardingType.GRID_SHARD.value):
+                for info in infos:
+                    out[info.embedding_config.pooling.value].extend(info.embedding_config.feature_names)
+        return out
 
     def reset_parameters(self) -> None:
         if self._device is not None and self._device.type == "meta":

@@ -187,6 +187,66 @@ class EmbeddingCollection(EmbeddingCollectionInterface):
         need_indices: bool = False,
     ) -> None:
         super().__init__()
+        self._embedding_configs = tables
+        self._need_indices: bool = need_indices
+        self._device: torch.device = torch.device("cpu") if device is None else device
+        names = [t.name for t in tables]
+        repeated = [n for n in names if names.count(n) > 1]
+        if repeated:
+            raise ValueError(f"Duplicate table name {repeated[0]}")
+        dims = {t.embedding_dim for t in tables}
+        self._embedding_dim: int = tables[0].embedding_dim if tables else -1
+        if len(dims) > 1:
+            odd = next(t for t in tables if t.embedding_dim != self._embedding_dim)
+            raise ValueError(
+                "All tables in a EmbeddingCollection are required to have same embedding dimension."
+                + f" Violating case: {odd.name}'s embedding_dim {odd.embedding_dim} != {self._embedding_dim}"
+            )
+        self.embeddings: nn.ModuleDict = nn.ModuleDict()
+        for t in tables:
+            t.feature_names = t.feature_names or [t.name]
+            self.embeddings[t.name] = nn.Embedding(t.num_embeddings, t.embedding_dim, device=device,
+                                                   dtype=torch.float32 if t.data_type == DataType.FP32 else data_type_to_dtype(t.data_type))
+        self._embedding_names_by_table: List[List[str]] = get_embedding_names_by_table(tables)
+        self._feature_names: List[List[str]] = [t.feature_names for t in tables]
+        self.reset_parameters()
+
+    def forward(self, features: KeyedJaggedTensor) -> Dict[str, JaggedTensor]:
+        per_feature = features.to_dict()
+        out: Dict[str, JaggedTensor] = {}
+        for table, feats, emb_names in zip(self.embeddings.values(), self._feature_names, self._embedding_names_by_table):
+            for feat, emb_name in zip(feats, emb_names):
+                jt = per_feature[feat]
+                ids = jt.values()
+                out[emb_name] = JaggedTensor(values=table(ids).float(), lengths=jt.lengths(), weights=ids if self._need_indices else None)
+        return out
+
+    def need_indices(self) -> bool:
+        ...
+
+    @abc.abstractmethod
+    def embedding_dim(self) -> int:
+        ...
+
+    @abc.abstractmethod
+    def embedding_names_by_table(self) -> List[List[str]]:
+        ...
+
+
+class EmbeddingCollection(EmbeddingCollectionInterface):
+    """A set of unpooled (sequence) embedding tables; every table has the same dim.
+
+    ``forward(KeyedJaggedTensor) -> Dict[feature, JaggedTensor]`` where each JT holds the
+    looked-up rows ``[sum L, D]`` with the input lengths.
+    """
+
+    def __init__(
+        self,
+        tables: List[EmbeddingConfig],
+        device: Optional[torch.device] = None,
+        need_indices: bool = False,
+    ) -> None:
+        super().__init__()
         self.embeddings: nn.ModuleDict = nn.ModuleDict()
         self._embedding_configs = tables
         self._embedding_dim: int = -1

@@ -272,6 +272,15 @@ class TableBatchedEmbeddingBags(nn.Module):
             self._err = torch.zeros(1, dtype=torch.int32, device=device)
         return self._meta
 
+    def _sr_counter(self) -> Optional[torch.Tensor]:
+        """Device-side call counter that salts stochastic rounding (16-bit tables with ``stochastic_rounding`` on), else None."""
+        if not self.optimizer_args.stochastic_rounding or self.weights.dtype == torch.float32 or not self.weights.is_cuda:
+            return None
+        c = self.__dict__.get("_sr_count")
+        if c is None or c.device != self.weights.device:
+            c = self.__dict__["_sr_count"] = torch.zeros(1, dtype=torch.int64, device=self.weights.device)
+        return c
+
     def split_embedding_weights(self) -> List[torch.Tensor]:
         """Per-table ``[rows, dim]`` views into the flat buffer."""
         return [
@@ -430,7 +439,7 @@ class TableBatchedEmbeddingBags(nn.Module):
                 w, self.momentum1 if self.momentum1.numel() else None, self.momentum2 if self.momentum2.numel() else None,
                 dense_grad, self._meta_tensor(w.device), plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale,
                 grad_out, grad_out.stride(0), B, self.max_D, self.pooling_mode != PoolingMode.NONE, code,
-                o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay, self.step, o.max_gradient, plan.n_valid, bool(o.stochastic_rounding),
+                o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay, self.step, o.max_gradient, plan.n_valid, self._sr_counter(),
             )
             return None if self.fused else dense_grad.to(w.dtype)
         return self._backward_cpu(w, grad_out, indices, offsets, psw, B)
@@ -506,7 +515,7 @@ class TableBatchedEmbeddingBags(nn.Module):
             w, self.momentum1 if self.momentum1.numel() else None, self.momentum2 if self.momentum2.numel() else None, None,
             self._meta_tensor_at(w.device, cols), plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale, grad, grad.stride(0), B,
             self.max_D, True, _OPT_CODE[o.optimizer], o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay, self.step, o.max_gradient,
-            plan.n_valid, bool(o.stochastic_rounding),
+            plan.n_valid, self._sr_counter(),
         )
 
     def _psw_grad(self, grad_out: torch.Tensor, indices: torch.Tensor, offsets: torch.Tensor, B: int) -> torch.Tensor:
