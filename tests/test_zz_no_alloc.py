@@ -135,3 +135,79 @@ def test_noalloc_rejects_oversize():
     rc = fn(ctypes.byref(a), None, err, len(err))
     assert rc == 2
     assert "beyond the fixed scratch" in err.value.decode()
+
+
+def _mem_counters():
+    st = torch.cuda.memory_stats()
+    return st["allocation.all.allocated"], st["segment.all.allocated"], torch.cuda.mem_get_info()[0]
+
+
+def test_noalloc_allocates_nothing_and_covers_wide_rows_half_types_and_long_chains():
+    """bf16 tables with dim 256 and fp16 gradients (the second scratch limit, blocks x dim, is the binding one here), one id
+    repeated far more than 17 x 64 times (a chain that the third pass folds), and allocator counters unchanged across the call."""
+    specs = [(2000, 256)]
+    B = 1024
+    opt = OptimizerArgs(optimizer=EmbOptimType.EXACT_ROWWISE_ADAGRAD, learning_rate=0.05, eps=1e-8, stochastic_rounding=False)
+    fn = _lib()
+    torch.manual_seed(3)
+    a = TableBatchedEmbeddingBags(specs, [0], PoolingMode.SUM, torch.bfloat16, torch.float32, opt, device="cuda")
+    a.init_embedding_weights_uniform(-0.5, 0.5)
+    b = TableBatchedEmbeddingBags(specs, [0], PoolingMode.SUM, torch.bfloat16, torch.float32, opt, device="cuda")
+    with torch.no_grad():
+        b.weights.copy_(a.weights)
+    lengths = torch.full((B,), 8, dtype=torch.int64)
+    idx = torch.randint(0, 2000, (B * 8,))
+    idx[: 3000] = 7  # one hot row: 3000 consecutive sorted entries span about 47 blocks
+    off = torch.cat([torch.zeros(1, dtype=torch.int64), lengths.cumsum(0)]).cuda()
+    plan = a.build_plan(idx.cuda(), off, None, B)
+    grad = torch.randn(B, 256, device="cuda").half()
+    _call_regular(a, plan, grad, B, 1)
+    torch.cuda.synchronize()
+    before = _mem_counters()
+    rc, msg = _call_noalloc(fn, b, plan, grad, B, 1)
+    torch.cuda.synchronize()
+    after = _mem_counters()
+    assert rc == 0, msg
+    assert before[0] == after[0] and before[1] == after[1], "the tensor library's allocator was used"
+    assert after[2] >= before[2] - (1 << 20), "device memory was allocated behind the allocator's back"
+    torch.testing.assert_close(b.weights.float(), a.weights.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(b.momentum1, a.momentum1, rtol=1e-4, atol=1e-6)
+
+
+def test_noalloc_unpooled_matches_operator():
+    specs = [(500, 64)]
+    opt = OptimizerArgs(optimizer=EmbOptimType.EXACT_SGD, learning_rate=0.1)
+    fn = _lib()
+    a = TableBatchedEmbeddingBags(specs, [0], PoolingMode.NONE, torch.float32, torch.float32, opt, device="cuda")
+    a.init_embedding_weights_uniform(-0.5, 0.5)
+    b = TableBatchedEmbeddingBags(specs, [0], PoolingMode.NONE, torch.float32, torch.float32, opt, device="cuda")
+    with torch.no_grad():
+        b.weights.copy_(a.weights)
+    B = 64
+    idx, off = _inputs(specs, [0], B, 9, seed=4)
+    plan = a.build_plan(idx, off, None, B)
+    grad = torch.randn(idx.numel(), 64, device="cuda")
+    _call_regular(a, plan, grad, B, 1)
+    rc, msg = _call_noalloc(fn, b, plan, grad, B, 1)
+    assert rc == 0, msg
+    torch.cuda.synchronize()
+    torch.testing.assert_close(b.weights, a.weights, rtol=1e-5, atol=1e-6)
+
+
+def test_noalloc_rejects_second_limit_and_bad_arguments():
+    fn = _lib()
+    dummy = torch.zeros(8, device="cuda")
+    err = ctypes.create_string_buffer(512)
+    # N is below the entry limit, but ceil(N / 64) * max_D exceeds the block x dim limit
+    a = _Args(N=200000, B=1, F=1, max_D=1024, pooled=1)
+    for name in ("weights", "meta", "sorted_keys", "sorted_src", "grad"):
+        setattr(a, name, dummy.data_ptr())
+    assert fn(ctypes.byref(a), None, err, len(err)) == 2
+    # a missing mandatory pointer and an unknown dtype code are argument errors, nothing is launched
+    a = _Args(N=64, B=1, F=1, max_D=128, pooled=1)
+    for name in ("meta", "sorted_keys", "sorted_src", "grad"):
+        setattr(a, name, dummy.data_ptr())
+    assert fn(ctypes.byref(a), None, err, len(err)) == 1
+    a.weights = dummy.data_ptr()
+    a.weights_dtype = 9
+    assert fn(ctypes.byref(a), None, err, len(err)) == 1

@@ -72,6 +72,8 @@ struct DistParams {
   PeerPtrs recv_len;   // int32 [J_max, W, B]
   PeerPtrs recv_val;   // ids [cap]
   PeerPtrs recv_w;     // float [cap] or null
+  PeerPtrs recv_ret;   // int64 [cap] or null: (source rank << 32 | position of the id in the source's KJT), for unpooled lookups
+  int has_ret;
   int64_t cap;
   long long wait_cycles;
 };
@@ -261,6 +263,10 @@ __global__ void __launch_bounds__(256) kjt_dist_scatter_kernel(DistParams p) {
           float* wout = reinterpret_cast<float*>(p.recv_w.p[d]) + dst;
           for (int64_t i = tid; i < src1 - src0; i += blockDim.x) wout[i] = p.weights[src0 + i];
         }
+        if (p.has_ret) {
+          int64_t* rout = reinterpret_cast<int64_t*>(p.recv_ret.p[d]) + dst;
+          for (int64_t i = tid; i < src1 - src0; i += blockDim.x) rout[i] = (int64_t(p.rank) << 32) | (src0 + i);
+        }
         int32_t* lout = reinterpret_cast<int32_t*>(p.recv_len.p[d]) + (int64_t(j) * p.W + p.rank) * p.B;
         for (int b = b0 + tid; b < b1; b += blockDim.x)
           lout[b] = int32_t(load_off(p.offsets, int64_t(f) * p.B + b + 1, p.off64) - load_off(p.offsets, int64_t(f) * p.B + b, p.off64));
@@ -336,6 +342,7 @@ __global__ void __launch_bounds__(256) kjt_dist_scatter_kernel(DistParams p) {
             const int64_t dst = s_base[sk] + s_off[sk][bi] + pos;
             reinterpret_cast<idx_t*>(p.recv_val.p[s_dest[sk]])[dst] = idx_t(id - s_lo[sk]);
             if (p.weights) reinterpret_cast<float*>(p.recv_w.p[s_dest[sk]])[dst] = p.weights[i0 + lane];
+            if (p.has_ret) reinterpret_cast<int64_t*>(p.recv_ret.p[s_dest[sk]])[dst] = (int64_t(p.rank) << 32) | (i0 + lane);
           }
         }
       }
@@ -433,6 +440,22 @@ __global__ void __launch_bounds__(256) grad_publish_kernel(const void* __restric
   }
 }
 
+// Sequence (unpooled) output: rows [0, n) of the peer-written buffer become a fresh tensor of the module's output dtype.  The
+// copy frees the shared buffer for the next step and, like the pooled finalize, turns the result into NaN when a wait ran
+// out in this step.
+__global__ void __launch_bounds__(256) seq_finalize_kernel(const void* __restrict__ staging, int st_dtype, int64_t st_stride,
+                                                           void* __restrict__ out, int out_dtype, int64_t n, int cols,
+                                                           const int* __restrict__ err) {
+  const int per_row = (cols + 3) / 4;
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n * per_row) return;
+  const int64_t r = i / per_row;
+  const int e = int(i - r * per_row) * 4;
+  float4 v = load4_dyn(staging, r * st_stride + e, st_dtype);
+  if (*err != 0) v.x = v.y = v.z = v.w = __int_as_float(0x7fc00000);
+  store4_dyn(out, r * cols + e, v, out_dtype);
+}
+
 // ---- host side -----------------------------------------------------------------------------------------------------
 static void fill_peers(PeerPtrs& dst, const std::vector<int64_t>& ptrs, int world) {
   TORCH_CHECK(int(ptrs.size()) == world, "one pointer per rank expected");
@@ -452,8 +475,8 @@ static DistParams make_params(int64_t rank, int64_t B, const std::vector<at::Ten
                               const std::vector<at::Tensor>& scratch, const at::Tensor& values, const at::Tensor& offsets,
                               const c10::optional<at::Tensor>& weights, const std::vector<int64_t>& flag_ptrs,
                               const std::vector<int64_t>& size_ptrs, const std::vector<int64_t>& len_ptrs,
-                              const std::vector<int64_t>& val_ptrs, const std::vector<int64_t>& w_ptrs, int64_t cap,
-                              int64_t wait_cycles, at::Tensor& err) {
+                              const std::vector<int64_t>& val_ptrs, const std::vector<int64_t>& w_ptrs,
+                              const std::vector<int64_t>& ret_ptrs, int64_t cap, int64_t wait_cycles, at::Tensor& err) {
   TORCH_CHECK(topo.size() == 6 && rows.size() == 2 && scratch.size() == 4);
   for (const auto& t : topo) TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous());
   for (const auto& t : rows) TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kLong && t.is_contiguous());
@@ -497,6 +520,9 @@ static DistParams make_params(int64_t rank, int64_t B, const std::vector<at::Ten
   fill_peers(p.recv_val, val_ptrs, p.W);
   if (weighted) fill_peers(p.recv_w, w_ptrs, p.W);
   else for (int i = 0; i < kMaxPeers; ++i) p.recv_w.p[i] = nullptr;
+  p.has_ret = ret_ptrs.empty() ? 0 : 1;
+  if (p.has_ret) fill_peers(p.recv_ret, ret_ptrs, p.W);
+  else for (int i = 0; i < kMaxPeers; ++i) p.recv_ret.p[i] = nullptr;
   p.cap = cap;
   p.wait_cycles = (long long)wait_cycles;
   return p;
@@ -507,11 +533,11 @@ static DistParams make_params(int64_t rank, int64_t B, const std::vector<at::Ten
 void kjt_dist_send(int64_t phase, int64_t rank, int64_t B, std::vector<at::Tensor> topo, std::vector<at::Tensor> rows,
                    std::vector<at::Tensor> scratch, const at::Tensor& values, const at::Tensor& offsets,
                    const c10::optional<at::Tensor>& weights, std::vector<int64_t> flag_ptrs, std::vector<int64_t> size_ptrs,
-                   std::vector<int64_t> len_ptrs, std::vector<int64_t> val_ptrs, std::vector<int64_t> w_ptrs, int64_t cap,
-                   int64_t wait_cycles, at::Tensor err) {
+                   std::vector<int64_t> len_ptrs, std::vector<int64_t> val_ptrs, std::vector<int64_t> w_ptrs,
+                   std::vector<int64_t> ret_ptrs, int64_t cap, int64_t wait_cycles, at::Tensor err) {
   c10::cuda::CUDAGuard guard(values.device());
   DistParams p = make_params(rank, B, topo, rows, scratch, values, offsets, weights, flag_ptrs, size_ptrs, len_ptrs, val_ptrs,
-                             w_ptrs, cap, wait_cycles, err);
+                             w_ptrs, ret_ptrs, cap, wait_cycles, err);
   auto stream = at::cuda::getCurrentCUDAStream();
   const bool i64 = values.scalar_type() == at::kLong;
   if (phase == 0) {
@@ -571,6 +597,19 @@ at::Tensor pooled_finalize(const at::Tensor& staging, int64_t st_stride, const a
   return out;
 }
 
+at::Tensor seq_finalize(const at::Tensor& staging, int64_t n, at::ScalarType out_dtype, const at::Tensor& err) {
+  TORCH_CHECK(staging.is_cuda() && staging.dim() == 2 && staging.is_contiguous() && n <= staging.size(0) && staging.size(1) % 4 == 0);
+  c10::cuda::CUDAGuard guard(staging.device());
+  const int cols = int(staging.size(1));
+  at::Tensor out = at::empty({n, cols}, staging.options().dtype(out_dtype));
+  if (n == 0) return out;
+  const int64_t work = n * ((cols + 3) / 4);
+  seq_finalize_kernel<<<(work + 255) / 256, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      staging.data_ptr(), dtype_code(staging.scalar_type()), cols, out.data_ptr(), dtype_code(out_dtype), n, cols, err.data_ptr<int>());
+  TRB_CUDA_CHECK(cudaGetLastError());
+  return out;
+}
+
 void grad_publish(const at::Tensor& grad, std::vector<int64_t> slab_ptrs, at::ScalarType slab_dtype, int64_t slab_stride, int64_t rank,
                   const at::Tensor& gseg, const at::Tensor& kjt_offsets, const at::Tensor& feat_pos, double scale) {
   TORCH_CHECK(grad.is_cuda() && grad.dim() == 2 && grad.stride(1) == 1);
@@ -596,7 +635,7 @@ void grad_publish(const at::Tensor& grad, std::vector<int64_t> slab_ptrs, at::Sc
 TORCH_LIBRARY_FRAGMENT(trb200, m) {
   m.def(
       "kjt_dist_send(int phase, int rank, int B, Tensor[] topo, Tensor[] rows, Tensor[] scratch, Tensor values, Tensor offsets, "
-      "Tensor? weights, int[] flag_ptrs, int[] size_ptrs, int[] len_ptrs, int[] val_ptrs, int[] w_ptrs, int cap, int wait_cycles, "
+      "Tensor? weights, int[] flag_ptrs, int[] size_ptrs, int[] len_ptrs, int[] val_ptrs, int[] w_ptrs, int[] ret_ptrs, int cap, int wait_cycles, "
       "Tensor(a!) err) -> ()");
   m.def(
       "kjt_dist_recv_offsets(Tensor recv_len, int n, bool out64, int[] flag_ptrs, int rank, Tensor epochs, int wait_cycles, "
@@ -604,6 +643,7 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
   m.def(
       "pooled_finalize(Tensor staging, int st_stride, Tensor seg, int B, int out_cols, ScalarType out_dtype, Tensor kjt_offsets, "
       "Tensor feat_pos, Tensor err) -> Tensor");
+  m.def("seq_finalize(Tensor staging, int n, ScalarType out_dtype, Tensor err) -> Tensor");
   m.def(
       "grad_publish(Tensor grad, int[] slab_ptrs, ScalarType slab_dtype, int slab_stride, int rank, Tensor gseg, Tensor kjt_offsets, "
       "Tensor feat_pos, float scale) -> ()");
@@ -614,4 +654,5 @@ TORCH_LIBRARY_IMPL(trb200, CompositeExplicitAutograd, m) {
   m.impl("kjt_dist_recv_offsets", &trb::kjt_dist_recv_offsets);
   m.impl("pooled_finalize", &trb::pooled_finalize);
   m.impl("grad_publish", &trb::grad_publish);
+  m.impl("seq_finalize", &trb::seq_finalize);
 }

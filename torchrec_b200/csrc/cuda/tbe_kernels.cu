@@ -201,6 +201,65 @@ __global__ void __launch_bounds__(256) tbe_seq_fwd_kernel(FwdParams p, int64_t N
   }
 }
 
+// Unpooled lookup whose ids arrived through the fused input distribution: id k of the receive buffer carries a return
+// address `ret[k]` = (requesting rank << 32 | position of the id in that rank's KJT), and its row is stored straight into
+// row `position` of the requester's output buffer (peer-mapped), at this table's output column.  This is the sequence
+// all-to-all folded into the lookup.  Only positions [offsets[0], offsets[F * B]) of the buffer belong to this module.
+template <typename emb_t, typename idx_t, int kVecs>
+__global__ void __launch_bounds__(256) tbe_seq_fwd_dist_kernel(FwdParams p, const int64_t* __restrict__ ret, int64_t out_rows, int nranks) {
+  const int lane = threadIdx.x & 31;
+  const idx_t* offsets = reinterpret_cast<const idx_t*>(p.offsets);
+  const idx_t* indices = reinterpret_cast<const idx_t*>(p.indices);
+  const int F = p.F;
+  const int64_t B = p.B;
+  const int64_t first = int64_t(offsets[0]), last = int64_t(offsets[int64_t(F) * B]);
+  const int64_t i0 = first + ((int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * kSeqPer;
+  if (i0 >= last) return;
+  const int cnt = int(min(int64_t(kSeqPer), last - i0));
+  int64_t my_idx = 0, my_ret = 0;
+  if (lane < cnt) {
+    my_idx = int64_t(indices[i0 + lane]);
+    my_ret = ret[i0 + lane];
+  }
+  int lo = 0, hi = F;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (int64_t(offsets[int64_t(mid) * B]) <= i0) lo = mid; else hi = mid;
+  }
+  int f = lo;
+  int64_t f_end = int64_t(offsets[int64_t(f + 1) * B]);
+  for (int j = 0; j < cnt; ++j) {
+    const int64_t i = i0 + j;
+    while (i >= f_end && f + 1 < F) {
+      ++f;
+      f_end = int64_t(offsets[int64_t(f + 1) * B]);
+    }
+    const int D = int(p.meta[M_DIM * F + f]);
+    const int64_t rows = p.meta[M_ROWS * F + f];
+    const int64_t col = p.meta[M_OUTOFF * F + f];
+    const emb_t* w = reinterpret_cast<const emb_t*>(p.weights) + p.meta[M_WOFF * F + f];
+    const int64_t r = __shfl_sync(0xffffffffu, my_idx, j);
+    const int64_t ra = __shfl_sync(0xffffffffu, my_ret, j);
+    const bool rok = r >= 0 && r < rows;
+    if (!rok && lane == 0) atomicExch(p.err, 1);
+    const int64_t dst_rank = ra >> 32, dst_row = ra & 0xffffffffLL;
+    if (dst_rank < 0 || dst_rank >= nranks || dst_row >= out_rows) {  // never store outside a peer's buffer
+      if (lane == 0) atomicExch(p.err, 2);
+      continue;
+    }
+    void* base = p.out.p[int(dst_rank)];
+    const int64_t row_e = dst_row * p.out_stride + col;
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+      const int e = v * 128 + lane * 4;
+      if (e < D) {
+        float4 x = rok ? Vec4<emb_t>::load(w + r * D + e) : f4zero();
+        store4_dyn(base, row_e + e, x, p.out_dtype);
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // backward
 // ------------------------------------------------------------------------------------------------
@@ -240,6 +299,8 @@ struct BwdParams {
   // pooled gradients that live on peer ranks (fused exchange): bag b of the global batch is row b % B_local of
   // rank b / B_local.  B_local == 0: all gradient rows are in `grad`.
   PeerPtrs grad_peers;
+  const int64_t* ret;  // unpooled, fused exchange: return address of every received id (see tbe_seq_fwd_dist_kernel); gradient rows
+                       // are pulled from row `position` of the requesting rank's gradient buffer
   int B_local;
   float grad_scale;  // factor on every gradient row (1 / world size when gradients are averaged over ranks)
   OptParams opt;
@@ -554,7 +615,14 @@ __global__ void __launch_bounds__(256, kVecs == 1 ? 4 : 2) tbe_bwd_block_kernel(
         if (p.bag_scale) w *= p.bag_scale[src];
       } else {
         f = p.src_feature[src];
-        goff = int64_t(src) * p.grad_stride;
+        if (p.ret != nullptr) {
+          const int64_t ra = p.ret[src];
+          gsrc = reinterpret_cast<const char*>(p.grad_peers.p[int(ra >> 32)]);
+          local_grad = gsrc == gbase;
+          goff = (ra & 0xffffffffLL) * p.grad_stride + meta[M_OUTOFF * F + f];
+        } else {
+          goff = int64_t(src) * p.grad_stride;
+        }
       }
       w *= p.grad_scale;
       const int D = int(meta[M_DIM * F + f]);
@@ -1027,7 +1095,8 @@ static void tbe_backward_apply_impl(at::Tensor weights, c10::optional<at::Tensor
                                     double beta2, double weight_decay, int64_t step, double max_grad,
                                     const std::vector<int64_t>& grad_ptrs, int64_t B_local, double grad_scale,
                                     const c10::optional<at::Tensor>& n_valid = c10::nullopt,
-                                    const c10::optional<at::Tensor>& sr_counter = c10::nullopt) {
+                                    const c10::optional<at::Tensor>& sr_counter = c10::nullopt,
+                                    const c10::optional<at::Tensor>& ret = c10::nullopt) {
   const int64_t N = sorted_keys.numel();
   if (N == 0) return;
   c10::cuda::CUDAGuard guard(weights.device());
@@ -1067,7 +1136,13 @@ static void tbe_backward_apply_impl(at::Tensor weights, c10::optional<at::Tensor
   p.B_local = 0;
   p.grad_scale = float(grad_scale);
   for (int i = 0; i < kMaxPeers; ++i) p.grad_peers.p[i] = nullptr;
-  if (!grad_ptrs.empty()) {
+  p.ret = nullptr;
+  if (ret.has_value() && ret->defined()) {
+    TORCH_CHECK(!pooled && !grad_ptrs.empty() && grad_ptrs.size() <= size_t(kMaxPeers), "return addresses serve the unpooled peer backward");
+    TORCH_CHECK(ret->scalar_type() == at::kLong && ret->is_contiguous() && ret->numel() >= N);
+    p.ret = ret->data_ptr<int64_t>();
+    for (size_t i = 0; i < grad_ptrs.size(); ++i) p.grad_peers.p[i] = reinterpret_cast<void*>(grad_ptrs[i]);
+  } else if (!grad_ptrs.empty()) {
     TORCH_CHECK(pooled && B_local > 0 && int64_t(grad_ptrs.size()) * B_local == B && grad_ptrs.size() <= size_t(kMaxPeers),
                 "peer gradients: B must be world * B_local");
     p.B_local = int(B_local);
@@ -1129,10 +1204,57 @@ void tbe_backward_apply_dist(at::Tensor weights, c10::optional<at::Tensor> mom1,
                              int64_t max_D, bool pooled, int64_t opt_type, double lr, double eps, double beta1,
                              double beta2, double weight_decay, int64_t step, double max_grad,
                              std::vector<int64_t> grad_ptrs, int64_t B_local, double grad_scale,
-                             c10::optional<at::Tensor> n_valid) {
+                             c10::optional<at::Tensor> n_valid, c10::optional<at::Tensor> ret,
+                             c10::optional<at::Tensor> sr_counter) {
   tbe_backward_apply_impl(weights, mom1, mom2, dense_grad, meta, sorted_keys, sorted_src, sorted_w, src_feature, bag_scale, grad,
                           grad_stride, B, max_D, pooled, opt_type, lr, eps, beta1, beta2, weight_decay, step, max_grad, grad_ptrs,
-                          B_local, grad_scale, n_valid);
+                          B_local, grad_scale, n_valid, sr_counter, ret);
+}
+
+// Unpooled forward of the fused exchange: row of id k goes to row (ret[k] & 0xffffffff) of the output buffer of rank
+// ret[k] >> 32, at the table's output column.  `indices` / `ret` are receive buffers of fixed capacity; `offsets` (F*B+1
+// entries, absolute positions in them) delimits this module's ids.
+void tbe_seq_forward_dist(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets,
+                          const at::Tensor& ret, std::vector<int64_t> out_ptrs, int64_t out_rows, int64_t out_dtype, int64_t out_stride,
+                          int64_t B, int64_t max_D, at::Tensor err) {
+  const int F = int(meta.size(1));
+  TORCH_CHECK(meta.size(0) == kMetaRows && meta.scalar_type() == at::kLong && meta.is_contiguous());
+  TORCH_CHECK(indices.scalar_type() == offsets.scalar_type(), "indices and offsets must share a dtype");
+  TORCH_CHECK(offsets.numel() == int64_t(F) * B + 1, "offsets must have F*B+1 entries");
+  TORCH_CHECK(ret.scalar_type() == at::kLong && ret.numel() >= indices.numel());
+  TORCH_CHECK(!out_ptrs.empty() && out_ptrs.size() <= size_t(kMaxPeers));
+  const int64_t cap = indices.numel();
+  if (F == 0 || B == 0 || cap == 0) return;
+  c10::cuda::CUDAGuard guard(weights.device());
+  FwdParams p;
+  p.weights = weights.data_ptr();
+  p.meta = meta.data_ptr<int64_t>();
+  p.indices = indices.data_ptr();
+  p.offsets = offsets.data_ptr();
+  p.psw = nullptr;
+  for (size_t i = 0; i < out_ptrs.size(); ++i) p.out.p[i] = reinterpret_cast<void*>(out_ptrs[i]);
+  p.out_dtype = int(out_dtype);
+  p.out_stride = out_stride;
+  p.B = int(B);
+  p.B_local = int(B);
+  p.F = F;
+  p.pooling = POOL_NONE;
+  p.accumulate = 0;
+  p.skip_empty = 0;
+  p.err = err.data_ptr<int>();
+  const int threads = 256;
+  const int64_t blocks = ((cap + kSeqPer - 1) / kSeqPer * 32 + threads - 1) / threads;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int nv = vecs_for_dim(max_D);
+  const bool i64 = indices.scalar_type() == at::kLong;
+  const int64_t* rp = ret.data_ptr<int64_t>();
+  TRB_DISPATCH_EMB(weights.scalar_type(), [&] {
+    TRB_DISPATCH_VECS(nv, [&] {
+      if (i64) tbe_seq_fwd_dist_kernel<emb_t, int64_t, kVecs><<<blocks, threads, 0, stream>>>(p, rp, out_rows, int(out_ptrs.size()));
+      else tbe_seq_fwd_dist_kernel<emb_t, int32_t, kVecs><<<blocks, threads, 0, stream>>>(p, rp, out_rows, int(out_ptrs.size()));
+    });
+  });
+  TRB_CUDA_CHECK(cudaGetLastError());
 }
 
 }  // namespace trb
@@ -1254,6 +1376,7 @@ extern "C" int trb_tbe_backward_apply_noalloc(const trb_tbe_bwd_noalloc_args* a,
   p.bag_scale = a->bag_scale;
   p.N = a->N;
   p.n_valid = nullptr;
+  p.ret = nullptr;
   p.B = a->B;
   p.F = a->F;
   p.pooled = a->pooled ? 1 : 0;
@@ -1312,7 +1435,11 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
       "tbe_backward_apply_dist(Tensor(a!) weights, Tensor(b!)? mom1, Tensor(c!)? mom2, Tensor(d!)? dense_grad, Tensor meta, "
       "Tensor sorted_keys, Tensor sorted_src, Tensor sorted_w, Tensor src_feature, Tensor bag_scale, Tensor grad, "
       "int grad_stride, int B, int max_D, bool pooled, int opt_type, float lr, float eps, float beta1, float beta2, "
-      "float weight_decay, int step, float max_grad, int[] grad_ptrs, int B_local, float grad_scale, Tensor? n_valid) -> ()");
+      "float weight_decay, int step, float max_grad, int[] grad_ptrs, int B_local, float grad_scale, Tensor? n_valid, "
+      "Tensor? ret=None, Tensor(e!)? sr_counter=None) -> ()");
+  m.def(
+      "tbe_seq_forward_dist(Tensor weights, Tensor meta, Tensor indices, Tensor offsets, Tensor ret, int[] out_ptrs, "
+      "int out_rows, int out_dtype, int out_stride, int B, int max_D, Tensor(a!) err) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(trb200, CUDA, m) {
@@ -1320,6 +1447,7 @@ TORCH_LIBRARY_IMPL(trb200, CUDA, m) {
   m.impl("tbe_build_plan", &trb::tbe_build_plan);
   m.impl("tbe_backward_apply", &trb::tbe_backward_apply);
   m.impl("tbe_backward_apply_dist", &trb::tbe_backward_apply_dist);
+  m.impl("tbe_seq_forward_dist", &trb::tbe_seq_forward_dist);
 }
 
 TORCH_LIBRARY_IMPL(trb200, CompositeExplicitAutograd, m) { m.impl("tbe_forward_dist", &trb::tbe_forward_dist); }

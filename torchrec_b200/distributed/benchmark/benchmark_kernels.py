@@ -116,9 +116,133 @@ def bench_tbe(B: int, row_cap: int, which: str, n: int, warm: int) -> None:
     m.check_error()
 
 
+def bench_tbe_uniform(B: int, n: int, warm: int) -> None:
+    """Pooled lookup with UNIFORM ids over tables far larger than L2 (4 tables x 2M rows x 512 B = 4 GiB): every id is a DRAM
+    row fetch, so gathered bytes / time is a DRAM figure (the Zipf case above is partly served from L2)."""
+    from torchrec_b200.modules.embedding_configs import PoolingMode
+    from torchrec_b200.ops.tbe import EmbOptimType, OptimizerArgs, TableBatchedEmbeddingBags
+
+    rows, pf = 2_000_000, 8
+    m = TableBatchedEmbeddingBags([(rows, 128)] * 4, pooling_mode=PoolingMode.SUM, output_dtype=torch.bfloat16,
+                                  optimizer_args=OptimizerArgs(EmbOptimType.EXACT_ROWWISE_ADAGRAD, 0.005), device="cuda")
+    m.init_embedding_weights_uniform(-0.01, 0.01)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    idx = torch.randint(0, rows, (4 * B * pf,), device="cuda", generator=g, dtype=torch.int32)
+    off = (torch.arange(4 * B + 1, device="cuda", dtype=torch.int64) * pf).to(torch.int32)
+    N = idx.numel()
+    with torch.no_grad():
+        t = timeit(lambda: m(idx, off), n, warm)
+    print(f"tbe fwd uniform ids: {N} ids, {t:.3f} ms, {N * 512 / t / 1e6:.0f} GB/s of rows from DRAM (+ {B * 4 * 256 / t / 1e6:.0f} GB/s output)", flush=True)
+    grad = torch.randn(B, 4 * 128, device="cuda").bfloat16()
+    plan = m.build_plan(idx, off, None, B)
+    uniq = int(torch.unique(plan.keys).numel())
+    t = timeit(lambda: m._backward_impl(grad, idx, off, None, B, plan), n, warm)
+    byt = uniq * 128 * 4 * 2 + N * 256  # row read + write per unique row, one bf16 gradient row slice per id
+    print(f"tbe bwd uniform ids: unique rows {uniq}, {t:.3f} ms, algorithmic traffic {byt / 1e9:.2f} GB -> {byt / t / 1e6:.0f} GB/s", flush=True)
+
+
+def bench_qtbe(B: int, n: int, warm: int) -> None:
+    """int8 / int4 row-wise quantized pooled lookup (inference)."""
+    from torchrec_b200.modules.embedding_configs import PoolingMode
+    from torchrec_b200.ops.qtbe import QuantTableBatchedEmbeddingBags
+
+    rows, pf = 4_000_000, 8
+    for bits in (8, 4):
+        m = QuantTableBatchedEmbeddingBags([(rows, 128, bits)] * 4, pooling_mode=PoolingMode.SUM, output_dtype=torch.float16, device=torch.device("cuda"))
+        m.weights.random_(0, 255)  # arbitrary row bytes: the kernel's traffic does not depend on the values
+        idx = torch.randint(0, rows, (4 * B * pf,), device="cuda", dtype=torch.int32)
+        off = (torch.arange(4 * B + 1, device="cuda", dtype=torch.int64) * pf).to(torch.int32)
+        t = timeit(lambda: m(idx, off), n, warm)
+        row_bytes = 128 * bits // 8 + 4
+        print(f"qtbe fwd int{bits}: {idx.numel()} ids, {t:.3f} ms, {idx.numel() * row_bytes / t / 1e6:.0f} GB/s of quantized rows", flush=True)
+
+
+def bench_dense_small(M: int, n: int, warm: int) -> None:
+    """Dot interaction forward / backward, the fused cross-layer backward pass and the one-launch dense optimizer."""
+    ops = torch.ops.trb200
+    dense = torch.randn(M, 128, device="cuda").bfloat16()
+    sparse = torch.randn(M, 26, 128, device="cuda").bfloat16()
+    t = timeit(lambda: ops.dot_interaction_fwd(dense, sparse), n, warm)
+    out = ops.dot_interaction_fwd(dense, sparse)
+    byt = (dense.numel() + sparse.numel() + out.numel()) * 2
+    print(f"dot fwd M={M}: {t:.3f} ms, {byt / t / 1e6:.0f} GB/s", flush=True)
+    dout = torch.randn_like(out)
+    t = timeit(lambda: ops.dot_interaction_bwd(dout, dense, sparse), n, warm)
+    print(f"dot bwd M={M}: {t:.3f} ms, {(2 * (dense.numel() + sparse.numel()) + out.numel()) * 2 / t / 1e6:.0f} GB/s", flush=True)
+    D = 3456
+    dy, x0, u = (torch.randn(M, D, device="cuda").bfloat16() for _ in range(3))
+    acc = torch.randn(M, D, device="cuda").bfloat16()
+    t = timeit(lambda: ops.cross_bwd_fused(dy, x0, u, acc, False), n, warm)
+    print(f"cross bwd fused M={M} D={D}: {t:.3f} ms, {6 * M * D * 2 / t / 1e6:.0f} GB/s (4 reads + 2 writes)", flush=True)
+    from torchrec_b200.optim.fused_dense import FusedDenseOptimizer
+
+    params = [torch.nn.Parameter(torch.randn(r, c, device="cuda")) for r, c in ((1024, 3456), (3456, 512), (512, 3456), (1024, 1024), (512, 1024))]
+    opt = FusedDenseOptimizer(params, "adagrad", lr=0.01)
+    opt.buffer.grad.normal_()
+    t = timeit(lambda: opt.step(), n, warm)
+    nel = sum(p.numel() for p in params)
+    print(f"dense optimizer (Adagrad + bf16 copies) {nel} elements: {t:.3f} ms, {nel * (4 * 5 + 2 * 2) / t / 1e6:.0f} GB/s", flush=True)
+
+
+def bench_sparse_kernels(B: int, n: int, warm: int) -> None:
+    """Row-wise bucketization and the 2-D jagged permute of the library-collective input distribution."""
+    from torchrec_b200.ops import sparse_ops as sops
+
+    F, pf, rows, W = 26, 8, 4_000_000, 8
+    lengths = torch.full((F * B,), pf, dtype=torch.int32, device="cuda")
+    idx = torch.randint(0, rows, (F * B * pf,), device="cuda", dtype=torch.int64)
+    block = torch.full((F,), (rows + W - 1) // W, dtype=torch.int64, device="cuda")
+    t = timeit(lambda: sops.block_bucketize_sparse_features(lengths, idx, bucketize_pos=False, sequence=False, block_sizes=block, my_size=W), n, warm)
+    print(f"block bucketize {idx.numel()} ids into {W} buckets: {t:.3f} ms, {idx.numel() * 16 / t / 1e6:.0f} GB/s (read + write ids)", flush=True)
+    perm = torch.randperm(F, device="cuda").to(torch.int32)
+    t = timeit(lambda: sops.permute_2D_sparse_data(perm, lengths.view(F, B), idx, None, idx.numel()), n, warm)
+    print(f"permute 2-D jagged {idx.numel()} ids: {t:.3f} ms, {idx.numel() * 16 / t / 1e6:.0f} GB/s", flush=True)
+
+
+def bench_engine(B: int, n: int, warm: int) -> None:
+    """The fused sparse engine's own kernels with two virtual ranks on this GPU (every phase runs for both ranks before the next
+    one, so nothing waits): id scatter, finalize, gradient publish.  Local memory stands in for the peer's, so these are the
+    kernels' HBM-side figures, not NVLink ones."""
+    import sys
+
+    sys.path.insert(0, "tests")
+    from test_fused_sparse_engine_gpu import _build, _kjt  # the virtual-rank harness of the tests
+
+    kinds = ["rw", "tw", "tw", "cw"]
+    tables, engines, _, _ = _build(2, kinds, [128, 128, 128, 128], [1_000_000, 500_000, 200_000, 100_000], ["sum"] * 4, stage_dtype=torch.float16, grad_dtype=torch.bfloat16)
+    kjts = [_kjt(tables, B, 16, r, idx_dtype=torch.int32) for r in range(2)]
+    for e, k in zip(engines, kjts):
+        e.prepare(k)
+    for e in engines:
+        e.prepare_finish()
+    grads = [torch.randn(B, 512, device="cuda").bfloat16() for _ in range(2)]
+
+    def step():
+        hs = [e.new_handle(k) for e, k in zip(engines, kjts)]
+        for ph in (0, 1):
+            for e, h in zip(engines, hs):
+                e.phase_send(h, ph)
+        for e, h in zip(engines, hs):
+            e.phase_push(h, build_plans=True)
+        for e, h in zip(engines, hs):
+            e.phase_finalize(h)
+        for e, h, g in zip(engines, hs, grads):
+            e.phase_publish(h, g, 1.0)
+        for e, h in zip(engines, hs):
+            e.phase_pull(h)
+
+    t = timeit(step, n, warm)
+    ids = sum(int(k.values().numel()) for k in kjts)
+    print(f"engine step, 2 virtual ranks, B={B}/rank, {ids} ids: {t:.3f} ms for both ranks", flush=True)
+    for e in engines:
+        e.peer.check_error()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm_nt", "gemm_tn", "gemm_cross", "tbe", "tbe_fwd", "tbe_sort", "tbe_bwd"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm_nt", "gemm_tn", "gemm_cross", "tbe", "tbe_fwd", "tbe_sort", "tbe_bwd",
+                                                       "tbe_uniform", "qtbe", "dense_small", "sparse", "engine"])
+    ap.add_argument("--shape", type=str, default="", help="N,K: run the GEMM benchmarks on this one shape only (profiler captures)")
     ap.add_argument("--small", action="store_true", help="profiler-sized case: few launches, a few GB on the device")
     ap.add_argument("--batch", type=int, default=65536)
     ap.add_argument("--row-cap", type=int, default=4000000)
@@ -129,14 +253,25 @@ def main() -> None:
     M = 16384 if args.small else args.batch
     n, warm = (2, 1) if args.small else (10, 3)
     row_cap = min(args.row_cap, 200000) if args.small else args.row_cap
+    one = [tuple(int(x) for x in args.shape.split(","))] if args.shape else None
     if args.op in ("all", "gemm_nt"):
-        bench_gemm_nt(M, [(512, 3456), (3456, 512), (1024, 3456), (1024, 1024), (512, 1024), (256, 512), (128, 256)], n, warm)
+        bench_gemm_nt(M, one or [(512, 3456), (3456, 512), (1024, 3456), (1024, 1024), (512, 1024), (256, 512), (128, 256)], n, warm)
     if args.op in ("all", "gemm_cross"):
         bench_gemm_cross(M, 3456, 512, n, warm)
     if args.op in ("all", "gemm_tn"):
-        bench_gemm_tn(M, [(512, 3456), (3456, 512), (1024, 3456), (1024, 1024), (512, 1024), (256, 512)], n, warm)
+        bench_gemm_tn(M, one or [(512, 3456), (3456, 512), (1024, 3456), (1024, 1024), (512, 1024), (256, 512)], n, warm)
     if args.op in ("all", "tbe", "tbe_fwd", "tbe_sort", "tbe_bwd"):
         bench_tbe(M, row_cap, args.op, n, warm)
+    if args.op in ("all", "tbe_uniform"):
+        bench_tbe_uniform(M, n, warm)
+    if args.op in ("all", "qtbe"):
+        bench_qtbe(M, n, warm)
+    if args.op in ("all", "dense_small"):
+        bench_dense_small(M, n, warm)
+    if args.op in ("all", "sparse"):
+        bench_sparse_kernels(M, n, warm)
+    if args.op in ("all", "engine"):
+        bench_engine(M // 4, n, warm)
     print("gemm status", int(torch.ops.trb200.gemm_error_status()), flush=True)
 
 

@@ -1,8 +1,8 @@
 """Row-wise sharding stress: an ``EmbeddingBagCollection`` of 64 tables x 10M rows x dim 256 in fp16 with a fixed pooling factor
 of 20 (sum pooling, uniform ids), batch 16384 per rank; one step is forward + backward with the fused row-wise Adagrad.  Besides
-the step time the three exchanges of a row-wise step are timed on their own with the step's shapes and reported as achieved GB/s
-per rank and as a fraction of the NVLink peer-copy bandwidth: the input-dist all-to-all (ids and lengths after bucketization), the
-pooled reduce-scatter and the gradient all-gather.
+the step time, the phases of the fused engine are device-timed inside real steps -- input distribution, lookup fused with the
+reduce-scatter, finalize, gradient all-gather, backward -- and reported as achieved GB/s over NVLink per rank and as a fraction of
+the measured peer-copy bandwidth; the same three exchanges are also timed as library collectives with the step's shapes.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 4 --master-addr 127.0.0.1 --master-port 29512 \\
         -m torchrec_b200.distributed.benchmark.benchmark_rw_stress --steps 10 --warmup 3
@@ -19,6 +19,7 @@ import torch
 import torch.distributed as dist
 
 NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU
+HBM_GBS = 6556.8    # measured copy bandwidth of one GPU
 
 
 def _time(fn, iters: int, device: torch.device) -> float:
@@ -56,6 +57,7 @@ def main() -> None:
     p.add_argument("--pooling", type=int, default=20)
     p.add_argument("--batch-per-rank", type=int, default=16384)
     p.add_argument("--cpu", action="store_true", help="plumbing check on the host (gloo); not a benchmark")
+    p.add_argument("--no-library-collectives", action="store_true", help="skip timing the exchanges as library collectives")
     a = p.parse_args()
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     device = torch.device("cpu") if a.cpu else torch.device(f"cuda:{local_rank}")
@@ -115,8 +117,42 @@ def main() -> None:
         step(i)
     step_ms = _time(lambda: step(0), a.steps, device)
 
-    # ---- the three exchanges on their own, with the step's shapes ------------------------------------------------
+    # ---- the fused engine's phases, device-timed inside real steps ----------------------------------------------------
     ids_per_rank = a.tables * B * a.pooling
+    frac = (world - 1) / world
+    phases = None
+    engine = getattr(sebc, "_engine", None)
+    if engine is not None:
+        engine.timing = {}
+        for i in range(a.steps):
+            step(i)
+        local = engine.timing_summary()
+        engine.timing = None
+        t = torch.tensor([local.get(k, 0.0) for k in ("input_dist", "lookup_push", "finalize", "grad_publish", "backward_update")], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = dict(zip(("input_dist", "lookup_push", "finalize", "grad_publish", "backward_update"), [float(x) for x in t]))
+        esz = {torch.float16: 2, torch.bfloat16: 2, torch.float32: 4}
+        # bytes that must cross NVLink per rank and step (what leaves this GPU)
+        in_bytes = frac * (ids_per_rank * 8 + a.tables * B * 4)
+        rs_bytes = frac * B * a.tables * a.dim * world * esz[engine.stage_dtype]      # a partial row to every other owner ... of every sample
+        gp_bytes = frac * B * a.tables * a.dim * world * esz[engine.grad_dtype]       # the gradient block to every other owner
+        gbs = lambda nbytes, t_ms: nbytes / (t_ms / 1e3) / 1e9 if t_ms > 0 else 0.0
+        # HBM side of the lookup: every id reads one table row; the backward reads a gradient row and reads + writes the table row
+        row_bytes = a.dim * 2
+        fwd_hbm = ids_per_rank * row_bytes
+        phases = {
+            "input_dist (count + scatter over peer stores)": {"ms": ms["input_dist"], "nvlink_GBps": gbs(in_bytes, ms["input_dist"]),
+                                                              "fraction_of_nvlink": gbs(in_bytes, ms["input_dist"]) / NVLINK_GBS},
+            "lookup + reduce-scatter (rows pushed to the owners inside the lookup kernel, incl. waiting for the ids)": {
+                "ms": ms["lookup_push"], "nvlink_GBps": gbs(rs_bytes, ms["lookup_push"]), "fraction_of_nvlink": gbs(rs_bytes, ms["lookup_push"]) / NVLINK_GBS,
+                "hbm_GBps_gathered": gbs(fwd_hbm, ms["lookup_push"]), "roofline_ms": max(rs_bytes / (NVLINK_GBS * 1e6), fwd_hbm / (HBM_GBS * 1e6))},
+            "finalize (sum of partial rows, cast)": {"ms": ms["finalize"]},
+            "gradient all-gather (blocks pushed to the owners)": {"ms": ms["grad_publish"], "nvlink_GBps": gbs(gp_bytes, ms["grad_publish"]),
+                                                                   "fraction_of_nvlink": gbs(gp_bytes, ms["grad_publish"]) / NVLINK_GBS},
+            "backward + row-wise Adagrad (local slab)": {"ms": ms["backward_update"]},
+        }
+
+    # ---- the three exchanges as library collectives with the step's shapes, for comparison -------------------------------
     id_send = torch.empty(ids_per_rank, dtype=torch.int64, device=device)
     id_recv = torch.empty_like(id_send)
     len_send = torch.empty(a.tables * B * world, dtype=torch.int32, device=device)
@@ -126,25 +162,26 @@ def main() -> None:
         dist.all_to_all_single(len_recv, len_send)
         dist.all_to_all_single(id_recv, id_send)
 
-    t_in = _time(input_dist, 10, device)
-    in_bytes = (id_send.numel() * 8 + len_send.numel() * 4) * (world - 1) / world
-    pooled = torch.empty(B * world, a.tables * a.dim, dtype=torch.float16, device=device)
-    rs_out = torch.empty(B, a.tables * a.dim, dtype=torch.float16, device=device)
-    t_rs = _time(lambda: dist.reduce_scatter_tensor(rs_out, pooled), 10, device)
-    rs_bytes = pooled.numel() * 2 * (world - 1) / world
-    t_ag = _time(lambda: dist.all_gather_into_tensor(pooled, rs_out), 10, device)
-    ag_bytes = rs_bytes
+    lib = None
+    if not a.no_library_collectives:
+        t_in = _time(input_dist, 10, device)
+        in_b = (id_send.numel() * 8 + len_send.numel() * 4) * frac
+        pooled = torch.empty(B * world, a.tables * a.dim, dtype=torch.float16, device=device)
+        rs_out = torch.empty(B, a.tables * a.dim, dtype=torch.float16, device=device)
+        t_rs = _time(lambda: dist.reduce_scatter_tensor(rs_out, pooled), 10, device)
+        rs_b = pooled.numel() * 2 * frac
+        t_ag = _time(lambda: dist.all_gather_into_tensor(pooled, rs_out), 10, device)
+        g = lambda nbytes, t_ms: nbytes / (t_ms / 1e3) / 1e9
+        lib = {"input_dist_a2a": {"ms": t_in, "GBps_per_rank": g(in_b, t_in)}, "pooled_reduce_scatter": {"ms": t_rs, "GBps_per_rank": g(rs_b, t_rs)},
+               "grad_all_gather": {"ms": t_ag, "GBps_per_rank": g(rs_b, t_ag)}, "sum_ms": t_in + t_rs + t_ag}
     if rank == 0:
-        gbs = lambda b, ms: b / (ms / 1e3) / 1e9
         print(json.dumps({
             "metric": "row-wise EBC step (forward + backward, fused row-wise Adagrad)", "n_gpus": world, "ms_per_step": step_ms,
             "samples_per_s": B * world / (step_ms / 1e3), "lookups_per_s": ids_per_rank * world / (step_ms / 1e3),
-            "input_dist_a2a": {"ms": t_in, "GBps_per_rank": gbs(in_bytes, t_in), "fraction_of_nvlink": gbs(in_bytes, t_in) / NVLINK_GBS},
-            "pooled_reduce_scatter": {"ms": t_rs, "GBps_per_rank": gbs(rs_bytes, t_rs), "fraction_of_nvlink": gbs(rs_bytes, t_rs) / NVLINK_GBS},
-            "grad_all_gather": {"ms": t_ag, "GBps_per_rank": gbs(ag_bytes, t_ag), "fraction_of_nvlink": gbs(ag_bytes, t_ag) / NVLINK_GBS},
-            "exchange_share_of_step": (t_in + t_rs + t_ag) / step_ms,
+            "path": "fused sparse engine over peer memory" if engine is not None else "library collectives",
+            "engine_phases": phases, "library_collectives_same_shapes": lib,
             "config": {"tables": a.tables, "rows": a.rows, "dim": a.dim, "dtype": "fp16", "pooling": a.pooling, "batch_per_rank": B, "data": "synthetic uniform ids",
-                       "exchange_timing": "library collectives with the step's shapes, device-timed, max over ranks"}}))
+                       "timing": "CUDA events, max over ranks; phase times are taken inside real steps and include waiting for peers"}}))
     dist.destroy_process_group()
 
 

@@ -34,6 +34,7 @@ from torchrec_b200.distributed.types import (
     Awaitable,
     EmbeddingModuleShardingPlan,
     LazyAwaitable,
+    NoWait,
     ParameterSharding,
     QuantizedCommCodecs,
     ShardedTensor,
@@ -121,6 +122,8 @@ class EmbeddingCollectionContext(Multistreamable):
         self.sharding_contexts: List[SequenceShardingContext] = sharding_contexts or []
         self.input_features: List[KeyedJaggedTensor] = input_features or []
         self.reverse_indices: List[torch.Tensor] = reverse_indices or []
+        self.engine_handle = None  # set when the fused sequence engine distributed this batch
+        self.engine_features: Optional[KeyedJaggedTensor] = None
 
     def record_stream(self, stream: torch.Stream) -> None:
         for ctx in self.sharding_contexts:
@@ -130,6 +133,8 @@ class EmbeddingCollectionContext(Multistreamable):
         for r in self.reverse_indices:
             if r.is_cuda:
                 r.record_stream(stream)
+        if self.engine_handle is not None:
+            self.engine_handle.record_stream(stream)
 
 
 class EmbeddingCollectionAwaitable(LazyAwaitable[Dict[str, JaggedTensor]]):
@@ -254,6 +259,8 @@ class ShardedEmbeddingCollection(
                     optims.append(("", m.fused_optimizer))
         self._optim: CombinedOptimizer = CombinedOptimizer(optims)
         self._hash_offsets_per_sharding: List[Optional[torch.Tensor]] = []
+        self._engine = None
+        self._engine_state: str = "auto"  # "auto" -> "on" | "off"
 
     # ---- plan -> sharding infos ---------------------------------------------------------------------
     @classmethod
@@ -346,6 +353,68 @@ class ShardedEmbeddingCollection(
     def create_context(self) -> EmbeddingCollectionContext:
         return EmbeddingCollectionContext(sharding_contexts=[])
 
+    # ---- fused sequence engine ----------------------------------------------------------------------
+    def disable_fused_engine(self) -> None:
+        """Wrappers that change the distributed ids between input dist and lookup (managed collision) need the classic
+        three-stage path."""
+        self._engine_state, self._engine = "off", None
+
+    def _fused_engine(self):
+        if self._engine_state == "auto":
+            self._engine = self._build_fused_engine()
+            self._engine_state = "on" if self._engine is not None else "off"
+        return self._engine
+
+    def _build_fused_engine(self):
+        """All ranks take the same decision: it depends on the plan, the environment and one collective agreement."""
+        from torchrec_b200.distributed.fbgemm_qcomm_codec import CastCodec
+        from torchrec_b200.distributed.fused_sequence_engine import FusedSequenceEngine
+        from torchrec_b200.distributed.peer_memory import PeerGroup
+        from torchrec_b200.distributed.types import CommOp
+
+        dev = self._device
+        if dev is None or dev.type != "cuda" or isinstance(self._env, ShardingEnv2D) or self._use_index_dedup:
+            return None
+        allowed = {ShardingType.TABLE_WISE.value, ShardingType.COLUMN_WISE.value, ShardingType.ROW_WISE.value}
+        if not self._sharding_types or any(t not in allowed for t in self._sharding_types):
+            return None
+        fused = (EmbeddingComputeKernel.FUSED, EmbeddingComputeKernel.FUSED_UVM, EmbeddingComputeKernel.FUSED_UVM_CACHING)
+        out_dtypes = set()
+        for sh, lk in zip(self._embedding_shardings, self._lookups):
+            if isinstance(lk, DistributedDataParallel):
+                return None
+            for groups in sh._grouped_embedding_configs_per_rank:
+                if any(g.compute_kernel not in fused or g.has_feature_processor for g in groups):
+                    return None
+            for emb in lk.emb_modules:
+                out_dtypes.add(emb.emb_module.output_dtype)
+        if len(out_dtypes) > 1:
+            return None
+        out_dtype = out_dtypes.pop() if out_dtypes else torch.float32
+        stage_dtype, grad_dtype = out_dtype, out_dtype
+        codecs = (self.qcomm_codecs_registry or {}).get(CommOp.SEQUENCE_EMBEDDINGS_ALL_TO_ALL.name)
+        if codecs is not None:
+            fwd, bwd = codecs.forward, codecs.backward
+            stage_dtype = fwd.quantized_dtype if isinstance(fwd, CastCodec) else torch.float16
+            grad_dtype = bwd.quantized_dtype if isinstance(bwd, CastCodec) else torch.bfloat16
+        peer = PeerGroup.get(self._env.process_group, dev)
+        if peer is None:
+            return None
+        try:
+            return FusedSequenceEngine(peer, self._embedding_configs, self._embedding_shardings, self._lookups, out_dtype, stage_dtype, grad_dtype)
+        except AssertionError as e:
+            import warnings
+
+            warnings.warn(f"fused sequence engine not used for this module: {e}")
+            return None
+
+    def _engine_output(self, ctx: EmbeddingCollectionContext, rows: torch.Tensor) -> LazyAwaitable[Dict[str, JaggedTensor]]:
+        """``rows [n, D]`` are in the order of the input KJT's values: cut them by that KJT's own lengths."""
+        feats = ctx.engine_features
+        wanted = self._engine.slot_names
+        per_key = construct_jagged_tensors(rows, feats, list(feats.keys()), need_indices=self._need_indices)
+        return NoWait({k: per_key[k] for k in wanted})
+
     # ---- the three stages ---------------------------------------------------------------------------
     def _create_input_dist(self, input_feature_names: List[str]) -> None:
         feature_names: List[str] = []
@@ -368,6 +437,13 @@ class ShardedEmbeddingCollection(
 
     def input_dist(self, ctx: EmbeddingCollectionContext, features: KeyedJaggedTensor) -> Awaitable[Awaitable[KJTList]]:
         assert not features.variable_stride_per_key(), "variable batch per feature is not supported for sequence embeddings"
+        engine = self._fused_engine() if self._engine_state != "off" else None
+        if engine is not None and engine.accepts(features):
+            from torchrec_b200.distributed.embeddingbag import EngineDistInput
+
+            ctx.engine_handle = engine.input_dist(features)
+            ctx.engine_features = features
+            return NoWait(NoWait(EngineDistInput(ctx.engine_handle)))
         if self._has_uninitialized_input_dist:
             self._create_input_dist(features.keys())
             self._has_uninitialized_input_dist = False
@@ -392,6 +468,8 @@ class ShardedEmbeddingCollection(
             return KJTListSplitsAwaitable(awaitables, ctx, self._module_fqn, self._sharding_types)
 
     def compute(self, ctx: EmbeddingCollectionContext, dist_input: KJTList) -> List[torch.Tensor]:
+        if ctx.engine_handle is not None:
+            return [self._engine.lookup(ctx.engine_handle)]
         ret: List[torch.Tensor] = []
         for lookup, features, sctx, sharding in zip(self._lookups, dist_input, ctx.sharding_contexts, self._embedding_shardings):
             sctx.lengths_after_input_dist = features.lengths().view(-1, features.stride())
@@ -403,6 +481,8 @@ class ShardedEmbeddingCollection(
         return ret
 
     def output_dist(self, ctx: EmbeddingCollectionContext, output: List[torch.Tensor]) -> LazyAwaitable[Dict[str, JaggedTensor]]:
+        if ctx.engine_handle is not None:
+            return self._engine_output(ctx, output[0])
         awaitables: List[Awaitable[torch.Tensor]] = []
         features_before: List[KeyedJaggedTensor] = []
         for odist, embeddings, sctx in zip(self._output_dists, output, ctx.sharding_contexts):

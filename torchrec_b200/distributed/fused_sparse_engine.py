@@ -105,6 +105,8 @@ class _Buffers:
 class FusedSparseEngine:
     """See the module docstring.  Built by ``ShardedEmbeddingBagCollection`` through :meth:`build`."""
 
+    sequence = False  # the unpooled variant (``FusedSequenceEngine``) lays its output out per id, not per bag
+
     def __init__(self, peer: _PeerBase, table_configs: Sequence[Any], shardings: Sequence[Any], lookups: Sequence[Any],
                  out_dtype: torch.dtype, stage_dtype: torch.dtype, grad_dtype: torch.dtype) -> None:
         self.peer = peer
@@ -120,6 +122,33 @@ class FusedSparseEngine:
         self.ids_dtype: Optional[torch.dtype] = None
         self.weighted = any(m.weighted for m in self.modules)
         self.recv_counts: List[int] = []
+        # optional per-phase device timing (benchmarks): phase -> list of (start event, end event)
+        self.timing: Optional[Dict[str, List[Tuple[torch.cuda.Event, torch.cuda.Event]]]] = None
+
+    def _timed(self, phase: str):
+        """Context manager that brackets a phase with CUDA events when ``timing`` is on."""
+        import contextlib
+
+        if self.timing is None or torch.cuda.is_current_stream_capturing():
+            return contextlib.nullcontext()
+        engine = self
+
+        class _T:
+            def __enter__(self_inner):
+                self_inner.e0 = torch.cuda.Event(enable_timing=True)
+                self_inner.e0.record()
+
+            def __exit__(self_inner, *exc):
+                e1 = torch.cuda.Event(enable_timing=True)
+                e1.record()
+                engine.timing.setdefault(phase, []).append((self_inner.e0, e1))
+
+        return _T()
+
+    def timing_summary(self) -> Dict[str, float]:
+        """Mean device milliseconds per phase since ``timing`` was switched on (synchronises)."""
+        torch.cuda.synchronize(self.device)
+        return {k: sum(a.elapsed_time(b) for a, b in v) / max(len(v), 1) for k, v in (self.timing or {}).items()}
 
     # ------------------------------------------------------------------------------------------------------------------
     # static layout
@@ -132,11 +161,16 @@ class FusedSparseEngine:
         rows_of: Dict[str, int] = {}
         acc = 0
         for cfg in table_configs:
-            pooling_of[cfg.name] = cfg.pooling
+            pooling_of[cfg.name] = getattr(cfg, "pooling", None)
             rows_of[cfg.name] = cfg.num_embeddings
             for f in (cfg.feature_names or [cfg.name]):
-                out_col[(cfg.name, f)] = acc
-                acc += cfg.embedding_dim
+                if self.sequence:  # one output row per id: every table starts at column 0 of it
+                    assert not any(k[1] == f for k in out_col), f"feature {f} feeds two tables"
+                    out_col[(cfg.name, f)] = 0
+                    acc = max(acc, cfg.embedding_dim)
+                else:
+                    out_col[(cfg.name, f)] = acc
+                    acc += cfg.embedding_dim
         self.total_D = acc
         jobs: List[_Job] = []
         self.dest_job_start = [0]
@@ -247,9 +281,9 @@ class FusedSparseEngine:
             m.slab_cols = [slab_col_of[g0 + j] for j in range(m.j0, m.j1)]
         self.has_mean_after = any(jb.mean_after for jb in jobs)
         # one rank and nothing to fix up afterwards: lookups write the output and read the gradient directly
-        self.direct = W == 1 and not self.has_mean_after
+        self.direct = W == 1 and not self.has_mean_after and not self.sequence
         covered = sum(s[1] for s in segs)
-        assert covered == self.total_D, f"shards cover {covered} of {self.total_D} output columns"
+        assert self.sequence or covered == self.total_D, f"shards cover {covered} of {self.total_D} output columns"
         dev = self.device
         i32 = dict(dtype=torch.int32, device=dev)
         self.t_seg = torch.tensor(segs, **i32).reshape(-1, 6)
@@ -328,6 +362,7 @@ class FusedSparseEngine:
         S = b.sizes.view(2, self.W, self.G + 2)[epoch & 1].cpu()
         recv = [int(S[:, self.dest_job_start[d]: self.dest_job_start[d + 1]].sum()) for d in range(self.W)]
         self.recv_counts = recv  # ids every rank's lookup receives for the batch that sized the buffers
+        b.max_values = int(S[:, self.G + 1].max())  # largest KJT (ids of all its features) over the ranks
         b.cap = max(1024, (int(max(recv) * dist_slack()) + 1023) // 1024 * 1024)
         ids_dtype = self.ids_dtype or torch.int64
         n_len = max(self.J_max * self.W * b.B, 1)
@@ -339,8 +374,14 @@ class FusedSparseEngine:
                 r.w, r.w_ptrs = self.peer.alloc_shared((b.cap,), torch.float32)
             else:
                 r.w, r.w_ptrs = None, []
+            if self.sequence:
+                r.ret, r.ret_ptrs = self.peer.alloc_shared((b.cap,), torch.int64)
+            else:
+                r.ret, r.ret_ptrs = None, []
             b.recv.append(r)
-        if not self.direct:
+        if self.sequence:
+            self._alloc_sequence_buffers(b)
+        elif not self.direct:
             b.staging, b.staging_ptrs = self.peer.alloc_shared((b.B, self.stage_cols), self.stage_dtype)
             b.gslab, b.gslab_ptrs = self.peer.alloc_shared((self.W * b.B, self.slab_cols), self.grad_dtype)
         if pg is not None:
@@ -358,12 +399,14 @@ class FusedSparseEngine:
         if probe:
             len_ptrs = val_ptrs = b.sizes_ptrs  # phase 0 touches neither
             w_ptrs = b.sizes_ptrs if weights is not None else []
+            ret_ptrs: List[int] = []
             cap = 0
         else:
             len_ptrs, val_ptrs, w_ptrs, cap = r.len_ptrs, r.val_ptrs, (r.w_ptrs if weights is not None else []), b.cap
+            ret_ptrs = r.ret_ptrs
         torch.ops.trb200.kjt_dist_send(
             phase, self.rank, b.B, self._topo(feat_pos), [self.t_row_lo, self.t_row_hi], [b.send_len, b.chunk_sum, b.counters, self.flags.epochs],
-            values, offsets, weights, self.flags.ptrs, b.sizes_ptrs, len_ptrs, val_ptrs, w_ptrs, cap, self.peer.wait_cycles, self.peer.err,
+            values, offsets, weights, self.flags.ptrs, b.sizes_ptrs, len_ptrs, val_ptrs, w_ptrs, ret_ptrs, cap, self.peer.wait_cycles, self.peer.err,
         )
 
     # ------------------------------------------------------------------------------------------------------------------
@@ -391,8 +434,9 @@ class FusedSparseEngine:
                 self.prepare(kjt)
                 self.prepare_finish()
             h = self.new_handle(kjt)
-            self.phase_send(h, 0)
-            self.phase_send(h, 1)
+            with self._timed("input_dist"):
+                self.phase_send(h, 0)
+                self.phase_send(h, 1)
         return h
 
     def phase_push(self, h: DistHandle, build_plans: bool) -> None:
@@ -481,8 +525,10 @@ class FusedSparseEngine:
 class _EngineLookup(torch.autograd.Function):
     @staticmethod
     def forward(ctx, anchor, engine: FusedSparseEngine, h: DistHandle):
-        engine.phase_push(h, build_plans=True)
-        out = engine.phase_finalize(h)
+        with engine._timed("lookup_push"):
+            engine.phase_push(h, build_plans=True)
+        with engine._timed("finalize"):
+            out = engine.phase_finalize(h)
         ctx.engine, ctx.h = engine, h
         return out
 
@@ -492,7 +538,9 @@ class _EngineLookup(torch.autograd.Function):
 
         engine, h = ctx.engine, ctx.h
         scale = 1.0 / engine.W if comm_ops.get_gradient_division() else 1.0
-        engine.phase_publish(h, grad, scale)
-        engine.phase_pull(h)
+        with engine._timed("grad_publish"):
+            engine.phase_publish(h, grad, scale)
+        with engine._timed("backward_update"):
+            engine.phase_pull(h)
         ctx.h = None
         return None, None, None

@@ -33,14 +33,8 @@ from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
 
 
 def get_embedding_shard_metadata(grouped_embedding_configs_per_rank):
-    is_even, prev = True, None
-    metas = []
-    for groups in grouped_embedding_configs_per_rank:
-        for g in groups:
-            for t in g.embedding_tables:
-                metas.append(t.local_metadata)
-    del is_even, prev
-    return metas
+    """Shard metadata of every table of every rank, in rank-major order."""
+    return [t.local_metadata for groups in grouped_embedding_configs_per_rank for g in groups for t in g.embedding_tables]
 
 
 class BaseRwEmbeddingSharding(BaseSharding[C, F, T, W]):

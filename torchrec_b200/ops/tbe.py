@@ -497,6 +497,42 @@ class TableBatchedEmbeddingBags(nn.Module):
             self.step, o.max_gradient, grad_ptrs, B_local, grad_scale, plan.n_valid,
         )
 
+    def seq_forward_push(self, indices: torch.Tensor, offsets: torch.Tensor, ret: torch.Tensor, B: int, out_ptrs: List[int], out_rows: int,
+                         out_stride: int, cols, out_dtype: torch.dtype) -> None:
+        """Unpooled lookup of ids that arrived with return addresses (``ret[k]`` = requesting rank << 32 | row): the row of id
+        ``k`` is stored into row ``ret[k] & 0xffffffff`` of ``out_ptrs[ret[k] >> 32]`` (``[out_rows, out_stride]`` buffers), at the
+        per-feature columns ``cols``.  ``indices`` / ``ret`` are fixed-capacity buffers delimited by ``offsets``."""
+        _ext.require_cuda_ext("tbe_seq_forward_dist")
+        assert self.pooling_mode == PoolingMode.NONE
+        w = self.weights.detach()
+        if indices.dtype != offsets.dtype:
+            offsets = offsets.to(indices.dtype)
+        torch.ops.trb200.tbe_seq_forward_dist(
+            w, self._meta_tensor_at(w.device, cols), indices, offsets.contiguous(), ret, out_ptrs, out_rows, _OUT_CODE[out_dtype], out_stride, B,
+            self.max_D, self._err,
+        )
+
+    def seq_backward_pull(self, grad_local: torch.Tensor, grad_ptrs: List[int], ret: torch.Tensor, indices: torch.Tensor, offsets: torch.Tensor,
+                          B: int, cols, grad_scale: float, plan: Optional[TBEPlan] = None) -> None:
+        """Backward + fused optimizer of :meth:`seq_forward_push`: the gradient row of id ``k`` is read from row
+        ``ret[k] & 0xffffffff`` of ``grad_ptrs[ret[k] >> 32]`` at the per-feature columns ``cols``."""
+        assert self.fused, "the fused exchange is for tables with an in-backward optimizer"
+        _ext.require_cuda_ext("tbe_backward_apply_dist")
+        w = self.weights.detach()
+        self.step += 1
+        if plan is None:
+            plan = self.build_plan(indices, offsets, None, B, True)
+        else:
+            plan.wait()
+        o = self.optimizer_args
+        eps = o.eta if o.optimizer == EmbOptimType.LARS_SGD else o.eps
+        torch.ops.trb200.tbe_backward_apply_dist(
+            w, self.momentum1 if self.momentum1.numel() else None, self.momentum2 if self.momentum2.numel() else None, None,
+            self._meta_tensor_at(w.device, cols), plan.keys, plan.src, plan.w, plan.src_feature, plan.bag_scale, grad_local,
+            grad_local.stride(0), B, self.max_D, False, _OPT_CODE[o.optimizer], o.learning_rate, eps, o.beta1, o.beta2, o.weight_decay,
+            self.step, o.max_gradient, grad_ptrs, 0, grad_scale, plan.n_valid, ret, self._sr_counter(),
+        )
+
     def backward_local(self, grad: torch.Tensor, indices: torch.Tensor, offsets: torch.Tensor, psw: Optional[torch.Tensor], B: int, cols,
                        plan: Optional[TBEPlan] = None, padded: bool = False) -> None:
         """Backward + fused optimizer reading the pooled gradient of bag ``b`` from row ``b`` of ``grad`` (a local ``[B, stride]``
