@@ -151,9 +151,11 @@ def main() -> None:
         print(f"kernel table ({sum(v[0] for v in agg.values()) / 1e3:.2f} ms of device time):", file=sys.stderr)
         for name, (t, n) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:30]:
             print(f"  {t / 1e3:8.3f} ms  x{n:<4d} {name}", file=sys.stderr)
+    sharded_ec = next((m for m in dmp.modules() if hasattr(m, "_engine_state") and hasattr(m, "_need_indices")), None)
+    exchange = "fused into the lookup over peer memory" if sharded_ec is not None and sharded_ec._engine_state == "on" else "library collectives"
     if rank == 0:
         print(json.dumps({
-            "metric": "BERT4Rec train sequences/sec", "value": a.batch_per_rank * world / (ms_per_step / 1e3), "unit": "sequences/s",
+            "metric": "BERT4Rec train sequences/sec", "exchange": exchange, "value": a.batch_per_rank * world / (ms_per_step / 1e3), "unit": "sequences/s",
             "tokens_per_s": float(tok) / (ms_per_step / 1e3), "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
             "loss": float(loss.detach()), "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic (Zipf(1.1) items, lengths U[20,200], 15% masked)",
             "config": {"model": "BERT4Rec 2 layers, 4 heads, hidden 256, FFN 1024, sampled softmax 8192 negatives", "item_tables": f"input and output embeddings, each {a.vocab} x {a.dim} bf16",
