@@ -72,15 +72,16 @@ def set_ec_index_dedup(val: bool) -> None:
 
 def create_embedding_sharding(sharding_type: str, sharding_infos: List[EmbeddingShardingInfo], env: ShardingEnv,
                               device: Optional[torch.device] = None, qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None):
-    if sharding_type == ShardingType.TABLE_WISE.value:
-        return TwSequenceEmbeddingSharding(sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
-    if sharding_type == ShardingType.ROW_WISE.value:
-        return RwSequenceEmbeddingSharding(sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
-    if sharding_type == ShardingType.DATA_PARALLEL.value:
+    by_type = {
+        ShardingType.TABLE_WISE.value: TwSequenceEmbeddingSharding,
+        ShardingType.ROW_WISE.value: RwSequenceEmbeddingSharding,
+        ShardingType.COLUMN_WISE.value: CwSequenceEmbeddingSharding,
+    }
+    if sharding_type == ShardingType.DATA_PARALLEL.value:  # replicated tables exchange nothing: no codecs
         return DpSequenceEmbeddingSharding(sharding_infos, env, device)
-    if sharding_type == ShardingType.COLUMN_WISE.value:
-        return CwSequenceEmbeddingSharding(sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
-    raise ValueError(f"Sharding not supported {sharding_type}")
+    if sharding_type not in by_type:
+        raise ValueError(f"Sharding not supported {sharding_type}")
+    return by_type[sharding_type](sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
 
 
 def construct_jagged_tensors(embeddings: torch.Tensor, features: KeyedJaggedTensor, embedding_names: List[str], need_indices: bool = False,
@@ -241,23 +242,11 @@ class ShardedEmbeddingCollection(
         self._has_features_permute: bool = True
         self._embedding_names_per_sharding: List[List[str]] = [s.embedding_names() for s in self._embedding_shardings]
         self._features_to_permute_indices: Dict[str, List[int]] = self._column_shard_order()
-        for i, (sharding, lookup) in enumerate(zip(self._embedding_shardings, self._lookups)):
-            if isinstance(sharding, DpSequenceEmbeddingSharding) and env.process_group is not None and dist.get_backend(env.process_group) != "fake":
-                self._lookups[i] = DistributedDataParallel(
-                    module=lookup, device_ids=[device] if device is not None and device.type == "cuda" else None,
-                    process_group=env.process_group, gradient_as_bucket_view=True, broadcast_buffers=True, static_graph=True,
-                )
+        self._replicate_data_parallel_lookups(DpSequenceEmbeddingSharding)
         # parameters / ShardedTensor state: same layout logic as the pooled module, under "embeddings."
         self._output_dtensor = getattr(env, "output_dtensor", False)
         self._initialize_torch_state()
-        optims = []
-        for lookup in self._lookups:
-            lk = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
-            for _, m in lk.named_modules():
-                if isinstance(m, FusedOptimizerModule):
-                    m.fused_optimizer.params = {"embeddings." + k: w for k, w in m.fused_optimizer.params.items()}
-                    optims.append(("", m.fused_optimizer))
-        self._optim: CombinedOptimizer = CombinedOptimizer(optims)
+        self._optim: CombinedOptimizer = self._gather_fused_optimizers()
         self._hash_offsets_per_sharding: List[Optional[torch.Tensor]] = []
         self._engine = None
         self._engine_state: str = "auto"  # "auto" -> "on" | "off"

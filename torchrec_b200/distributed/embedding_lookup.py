@@ -33,30 +33,47 @@ from torchrec_b200.optim.keyed import CombinedOptimizer, KeyedOptimizer
 from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
 
 
+def _copy_checkpoint_entry(dst: Any, src: Any) -> None:
+    """One state-dict entry into the live table memory; sharded entries are matched shard by shard on (offsets, sizes)."""
+    if isinstance(dst, ShardedTensor):
+        assert isinstance(src, ShardedTensor), "a sharded table loads from a sharded checkpoint entry"
+        ours, theirs = dst.local_shards(), src.local_shards()
+        assert len(ours) == len(theirs), f"{len(theirs)} checkpoint shards for {len(ours)} local shards"
+        for mine, other in zip(ours, theirs):
+            assert (mine.metadata.shard_offsets, mine.metadata.shard_sizes) == (other.metadata.shard_offsets, other.metadata.shard_sizes)
+            mine.tensor.detach().copy_(other.tensor)
+        return
+    if isinstance(src, ShardedTensor):
+        src = src.local_shards()[0].tensor
+    assert isinstance(src, torch.Tensor) and isinstance(dst, torch.Tensor)
+    dst.detach().copy_(src)
+
+
 def _load_state_dict(emb_modules: "nn.ModuleList", state_dict: Dict[str, Any]) -> Tuple[List[str], List[str]]:
-    """Copy checkpoint shards into the local table views, matching shards by their offsets."""
-    missing_keys: List[str] = []
-    unexpected_keys = list(state_dict.keys())
-    for emb_module in emb_modules:
-        for key, dst_param in emb_module.state_dict().items():
-            if key in state_dict:
-                src_param = state_dict[key]
-                if isinstance(dst_param, ShardedTensor):
-                    assert isinstance(src_param, ShardedTensor)
-                    assert len(dst_param.local_shards()) == len(src_param.local_shards())
-                    for dst_shard, src_shard in zip(dst_param.local_shards(), src_param.local_shards()):
-                        assert dst_shard.metadata.shard_offsets == src_shard.metadata.shard_offsets
-                        assert dst_shard.metadata.shard_sizes == src_shard.metadata.shard_sizes
-                        dst_shard.tensor.detach().copy_(src_shard.tensor)
-                elif isinstance(src_param, ShardedTensor):
-                    dst_param.detach().copy_(src_param.local_shards()[0].tensor)
-                else:
-                    assert isinstance(src_param, torch.Tensor) and isinstance(dst_param, torch.Tensor)
-                    dst_param.detach().copy_(src_param)
-                unexpected_keys.remove(key)
-            else:
-                missing_keys.append(key)
-    return missing_keys, unexpected_keys
+    """Copy checkpoint shards into the local table views.  Returns (keys the kernels hold that the checkpoint lacks, keys
+    of the checkpoint that no kernel holds)."""
+    missing: List[str] = []
+    leftover = dict.fromkeys(state_dict.keys())
+    for kernel in emb_modules:
+        for key, live in kernel.state_dict().items():
+            if key not in state_dict:
+                missing.append(key)
+                continue
+            _copy_checkpoint_entry(live, state_dict[key])
+            leftover.pop(key, None)
+    return missing, list(leftover)
+
+
+_FUSED_KERNELS = (EmbeddingComputeKernel.FUSED, EmbeddingComputeKernel.FUSED_UVM, EmbeddingComputeKernel.FUSED_UVM_CACHING)
+
+
+def _kernel_class(compute_kernel: EmbeddingComputeKernel, dense_cls: type, fused_cls: type) -> type:
+    """The UVM kinds run as HBM-resident fused kernels: 180 GB per GPU holds what the reference spills to host memory."""
+    if compute_kernel == EmbeddingComputeKernel.DENSE:
+        return dense_cls
+    if compute_kernel in _FUSED_KERNELS:
+        return fused_cls
+    raise ValueError(f"Compute kernel not supported {compute_kernel}")
 
 
 class CommOpGradientScaling(torch.autograd.Function):
@@ -138,23 +155,18 @@ class GroupedEmbeddingsLookup(_GroupedLookupBase):
 
     @staticmethod
     def _create_embedding_kernel(config: GroupedEmbeddingConfig, pg, device) -> BaseEmbedding:
-        if config.compute_kernel == EmbeddingComputeKernel.DENSE:
-            return BatchedDenseEmbedding(config=config, pg=pg, device=device)
-        if config.compute_kernel in (EmbeddingComputeKernel.FUSED, EmbeddingComputeKernel.FUSED_UVM, EmbeddingComputeKernel.FUSED_UVM_CACHING):
-            return BatchedFusedEmbedding(config=config, pg=pg, device=device)
-        raise ValueError(f"Compute kernel not supported {config.compute_kernel}")
+        cls = _kernel_class(config.compute_kernel, BatchedDenseEmbedding, BatchedFusedEmbedding)
+        return cls(config=config, pg=pg, device=device)
 
     def forward(self, sparse_features: KeyedJaggedTensor) -> torch.Tensor:
-        embeddings: List[torch.Tensor] = []
-        features_by_group = sparse_features.split(self._feature_splits) if len(self._emb_modules) > 1 else [sparse_features]
-        for emb_op, features in zip(self._emb_modules, features_by_group):
-            embeddings.append(emb_op(features).view(-1))
-        if len(embeddings) == 0:
+        kernels = list(self._emb_modules)
+        if not kernels:
             return self._dummy_embs_tensor
-        dim = self._emb_modules[0].emb_module.max_D
-        if len(embeddings) == 1:
-            return embeddings[0].view(-1, dim)
-        return torch.cat(embeddings).view(-1, dim)
+        width = kernels[0].emb_module.max_D
+        if len(kernels) == 1:
+            return kernels[0](sparse_features).reshape(-1, width)
+        parts = sparse_features.split(self._feature_splits)
+        return torch.cat([k(f).reshape(-1) for k, f in zip(kernels, parts)]).view(-1, width)
 
 
 class GroupedPooledEmbeddingsLookup(_GroupedLookupBase):
@@ -176,26 +188,26 @@ class GroupedPooledEmbeddingsLookup(_GroupedLookupBase):
 
     @staticmethod
     def _create_embedding_kernel(config: GroupedEmbeddingConfig, device, pg, sharding_type) -> BaseEmbedding:
-        if config.compute_kernel == EmbeddingComputeKernel.DENSE:
-            return BatchedDenseEmbeddingBag(config=config, pg=pg, device=device, sharding_type=sharding_type)
-        if config.compute_kernel in (EmbeddingComputeKernel.FUSED, EmbeddingComputeKernel.FUSED_UVM, EmbeddingComputeKernel.FUSED_UVM_CACHING):
-            return BatchedFusedEmbeddingBag(config=config, pg=pg, device=device, sharding_type=sharding_type)
-        raise ValueError(f"Compute kernel not supported {config.compute_kernel}")
+        cls = _kernel_class(config.compute_kernel, BatchedDenseEmbeddingBag, BatchedFusedEmbeddingBag)
+        return cls(config=config, pg=pg, device=device, sharding_type=sharding_type)
 
     def forward(self, sparse_features: KeyedJaggedTensor) -> torch.Tensor:
         if len(self._emb_modules) == 0:
             return self._dummy_embs_tensor.view(sparse_features.stride(), 0) if sparse_features.stride() else self._dummy_embs_tensor
-        embeddings: List[torch.Tensor] = []
-        features_by_group = sparse_features.split(self._feature_splits) if len(self._emb_modules) > 1 else [sparse_features]
-        for config, emb_op, features in zip(self.grouped_configs, self._emb_modules, features_by_group):
-            if config.has_feature_processor and self._feature_processor is not None and isinstance(self._feature_processor, BaseGroupedFeatureProcessor):
-                features = self._feature_processor(features)
-            if config.is_weighted and self._scale_gradient_factor != 1 and features.weights_or_none() is not None and features.weights().requires_grad:
-                features._weights = CommOpGradientScaling.apply(features._weights, self._scale_gradient_factor)
-            embeddings.append(emb_op(features))
-        if len(embeddings) == 1:
-            return embeddings[0]
-        return torch.cat(embeddings, dim=1)
+        parts = [sparse_features] if len(self._emb_modules) == 1 else sparse_features.split(self._feature_splits)
+        pooled = [kernel(self._prepare_group_input(cfg, f)) for cfg, kernel, f in zip(self.grouped_configs, self._emb_modules, parts)]
+        return pooled[0] if len(pooled) == 1 else torch.cat(pooled, dim=1)
+
+    def _prepare_group_input(self, config: GroupedEmbeddingConfig, features: KeyedJaggedTensor) -> KeyedJaggedTensor:
+        """Feature processors run on the owning rank, after the input dist; learnable per-id weights get their gradient scaled
+        back up when the pooled gradient was divided by the world size on its way here."""
+        fp = self._feature_processor
+        if config.has_feature_processor and isinstance(fp, BaseGroupedFeatureProcessor):
+            features = fp(features)
+        w = features.weights_or_none()
+        if config.is_weighted and self._scale_gradient_factor != 1 and w is not None and w.requires_grad:
+            features._weights = CommOpGradientScaling.apply(w, self._scale_gradient_factor)
+        return features
 
 
 def fused_optimizer_of_lookups(lookups: List[nn.Module]) -> KeyedOptimizer:

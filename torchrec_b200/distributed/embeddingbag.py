@@ -105,24 +105,28 @@ def create_embedding_bag_sharding(
     sharding_infos: List[EmbeddingShardingInfo], env: ShardingEnv, device: Optional[torch.device] = None,
     permute_embeddings: bool = False, qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None,
 ) -> EmbeddingSharding[EmbeddingShardingContext, KeyedJaggedTensor, torch.Tensor, torch.Tensor]:
-    sharding_type = sharding_infos[0].param_sharding.sharding_type
+    kind = sharding_infos[0].param_sharding.sharding_type
     if device is not None and device.type == "meta":
         replace_placement_with_meta_device(sharding_infos)
-    if sharding_type == ShardingType.TABLE_WISE.value:
-        return TwPooledEmbeddingSharding(sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
-    if sharding_type == ShardingType.ROW_WISE.value:
-        return RwPooledEmbeddingSharding(sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
-    if sharding_type == ShardingType.DATA_PARALLEL.value:
-        return DpPooledEmbeddingSharding(sharding_infos, env, device)
-    if sharding_type == ShardingType.TABLE_ROW_WISE.value:
-        return TwRwPooledEmbeddingSharding(sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
-    if sharding_type == ShardingType.COLUMN_WISE.value:
-        return CwPooledEmbeddingSharding(sharding_infos, env, device, permute_embeddings=permute_embeddings, qcomm_codecs_registry=qcomm_codecs_registry)
-    if sharding_type == ShardingType.TABLE_COLUMN_WISE.value:
-        return TwCwPooledEmbeddingSharding(sharding_infos, env, device, permute_embeddings=permute_embeddings, qcomm_codecs_registry=qcomm_codecs_registry)
-    if sharding_type == ShardingType.GRID_SHARD.value:
-        return GridPooledEmbeddingSharding(sharding_infos, env, device, qcomm_codecs_registry=qcomm_codecs_registry)
-    raise ValueError(f"Sharding type not supported {sharding_type}")
+    # sharding type -> (class, takes a codec registry, takes permute_embeddings)
+    table = {
+        ShardingType.TABLE_WISE.value: (TwPooledEmbeddingSharding, True, False),
+        ShardingType.ROW_WISE.value: (RwPooledEmbeddingSharding, True, False),
+        ShardingType.DATA_PARALLEL.value: (DpPooledEmbeddingSharding, False, False),
+        ShardingType.TABLE_ROW_WISE.value: (TwRwPooledEmbeddingSharding, True, False),
+        ShardingType.COLUMN_WISE.value: (CwPooledEmbeddingSharding, True, True),
+        ShardingType.TABLE_COLUMN_WISE.value: (TwCwPooledEmbeddingSharding, True, True),
+        ShardingType.GRID_SHARD.value: (GridPooledEmbeddingSharding, True, False),
+    }
+    if kind not in table:
+        raise ValueError(f"Sharding type not supported {kind}")
+    cls, with_codecs, with_permute = table[kind]
+    extra: Dict[str, Any] = {}
+    if with_codecs:
+        extra["qcomm_codecs_registry"] = qcomm_codecs_registry
+    if with_permute:
+        extra["permute_embeddings"] = permute_embeddings
+    return cls(sharding_infos, env, device, **extra)
 
 
 def construct_output_kt(embeddings: List[torch.Tensor], embedding_names: List[str], embedding_dims: List[int]) -> KeyedTensor:
@@ -239,6 +243,32 @@ class ShardedTableStateMixin:
     """Parameters and checkpoint views of the tables of a sharded embedding module (pooled or unpooled): what
     ``named_parameters`` / ``state_dict`` / ``load_state_dict`` see.  The module provides ``_TABLE_ATTR``, ``_table_configs()``,
     ``_sharding_types``, ``_lookups``, ``module_sharding_plan``, ``_env``, ``_device`` and ``_output_dtensor``."""
+
+    # ---- construction steps shared by the pooled and the unpooled module ---------------------------------
+    def _replicate_data_parallel_lookups(self, dp_sharding_cls: type) -> None:
+        """Lookups of replicated (data-parallel) tables get their dense gradient all-reduced by DDP."""
+        pg = self._env.process_group
+        if pg is None or dist.get_backend(pg) == "fake":
+            return
+        on_cuda = self._device is not None and self._device.type == "cuda"
+        for i, sharding in enumerate(self._embedding_shardings):
+            if isinstance(sharding, dp_sharding_cls):
+                self._lookups[i] = DistributedDataParallel(
+                    module=self._lookups[i], device_ids=[self._device] if on_cuda else None, process_group=pg,
+                    gradient_as_bucket_view=True, broadcast_buffers=True, static_graph=True,
+                )
+
+    def _gather_fused_optimizers(self) -> CombinedOptimizer:
+        """One optimizer over the in-backward optimizers of all kernels, with keys ``<tables attr>.<table>.weight``."""
+        prefix = self._TABLE_ATTR + "."
+        found = []
+        for _, lookup in self._unwrapped_lookups():
+            for kernel in lookup.modules():
+                if isinstance(kernel, FusedOptimizerModule):
+                    opt = kernel.fused_optimizer
+                    opt.params = {prefix + key: weight for key, weight in opt.params.items()}
+                    found.append(("", opt))
+        return CombinedOptimizer(found)
 
     # ---- torch state: parameters and state dict -----------------------------------------------------
     def _unwrapped_lookups(self):
@@ -436,43 +466,12 @@ class ShardedEmbeddingBagCollection(
         ]
         self._is_weighted: bool = module.is_weighted()
         self._device = device
-        self._input_dists: List[nn.Module] = []
         self._lookups: List[nn.Module] = []
         self._create_lookups()
-        self._output_dists: List[nn.Module] = []
-        self._embedding_names: List[str] = []
-        self._embedding_dims: List[int] = []
-        self._feature_splits: List[int] = []
-        self._features_order: List[int] = []
-        self._uncombined_embedding_names: List[str] = []
-        self._uncombined_embedding_dims: List[int] = []
-        self._inverse_indices_permute_indices: Optional[torch.Tensor] = None
-        # output order: embeddings come out grouped by sharding type; permute back to table order
-        self._permute_op: Optional[nn.Module] = None
-        self._has_uninitialized_input_dist: bool = True
-        self._has_features_permute: bool = True
-        # lookups that hold data-parallel tables are wrapped in DDP so their dense gradient is all-reduced
-        for i, (sharding, lookup) in enumerate(zip(self._embedding_shardings, self._lookups)):
-            if isinstance(sharding, DpPooledEmbeddingSharding) and env.process_group is not None and dist.get_world_size(env.process_group) >= 1:
-                if dist.get_backend(env.process_group) != "fake":
-                    self._lookups[i] = DistributedDataParallel(
-                        module=lookup, device_ids=[device] if device is not None and device.type == "cuda" else None,
-                        process_group=env.process_group, gradient_as_bucket_view=True, broadcast_buffers=True, static_graph=True,
-                    )
+        self._reset_dist_layout()
+        self._replicate_data_parallel_lookups(DpPooledEmbeddingSharding)
         self._initialize_torch_state()
-        # optimizer
-        optims = []
-        for lookup in self._lookups:
-            lk = lookup.module if isinstance(lookup, DistributedDataParallel) else lookup
-            for _, tbe_module in lk.named_modules():
-                if isinstance(tbe_module, FusedOptimizerModule):
-                    # keys of the fused optimizer are "<table>.weight"; make them "embedding_bags.<table>.weight"
-                    params: Dict[str, Union[torch.Tensor, ShardedTensor]] = {}
-                    for param_key, weight in tbe_module.fused_optimizer.params.items():
-                        params["embedding_bags." + param_key] = weight
-                    tbe_module.fused_optimizer.params = params
-                    optims.append(("", tbe_module.fused_optimizer))
-        self._optim: CombinedOptimizer = CombinedOptimizer(optims)
+        self._optim: CombinedOptimizer = self._gather_fused_optimizers()
         # mean pooling for row-split tables is applied after the reduction
         self._has_mean_pooling_callback: bool = PoolingType.MEAN.value in self._pooling_type_to_rs_features()
         # fused sparse engine (peer-memory input dist + lookup + output hand-over): built on the first batch, collectively
@@ -481,6 +480,16 @@ class ShardedEmbeddingBagCollection(
         self._dim_per_key: Optional[torch.Tensor] = None
         self._kjt_key_indices: Dict[str, int] = {}
         self._kt_key_ordering: Optional[torch.Tensor] = None
+
+    def _reset_dist_layout(self) -> None:
+        """Everything the first batch fills in (the key order of the incoming KJT decides it): dist modules, output names and
+        dims, feature order, the column permutation back to table order."""
+        for name in ("_input_dists", "_output_dists", "_embedding_names", "_embedding_dims", "_feature_splits", "_features_order",
+                     "_uncombined_embedding_names", "_uncombined_embedding_dims"):
+            setattr(self, name, [])
+        self._inverse_indices_permute_indices: Optional[torch.Tensor] = None
+        self._permute_op: Optional[nn.Module] = None
+        self._has_uninitialized_input_dist, self._has_features_permute = True, True
 
     # ---- plan -> sharding infos ------------------------------------------------------------------
     @classmethod
@@ -577,38 +586,35 @@ class ShardedEmbeddingBagCollection(
             self._lookups.append(sharding.create_lookup())
 
     def _create_input_dist(self, input_feature_names: List[str]) -> None:
-        feature_names: List[str] = []
-        for sharding in self._embedding_shardings:
-            self._input_dists.append(sharding.create_input_dist())
-            feature_names.extend(sharding.feature_names())
-            self._feature_splits.append(len(sharding.feature_names()))
-        if feature_names == input_feature_names:
-            self._has_features_permute = False
-        else:
-            for f in feature_names:
-                self._features_order.append(input_feature_names.index(f))
-            dev = self._device if self._device is not None and self._device.type != "meta" else torch.device("cpu")
+        """One input dist per sharding; the incoming KJT is permuted only if its key order differs from the shardings'."""
+        per_sharding = [sh.feature_names() for sh in self._embedding_shardings]
+        self._input_dists.extend(sh.create_input_dist() for sh in self._embedding_shardings)
+        self._feature_splits.extend(len(names) for names in per_sharding)
+        wanted = [f for names in per_sharding for f in names]
+        self._has_features_permute = wanted != list(input_feature_names)
+        if self._has_features_permute:
+            position = {f: i for i, f in reversed(list(enumerate(input_feature_names)))}  # first occurrence wins
+            self._features_order.extend(position[f] for f in wanted)
+            dev = torch.device("cpu") if self._device is None or self._device.type == "meta" else self._device
             self.register_buffer("_features_order_tensor", torch.tensor(self._features_order, device=dev, dtype=torch.int32), persistent=False)
 
     def _create_output_dist(self) -> None:
-        embedding_shard_metadata = []
-        for sharding in self._embedding_shardings:
-            self._output_dists.append(sharding.create_output_dist(device=self._device))
-            self._embedding_names.extend(sharding.embedding_names())
-            self._embedding_dims.extend(sharding.embedding_dims())
-            self._uncombined_embedding_names.extend(sharding.uncombined_embedding_names())
-            self._uncombined_embedding_dims.extend(sharding.uncombined_embedding_dims())
-            embedding_shard_metadata.extend(sharding.embedding_shard_metadata())
-        # restore the embedding order of the unsharded module
-        wanted = [n for names in _embedding_names_by_table(self._embedding_bag_configs) for n in names]
-        if wanted != self._embedding_names:
-            from torchrec_b200.distributed.sharding.cw_sharding import PermutePooledEmbeddingsSplit
+        """One output dist per sharding, plus the column permutation that restores the unsharded module's embedding order."""
+        for sh in self._embedding_shardings:
+            self._output_dists.append(sh.create_output_dist(device=self._device))
+            for attr, values in (("_embedding_names", sh.embedding_names()), ("_embedding_dims", sh.embedding_dims()),
+                                 ("_uncombined_embedding_names", sh.uncombined_embedding_names()),
+                                 ("_uncombined_embedding_dims", sh.uncombined_embedding_dims())):
+                getattr(self, attr).extend(values)
+        module_order = [n for names in _embedding_names_by_table(self._embedding_bag_configs) for n in names]
+        if module_order == self._embedding_names:
+            return
+        from torchrec_b200.distributed.sharding.cw_sharding import PermutePooledEmbeddingsSplit
 
-            order = [self._embedding_names.index(n) for n in wanted]
-            self._pre_names, self._pre_dims = list(self._embedding_names), list(self._embedding_dims)
-            self._permute_op = PermutePooledEmbeddingsSplit(self._embedding_dims, order, device=self._device)
-            self._embedding_names = wanted
-            self._embedding_dims = [self._embedding_dims[i] for i in order]
+        order = [self._embedding_names.index(n) for n in module_order]
+        self._pre_names, self._pre_dims = list(self._embedding_names), list(self._embedding_dims)
+        self._permute_op = PermutePooledEmbeddingsSplit(self._pre_dims, order, device=self._device)
+        self._embedding_names, self._embedding_dims = module_order, [self._pre_dims[i] for i in order]
 
     def _init_mean_pooling_callback(self, input_feature_names: List[str]) -> None:
         keys = [input_feature_names[i] for i in self._features_order] if self._features_order else list(input_feature_names)
@@ -702,37 +708,37 @@ class ShardedEmbeddingBagCollection(
             ctx.engine_handle = engine.input_dist(features)
             return NoWait(NoWait(EngineDistInput(ctx.engine_handle)))
         if self._has_uninitialized_input_dist:
-            self._create_input_dist(features.keys())
-            self._has_uninitialized_input_dist = False
-            if not self._output_dists:
-                self._create_output_dist()
-            if ctx.variable_batch_per_feature and ctx.inverse_indices is not None:
-                self._create_inverse_indices_permute_indices(ctx.inverse_indices)
-            if self._has_mean_pooling_callback:
-                self._init_mean_pooling_callback(features.keys())
+            self._first_batch_setup(features, ctx)
         with torch.no_grad():
             if self._has_features_permute:
                 features = features.permute(self._features_order, self._features_order_tensor)
             if self._has_mean_pooling_callback:
-                ctx.divisor = _create_mean_pooling_divisor(
-                    lengths=features.lengths(), keys=features.keys(), offsets=features.offsets(), stride=features.stride(),
-                    dim_per_key=self._dim_per_key, mean_features=self._pooling_type_to_rs_features()[PoolingType.MEAN.value],
-                    embedding_names=self._embedding_names, embedding_dims=self._embedding_dims,
-                    kjt_key_indices=self._kjt_key_indices, kt_key_ordering=self._kt_key_ordering,
-                    weights=features.weights_or_none() if self._is_weighted else None,
-                )
-            features_by_shards = features.split(self._feature_splits)
-            awaitables = []
-            for input_dist, features_by_shard, sharding_type in zip(self._input_dists, features_by_shards, self._sharding_types):
+                ctx.divisor = self._mean_divisor(features)
+            requests = []
+            for dist_module, shard_features, sharding_type in zip(self._input_dists, features.split(self._feature_splits), self._sharding_types):
                 with maybe_annotate_embedding_event(EmbeddingEvent.KJT_SPLITS_DIST, self._module_fqn, sharding_type):
-                    awaitables.append(input_dist(features_by_shard))
-                ctx.sharding_contexts.append(
-                    EmbeddingShardingContext(
-                        batch_size_per_feature_pre_a2a=features_by_shard.stride_per_key(),
-                        variable_batch_per_feature=features_by_shard.variable_stride_per_key(),
-                    )
-                )
-            return KJTListSplitsAwaitable(awaitables, ctx, self._module_fqn, self._sharding_types)
+                    requests.append(dist_module(shard_features))
+                ctx.sharding_contexts.append(EmbeddingShardingContext(
+                    batch_size_per_feature_pre_a2a=shard_features.stride_per_key(),
+                    variable_batch_per_feature=shard_features.variable_stride_per_key()))
+            return KJTListSplitsAwaitable(requests, ctx, self._module_fqn, self._sharding_types)
+
+    def _first_batch_setup(self, features: KeyedJaggedTensor, ctx: EmbeddingBagCollectionContext) -> None:
+        self._create_input_dist(features.keys())
+        self._has_uninitialized_input_dist = False
+        if not self._output_dists:
+            self._create_output_dist()
+        if ctx.variable_batch_per_feature and ctx.inverse_indices is not None:
+            self._create_inverse_indices_permute_indices(ctx.inverse_indices)
+        if self._has_mean_pooling_callback:
+            self._init_mean_pooling_callback(features.keys())
+
+    def _mean_divisor(self, features: KeyedJaggedTensor) -> torch.Tensor:
+        return _create_mean_pooling_divisor(
+            lengths=features.lengths(), keys=features.keys(), offsets=features.offsets(), stride=features.stride(),
+            dim_per_key=self._dim_per_key, mean_features=self._pooling_type_to_rs_features()[PoolingType.MEAN.value],
+            embedding_names=self._embedding_names, embedding_dims=self._embedding_dims, kjt_key_indices=self._kjt_key_indices,
+            kt_key_ordering=self._kt_key_ordering, weights=features.weights_or_none() if self._is_weighted else None)
 
     def _create_inverse_indices_permute_indices(self, inverse_indices: Optional[Tuple[List[str], torch.Tensor]]) -> None:
         assert inverse_indices is not None, "inverse indices must be provided from KJT if using variable batch size per feature."

@@ -97,41 +97,36 @@ class RecMetricModule(nn.Module):
                  throughput_metric: Optional[ThroughputMetric] = None, state_metrics: Optional[Dict[str, StateMetric]] = None,
                  compute_interval_steps: int = 100, min_compute_interval: float = 0.0, max_compute_interval: float = float("inf")) -> None:
         super().__init__()
-        self.rec_tasks = rec_tasks if rec_tasks else []
-        self.rec_metrics = rec_metrics if rec_metrics else RecMetricList([])
+        self.batch_size, self.world_size = batch_size, world_size
+        self.rec_tasks = list(rec_tasks or [])
+        self.rec_metrics = rec_metrics or RecMetricList([])
         self.throughput_metric = throughput_metric
-        self.state_metrics = state_metrics if state_metrics else {}
-        self.trained_batches: int = 0
-        self.batch_size = batch_size
-        self.world_size = world_size
-        self.oom_count = 0
-        self.compute_count = 0
+        self.state_metrics = dict(state_metrics or {})
+        self.trained_batches = self.oom_count = self.compute_count = 0
         self.compute_interval_steps = compute_interval_steps
-        self.min_compute_interval = min_compute_interval
-        self.max_compute_interval = max_compute_interval
-        if self.min_compute_interval == 0.0 and self.max_compute_interval == float("inf"):
-            self.min_compute_interval = -1.0
-            self.max_compute_interval = -1.0
-        else:
-            if self.max_compute_interval <= 0.0:
-                raise ValueError("Max compute interval should not be smaller than or equal to 0.")
-            if self.min_compute_interval < 0.0:
-                raise ValueError("Min compute interval should not be smaller than 0.")
         self.last_compute_time = -1.0
+        # time bounds on the compute interval are either both left at their defaults (switched off, stored as -1) or validated
+        timed = (min_compute_interval, max_compute_interval) != (0.0, float("inf"))
+        if timed and max_compute_interval <= 0.0:
+            raise ValueError("Max compute interval should not be smaller than or equal to 0.")
+        if timed and min_compute_interval < 0.0:
+            raise ValueError("Min compute interval should not be smaller than 0.")
+        self.min_compute_interval, self.max_compute_interval = (min_compute_interval, max_compute_interval) if timed else (-1.0, -1.0)
 
     def _update_rec_metrics(self, model_out: Dict[str, torch.Tensor], **kwargs: Any) -> None:
-        if self.rec_metrics and self.rec_tasks:
-            labels, predictions, weights, required_inputs = parse_task_model_outputs(self.rec_tasks, model_out, self.get_required_inputs())
-            if required_inputs:
-                kwargs["required_inputs"] = required_inputs
-            self.rec_metrics.update(predictions=predictions, labels=labels, weights=weights, **kwargs)
+        if not (self.rec_metrics and self.rec_tasks):
+            return
+        labels, predictions, weights, extra = parse_task_model_outputs(self.rec_tasks, model_out, self.get_required_inputs())
+        if extra:
+            kwargs["required_inputs"] = extra
+        self.rec_metrics.update(predictions=predictions, labels=labels, weights=weights, **kwargs)
 
     def update(self, model_out: Dict[str, torch.Tensor], **kwargs: Any) -> None:
         """Feed one batch of model outputs to every metric and count it for throughput."""
         self._update_rec_metrics(model_out, **kwargs)
-        if self.throughput_metric:
-            self.throughput_metric.update()
         self.trained_batches += 1
+        if self.throughput_metric is not None:
+            self.throughput_metric.update()
 
     def _adjust_compute_interval(self) -> None:
         """After the second compute: steps-per-interval from the measured time per step, the same on every rank."""
@@ -158,27 +153,26 @@ class RecMetricModule(nn.Module):
     def should_compute(self) -> bool:
         return self.trained_batches % self.compute_interval_steps == 0
 
+    def _throughput_values(self) -> Dict[str, MetricValue]:
+        return dict(self.throughput_metric.compute()) if self.throughput_metric is not None else {}
+
     def compute(self) -> Dict[str, MetricValue]:
         """All metric values; every rank must call it (the states are combined across ranks)."""
         self.compute_count += 1
-        ret: Dict[str, MetricValue] = {}
+        values: Dict[str, MetricValue] = {}
         if self.rec_metrics:
             self._adjust_compute_interval()
-            ret.update(self.rec_metrics.compute())
-        if self.throughput_metric:
-            ret.update(self.throughput_metric.compute())
-        if self.state_metrics:
-            for namespace, component in self.state_metrics.items():
-                ret.update({compose_customized_metric_key(namespace, k): v for k, v in component.get_metrics().items()})
-        return ret
+            values.update(self.rec_metrics.compute())
+        values.update(self._throughput_values())
+        for namespace, component in self.state_metrics.items():
+            for key, value in component.get_metrics().items():
+                values[compose_customized_metric_key(namespace, key)] = value
+        return values
 
     def local_compute(self) -> Dict[str, MetricValue]:
-        ret: Dict[str, MetricValue] = {}
-        if self.rec_metrics:
-            ret.update(self.rec_metrics.local_compute())
-        if self.throughput_metric:
-            ret.update(self.throughput_metric.compute())
-        return ret
+        values: Dict[str, MetricValue] = dict(self.rec_metrics.local_compute()) if self.rec_metrics else {}
+        values.update(self._throughput_values())
+        return values
 
     def sync(self) -> None:
         self.rec_metrics.sync()
@@ -242,31 +236,25 @@ class RecMetricModule(nn.Module):
 
 def _generate_rec_metrics(metrics_config: MetricsConfig, world_size: int, my_rank: int, batch_size: int,
                           process_group: Optional[dist.ProcessGroup] = None, batch_size_stages: Optional[List[BatchSizeStage]] = None) -> RecMetricList:
-    rec_metrics = []
-    for metric_enum, metric_def in metrics_config.rec_metrics.items():
-        kwargs: Dict[str, Any] = {}
-        if metric_def and metric_def.arguments is not None:
-            kwargs = dict(metric_def.arguments)
-        if metric_enum == RecMetricEnum.LOG_LOSS:
-            kwargs["include_logloss"] = True
-        rec_tasks: List[RecTaskInfo] = []
-        if metric_def.rec_tasks and metric_def.rec_task_indices:
+    shared = dict(world_size=world_size, my_rank=my_rank, batch_size=batch_size, compute_mode=metrics_config.rec_compute_mode,
+                  fused_update_limit=metrics_config.fused_update_limit, compute_on_all_ranks=metrics_config.compute_on_all_ranks,
+                  should_validate_update=metrics_config.should_validate_update, process_group=process_group)
+
+    def tasks_of(metric_def) -> List[RecTaskInfo]:
+        by_object, by_index = metric_def.rec_tasks, metric_def.rec_task_indices
+        if by_object and by_index:
             raise ValueError("Only one of RecMetricDef.rec_tasks and RecMetricDef.rec_task_indices should be specified.")
-        if metric_def.rec_tasks:
-            rec_tasks = metric_def.rec_tasks
-        elif metric_def.rec_task_indices:
-            rec_tasks = [metrics_config.rec_tasks[i] for i in metric_def.rec_task_indices]
-        else:
+        if not by_object and not by_index:
             raise ValueError("One of RecMetricDef.rec_tasks and RecMetricDef.rec_task_indices should be a non-empty list")
-        rec_metrics.append(
-            REC_METRICS_MAPPING[metric_enum](
-                world_size=world_size, my_rank=my_rank, batch_size=batch_size, tasks=rec_tasks, compute_mode=metrics_config.rec_compute_mode,
-                window_size=metric_def.window_size, fused_update_limit=metrics_config.fused_update_limit,
-                compute_on_all_ranks=metrics_config.compute_on_all_ranks, should_validate_update=metrics_config.should_validate_update,
-                process_group=process_group, **kwargs,
-            )
-        )
-    return RecMetricList(rec_metrics)
+        return by_object or [metrics_config.rec_tasks[i] for i in by_index]
+
+    built = []
+    for kind, metric_def in metrics_config.rec_metrics.items():
+        own = dict(metric_def.arguments or {}) if metric_def else {}
+        if kind == RecMetricEnum.LOG_LOSS:  # log loss is the NE computation with one more output
+            own["include_logloss"] = True
+        built.append(REC_METRICS_MAPPING[kind](tasks=tasks_of(metric_def), window_size=metric_def.window_size, **shared, **own))
+    return RecMetricList(built)
 
 
 STATE_METRICS_NAMESPACE_MAPPING: Dict[StateMetricEnum, str] = {
@@ -286,16 +274,15 @@ def generate_metric_module(metric_class: Type[RecMetricModule], metrics_config: 
                            process_group: Optional[dist.ProcessGroup] = None, batch_size_stages: Optional[List[BatchSizeStage]] = None) -> RecMetricModule:
     """Build the metric module described by ``metrics_config`` and move it to ``device``."""
     validate_batch_size_stages(batch_size_stages)
-    rec_metrics = _generate_rec_metrics(metrics_config, world_size, my_rank, batch_size, process_group, batch_size_stages)
-    throughput_metric = None
-    if metrics_config.throughput_metric:
-        throughput_metric = ThroughputMetric(batch_size=batch_size, world_size=world_size, window_seconds=metrics_config.throughput_metric.window_size,
-                                             warmup_steps=metrics_config.throughput_metric.warmup_steps, batch_size_stages=batch_size_stages)
-    state_metrics = _generate_state_metrics(metrics_config, state_metrics_mapping)
-    metrics = metric_class(
-        batch_size=batch_size, world_size=world_size, rec_tasks=metrics_config.rec_tasks, rec_metrics=rec_metrics, throughput_metric=throughput_metric,
-        state_metrics=state_metrics, compute_interval_steps=metrics_config.compute_interval_steps,
-        min_compute_interval=metrics_config.min_compute_interval, max_compute_interval=metrics_config.max_compute_interval,
+    cfg = metrics_config
+    throughput = None
+    if cfg.throughput_metric:
+        throughput = ThroughputMetric(batch_size=batch_size, world_size=world_size, window_seconds=cfg.throughput_metric.window_size,
+                                      warmup_steps=cfg.throughput_metric.warmup_steps, batch_size_stages=batch_size_stages)
+    module = metric_class(
+        batch_size=batch_size, world_size=world_size, rec_tasks=cfg.rec_tasks,
+        rec_metrics=_generate_rec_metrics(cfg, world_size, my_rank, batch_size, process_group, batch_size_stages), throughput_metric=throughput,
+        state_metrics=_generate_state_metrics(cfg, state_metrics_mapping), compute_interval_steps=cfg.compute_interval_steps,
+        min_compute_interval=cfg.min_compute_interval, max_compute_interval=cfg.max_compute_interval,
     )
-    metrics.to(device)
-    return metrics
+    return module.to(device)
