@@ -98,3 +98,57 @@ def test_qtbe_kernel_matches_cpu(bits, pooling):
     out = gpu(kjt.values().cuda(), kjt.offsets().cuda(), None if psw is None else psw.cuda())
     gpu.check_error()
     torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-4)
+
+
+def test_quant_fp_ebc_matches_float():
+    """Position-weighted pooled lookups: the quantized module applies the same processors and pools with their weights."""
+    from torchrec_b200.modules.feature_processor_ import PositionWeightedModuleCollection
+    from torchrec_b200.modules.fp_embedding_modules import FeatureProcessedEmbeddingBagCollection
+    from torchrec_b200.quant.embedding_modules import FeatureProcessedEmbeddingBagCollection as QFPEBC
+
+    tables = [EmbeddingBagConfig(name="t0", num_embeddings=40, embedding_dim=16, feature_names=["f0"], pooling=PoolingType.SUM),
+              EmbeddingBagConfig(name="t1", num_embeddings=30, embedding_dim=16, feature_names=["f1"], pooling=PoolingType.SUM)]
+    torch.manual_seed(0)
+    fp = PositionWeightedModuleCollection({"f0": 8, "f1": 8})
+    with torch.no_grad():
+        for p in fp.parameters():
+            p.uniform_(0.5, 1.5)
+    fp_ebc = FeatureProcessedEmbeddingBagCollection(EmbeddingBagCollection(tables, is_weighted=True), fp)
+    fp_ebc.qconfig = _qconfig(torch.quint8)
+    q = QFPEBC.from_float(fp_ebc)
+    assert q._get_name() == "QuantFeatureProcessedEmbeddingBagCollection"
+    kjt = _kjt(["f0", "f1"], [40, 30])
+    ref, out = fp_ebc(kjt), q(kjt)
+    assert out.keys() == ref.keys()
+    torch.testing.assert_close(out.values(), ref.values().detach(), rtol=0, atol=0.08)
+    with pytest.raises(AssertionError):
+        QFPEBC(tables, True, torch.device("cpu"))
+
+
+def test_quant_mc_ec_remaps_then_looks_up():
+    """Raw ids go through the trained id map, then into the quantized table; the remapped KJT comes back with the rows."""
+    from torchrec_b200.modules.mc_embedding_modules import ManagedCollisionEmbeddingCollection
+    from torchrec_b200.modules.mc_modules import LFU_EvictionPolicy, ManagedCollisionCollection, MCHManagedCollisionModule
+    from torchrec_b200.quant.embedding_modules import QuantManagedCollisionEmbeddingCollection
+
+    cfg = EmbeddingConfig(name="t", num_embeddings=8, embedding_dim=16, feature_names=["f"])
+    torch.manual_seed(0)
+    ec = EmbeddingCollection(tables=[cfg])
+    mcc = ManagedCollisionCollection({"t": MCHManagedCollisionModule(zch_size=8, device=torch.device("cpu"), eviction_policy=LFU_EvictionPolicy(), eviction_interval=1)}, [cfg])
+    mc_ec = ManagedCollisionEmbeddingCollection(ec, mcc, return_remapped_features=True)
+    raw = KeyedJaggedTensor.from_lengths_sync(keys=["f"], values=torch.tensor([1000, 2000, 1000, 3000, 1000]), lengths=torch.tensor([2, 3]))
+    mc_ec.train()
+    for _ in range(3):
+        mc_ec(raw)
+    mc_ec.eval()
+    ref_out, ref_remapped = mc_ec(raw)
+    mc_ec.qconfig = _qconfig(torch.float16)
+    q = QuantManagedCollisionEmbeddingCollection.from_float(mc_ec)
+    out, remapped = q(raw)
+    assert torch.equal(remapped.values(), ref_remapped.values())
+    torch.testing.assert_close(out["f"].values(), ref_out["f"].values().detach(), rtol=0, atol=5e-3)
+    assert torch.equal(out["f"].lengths(), ref_out["f"].lengths())
+    # serving does not learn: unseen ids fall back to the modulo slot and the map stays as it was
+    before = q._managed_collision_collection._managed_collision_modules["t"]._mch_sorted_raw_ids.clone()
+    q(KeyedJaggedTensor.from_lengths_sync(keys=["f"], values=torch.tensor([777, 778]), lengths=torch.tensor([1, 1])))
+    assert torch.equal(before, q._managed_collision_collection._managed_collision_modules["t"]._mch_sorted_raw_ids)

@@ -165,3 +165,84 @@ def test_shard_quant_model_splits_tables_that_do_not_fit():
     q2, _ = _quantized(DataType.INT8, False)
     _, roomy = shard_quant_model(torch.nn.Sequential(q2), world_size=2, compute_device="cpu", device_memory_size=10 * sum(sizes.values()))
     assert {ps.sharding_type for ps in roomy.plan["0"].values()} == {"table_wise"}
+
+
+def test_sharded_state_reassembles_the_unsharded_tables():
+    """The checkpoint view of a sharded serving module: pieces carry offsets that put the unsharded packed table back together."""
+    q, tables = _quantized(DataType.INT8, False)
+    W = 3
+    plan = {"tw": ParameterSharding(sharding_type="table_wise", compute_kernel="quant", ranks=[1]),
+            "rw_sum": ParameterSharding(sharding_type="row_wise", compute_kernel="quant", ranks=list(range(W))),
+            "rw_mean": ParameterSharding(sharding_type="row_wise", compute_kernel="quant", ranks=list(range(W))),
+            "cw": ParameterSharding(sharding_type="column_wise", compute_kernel="quant", ranks=[2, 0, 1])}
+    sharded = ShardedQuantEmbeddingBagCollection(q, plan, ShardingEnv.from_local(world_size=W, rank=0), device=torch.device("cpu"))
+    sd = sharded.sharded_state_dict(prefix="m.")
+    for t in tables:
+        packed = q.embedding_bags[t.name].weight
+        payload = t.embedding_dim  # int8: one byte per element
+        got = sd[f"m.embedding_bags.{t.name}.weight"]
+        tail = sd[f"m.embedding_bags.{t.name}.weight_qscalebias"]
+        if t.name == "tw":
+            assert torch.equal(got, packed[:, :payload]) and torch.equal(tail, packed[:, payload:])
+            continue
+        rebuilt = torch.zeros(t.num_embeddings, payload, dtype=torch.uint8)
+        for sh in got.local_shards():
+            (r0, c0), (nr, nc) = sh.metadata.shard_offsets, sh.metadata.shard_sizes
+            rebuilt[r0: r0 + nr, c0: c0 + nc] = sh.tensor
+        assert torch.equal(rebuilt, packed[:, :payload]), t.name
+        for sh in tail.local_shards():
+            r0, nr = sh.metadata.shard_offsets[0], sh.metadata.shard_sizes[0]
+            assert torch.equal(sh.tensor, packed[r0: r0 + nr, payload:])
+
+
+def test_sharded_quant_fp_ebc_and_mc_ec_match_unsharded():
+    import torch.ao.quantization as tq
+
+    from torchrec_b200.distributed.quant_embedding import QuantManagedCollisionEmbeddingCollectionSharder, ShardedQuantManagedCollisionEmbeddingCollection
+    from torchrec_b200.distributed.quant_embeddingbag import QuantFeatureProcessedEmbeddingBagCollectionSharder, ShardedQuantFeatureProcessedEmbeddingBagCollection
+    from torchrec_b200.modules.embedding_configs import EmbeddingConfig, QuantConfig
+    from torchrec_b200.modules.embedding_modules import EmbeddingCollection
+    from torchrec_b200.modules.feature_processor_ import PositionWeightedModuleCollection
+    from torchrec_b200.modules.fp_embedding_modules import FeatureProcessedEmbeddingBagCollection
+    from torchrec_b200.modules.mc_embedding_modules import ManagedCollisionEmbeddingCollection
+    from torchrec_b200.modules.mc_modules import LFU_EvictionPolicy, ManagedCollisionCollection, MCHManagedCollisionModule
+    from torchrec_b200.quant.embedding_modules import FeatureProcessedEmbeddingBagCollection as QFPEBC
+    from torchrec_b200.quant.embedding_modules import QuantManagedCollisionEmbeddingCollection as QMCEC
+
+    qconfig = QuantConfig(activation=tq.PlaceholderObserver.with_args(dtype=torch.float), weight=tq.PlaceholderObserver.with_args(dtype=torch.qint8))
+    torch.manual_seed(2)
+    tables = [EmbeddingBagConfig(name="a", embedding_dim=16, num_embeddings=33, feature_names=["fa"], pooling=PoolingType.SUM),
+              EmbeddingBagConfig(name="b", embedding_dim=32, num_embeddings=21, feature_names=["fb"], pooling=PoolingType.SUM)]
+    fp = PositionWeightedModuleCollection({"fa": 6, "fb": 6})
+    with torch.no_grad():
+        for p in fp.parameters():
+            p.uniform_(0.5, 1.5)
+    fp_ebc = FeatureProcessedEmbeddingBagCollection(EmbeddingBagCollection(tables, is_weighted=True), fp)
+    fp_ebc.qconfig = qconfig
+    q = QFPEBC.from_float(fp_ebc)
+    plan = {"a": ParameterSharding(sharding_type="row_wise", compute_kernel="quant", ranks=[0, 1]),
+            "b": ParameterSharding(sharding_type="column_wise", compute_kernel="quant", ranks=[1, 0])}
+    sharder = QuantFeatureProcessedEmbeddingBagCollectionSharder()
+    assert sharder.module_type is QFPEBC
+    sharded = sharder.shard(q, plan, ShardingEnv.from_local(world_size=2, rank=0), torch.device("cpu"))
+    assert isinstance(sharded, ShardedQuantFeatureProcessedEmbeddingBagCollection)
+    kjt = _kjt(tables, 7, False, 3)
+    torch.testing.assert_close(sharded(kjt).values(), q(kjt).values(), rtol=1e-5, atol=1e-6)
+
+    cfg = EmbeddingConfig(name="t", num_embeddings=8, embedding_dim=16, feature_names=["f"])
+    ec = EmbeddingCollection(tables=[cfg])
+    mcc = ManagedCollisionCollection({"t": MCHManagedCollisionModule(zch_size=8, device=torch.device("cpu"), eviction_policy=LFU_EvictionPolicy(), eviction_interval=1)}, [cfg])
+    mc_ec = ManagedCollisionEmbeddingCollection(ec, mcc, return_remapped_features=True)
+    raw = KeyedJaggedTensor.from_lengths_sync(keys=["f"], values=torch.tensor([1000, 2000, 1000, 3000, 1000, 4000]), lengths=torch.tensor([2, 4]))
+    mc_ec.train()
+    for _ in range(3):
+        mc_ec(raw)
+    mc_ec.eval()
+    mc_ec.qconfig = qconfig
+    qmc = QMCEC.from_float(mc_ec)
+    sharded_mc = QuantManagedCollisionEmbeddingCollectionSharder().shard(
+        qmc, {"t": ParameterSharding(sharding_type="row_wise", compute_kernel="quant", ranks=[0, 1])}, ShardingEnv.from_local(world_size=2, rank=0), torch.device("cpu"))
+    assert isinstance(sharded_mc, ShardedQuantManagedCollisionEmbeddingCollection)
+    (want, want_ids), (got, got_ids) = qmc(raw), sharded_mc(raw)
+    assert torch.equal(want_ids.values(), got_ids.values())
+    torch.testing.assert_close(got["f"].values(), want["f"].values(), rtol=1e-5, atol=1e-6)

@@ -189,7 +189,7 @@ def bench_sparse_kernels(B: int, n: int, warm: int) -> None:
     from torchrec_b200.ops import sparse_ops as sops
 
     F, pf, rows, W = 26, 8, 4_000_000, 8
-    lengths = torch.full((F * B,), pf, dtype=torch.int32, device="cuda")
+    lengths = torch.full((F * B,), pf, dtype=torch.int64, device="cuda")
     idx = torch.randint(0, rows, (F * B * pf,), device="cuda", dtype=torch.int64)
     block = torch.full((F,), (rows + W - 1) // W, dtype=torch.int64, device="cuda")
     t = timeit(lambda: sops.block_bucketize_sparse_features(lengths, idx, bucketize_pos=False, sequence=False, block_sizes=block, my_size=W), n, warm)

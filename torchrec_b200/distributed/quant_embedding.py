@@ -11,11 +11,13 @@ from torch import nn
 from torchrec_b200.distributed.embedding_types import BaseQuantEmbeddingSharder
 from torchrec_b200.distributed.quant_embeddingbag import _device_for
 from torchrec_b200.distributed.types import ParameterSharding, ShardingEnv, ShardingType
+from torchrec_b200.distributed.quant_state import ShardedQuantEmbeddingModuleState
 from torchrec_b200.quant.embedding_modules import EmbeddingCollection as QuantEmbeddingCollection
+from torchrec_b200.quant.embedding_modules import QuantManagedCollisionEmbeddingCollection
 from torchrec_b200.sparse.jagged_tensor import JaggedTensor, KeyedJaggedTensor
 
 
-class ShardedQuantEmbeddingCollection(nn.Module):
+class ShardedQuantEmbeddingCollection(ShardedQuantEmbeddingModuleState, nn.Module):
     """Sequence (unpooled) quantized lookups over the local devices.  ``table_wise``: whole table on ``ranks[0]``.  ``row_wise``: equal
     row blocks over all devices; ids are bucketized by block, every device returns the rows of its ids, and the rows are put back in
     request order.  ``column_wise``: one column range per entry of ``ranks`` (distinct devices); the ranges of every id are
@@ -89,6 +91,7 @@ class ShardedQuantEmbeddingCollection(nn.Module):
         self._rw_out_names: List[str] = [module._name_of[f"{cfg.name}:{f}"] for cfg, _ in self._rw_tables for f in cfg.feature_names]
         self.register_buffer("_rw_block_sizes", torch.tensor([b for cfg, b in self._rw_tables for _ in cfg.feature_names], dtype=torch.int64), persistent=False)
         self._name_of = dict(module._name_of)
+        self._init_quant_state("embeddings", {c.name: table_name_to_parameter_sharding[c.name].sharding_type for c in self._configs})
 
     def forward(self, features: KeyedJaggedTensor) -> Dict[str, JaggedTensor]:
         from torchrec_b200.distributed.embedding_sharding import bucketize_kjt_before_all2all
@@ -145,3 +148,36 @@ class QuantEmbeddingCollectionSharder(BaseQuantEmbeddingSharder[QuantEmbeddingCo
     @property
     def module_type(self) -> Type[QuantEmbeddingCollection]:
         return QuantEmbeddingCollection
+
+
+class ShardedQuantManagedCollisionEmbeddingCollection(ShardedQuantEmbeddingCollection):
+    """Sharded form of the quantized managed-collision collection.  The id maps stay whole on the device that receives the
+    request (a sorted id array per table: megabytes against gigabytes of rows), ids are remapped there and the remapped ids are
+    then distributed like any others.  ``forward`` returns ``(embeddings, remapped KJT)``
+    (``torchrec/distributed/quant_embedding.py:1003-1260``)."""
+
+    def __init__(self, module: QuantManagedCollisionEmbeddingCollection, table_name_to_parameter_sharding: Dict[str, ParameterSharding],
+                 env: ShardingEnv, fused_params: Optional[Dict[str, Any]] = None, device: Optional[torch.device] = None) -> None:
+        super().__init__(module, table_name_to_parameter_sharding, env, fused_params, device)
+        self._managed_collision_collection = module._managed_collision_collection
+        self._return_remapped_features = module._return_remapped_features
+
+    def forward(self, features: KeyedJaggedTensor):  # type: ignore[override]
+        remapped = self._managed_collision_collection(features)
+        return super().forward(remapped), remapped
+
+
+class QuantManagedCollisionEmbeddingCollectionSharder(BaseQuantEmbeddingSharder[QuantManagedCollisionEmbeddingCollection]):
+    def shard(self, module: QuantManagedCollisionEmbeddingCollection, params: Dict[str, ParameterSharding], env: ShardingEnv,
+              device: Optional[torch.device] = None, module_fqn: Optional[str] = None) -> ShardedQuantManagedCollisionEmbeddingCollection:
+        return ShardedQuantManagedCollisionEmbeddingCollection(module, params, env, getattr(self, "fused_params", None), device)
+
+    def shardable_parameters(self, module: QuantManagedCollisionEmbeddingCollection) -> Dict[str, torch.Tensor]:
+        return {name: m.weight for name, m in module.embeddings.items()}
+
+    def sharding_types(self, compute_device_type: str) -> List[str]:
+        return [ShardingType.TABLE_WISE.value, ShardingType.ROW_WISE.value, ShardingType.COLUMN_WISE.value]
+
+    @property
+    def module_type(self) -> Type[QuantManagedCollisionEmbeddingCollection]:
+        return QuantManagedCollisionEmbeddingCollection

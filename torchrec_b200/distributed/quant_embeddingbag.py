@@ -17,7 +17,9 @@ from torch import nn
 from torchrec_b200.distributed.embedding_types import BaseQuantEmbeddingSharder
 from torchrec_b200.distributed.types import ParameterSharding, ShardingEnv, ShardingType
 from torchrec_b200.modules.embedding_configs import PoolingType
+from torchrec_b200.distributed.quant_state import ShardedQuantEmbeddingModuleState
 from torchrec_b200.quant.embedding_modules import EmbeddingBagCollection as QuantEmbeddingBagCollection
+from torchrec_b200.quant.embedding_modules import FeatureProcessedEmbeddingBagCollection as QuantFeatureProcessedEmbeddingBagCollection
 from torchrec_b200.quant.embedding_modules import EmbeddingCollection as QuantEmbeddingCollection
 from torchrec_b200.sparse.jagged_tensor import JaggedTensor, KeyedJaggedTensor, KeyedTensor
 
@@ -26,7 +28,7 @@ def _device_for(rank: int, device_type: str) -> torch.device:
     return torch.device("cuda", rank) if device_type == "cuda" else torch.device(device_type)
 
 
-class ShardedQuantEmbeddingBagCollection(nn.Module):
+class ShardedQuantEmbeddingBagCollection(ShardedQuantEmbeddingModuleState, nn.Module):
     """Placement per table: ``table_wise`` (whole table on ``ranks[0]``), ``row_wise`` (equal row blocks over all devices; ids are
     bucketized by block, every device pools its part, the parts are summed) or ``column_wise`` (one column range per entry of
     ``ranks``, all on distinct devices; every device pools its columns, the ranges are concatenated).  Quantized rows are cut
@@ -122,6 +124,8 @@ class ShardedQuantEmbeddingBagCollection(nn.Module):
                 self._name_table[self._embedding_names[i]] = cfg.name
                 i += 1
 
+        self._init_quant_state("embedding_bags", {c.name: table_name_to_parameter_sharding[c.name].sharding_type for c in self._configs})
+
     def _local(self, features: KeyedJaggedTensor, keys: List[str], names: List[str], rank: int) -> KeyedJaggedTensor:
         return features.permute([keys.index(f) for f in names]).to(_device_for(rank, self._device_type), non_blocking=True)
 
@@ -181,3 +185,37 @@ class QuantEmbeddingBagCollectionSharder(BaseQuantEmbeddingSharder[QuantEmbeddin
     @property
     def module_type(self) -> Type[QuantEmbeddingBagCollection]:
         return QuantEmbeddingBagCollection
+
+
+class ShardedQuantFeatureProcessedEmbeddingBagCollection(ShardedQuantEmbeddingBagCollection):
+    """Sharded form of the quantized feature-processed collection: the processors (position weights, a few KB) run once on
+    the request before it is cut up for the devices; the per-id weights they produce travel with the ids
+    (``torchrec/distributed/quant_embeddingbag.py:471-620``)."""
+
+    def __init__(self, module: QuantFeatureProcessedEmbeddingBagCollection, table_name_to_parameter_sharding: Dict[str, ParameterSharding],
+                 env: ShardingEnv, fused_params: Optional[Dict[str, Any]] = None, device: Optional[torch.device] = None) -> None:
+        super().__init__(module, table_name_to_parameter_sharding, env, fused_params, device)
+        self.feature_processor = copy.deepcopy(module.feature_processor)
+
+    def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
+        fp = self.feature_processor
+        first = next(fp.parameters(), None)
+        if first is not None and first.device != features.values().device:
+            fp.to(features.values().device)
+        return super().forward(fp(features))
+
+
+class QuantFeatureProcessedEmbeddingBagCollectionSharder(BaseQuantEmbeddingSharder[QuantFeatureProcessedEmbeddingBagCollection]):
+    def shard(self, module: QuantFeatureProcessedEmbeddingBagCollection, params: Dict[str, ParameterSharding], env: ShardingEnv,
+              device: Optional[torch.device] = None, module_fqn: Optional[str] = None) -> ShardedQuantFeatureProcessedEmbeddingBagCollection:
+        return ShardedQuantFeatureProcessedEmbeddingBagCollection(module, params, env, getattr(self, "fused_params", None), device)
+
+    def shardable_parameters(self, module: QuantFeatureProcessedEmbeddingBagCollection) -> Dict[str, torch.Tensor]:
+        return {name: m.weight for name, m in module.embedding_bags.items()}
+
+    def sharding_types(self, compute_device_type: str) -> List[str]:
+        return [ShardingType.TABLE_WISE.value, ShardingType.ROW_WISE.value, ShardingType.COLUMN_WISE.value]
+
+    @property
+    def module_type(self) -> Type[QuantFeatureProcessedEmbeddingBagCollection]:
+        return QuantFeatureProcessedEmbeddingBagCollection

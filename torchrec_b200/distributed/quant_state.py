@@ -36,6 +36,82 @@ def get_param_id_from_type(is_sqebc: bool, is_sqmcec: bool, is_sfpebc: bool) -> 
     return "embeddings"
 
 
+class ShardedQuantEmbeddingModuleState:
+    """Checkpoint view of a sharded quantized collection under the UNSHARDED module's keys: ``<container>.<table>.weight`` is the
+    packed table itself when it sits whole on one device, else a ``ShardedTensorBase`` whose local shards are the per-device
+    pieces with their (row, payload-byte column) offsets; sub-16-bit tables also expose ``weight_qscalebias`` (the two fp16
+    row parameters).  A publishing tool can thus read or overwrite a sharded serving model table by table without knowing where the
+    pieces live.  The module provides ``_configs``, ``_shards`` / ``_rw_shards`` / ``_cw_shards`` and the row-block / column-order
+    tables filled in by its constructor (``torchrec/distributed/quant_state.py:70-380``)."""
+
+    def _init_quant_state(self, container: str, sharding_type_by_table: Dict[str, str]) -> None:
+        self._state_container = container
+        self._state_sharding = dict(sharding_type_by_table)
+
+    def _pieces_of(self, table: str):
+        """(row offset, payload column offset, packed rows) of every device's piece of ``table``."""
+        kind = self._state_sharding[table]
+        full = {c.name: c for c in self._configs}[table]
+        bits = BITS[full.data_type]
+        if kind == ShardingType.TABLE_WISE.value:
+            for shard in self._shards:
+                if hasattr(shard, self._state_container) and table in getattr(shard, self._state_container):
+                    yield 0, 0, getattr(shard, self._state_container)[table].weight
+        elif kind == ShardingType.ROW_WISE.value:
+            block = {c.name: b for c, b in self._rw_tables}[table]
+            for rank, shard in enumerate(self._rw_shards):
+                rows = max(0, min(block, full.num_embeddings - rank * block))
+                if rows > 0 and hasattr(shard, self._state_container):
+                    yield rank * block, 0, getattr(shard, self._state_container)[table].weight[:rows]
+        else:
+            shards = self._cw_shards
+            by_rank = dict(enumerate(shards)) if not isinstance(shards, torch.nn.ModuleDict) else None
+            order = self._cw_order[table] if hasattr(self, "_cw_order") else next(r for c, r, _ in self._cw_tables if c.name == table)
+            width_bytes = full.embedding_dim // len(order) * bits // 8
+            for j, rank in enumerate(order):
+                if by_rank is not None:
+                    shard = by_rank[rank]
+                else:
+                    shard = shards[f"{rank}_{full.embedding_dim // len(order)}"]
+                yield 0, j * width_bytes, getattr(shard, self._state_container)[table].weight
+
+    def sharded_state_dict(self, prefix: str = "") -> Dict[str, object]:
+        from torch.distributed._shard.sharded_tensor import Shard, ShardedTensorBase, ShardedTensorMetadata, ShardMetadata
+        from torch.distributed._shard.sharded_tensor.metadata import TensorProperties
+
+        out: Dict[str, object] = {}
+        for cfg in self._configs:
+            bits = BITS[cfg.data_type]
+            payload = cfg.embedding_dim * bits // 8
+            pieces = list(self._pieces_of(cfg.name))
+            key = f"{prefix}{self._state_container}.{cfg.name}.weight"
+            if self._state_sharding[cfg.name] == ShardingType.TABLE_WISE.value:
+                whole = pieces[0][2]
+                out[key] = whole[:, :payload] if bits < 16 else whole
+                if bits < 16:
+                    out[key + "_qscalebias"] = whole[:, payload: payload + 4]
+                continue
+            shards, tails = [], []
+            for row_off, col_off, packed in pieces:
+                width = packed.shape[1] - (4 if bits < 16 else 0)
+                meta = ShardMetadata(shard_offsets=[row_off, col_off], shard_sizes=[packed.shape[0], width], placement=f"rank:0/{packed.device}")
+                shards.append(Shard(tensor=packed[:, :width], metadata=meta))
+                if bits < 16:
+                    tails.append(Shard(tensor=packed[:, width: width + 4],
+                                       metadata=ShardMetadata(shard_offsets=[row_off, 4 * (col_off // max(width, 1))], shard_sizes=[packed.shape[0], 4], placement=f"rank:0/{packed.device}")))
+
+            def wrap(parts, size):
+                props = TensorProperties(dtype=parts[0].tensor.dtype)
+                meta = ShardedTensorMetadata(shards_metadata=[p.metadata for p in parts], size=torch.Size(size), tensor_properties=props)
+                return ShardedTensorBase._init_from_local_shards_and_global_metadata(parts, meta)
+
+            out[key] = wrap(shards, [cfg.num_embeddings, payload])
+            if tails:
+                n_col = len({p.metadata.shard_offsets[1] for p in tails})
+                out[key + "_qscalebias"] = wrap(tails, [cfg.num_embeddings, 4 * n_col])
+        return out
+
+
 def sharded_tbes_weights_spec(sharded_model: torch.nn.Module, virtual_table_name_to_bucket_lengths: Optional[Dict[str, List[int]]] = None) -> Dict[str, WeightSpec]:
     """Walk ``sharded_model`` for sharded quantized collections and describe every table shard of every kernel."""
     from torchrec_b200.distributed.quant_embedding import ShardedQuantEmbeddingCollection

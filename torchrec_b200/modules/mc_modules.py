@@ -148,6 +148,10 @@ class ManagedCollisionModule(nn.Module):
         ...
 
     @abc.abstractmethod
+    def reset_inference_mode(self) -> None:
+        """Called when the module is moved into a serving (quantized) model: drop whatever only training needs."""
+        return None
+
     def rebuild_with_output_id_range(self, output_id_range: Tuple[int, int], output_segments: List[int], device: Optional[torch.device] = None) -> "ManagedCollisionModule":
         ...
 
@@ -298,6 +302,12 @@ class MCHManagedCollisionModule(ManagedCollisionModule):
             self._evicted = False
             return self._evicted_emb_indices
         return None
+
+    def reset_inference_mode(self) -> None:
+        """Serving keeps the id -> slot map and nothing else: no pending eviction report, no admission candidates."""
+        self._evicted, self._last_eviction_iter = False, -1
+        self._evicted_emb_indices = self._evicted_emb_indices[:0]
+        self._history_ids, self._history_counts, self._history_last = self._history_ids[:0], self._history_counts[:0], self._history_last[:0]
 
     def rebuild_with_output_id_range(self, output_id_range: Tuple[int, int], output_segments: List[int], device: Optional[torch.device] = None) -> "MCHManagedCollisionModule":
         return type(self)(zch_size=int(output_id_range[1] - output_id_range[0]), device=device or self.device, eviction_policy=self._eviction_policy,

@@ -122,6 +122,12 @@ class _QuantCollectionBase(nn.Module):
             self._feature_splits.append(len(ftm))
         self._feature_names: List[str] = [f for group in self._group_tables for t in group for f in t.feature_names]
 
+    def _packed_tables(self):
+        """(table config, packed rows as stored by the kernel) for every table."""
+        for group, emb in zip(self._group_tables, self._emb_modules):
+            for i, t in enumerate(group):
+                yield t, emb.table_view(i)
+
     def _split_scale_bias_state(self, destination: Dict[str, Any], prefix: str) -> None:
         for group, emb in zip(self._group_tables, self._emb_modules):
             for i, t in enumerate(group):
@@ -239,6 +245,43 @@ class EmbeddingBagCollection(EmbeddingBagCollectionInterface, _QuantCollectionBa
         return self._output_dtype
 
 
+class FeatureProcessedEmbeddingBagCollection(EmbeddingBagCollection):
+    """Quantized pooled lookups behind feature processors (position weights and the like): the processors rewrite the per-id
+    weights of the incoming KJT, the quantized kernel pools with them (``torchrec/quant/embedding_modules.py:633-731``)."""
+
+    def __init__(self, tables: List[EmbeddingBagConfig], is_weighted: bool, device: torch.device, output_dtype: torch.dtype = torch.float,
+                 table_name_to_quantized_weights: Optional[Dict[str, Tuple[torch.Tensor, Optional[torch.Tensor]]]] = None,
+                 register_tbes: bool = False, quant_state_dict_split_scale_bias: bool = False, row_alignment: int = DEFAULT_ROW_ALIGNMENT,
+                 feature_processor: Optional[nn.Module] = None, cache_features_order: bool = False) -> None:
+        if feature_processor is None:
+            raise AssertionError("Use EmbeddingBagCollection for no feature_processor")
+        super().__init__(tables, is_weighted, device, output_dtype, table_name_to_quantized_weights, register_tbes,
+                         quant_state_dict_split_scale_bias, row_alignment, cache_features_order)
+        self.feature_processor = feature_processor
+
+    def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
+        return super().forward(self.feature_processor(features))
+
+    def _get_name(self) -> str:
+        return "QuantFeatureProcessedEmbeddingBagCollection"
+
+    @classmethod
+    def from_float(cls, module: nn.Module, use_precomputed_fake_quant: bool = False) -> "FeatureProcessedEmbeddingBagCollection":
+        assert hasattr(module, "qconfig"), "FeatureProcessedEmbeddingBagCollection input float module must have qconfig defined"
+        inner = module._embedding_bag_collection
+        # the wrapped collection is converted by the plain class method, under the wrapper's settings
+        for attr in ("qconfig", MODULE_ATTR_EMB_CONFIG_NAME_TO_NUM_ROWS_POST_PRUNING_DICT, MODULE_ATTR_REGISTER_TBES_BOOL):
+            if hasattr(module, attr):
+                setattr(inner, attr, getattr(module, attr))
+        plain = EmbeddingBagCollection.from_float(inner)
+        packed = {t.name: (w, None) for t, w in plain._packed_tables()}
+        return cls(plain.embedding_bag_configs(), plain.is_weighted(), device=plain.device, output_dtype=plain.output_dtype(),
+                   table_name_to_quantized_weights=packed, register_tbes=getattr(module, MODULE_ATTR_REGISTER_TBES_BOOL, False),
+                   quant_state_dict_split_scale_bias=getattr(inner, MODULE_ATTR_QUANT_STATE_DICT_SPLIT_SCALE_BIAS, False),
+                   row_alignment=getattr(inner, MODULE_ATTR_ROW_ALIGNMENT_INT, DEFAULT_ROW_ALIGNMENT),
+                   feature_processor=module._feature_processors, cache_features_order=getattr(module, MODULE_ATTR_CACHE_FEATURES_ORDER, False))
+
+
 class EmbeddingCollection(EmbeddingCollectionInterface, _QuantCollectionBase):
     """Quantized unpooled lookups: ``forward(KJT) -> Dict[feature, JaggedTensor]``."""
 
@@ -309,3 +352,54 @@ class EmbeddingCollection(EmbeddingCollectionInterface, _QuantCollectionBase):
 
     def output_dtype(self) -> torch.dtype:
         return self._output_dtype
+
+
+class QuantManagedCollisionEmbeddingCollection(EmbeddingCollection):
+    """Quantized unpooled lookups behind managed-collision modules: raw ids are first mapped to table slots by the trained id
+    maps (serving never admits or evicts), then looked up.  ``forward`` returns ``(embeddings, remapped KJT)``
+    (``torchrec/quant/embedding_modules.py:1029-1190``)."""
+
+    def __init__(self, tables: List[EmbeddingConfig], device: torch.device, need_indices: bool = False, output_dtype: torch.dtype = torch.float,
+                 table_name_to_quantized_weights: Optional[Dict[str, Tuple[torch.Tensor, Optional[torch.Tensor]]]] = None,
+                 register_tbes: bool = False, quant_state_dict_split_scale_bias: bool = False, row_alignment: int = DEFAULT_ROW_ALIGNMENT,
+                 managed_collision_collection: Optional[nn.Module] = None, return_remapped_features: bool = False,
+                 cache_features_order: bool = False) -> None:
+        if not managed_collision_collection:
+            raise AssertionError("Managed collision collection cannot be None")
+        super().__init__(tables, device, need_indices, output_dtype, table_name_to_quantized_weights, register_tbes,
+                         quant_state_dict_split_scale_bias, row_alignment, cache_features_order)
+        self._managed_collision_collection = managed_collision_collection
+        self._return_remapped_features = return_remapped_features
+        ours = [(t.name, t.num_embeddings, t.embedding_dim, tuple(t.feature_names)) for t in self.embedding_configs()]
+        theirs = [(t.name, t.num_embeddings, t.embedding_dim, tuple(t.feature_names)) for t in managed_collision_collection.embedding_configs()]
+        assert ours == theirs, "Embedding Collection and Managed Collision Collection must contain the same Embedding Configs"
+        managed_collision_collection.eval()
+        for mc in managed_collision_collection._managed_collision_modules.values():
+            mc.reset_inference_mode()
+
+    def forward(self, features: KeyedJaggedTensor):
+        remapped = self._managed_collision_collection(features)
+        return super().forward(remapped), remapped
+
+    def _get_name(self) -> str:
+        return "QuantManagedCollisionEmbeddingCollection"
+
+    @classmethod
+    def from_float(cls, module: nn.Module, return_remapped_features: bool = False) -> "QuantManagedCollisionEmbeddingCollection":
+        assert hasattr(module, "qconfig"), "QuantManagedCollisionEmbeddingCollection input float module must have qconfig defined"
+        inner = module._embedding_module
+        if isinstance(inner, EmbeddingCollection):  # already quantized: take its packed tables as they are
+            plain = inner
+        else:
+            inner.qconfig = module.qconfig
+            plain = EmbeddingCollection.from_float(inner)
+        mcc = module._managed_collision_collection
+        for cfg, qcfg in zip(mcc.embedding_configs(), plain.embedding_configs()):
+            cfg.data_type = qcfg.data_type
+        packed = {t.name: (w, None) for t, w in plain._packed_tables()}
+        return cls(plain.embedding_configs(), device=plain.device, need_indices=plain.need_indices(), output_dtype=plain.output_dtype(),
+                   table_name_to_quantized_weights=packed, register_tbes=getattr(module, MODULE_ATTR_REGISTER_TBES_BOOL, False),
+                   quant_state_dict_split_scale_bias=getattr(inner, MODULE_ATTR_QUANT_STATE_DICT_SPLIT_SCALE_BIAS, False),
+                   row_alignment=getattr(inner, MODULE_ATTR_ROW_ALIGNMENT_INT, DEFAULT_ROW_ALIGNMENT), managed_collision_collection=mcc,
+                   return_remapped_features=getattr(module, "_return_remapped_features", return_remapped_features),
+                   cache_features_order=getattr(inner, MODULE_ATTR_CACHE_FEATURES_ORDER, False))

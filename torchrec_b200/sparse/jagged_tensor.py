@@ -128,15 +128,12 @@ class JaggedTensor(Pipelineable, metaclass=JaggedTensorMeta):
         lengths: Optional[torch.Tensor] = None,
         offsets: Optional[torch.Tensor] = None,
     ) -> None:
-        self._values: torch.Tensor = values
-        self._weights: Optional[torch.Tensor] = weights
         _assert_offsets_or_lengths_is_provided(offsets, lengths)
-        if offsets is not None:
-            _assert_tensor_has_no_elements_or_has_integers(offsets, "offsets")
-        if lengths is not None:
-            _assert_tensor_has_no_elements_or_has_integers(lengths, "lengths")
-        self._lengths: Optional[torch.Tensor] = lengths
-        self._offsets: Optional[torch.Tensor] = offsets
+        for name, t in (("offsets", offsets), ("lengths", lengths)):
+            if t is not None:
+                _assert_tensor_has_no_elements_or_has_integers(t, name)
+        self._values, self._weights = values, weights
+        self._lengths, self._offsets = lengths, offsets
 
     @staticmethod
     def empty(
@@ -370,25 +367,18 @@ class KeyedJaggedTensor(Pipelineable, metaclass=JaggedTensorMeta):
         jt_dict: Optional[Dict[str, JaggedTensor]] = None,
         inverse_indices: Optional[Tuple[List[str], torch.Tensor]] = None,
     ) -> None:
-        self._keys: List[str] = keys
-        self._values: torch.Tensor = values
-        self._weights: Optional[torch.Tensor] = weights
-        self._lengths: Optional[torch.Tensor] = lengths
-        self._offsets: Optional[torch.Tensor] = offsets
-        self._stride: Optional[int] = stride
-        if stride_per_key_per_rank is not None and not isinstance(stride_per_key_per_rank, torch.Tensor):
-            stride_per_key_per_rank = torch.tensor(stride_per_key_per_rank, dtype=torch.int64, device="cpu").view(
-                len(stride_per_key_per_rank), -1
-            )
-        self._stride_per_key_per_rank: Optional[torch.Tensor] = stride_per_key_per_rank
-        self._stride_per_key: Optional[List[int]] = stride_per_key
-        self._length_per_key: Optional[List[int]] = length_per_key
-        self._offset_per_key: Optional[List[int]] = offset_per_key
-        self._lengths_offset_per_key: Optional[List[int]] = lengths_offset_per_key
-        self._index_per_key: Optional[Dict[str, int]] = index_per_key
-        self._jt_dict: Optional[Dict[str, JaggedTensor]] = jt_dict
-        self._inverse_indices: Optional[Tuple[List[str], torch.Tensor]] = inverse_indices
         _assert_offsets_or_lengths_is_provided(offsets, lengths)
+        # the data: ids (+ weights) of all keys back to back, and how they split into bags
+        self._keys, self._values, self._weights = keys, values, weights
+        self._lengths, self._offsets, self._stride = lengths, offsets, stride
+        if stride_per_key_per_rank is not None and not isinstance(stride_per_key_per_rank, torch.Tensor):
+            rows = len(stride_per_key_per_rank)
+            stride_per_key_per_rank = torch.tensor(stride_per_key_per_rank, dtype=torch.int64, device="cpu").view(rows, -1)
+        self._stride_per_key_per_rank = stride_per_key_per_rank
+        self._inverse_indices = inverse_indices
+        # host-side caches: computed lazily, or handed over by a producer that already knows them (split, permute, dist)
+        self._stride_per_key, self._index_per_key, self._jt_dict = stride_per_key, index_per_key, jt_dict
+        self._length_per_key, self._offset_per_key, self._lengths_offset_per_key = length_per_key, offset_per_key, lengths_offset_per_key
 
     # ---- constructors ---------------------------------------------------------------
     @staticmethod
@@ -424,33 +414,20 @@ class KeyedJaggedTensor(Pipelineable, metaclass=JaggedTensorMeta):
     @staticmethod
     def concat(kjt_list: List["KeyedJaggedTensor"]) -> "KeyedJaggedTensor":
         """Concatenate along the key dimension (all inputs share the batch)."""
-        if len(kjt_list) == 0:
+        if not kjt_list:
             raise ValueError("Can't concat empty KJT list")
-        is_weighted = kjt_list[0].weights_or_none() is not None
-        has_length_per_key = True
-        keys: List[str] = []
-        length_per_key: List[int] = []
-        stride_per_key_rows = []
+        first = kjt_list[0]
+        weighted = first.weights_or_none() is not None
         variable = any(k.variable_stride_per_key() for k in kjt_list)
-        for kjt in kjt_list:
-            if kjt._length_per_key is None:
-                has_length_per_key = False
-            else:
-                length_per_key += kjt._length_per_key
-            keys += kjt.keys()
-            if variable:
-                stride_per_key_rows.append(kjt.stride_per_key_per_rank_tensor())
-        stride, spkpr = (
-            (None, torch.cat(stride_per_key_rows, dim=0)) if variable else (kjt_list[0].stride(), None)
-        )
+        known = [k._length_per_key for k in kjt_list]  # the cached per-key totals survive only if every input has them
         return KeyedJaggedTensor(
-            keys=keys,
+            keys=[key for k in kjt_list for key in k.keys()],
             values=torch.cat([k.values() for k in kjt_list], dim=0),
-            weights=torch.cat([k.weights() for k in kjt_list], dim=0) if is_weighted else None,
+            weights=torch.cat([k.weights() for k in kjt_list], dim=0) if weighted else None,
             lengths=torch.cat([k.lengths() for k in kjt_list], dim=0),
-            stride=stride,
-            stride_per_key_per_rank=spkpr,
-            length_per_key=length_per_key if has_length_per_key else None,
+            stride=None if variable else first.stride(),
+            stride_per_key_per_rank=torch.cat([k.stride_per_key_per_rank_tensor() for k in kjt_list], dim=0) if variable else None,
+            length_per_key=[n for per in known for n in per] if all(per is not None for per in known) else None,
         )
 
     @staticmethod
@@ -474,26 +451,17 @@ class KeyedJaggedTensor(Pipelineable, metaclass=JaggedTensorMeta):
     @staticmethod
     def from_jt_dict(jt_dict: Dict[str, JaggedTensor]) -> "KeyedJaggedTensor":
         """Build from per-key ``JaggedTensor``s that all have the same batch size."""
-        kjt_keys = list(jt_dict.keys())
-        kjt_vals_list, kjt_lens_list, kjt_weights_list = [], [], []
-        stride_per_key: List[int] = []
-        for jt in jt_dict.values():
-            stride_per_key.append(len(jt.lengths()))
-            kjt_vals_list.append(jt.values())
-            kjt_lens_list.append(jt.lengths())
-            if jt.weights_or_none() is not None:
-                kjt_weights_list.append(jt.weights())
-        kjt_vals = torch.concat(kjt_vals_list)
-        kjt_lens = torch.concat(kjt_lens_list)
-        kjt_weights = torch.concat(kjt_weights_list) if len(kjt_weights_list) > 0 else None
-        kjt_stride, kjt_spkpr = (
-            (stride_per_key[0], None)
-            if all(s == stride_per_key[0] for s in stride_per_key)
-            else (None, [[s] for s in stride_per_key])
-        )
+        jts = list(jt_dict.values())
+        batch_sizes = [jt.lengths().numel() for jt in jts]
+        uniform = len(set(batch_sizes)) <= 1
+        weights = [jt.weights() for jt in jts if jt.weights_or_none() is not None]
         return KeyedJaggedTensor(
-            keys=kjt_keys, values=kjt_vals, weights=kjt_weights, lengths=kjt_lens,
-            stride=kjt_stride, stride_per_key_per_rank=kjt_spkpr,
+            keys=list(jt_dict.keys()),
+            values=torch.cat([jt.values() for jt in jts]),
+            weights=torch.cat(weights) if weights else None,
+            lengths=torch.cat([jt.lengths() for jt in jts]),
+            stride=(batch_sizes[0] if batch_sizes else 0) if uniform else None,
+            stride_per_key_per_rank=None if uniform else [[b] for b in batch_sizes],
         ).sync()
 
     # ---- caches ---------------------------------------------------------------------
@@ -611,52 +579,34 @@ class KeyedJaggedTensor(Pipelineable, metaclass=JaggedTensorMeta):
     # ---- restructuring --------------------------------------------------------------
     def split(self, segments: List[int]) -> List["KeyedJaggedTensor"]:
         """Split along keys into consecutive groups of ``segments[i]`` keys."""
-        split_list: List[KeyedJaggedTensor] = []
-        start = 0
-        start_offset = 0
-        _length_per_key = self.length_per_key()
-        _offset_per_key = self.offset_per_key()
-        spkpr = self._stride_per_key_per_rank
-        lopk = self.lengths_offset_per_key() if self.variable_stride_per_key() else None
-        for segment in segments:
-            end = start + segment
-            end_offset = _offset_per_key[end]
-            keys = self._keys[start:end]
-            sub_spkpr = spkpr[start:end, :] if spkpr is not None else None
-            if segment == len(self._keys):
-                split_list.append(self)
-            elif segment == 0:
-                split_list.append(
-                    KeyedJaggedTensor(
-                        keys=keys,
-                        values=torch.empty(0, device=self.device(), dtype=self._values.dtype),
-                        weights=None if self._weights is None else torch.empty(0, device=self.device(), dtype=self._weights.dtype),
-                        lengths=torch.empty(0, device=self.device(), dtype=self.lengths().dtype),
-                        offsets=torch.empty(0, device=self.device(), dtype=self.lengths().dtype),
-                        stride=self._stride,
-                        stride_per_key_per_rank=sub_spkpr,
-                    )
-                )
+        n_keys = len(self._keys)
+        totals, id_bounds = self.length_per_key(), self.offset_per_key()
+        strides = self._stride_per_key_per_rank
+        bag_bounds = self.lengths_offset_per_key() if self.variable_stride_per_key() else [k * self.stride() for k in range(n_keys + 1)]
+
+        def empty_like_me(dtype: torch.dtype) -> torch.Tensor:
+            return torch.empty(0, device=self.device(), dtype=dtype)
+
+        pieces: List[KeyedJaggedTensor] = []
+        k0 = 0
+        for width in segments:
+            k1 = k0 + width
+            sub_strides = None if strides is None else strides[k0:k1, :]
+            if width == n_keys:  # the whole thing: no copy, caches kept
+                pieces.append(self)
+            elif width == 0:
+                bag_dtype = self.lengths().dtype
+                pieces.append(KeyedJaggedTensor(
+                    keys=[], values=empty_like_me(self._values.dtype), weights=None if self._weights is None else empty_like_me(self._weights.dtype),
+                    lengths=empty_like_me(bag_dtype), offsets=empty_like_me(bag_dtype), stride=self._stride, stride_per_key_per_rank=sub_strides))
             else:
-                if lopk is not None:
-                    l0, l1 = lopk[start], lopk[end]
-                else:
-                    l0, l1 = start * self.stride(), end * self.stride()
-                split_list.append(
-                    KeyedJaggedTensor(
-                        keys=keys,
-                        values=self._values[start_offset:end_offset],
-                        weights=None if self._weights is None else self._weights[start_offset:end_offset],
-                        lengths=self.lengths()[l0:l1],
-                        offsets=None,
-                        stride=self._stride,
-                        stride_per_key_per_rank=sub_spkpr,
-                        length_per_key=_length_per_key[start:end],
-                    )
-                )
-            start = end
-            start_offset = end_offset
-        return split_list
+                ids = slice(id_bounds[k0], id_bounds[k1])
+                pieces.append(KeyedJaggedTensor(
+                    keys=self._keys[k0:k1], values=self._values[ids], weights=None if self._weights is None else self._weights[ids],
+                    lengths=self.lengths()[bag_bounds[k0]: bag_bounds[k1]], stride=self._stride, stride_per_key_per_rank=sub_strides,
+                    length_per_key=totals[k0:k1]))
+            k0 = k1
+        return pieces
 
     def permute(self, indices: List[int], indices_tensor: Optional[torch.Tensor] = None) -> "KeyedJaggedTensor":
         """Reorder (or repeat / drop) keys."""
@@ -717,17 +667,11 @@ class KeyedJaggedTensor(Pipelineable, metaclass=JaggedTensorMeta):
         )
 
     def __getitem__(self, key: str) -> JaggedTensor:
-        offset_per_key = self.offset_per_key()
-        index = self._key_indices()[key]
-        start_offset = offset_per_key[index]
-        end_offset = offset_per_key[index + 1] if index + 1 < len(offset_per_key) else start_offset
-        lopk = self.lengths_offset_per_key()
-        return JaggedTensor(
-            values=self._values[start_offset:end_offset],
-            weights=None if self._weights is None else self._weights[start_offset:end_offset],
-            lengths=self.lengths()[lopk[index]: lopk[index + 1]],
-            offsets=None,
-        )
+        k = self._key_indices()[key]
+        id_bounds, bag_bounds = self.offset_per_key(), self.lengths_offset_per_key()
+        ids = slice(id_bounds[k], id_bounds[k + 1]) if k + 1 < len(id_bounds) else slice(id_bounds[k], id_bounds[k])
+        return JaggedTensor(values=self._values[ids], weights=None if self._weights is None else self._weights[ids],
+                            lengths=self.lengths()[bag_bounds[k]: bag_bounds[k + 1]])
 
     def to_dict(self) -> Dict[str, JaggedTensor]:
         if self._jt_dict is None:
@@ -806,32 +750,28 @@ class KeyedJaggedTensor(Pipelineable, metaclass=JaggedTensorMeta):
         return out + "})\n"
 
     # ---- distributed protocol -------------------------------------------------------
+    def _dist_parts(self) -> List[str]:
+        """What travels in the input all-to-all, in order: bag lengths and ids always; per-key batch sizes when every key has
+        its own; per-id weights when present."""
+        optional = (("strides", self.variable_stride_per_key()), ("weights", self.weights_or_none() is not None))
+        return ["lengths", "values"] + [name for name, present in optional if present]
+
     def dist_labels(self) -> List[str]:
-        labels = ["lengths", "values"]
-        if self.variable_stride_per_key():
-            labels.append("strides")
-        if self.weights_or_none() is not None:
-            labels.append("weights")
-        return labels
+        return self._dist_parts()
 
     def dist_splits(self, key_splits: List[int]) -> List[List[int]]:
-        batch_size_per_split = _sum_by_splits(self.stride_per_key(), key_splits)
-        length_per_split = _sum_by_splits(self.length_per_key(), key_splits)
-        splits = [batch_size_per_split, length_per_split]
-        if self.variable_stride_per_key():
-            splits.append(key_splits)
-        if self.weights_or_none() is not None:
-            splits.append(length_per_split)
-        return splits
+        """Per part of :meth:`dist_labels`, how many elements go to every destination."""
+        bags = _sum_by_splits(self.stride_per_key(), key_splits)
+        ids = _sum_by_splits(self.length_per_key(), key_splits)
+        per_part = {"lengths": bags, "values": ids, "strides": key_splits, "weights": ids}
+        return [per_part[name] for name in self._dist_parts()]
 
     def dist_tensors(self) -> List[torch.Tensor]:
-        tensors = [self.lengths(), self.values()]
-        if self.variable_stride_per_key():
-            strides = torch.tensor(self.stride_per_key(), dtype=torch.int64).to(self.device(), non_blocking=True)
-            tensors.append(strides)
-        if self.weights_or_none() is not None:
-            tensors.append(self.weights())
-        return tensors
+        def strides_on_device() -> torch.Tensor:
+            return torch.tensor(self.stride_per_key(), dtype=torch.int64).to(self.device(), non_blocking=True)
+
+        per_part = {"lengths": self.lengths, "values": self.values, "strides": strides_on_device, "weights": self.weights}
+        return [per_part[name]() for name in self._dist_parts()]
 
     @staticmethod
     def dist_init(
@@ -849,46 +789,33 @@ class KeyedJaggedTensor(Pipelineable, metaclass=JaggedTensorMeta):
         that each key's bags from all ranks are contiguous.
         """
         assert len(tensors) in (2, 3, 4)
-        lengths, values = tensors[0], tensors[1]
-        stride_per_rank_per_key = tensors[2] if variable_stride_per_key else None
-        weights = (
-            tensors[-1]
-            if (variable_stride_per_key and len(tensors) == 4) or (not variable_stride_per_key and len(tensors) == 3)
-            else None
-        )
+        parts = ["lengths", "values"] + (["strides"] if variable_stride_per_key else [])
+        named = dict(zip(parts + ["weights"], tensors))  # weights, when sent, come last
+        lengths, values, weights = named["lengths"], named["values"], named.get("weights")
         if variable_stride_per_key:
-            assert stride_per_rank_per_key is not None
-            spkpr = stride_per_rank_per_key.view(num_workers, len(keys)).T.cpu()
-            strides_cumsum = sops.asynchronous_complete_cumsum(stride_per_rank_per_key).to(torch.int64)
-            cumsum_lengths = sops.asynchronous_complete_cumsum(lengths)
-            length_per_key_tensor = cumsum_lengths[strides_cumsum[1:]] - cumsum_lengths[strides_cumsum[:-1]]
+            sent_strides = named["strides"]  # (source rank, key)-major batch sizes
+            matrix = sent_strides.view(num_workers, len(keys)).T.cpu()
             if recat is not None:
-                lengths, _ = _permute_tensor_by_segments(lengths, stride_per_rank_per_key, recat, None)
-                values, weights = _permute_tensor_by_segments(values, length_per_key_tensor, recat, weights)
-            if spkpr.numel() == 0:
-                spkpr = torch.zeros((len(keys), 1), device="cpu", dtype=torch.int64)
+                bag_bounds = sops.asynchronous_complete_cumsum(sent_strides).to(torch.int64)
+                id_prefix = sops.asynchronous_complete_cumsum(lengths)
+                ids_per_segment = id_prefix[bag_bounds[1:]] - id_prefix[bag_bounds[:-1]]
+                lengths, _ = _permute_tensor_by_segments(lengths, sent_strides, recat, None)
+                values, weights = _permute_tensor_by_segments(values, ids_per_segment, recat, weights)
+            if matrix.numel() == 0:
+                matrix = torch.zeros((len(keys), 1), device="cpu", dtype=torch.int64)
             if stagger > 1:
-                idx = torch.arange(num_workers).view(stagger, -1).T.reshape(-1)
-                spkpr = spkpr[:, idx]
-            return KeyedJaggedTensor(
-                keys=keys, values=values, weights=weights, lengths=lengths, stride_per_key_per_rank=spkpr
-            ).sync()
+                matrix = matrix[:, torch.arange(num_workers).view(stagger, -1).T.reshape(-1)]
+            return KeyedJaggedTensor(keys=keys, values=values, weights=weights, lengths=lengths, stride_per_key_per_rank=matrix).sync()
         assert stride_per_rank is not None
         if recat is not None:
-            stride = stride_per_rank[0]
-            if all(s == stride for s in stride_per_rank):
-                if stride > 0:
-                    lengths, values, weights = sops.permute_2D_sparse_data(
-                        recat, lengths.view(-1, stride), values, weights, values.numel()
-                    )
-                    lengths = lengths.view(-1)
-            else:
-                lengths, values, weights = sops.permute_1D_sparse_data(
-                    recat, lengths.view(-1), values, weights, values.numel()
-                )
-        return KeyedJaggedTensor(
-            keys=keys, values=values, weights=weights, lengths=lengths, stride=sum(stride_per_rank)
-        ).sync()
+            same_batch_everywhere = len(set(stride_per_rank)) <= 1
+            if not same_batch_everywhere:
+                lengths, values, weights = sops.permute_1D_sparse_data(recat, lengths.view(-1), values, weights, values.numel())
+            elif stride_per_rank and stride_per_rank[0] > 0:
+                rows = lengths.view(-1, stride_per_rank[0])
+                rows, values, weights = sops.permute_2D_sparse_data(recat, rows, values, weights, values.numel())
+                lengths = rows.view(-1)
+        return KeyedJaggedTensor(keys=keys, values=values, weights=weights, lengths=lengths, stride=sum(stride_per_rank)).sync()
 
 
 def _kjt_flatten(t: KeyedJaggedTensor):
