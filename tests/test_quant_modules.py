@@ -152,3 +152,40 @@ def test_quant_mc_ec_remaps_then_looks_up():
     before = q._managed_collision_collection._managed_collision_modules["t"]._mch_sorted_raw_ids.clone()
     q(KeyedJaggedTensor.from_lengths_sync(keys=["f"], values=torch.tensor([777, 778]), lengths=torch.tensor([1, 1])))
     assert torch.equal(before, q._managed_collision_collection._managed_collision_modules["t"]._mch_sorted_raw_ids)
+
+
+def _forward_into_case(device):
+    from torchrec_b200.modules.embedding_configs import PoolingMode
+    from torchrec_b200.ops.qtbe import QuantTableBatchedEmbeddingBags
+    from torchrec_b200.ops.quant_ops import quantize_rowwise_nbit
+
+    torch.manual_seed(3)
+    specs = [(300, 64, 8), (50, 128, 4)]
+    ftm = [0, 1, 1]
+    m = QuantTableBatchedEmbeddingBags(specs, ftm, PoolingMode.SUM, torch.float32, device=device)
+    for t, (r, d, b) in enumerate(specs):
+        m.table_view(t).copy_(quantize_rowwise_nbit(torch.randn(r, d), b).to(device))
+    # bags long enough that the id fetch (32 per round) and the row unrolling both wrap around
+    g = torch.Generator().manual_seed(0)
+    B = 17
+    lens = torch.randint(0, 80, (3 * B,), generator=g)
+    rows = [300, 50, 50]
+    vals = torch.cat([torch.randint(0, rows[k], (int(lens[k * B:(k + 1) * B].sum()),), generator=g) for k in range(3)])
+    off = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)])
+    want = m(vals.to(device), off.to(device))
+    out = torch.full((B + 2, 400), -1.0, device=device)
+    cols = [130, 0, 260]  # any order, with gaps
+    m.forward_into(vals.to(device), off.to(device), None, out, cols)
+    for f, c in enumerate(cols):
+        d = m.D_offsets[f + 1] - m.D_offsets[f]
+        torch.testing.assert_close(out[:B, c: c + d], want[:, m.D_offsets[f]: m.D_offsets[f + 1]], rtol=1e-5, atol=1e-5)
+    assert bool((out[B:] == -1).all()) and bool((out[:, 128:130] == -1).all()) and bool((out[:, 194:260] == -1).all())
+
+
+def test_qtbe_forward_into_cpu():
+    _forward_into_case("cpu")
+
+
+@pytest.mark.gpu
+def test_qtbe_forward_into_gpu():
+    _forward_into_case("cuda")

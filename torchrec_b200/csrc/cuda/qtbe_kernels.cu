@@ -14,6 +14,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <ATen/cuda/PeerToPeerAccess.h>
+
 #include "common.cuh"
 
 namespace trb {
@@ -36,24 +38,89 @@ struct QFwdParams {
 
 __device__ __forceinline__ int64_t qrow_bytes(int D, int bits) { return bits >= 16 ? int64_t(D) * bits / 8 : int64_t(D) * bits / 8 + 4; }
 
-// elements [e, e+4) of one row as fp32
-__device__ __forceinline__ float4 qload4(const uint8_t* row, int D, int bits, int e) {
-  if (bits == 32) return *reinterpret_cast<const float4*>(row + int64_t(e) * 4);
-  if (bits == 16) return Vec4<__half>::load_plain(reinterpret_cast<const __half*>(row) + e);
-  const __half2 sb = *reinterpret_cast<const __half2*>(row + int64_t(D) * bits / 8);
+// elements [e, e+4) of one row as fp32; BITS is a compile-time constant so that the loads of several rows can be issued
+// back to back without a branch between them
+template <int BITS>
+__device__ __forceinline__ float4 qload4(const uint8_t* row, int D, int e) {
+  if (BITS == 32) return __ldg(reinterpret_cast<const float4*>(row + int64_t(e) * 4));
+  if (BITS == 16) return Vec4<__half>::load(reinterpret_cast<const __half*>(row) + e);
+  const __half2 sb = *reinterpret_cast<const __half2*>(row + int64_t(D) * BITS / 8);
   const float scale = __low2float(sb), bias = __high2float(sb);
   uint32_t q0, q1, q2, q3;
-  if (bits == 8) {
-    const uint32_t w = *reinterpret_cast<const uint32_t*>(row + e);
+  if (BITS == 8) {
+    const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(row + e));
     q0 = w & 0xff; q1 = (w >> 8) & 0xff; q2 = (w >> 16) & 0xff; q3 = w >> 24;
-  } else if (bits == 4) {
-    const uint32_t w = *reinterpret_cast<const uint16_t*>(row + e / 2);
+  } else if (BITS == 4) {
+    const uint32_t w = __ldg(reinterpret_cast<const uint16_t*>(row + e / 2));
     q0 = w & 0xf; q1 = (w >> 4) & 0xf; q2 = (w >> 8) & 0xf; q3 = (w >> 12) & 0xf;
   } else {  // 2 bits
-    const uint32_t w = row[e / 4];
+    const uint32_t w = __ldg(row + e / 4);
     q0 = w & 3; q1 = (w >> 2) & 3; q2 = (w >> 4) & 3; q3 = (w >> 6) & 3;
   }
   return make_float4(fmaf(scale, float(q0), bias), fmaf(scale, float(q1), bias), fmaf(scale, float(q2), bias), fmaf(scale, float(q3), bias));
+}
+
+
+// One bag (ids [start, end)) of one table.  Ids and weights are fetched 32 at a time, one per lane, and handed round by
+// shuffles; rows are then read kQUnroll at a time so that a warp keeps several DRAM requests in flight instead of one.
+template <int BITS, typename idx_t, int kVecs>
+__device__ __forceinline__ void qbag(const QFwdParams& p, const uint8_t* table, int64_t rb, int D, int64_t rows, int64_t start,
+                                     int64_t end, int lane, float4 (&acc)[kVecs]) {
+  constexpr int kQUnroll = kVecs >= 4 ? 2 : 4;  // rows whose loads are in flight together per warp (bounded by registers)
+  const idx_t* indices = reinterpret_cast<const idx_t*>(p.indices);
+  const bool unpooled = p.pooling == 2;
+  for (int64_t c = start; c < end; c += 32) {
+    const int n = int(min(int64_t(32), end - c));
+    int64_t my_r = 0;
+    float my_w = 0.f;
+    if (lane < n) {
+      my_r = int64_t(indices[c + lane]);
+      my_w = p.psw ? p.psw[c + lane] : 1.f;
+      if (my_r < 0 || my_r >= rows) {
+        atomicExch(p.err, 1);
+        my_r = 0;
+        my_w = 0.f;
+      }
+    }
+    for (int j0 = 0; j0 < n; j0 += kQUnroll) {
+      float4 x[kQUnroll][kVecs];
+      float w[kQUnroll];
+#pragma unroll
+      for (int u = 0; u < kQUnroll; ++u) {
+        const int j = min(j0 + u, n - 1);  // the tail re-reads the last row (weight 0 below)
+        const int64_t r = __shfl_sync(0xffffffffu, my_r, j);
+        w[u] = (j0 + u < n) ? __shfl_sync(0xffffffffu, my_w, j) : 0.f;
+        const uint8_t* row = table + r * rb;
+#pragma unroll
+        for (int v = 0; v < kVecs; ++v) {
+          const int e = v * 128 + lane * 4;
+          x[u][v] = e < D ? qload4<BITS>(row, D, e) : f4zero();
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kQUnroll; ++u) {
+        if (unpooled) {
+          if (j0 + u < n) {
+#pragma unroll
+            for (int v = 0; v < kVecs; ++v) {
+              const int e = v * 128 + lane * 4;
+              if (e < D) {
+                float4 y = x[u][v];
+                if (w[u] == 0.f) y = f4zero();  // an id outside the table yields a zero row
+                store4_dyn(p.out, (c + j0 + u) * p.out_stride + e, y, p.out_dtype);
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < kVecs; ++v) {
+            acc[v].x = fmaf(w[u], x[u][v].x, acc[v].x); acc[v].y = fmaf(w[u], x[u][v].y, acc[v].y);
+            acc[v].z = fmaf(w[u], x[u][v].z, acc[v].z); acc[v].w = fmaf(w[u], x[u][v].w, acc[v].w);
+          }
+        }
+      }
+    }
+  }
 }
 
 template <typename idx_t, int kVecs>
@@ -64,7 +131,6 @@ __global__ void __launch_bounds__(256) qtbe_fwd_kernel(QFwdParams p) {
   const int f = int(bag / p.B), b = int(bag - int64_t(f) * p.B);
   const int F = p.F;
   const idx_t* offsets = reinterpret_cast<const idx_t*>(p.offsets);
-  const idx_t* indices = reinterpret_cast<const idx_t*>(p.indices);
   const int64_t start = offsets[bag], end = offsets[bag + 1];
   const int D = int(p.meta[QM_DIM * F + f]), bits = int(p.meta[QM_BITS * F + f]);
   const int64_t rows = p.meta[QM_ROWS * F + f];
@@ -74,32 +140,12 @@ __global__ void __launch_bounds__(256) qtbe_fwd_kernel(QFwdParams p) {
   float4 acc[kVecs];
 #pragma unroll
   for (int v = 0; v < kVecs; ++v) acc[v] = f4zero();
-  for (int64_t i = start; i < end; ++i) {
-    int64_t r = int64_t(indices[i]);
-    float w = p.psw ? p.psw[i] : 1.f;
-    if (r < 0 || r >= rows) {
-      if (lane == 0) atomicExch(p.err, 1);
-      r = 0;
-      w = 0.f;
-    }
-    const uint8_t* row = table + r * rb;
-    if (p.pooling == 2) {
-#pragma unroll
-      for (int v = 0; v < kVecs; ++v) {
-        const int e = v * 128 + lane * 4;
-        if (e < D) store4_dyn(p.out, i * p.out_stride + e, qload4(row, D, bits, e), p.out_dtype);
-      }
-      continue;
-    }
-#pragma unroll
-    for (int v = 0; v < kVecs; ++v) {
-      const int e = v * 128 + lane * 4;
-      if (e < D) {
-        const float4 x = qload4(row, D, bits, e);
-        acc[v].x = fmaf(w, x.x, acc[v].x); acc[v].y = fmaf(w, x.y, acc[v].y);
-        acc[v].z = fmaf(w, x.z, acc[v].z); acc[v].w = fmaf(w, x.w, acc[v].w);
-      }
-    }
+  switch (bits) {
+    case 8: qbag<8, idx_t, kVecs>(p, table, rb, D, rows, start, end, lane, acc); break;
+    case 4: qbag<4, idx_t, kVecs>(p, table, rb, D, rows, start, end, lane, acc); break;
+    case 2: qbag<2, idx_t, kVecs>(p, table, rb, D, rows, start, end, lane, acc); break;
+    case 16: qbag<16, idx_t, kVecs>(p, table, rb, D, rows, start, end, lane, acc); break;
+    default: qbag<32, idx_t, kVecs>(p, table, rb, D, rows, start, end, lane, acc); break;
   }
   if (p.pooling == 2) return;
   if (p.pooling == 1 && end > start) {
@@ -114,33 +160,17 @@ __global__ void __launch_bounds__(256) qtbe_fwd_kernel(QFwdParams p) {
   }
 }
 
-at::Tensor qtbe_forward(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets,
-                        const c10::optional<at::Tensor>& psw, int64_t B, int64_t total_D, int64_t max_D, int64_t pooling,
-                        int64_t out_dtype, at::Tensor err) {
-  TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == at::kByte && weights.is_contiguous());
-  TORCH_CHECK(meta.size(0) == kQMetaRows && meta.scalar_type() == at::kLong && meta.is_contiguous());
-  TORCH_CHECK(indices.scalar_type() == offsets.scalar_type(), "indices and offsets must share a dtype");
-  TORCH_CHECK(max_D % 4 == 0 && max_D <= 1024, "embedding dims must be multiples of 4, at most 1024");
+static void qtbe_launch(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets,
+                        const c10::optional<at::Tensor>& psw, void* out, int64_t out_dtype, int64_t stride, int64_t B, int64_t max_D,
+                        int64_t pooling, at::Tensor& err) {
   const int F = int(meta.size(1));
-  c10::cuda::CUDAGuard guard(weights.device());
-  auto dt = out_dtype == OUT_F32 ? at::kFloat : (out_dtype == OUT_F16 ? at::kHalf : at::kBFloat16);
-  at::Tensor out;
-  int64_t stride;
-  if (pooling == 2) {
-    out = at::empty({indices.numel(), max_D}, weights.options().dtype(dt));
-    stride = max_D;
-  } else {
-    out = at::empty({B, total_D}, weights.options().dtype(dt));
-    stride = total_D;
-  }
-  if (F == 0 || B == 0) return out;
   QFwdParams p;
   p.weights = weights.data_ptr<uint8_t>();
   p.meta = meta.data_ptr<int64_t>();
   p.indices = indices.data_ptr();
   p.offsets = offsets.data_ptr();
   p.psw = psw.has_value() && psw->defined() ? psw->data_ptr<float>() : nullptr;
-  p.out = out.data_ptr();
+  p.out = out;
   p.out_dtype = int(out_dtype);
   p.out_stride = stride;
   p.B = int(B);
@@ -158,7 +188,54 @@ at::Tensor qtbe_forward(const at::Tensor& weights, const at::Tensor& meta, const
   if (nv == 1) { TRB_Q_LAUNCH(1) } else if (nv == 2) { TRB_Q_LAUNCH(2) } else if (nv == 4) { TRB_Q_LAUNCH(4) } else { TRB_Q_LAUNCH(8) }
 #undef TRB_Q_LAUNCH
   TRB_CUDA_CHECK(cudaGetLastError());
+}
+
+static void qtbe_check(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets, int64_t max_D) {
+  TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == at::kByte && weights.is_contiguous());
+  TORCH_CHECK(meta.size(0) == kQMetaRows && meta.scalar_type() == at::kLong && meta.is_contiguous());
+  TORCH_CHECK(indices.scalar_type() == offsets.scalar_type(), "indices and offsets must share a dtype");
+  TORCH_CHECK(max_D % 4 == 0 && max_D <= 1024, "embedding dims must be multiples of 4, at most 1024");
+}
+
+at::Tensor qtbe_forward(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets,
+                        const c10::optional<at::Tensor>& psw, int64_t B, int64_t total_D, int64_t max_D, int64_t pooling,
+                        int64_t out_dtype, at::Tensor err) {
+  qtbe_check(weights, meta, indices, offsets, max_D);
+  const int F = int(meta.size(1));
+  c10::cuda::CUDAGuard guard(weights.device());
+  auto dt = out_dtype == OUT_F32 ? at::kFloat : (out_dtype == OUT_F16 ? at::kHalf : at::kBFloat16);
+  at::Tensor out;
+  int64_t stride;
+  if (pooling == 2) {
+    out = at::empty({indices.numel(), max_D}, weights.options().dtype(dt));
+    stride = max_D;
+  } else {
+    out = at::empty({B, total_D}, weights.options().dtype(dt));
+    stride = total_D;
+  }
+  if (F == 0 || B == 0) return out;
+  qtbe_launch(weights, meta, indices, offsets, psw, out.data_ptr(), out_dtype, stride, B, max_D, pooling, err);
   return out;
+}
+
+// Pooled lookup stored into an existing [B, stride] buffer at the per-feature columns of `meta` (row QM_OUTOFF).  The buffer
+// may live on ANOTHER device of this process (the serving GPU that assembles the request's result): peer access is switched
+// on for the pair and the rows travel over NVLink as plain stores from this kernel; no copy kernel, no concatenation.
+void qtbe_forward_into(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets,
+                       const c10::optional<at::Tensor>& psw, at::Tensor out, int64_t B, int64_t max_D, int64_t pooling, at::Tensor err) {
+  qtbe_check(weights, meta, indices, offsets, max_D);
+  TORCH_CHECK(pooling != 2, "pooled lookups only");
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.size(0) >= B);
+  const int F = int(meta.size(1));
+  if (F == 0 || B == 0) return;
+  if (out.device() != weights.device()) {
+    TORCH_CHECK(at::cuda::get_p2p_access(weights.device().index(), out.device().index()),
+                "no peer access from device ", int(weights.device().index()), " to device ", int(out.device().index()));
+  }
+  c10::cuda::CUDAGuard guard(weights.device());
+  const int64_t code = out.scalar_type() == at::kFloat ? OUT_F32 : (out.scalar_type() == at::kHalf ? OUT_F16 : OUT_BF16);
+  TORCH_CHECK(code != OUT_BF16 || out.scalar_type() == at::kBFloat16, "output must be fp32, fp16 or bf16");
+  qtbe_launch(weights, meta, indices, offsets, psw, out.data_ptr(), code, out.stride(0), B, max_D, pooling, err);
 }
 
 }  // namespace trb
@@ -167,6 +244,12 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
   m.def(
       "qtbe_forward(Tensor weights, Tensor meta, Tensor indices, Tensor offsets, Tensor? psw, int B, int total_D, int max_D, "
       "int pooling, int out_dtype, Tensor(a!) err) -> Tensor");
+  m.def(
+      "qtbe_forward_into(Tensor weights, Tensor meta, Tensor indices, Tensor offsets, Tensor? psw, Tensor(a!) out, int B, int max_D, "
+      "int pooling, Tensor(b!) err) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(trb200, CUDA, m) { m.impl("qtbe_forward", &trb::qtbe_forward); }
+
+// dispatched by hand: `out` may sit on another device than the tables
+TORCH_LIBRARY_IMPL(trb200, CompositeExplicitAutograd, m) { m.impl("qtbe_forward_into", &trb::qtbe_forward_into); }

@@ -42,6 +42,7 @@ class ShardedQuantEmbeddingBagCollection(ShardedQuantEmbeddingModuleState, nn.Mo
 
         self._configs = module.embedding_bag_configs()
         self._is_weighted = module.is_weighted()
+        self._out_dtype = module.output_dtype()
         self._world_size = env.world_size
         self._device_type = (device.type if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
         self._out_device = device if device is not None else _device_for(0, self._device_type)
@@ -133,6 +134,8 @@ class ShardedQuantEmbeddingBagCollection(ShardedQuantEmbeddingModuleState, nn.Mo
         from torchrec_b200.distributed.embedding_sharding import bucketize_kjt_before_all2all
 
         keys = features.keys()
+        if self._device_type == "cuda" and not self._rw_feature_names:
+            return self._forward_direct(features, keys)
         pieces: Dict[str, torch.Tensor] = {}
         for rank, (shard, fnames) in enumerate(zip(self._shards, self._feature_names_per_rank)):
             if fnames:
@@ -162,6 +165,42 @@ class ShardedQuantEmbeddingBagCollection(ShardedQuantEmbeddingModuleState, nn.Mo
             pieces[name] = torch.cat([by_rank[r] for r in self._cw_order[self._name_table[name]]], dim=1)
         values = torch.cat([pieces[n] for n in self._embedding_names], dim=1)
         return KeyedTensor(keys=self._embedding_names, values=values, length_per_key=self._length_per_key)
+
+    def _forward_direct(self, features: KeyedJaggedTensor, keys: List[str]) -> KeyedTensor:
+        """Table-wise and column-wise shards on GPUs: every device's lookup kernel stores its pooled rows straight into the
+        result buffer on the output device, at the final column of each embedding (column shards at their offset inside it).
+        No per-table copy, no concatenation; the output device's stream waits for one event per contributing device."""
+        out_dev = self._out_device
+        col, start = {}, 0
+        for name, width in zip(self._embedding_names, self._length_per_key):
+            col[name] = start
+            start += width
+        out = torch.empty((features.stride(), start), dtype=self._out_dtype, device=out_dev)
+        out_stream = torch.cuda.current_stream(out_dev)
+        ready = torch.cuda.Event()
+        ready.record(out_stream)  # the buffer exists (allocator-wise) before a peer writes into it
+        done = []
+        for kind, shards, names_per_rank in (("tw", self._shards, self._feature_names_per_rank), ("cw", self._cw_shards, self._cw_feature_names_per_rank)):
+            for rank, (shard, fnames) in enumerate(zip(shards, names_per_rank)):
+                if not fnames:
+                    continue
+                dev = _device_for(rank, self._device_type)
+                local = self._local(features, keys, fnames, rank)
+                columns = dict(col)
+                if kind == "cw":
+                    for name in shard._embedding_names:
+                        order = self._cw_order[self._name_table[name]]
+                        columns[name] = col[name] + order.index(rank) * (self._length_per_key[self._embedding_names.index(name)] // len(order))
+                with torch.cuda.device(dev):
+                    stream = torch.cuda.current_stream(dev)
+                    stream.wait_event(ready)
+                    shard.forward_into(local, out, columns)
+                    ev = torch.cuda.Event()
+                    ev.record(stream)
+                    done.append(ev)
+        for ev in done:
+            out_stream.wait_event(ev)
+        return KeyedTensor(keys=self._embedding_names, values=out, length_per_key=self._length_per_key)
 
     def sharded_parameter_names(self, prefix: str = ""):
         for attr in ("_shards", "_rw_shards", "_cw_shards"):

@@ -77,6 +77,31 @@ class QuantTableBatchedEmbeddingBags(nn.Module):
                                                  int(self.pooling_mode), _OUT_CODE[self.output_dtype], self._err)
         return self._forward_cpu(indices, offsets, per_sample_weights, B)
 
+    def forward_into(self, indices: torch.Tensor, offsets: torch.Tensor, per_sample_weights: Optional[torch.Tensor], out: torch.Tensor,
+                     cols: List[int]) -> None:
+        """Pooled lookup stored into ``out[:, cols[f] : cols[f] + dim_f]`` for every feature ``f``.  ``out`` may sit on another CUDA
+        device of this process (peer stores over NVLink); on CPU it is a plain slice assignment."""
+        F = len(self.feature_table_map)
+        assert len(cols) == F and self.pooling_mode != PoolingMode.NONE
+        B = (offsets.numel() - 1) // F if F else 0
+        if not self.weights.is_cuda:
+            res = self._forward_cpu(indices, offsets, per_sample_weights, B)
+            for f, c in enumerate(cols):
+                out[:B, c: c + self.D_offsets[f + 1] - self.D_offsets[f]] = res[:, self.D_offsets[f]: self.D_offsets[f + 1]].to(out.dtype)
+            return
+        _ext.require_cuda_ext("qtbe_forward_into")
+        key = tuple(int(c) for c in cols)
+        cache = self.__dict__.setdefault("_meta_into", {})
+        if key not in cache:
+            m = self._meta_tensor(self.weights.device).clone()
+            m[3] = torch.tensor(key, dtype=m.dtype, device=m.device)
+            cache[key] = m
+        if indices.dtype != offsets.dtype:
+            offsets = offsets.to(indices.dtype)
+        psw = per_sample_weights.float() if per_sample_weights is not None else None
+        torch.ops.trb200.qtbe_forward_into(self.weights, cache[key], indices.contiguous(), offsets.contiguous(), psw, out, B, self.max_D,
+                                           int(self.pooling_mode), self._err)
+
     def _forward_cpu(self, indices, offsets, psw, B) -> torch.Tensor:
         off = offsets.to(torch.int64)
         idx = indices.to(torch.int64)

@@ -191,6 +191,7 @@ class EmbeddingBagCollection(EmbeddingBagCollectionInterface, _QuantCollectionBa
         grouped_names = [n for group in self._group_tables for names_ in get_embedding_names_by_table(group) for n in names_]
         shared = dict(zip([f"{t.name}:{f}" for t in tables for f in t.feature_names], self._embedding_names))
         grouped_names = [shared[f"{t.name}:{f}"] for group in self._group_tables for t in group for f in t.feature_names]
+        self._grouped_names: List[str] = grouped_names
         self._out_perm: Optional[List[int]] = None
         if grouped_names != self._embedding_names:
             self._out_perm = [grouped_names.index(n) for n in self._embedding_names]
@@ -210,6 +211,16 @@ class EmbeddingBagCollection(EmbeddingBagCollectionInterface, _QuantCollectionBa
             pieces = values.split(self._grouped_dims, dim=1)
             values = torch.cat([pieces[i] for i in self._out_perm], dim=1)
         return KeyedTensor(keys=self._embedding_names, values=values, length_per_key=self._length_per_key)
+
+    def forward_into(self, features: KeyedJaggedTensor, out: torch.Tensor, column_of: Dict[str, int]) -> None:
+        """Pooled lookups stored straight into ``out [B, width]`` at ``column_of[embedding name]`` (a buffer that may belong to
+        another device of this process): what a sharded serving model uses instead of returning pieces to be copied and joined."""
+        kjt = features.permute([features.keys().index(f) for f in self._feature_names]) if features.keys() != self._feature_names else features
+        groups = kjt.split(self._feature_splits) if len(self._emb_modules) > 1 else [kjt]
+        names = iter(self._grouped_names)
+        for emb, f in zip(self._emb_modules, groups):
+            cols = [column_of[next(names)] for _ in emb.feature_table_map]
+            emb.forward_into(f.values(), f.offsets(), f.weights_or_none() if self._is_weighted else None, out, cols)
 
     @classmethod
     def from_float(cls, module: OriginalEmbeddingBagCollection, use_precomputed_fake_quant: bool = False) -> "EmbeddingBagCollection":
