@@ -37,6 +37,8 @@ def main() -> None:
     p.add_argument("--request-size", type=int, default=2048)
     p.add_argument("--int4-big", action="store_true", help="int4 for the four 40M-row tables")
     p.add_argument("--row-cap", type=int, default=0, help="cap table rows (smoke runs)")
+    p.add_argument("--gpus", type=int, default=1, help="place the tables table-wise over this many GPUs of one process; requests arrive at GPU 0, "
+                   "every GPU's lookup kernel stores its pooled rows straight into GPU 0's buffer")
     p.add_argument("--cuda-graph", action="store_true", help="replay the forward as one CUDA graph (static buffers) instead of launching it eagerly")
     a = p.parse_args()
 
@@ -62,6 +64,24 @@ def main() -> None:
     model = DLRM_DCN(qebc, dense_in_features=13, dense_arch_layer_sizes=[512, 256, 128], over_arch_layer_sizes=[1024, 1024, 512, 256, 1], dcn_num_layers=3,
                      dcn_low_rank_dim=512, dense_device=device).eval()
     table_bytes = sum(m.weight.numel() for m in qebc.embedding_bags.values())
+    if a.gpus > 1:
+        from torchrec_b200.distributed.quant_embeddingbag import ShardedQuantEmbeddingBagCollection
+        from torchrec_b200.distributed.types import ParameterSharding, ShardingEnv
+
+        assert not a.cuda_graph, "the multi-GPU path is launched eagerly"
+        # largest tables first, each onto the GPU that holds the fewest bytes so far
+        load = [0] * a.gpus
+        plan = {}
+        for t in sorted(tables, key=lambda t: -t.num_embeddings):
+            r = min(range(a.gpus), key=lambda i: load[i])
+            load[r] += t.num_embeddings * 132
+            plan[t.name] = ParameterSharding(sharding_type="table_wise", compute_kernel="quant", ranks=[r])
+        sharded = ShardedQuantEmbeddingBagCollection(qebc, plan, ShardingEnv.from_local(world_size=a.gpus, rank=0), device=device)
+        model.sparse_arch.embedding_bag_collection = sharded
+        for m in qebc.embedding_bags.values():  # the unsharded copy on GPU 0 is no longer needed
+            m.weight.set_(torch.empty(0, dtype=torch.uint8, device=device))
+        qebc._emb_modules = torch.nn.ModuleList()
+        torch.cuda.empty_cache()
 
     ds = RandomRecDataset(keys=keys, batch_size=a.request_size, hash_sizes=rows, ids_per_features=POOLING, min_ids_per_features=POOLING, num_dense=13, manual_seed=99,
                           num_generated_batches=16, zipf_s=1.05, idx_dtype=torch.int32, label_positive_rate=0.25, dense_log_transform=True)
@@ -119,7 +139,7 @@ def main() -> None:
     for emb in qebc._emb_modules:
         emb.check_error()
     print(json.dumps({
-        "metric": "quantized DLRM-DCNv2 inference latency", "n_gpus": 1, "request_size": a.request_size, "requests": a.requests, "warmup": a.warmup,
+        "metric": "quantized DLRM-DCNv2 inference latency", "n_gpus": a.gpus, "request_size": a.request_size, "requests": a.requests, "warmup": a.warmup,
         "p50_ms": lat[len(lat) // 2], "p99_ms": lat[min(len(lat) - 1, int(len(lat) * 0.99))], "mean_ms": sum(lat) / len(lat),
         "qps_requests": a.requests / (back_to_back_ms / 1e3), "samples_per_s": a.requests * a.request_size / (back_to_back_ms / 1e3), "host_wall_s": wall,
         "h2d_bytes_per_request": h2d, "d2h_bytes_per_request": a.request_size * 4, "table_bytes": table_bytes,

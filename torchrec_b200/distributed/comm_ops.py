@@ -210,6 +210,52 @@ def _decode(codecs, direction: str, t, ctx=None) -> Tensor:
     return getattr(codecs, direction).decode(t, ctx)
 
 
+def _chunk_ctx(codec, width: int):
+    """Context of one destination's chunk: codecs that quantise by row and were given no row length use the chunk's row width."""
+    ctx = codec.create_context()
+    if ctx is not None and getattr(ctx, "row_dim", 1) <= 0:
+        ctx.row_dim = int(width)
+    return ctx
+
+
+def _is_byte_codec(codec) -> bool:
+    return codec.quantized_dtype == torch.uint8
+
+
+def _encode_chunks(codec, flat: Tensor, elem_splits: List[int], widths: List[int]) -> Tuple[Tensor, List[int]]:
+    """Encode what goes to every destination.  Cast codecs keep the element count and run once over the whole buffer; byte codecs
+    (FP8 / INT8 / MX4 containers) run per destination so that no quantisation block straddles two destinations, and report the
+    encoded split sizes."""
+    if not _is_byte_codec(codec):
+        return codec.encode(flat, codec.create_context()), [int(n) for n in elem_splits]
+    parts = [codec.encode(c, _chunk_ctx(codec, w)) if c.numel() else flat.new_empty(0, dtype=torch.uint8) for c, w in zip(flat.split(elem_splits), widths)]
+    return torch.cat(parts), [int(e.numel()) for e in parts]
+
+
+def _encoded_sizes(codec, elem_splits: List[int], widths: List[int]) -> List[int]:
+    if not _is_byte_codec(codec):
+        return [int(n) for n in elem_splits]
+    return [int(codec.calc_quantized_size(int(n), _chunk_ctx(codec, w))) if n else 0 for n, w in zip(elem_splits, widths)]
+
+
+def _decode_chunks(codec, flat: Tensor, elem_splits: List[int], widths: List[int], out_dtype: torch.dtype) -> Tensor:
+    """Inverse of :func:`_encode_chunks` for what arrived from every source."""
+    if not _is_byte_codec(codec):
+        ctx = codec.create_context()
+        if ctx is not None:
+            ctx.dtype = out_dtype
+        return codec.decode(flat, ctx)
+    out = []
+    for part, n, w in zip(flat.split(_encoded_sizes(codec, elem_splits, widths)), elem_splits, widths):
+        if n == 0:
+            continue
+        ctx = _chunk_ctx(codec, w)
+        ctx.dtype = out_dtype
+        ctx.numel = int(n)
+        out.append(codec.decode(part, ctx)[: int(n)])
+    return torch.cat(out) if out else flat.new_empty(0, dtype=out_dtype)
+
+
 # ---- pooled all-to-all -----------------------------------------------------------------------------
 def _recat_pooled_embedding_grad_out(grad_output: Tensor, num_features_per_rank: List[int]) -> Tensor:
     """``[B_local, sum(D_r)]`` -> flat buffer with rank r's ``[B_local, D_r]`` block contiguous."""
@@ -228,11 +274,12 @@ class All2All_Pooled_Req(Function):
         assert B_global == sum(batch_size_per_rank)
         sharded_input = input_embeddings.contiguous().view(-1)
         qctx = None
-        if a2ai.codecs is not None:
-            qctx = a2ai.codecs.forward.create_context()
-            sharded_input = a2ai.codecs.forward.encode(sharded_input, qctx)
         input_split_sizes = [D_local_sum * b for b in batch_size_per_rank]
         output_split_sizes = [B_local * d for d in dim_sum_per_rank]
+        a2ai.value_dtype = input_embeddings.dtype
+        if a2ai.codecs is not None:
+            sharded_input, input_split_sizes = _encode_chunks(a2ai.codecs.forward, sharded_input, input_split_sizes, [D_local_sum] * len(batch_size_per_rank))
+            output_split_sizes = _encoded_sizes(a2ai.codecs.forward, output_split_sizes, dim_sum_per_rank)
         sharded_output = torch.empty(sum(output_split_sizes), dtype=sharded_input.dtype, device=sharded_input.device)
         with record_function("## alltoall_fwd_single ##"):
             req = _all_to_all_single(sharded_output, sharded_input, output_split_sizes, input_split_sizes, pg, async_op=True)
@@ -253,8 +300,10 @@ class All2All_Pooled_Req(Function):
         myreq.req = None
         grad_output = myreq.tensor
         my_rank = dist.get_rank(ctx.pg)
-        grad_output = _decode(a2ai.codecs, "backward", grad_output, myreq.qcomm_ctx)
         D_local_sum = a2ai.dim_sum_per_rank[my_rank]
+        if a2ai.codecs is not None:
+            grad_output = _decode_chunks(a2ai.codecs.backward, grad_output, [D_local_sum * b for b in a2ai.batch_size_per_rank],
+                                         [D_local_sum] * len(a2ai.batch_size_per_rank), getattr(a2ai, "grad_dtype", torch.float32))
         grad_input = grad_output.view(sum(a2ai.batch_size_per_rank), D_local_sum)
         if GRADIENT_DIVISION:
             grad_input = grad_input / dist.get_world_size(ctx.pg)
@@ -274,9 +323,11 @@ class All2All_Pooled_Wait(Function):
         sharded_output = myreq.tensor
         myreq.req = None
         myreq.tensor = None
-        sharded_output = _decode(a2ai.codecs, "forward", sharded_output, myreq.qcomm_ctx)
         my_rank = dist.get_rank(pg)
         B_local = a2ai.batch_size_per_rank[my_rank]
+        if a2ai.codecs is not None:
+            sharded_output = _decode_chunks(a2ai.codecs.forward, sharded_output, [B_local * d for d in a2ai.dim_sum_per_rank], a2ai.dim_sum_per_rank,
+                                            getattr(a2ai, "value_dtype", torch.float32))
         outputs = sharded_output.split([B_local * d for d in a2ai.dim_sum_per_rank])
         return torch.cat([o.view(B_local, -1) for o in outputs], dim=1)
 
@@ -290,11 +341,12 @@ class All2All_Pooled_Wait(Function):
         D_local_sum = a2ai.dim_sum_per_rank[my_rank]
         sharded_grad_output = _recat_pooled_embedding_grad_out(grad_output.contiguous(), a2ai.dim_sum_per_rank)
         qctx = None
-        if a2ai.codecs is not None:
-            qctx = a2ai.codecs.backward.create_context()
-            sharded_grad_output = a2ai.codecs.backward.encode(sharded_grad_output, qctx)
         input_split_sizes = [B_local * d for d in a2ai.dim_sum_per_rank]
         output_split_sizes = [D_local_sum * b for b in a2ai.batch_size_per_rank]
+        a2ai.grad_dtype = grad_output.dtype
+        if a2ai.codecs is not None:
+            sharded_grad_output, input_split_sizes = _encode_chunks(a2ai.codecs.backward, sharded_grad_output, input_split_sizes, a2ai.dim_sum_per_rank)
+            output_split_sizes = _encoded_sizes(a2ai.codecs.backward, output_split_sizes, [D_local_sum] * len(a2ai.batch_size_per_rank))
         sharded_grad_input = torch.empty(sum(output_split_sizes), device=sharded_grad_output.device, dtype=sharded_grad_output.dtype)
         with record_function("## alltoall_bwd_single ##"):
             req = _all_to_all_single(sharded_grad_input, sharded_grad_output, output_split_sizes, input_split_sizes, pg, async_op=True)
@@ -346,13 +398,14 @@ class All2All_Seq_Req(Function):
             )
             a2ai.permuted_lengths_after_sparse_data_all2all = plen
         del local_T
+        a2ai.value_dtype = sharded_input_embeddings.dtype
         sharded_input_embeddings = sharded_input_embeddings.reshape(-1)
-        if a2ai.codecs is not None:
-            qctx = a2ai.codecs.forward.create_context()
-            sharded_input_embeddings = a2ai.codecs.forward.encode(sharded_input_embeddings, qctx)
         # rows travel the routes of the ids in reverse: what the id all-to-all received from a peer is sent back to it
         out_splits = [s * D for s in a2ai.input_splits]
         in_splits = [s * D for s in a2ai.output_splits]
+        if a2ai.codecs is not None:
+            sharded_input_embeddings, in_splits = _encode_chunks(a2ai.codecs.forward, sharded_input_embeddings, in_splits, [D] * len(in_splits))
+            out_splits = _encoded_sizes(a2ai.codecs.forward, out_splits, [D] * len(out_splits))
         sharded_output = torch.empty(sum(out_splits), dtype=sharded_input_embeddings.dtype, device=sharded_input_embeddings.device)
         with record_function("## alltoall_seq_embedding_fwd_single ##"):
             req = _all_to_all_single(sharded_output, sharded_input_embeddings, out_splits, in_splits, pg, async_op=True)
@@ -371,7 +424,10 @@ class All2All_Seq_Req(Function):
         a2ai: All2AllSequenceInfo = myreq.info
         D = a2ai.embedding_dim
         myreq.req.wait()
-        grad = _decode(a2ai.codecs, "backward", myreq.tensor, myreq.qcomm_ctx)
+        grad = myreq.tensor
+        if a2ai.codecs is not None:
+            splits = [s * D for s in a2ai.output_splits]
+            grad = _decode_chunks(a2ai.codecs.backward, grad, splits, [D] * len(splits), getattr(a2ai, "grad_dtype", torch.float32))
         myreq.req = None
         myreq.tensor = None
         backward_recat = a2ai.backward_recat_tensor
@@ -398,7 +454,10 @@ class All2All_Seq_Req_Wait(Function):
         ctx.pg = pg
         ctx.myreq = myreq
         myreq.req.wait()
-        out = _decode(a2ai.codecs, "forward", myreq.tensor, myreq.qcomm_ctx)
+        out = myreq.tensor
+        if a2ai.codecs is not None:
+            splits = [s * a2ai.embedding_dim for s in a2ai.input_splits]
+            out = _decode_chunks(a2ai.codecs.forward, out, splits, [a2ai.embedding_dim] * len(splits), getattr(a2ai, "value_dtype", torch.float32))
         myreq.req = None
         myreq.tensor = None
         return out.view(-1, a2ai.embedding_dim)
@@ -410,11 +469,12 @@ class All2All_Seq_Req_Wait(Function):
         D = a2ai.embedding_dim
         g = sharded_grad_output.contiguous().view(-1)
         qctx = None
-        if a2ai.codecs is not None:
-            qctx = a2ai.codecs.backward.create_context()
-            g = a2ai.codecs.backward.encode(g, qctx)
+        a2ai.grad_dtype = sharded_grad_output.dtype
         out_splits = [s * D for s in a2ai.output_splits]
         in_splits = [s * D for s in a2ai.input_splits]
+        if a2ai.codecs is not None:
+            g, in_splits = _encode_chunks(a2ai.codecs.backward, g, in_splits, [D] * len(in_splits))
+            out_splits = _encoded_sizes(a2ai.codecs.backward, out_splits, [D] * len(out_splits))
         grad_input = torch.empty(sum(out_splits), device=g.device, dtype=g.dtype)
         with record_function("## alltoall_seq_embedding_bwd_single ##"):
             req = _all_to_all_single(grad_input, g, out_splits, in_splits, ctx.pg, async_op=True)

@@ -118,7 +118,7 @@ class CastCodec(QuantizedCommCodec):
 class RowwiseInt8Codec(QuantizedCommCodec):
     """Row-wise 8-bit quantisation: every ``row_dim`` values share an fp32 scale and bias appended to the
     row (``row_dim + 8`` bytes per row).  Used for ``CommType.INT8`` and as the container of ``FP8``
-    (scaled e4m3 stored in a byte) and ``MX4`` is mapped to it as well (block scale granularity ``row_dim``)."""
+    (scaled e4m3 stored in a byte)."""
 
     def __init__(self, comm_type: CommType, row_dim: Optional[int] = None, is_fwd: bool = True) -> None:
         self._comm_type = comm_type
@@ -132,7 +132,10 @@ class RowwiseInt8Codec(QuantizedCommCodec):
 
     def encode(self, input_tensor: torch.Tensor, ctx: Optional[_Ctx] = None) -> torch.Tensor:
         flat = input_tensor.reshape(-1).float()
-        n, rd = self._rows(flat.numel())
+        if ctx is not None and ctx.row_dim > 0 and self._row_dim <= 0 and flat.numel() % ctx.row_dim == 0:
+            n, rd = flat.numel() // ctx.row_dim, ctx.row_dim  # the caller knows the row width of this chunk
+        else:
+            n, rd = self._rows(flat.numel())
         x = flat.view(n, rd)
         if ctx is not None:
             ctx.dtype = input_tensor.dtype
@@ -188,12 +191,79 @@ class RowwiseInt8Codec(QuantizedCommCodec):
         return dim_sum, 0
 
 
+class Mx4Codec(QuantizedCommCodec):
+    """Microscaling 4-bit format: blocks of ``group`` values (default 32) share one power-of-two scale stored as a biased
+    8-bit exponent, every value is a 4-bit e2m1 float (sign, magnitudes 0 / 0.5 / 1 / 1.5 / 2 / 3 / 4 / 6), two per byte:
+    ``group / 2 + 1`` bytes per block, 4.25 bits per value at group 32.  The payload is padded to whole blocks."""
+
+    _LEVELS = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+    def __init__(self, group: Optional[int] = None, is_fwd: bool = True) -> None:
+        self._group = int(group) if group and group > 0 else 32
+        assert self._group % 2 == 0, "two 4-bit codes share a byte"
+        self._is_fwd = is_fwd
+
+    def encode(self, input_tensor: torch.Tensor, ctx: Optional[_Ctx] = None) -> torch.Tensor:
+        g = self._group
+        flat = input_tensor.reshape(-1).float()
+        if ctx is not None:
+            ctx.dtype = input_tensor.dtype
+            ctx.numel = flat.numel()
+        pad = (-flat.numel()) % g
+        if pad:
+            flat = torch.cat([flat, flat.new_zeros(pad)])
+        x = flat.view(-1, g)
+        amax = x.abs().amax(dim=1, keepdim=True)
+        # largest magnitude maps into (4, 6]: shared exponent = floor(log2(amax)) - 2, kept in [-127, 127]
+        exp = torch.where(amax > 0, torch.floor(torch.log2(amax.clamp(min=1e-38))) - 2, torch.full_like(amax, -127.0)).clamp(-127, 127)
+        y = x / torch.exp2(exp)
+        levels = torch.tensor(self._LEVELS, device=x.device)
+        mag = (y.abs().unsqueeze(-1) - levels).abs().argmin(dim=-1)  # nearest representable magnitude (saturates at 6)
+        code = (mag | ((y < 0).to(torch.int64) << 3)).to(torch.uint8)
+        packed = code[:, 0::2] | (code[:, 1::2] << 4)
+        return torch.cat([packed, (exp + 127).to(torch.uint8)], dim=1).reshape(-1)
+
+    def decode(self, input_grad: torch.Tensor, ctx: Optional[_Ctx] = None) -> torch.Tensor:
+        g = self._group
+        blocks = input_grad.view(-1, g // 2 + 1)
+        packed, exp = blocks[:, : g // 2], blocks[:, g // 2:].float() - 127
+        code = torch.stack([packed & 0xF, packed >> 4], dim=2).reshape(-1, g).long()
+        levels = torch.tensor(self._LEVELS, device=input_grad.device)
+        val = levels[code & 7] * torch.where((code & 8) != 0, -1.0, 1.0) * torch.exp2(exp)
+        out = val.reshape(-1)
+        n = getattr(ctx, "numel", None) if ctx is not None else None
+        if n is not None:
+            out = out[:n]
+        out_dtype = ctx.dtype if ctx is not None and ctx.dtype is not None else torch.float32
+        return out.to(out_dtype)
+
+    @property
+    def quantized_dtype(self) -> torch.dtype:
+        return torch.uint8
+
+    def calc_quantized_size(self, input_len: int, ctx: Optional[_Ctx] = None) -> int:
+        g = self._group
+        return (input_len + g - 1) // g * (g // 2 + 1)
+
+    def create_context(self) -> Optional[_Ctx]:
+        return _Ctx(self._group)
+
+    def padded_size(self, input_tensor: torch.Tensor, dim_per_rank: List[int], my_rank: int, qcomm_ctx: _Ctx) -> Tuple[int, int]:
+        if input_tensor.ndim == 1:
+            return input_tensor.shape[0], 0
+        width, g = input_tensor.shape[1], self._group
+        padded = (width + g - 1) // g * g
+        return padded, padded - width
+
+
 def get_qcomm_codecs(qcomms_config: Optional[QCommsConfig]) -> QuantizedCommCodecs:
     codecs = QuantizedCommCodecs()
     if qcomms_config is not None:
         def make(comm_type: CommType, loss_scale, row_dim, is_fwd: bool) -> QuantizedCommCodec:
             if comm_type in (CommType.FP32, CommType.FP16, CommType.BF16):
                 return CastCodec(comm_type, loss_scale, is_fwd)
+            if comm_type == CommType.MX4:
+                return Mx4Codec(row_dim, is_fwd)
             return RowwiseInt8Codec(comm_type, row_dim, is_fwd)
 
         fwd_dim = qcomms_config.fp8_quantize_dim if qcomms_config.forward_precision == CommType.FP8 else qcomms_config.mx4_quantize_dim
