@@ -172,6 +172,22 @@ def test_backward_updates_match_rowwise_adagrad(world):
 def test_sharded_embedding_collection_uses_the_engine_on_one_rank():
     """The module-level path: ``ShardedEmbeddingCollection`` on a one-rank environment routes through the engine and returns
     the same per-feature jagged tensors as the unsharded module; its backward updates the tables in place."""
+    import tempfile
+
+    import torch.distributed as dist
+
+    dev = torch.device("cuda:0")
+    own_group = not dist.is_initialized()
+    if own_group:  # the module builds its (unused) library output dists against a process group
+        dist.init_process_group("gloo", store=dist.FileStore(tempfile.mktemp(), 1), rank=0, world_size=1)
+    try:
+        _one_rank_module_case(dev)
+    finally:
+        if own_group:
+            dist.destroy_process_group()
+
+
+def _one_rank_module_case(dev):
     from torchrec_b200.distributed.embedding import EmbeddingCollectionSharder
     from torchrec_b200.distributed.sharding_plan import construct_module_sharding_plan, table_wise
     from torchrec_b200.distributed.types import ShardingEnv
@@ -179,8 +195,8 @@ def test_sharded_embedding_collection_uses_the_engine_on_one_rank():
     from torchrec_b200.modules.embedding_modules import EmbeddingCollection
     from torchrec_b200.optim.apply_optimizer_in_backward import apply_optimizer_in_backward
     from torchrec_b200.optim.rowwise_adagrad import RowWiseAdagrad
+    import torch.distributed as dist
 
-    dev = torch.device("cuda:0")
     tables = [EmbeddingConfig(name=f"t{i}", embedding_dim=32, num_embeddings=r, feature_names=[f"f{i}"]) for i, r in enumerate([100, 2000])]
     torch.manual_seed(1)
     ec = EmbeddingCollection(tables=tables, device=dev)
@@ -189,7 +205,7 @@ def test_sharded_embedding_collection_uses_the_engine_on_one_rank():
     sharder = EmbeddingCollectionSharder()
     plan = construct_module_sharding_plan(ec, {"t0": table_wise(rank=0), "t1": table_wise(rank=0)}, sharder=sharder, local_size=1, world_size=1,
                                           device_type="cuda")
-    sec = sharder.shard(ec, plan, ShardingEnv(1, 0, None), dev)
+    sec = sharder.shard(ec, plan, ShardingEnv.from_process_group(dist.group.WORLD), dev)
     kjt = _kjt(tables, 50, 5, 7)
     out = sec(kjt).wait()
     assert sec._engine_state == "on"

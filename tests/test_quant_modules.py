@@ -174,12 +174,14 @@ def _forward_into_case(device):
     off = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)])
     want = m(vals.to(device), off.to(device))
     out = torch.full((B + 2, 400), -1.0, device=device)
-    cols = [130, 0, 260]  # any order, with gaps
+    cols = [132, 0, 260]  # any order, with gaps; multiples of 4 (the kernel stores four elements at a time)
     m.forward_into(vals.to(device), off.to(device), None, out, cols)
     for f, c in enumerate(cols):
         d = m.D_offsets[f + 1] - m.D_offsets[f]
         torch.testing.assert_close(out[:B, c: c + d], want[:, m.D_offsets[f]: m.D_offsets[f + 1]], rtol=1e-5, atol=1e-5)
-    assert bool((out[B:] == -1).all()) and bool((out[:, 128:130] == -1).all()) and bool((out[:, 194:260] == -1).all())
+    with pytest.raises(ValueError):
+        m.forward_into(vals.to(device), off.to(device), None, out, [130, 0, 260])
+    assert bool((out[B:] == -1).all()) and bool((out[:, 128:132] == -1).all()) and bool((out[:, 196:260] == -1).all())
 
 
 def test_qtbe_forward_into_cpu():

@@ -226,6 +226,8 @@ void qtbe_forward_into(const at::Tensor& weights, const at::Tensor& meta, const 
   qtbe_check(weights, meta, indices, offsets, max_D);
   TORCH_CHECK(pooling != 2, "pooled lookups only");
   TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.size(0) >= B);
+  TORCH_CHECK(out.stride(0) % 4 == 0 && reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0,
+              "rows of the output buffer must start on 16-byte boundaries (the kernel stores four elements at a time)");
   const int F = int(meta.size(1));
   if (F == 0 || B == 0) return;
   if (out.device() != weights.device()) {

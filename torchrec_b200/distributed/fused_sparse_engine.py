@@ -189,6 +189,8 @@ class FusedSparseEngine:
                                              mean_after=False, module=(si, gi)))
                             j += 1
             self.dest_job_start.append(self.dest_job_start[-1] + j)
+        # the kernels move four elements at a time: every column block must start and end on a multiple of 4
+        assert all(jb.cols % 4 == 0 and jb.col_off % 4 == 0 and jb.out_col % 4 == 0 for jb in jobs), "embedding dims and column shards must be multiples of 4"
         self.jobs = jobs
         self.G = len(jobs)
         self.J_max = max((self.dest_job_start[d + 1] - self.dest_job_start[d] for d in range(W)), default=0)

@@ -83,6 +83,9 @@ class QuantTableBatchedEmbeddingBags(nn.Module):
         device of this process (peer stores over NVLink); on CPU it is a plain slice assignment."""
         F = len(self.feature_table_map)
         assert len(cols) == F and self.pooling_mode != PoolingMode.NONE
+        # the kernel stores four elements at a time: every destination column must keep those stores aligned
+        if any(int(c) % 4 for c in cols) or out.stride(0) % 4:
+            raise ValueError(f"output columns {list(cols)} and row stride {out.stride(0)} must be multiples of 4 elements")
         B = (offsets.numel() - 1) // F if F else 0
         if not self.weights.is_cuda:
             res = self._forward_cpu(indices, offsets, per_sample_weights, B)
