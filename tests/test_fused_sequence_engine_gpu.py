@@ -200,12 +200,13 @@ def _one_rank_module_case(dev):
     tables = [EmbeddingConfig(name=f"t{i}", embedding_dim=32, num_embeddings=r, feature_names=[f"f{i}"]) for i, r in enumerate([100, 2000])]
     torch.manual_seed(1)
     ec = EmbeddingCollection(tables=tables, device=dev)
-    ref = {f"t{i}": ec.embeddings[f"t{i}"].weight.detach().clone() for i in range(2)}
     apply_optimizer_in_backward(RowWiseAdagrad, ec.parameters(), {"lr": 0.05, "eps": 1e-8})
     sharder = EmbeddingCollectionSharder()
     plan = construct_module_sharding_plan(ec, {"t0": table_wise(rank=0), "t1": table_wise(rank=0)}, sharder=sharder, local_size=1, world_size=1,
                                           device_type="cuda")
     sec = sharder.shard(ec, plan, ShardingEnv.from_process_group(dist.group.WORLD), dev)
+    # the sharded module initialises its own table memory: the oracle reads it back before the step
+    ref = {t.name: w.detach().clone() for lk in sec._lookups for emb in lk.emb_modules for t, w in zip(emb.config.embedding_tables, emb.split_embedding_weights())}
     kjt = _kjt(tables, 50, 5, 7)
     out = sec(kjt).wait()
     assert sec._engine_state == "on"

@@ -136,3 +136,50 @@ def test_sequence_sharding_parity(sharding):
 @pytest.mark.parametrize("sharding", ["tw", "rw"])
 def test_sequence_sharding_index_dedup(sharding):
     run_multi_process(_parity, world_size=2, sharding=sharding, dedup=True)
+
+
+def _write_rows(rank, world_size):
+    """Online row writes: every rank writes a few rows; afterwards the assembled tables hold them, whatever the sharding."""
+    from torchrec_b200.distributed.embedding import EmbeddingCollectionSharder
+    from torchrec_b200.distributed.model_parallel import DistributedModelParallel
+    from torchrec_b200.distributed.types import ShardingEnv, ShardingPlan
+    from torchrec_b200.optim.apply_optimizer_in_backward import apply_optimizer_in_backward
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    with MultiProcessContext(rank, world_size, "gloo") as ctx:
+        torch.manual_seed(0)
+        reference = _Model(_make_ec())
+        local_model = copy.deepcopy(reference)
+        apply_optimizer_in_backward(torch.optim.SGD, local_model.ec.parameters(), {"lr": 0.1})
+        plan = ShardingPlan({"ec": _plan_for(local_model.ec, "mixed", world_size)})  # t0 table-wise, t1 row-wise, t2 column-wise
+        dmp = DistributedModelParallel(local_model, env=ShardingEnv.from_process_group(ctx.pg), device=torch.device("cpu"), plan=plan,
+                                       sharders=[EmbeddingCollectionSharder()])
+        dmp.load_state_dict(copy.deepcopy(reference.state_dict()))
+        # rank r writes rows 10+r and 50+r of t1 (through f2), row 3+r of t0 and row 20+r of t2
+        ids = {"f0": [3 + rank], "f2": [10 + rank, 50 + rank], "f3": [20 + rank]}
+        keys = list(ids)
+        values = torch.tensor([i for k in keys for i in ids[k]])
+        rows = torch.arange(values.numel() * 16, dtype=torch.float32).view(-1, 16) + 1000 * (rank + 1)
+        kjt = KeyedJaggedTensor(keys=keys, values=values, weights=rows, lengths=torch.tensor([len(ids[k]) for k in keys]), stride=1)
+        sharded_ec = dmp.module.ec
+        sharded_ec.write(kjt)
+        want = {n: t.clone() for n, t in reference.state_dict().items()}
+        for r in range(world_size):
+            r_rows = torch.arange(4 * 16, dtype=torch.float32).view(-1, 16) + 1000 * (r + 1)
+            want["ec.embeddings.t0.weight"][3 + r] = r_rows[0]
+            want["ec.embeddings.t1.weight"][10 + r] = r_rows[1]
+            want["ec.embeddings.t1.weight"][50 + r] = r_rows[2]
+            want["ec.embeddings.t2.weight"][20 + r] = r_rows[3]
+        sd = dmp.state_dict()
+        for name in ("ec.embeddings.t0.weight", "ec.embeddings.t1.weight", "ec.embeddings.t2.weight"):
+            mine = torch.zeros_like(want[name])
+            for s in sd[name].local_shards():
+                ro, co = s.metadata.shard_offsets
+                rs, cs = s.metadata.shard_sizes
+                mine[ro:ro + rs, co:co + cs] = s.tensor
+            dist.all_reduce(mine)
+            torch.testing.assert_close(mine, want[name], rtol=0, atol=0)
+
+
+def test_embedding_rows_can_be_written_online():
+    run_multi_process(_write_rows, world_size=2)

@@ -486,6 +486,47 @@ class ShardedEmbeddingCollection(
     def compute_and_output_dist(self, ctx: EmbeddingCollectionContext, input: KJTList) -> LazyAwaitable[Dict[str, JaggedTensor]]:
         return self.output_dist(ctx, self.compute(ctx, input))
 
+    # ---- embedding write path (``torchrec/distributed/embedding.py:1640-1672``) ----------------------------
+    def write_dist(self, ctx: EmbeddingCollectionContext, embeddings: KeyedJaggedTensor) -> Awaitable[Awaitable[Any]]:
+        """First half of an online row write: ``embeddings`` holds, per feature, the ids to overwrite (``values``) and the new
+        rows (``weights``, ``[ids, D]``).  Every rank contributes its own writes; all of them reach every rank, and ``update``
+        lets each rank keep what falls into its shards.  Writes are rare and small next to a training step, so they travel as
+        one gather rather than through the sharding-specific id exchange."""
+        rows = embeddings.weights()
+        assert rows.dim() == 2 and rows.shape[0] == embeddings.values().numel(), "weights must hold one row per id"
+        lpk = embeddings.length_per_key()
+        mine = [(key, ids, r) for key, ids, r in zip(embeddings.keys(), embeddings.values().split(lpk), rows.split(lpk)) if ids.numel()]
+        pg = self._env.process_group
+        if pg is None or dist.get_world_size(pg) == 1:
+            return NoWait(NoWait([mine]))
+        gathered: List[Any] = [None] * dist.get_world_size(pg)
+        dist.all_gather_object(gathered, [(k, i.cpu(), r.cpu()) for k, i, r in mine], group=pg)
+        return NoWait(NoWait(gathered))
+
+    @torch.no_grad()
+    def update(self, ctx: EmbeddingCollectionContext, dist_input: Any) -> None:
+        """Second half: write every received row (or its column slice) into the local shards whose row range holds the id.  Writes
+        are applied in rank order, so on a conflict the highest rank's row stays, on every shard alike."""
+        table_of = {f: cfg.name for cfg in self._embedding_configs for f in cfg.feature_names}
+        for per_rank in dist_input:
+            for feature, ids, rows in per_rank:
+                table = table_of[feature]
+                for _, lookup in self._unwrapped_lookups():
+                    for emb in lookup.emb_modules:
+                        for shard, weight in zip(emb.config.embedding_tables, emb.split_embedding_weights()):
+                            if shard.name != table:
+                                continue
+                            (r0, c0), (nr, nc) = shard.local_metadata.shard_offsets, shard.local_metadata.shard_sizes
+                            ids_d = ids.to(weight.device).long()
+                            here = (ids_d >= r0) & (ids_d < r0 + nr)
+                            if bool(here.any()):
+                                weight[ids_d[here] - r0] = rows.to(weight.device)[here][:, c0: c0 + nc].to(weight.dtype)
+
+    def write(self, embeddings: KeyedJaggedTensor) -> None:
+        """``write_dist`` + ``update`` in one call (collective: every rank calls it, with an empty KJT if it has nothing to write)."""
+        ctx = self.create_context()
+        self.update(ctx, self.write_dist(ctx, embeddings).wait().wait())
+
 
 class EmbeddingCollectionSharder(BaseEmbeddingSharder[EmbeddingCollection]):
     """Shards an ``EmbeddingCollection`` (``torchrec/distributed/embedding.py:1675``)."""
