@@ -379,3 +379,66 @@ def _pool_run(rank, world_size):
 
 def test_sharded_object_pools():
     run_multi_process(_pool_run, world_size=3)
+
+
+def _single_embedding_bag(rank, world_size, kind):
+    """A plain ``nn.EmbeddingBag`` sharded row-wise / column-wise: forward and one in-backward SGD step against the module itself."""
+    import copy
+
+    import torch.distributed as dist
+
+    from torchrec_b200.distributed.embeddingbag import EmbeddingBagSharder, ShardedEmbeddingBag
+    from torchrec_b200.distributed.sharding_plan import column_wise, construct_module_sharding_plan, row_wise
+    from torchrec_b200.distributed.types import ShardingEnv
+    from torchrec_b200.optim.apply_optimizer_in_backward import apply_optimizer_in_backward
+    from torchrec_b200.test_utils.multi_process import MultiProcessContext
+
+    with MultiProcessContext(rank, world_size, "gloo") as ctx:
+        torch.manual_seed(0)
+        bag = torch.nn.EmbeddingBag(40, 16, mode="sum", include_last_offset=False)
+        local = copy.deepcopy(bag)
+        apply_optimizer_in_backward(torch.optim.SGD, local.parameters(), {"lr": 0.1})
+        sharder = EmbeddingBagSharder()
+        assert sharder.module_type is torch.nn.EmbeddingBag and list(sharder.shardable_parameters(local)) == ["weight"]
+        gen = row_wise() if kind == "rw" else column_wise(ranks=[1, 0])
+        plan = construct_module_sharding_plan(local, {"weight": gen}, sharder=sharder, world_size=world_size, local_size=world_size, device_type="cpu")
+        sharded = sharder.shard(local, plan, ShardingEnv.from_process_group(ctx.pg), torch.device("cpu"))
+        assert isinstance(sharded, ShardedEmbeddingBag), type(sharded)
+        assert [n for n, _ in sharded.named_parameters()] == ["weight"], [n for n, _ in sharded.named_parameters()]
+        sharded.load_state_dict({"weight": _as_sharded_like(sharded.state_dict()["weight"], bag.weight.detach())})
+        g = torch.Generator().manual_seed(5)
+        inputs, offsets, weights = [], [], []
+        for r in range(world_size):
+            lens = torch.randint(0, 4, (5,), generator=g)
+            inputs.append(torch.randint(0, 40, (int(lens.sum()),), generator=g))
+            offsets.append(torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)[:-1]]))
+            weights.append(torch.rand(int(lens.sum()), generator=g))
+        want_all = [bag(i, o, per_sample_weights=w) for i, o, w in zip(inputs, offsets, weights)]
+        got = sharded(inputs[rank], offsets[rank], weights[rank]).wait()
+        torch.testing.assert_close(got.detach(), want_all[rank].detach(), rtol=1e-5, atol=1e-6)
+        (sum(w.sum() for w in want_all) / world_size).backward()
+        got.sum().backward()
+        with torch.no_grad():
+            want_w = bag.weight - 0.1 * bag.weight.grad
+        mine = torch.zeros_like(want_w)
+        for s in sharded.state_dict()["weight"].local_shards():
+            (r0, c0), (nr, nc) = s.metadata.shard_offsets, s.metadata.shard_sizes
+            mine[r0:r0 + nr, c0:c0 + nc] = s.tensor
+        dist.all_reduce(mine)
+        torch.testing.assert_close(mine, want_w, rtol=1e-5, atol=1e-6)
+
+
+def _as_sharded_like(template, full):
+    """A copy of ``template`` (a ShardedTensor) whose local shards hold the matching blocks of ``full``."""
+    import copy
+
+    out = copy.deepcopy(template)
+    for s in out.local_shards():
+        (r0, c0), (nr, nc) = s.metadata.shard_offsets, s.metadata.shard_sizes
+        s.tensor.copy_(full[r0:r0 + nr, c0:c0 + nc])
+    return out
+
+
+@pytest.mark.parametrize("kind", ["rw", "cw"])
+def test_single_embedding_bag_sharded(kind):
+    run_multi_process(_single_embedding_bag, world_size=2, kind=kind)

@@ -43,11 +43,12 @@ def bench_gemm_nt(M: int, shapes: List[tuple], n: int, warm: int) -> None:
         a = torch.randn(M, K, device="cuda").bfloat16()
         b = torch.randn(N, K, device="cuda").bfloat16()
         bias = torch.randn(N, device="cuda")
+        t0 = timeit(lambda: ops.gemm_nt_bf16(a, b, None, 0, False), n, warm)
         t1 = timeit(lambda: ops.gemm_nt_bf16(a, b, bias, 1, False), n, warm)
         t2 = timeit(lambda: torch.relu(torch.nn.functional.linear(a, b, bias.bfloat16())), n, warm)
         t3 = timeit(lambda: torch.matmul(a, b.t()), n, warm)
         fl = 2 * M * N * K
-        print(f"NT  M={M} N={N} K={K}: tcgen05+bias+relu {t1:.3f} ms ({fl / t1 / 1e9:.0f} TF) | torch linear+relu {t2:.3f} ms | "
+        print(f"NT  M={M} N={N} K={K}: tcgen05 plain {t0:.3f} ms ({fl / t0 / 1e9:.0f} TF) | tcgen05+bias+relu {t1:.3f} ms ({fl / t1 / 1e9:.0f} TF) | torch linear+relu {t2:.3f} ms | "
               f"matmul only {t3:.3f} ms ({fl / t3 / 1e9:.0f} TF)", flush=True)
 
 
@@ -244,6 +245,7 @@ def main() -> None:
                                                        "tbe_uniform", "qtbe", "dense_small", "sparse", "engine"])
     ap.add_argument("--shape", type=str, default="", help="N,K: run the GEMM benchmarks on this one shape only (profiler captures)")
     ap.add_argument("--small", action="store_true", help="profiler-sized case: few launches, a few GB on the device")
+    ap.add_argument("--quick", action="store_true", help="full-size operands (larger than L2) but one warm-up and two timed launches per kernel: what a profiler capture runs")
     ap.add_argument("--batch", type=int, default=65536)
     ap.add_argument("--row-cap", type=int, default=4000000)
     args = ap.parse_args()
@@ -251,7 +253,7 @@ def main() -> None:
 
     _ext.require_cuda_ext("benchmark_kernels")
     M = 16384 if args.small else args.batch
-    n, warm = (2, 1) if args.small else (10, 3)
+    n, warm = (2, 1) if (args.small or args.quick) else (10, 3)
     row_cap = min(args.row_cap, 200000) if args.small else args.row_cap
     one = [tuple(int(x) for x in args.shape.split(","))] if args.shape else None
     if args.op in ("all", "gemm_nt"):

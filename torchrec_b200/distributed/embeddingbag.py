@@ -50,6 +50,7 @@ from torchrec_b200.distributed.types import (
     EmbeddingModuleShardingPlan,
     LazyAwaitable,
     LazyGetItemMixin,
+    NullShardedModuleContext,
     ParameterSharding,
     QuantizedCommCodecs,
     ShardedTensor,
@@ -839,6 +840,140 @@ def _embedding_names_by_table(tables) -> List[List[str]]:
         for f in cfg.feature_names:
             shared[f] = f in shared
     return [[f + "@" + cfg.name if shared[f] else f for f in cfg.feature_names] for cfg in tables]
+
+
+class ShardedEmbeddingBag(ShardedEmbeddingModule[KeyedJaggedTensor, torch.Tensor, torch.Tensor, NullShardedModuleContext], FusedOptimizerModule):
+    """A single ``nn.EmbeddingBag`` (sum pooling) sharded row-wise, column-wise or data-parallel
+    (``torchrec/distributed/embeddingbag.py:2013-2227``).  It is a one-table sharded collection under the hood: the bag's
+    ``(input, offsets, per_sample_weights)`` call becomes a one-feature weighted KJT, and state-dict / parameter names lose the
+    table prefix so that they read ``weight`` like the module it replaces."""
+
+    _TABLE, _FEATURE = "embedding_bag", "ids"
+
+    def __init__(self, module: nn.EmbeddingBag, table_name_to_parameter_sharding: Dict[str, ParameterSharding], env: ShardingEnv,
+                 fused_params: Optional[Dict[str, Any]] = None, device: Optional[torch.device] = None) -> None:
+        super().__init__()
+        if len(table_name_to_parameter_sharding) != 1:
+            raise AssertionError(f"expect 1 table, but got {len(table_name_to_parameter_sharding)}")
+        if module.mode != "sum":
+            raise AssertionError("ShardedEmbeddingBag only supports sum pooling")
+        self.parameter_sharding: ParameterSharding = next(iter(table_name_to_parameter_sharding.values()))
+        if self.parameter_sharding.sharding_type == ShardingType.TABLE_WISE.value:
+            raise RuntimeError("table-wise sharding on a single EmbeddingBag is not supported yet")
+        table = EmbeddingTableConfig(num_embeddings=module.num_embeddings, embedding_dim=module.embedding_dim, name=self._TABLE,
+                                     feature_names=[self._FEATURE], pooling=PoolingType.SUM, is_weighted=True, embedding_names=[self._FEATURE])
+        # the optimizer attached to the bag's weight (apply_optimizer_in_backward) becomes the kernel's in-backward optimizer
+        per_table = ShardedEmbeddingBagCollection._table_fused_params(module.weight, self.parameter_sharding, fused_params or {})
+        info = EmbeddingShardingInfo(embedding_config=table, param_sharding=self.parameter_sharding, param=module.weight, fused_params=per_table)
+        self._env = env
+        self._embedding_sharding = create_embedding_bag_sharding([info], env, device, permute_embeddings=True)
+        self._input_dist: nn.Module = self._embedding_sharding.create_input_dist()
+        self._lookup: nn.Module = self._embedding_sharding.create_lookup()
+        self._output_dist: nn.Module = self._embedding_sharding.create_output_dist(device=device)
+        found = []
+        for kernel in self._lookup.modules():
+            if isinstance(kernel, FusedOptimizerModule):
+                kernel.fused_optimizer.params = {self._short(k): w for k, w in kernel.fused_optimizer.params.items()}
+                found.append(("", kernel.fused_optimizer))
+        self._optim: CombinedOptimizer = CombinedOptimizer(found)
+
+    @staticmethod
+    def _short(name: str) -> str:
+        return name.rsplit(".", 1)[-1]
+
+    # ---- stages ---------------------------------------------------------------------------------------------
+    def create_context(self) -> NullShardedModuleContext:
+        return NullShardedModuleContext()
+
+    def input_dist(self, ctx: NullShardedModuleContext, input: torch.Tensor, offsets: Optional[torch.Tensor] = None,
+                   per_sample_weights: Optional[torch.Tensor] = None) -> Awaitable[Awaitable[KeyedJaggedTensor]]:
+        if offsets is None:  # 2-D input: every row is one bag
+            assert input.dim() == 2, "offsets are required for 1-D input"
+            offsets = torch.arange(0, input.numel() + 1, input.shape[1], device=input.device)
+            input = input.reshape(-1)
+        elif offsets.numel() == 0 or int(offsets[-1]) != input.numel():
+            offsets = torch.cat([offsets, offsets.new_tensor([input.numel()])])  # nn.EmbeddingBag's offsets omit the end
+        weights = per_sample_weights if per_sample_weights is not None else torch.ones_like(input, dtype=torch.float)
+        features = KeyedJaggedTensor(keys=[self._FEATURE], values=input, offsets=offsets, weights=weights.reshape(-1))
+        copies = len(self._embedding_sharding.feature_names())  # column shards each want the ids
+        if copies != 1:
+            features = features.permute([0] * copies)
+        return self._input_dist(features)
+
+    def compute(self, ctx: NullShardedModuleContext, dist_input: KeyedJaggedTensor) -> torch.Tensor:
+        return self._lookup(dist_input)
+
+    def output_dist(self, ctx: NullShardedModuleContext, output: torch.Tensor) -> LazyAwaitable[torch.Tensor]:
+        return self._output_dist(output)
+
+    # ---- state under the names of the module it replaces --------------------------------------------------------------
+    def _checkpoint_weight(self):
+        """``weight`` as the checkpoint sees it: a ``ShardedTensor`` over the group whose local shards are views of the kernel's
+        memory (built once; collective on first use), or the plain tensor without a process group."""
+        if "_weight_view" not in self.__dict__:
+            local = [(t, w) for emb in self._lookup.emb_modules for t, w in zip(emb.config.embedding_tables, emb.split_embedding_weights())]
+            pg = self._env.process_group
+            if pg is None or self.parameter_sharding.sharding_type == ShardingType.DATA_PARALLEL.value:
+                self.__dict__["_weight_view"] = local[0][1]
+            else:
+                self.__dict__["_weight_view"] = get_state_dict([t for t, _ in local], [w for _, w in local], pg=pg)[f"{self._TABLE}.weight"]
+        return self.__dict__["_weight_view"]
+
+    def state_dict(self, destination: Optional[Dict[str, Any]] = None, prefix: str = "", keep_vars: bool = False) -> Dict[str, Any]:
+        out = OrderedDict() if destination is None else destination
+        out[prefix + "weight"] = self._checkpoint_weight()
+        return out
+
+    def load_state_dict(self, state_dict, strict: bool = True):  # type: ignore[override]
+        from torchrec_b200.distributed.embedding_lookup import _copy_checkpoint_entry
+
+        missing = [] if "weight" in state_dict else ["weight"]
+        if not missing:
+            _copy_checkpoint_entry(self._checkpoint_weight(), state_dict["weight"])
+        return torch.nn.modules.module._IncompatibleKeys(missing_keys=missing, unexpected_keys=[k for k in state_dict if k != "weight"])
+
+    def named_modules(self, memo=None, prefix: str = "", remove_duplicate: bool = True):
+        yield prefix, self
+
+    def named_parameters(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True) -> Iterator[Tuple[str, nn.Parameter]]:
+        """This rank's shard of the table as ``weight`` (a view of the kernel's memory; fused kernels update it in backward)."""
+        views = self.__dict__.setdefault("_weight_views", {})
+        for _, w in self._lookup.named_parameters_by_table():
+            if w.data_ptr() not in views:
+                views[w.data_ptr()] = w if isinstance(w, nn.Parameter) else _ViewParameter(w)
+            yield append_prefix(prefix, "weight"), views[w.data_ptr()]
+
+    def named_buffers(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True) -> Iterator[Tuple[str, torch.Tensor]]:
+        for name, b in self._lookup.named_buffers("", recurse):
+            yield append_prefix(prefix, self._short(name)), b
+
+    def sharded_parameter_names(self, prefix: str = "") -> Iterator[str]:
+        if self.parameter_sharding.sharding_type != ShardingType.DATA_PARALLEL.value:
+            for name, _ in self.named_parameters(prefix):
+                yield name
+
+    @property
+    def fused_optimizer(self) -> KeyedOptimizer:
+        return self._optim
+
+    @property
+    def unsharded_module_type(self) -> Type[nn.EmbeddingBag]:
+        return nn.EmbeddingBag
+
+
+class EmbeddingBagSharder(BaseEmbeddingSharder[nn.EmbeddingBag]):
+    """Shards a plain ``nn.EmbeddingBag`` (``torchrec/distributed/embeddingbag.py:2230-2255``)."""
+
+    def shard(self, module: nn.EmbeddingBag, params: Dict[str, ParameterSharding], env: ShardingEnv,
+              device: Optional[torch.device] = None, module_fqn: Optional[str] = None) -> ShardedEmbeddingBag:
+        return ShardedEmbeddingBag(module, params, env, self.fused_params, device)
+
+    def shardable_parameters(self, module: nn.EmbeddingBag) -> Dict[str, nn.Parameter]:
+        return dict(module.named_parameters())
+
+    @property
+    def module_type(self) -> Type[nn.EmbeddingBag]:
+        return nn.EmbeddingBag
 
 
 class EmbeddingBagCollectionSharder(BaseEmbeddingSharder[EmbeddingBagCollection]):

@@ -433,6 +433,10 @@ class NullShardingContext(Multistreamable):
         pass
 
 
+class NullShardedModuleContext(NullShardingContext):
+    """Context of a sharded module that carries nothing from its input dist to its output dist."""
+
+
 Out = TypeVar("Out")
 CompIn = TypeVar("CompIn")
 DistOut = TypeVar("DistOut")
