@@ -56,15 +56,18 @@ def main() -> None:
     keys = [f"cat_{i}" for i in range(len(rows))]
     tables = [EmbeddingBagConfig(name=f"t_{k}", embedding_dim=128, num_embeddings=r, feature_names=[k],
                                  data_type=DataType.INT4 if (a.int4_big and r >= 40_000_000) else DataType.INT8) for k, r in zip(keys, rows)]
-    qebc = QuantEmbeddingBagCollection(tables=tables, is_weighted=False, device=device, output_dtype=torch.bfloat16)
-    gen = torch.Generator(device=device).manual_seed(7)
-    for m in qebc.embedding_bags.values():
-        _fill_quantized(m.weight, gen)
+    sharded_serving = a.gpus > 1
+    # several GPUs: the unsharded module only describes the tables (meta device); every shard is created and filled on its own GPU
+    qebc = QuantEmbeddingBagCollection(tables=tables, is_weighted=False, device=torch.device("meta") if sharded_serving else device, output_dtype=torch.bfloat16)
+    if not sharded_serving:
+        gen = torch.Generator(device=device).manual_seed(7)
+        for m in qebc.embedding_bags.values():
+            _fill_quantized(m.weight, gen)
     torch.manual_seed(0)
     model = DLRM_DCN(qebc, dense_in_features=13, dense_arch_layer_sizes=[512, 256, 128], over_arch_layer_sizes=[1024, 1024, 512, 256, 1], dcn_num_layers=3,
                      dcn_low_rank_dim=512, dense_device=device).eval()
-    table_bytes = sum(m.weight.numel() for m in qebc.embedding_bags.values())
-    if a.gpus > 1:
+    table_bytes = sum(t.num_embeddings * (t.embedding_dim * (4 if t.data_type == DataType.INT4 else 8) // 8 + 4) for t in tables)
+    if sharded_serving:
         from torchrec_b200.distributed.quant_embeddingbag import ShardedQuantEmbeddingBagCollection
         from torchrec_b200.distributed.types import ParameterSharding, ShardingEnv
 
@@ -77,11 +80,15 @@ def main() -> None:
             load[r] += t.num_embeddings * 132
             plan[t.name] = ParameterSharding(sharding_type="table_wise", compute_kernel="quant", ranks=[r])
         sharded = ShardedQuantEmbeddingBagCollection(qebc, plan, ShardingEnv.from_local(world_size=a.gpus, rank=0), device=device)
+        for r, shard in enumerate(sharded._shards):
+            if hasattr(shard, "embedding_bags"):
+                gen_r = torch.Generator(device=torch.device("cuda", r)).manual_seed(7 + r)
+                for m in shard.embedding_bags.values():
+                    _fill_quantized(m.weight, gen_r)
         model.sparse_arch.embedding_bag_collection = sharded
-        for m in qebc.embedding_bags.values():  # the unsharded copy on GPU 0 is no longer needed
-            m.weight.set_(torch.empty(0, dtype=torch.uint8, device=device))
-        qebc._emb_modules = torch.nn.ModuleList()
-        torch.cuda.empty_cache()
+        qebc = sharded
+        for r in range(a.gpus):
+            torch.cuda.synchronize(r)
 
     ds = RandomRecDataset(keys=keys, batch_size=a.request_size, hash_sizes=rows, ids_per_features=POOLING, min_ids_per_features=POOLING, num_dense=13, manual_seed=99,
                           num_generated_batches=16, zipf_s=1.05, idx_dtype=torch.int32, label_positive_rate=0.25, dense_log_transform=True)
@@ -136,8 +143,9 @@ def main() -> None:
     torch.cuda.synchronize()
     back_to_back_ms = e0.elapsed_time(e1)
     wall = time.perf_counter() - t0
-    for emb in qebc._emb_modules:
-        emb.check_error()
+    for part in (qebc._shards if sharded_serving else [qebc]):
+        for emb in getattr(part, "_emb_modules", []):
+            emb.check_error()
     print(json.dumps({
         "metric": "quantized DLRM-DCNv2 inference latency", "n_gpus": a.gpus, "request_size": a.request_size, "requests": a.requests, "warmup": a.warmup,
         "p50_ms": lat[len(lat) // 2], "p99_ms": lat[min(len(lat) - 1, int(len(lat) * 0.99))], "mean_ms": sum(lat) / len(lat),

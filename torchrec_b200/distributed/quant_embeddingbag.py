@@ -101,7 +101,9 @@ class ShardedQuantEmbeddingBagCollection(ShardedQuantEmbeddingModuleState, nn.Mo
                 dev = _device_for(rank, self._device_type)
                 shard = QuantEmbeddingBagCollection(copy.deepcopy(cfgs), self._is_weighted, dev, output_dtype=module.output_dtype())
                 for cfg in cfgs:
-                    shard.embedding_bags[cfg.name].weight.copy_(slices[(kind, rank, cfg.name)].to(dev))
+                    piece = slices[(kind, rank, cfg.name)]
+                    if not piece.is_meta:  # a module built on the meta device is sharded without data: the caller loads every shard in place
+                        shard.embedding_bags[cfg.name].weight.copy_(piece.to(dev))
                 out.append(shard)
             return out
 

@@ -108,7 +108,7 @@ class _QuantCollectionBase(nn.Module):
             specs = [(t.num_embeddings_post_pruning or t.num_embeddings if hasattr(t, "num_embeddings_post_pruning") else t.num_embeddings, t.embedding_dim, BITS[t.data_type]) for t in group]
             ftm = [i for i, t in enumerate(group) for _ in t.feature_names]
             mode = pooling_type_to_pooling_mode(key) if pooled else PoolingMode.NONE
-            emb = QuantTableBatchedEmbeddingBags(specs, ftm, mode, output_dtype, device=device if device is not None and device.type != "meta" else None, persistent_weights=False)
+            emb = QuantTableBatchedEmbeddingBags(specs, ftm, mode, output_dtype, device=device, persistent_weights=False)
             for i, t in enumerate(group):
                 if table_name_to_quantized_weights and t.name in table_name_to_quantized_weights:
                     packed = table_name_to_quantized_weights[t.name][0]
