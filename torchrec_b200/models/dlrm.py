@@ -38,21 +38,19 @@ class SparseArch(nn.Module):
 
     def __init__(self, embedding_bag_collection: EmbeddingBagCollection) -> None:
         super().__init__()
+        configs = embedding_bag_collection.embedding_bag_configs()
+        assert configs, "Embedding bag collection cannot be empty!"
         self.embedding_bag_collection = embedding_bag_collection
-        assert self.embedding_bag_collection.embedding_bag_configs, "Embedding bag collection cannot be empty!"
-        self.D: int = self.embedding_bag_collection.embedding_bag_configs()[0].embedding_dim
-        self._sparse_feature_names: List[str] = [
-            name for conf in embedding_bag_collection.embedding_bag_configs() for name in conf.feature_names
-        ]
-        self.F: int = len(self._sparse_feature_names)
+        self._sparse_feature_names: List[str] = [feature for cfg in configs for feature in cfg.feature_names]
+        self.F, self.D = len(self._sparse_feature_names), int(configs[0].embedding_dim)
 
     def forward(self, features: KeyedJaggedTensor) -> torch.Tensor:
-        sparse_features: KeyedTensor = self.embedding_bag_collection(features)
-        if sparse_features.keys() == self._sparse_feature_names:
-            # already in feature order: the pooled buffer is used as is (no split + cat copy)
-            return sparse_features.values().reshape(-1, self.F, self.D)
-        sparse: Dict[str, torch.Tensor] = sparse_features.to_dict()
-        return torch.cat([sparse[n] for n in self._sparse_feature_names], dim=1).reshape(-1, self.F, self.D)
+        pooled: KeyedTensor = self.embedding_bag_collection(features)
+        values = pooled.values()
+        if pooled.keys() != self._sparse_feature_names:  # rare: put the blocks in feature order (one gathering copy)
+            by_key = pooled.to_dict()
+            values = torch.cat([by_key[name] for name in self._sparse_feature_names], dim=1)
+        return values.reshape(-1, self.F, self.D)
 
     @property
     def sparse_feature_names(self) -> List[str]:
@@ -86,6 +84,11 @@ class InteractionArch(nn.Module):
         return dense_ops.dot_interaction(dense_features, sparse_features)
 
 
+def _dense_and_sparse_flat(dense_features: torch.Tensor, sparse_features: torch.Tensor) -> torch.Tensor:
+    """``[B, D]`` and ``[B, F, D]`` side by side as one ``[B, (F + 1) * D]`` row per sample, dense block first."""
+    return torch.cat((dense_features, sparse_features.to(dense_features.dtype).flatten(1)), dim=1)
+
+
 class InteractionDCNArch(nn.Module):
     """Cross-network interaction over the flattened ``[dense, sparse]`` vector -> ``[B, (F+1)*D]``."""
 
@@ -95,11 +98,7 @@ class InteractionDCNArch(nn.Module):
         self.crossnet = crossnet
 
     def forward(self, dense_features: torch.Tensor, sparse_features: torch.Tensor) -> torch.Tensor:
-        if self.F <= 0:
-            return dense_features
-        B = dense_features.shape[0]
-        combined = torch.cat((dense_features.unsqueeze(1), sparse_features.to(dense_features.dtype)), dim=1)
-        return self.crossnet(combined.reshape([B, -1]))
+        return self.crossnet(_dense_and_sparse_flat(dense_features, sparse_features)) if self.F > 0 else dense_features
 
 
 class InteractionProjectionArch(nn.Module):
@@ -115,11 +114,11 @@ class InteractionProjectionArch(nn.Module):
         if self.F <= 0:
             return dense_features
         B, D = dense_features.shape
-        combined = torch.cat((dense_features.unsqueeze(1), sparse_features.to(dense_features.dtype)), dim=1)
-        b1 = self.interaction_branch1(torch.reshape(combined, (B, -1)))
-        b2 = self.interaction_branch2(torch.reshape(combined, (B, -1)))
-        interactions = torch.bmm(b1.reshape([B, -1, D]), b2.reshape([B, D, -1]))
-        return torch.cat((dense_features, torch.reshape(interactions, (B, -1)).to(dense_features.dtype)), dim=1)
+        flat = _dense_and_sparse_flat(dense_features, sparse_features)
+        left = self.interaction_branch1(flat).view(B, -1, D)    # [B, F1, D]
+        right = self.interaction_branch2(flat).view(B, D, -1)   # [B, D, F2]
+        pairwise = torch.bmm(left, right).flatten(1).to(dense_features.dtype)
+        return torch.cat((dense_features, pairwise), dim=1)
 
 
 class OverArch(nn.Module):

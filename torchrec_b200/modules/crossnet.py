@@ -14,26 +14,29 @@ import torch
 from torchrec_b200.ops import dense_ops
 
 
+def _xavier(count: int, *shape: int) -> torch.nn.ParameterList:
+    """``count`` Xavier-normal parameters of ``shape`` (one per layer)."""
+    return torch.nn.ParameterList([torch.nn.Parameter(torch.nn.init.xavier_normal_(torch.empty(*shape))) for _ in range(count)])
+
+
+def _zeros(count: int, *shape: int) -> torch.nn.ParameterList:
+    return torch.nn.ParameterList([torch.nn.Parameter(torch.zeros(*shape)) for _ in range(count)])
+
+
 class CrossNet(torch.nn.Module):
     """Full-rank cross network: ``x_{l+1} = x_0 * (W_l x_l + b_l) + x_l`` with ``W_l [N, N]``."""
 
     def __init__(self, in_features: int, num_layers: int) -> None:
         super().__init__()
         self._num_layers = num_layers
-        self.kernels: torch.nn.ParameterList = torch.nn.ParameterList(
-            [torch.nn.Parameter(torch.nn.init.xavier_normal_(torch.empty(in_features, in_features))) for _ in range(num_layers)]
-        )
-        self.bias: torch.nn.ParameterList = torch.nn.ParameterList(
-            [torch.nn.Parameter(torch.nn.init.zeros_(torch.empty(in_features, 1))) for _ in range(num_layers)]
-        )
+        self.kernels = _xavier(num_layers, in_features, in_features)
+        self.bias = _zeros(num_layers, in_features, 1)
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
-        x_0 = input.unsqueeze(2)  # (B, N, 1)
-        x_l = x_0
-        for layer in range(self._num_layers):
-            xl_w = torch.matmul(self.kernels[layer], x_l)
-            x_l = x_0 * (xl_w + self.bias[layer]) + x_l
-        return torch.squeeze(x_l, dim=2)
+        x = input
+        for w, b in zip(self.kernels, self.bias):  # rows of the batch are independent: plain [B, N] algebra
+            x = torch.addcmul(x, input, torch.nn.functional.linear(x, w, b.view(-1)))
+        return x
 
 
 class LowRankCrossNet(torch.nn.Module):
@@ -42,29 +45,21 @@ class LowRankCrossNet(torch.nn.Module):
     def __init__(self, in_features: int, num_layers: int, low_rank: int = 1) -> None:
         super().__init__()
         assert low_rank >= 1, "Low rank must be larger or equal to 1"
-        self._num_layers = num_layers
-        self._low_rank = low_rank
-        self.W_kernels: torch.nn.ParameterList = torch.nn.ParameterList(
-            [torch.nn.Parameter(torch.nn.init.xavier_normal_(torch.empty(in_features, low_rank))) for _ in range(num_layers)]
-        )
-        self.V_kernels: torch.nn.ParameterList = torch.nn.ParameterList(
-            [torch.nn.Parameter(torch.nn.init.xavier_normal_(torch.empty(low_rank, in_features))) for _ in range(num_layers)]
-        )
-        self.bias: torch.nn.ParameterList = torch.nn.ParameterList(
-            [torch.nn.Parameter(torch.nn.init.zeros_(torch.empty(in_features))) for _ in range(num_layers)]
-        )
+        self._num_layers, self._low_rank = num_layers, low_rank
+        self.W_kernels = _xavier(num_layers, in_features, low_rank)
+        self.V_kernels = _xavier(num_layers, low_rank, in_features)
+        self.bias = _zeros(num_layers, in_features)
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
-        x_0 = input
-        x_l = x_0
-        if dense_ops.fused_dense_enabled(input) and input.shape[1] % 8 == 0 and self._low_rank % 8 == 0:
-            x_0 = x_0 if x_0.dtype == torch.bfloat16 else x_0.to(torch.bfloat16)
-            return dense_ops.lowrank_cross_stack(x_0, list(self.V_kernels), list(self.W_kernels), list(self.bias))
-        for layer in range(self._num_layers):
-            x_l_v = torch.nn.functional.linear(x_l, self.V_kernels[layer])
-            x_l_w = torch.nn.functional.linear(x_l_v, self.W_kernels[layer])
-            x_l = x_0 * (x_l_w + self.bias[layer]) + x_l
-        return x_l
+        tensor_core_shapes = input.shape[1] % 8 == 0 and self._low_rank % 8 == 0
+        if tensor_core_shapes and dense_ops.fused_dense_enabled(input):
+            x0 = input if input.dtype == torch.bfloat16 else input.to(torch.bfloat16)
+            return dense_ops.lowrank_cross_stack(x0, list(self.V_kernels), list(self.W_kernels), list(self.bias))
+        x = input
+        for v, w, b in zip(self.V_kernels, self.W_kernels, self.bias):
+            projected = torch.nn.functional.linear(torch.nn.functional.linear(x, v), w, b)
+            x = torch.addcmul(x, input, projected)
+        return x
 
 
 class VectorCrossNet(torch.nn.Module):
@@ -73,20 +68,14 @@ class VectorCrossNet(torch.nn.Module):
     def __init__(self, in_features: int, num_layers: int) -> None:
         super().__init__()
         self._num_layers = num_layers
-        self.kernels: torch.nn.ParameterList = torch.nn.ParameterList(
-            [torch.nn.Parameter(torch.nn.init.xavier_normal_(torch.empty(in_features, 1))) for _ in range(num_layers)]
-        )
-        self.bias: torch.nn.ParameterList = torch.nn.ParameterList(
-            [torch.nn.Parameter(torch.nn.init.zeros_(torch.empty(in_features, 1))) for _ in range(num_layers)]
-        )
+        self.kernels = _xavier(num_layers, in_features, 1)
+        self.bias = _zeros(num_layers, in_features, 1)
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
-        x_0 = input.unsqueeze(2)
-        x_l = x_0
-        for layer in range(self._num_layers):
-            xl_w = torch.tensordot(x_l, self.kernels[layer], dims=([1], [0]))
-            x_l = torch.matmul(x_0, xl_w) + self.bias[layer] + x_l
-        return torch.squeeze(x_l, dim=2)
+        x = input
+        for w, b in zip(self.kernels, self.bias):
+            x = input * (x @ w) + b.view(-1) + x  # (x @ w) is one scalar per sample
+        return x
 
 
 class LowRankMixtureCrossNet(torch.nn.Module):
@@ -103,40 +92,27 @@ class LowRankMixtureCrossNet(torch.nn.Module):
         super().__init__()
         assert num_experts >= 1, "num_experts must be larger or equal to 1"
         assert low_rank >= 1, "Low rank must be larger or equal to 1"
-        self._num_layers = num_layers
-        self._num_experts = num_experts
-        self._low_rank = low_rank
-        self._in_features = in_features
-        mk = lambda *s: torch.nn.Parameter(torch.nn.init.xavier_normal_(torch.empty(*s)))  # noqa: E731
-        self.U_kernels = torch.nn.ParameterList([mk(num_experts, in_features, low_rank) for _ in range(num_layers)])
-        self.V_kernels = torch.nn.ParameterList([mk(num_experts, low_rank, in_features) for _ in range(num_layers)])
-        self.bias = torch.nn.ParameterList(
-            [torch.nn.Parameter(torch.nn.init.zeros_(torch.empty(in_features, 1))) for _ in range(num_layers)]
-        )
-        self.gates: Optional[torch.nn.Module] = (
-            torch.nn.ModuleList([torch.nn.Linear(in_features, 1, bias=False) for _ in range(num_experts)])
-            if num_experts > 1 else None
-        )
+        self._num_layers, self._num_experts, self._low_rank, self._in_features = num_layers, num_experts, low_rank, in_features
         self._activation = activation
-        self.C_kernels = torch.nn.ParameterList([mk(num_experts, low_rank, low_rank) for _ in range(num_layers)])
+        self.U_kernels = _xavier(num_layers, num_experts, in_features, low_rank)
+        self.V_kernels = _xavier(num_layers, num_experts, low_rank, in_features)
+        self.bias = _zeros(num_layers, in_features, 1)
+        self.gates: Optional[torch.nn.Module] = None
+        if num_experts > 1:
+            self.gates = torch.nn.ModuleList([torch.nn.Linear(in_features, 1, bias=False) for _ in range(num_experts)])
+        self.C_kernels = _xavier(num_layers, num_experts, low_rank, low_rank)
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
-        x_0 = input.unsqueeze(2)
-        x_l = x_0
-        for layer in range(self._num_layers):
-            gating = None
-            if self._num_experts > 1:
-                gating = torch.stack([self.gates[i](x_l.squeeze(2)) for i in range(self._num_experts)], 1)
-            experts = []
-            for i in range(self._num_experts):
-                e = torch.matmul(self.V_kernels[layer][i], x_l)
-                e = torch.matmul(self.C_kernels[layer][i], self._activation(e))
-                e = torch.matmul(self.U_kernels[layer][i], self._activation(e))
-                e = x_0 * (e + self.bias[layer])
-                experts.append(e.squeeze(2))
-            experts = torch.stack(experts, 2)
-            if gating is not None:
-                x_l = torch.matmul(experts, torch.nn.functional.softmax(gating, 1)) + x_l
+        act = self._activation
+        x = input
+        for u, c, v, b in zip(self.U_kernels, self.C_kernels, self.V_kernels, self.bias):
+            # all experts at once: [B, N] -> [B, E, r] -> [B, E, r] -> [B, E, N]
+            h = act(torch.einsum("ern,bn->ber", v, x))
+            h = act(torch.einsum("ers,bes->ber", c, h))
+            experts = input.unsqueeze(1) * (torch.einsum("enr,ber->ben", u, h) + b.view(1, 1, -1))
+            if self.gates is None:
+                x = experts.squeeze(1) + x
             else:
-                x_l = experts + x_l
-        return torch.squeeze(x_l, dim=2)
+                scores = torch.cat([gate(x) for gate in self.gates], dim=1)  # [B, E]
+                x = torch.einsum("ben,be->bn", experts, torch.softmax(scores, dim=1)) + x
+        return x
