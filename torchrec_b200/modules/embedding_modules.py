@@ -54,6 +54,18 @@ def get_embedding_names_by_table(tables) -> List[List[str]]:
     return out
 
 
+def _reject_duplicate_names(tables) -> None:
+    seen = set()
+    for cfg in tables:
+        if cfg.name in seen:
+            raise ValueError(f"Duplicate table name {cfg.name}")
+        seen.add(cfg.name)
+
+
+def _table_dtype(cfg) -> torch.dtype:
+    return torch.float32 if cfg.data_type == DataType.FP32 else data_type_to_dtype(cfg.data_type)
+
+
 class EmbeddingBagCollectionInterface(abc.ABC, nn.Module):
     @abc.abstractmethod
     def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
@@ -82,53 +94,34 @@ class EmbeddingBagCollection(EmbeddingBagCollectionInterface):
         device: Optional[torch.device] = None,
     ) -> None:
         super().__init__()
-        self._is_weighted = is_weighted
-        self.embedding_bags: nn.ModuleDict = nn.ModuleDict()
-        self._embedding_bag_configs = tables
-        self._lengths_per_embedding: List[int] = []
-        self._dtypes: List[int] = []
-        table_names = set()
+        _reject_duplicate_names(tables)
+        self._is_weighted, self._embedding_bag_configs = is_weighted, tables
         for cfg in tables:
-            if cfg.name in table_names:
-                raise ValueError(f"Duplicate table name {cfg.name}")
-            table_names.add(cfg.name)
-            dtype = torch.float32 if cfg.data_type == DataType.FP32 else data_type_to_dtype(cfg.data_type)
-            self.embedding_bags[cfg.name] = nn.EmbeddingBag(
-                num_embeddings=cfg.num_embeddings,
-                embedding_dim=cfg.embedding_dim,
-                mode=pooling_type_to_str(cfg.pooling),
-                device=device,
-                include_last_offset=True,
-                dtype=dtype,
-            )
-            if device is None:
-                device = self.embedding_bags[cfg.name].weight.device
-            if not cfg.feature_names:
-                cfg.feature_names = [cfg.name]
-            self._lengths_per_embedding.extend(len(cfg.feature_names) * [cfg.embedding_dim])
-        self._device: torch.device = device if device is not None else torch.device("cpu")
+            cfg.feature_names = cfg.feature_names or [cfg.name]
+        self.embedding_bags = nn.ModuleDict({
+            cfg.name: nn.EmbeddingBag(cfg.num_embeddings, cfg.embedding_dim, mode=pooling_type_to_str(cfg.pooling), device=device,
+                                      include_last_offset=True, dtype=_table_dtype(cfg))
+            for cfg in tables
+        })
+        if device is None and tables:
+            device = self.embedding_bags[tables[0].name].weight.device
+        self._device: torch.device = torch.device("cpu") if device is None else device
+        self._lengths_per_embedding: List[int] = [cfg.embedding_dim for cfg in tables for _ in cfg.feature_names]
         self._embedding_names: List[str] = [n for names in get_embedding_names_by_table(tables) for n in names]
-        self._feature_names: List[List[str]] = [t.feature_names for t in tables]
+        self._feature_names: List[List[str]] = [cfg.feature_names for cfg in tables]
         self.reset_parameters()
 
     def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
-        flat_feature_names = [n for names in self._feature_names for n in names]
-        inverse_indices = reorder_inverse_indices(features.inverse_indices_or_none(), flat_feature_names)
+        inverse_indices = reorder_inverse_indices(features.inverse_indices_or_none(), [f for names in self._feature_names for f in names])
+        per_feature = features.to_dict()
         pooled: List[torch.Tensor] = []
-        feature_dict = features.to_dict()
-        for i, bag in enumerate(self.embedding_bags.values()):
-            for feature_name in self._feature_names[i]:
-                f = feature_dict[feature_name]
-                w = f.weights() if self._is_weighted else None
-                if w is not None and w.dtype != bag.weight.dtype:
-                    w = w.to(bag.weight.dtype)
-                res = bag(input=f.values(), offsets=f.offsets(), per_sample_weights=w).float()
-                pooled.append(res)
-        return KeyedTensor(
-            keys=self._embedding_names,
-            values=process_pooled_embeddings(pooled, inverse_indices),
-            length_per_key=self._lengths_per_embedding,
-        )
+        for bag, features_of_table in zip(self.embedding_bags.values(), self._feature_names):
+            for feature in features_of_table:
+                jt = per_feature[feature]
+                weights = jt.weights().to(bag.weight.dtype) if self._is_weighted else None
+                pooled.append(bag(jt.values(), jt.offsets(), per_sample_weights=weights).float())
+        return KeyedTensor(keys=self._embedding_names, values=process_pooled_embeddings(pooled, inverse_indices),
+                           length_per_key=self._lengths_per_embedding)
 
     def is_weighted(self) -> bool:
         return self._is_weighted
@@ -247,45 +240,34 @@ class EmbeddingCollection(EmbeddingCollectionInterface):
         need_indices: bool = False,
     ) -> None:
         super().__init__()
-        self.embeddings: nn.ModuleDict = nn.ModuleDict()
-        self._embedding_configs = tables
-        self._embedding_dim: int = -1
-        self._need_indices: bool = need_indices
-        self._device: torch.device = device if device is not None else torch.device("cpu")
-        table_names = set()
-        for config in tables:
-            if config.name in table_names:
-                raise ValueError(f"Duplicate table name {config.name}")
-            table_names.add(config.name)
-            self._embedding_dim = config.embedding_dim if self._embedding_dim < 0 else self._embedding_dim
-            if self._embedding_dim != config.embedding_dim:
-                raise ValueError(
-                    "All tables in a EmbeddingCollection are required to have same embedding dimension."
-                    + f" Violating case: {config.name}'s embedding_dim {config.embedding_dim} != {self._embedding_dim}"
-                )
-            dtype = torch.float32 if config.data_type == DataType.FP32 else data_type_to_dtype(config.data_type)
-            self.embeddings[config.name] = nn.Embedding(
-                num_embeddings=config.num_embeddings, embedding_dim=config.embedding_dim, device=device, dtype=dtype,
-            )
-            if not config.feature_names:
-                config.feature_names = [config.name]
+        _reject_duplicate_names(tables)
+        dims = {cfg.embedding_dim for cfg in tables}
+        if len(dims) > 1:
+            first = tables[0].embedding_dim
+            odd = next(cfg for cfg in tables if cfg.embedding_dim != first)
+            raise ValueError("All tables in a EmbeddingCollection are required to have same embedding dimension."
+                             f" Violating case: {odd.name}'s embedding_dim {odd.embedding_dim} != {first}")
+        self._embedding_configs, self._need_indices = tables, need_indices
+        self._embedding_dim: int = dims.pop() if dims else -1
+        self._device: torch.device = torch.device("cpu") if device is None else device
+        self.embeddings = nn.ModuleDict({
+            cfg.name: nn.Embedding(cfg.num_embeddings, cfg.embedding_dim, device=device, dtype=_table_dtype(cfg)) for cfg in tables
+        })
+        for cfg in tables:
+            cfg.feature_names = cfg.feature_names or [cfg.name]
         self._embedding_names_by_table: List[List[str]] = get_embedding_names_by_table(tables)
-        self._feature_names: List[List[str]] = [t.feature_names for t in tables]
+        self._feature_names: List[List[str]] = [cfg.feature_names for cfg in tables]
         self.reset_parameters()
 
     def forward(self, features: KeyedJaggedTensor) -> Dict[str, JaggedTensor]:
-        feature_embeddings: Dict[str, JaggedTensor] = {}
-        jt_dict = features.to_dict()
-        for i, emb_module in enumerate(self.embeddings.values()):
-            feature_names = self._feature_names[i]
-            embedding_names = self._embedding_names_by_table[i]
-            for j, embedding_name in enumerate(embedding_names):
-                f = jt_dict[feature_names[j]]
-                lookup = emb_module(input=f.values()).float()
-                feature_embeddings[embedding_name] = JaggedTensor(
-                    values=lookup, lengths=f.lengths(), weights=f.values() if self._need_indices else None,
-                )
-        return feature_embeddings
+        per_feature = features.to_dict()
+        out: Dict[str, JaggedTensor] = {}
+        for table, features_of_table, names_of_table in zip(self.embeddings.values(), self._feature_names, self._embedding_names_by_table):
+            for feature, name in zip(features_of_table, names_of_table):
+                jt = per_feature[feature]
+                ids = jt.values()
+                out[name] = JaggedTensor(values=table(ids).float(), lengths=jt.lengths(), weights=ids if self._need_indices else None)
+        return out
 
     def need_indices(self) -> bool:
         return self._need_indices
