@@ -50,6 +50,7 @@ def main() -> None:
     p.add_argument("--max-len", type=int, default=200)
     p.add_argument("--negatives", type=int, default=8192)
     p.add_argument("--pool", type=int, default=4, help="distinct batches cycled")
+    p.add_argument("--padded", action="store_true", help="run the encoder on padded [B, max_len, D] tensors through the library modules (the packed, fused path is the default)")
     p.add_argument("--cpu", action="store_true", help="plumbing check on the host (gloo); not a benchmark")
     p.add_argument("--kernel-table", action="store_true", help="print the device time per kernel of one untimed step to stderr")
     a = p.parse_args()
@@ -84,6 +85,11 @@ def main() -> None:
     torch.manual_seed(0)
     model = BERT4RecSampled(a.vocab, a.max_len, a.dim, nhead=4, num_layers=2, dim_feedforward=1024, dropout=0.1, device=device,
                             embedding_device=torch.device("meta"), data_type=DataType.BF16)
+    model.packed = not a.padded
+    if not a.cpu and not a.padded:
+        from torchrec_b200.ops import dense_ops
+
+        dense_ops.set_dense_compute_dtype(torch.bfloat16)  # the packed encoder's projections run on the tcgen05 GEMMs
     ec = model.history.ec
     apply_optimizer_in_backward(torch.optim.Adam, ec.parameters(), {"lr": 1e-3})
     sharder = EmbeddingCollectionSharder()
@@ -155,7 +161,7 @@ def main() -> None:
     exchange = "fused into the lookup over peer memory" if sharded_ec is not None and sharded_ec._engine_state == "on" else "library collectives"
     if rank == 0:
         print(json.dumps({
-            "metric": "BERT4Rec train sequences/sec", "exchange": exchange, "value": a.batch_per_rank * world / (ms_per_step / 1e3), "unit": "sequences/s",
+            "metric": "BERT4Rec train sequences/sec", "exchange": exchange, "encoder": "padded, library modules" if a.padded else "packed tokens, fused kernels", "value": a.batch_per_rank * world / (ms_per_step / 1e3), "unit": "sequences/s",
             "tokens_per_s": float(tok) / (ms_per_step / 1e3), "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
             "loss": float(loss.detach()), "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic (Zipf(1.1) items, lengths U[20,200], 15% masked)",
             "config": {"model": "BERT4Rec 2 layers, 4 heads, hidden 256, FFN 1024, sampled softmax 8192 negatives", "item_tables": f"input and output embeddings, each {a.vocab} x {a.dim} bf16",

@@ -18,8 +18,10 @@ from typing import Dict, Optional, Tuple
 import torch
 from torch import nn
 
+from torchrec_b200.modules import jagged_transformer
 from torchrec_b200.modules.embedding_configs import DataType, EmbeddingConfig
 from torchrec_b200.modules.embedding_modules import EmbeddingCollection
+from torchrec_b200.ops.transformer_ops import residual_layer_norm
 from torchrec_b200.ops import sparse_ops as sops
 from torchrec_b200.sparse.jagged_tensor import JaggedTensor, KeyedJaggedTensor
 
@@ -54,11 +56,32 @@ class HistoryArch(nn.Module):
         x = padded + self.positional.unsqueeze(0).to(padded.dtype)
         return self.dropout(self.layernorm(x)), mask, jt_dict
 
+    def forward_packed(self, id_list_features: KeyedJaggedTensor) -> Tuple[torch.Tensor, torch.Tensor, Dict[str, JaggedTensor]]:
+        """The same embedding stage without padding: ``[T, D]`` rows of all histories back to back, their ``offsets [B + 1]``, and
+        the looked-up jagged tensors.  Histories are expected to hold at most ``history_len`` items."""
+        jt_dict = self.ec(id_list_features)
+        if hasattr(jt_dict, "wait"):
+            jt_dict = jt_dict.wait()
+        jt: JaggedTensor = jt_dict[self.feature_name]
+        rows, lengths, offsets = jt.values(), jt.lengths(), jt.offsets()
+        T = rows.shape[0]
+        first = torch.repeat_interleave(offsets[:-1].to(torch.int64), lengths.to(torch.int64), output_size=T)
+        position = (torch.arange(T, device=rows.device) - first).clamp_(max=self.history_len - 1)
+        x = rows + self.positional.to(rows.dtype).index_select(0, position)
+        _, y = residual_layer_norm(None, x.contiguous(), self.layernorm.weight, self.layernorm.bias, 0.0, self.training, self.layernorm.eps)
+        return self.dropout(y), offsets, jt_dict
+
 
 def _encoder(emb_dim: int, nhead: int, num_layers: int, dim_feedforward: Optional[int], dropout: float, device: Optional[torch.device]) -> nn.TransformerEncoder:
     layer = nn.TransformerEncoderLayer(d_model=emb_dim, nhead=nhead, dim_feedforward=dim_feedforward or 4 * emb_dim, dropout=dropout, activation="gelu",
                                        batch_first=True, norm_first=True, device=device)
     return nn.TransformerEncoder(layer, num_layers=num_layers, enable_nested_tensor=False)
+
+
+def _packed_positions(positions: torch.Tensor, offsets: torch.Tensor, max_len: int) -> torch.Tensor:
+    """Flat positions into the padded ``[B * max_len]`` layout -> row indices of the packed ``[T]`` layout."""
+    sample = torch.div(positions, max_len, rounding_mode="floor")
+    return offsets.to(torch.int64).index_select(0, sample) + (positions - sample * max_len)
 
 
 class BERT4Rec(nn.Module):
@@ -76,6 +99,11 @@ class BERT4Rec(nn.Module):
         h = self.encoder(x, src_key_padding_mask=~mask)
         return h, mask
 
+    def encode_packed(self, input: KeyedJaggedTensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Hidden states of the real tokens only, ``[T, D]`` with the sequence ``offsets`` (no padding position is computed)."""
+        x, offsets, _ = self.history.forward_packed(input)
+        return jagged_transformer.jagged_encoder_forward(self.encoder, x, offsets, self.max_len), offsets
+
     def forward(self, input: KeyedJaggedTensor, positions: Optional[torch.Tensor] = None, targets: Optional[torch.Tensor] = None,
                 negatives: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Logits ``[B, max_len, vocab]`` over the full vocabulary; with ``positions`` / ``targets`` / ``negatives`` the sampled
@@ -89,8 +117,12 @@ class BERT4Rec(nn.Module):
     def sampled_logits(self, input: KeyedJaggedTensor, positions: torch.Tensor, targets: torch.Tensor, negatives: torch.Tensor) -> torch.Tensor:
         """Scores of the hidden states at flat ``positions`` (into ``[B*max_len]``) against their target item and a shared set of
         sampled negatives: ``[P, 1 + N]`` (column 0 is the positive)."""
-        h, _ = self.encode(input)
-        hp = h.reshape(-1, h.shape[-1]).index_select(0, positions)
+        if jagged_transformer.supports(self.encoder):
+            h, offsets = self.encode_packed(input)
+            hp = h.index_select(0, _packed_positions(positions, offsets, self.max_len)).to(self.out.weight.dtype)
+        else:
+            h, _ = self.encode(input)
+            hp = h.reshape(-1, h.shape[-1]).index_select(0, positions)
         w = self.out.weight
         pos = (hp * w.index_select(0, targets)).sum(-1, keepdim=True) + self.out.bias.index_select(0, targets).unsqueeze(1)
         neg = hp @ w.index_select(0, negatives).t() + self.out.bias.index_select(0, negatives).unsqueeze(0)
@@ -111,6 +143,7 @@ class BERT4RecSampled(nn.Module):
         self.vocab_size, self.max_len = vocab_size, max_len
         self.history = HistoryArch(vocab_size, max_len, emb_dim, dropout, device, embedding_device=embedding_device, data_type=data_type, output_table_feature="cand")
         self.encoder = _encoder(emb_dim, nhead, num_layers, dim_feedforward, dropout, device)
+        self.packed = True  # run the encoder over the real tokens only (False: padded [B, max_len, D] through the library modules)
 
     @staticmethod
     def make_input(items: torch.Tensor, lengths: torch.Tensor, targets: torch.Tensor, negatives: torch.Tensor) -> KeyedJaggedTensor:
@@ -120,9 +153,14 @@ class BERT4RecSampled(nn.Module):
         return KeyedJaggedTensor(keys=["item", "cand"], values=torch.cat([items, targets, negatives]), lengths=torch.cat([lengths, cand_len]), stride=B)
 
     def forward(self, input: KeyedJaggedTensor, positions: torch.Tensor) -> torch.Tensor:
-        x, mask, jts = self.history(input)
-        h = self.encoder(x, src_key_padding_mask=~mask)
-        hp = h.reshape(-1, h.shape[-1]).index_select(0, positions)
+        if self.packed and jagged_transformer.supports(self.encoder):
+            x, offsets, jts = self.history.forward_packed(input)
+            h = jagged_transformer.jagged_encoder_forward(self.encoder, x, offsets, self.max_len)
+            hp = h.index_select(0, _packed_positions(positions, offsets, self.max_len))
+        else:
+            x, mask, jts = self.history(input)
+            h = self.encoder(x, src_key_padding_mask=~mask)
+            hp = h.reshape(-1, h.shape[-1]).index_select(0, positions)
         cand = jts["cand"].values().to(hp.dtype)
         P = positions.numel()
         pos = (hp * cand[:P]).sum(-1, keepdim=True)
