@@ -149,3 +149,64 @@ def test_plan_report_lists_every_table():
     for t in ("t0", "t1", "t2"):
         assert t in report
     assert "Rank" in report or "rank" in report
+
+
+def test_perf_estimator_matches_hand_computed_numbers():
+    """The wall-time model on round numbers, worked out by hand here (cf. ``torchrec/distributed/planner/tests/test_shard_estimators.py``):
+    bandwidths of 1000 bytes/ms for memory and 100 bytes/ms for the links make every term readable."""
+    from torchrec_b200.distributed.planner.shard_estimators import EmbeddingPerfEstimator
+    from torchrec_b200.distributed.planner.types import BasicCommsBandwidths
+
+    common = dict(
+        compute_kernel="fused", compute_device="cuda", batch_sizes=[10], world_size=2, local_world_size=2, input_lengths=[4.0],
+        input_data_type_size=8.0, table_data_type_size=4.0, output_data_type_size=4.0, fwd_a2a_comm_data_type_size=4.0,
+        bwd_a2a_comm_data_type_size=4.0, fwd_sr_comm_data_type_size=4.0, bwd_sr_comm_data_type_size=4.0, num_poolings=[1.0],
+        hbm_mem_bw=1250.0, ddr_mem_bw=100.0, hbm_to_ddr_mem_bw=10.0, comms_bandwidths=BasicCommsBandwidths(inter_host_bw=10.0, intra_host_bw=100.0),
+        bwd_compute_multiplier=2.0, weighted_feature_bwd_compute_multiplier=1.0, is_pooled=True,
+    )
+    # fused kernels read at 0.8 x HBM = 1000 bytes/ms; dim 128 carries no narrow-row penalty
+    (tw,) = EmbeddingPerfEstimator.perf_func_emb_wall_time(shard_sizes=[[1000, 128]], sharding_type="table_wise", **common)
+    ids = 4 * 10 * 2                      # pooling x batch x world: the owner looks up the global batch
+    id_bytes, row_bytes, out_bytes = ids * 8, ids * 128 * 4, 10 * 2 * 128 * 4
+    assert tw.fwd_compute == pytest.approx((id_bytes + row_bytes + out_bytes) / 1000.0)
+    assert tw.fwd_comms == pytest.approx(out_bytes * 0.5 / 100.0)     # half of the pooled rows leave the owner
+    assert tw.bwd_compute == pytest.approx(2.0 * tw.fwd_compute)
+    assert tw.bwd_comms == pytest.approx(tw.fwd_comms)
+    # exchanges fused into the lookup kernels overlap with them: the slower of the two sides is the cost
+    from torchrec_b200.distributed.planner.constants import FUSED_DIST_OVERLAP
+
+    overlapped = max(tw.fwd_compute, tw.fwd_comms) + max(tw.bwd_compute, tw.bwd_comms)
+    assert tw.total == pytest.approx(overlapped if FUSED_DIST_OVERLAP else tw.fwd_compute + tw.fwd_comms + tw.bwd_compute + tw.bwd_comms)
+    # row-wise over 2 shards: half the ids per shard, a partial row for every bag of the global batch from every shard
+    (rw, rw2) = EmbeddingPerfEstimator.perf_func_emb_wall_time(shard_sizes=[[500, 128], [500, 128]], sharding_type="row_wise", **common)
+    assert rw.fwd_compute == pytest.approx((id_bytes / 2 + row_bytes / 2 + out_bytes) / 1000.0)
+    assert rw.fwd_comms == pytest.approx(out_bytes * 0.5 / 100.0)
+    assert rw2.total == pytest.approx(rw.total)
+    # data parallel: local batch only, no exchange forward, the whole table's gradient all-reduced backward
+    (dp,) = EmbeddingPerfEstimator.perf_func_emb_wall_time(shard_sizes=[[1000, 128]], sharding_type="data_parallel", **common)
+    local_ids = 4 * 10
+    assert dp.fwd_comms == 0
+    assert dp.fwd_compute == pytest.approx((local_ids * 8 + local_ids * 128 * 4 + 10 * 128 * 4) / 1000.0)
+    assert dp.bwd_comms == pytest.approx(1000 * 128 * 4 / 100.0)
+    # narrow rows waste part of every memory transaction
+    (narrow,) = EmbeddingPerfEstimator.perf_func_emb_wall_time(shard_sizes=[[1000, 16]], sharding_type="table_wise", **common)
+    assert narrow.fwd_compute > (id_bytes + ids * 32 * 4 + 10 * 2 * 16 * 4) / 1000.0
+    # inference has no backward
+    (inf,) = EmbeddingPerfEstimator.perf_func_emb_wall_time(shard_sizes=[[1000, 128]], sharding_type="table_wise", is_inference=True, **common)
+    assert inf.bwd_compute == 0 and inf.bwd_comms == 0 and inf.fwd_compute == pytest.approx(tw.fwd_compute)
+
+
+def test_perf_estimator_tracks_the_measured_lookup():
+    """Calibration against a measured kernel time on B200: the pooled forward over 14.0 M ids x 512 B rows took 1.31 ms; the model's
+    forward-compute figure for the same work on the default topology must land within a factor 1.5 of it."""
+    from torchrec_b200.distributed.planner.constants import HBM_MEM_BW
+    from torchrec_b200.distributed.planner.shard_estimators import EmbeddingPerfEstimator
+    from torchrec_b200.distributed.planner.types import BasicCommsBandwidths
+
+    (p,) = EmbeddingPerfEstimator.perf_func_emb_wall_time(
+        shard_sizes=[[40_000_000, 128]], compute_kernel="fused", compute_device="cuda", sharding_type="table_wise", batch_sizes=[65536], world_size=1,
+        local_world_size=1, input_lengths=[214.0], input_data_type_size=4.0, table_data_type_size=4.0, output_data_type_size=2.0,
+        fwd_a2a_comm_data_type_size=2.0, bwd_a2a_comm_data_type_size=2.0, fwd_sr_comm_data_type_size=2.0, bwd_sr_comm_data_type_size=2.0,
+        num_poolings=[1.0], hbm_mem_bw=HBM_MEM_BW, ddr_mem_bw=1.0, hbm_to_ddr_mem_bw=1.0, comms_bandwidths=BasicCommsBandwidths(),
+        bwd_compute_multiplier=2.0, weighted_feature_bwd_compute_multiplier=1.0, is_pooled=True)
+    assert 1.31 / 1.5 < p.fwd_compute < 1.31 * 1.5, p.fwd_compute

@@ -57,6 +57,7 @@ def main() -> None:
     p.add_argument("--pooling", type=int, default=20)
     p.add_argument("--batch-per-rank", type=int, default=16384)
     p.add_argument("--cpu", action="store_true", help="plumbing check on the host (gloo); not a benchmark")
+    p.add_argument("--qcomm", action="store_true", help="16-bit exchanges: fp16 partial rows forward, bf16 gradients backward (quantised-comms config); default fp32")
     p.add_argument("--no-library-collectives", action="store_true", help="skip timing the exchanges as library collectives")
     a = p.parse_args()
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -97,7 +98,12 @@ def main() -> None:
     model = torch.nn.Module()
     model.ebc = ebc
     apply_optimizer_in_backward(RowWiseAdagrad, ebc.parameters(), {"lr": 0.01, "eps": 1e-8})
-    sharder = EmbeddingBagCollectionSharder(fused_params={"output_dtype": DataType.FP16})
+    registry = None
+    if a.qcomm:
+        from torchrec_b200.distributed.fbgemm_qcomm_codec import CommType, QCommsConfig, get_qcomm_codecs_registry
+
+        registry = get_qcomm_codecs_registry(QCommsConfig(forward_precision=CommType.FP16, backward_precision=CommType.BF16))
+    sharder = EmbeddingBagCollectionSharder(fused_params={"output_dtype": DataType.FP16}, qcomm_codecs_registry=registry)
     mplan = sp.construct_module_sharding_plan(ebc, {t.name: sp.row_wise() for t in tables}, sharder=sharder, world_size=world, local_size=world, device_type=device.type)
     dmp = DistributedModelParallel(model, env=ShardingEnv.from_process_group(dist.group.WORLD), device=device, plan=ShardingPlan({"ebc": mplan}), sharders=[sharder])
     sebc = dmp.module.ebc
@@ -181,6 +187,7 @@ def main() -> None:
             "path": "fused sparse engine over peer memory" if engine is not None else "library collectives",
             "engine_phases": phases, "library_collectives_same_shapes": lib,
             "config": {"tables": a.tables, "rows": a.rows, "dim": a.dim, "dtype": "fp16", "pooling": a.pooling, "batch_per_rank": B, "data": "synthetic uniform ids",
+                       "exchange_precision": "fp16 forward / bf16 backward" if a.qcomm else "fp32",
                        "timing": "CUDA events, max over ranks; phase times are taken inside real steps and include waiting for peers"}}))
     dist.destroy_process_group()
 

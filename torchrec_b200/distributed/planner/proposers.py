@@ -54,21 +54,30 @@ class GreedyProposer(Proposer):
             return [self._sharding_options_by_fqn[fqn][i] for fqn, i in self._current_proposal.items()]
         return None
 
+    def _patience_ran_out(self, perf_rating: Optional[float]) -> bool:
+        """With a threshold: stop after that many proposals in a row that did not improve on the best rating seen."""
+        if not (self._threshold and perf_rating):
+            return False
+        improved = perf_rating < self._best_perf_rating
+        self._best_perf_rating = min(self._best_perf_rating, perf_rating)
+        self._num_inferior_perf = 0 if improved else self._num_inferior_perf + 1
+        return self._num_inferior_perf > self._threshold
+
     def feedback(self, partitionable: bool, plan: Optional[List[ShardingOption]] = None, perf_rating: Optional[float] = None,
                  storage_constraint: Optional[Topology] = None) -> None:
-        if self._threshold and perf_rating:
-            if perf_rating < self._best_perf_rating:
-                self._best_perf_rating = perf_rating
-                self._num_inferior_perf = 0
-            else:
-                self._num_inferior_perf += 1
-                if self._num_inferior_perf > self._threshold:
-                    self._current_proposal = {}
-                    return
-        # move the largest table to its next option
-        largest_fqn = max(self._current_proposal, key=lambda x: self._sharding_options_by_fqn[x][self._current_proposal[x]].total_storage.hbm)
-        self._current_proposal[largest_fqn] += 1
-        if self._current_proposal[largest_fqn] >= len(self._sharding_options_by_fqn[largest_fqn]):
+        if self._patience_ran_out(perf_rating):
+            self._current_proposal = {}
+            return
+        # the table whose current option needs the most HBM moves on to its next cheapest option; when it has none left, the search ends
+        chosen = self._current_proposal
+
+        def hbm_of(fqn: str) -> int:
+            return self._sharding_options_by_fqn[fqn][chosen[fqn]].total_storage.hbm
+
+        heaviest = max(chosen, key=hbm_of)
+        if chosen[heaviest] + 1 < len(self._sharding_options_by_fqn[heaviest]):
+            chosen[heaviest] += 1
+        else:
             self._current_proposal = {}
 
 
@@ -280,17 +289,17 @@ class EmbeddingOffloadScaleupProposer(Proposer):
 
 def proposers_to_proposals_list(proposers_list: List[Proposer], search_space: List[ShardingOption]) -> List[List[ShardingOption]]:
     """All proposals of all proposers (feedback is always "not partitionable" so each one runs to exhaustion)."""
-    proposals_list: List[List[ShardingOption]] = []
-    seen: Set[Tuple[int, ...]] = set()
-    for proposer in proposers_list:
+    def drain(proposer: Proposer):
         proposer.load(search_space=search_space)
-    for proposer in proposers_list:
-        proposal = proposer.propose()
-        while proposal:
-            key = tuple(sorted(id(so) for so in proposal))
-            proposer.feedback(partitionable=True)
-            if key not in seen:
-                seen.add(key)
-                proposals_list.append(proposal)
+        while True:
             proposal = proposer.propose()
-    return proposals_list
+            if not proposal:
+                return
+            yield proposal
+            proposer.feedback(partitionable=True)
+
+    distinct: Dict[Tuple[int, ...], List[ShardingOption]] = {}  # keyed by the set of options, first occurrence kept, order of discovery
+    for proposer in proposers_list:
+        for proposal in drain(proposer):
+            distinct.setdefault(tuple(sorted(map(id, proposal))), proposal)
+    return list(distinct.values())
