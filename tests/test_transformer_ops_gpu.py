@@ -22,7 +22,7 @@ def test_residual_layer_norm_matches_torch_without_dropout(D, with_a):
     r32, a32 = r.detach().float().requires_grad_(True), (a.detach().float().requires_grad_(True) if with_a else None)
     w32, b32 = w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
     s32 = (r32 + a32) if with_a else r32
-    s_ref = s32.bfloat16().float() + (s32 - s32.detach())  # value rounded, gradient straight through
+    s_ref = s32.detach().bfloat16().float() + (s32 - s32.detach())  # value rounded, gradient straight through
     y_ref = torch.nn.functional.layer_norm(s_ref, (D,), w32, b32, 1e-5)
     torch.testing.assert_close(s.float(), s_ref.detach(), rtol=0, atol=0)
     torch.testing.assert_close(y.float(), y_ref.detach(), rtol=2e-2, atol=2e-2)
@@ -65,7 +65,8 @@ def test_dropout_mask_is_shared_by_forward_and_backward():
     h.float().sum().backward()
     zz = z.detach().float().requires_grad_(True)
     torch.nn.functional.gelu(zz).sum().backward()
-    torch.testing.assert_close(z.grad.float(), zz.grad * kept.float() / (1 - p), rtol=3e-2, atol=3e-2)
+    sure = ref.abs() > 1e-2  # where gelu(z) itself rounds to zero, h == 0 says nothing about the mask
+    torch.testing.assert_close(z.grad.float()[sure], (zz.grad * kept.float() / (1 - p))[sure], rtol=3e-2, atol=3e-2)
 
 
 def test_packed_encoder_matches_padded_encoder():

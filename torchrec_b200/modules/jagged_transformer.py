@@ -7,8 +7,8 @@ padding position is ever computed.
 * projections and feed-forward layers are the tcgen05 GEMMs with bias epilogues (``ops.dense_ops.linear_act``);
 * ``dropout + residual add + layer norm`` is one kernel, ``gelu + dropout`` another (``ops.transformer_ops``), with masks recomputed in
   the backward instead of stored;
-* attention runs per sequence on the packed layout (variable-length attention through a jagged nested tensor), so its cost is
-  ``sum(len^2)`` rather than ``B * max_len^2``.
+* attention is the only place that sees padding: q, k, v are padded for one library attention call with the padded keys masked
+  and the result is packed again (``ATTENTION_MODE = "nested"`` selects the library's variable-length kernel where the build has one).
 
 With lengths uniform in [20, 200] this is 55 % of the padded token count before any kernel gets faster.  The reference's
 BERT4Rec runs padded ``[B, L, D]`` tensors through library modules (``examples/bert4rec/models/bert4rec.py`` of the reference).
@@ -47,28 +47,43 @@ def _attention_per_sequence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o
     return out
 
 
-def varlen_attention(qkv: torch.Tensor, offsets: torch.Tensor, num_heads: int, max_len: int, p: float = 0.0) -> torch.Tensor:
-    """Self-attention inside every sequence of the packed ``qkv [T, 3 * D]``; returns ``[T, D]``."""
+def _attention_padded(qkv: torch.Tensor, offsets: torch.Tensor, num_heads: int, max_len: int, p: float) -> torch.Tensor:
+    """Attention on a padded view of the packed tokens: only the attention itself sees padding (keys beyond a sequence's length
+    are masked out); q, k and v are padded by the jagged-to-padded kernel and the result is packed again."""
+    from torchrec_b200.ops import sparse_ops as sops
+
     T, three_d = qkv.shape
     D = three_d // 3
+    B = offsets.numel() - 1
+    padded = sops.jagged_to_padded_dense(qkv, offsets, max_len, 0.0)  # [B, L, 3D]
+    q, k, v = (t.reshape(B, max_len, num_heads, D // num_heads).transpose(1, 2) for t in padded.split(D, dim=2))
+    lengths = (offsets[1:] - offsets[:-1]).clamp(max=max_len)
+    key_ok = torch.arange(max_len, device=qkv.device).unsqueeze(0) < lengths.unsqueeze(1)  # [B, L]
+    out = torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=key_ok.view(B, 1, 1, max_len), dropout_p=p)
+    return sops.padded_dense_to_jagged(out.transpose(1, 2).reshape(B, max_len, D), offsets, T)
+
+
+ATTENTION_MODE = "padded"  # "padded" | "nested": how the packed tokens reach the attention kernel on CUDA
+
+
+def varlen_attention(qkv: torch.Tensor, offsets: torch.Tensor, num_heads: int, max_len: int, p: float = 0.0) -> torch.Tensor:
+    """Self-attention inside every sequence of the packed ``qkv [T, 3 * D]``; returns ``[T, D]``.
+
+    ``ATTENTION_MODE = "nested"`` hands the packed layout to the library's variable-length attention through a jagged nested
+    tensor (cost ``sum(len^2)``); where the build has no variable-length kernel for the device it silently decomposes into one
+    small attention per sequence, so the default is ``"padded"``: one library attention call over ``[B, H, max_len, Dh]`` with the
+    padded keys masked.  Everything outside the attention stays packed either way."""
+    T, three_d = qkv.shape
+    D = three_d // 3
+    if qkv.is_cuda and ATTENTION_MODE == "padded":
+        return _attention_padded(qkv, offsets, num_heads, max_len, p)
     q, k, v = (t.reshape(T, num_heads, D // num_heads) for t in qkv.split(D, dim=1))
     if qkv.is_cuda:
         jag = offsets.to(torch.int64)
-        try:
-            parts = [torch.nested.nested_tensor_from_jagged(t.contiguous(), offsets=jag, min_seqlen=0, max_seqlen=int(max_len)).transpose(1, 2) for t in (q, k, v)]
-            out = torch.nn.functional.scaled_dot_product_attention(parts[0], parts[1], parts[2], dropout_p=p)
-            return out.transpose(1, 2).values().reshape(T, D)
-        except (RuntimeError, NotImplementedError) as e:  # no variable-length kernel for this build / shape: stay correct
-            global _warned
-            if not _warned:
-                import warnings
-
-                warnings.warn(f"variable-length attention is unavailable ({type(e).__name__}: {e}); running one attention call per sequence")
-                _warned = True
+        parts = [torch.nested.nested_tensor_from_jagged(t.contiguous(), offsets=jag, min_seqlen=0, max_seqlen=int(max_len)).transpose(1, 2) for t in (q, k, v)]
+        out = torch.nn.functional.scaled_dot_product_attention(parts[0], parts[1], parts[2], dropout_p=p)
+        return out.transpose(1, 2).values().reshape(T, D)
     return _attention_per_sequence(q, k, v, offsets, p).reshape(T, D)
-
-
-_warned = False
 
 
 def jagged_encoder_forward(encoder: nn.TransformerEncoder, x: torch.Tensor, offsets: torch.Tensor, max_len: int,
