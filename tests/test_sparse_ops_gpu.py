@@ -88,3 +88,40 @@ def test_jagged_padded_kernels_are_differentiable():
     mask = torch.arange(8, device="cuda").unsqueeze(0) < lengths.cuda().unsqueeze(1)
     (dr[mask] * wj).sum().backward()
     torch.testing.assert_close(d.grad, dr.grad)
+
+
+def test_offsets_range_and_segment_sum_match_composite():
+    from torchrec_b200.ops import sparse_ops as sops
+
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(0, 9, (500,), generator=g)
+    starts = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)[:-1]])
+    total = int(lens.sum())
+    for dt in (torch.int32, torch.int64):
+        got = sops.offsets_range(starts.to(dt).cuda(), total)
+        want = sops.offsets_range(starts.to(dt), total)
+        assert got.dtype == dt and torch.equal(got.cpu(), want)
+    csr = torch.cat([torch.zeros(1, dtype=torch.long), torch.randint(0, 5, (300,), generator=g).cumsum(0)])
+    batch = 7
+    n = int(csr[-1]) * batch
+    for values in (torch.randint(0, 100, (n,), generator=g), torch.rand(n, generator=g)):
+        got = sops.segment_sum_csr(batch, csr.int().cuda(), values.cuda())
+        want = sops.segment_sum_csr(batch, csr, values)
+        torch.testing.assert_close(got.cpu(), want, rtol=1e-5, atol=1e-5)
+
+
+def test_vbe_expand_matches_index_select_and_routes_gradients():
+    from torchrec_b200.ops import sparse_ops as sops
+
+    torch.manual_seed(1)
+    rows, dims, B = [5, 1, 9], [16, 8, 40], 33
+    flat = torch.randn(sum(r * d for r, d in zip(rows, dims)), device="cuda", requires_grad=True)
+    inverse = torch.stack([torch.randint(0, r, (B,)) for r in rows]).cuda()
+    got = sops.vbe_expand(flat, inverse, rows, dims)
+    ref_in = flat.detach().cpu().requires_grad_(True)
+    want = sops.vbe_expand(ref_in, inverse.cpu(), rows, dims)
+    torch.testing.assert_close(got.detach().cpu(), want.detach(), rtol=0, atol=0)
+    g = torch.randn(B, sum(dims))
+    got.backward(g.cuda())
+    want.backward(g)
+    torch.testing.assert_close(flat.grad.cpu(), ref_in.grad, rtol=1e-5, atol=1e-5)

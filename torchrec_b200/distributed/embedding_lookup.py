@@ -72,8 +72,22 @@ def _kernel_class(compute_kernel: EmbeddingComputeKernel, dense_cls: type, fused
     if compute_kernel == EmbeddingComputeKernel.DENSE:
         return dense_cls
     if compute_kernel in _FUSED_KERNELS:
+        if compute_kernel != EmbeddingComputeKernel.FUSED:
+            _warn_once(f"compute kernel {compute_kernel.value}: no host-memory tier is built; the table stays resident in HBM "
+                       "(plan memory accordingly: the planner's UVM storage figures do not apply)")
         return fused_cls
     raise ValueError(f"Compute kernel not supported {compute_kernel}")
+
+
+_warned: set = set()
+
+
+def _warn_once(message: str) -> None:
+    if message not in _warned:
+        _warned.add(message)
+        import warnings
+
+        warnings.warn(message, stacklevel=3)
 
 
 class CommOpGradientScaling(torch.autograd.Function):
@@ -129,8 +143,9 @@ class _GroupedLookupBase(BaseEmbeddingLookup[KeyedJaggedTensor, torch.Tensor]):
                 yield cfg.name, w
 
     def prefetch(self, sparse_features: KeyedJaggedTensor, forward_stream=None) -> None:
-        # every table is resident in HBM: nothing to stage
-        return None
+        """Every table is resident in HBM, so there are no rows to stage ahead of the lookup; a pipeline that schedules prefetches
+        keeps working, and is told once that they are free."""
+        _warn_once("embedding prefetch requested: tables are HBM-resident here, prefetch is a no-op")
 
     def flush(self) -> None:
         for m in self._emb_modules:

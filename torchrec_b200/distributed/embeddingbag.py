@@ -159,12 +159,7 @@ class VariableBatchEmbeddingBagCollectionAwaitable(LazyGetItemMixin[str, torch.T
         inv = self._inverse_indices[1]
         if self._inverse_indices_permute_indices is not None:
             inv = torch.index_select(inv, 0, self._inverse_indices_permute_indices)
-        outs, off = [], 0
-        for i, (b, d) in enumerate(zip(self._batch_size_per_feature_pre_a2a, self._uncombined_embedding_dims)):
-            block = flat[off: off + b * d].view(b, d)
-            outs.append(block.index_select(0, inv[i].to(torch.int64)))
-            off += b * d
-        values = torch.cat(outs, dim=1)
+        values = sops.vbe_expand(flat, inv, self._batch_size_per_feature_pre_a2a, self._uncombined_embedding_dims)
         if self._permute_op is not None:
             values = self._permute_op(values)
         return KeyedTensor(keys=self._embedding_names, length_per_key=self._embedding_dims, values=values, key_dim=1)

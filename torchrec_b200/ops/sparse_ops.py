@@ -80,6 +80,8 @@ def offsets_range(offsets: torch.Tensor, range_size: int) -> torch.Tensor:
     """
     if range_size == 0:
         return offsets.new_empty(0)
+    if offsets.dtype in (torch.int32, torch.int64) and offsets.numel() > 0 and _kern(offsets, "offsets_range"):
+        return torch.ops.trb200.offsets_range(offsets.contiguous(), int(range_size))
     starts = offsets.to(torch.int64)
     ends = torch.cat([starts[1:], starts.new_tensor([range_size])])
     lens = ends - starts
@@ -92,6 +94,8 @@ def segment_sum_csr(batch_size: int, csr_seg: torch.Tensor, values: torch.Tensor
     n = csr_seg.numel() - 1
     if n <= 0:
         return values.new_zeros(0)
+    if csr_seg.dtype in (torch.int32, torch.int64) and not values.requires_grad and _kern(values, "segment_sum_csr"):
+        return torch.ops.trb200.segment_sum_csr(int(batch_size), csr_seg.contiguous(), values.reshape(-1).contiguous())
     cs = asynchronous_complete_cumsum(values.reshape(-1))
     idx = csr_seg.to(torch.int64) * batch_size
     return (cs[idx[1:]] - cs[idx[:-1]]).to(values.dtype)
@@ -589,3 +593,43 @@ def itep_remap(values: torch.Tensor, feature_offsets: torch.Tensor, feature_buff
     op = torch.ops.trb200.itep_remap if _kern(v, "itep_remap") else _ext.cpu_ops().itep_remap
     return op(v, feature_offsets.to(device=v.device, dtype=torch.int64), feature_buffer.to(device=v.device, dtype=torch.int32), address_lookup, row_util,
               buffer_offsets.to(device=v.device, dtype=torch.int64), bool(update_util)).to(values.dtype)
+
+
+# --------------------------------------------------------------------------------------
+# variable batch per feature: expand deduplicated pooled rows to the full batch
+# --------------------------------------------------------------------------------------
+class _VbeExpand(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, flat, inverse, rows_per_feature, dims):
+        desc, base, col = [], 0, 0
+        for b, d in zip(rows_per_feature, dims):
+            desc.append([base, b, d, col])
+            base += b * d
+            col += d
+        err = torch.zeros(1, dtype=torch.int32, device=flat.device)
+        out = torch.ops.trb200.vbe_expand(flat.contiguous(), torch.tensor(desc, dtype=torch.int64).to(flat.device, non_blocking=True),
+                                          inverse.contiguous(), col, err)
+        ctx.save_for_backward(inverse)
+        ctx.layout = (desc, flat.numel())
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        (inverse,) = ctx.saved_tensors
+        desc, n = ctx.layout
+        g = grad.new_zeros(n)
+        for f, (base, b, d, col) in enumerate(desc):  # rows that several samples share collect all their gradients
+            g[base: base + b * d].view(b, d).index_add_(0, inverse[f].to(torch.int64), grad[:, col: col + d])
+        return g, None, None, None
+
+
+def vbe_expand(flat: torch.Tensor, inverse: torch.Tensor, rows_per_feature: List[int], dims: List[int]) -> torch.Tensor:
+    """``flat`` holds, feature after feature, the pooled rows ``[rows_f, dim_f]`` of the deduplicated batches; ``inverse [F, B]``
+    names for every sample of the full batch the row to use.  Returns ``[B, sum(dim_f)]``."""
+    if flat.is_cuda and inverse.dtype in (torch.int32, torch.int64) and _kern(flat, "vbe_expand"):
+        return _VbeExpand.apply(flat, inverse, list(rows_per_feature), list(dims))
+    outs, base = [], 0
+    for f, (b, d) in enumerate(zip(rows_per_feature, dims)):
+        outs.append(flat[base: base + b * d].view(b, d).index_select(0, inverse[f].to(torch.int64)))
+        base += b * d
+    return torch.cat(outs, dim=1)
