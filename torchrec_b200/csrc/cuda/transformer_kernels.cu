@@ -5,8 +5,9 @@
 //   ln_residual_bwd   from dy (and the gradient that reaches s from later blocks) -> ds, da, dgamma, dbeta
 //   gelu_dropout_fwd  h = dropout(gelu(z));   gelu_dropout_bwd   dz = dh * mask * gelu'(z)
 //
-// Dropout masks are never stored: element i of a call is kept iff hash(seed, i) falls below the keep threshold, and the
-// backward recomputes the same hash.  One warp owns one token row (D <= 1024, D % 256 == 0: every lane moves 16 bytes at a
+// Dropout masks are never stored: an element is kept iff its 16 bits of hash(seed, position) fall below the keep threshold
+// (the keep probability is rounded to a multiple of 2^-16 and the rescale factor matches the rounded value), and the backward
+// recomputes the same hash.  One warp owns one token row (D <= 1024, D % 256 == 0: every lane moves 16 bytes at a
 // time); statistics are fp32.  The reference model runs these as separate library kernels on padded [B, L, D] tensors
 // (examples/bert4rec/models/bert4rec.py of the reference: nn.LayerNorm, nn.Dropout, GELU between nn.Linear layers).
 #include <ATen/ATen.h>
@@ -19,22 +20,33 @@
 
 namespace trb {
 
-// splitmix64 finaliser over (seed, element index) -> uniform 32 bits
-__device__ __forceinline__ uint32_t drop_hash(uint64_t seed, uint64_t i) {
+// splitmix64 finaliser over (seed, index)
+// 64 hash bits -> four 16-bit lanes
+__device__ __forceinline__ uint64_t drop_hash64(uint64_t seed, uint64_t i) {
   uint64_t z = seed + (i + 1) * 0x9E3779B97F4A7C15ull;
   z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
   z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-  return uint32_t((z ^ (z >> 31)) >> 32);
+  return z ^ (z >> 31);
 }
 
 struct Drop {
   uint64_t seed;
-  uint32_t keep_below;  // keep iff hash < keep_below (p == 0: everything is kept, no hash computed)
-  float scale;          // 1 / (1 - p)
+  uint32_t keep_below;  // an element is kept iff its 16 random bits are below this (p == 0: everything is kept, nothing is hashed)
+  float scale;          // 1 / (realised keep probability): keep_below is a multiple of 2^-16, the scale matches it exactly
   int on;
-  __device__ __forceinline__ float factor(uint64_t i) const {
-    if (!on) return 1.f;
-    return drop_hash(seed, i) < keep_below ? scale : 0.f;
+  // the eight factors of elements [i8 * 8, i8 * 8 + 8): two hashes, sixteen bits per element
+  __device__ __forceinline__ void factors8(uint64_t i8, float (&f)[8]) const {
+    if (!on) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] = 1.f;
+      return;
+    }
+    const uint64_t h0 = drop_hash64(seed, i8 * 2), h1 = drop_hash64(seed, i8 * 2 + 1);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      f[k] = uint32_t((h0 >> (16 * k)) & 0xffff) < keep_below ? scale : 0.f;
+      f[4 + k] = uint32_t((h1 >> (16 * k)) & 0xffff) < keep_below ? scale : 0.f;
+    }
   }
 };
 
@@ -42,9 +54,9 @@ static Drop make_drop(double p, int64_t seed) {
   Drop d;
   d.on = p > 0.0 ? 1 : 0;
   d.seed = uint64_t(seed);
-  d.scale = d.on ? float(1.0 / (1.0 - p)) : 1.f;
-  const double keep = (1.0 - p) * 4294967296.0;
-  d.keep_below = keep >= 4294967295.0 ? 0xffffffffu : uint32_t(keep);
+  const double keep = std::min(65536.0, std::max(1.0, std::floor((1.0 - p) * 65536.0 + 0.5)));
+  d.keep_below = uint32_t(keep);
+  d.scale = d.on ? float(65536.0 / keep) : 1.f;
   return d;
 }
 
@@ -85,10 +97,11 @@ __global__ void __launch_bounds__(256) ln_residual_fwd_kernel(const __nv_bfloat1
     const int e = c * 256 + lane * 8;
     load8(r + row * D + e, s[c]);
     if (a != nullptr) {
-      float av[8];
+      float av[8], fk[8];
       load8(a + row * D + e, av);
+      drop.factors8((uint64_t(row) * D + e) >> 3, fk);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) s[c][k] += av[k] * drop.factor(uint64_t(row) * D + e + k);
+      for (int k = 0; k < 8; ++k) s[c][k] += av[k] * fk[k];
       // the residual stream is stored in bf16: normalise what the next block will read, not the unrounded sum
 #pragma unroll
       for (int k = 0; k < 8; ++k) s[c][k] = __bfloat162float(__float2bfloat16(s[c][k]));
@@ -182,9 +195,10 @@ __global__ void __launch_bounds__(256) ln_residual_bwd_kernel(const __nv_bfloat1
       }
       store8(ds_out + row * D + e, dsv);
       if (da_out != nullptr) {
-        float dav[8];
+        float dav[8], fk[8];
+        drop.factors8((uint64_t(row) * D + e) >> 3, fk);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) dav[k] = dsv[k] * drop.factor(uint64_t(row) * D + e + k);
+        for (int k = 0; k < 8; ++k) dav[k] = dsv[k] * fk[k];
         store8(da_out + row * D + e, dav);
       }
     }
@@ -221,16 +235,17 @@ __global__ void __launch_bounds__(256) gelu_dropout_kernel(const __nv_bfloat16* 
                                                            __nv_bfloat16* __restrict__ out, int64_t n8, Drop drop) {
   const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n8) return;
-  float zv[8], o[8];
+  float zv[8], o[8], fk[8];
   load8(z + i * 8, zv);
+  drop.factors8(uint64_t(i), fk);
   if (kBackward) {
     float g[8];
     load8(dh + i * 8, g);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) o[k] = g[k] * drop.factor(uint64_t(i) * 8 + k) * gelu_grad_f(zv[k]);
+    for (int k = 0; k < 8; ++k) o[k] = fk[k] != 0.f ? g[k] * fk[k] * gelu_grad_f(zv[k]) : 0.f;
   } else {
 #pragma unroll
-    for (int k = 0; k < 8; ++k) o[k] = gelu_f(zv[k]) * drop.factor(uint64_t(i) * 8 + k);
+    for (int k = 0; k < 8; ++k) o[k] = fk[k] != 0.f ? gelu_f(zv[k]) * fk[k] : 0.f;
   }
   store8(out + i * 8, o);
 }

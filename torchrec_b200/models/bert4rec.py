@@ -22,6 +22,7 @@ from torchrec_b200.modules import jagged_transformer
 from torchrec_b200.modules.embedding_configs import DataType, EmbeddingConfig
 from torchrec_b200.modules.embedding_modules import EmbeddingCollection
 from torchrec_b200.ops.transformer_ops import residual_layer_norm
+from torchrec_b200.ops import dense_ops
 from torchrec_b200.ops import sparse_ops as sops
 from torchrec_b200.sparse.jagged_tensor import JaggedTensor, KeyedJaggedTensor
 
@@ -67,6 +68,8 @@ class HistoryArch(nn.Module):
         T = rows.shape[0]
         first = torch.repeat_interleave(offsets[:-1].to(torch.int64), lengths.to(torch.int64), output_size=T)
         position = (torch.arange(T, device=rows.device) - first).clamp_(max=self.history_len - 1)
+        if dense_ops.fused_dense_enabled(rows):  # the packed encoder keeps its activations in bf16 from here on
+            rows = rows.to(torch.bfloat16)
         x = rows + self.positional.to(rows.dtype).index_select(0, position)
         _, y = residual_layer_norm(None, x.contiguous(), self.layernorm.weight, self.layernorm.bias, 0.0, self.training, self.layernorm.eps)
         return self.dropout(y), offsets, jt_dict
