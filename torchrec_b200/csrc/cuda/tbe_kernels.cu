@@ -854,6 +854,34 @@ __global__ void __launch_bounds__(256) tbe_linearize_kernel(
   }
 }
 
+// Unpooled variant: one thread per id, whatever the bag sizes (a single bag may hold most of the ids, e.g. a candidate list), the
+// feature of a position found by a search over the F + 1 feature boundaries.
+template <typename idx_t>
+__global__ void __launch_bounds__(256) tbe_linearize_seq_kernel(const idx_t* __restrict__ indices, const idx_t* __restrict__ offsets,
+                                                                const int64_t* __restrict__ meta, int F, int B, int64_t* __restrict__ keys,
+                                                                int32_t* __restrict__ src, int32_t* __restrict__ src_feature, int* err) {
+  const int64_t first = int64_t(offsets[0]), last = int64_t(offsets[int64_t(F) * B]);
+  const int64_t i = first + int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= last) return;
+  int lo = 0, hi = F;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (int64_t(offsets[int64_t(mid) * B]) <= i) lo = mid; else hi = mid;
+  }
+  // features without ids share a boundary: take the last feature that starts at or before i and still has ids there
+  int f = lo;
+  while (f + 1 < F && int64_t(offsets[int64_t(f + 1) * B]) <= i) ++f;
+  int64_t r = int64_t(indices[i]);
+  const bool bad = r < 0 || r >= meta[M_ROWS * F + f];
+  if (bad) {
+    atomicExch(err, 1);
+    r = 0;
+  }
+  keys[i] = meta[M_HASHOFF * F + f] + r;
+  src[i] = bad ? -int32_t(i) - 1 : int32_t(i);
+  src_feature[i] = f;
+}
+
 __global__ void tbe_bump_counter_kernel(int64_t* counter) { counter[0] += 1; }
 
 template <typename idx_t>
@@ -1031,7 +1059,12 @@ std::vector<at::Tensor> tbe_build_plan(const at::Tensor& meta, const at::Tensor&
       bag_of_pos = at::empty({N}, opts_i32);
       src_ptr = bag_of_pos.data_ptr<int32_t>();
     }
-    if (i64) {
+    if (!pooled && !weighted) {
+      // positions [offsets[0], offsets[F*B]) hold this module's ids; the grid covers the whole buffer and idle threads return
+      const int64_t seq_blocks = (N + threads - 1) / threads;
+      if (i64) tbe_linearize_seq_kernel<int64_t><<<seq_blocks, threads, 0, stream>>>(indices.data_ptr<int64_t>(), offsets.data_ptr<int64_t>(), meta.data_ptr<int64_t>(), F, int(B), keys.data_ptr<int64_t>(), src_ptr, src_feature.data_ptr<int32_t>(), err.data_ptr<int>());
+      else tbe_linearize_seq_kernel<int32_t><<<seq_blocks, threads, 0, stream>>>(indices.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), meta.data_ptr<int64_t>(), F, int(B), keys.data_ptr<int64_t>(), src_ptr, src_feature.data_ptr<int32_t>(), err.data_ptr<int>());
+    } else if (i64) {
       tbe_linearize_kernel<int64_t><<<blocks, threads, 0, stream>>>(
           indices.data_ptr<int64_t>(), offsets.data_ptr<int64_t>(), meta.data_ptr<int64_t>(), F, int(B), pooled ? 1 : 0,
           keys.data_ptr<int64_t>(), src_ptr, pooled ? nullptr : src_feature.data_ptr<int32_t>(),
