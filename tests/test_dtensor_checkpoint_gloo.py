@@ -72,6 +72,14 @@ def _run(rank, world_size, dtensor, tmp):
             assert type(sd_a["ebc.embedding_bags.t0.weight"]).__name__ == "DTensor"
         else:
             assert hasattr(v, "local_shards") and len(v.local_shards()) == 2
+        # the in-backward optimizer's states leave in the same form as the tables
+        opt_state = a.fused_optimizer.state_dict()["state"]
+        sharded_states = [v for per_param in opt_state.values() for v in per_param.values() if not isinstance(v, (int, float)) and type(v).__name__ in ("DTensor", "ShardedTensor")]
+        assert sharded_states, "the row-wise Adagrad state of sharded tables is missing"
+        assert all(type(v).__name__ == ("DTensor" if dtensor else "ShardedTensor") for v in sharded_states), [type(v).__name__ for v in sharded_states]
+        if dtensor:
+            rowwise = [v for v in sharded_states if len(v.shape) == 1]
+            assert rowwise and all(sum(int(s.shape[0]) for s in v.to_local().local_shards()) > 0 for v in rowwise)
         want = {f"ebc.embedding_bags.t{i}.weight": _full_table(a, f"ebc.embedding_bags.t{i}.weight", r, d) for i, (r, d, _) in enumerate(TABLES)}
         dcp.save(sd_a, checkpoint_id=tmp)
         b = _build(ctx, ["cw2" if False else "tw", "rw"], dtensor)  # another layout: table-wise and row-wise

@@ -264,7 +264,47 @@ class ShardedTableStateMixin:
                     opt = kernel.fused_optimizer
                     opt.params = {prefix + key: weight for key, weight in opt.params.items()}
                     found.append(("", opt))
+        if getattr(self, "_output_dtensor", False):
+            for _, opt in found:
+                self._optimizer_states_as_dtensor(opt)
         return CombinedOptimizer(found)
+
+    def _optimizer_states_as_dtensor(self, opt) -> None:
+        """With ``env.output_dtensor`` the in-backward optimizer states leave as ``DTensor`` s like the tables do: every sharded state
+        is re-wrapped around the SAME local shard tensors (views of the kernel's state memory), with their offsets, over the
+        sharding group's mesh; row-wise states (one value per row) and row-split tables shard dim 0, column-split 2-D states dim 1."""
+        try:
+            from torch.distributed.device_mesh import DeviceMesh
+            from torch.distributed.tensor import DTensor, Replicate, Shard
+
+            from torchrec_b200.distributed.shards_wrapper import LocalShardsWrapper
+        except Exception:
+            return
+        pg = self._env.sharding_pg if isinstance(self._env, ShardingEnv2D) else self._env.process_group
+        if pg is None:
+            return
+        mesh = getattr(self._env, "device_mesh", None)
+        if mesh is None or mesh.ndim != 1:
+            mesh = DeviceMesh.from_group(pg, self._device.type if self._device is not None else "cpu")
+        row_kinds = (ShardingType.ROW_WISE.value, ShardingType.TABLE_ROW_WISE.value, ShardingType.GRID_SHARD.value)
+        col_kinds = (ShardingType.COLUMN_WISE.value, ShardingType.TABLE_COLUMN_WISE.value)
+        for per_param in opt.state.values():
+            for key, value in list(per_param.items()):
+                if not isinstance(value, ShardedTensor):
+                    continue
+                table = key.rsplit(".", 1)[0].split(".")[-1]
+                kind = self.module_sharding_plan[table].sharding_type if table in self.module_sharding_plan else None
+                shards = value.local_shards()
+                size = value.size()
+                if len(size) == 1 or kind in row_kinds:
+                    placements = (Shard(0),)
+                elif kind in col_kinds:
+                    placements = (Shard(1),)
+                else:
+                    placements = (Replicate(),)
+                wrapper = LocalShardsWrapper([s.tensor for s in shards], [tuple(int(x) for x in s.metadata.shard_offsets) for s in shards])
+                stride = (int(size[1]), 1) if len(size) == 2 else (1,)
+                per_param[key] = DTensor.from_local(wrapper, mesh, placements, run_check=False, shape=torch.Size(size), stride=stride)
 
     # ---- torch state: parameters and state dict -----------------------------------------------------
     def _unwrapped_lookups(self):
