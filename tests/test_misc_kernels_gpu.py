@@ -132,3 +132,32 @@ def test_kt_regroup_forward_backward(dtype):
     (o2,) = sops.permute_multi_embedding(vals2, in_lengths, in_keys, [["b"]])
     o2.sum().backward()
     assert vals2[1].grad.abs().sum() == 0 and vals2[0].grad[:, 16:24].eq(1).all() and vals2[0].grad[:, :16].eq(0).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,F,D", [(torch.bfloat16, 26, 128), (torch.bfloat16, 31, 64), (torch.bfloat16, 3, 16), (torch.bfloat16, 40, 32), (torch.float32, 26, 128)])
+def test_dot_interaction_matches_torch(dtype, F, D):
+    """bf16 with at most 32 vectors per sample runs on the tensor cores, everything else on the scalar kernel; both against the
+    triu(X X^T) definition in fp32 on the same inputs, forward and backward."""
+    import os
+
+    from torchrec_b200.ops.dense_ops import dot_interaction
+
+    torch.manual_seed(F * D)
+    B = 77  # not a multiple of the samples a block handles
+    dense = (torch.randn(B, D, device="cuda") * 0.5).to(dtype).requires_grad_(True)
+    sparse = (torch.randn(B, F, D, device="cuda") * 0.5).to(dtype).requires_grad_(True)
+    out = dot_interaction(dense, sparse)
+    d32, s32 = dense.detach().float().requires_grad_(True), sparse.detach().float().requires_grad_(True)
+    x = torch.cat((d32.unsqueeze(1), s32), dim=1)
+    z = torch.bmm(x, x.transpose(1, 2))
+    iu = torch.triu_indices(F + 1, F + 1, offset=1, device="cuda")
+    want = torch.cat((d32, z[:, iu[0], iu[1]]), dim=1)
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    assert out.shape == want.shape
+    torch.testing.assert_close(out.float(), want.detach(), rtol=tol, atol=tol * float(want.abs().max()))
+    g = torch.randn_like(want).to(dtype)
+    out.backward(g)
+    want.backward(g.float())
+    torch.testing.assert_close(dense.grad.float(), d32.grad, rtol=tol, atol=tol * float(d32.grad.abs().max()))
+    torch.testing.assert_close(sparse.grad.float(), s32.grad, rtol=tol, atol=tol * float(s32.grad.abs().max()))

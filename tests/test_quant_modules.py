@@ -191,3 +191,36 @@ def test_qtbe_forward_into_cpu():
 @pytest.mark.gpu
 def test_qtbe_forward_into_gpu():
     _forward_into_case("cuda")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits,D", [(8, 128), (8, 32), (8, 256), (4, 128), (4, 32), (4, 256)])
+@pytest.mark.parametrize("pooling", [0, 1, 2])
+def test_qtbe_shared_lane_kernel_matches_cpu(bits, D, pooling):
+    """Tables that all share one low-bit row format take the kernel that spreads a warp's lanes over several rows per load:
+    bags longer than one round of ids, weighted, mean and unpooled forms against the host implementation."""
+    from torchrec_b200.modules.embedding_configs import PoolingMode
+    from torchrec_b200.ops.qtbe import QuantTableBatchedEmbeddingBags
+    from torchrec_b200.ops.quant_ops import quantize_rowwise_nbit
+
+    torch.manual_seed(bits * D + pooling)
+    specs = [(300, D, bits), (50, D, bits)]
+    ftm = [0, 1, 1]
+    cpu = QuantTableBatchedEmbeddingBags(specs, ftm, PoolingMode(pooling), torch.float32)
+    assert cpu._uniform_bits == bits
+    for t, (r, d, b) in enumerate(specs):
+        cpu.table_view(t).copy_(quantize_rowwise_nbit(torch.randn(r, d), b))
+    gpu = QuantTableBatchedEmbeddingBags(specs, ftm, PoolingMode(pooling), torch.float32, device="cuda")
+    gpu.weights.copy_(cpu.weights)
+    g = torch.Generator().manual_seed(1)
+    B = 19
+    lens = torch.randint(0, 90, (3 * B,), generator=g)
+    lens[5] = 0
+    rows = [300, 50, 50]
+    vals = torch.cat([torch.randint(0, rows[k], (int(lens[k * B:(k + 1) * B].sum()),), generator=g) for k in range(3)])
+    off = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)])
+    psw = torch.rand(vals.numel(), generator=g) if pooling == 0 else None
+    ref = cpu(vals, off, psw)
+    out = gpu(vals.cuda(), off.cuda(), None if psw is None else psw.cuda())
+    gpu.check_error()
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-3)

@@ -9,6 +9,7 @@
 #include <torch/library.h>
 
 #include "common.cuh"
+#include "dot_mma.cuh"
 
 namespace trb {
 
@@ -331,6 +332,13 @@ at::Tensor dot_interaction_fwd(const at::Tensor& dense, const at::Tensor& sparse
     cudaFuncSetAttribute(dot_fwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     dot_fwd_kernel<float><<<B, 128, smem, stream>>>(dense.data_ptr<float>(), sparse.data_ptr<float>(),
                                                     out.data_ptr<float>(), F, D, out_dim);
+  } else if (dot_mma_ok(F, D)) {
+    TORCH_CHECK(dense.scalar_type() == at::kBFloat16);
+    const size_t msmem = dot_fwd_mma_smem(D);
+    if (msmem > 48 * 1024) cudaFuncSetAttribute(dot_fwd_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(msmem));
+    dot_fwd_mma_kernel<<<(B + kDotWarps - 1) / kDotWarps, 32 * kDotWarps, msmem, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(dense.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(sparse.data_ptr()),
+        reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), B, F, D, out_dim);
   } else {
     TORCH_CHECK(dense.scalar_type() == at::kBFloat16);
     cudaFuncSetAttribute(dot_fwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -359,6 +367,13 @@ std::tuple<at::Tensor, at::Tensor> dot_interaction_bwd(const at::Tensor& dout, c
     dot_bwd_kernel<float><<<B, 128, smem, stream>>>(dout.data_ptr<float>(), dense.data_ptr<float>(),
                                                     sparse.data_ptr<float>(), dd.data_ptr<float>(),
                                                     ds.data_ptr<float>(), F, D, out_dim);
+  } else if (dot_mma_ok(F, D)) {
+    const size_t msmem = dot_bwd_mma_smem(D);
+    if (msmem > 48 * 1024) cudaFuncSetAttribute(dot_bwd_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(msmem));
+    dot_bwd_mma_kernel<<<(B + kDotWarps - 1) / kDotWarps, 32 * kDotWarps, msmem, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(dout.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(dense.data_ptr()),
+        reinterpret_cast<const __nv_bfloat16*>(sparse.data_ptr()), reinterpret_cast<__nv_bfloat16*>(dd.data_ptr()),
+        reinterpret_cast<__nv_bfloat16*>(ds.data_ptr()), B, F, D, out_dim);
   } else {
     cudaFuncSetAttribute(dot_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     dot_bwd_kernel<__nv_bfloat16><<<B, 128, smem, stream>>>(

@@ -123,6 +123,111 @@ __device__ __forceinline__ void qbag(const QFwdParams& p, const uint8_t* table, 
   }
 }
 
+// ---- low-bit rows, several rows per load instruction -------------------------------------------------------------------
+// A row of D int8 / int4 values is only D or D / 2 payload bytes: with one row per warp a load instruction moves 128 bytes or
+// less and a warp has a handful of requests in flight.  Here kLanes = payload / 16 lanes cover one row with a 16-byte load each
+// and the 32 / kLanes groups of a warp work on DIFFERENT ids of the bag at the same time (two rounds unrolled), so one load
+// instruction fetches up to eight rows.  Partial sums of the groups are combined by shuffles at the end of the bag.
+template <int BITS>
+__device__ __forceinline__ void qdequant16(const uint4& raw, float scale, float bias, float w, float* acc) {
+  const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+  constexpr int kPerByte = 8 / BITS;
+  constexpr uint32_t kMask = (1u << BITS) - 1u;
+  const float ws = w * scale, wb = w * bias;
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const uint32_t byte = (words[k >> 2] >> (8 * (k & 3))) & 0xffu;
+#pragma unroll
+    for (int q = 0; q < kPerByte; ++q) acc[k * kPerByte + q] += fmaf(ws, float((byte >> (BITS * q)) & kMask), wb);
+  }
+}
+
+template <int BITS, int kLanes, typename idx_t>
+__global__ void __launch_bounds__(256) qtbe_fwd_sub_kernel(QFwdParams p) {
+  constexpr int kGroups = 32 / kLanes;
+  constexpr int kElems = 16 * 8 / BITS;  // elements per lane
+  const int lane = threadIdx.x & 31;
+  const int64_t bag = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (bag >= int64_t(p.F) * p.B) return;
+  const int f = int(bag / p.B), b = int(bag - int64_t(f) * p.B);
+  const int F = p.F;
+  const idx_t* offsets = reinterpret_cast<const idx_t*>(p.offsets);
+  const idx_t* indices = reinterpret_cast<const idx_t*>(p.indices);
+  const int64_t start = offsets[bag], end = offsets[bag + 1];
+  const int D = int(p.meta[QM_DIM * F + f]);
+  const int64_t rows = p.meta[QM_ROWS * F + f];
+  const uint8_t* table = p.weights + p.meta[QM_WOFF * F + f];
+  const int payload = D * BITS / 8;
+  const int64_t rb = payload + 4;
+  const int out_off = int(p.meta[QM_OUTOFF * F + f]);
+  const int grp = lane / kLanes, lig = lane - grp * kLanes;
+  const bool unpooled = p.pooling == 2;
+  float acc[kElems];
+#pragma unroll
+  for (int e = 0; e < kElems; ++e) acc[e] = 0.f;
+  for (int64_t c = start; c < end; c += 32) {
+    const int n = int(min(int64_t(32), end - c));
+    int64_t my_r = 0;
+    float my_w = 0.f;
+    if (lane < n) {
+      my_r = int64_t(indices[c + lane]);
+      my_w = p.psw ? p.psw[c + lane] : 1.f;
+      if (my_r < 0 || my_r >= rows) {
+        atomicExch(p.err, 1);
+        my_r = 0;
+        my_w = 0.f;
+      }
+    }
+    for (int j0 = 0; j0 < n; j0 += 2 * kGroups) {
+      uint4 raw[2];
+      __half2 sb[2];
+      float w[2];
+      int jj[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        jj[u] = j0 + u * kGroups + grp;
+        const int src = min(jj[u], n - 1);  // groups past the end re-read the last row with weight 0
+        const int64_t r = __shfl_sync(0xffffffffu, my_r, src);
+        const float ww = __shfl_sync(0xffffffffu, my_w, src);
+        w[u] = jj[u] < n ? ww : 0.f;
+        const uint8_t* row = table + r * rb;
+        // rows start at multiples of (payload + 4) bytes: 4-byte aligned only, so the 16 bytes arrive as four words
+        const uint32_t* q = reinterpret_cast<const uint32_t*>(row + lig * 16);
+        raw[u] = make_uint4(__ldg(q), __ldg(q + 1), __ldg(q + 2), __ldg(q + 3));
+        sb[u] = *reinterpret_cast<const __half2*>(row + payload);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const float scale = __low2float(sb[u]), bias = __high2float(sb[u]);
+        if (unpooled) {
+          if (jj[u] < n) {
+            float rowv[kElems];
+#pragma unroll
+            for (int e = 0; e < kElems; ++e) rowv[e] = 0.f;
+            qdequant16<BITS>(raw[u], scale, bias, w[u] == 0.f ? 0.f : 1.f, rowv);
+#pragma unroll
+            for (int e = 0; e < kElems; e += 4)
+              store4_dyn(p.out, (c + jj[u]) * p.out_stride + lig * kElems + e, make_float4(rowv[e], rowv[e + 1], rowv[e + 2], rowv[e + 3]), p.out_dtype);
+          }
+        } else {
+          qdequant16<BITS>(raw[u], scale, bias, w[u], acc);
+        }
+      }
+    }
+  }
+  if (unpooled) return;
+#pragma unroll
+  for (int o = kLanes; o < 32; o <<= 1)
+#pragma unroll
+    for (int e = 0; e < kElems; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+  if (grp != 0) return;
+  const float s = (p.pooling == 1 && end > start) ? 1.f / float(end - start) : 1.f;
+#pragma unroll
+  for (int e = 0; e < kElems; e += 4)
+    store4_dyn(p.out, int64_t(b) * p.out_stride + out_off + lig * kElems + e,
+               make_float4(acc[e] * s, acc[e + 1] * s, acc[e + 2] * s, acc[e + 3] * s), p.out_dtype);
+}
+
 template <typename idx_t, int kVecs>
 __global__ void __launch_bounds__(256) qtbe_fwd_kernel(QFwdParams p) {
   const int lane = threadIdx.x & 31;
@@ -162,7 +267,7 @@ __global__ void __launch_bounds__(256) qtbe_fwd_kernel(QFwdParams p) {
 
 static void qtbe_launch(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets,
                         const c10::optional<at::Tensor>& psw, void* out, int64_t out_dtype, int64_t stride, int64_t B, int64_t max_D,
-                        int64_t pooling, at::Tensor& err) {
+                        int64_t pooling, at::Tensor& err, int64_t sub_bits) {
   const int F = int(meta.size(1));
   QFwdParams p;
   p.weights = weights.data_ptr<uint8_t>();
@@ -181,6 +286,20 @@ static void qtbe_launch(const at::Tensor& weights, const at::Tensor& meta, const
   const int64_t blocks = (nbags * 32 + 255) / 256;
   auto stream = at::cuda::getCurrentCUDAStream();
   const bool i64 = indices.scalar_type() == at::kLong;
+  if (sub_bits > 0) {
+    // every feature of the module has the same low-bit row format: rows shared out over lane groups
+    const int lanes = int(max_D) * int(sub_bits) / 8 / 16;
+#define TRB_QSUB(BITS_, LANES_)                                                                                   \
+  if (sub_bits == BITS_ && lanes == LANES_) {                                                                     \
+    if (i64) qtbe_fwd_sub_kernel<BITS_, LANES_, int64_t><<<blocks, 256, 0, stream>>>(p);                          \
+    else qtbe_fwd_sub_kernel<BITS_, LANES_, int32_t><<<blocks, 256, 0, stream>>>(p);                              \
+    TRB_CUDA_CHECK(cudaGetLastError());                                                                           \
+    return;                                                                                                       \
+  }
+    TRB_QSUB(8, 2) TRB_QSUB(8, 4) TRB_QSUB(8, 8) TRB_QSUB(8, 16)
+    TRB_QSUB(4, 1) TRB_QSUB(4, 2) TRB_QSUB(4, 4) TRB_QSUB(4, 8)
+#undef TRB_QSUB
+  }
   const int nv = max_D <= 128 ? 1 : (max_D <= 256 ? 2 : (max_D <= 512 ? 4 : 8));
 #define TRB_Q_LAUNCH(NV)                                                                          \
   if (i64) qtbe_fwd_kernel<int64_t, NV><<<blocks, 256, 0, stream>>>(p);                             \
@@ -199,7 +318,7 @@ static void qtbe_check(const at::Tensor& weights, const at::Tensor& meta, const 
 
 at::Tensor qtbe_forward(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets,
                         const c10::optional<at::Tensor>& psw, int64_t B, int64_t total_D, int64_t max_D, int64_t pooling,
-                        int64_t out_dtype, at::Tensor err) {
+                        int64_t out_dtype, at::Tensor err, int64_t uniform_bits) {
   qtbe_check(weights, meta, indices, offsets, max_D);
   const int F = int(meta.size(1));
   c10::cuda::CUDAGuard guard(weights.device());
@@ -214,7 +333,7 @@ at::Tensor qtbe_forward(const at::Tensor& weights, const at::Tensor& meta, const
     stride = total_D;
   }
   if (F == 0 || B == 0) return out;
-  qtbe_launch(weights, meta, indices, offsets, psw, out.data_ptr(), out_dtype, stride, B, max_D, pooling, err);
+  qtbe_launch(weights, meta, indices, offsets, psw, out.data_ptr(), out_dtype, stride, B, max_D, pooling, err, uniform_bits);
   return out;
 }
 
@@ -222,7 +341,8 @@ at::Tensor qtbe_forward(const at::Tensor& weights, const at::Tensor& meta, const
 // may live on ANOTHER device of this process (the serving GPU that assembles the request's result): peer access is switched
 // on for the pair and the rows travel over NVLink as plain stores from this kernel; no copy kernel, no concatenation.
 void qtbe_forward_into(const at::Tensor& weights, const at::Tensor& meta, const at::Tensor& indices, const at::Tensor& offsets,
-                       const c10::optional<at::Tensor>& psw, at::Tensor out, int64_t B, int64_t max_D, int64_t pooling, at::Tensor err) {
+                       const c10::optional<at::Tensor>& psw, at::Tensor out, int64_t B, int64_t max_D, int64_t pooling, at::Tensor err,
+                       int64_t uniform_bits) {
   qtbe_check(weights, meta, indices, offsets, max_D);
   TORCH_CHECK(pooling != 2, "pooled lookups only");
   TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.size(0) >= B);
@@ -237,7 +357,7 @@ void qtbe_forward_into(const at::Tensor& weights, const at::Tensor& meta, const 
   c10::cuda::CUDAGuard guard(weights.device());
   const int64_t code = out.scalar_type() == at::kFloat ? OUT_F32 : (out.scalar_type() == at::kHalf ? OUT_F16 : OUT_BF16);
   TORCH_CHECK(code != OUT_BF16 || out.scalar_type() == at::kBFloat16, "output must be fp32, fp16 or bf16");
-  qtbe_launch(weights, meta, indices, offsets, psw, out.data_ptr(), code, out.stride(0), B, max_D, pooling, err);
+  qtbe_launch(weights, meta, indices, offsets, psw, out.data_ptr(), code, out.stride(0), B, max_D, pooling, err, uniform_bits);
 }
 
 }  // namespace trb
@@ -245,10 +365,10 @@ void qtbe_forward_into(const at::Tensor& weights, const at::Tensor& meta, const 
 TORCH_LIBRARY_FRAGMENT(trb200, m) {
   m.def(
       "qtbe_forward(Tensor weights, Tensor meta, Tensor indices, Tensor offsets, Tensor? psw, int B, int total_D, int max_D, "
-      "int pooling, int out_dtype, Tensor(a!) err) -> Tensor");
+      "int pooling, int out_dtype, Tensor(a!) err, int uniform_bits=0) -> Tensor");
   m.def(
       "qtbe_forward_into(Tensor weights, Tensor meta, Tensor indices, Tensor offsets, Tensor? psw, Tensor(a!) out, int B, int max_D, "
-      "int pooling, Tensor(b!) err) -> ()");
+      "int pooling, Tensor(b!) err, int uniform_bits=0) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(trb200, CUDA, m) { m.impl("qtbe_forward", &trb::qtbe_forward); }

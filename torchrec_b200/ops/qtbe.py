@@ -45,6 +45,15 @@ class QuantTableBatchedEmbeddingBags(nn.Module):
         self.register_buffer("weights", torch.zeros(max(self.total_bytes, 16), dtype=torch.uint8, device=device), persistent=persistent_weights)
         self._meta: Optional[torch.Tensor] = None
         self._err: Optional[torch.Tensor] = None
+        # all tables int8 or all int4 with one dim whose payload is 16 bytes x a power of two: the kernel shares a warp's lanes
+        # out over several rows per load instruction
+        self._uniform_bits = 0
+        formats = {(d, b) for _, d, b in self.embedding_specs}
+        if len(formats) == 1:
+            d, b = next(iter(formats))
+            lanes = d * b // 8 // 16
+            if b in (8, 4) and (d * b // 8) % 16 == 0 and lanes in ((2, 4, 8, 16) if b == 8 else (1, 2, 4, 8)):
+                self._uniform_bits = b
 
     def table_view(self, t: int) -> torch.Tensor:
         """uint8 ``[rows, row_bytes]`` view of table ``t`` inside the flat buffer."""
@@ -74,7 +83,7 @@ class QuantTableBatchedEmbeddingBags(nn.Module):
                 offsets = offsets.to(indices.dtype)
             psw = per_sample_weights.float() if per_sample_weights is not None else None
             return torch.ops.trb200.qtbe_forward(self.weights, meta, indices.contiguous(), offsets.contiguous(), psw, B, self.total_D, self.max_D,
-                                                 int(self.pooling_mode), _OUT_CODE[self.output_dtype], self._err)
+                                                 int(self.pooling_mode), _OUT_CODE[self.output_dtype], self._err, self._uniform_bits)
         return self._forward_cpu(indices, offsets, per_sample_weights, B)
 
     def forward_into(self, indices: torch.Tensor, offsets: torch.Tensor, per_sample_weights: Optional[torch.Tensor], out: torch.Tensor,
@@ -103,7 +112,7 @@ class QuantTableBatchedEmbeddingBags(nn.Module):
             offsets = offsets.to(indices.dtype)
         psw = per_sample_weights.float() if per_sample_weights is not None else None
         torch.ops.trb200.qtbe_forward_into(self.weights, cache[key], indices.contiguous(), offsets.contiguous(), psw, out, B, self.max_D,
-                                           int(self.pooling_mode), self._err)
+                                           int(self.pooling_mode), self._err, self._uniform_bits)
 
     def _forward_cpu(self, indices, offsets, psw, B) -> torch.Tensor:
         off = offsets.to(torch.int64)
