@@ -106,8 +106,11 @@ def test_offsets_range_and_segment_sum_match_composite():
     n = int(csr[-1]) * batch
     for values in (torch.randint(0, 100, (n,), generator=g), torch.rand(n, generator=g)):
         got = sops.segment_sum_csr(batch, csr.int().cuda(), values.cuda())
-        want = sops.segment_sum_csr(batch, csr, values)
-        torch.testing.assert_close(got.cpu(), want, rtol=1e-5, atol=1e-5)
+        # oracle: every segment summed on its own in float64 (a prefix-sum difference in fp32 loses digits on long inputs)
+        bounds = (csr * batch).tolist()
+        want = torch.stack([values[lo:hi].double().sum() for lo, hi in zip(bounds[:-1], bounds[1:])]).to(values.dtype)
+        torch.testing.assert_close(got.cpu(), want, rtol=1e-6, atol=1e-6)
+        torch.testing.assert_close(sops.segment_sum_csr(batch, csr, values), want, rtol=1e-4, atol=2e-4)
 
 
 def test_vbe_expand_matches_index_select_and_routes_gradients():
