@@ -210,3 +210,22 @@ def test_perf_estimator_tracks_the_measured_lookup():
         num_poolings=[1.0], hbm_mem_bw=HBM_MEM_BW, ddr_mem_bw=1.0, hbm_to_ddr_mem_bw=1.0, comms_bandwidths=BasicCommsBandwidths(),
         bwd_compute_multiplier=2.0, weighted_feature_bwd_compute_multiplier=1.0, is_pooled=True)
     assert 1.31 / 1.5 < p.fwd_compute < 1.31 * 1.5, p.fwd_compute
+
+
+def test_local_refinement_never_rates_worse_and_balances_a_skewed_model():
+    """One table with a far larger pooling factor than the rest: the proposers alone keep it table-wise on one rank in the best
+    plan they suggest; the refinement step may only improve the rating, and it is off when the caller chooses the proposers."""
+    tables = [EmbeddingBagConfig(name=f"t{i}", embedding_dim=128, num_embeddings=4_000_000, feature_names=[f"f{i}"]) for i in range(10)]
+    pooling = [1, 1, 1, 2, 3, 4, 6, 9, 27, 100]
+    constraints = {f"t{i}": ParameterConstraints(pooling_factors=[float(p)]) for i, p in enumerate(pooling)}
+    ratings = {}
+    for steps in (0, 16):
+        planner = EmbeddingShardingPlanner(topology=Topology(world_size=8, local_world_size=8, compute_device="cuda"), batch_size=8192,
+                                           constraints=constraints, debug=False, refine_steps=steps)
+        plan = planner.plan(_Model(tables), [EmbeddingBagCollectionSharder()])
+        assert set(plan.plan["sparse"]) == {f"t{i}" for i in range(10)}
+        ratings[steps] = planner._perf_model.rate(planner._best_plan)
+    assert ratings[16] <= ratings[0]
+    chosen = EmbeddingShardingPlanner(topology=Topology(world_size=8, local_world_size=8, compute_device="cuda"), batch_size=8192,
+                                      proposer=GreedyProposer(), debug=False)
+    assert chosen._refine_steps == 0

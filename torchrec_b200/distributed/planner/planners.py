@@ -27,6 +27,7 @@ from torchrec_b200.distributed.planner.types import (
     Enumerator,
     ParameterConstraints,
     Partitioner,
+    Perf,
     PerfModel,
     PlannerError,
     PlannerErrorType,
@@ -122,6 +123,7 @@ class EmbeddingShardingPlanner(ShardingPlanner):
         debug: bool = True,
         callbacks: Optional[List[Callable[[List[ShardingOption]], List[ShardingOption]]]] = None,
         timeout_seconds: Optional[int] = None,
+        refine_steps: Optional[int] = None,
     ) -> None:
         if topology is None:
             world = dist.get_world_size() if dist.is_initialized() else 1
@@ -149,6 +151,10 @@ class EmbeddingShardingPlanner(ShardingPlanner):
         if timeout_seconds is not None:
             assert timeout_seconds > 0, "Timeout must be positive"
         self._timeout_seconds = timeout_seconds
+        # local search after the proposers (see _refine): on with the default proposers, off when the caller chose the proposers
+        self._refine_steps: int = (16 if not proposer else 0) if refine_steps is None else refine_steps
+        self._refine_width: int = 2
+        self._refine_seconds: float = 10.0
         self._num_proposals: int = 0
         self._num_plans: int = 0
         self._best_plan: Optional[List[ShardingOption]] = None
@@ -187,6 +193,8 @@ class EmbeddingShardingPlanner(ShardingPlanner):
                 self._try_proposal(search, proposer, proposal, budget)
             if search.out_of_time():
                 break
+        if search.best_plan is not None and self._refine_steps > 0:
+            self._refine(search, options, budget)
         if search.best_plan is None:
             raise self._no_plan_error(search, budget)
         plan = search.best_plan
@@ -201,28 +209,71 @@ class EmbeddingShardingPlanner(ShardingPlanner):
                      constraints=self._constraints, sharders=sharders, enumerator=self._enumerator, debug=self._debug)
         return result
 
-    def _try_proposal(self, search: "_Search", proposer: Proposer, proposal: List[ShardingOption], budget: Topology) -> None:
+    def _try_proposal(self, search: "_Search", proposer: Optional[Proposer], proposal: List[ShardingOption], budget: Topology) -> Optional[float]:
+        """Place and rate one proposal (or replay the verdict if it was seen before); returns the rating, None if it does not fit."""
         key = tuple(sorted(hash(o) for o in proposal))
         known = search.seen.get(key)
         if known is not None:  # another proposer already suggested exactly this: replay the verdict
             ok, placed, rating = known
-            proposer.feedback(partitionable=ok, plan=placed, perf_rating=rating, storage_constraint=budget)
-            return
+            if proposer is not None:
+                proposer.feedback(partitionable=ok, plan=placed, perf_rating=rating, storage_constraint=budget)
+            return rating
         self._num_proposals += 1
+        rating: Optional[float] = None
         try:
             placed = self._partitioner.partition(proposal=proposal, storage_constraint=budget)
         except PlannerError as err:
             search.note_failure(err, proposal)
             search.seen[key] = (False, proposal, None)
-            proposer.feedback(partitionable=False, plan=proposal, storage_constraint=budget)
+            if proposer is not None:
+                proposer.feedback(partitionable=False, plan=proposal, storage_constraint=budget)
         else:
             self._num_plans += 1
             rating = self._perf_model.rate(plan=placed)
             search.note_success(placed, rating)
             search.seen[key] = (True, placed, rating)
-            proposer.feedback(partitionable=True, plan=placed, perf_rating=rating, storage_constraint=budget)
+            if proposer is not None:
+                proposer.feedback(partitionable=True, plan=placed, perf_rating=rating, storage_constraint=budget)
         search.last_proposal = copy.deepcopy(proposal)
         reset_shard_rank(proposal)  # the option objects are shared between proposals: forget this placement
+        return rating
+
+    def _refine(self, search: "_Search", options: List[ShardingOption], budget: Topology) -> None:
+        """Local search around the proposers' best plan: while the rating improves, take the most loaded rank, and for its most
+        expensive tables try every other way of sharding that one table (all other tables keep their option; the partitioner
+        places the whole proposal again).  The proposers walk the search space along one ordering of the options, so a plan
+        that differs from their best one in a single table (one heavy table-wise table split row-wise, say) is often never
+        suggested; this step finds it.  The reference's planner stops after the proposers
+        (torchrec/distributed/planner/planners.py:520-640)."""
+        def shape(o: ShardingOption):
+            return (o.fqn, o.sharding_type, o.compute_kernel, tuple((tuple(s.size), tuple(s.offset)) for s in o.shards), o.cache_params)
+
+        unplaced = {shape(o): o for o in options}
+        by_table: Dict[str, List[ShardingOption]] = {}
+        for o in options:
+            by_table.setdefault(o.fqn, []).append(o)
+        deadline = time.perf_counter() + self._refine_seconds
+        for _ in range(self._refine_steps):
+            base = [unplaced.get(shape(o)) for o in cast(List[ShardingOption], search.best_plan)]
+            if any(o is None for o in base):  # a callback or proposer changed the options: nothing to vary safely
+                return
+            load: Dict[int, float] = {}
+            for o in cast(List[ShardingOption], search.best_plan):
+                for s in o.shards:
+                    load[cast(int, s.rank)] = load.get(cast(int, s.rank), 0.0) + cast(Perf, s.perf).total
+            worst = max(load, key=lambda r: load[r])
+            on_worst = sorted(((max(cast(Perf, s.perf).total for s in o.shards if s.rank == worst), i)
+                               for i, o in enumerate(cast(List[ShardingOption], search.best_plan)) if any(s.rank == worst for s in o.shards)), reverse=True)
+            before = search.best_rating
+            for _, i in on_worst[: self._refine_width]:
+                for alt in by_table[cast(ShardingOption, base[i]).fqn]:
+                    if alt is base[i]:
+                        continue
+                    if search.out_of_time() or time.perf_counter() > deadline:
+                        return
+                    self._try_proposal(search, None, [alt if j == i else cast(ShardingOption, o) for j, o in enumerate(base)], budget)
+            if search.best_rating >= before:
+                return
 
     def _no_plan_error(self, search: "_Search", budget: Topology) -> PlannerError:
         def total(devices) -> Storage:
