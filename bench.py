@@ -62,7 +62,6 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--loop", choices=["graph", "pipeline", "plain"], default="graph",
                    help="timed loop: TrainPipelineGraphed (whole step replayed as one CUDA graph), TrainPipelineSparseDist, or a plain forward/backward/step loop")
-    p.add_argument("--breakdown", action="store_true", help="print a per-phase device-time breakdown to stderr")
     p.add_argument("--kernel-table", action="store_true", help="print per-kernel device time of one step to stderr (diagnostic)")
     p.add_argument("--host-profile", action="store_true", help="print the host-side profile (cProfile) of 10 untimed steps to stderr (diagnostic)")
     return p.parse_args()

@@ -222,10 +222,18 @@ def _mc_run(rank, world_size):
         for f in ("f0", "f1"):
             torch.testing.assert_close(l_out[f], g_out[f][rank * B:(rank + 1) * B], rtol=1e-5, atol=1e-6)
         assert l_out["f2"].shape == (B, 8)
+        # the remapped ids come back to the rank whose batch they belong to, in the order of its input
         rk = l_remapped.wait()
-        lo0, lo1 = 32 * rank, 16 * rank
-        assert ((rk["f0"].values() >= lo0) & (rk["f0"].values() < lo0 + 32)).all()
-        assert ((rk["f2"].values() >= lo1) & (rk["f2"].values() < lo1 + 16)).all()
+        mine = mk(*per_rank[rank])
+        assert rk.keys() == keys and torch.equal(rk.lengths(), mine.lengths())
+        for f in ("f0", "f1"):
+            lens = mine[f].lengths()
+            g_jt = g_remapped[f]
+            g_off = g_jt.offsets()
+            want = g_jt.values()[int(g_off[rank * B]):int(g_off[(rank + 1) * B])]
+            assert torch.equal(rk[f].values(), want), (f, rk[f].values(), want)
+            assert torch.equal(rk[f].lengths(), lens)
+        assert ((rk["f2"].values() >= 0) & (rk["f2"].values() < 32)).all()
         l_out.values().sum().backward()
         # checkpoint: slot tables come out as shards of the global table and load back
         full = dmp.state_dict()

@@ -51,6 +51,7 @@ def main() -> None:
     p.add_argument("--negatives", type=int, default=8192)
     p.add_argument("--pool", type=int, default=4, help="distinct batches cycled")
     p.add_argument("--padded", action="store_true", help="run the encoder on padded [B, max_len, D] tensors through the library modules (the packed, fused path is the default)")
+    p.add_argument("--library-loss", action="store_true", help="materialise the [P, 1 + N] scores and call the library's cross entropy on them")
     p.add_argument("--cpu", action="store_true", help="plumbing check on the host (gloo); not a benchmark")
     p.add_argument("--kernel-table", action="store_true", help="print the device time per kernel of one untimed step to stderr")
     a = p.parse_args()
@@ -111,8 +112,11 @@ def main() -> None:
         kjt, pos = batches[i % len(batches)]
         opt.zero_grad()
         with torch.autocast(device.type, dtype=torch.bfloat16):
-            logits = dmp(kjt, pos)
-        loss = torch.nn.functional.cross_entropy(logits.float(), torch.zeros(logits.shape[0], dtype=torch.long, device=device))
+            if a.library_loss:
+                logits = dmp(kjt, pos)
+                loss = torch.nn.functional.cross_entropy(logits.float(), torch.zeros(logits.shape[0], dtype=torch.long, device=device))
+            else:
+                loss = dmp(kjt, pos, True)  # sampled-softmax cross entropy fused with its gradient
         loss.backward()
         opt.step()
         return loss

@@ -39,7 +39,61 @@ class BaseShardedManagedCollisionEmbeddingCollection(ShardedEmbeddingModule):
         self._init_bounds = {c.name: (c.get_weight_init_min(), c.get_weight_init_max()) for c in self._managed_collision_collection._embedding_configs}
 
     def input_dist(self, ctx, features: KeyedJaggedTensor) -> Awaitable[Awaitable[KJTList]]:
-        return self._embedding_module.input_dist(ctx, self._managed_collision_collection.preprocess(features))
+        features = self._managed_collision_collection.preprocess(features)
+        pending = self._embedding_module.input_dist(ctx, features)
+        if self._return_remapped_features and self._env.world_size > 1:
+            ctx.id_return_plan = self._plan_id_return(features)
+            ctx.id_return_keys = list(features.keys())
+        return pending
+
+    # ---- remapped ids travel back to the rank that asked ------------------------------------------------------------------
+    @torch.no_grad()
+    def _plan_id_return(self, features: KeyedJaggedTensor) -> List[Tuple[KeyedJaggedTensor, torch.Tensor, torch.Tensor]]:
+        """Per sharding group: (this rank's features in the group's order, the position of every id in the bucketized order, the
+        number of ids routed to every owner).  The bucketization is the input distribution's own, run once more with the
+        permutation output switched on (the pooled distribution does not keep one)."""
+        from torchrec_b200.distributed.embedding_sharding import bucketize_kjt_before_all2all
+
+        em = self._embedding_module
+        ordered = features.permute(em._features_order, em._features_order_tensor) if em._has_features_permute else features
+        plans = []
+        for dist_module, part in zip(em._input_dists, ordered.split(em._feature_splits)):
+            assert not part.variable_stride_per_key(), "remapped ids are returned for fixed-batch inputs only"
+            world = dist_module._world_size
+            bucketized, position = bucketize_kjt_before_all2all(
+                part, num_buckets=world, block_sizes=dist_module._feature_block_sizes_tensor,
+                total_num_blocks=dist_module._feature_total_num_blocks_tensor if dist_module._has_multiple_blocks_per_shard else None,
+                output_permute=True, keep_original_indices=True)
+            plans.append((part, position, bucketized.lengths().view(world, -1).sum(1)))
+        return plans
+
+    def _return_ids(self, ctx) -> KeyedJaggedTensor:
+        """Send every remapped id (global row number) from the rank that owns its row back to the rank whose batch it came from,
+        in the order of that rank's input (``torchrec/distributed/mc_modules.py:173-960`` of the reference returns them
+        through a sequence output distribution of width one)."""
+        import torch.distributed as dist
+
+        from torchrec_b200.ops import sparse_ops as sops
+
+        world, pg = self._env.world_size, self._env.process_group
+        groups = []
+        for (part, position, routed), owned in zip(ctx.id_return_plan, ctx.remapped_kjt):
+            n_keys = len(owned.keys())
+            lengths = owned.lengths().view(n_keys, -1)
+            assert lengths.shape[1] % world == 0, "remapped ids are returned for equal batch sizes per rank only"
+            per_key_rank = lengths.view(n_keys, world, -1).sum(2)  # ids of (feature, requesting rank)
+            rank_major = torch.arange(n_keys * world, device=lengths.device).view(n_keys, world).t().reshape(-1)
+            _, outgoing, _ = sops.permute_2D_sparse_data(rank_major, per_key_rank.reshape(-1, 1), owned.values())
+            send_counts, recv_counts = per_key_rank.sum(0).tolist(), routed.tolist()
+            incoming = outgoing.new_empty(sum(recv_counts))
+            dist.all_to_all_single(incoming, outgoing.contiguous(), recv_counts, send_counts, group=pg)
+            groups.append(KeyedJaggedTensor(keys=part.keys(), values=incoming.index_select(0, position.to(torch.int64)), weights=part.weights_or_none(),
+                                            lengths=part.lengths(), offsets=part._offsets, stride=part._stride))
+        merged = groups[0] if len(groups) == 1 else KeyedJaggedTensor.concat(groups)
+        wanted = ctx.id_return_keys
+        if merged.keys() != wanted and sorted(merged.keys()) == sorted(wanted):
+            merged = merged.permute([merged.keys().index(k) for k in wanted])
+        return merged
 
     @torch.no_grad()
     def _reset_rows(self, evictions: Dict[str, Optional[torch.Tensor]]) -> None:
@@ -73,12 +127,16 @@ class BaseShardedManagedCollisionEmbeddingCollection(ShardedEmbeddingModule):
     def _finish(self, ctx, lazy):
         if not self._return_remapped_features:
             return lazy, None
-        # the remapped ids stay on the rank that owns their rows (global row numbers, one KJT per sharding group)
+        if ctx.id_return_plan is not None:
+            return lazy, NoWait(self._return_ids(ctx))
+        # one rank: the remapped ids (global row numbers) are already where they were asked for
         return lazy, NoWait(ctx.remapped_kjt[0] if len(ctx.remapped_kjt) == 1 else ctx.remapped_kjt)
 
     def create_context(self):
         ctx = self._embedding_module.create_context()
         ctx.remapped_kjt = None
+        ctx.id_return_plan = None
+        ctx.id_return_keys = None
         return ctx
 
     def sharded_parameter_names(self, prefix: str = "") -> Iterator[str]:

@@ -137,7 +137,8 @@ class BERT4RecSampled(nn.Module):
 
     ``forward(kjt, positions)``: ``kjt`` has the features ``"item"`` (the masked histories) and ``"cand"`` (sample 0 holds the ``P``
     target ids of the masked positions followed by the ``N`` shared negatives, the other samples are empty); ``positions [P]`` are
-    the flat indices of the masked positions in ``[B * max_len]``.  Returns ``[P, 1 + N]`` scores, column 0 the positive.
+    the flat indices of the masked positions in ``[B * max_len]``.  Returns ``[P, 1 + N]`` scores, column 0 the positive; with
+    ``loss=True`` the mean sampled-softmax cross entropy instead (the scores then never leave bf16 and are read once).
     """
 
     def __init__(self, vocab_size: int, max_len: int, emb_dim: int, nhead: int, num_layers: int, dim_feedforward: Optional[int] = None, dropout: float = 0.1,
@@ -155,7 +156,7 @@ class BERT4RecSampled(nn.Module):
         cand_len[0] = targets.numel() + negatives.numel()
         return KeyedJaggedTensor(keys=["item", "cand"], values=torch.cat([items, targets, negatives]), lengths=torch.cat([lengths, cand_len]), stride=B)
 
-    def forward(self, input: KeyedJaggedTensor, positions: torch.Tensor) -> torch.Tensor:
+    def forward(self, input: KeyedJaggedTensor, positions: torch.Tensor, loss: bool = False) -> torch.Tensor:
         if self.packed and jagged_transformer.supports(self.encoder):
             x, offsets, jts = self.history.forward_packed(input)
             h = jagged_transformer.jagged_encoder_forward(self.encoder, x, offsets, self.max_len)
@@ -164,8 +165,13 @@ class BERT4RecSampled(nn.Module):
             x, mask, jts = self.history(input)
             h = self.encoder(x, src_key_padding_mask=~mask)
             hp = h.reshape(-1, h.shape[-1]).index_select(0, positions)
-        cand = jts["cand"].values().to(hp.dtype)
         P = positions.numel()
+        if loss:
+            from torchrec_b200.ops.transformer_ops import sampled_softmax_loss
+
+            cand = jts["cand"].values()
+            return sampled_softmax_loss(hp, cand[:P], cand[P:])
+        cand = jts["cand"].values().to(hp.dtype)
         pos = (hp * cand[:P]).sum(-1, keepdim=True)
         neg = hp @ cand[P:].t()
         return torch.cat([pos, neg], dim=1)

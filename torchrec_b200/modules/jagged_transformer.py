@@ -7,8 +7,10 @@ padding position is ever computed.
 * projections and feed-forward layers are the tcgen05 GEMMs with bias epilogues (``ops.dense_ops.linear_act``);
 * ``dropout + residual add + layer norm`` is one kernel, ``gelu + dropout`` another (``ops.transformer_ops``), with masks recomputed in
   the backward instead of stored;
-* attention is the only place that sees padding: q, k, v are padded for one library attention call with the padded keys masked
-  and the result is packed again (``ATTENTION_MODE = "nested"`` selects the library's variable-length kernel where the build has one).
+* attention runs on the packed tokens too: one CTA per (sequence, head) with the sequence's K and V in shared memory
+  (``ops.transformer_ops.packed_attention``, head dimension 64, sequences up to 384 tokens).  Other shapes pad q, k, v for one
+  library attention call with the padded keys masked (``ATTENTION_MODE = "padded"``; ``"nested"`` selects the library's
+  variable-length kernel where the build has one).
 
 With lengths uniform in [20, 200] this is 55 % of the padded token count before any kernel gets faster.  The reference's
 BERT4Rec runs padded ``[B, L, D]`` tensors through library modules (``examples/bert4rec/models/bert4rec.py`` of the reference).
@@ -21,7 +23,7 @@ import torch
 from torch import nn
 
 from torchrec_b200.ops import dense_ops
-from torchrec_b200.ops.transformer_ops import gelu_dropout, residual_layer_norm
+from torchrec_b200.ops.transformer_ops import gelu_dropout, packed_attention, packed_attention_supported, residual_layer_norm
 
 
 def supports(encoder: nn.TransformerEncoder) -> bool:
@@ -63,19 +65,22 @@ def _attention_padded(qkv: torch.Tensor, offsets: torch.Tensor, num_heads: int, 
     return sops.padded_dense_to_jagged(out.transpose(1, 2).reshape(B, max_len, D), offsets, T)
 
 
-ATTENTION_MODE = "padded"  # "padded" | "nested": how the packed tokens reach the attention kernel on CUDA
+ATTENTION_MODE = "kernel"  # "kernel" | "padded" | "nested": how the packed tokens reach an attention kernel on CUDA
 
 
 def varlen_attention(qkv: torch.Tensor, offsets: torch.Tensor, num_heads: int, max_len: int, p: float = 0.0) -> torch.Tensor:
     """Self-attention inside every sequence of the packed ``qkv [T, 3 * D]``; returns ``[T, D]``.
 
-    ``ATTENTION_MODE = "nested"`` hands the packed layout to the library's variable-length attention through a jagged nested
-    tensor (cost ``sum(len^2)``); where the build has no variable-length kernel for the device it silently decomposes into one
-    small attention per sequence, so the default is ``"padded"``: one library attention call over ``[B, H, max_len, Dh]`` with the
-    padded keys masked.  Everything outside the attention stays packed either way."""
+    ``ATTENTION_MODE = "kernel"`` (default) runs this package's packed-attention kernel where the shape allows (bf16, head
+    dimension 64, ``max_len <= 384``; cost ``sum(len^2)``) and the padded form elsewhere.  ``"padded"`` is one library attention
+    call over ``[B, H, max_len, Dh]`` with the padded keys masked.  ``"nested"`` hands the packed layout to the library's
+    variable-length attention through a jagged nested tensor; where the build has no variable-length kernel for the device that
+    silently decomposes into one small attention per sequence.  Everything outside the attention stays packed in every mode."""
     T, three_d = qkv.shape
     D = three_d // 3
-    if qkv.is_cuda and ATTENTION_MODE == "padded":
+    if qkv.is_cuda and ATTENTION_MODE == "kernel" and packed_attention_supported(qkv, num_heads, max_len):
+        return packed_attention(qkv, offsets, num_heads, max_len, p)
+    if qkv.is_cuda and ATTENTION_MODE in ("padded", "kernel"):
         return _attention_padded(qkv, offsets, num_heads, max_len, p)
     q, k, v = (t.reshape(T, num_heads, D // num_heads) for t in qkv.split(D, dim=1))
     if qkv.is_cuda:

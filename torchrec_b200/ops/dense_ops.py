@@ -235,11 +235,51 @@ def _tcgen05_tn_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
     )
 
 
+class _LinearSmallK(torch.autograd.Function):
+    """``act(x W^T + b)`` for a layer with a handful of input features (K <= 32, e.g. the 13 dense features of the Criteo models):
+    CUDA-core kernels that keep the weight in shared memory; the weight gradient is accumulated in fp32."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, act: int):
+        x16 = (x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)).contiguous()
+        y = torch.ops.trb200.linear_small_k_fwd(x16, weight.detach().float().contiguous(), None if bias is None else bias.detach().float(), act)
+        ctx.act = act
+        ctx.bias_ref = weakref.ref(bias) if bias is not None else None
+        ctx.save_for_backward(x16, weight, y)
+        ctx.x_dtype = x.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, weight, y = ctx.saved_tensors
+        dy = dy.contiguous()
+        if dy.dtype != torch.bfloat16:
+            dy = dy.to(torch.bfloat16)
+        dz = act_backward(dy, y, ctx.act) if ctx.act in (ACT_RELU, ACT_SIGMOID) else dy
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.matmul(dz, weight.to(torch.bfloat16)).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            sink = _grad_sink(weight)
+            target = sink if sink is not None else torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+            torch.ops.trb200.linear_small_k_wgrad_acc(dz, x16, target)
+            dw = None if sink is not None else target.to(weight.dtype)
+        if ctx.bias_ref is not None and ctx.needs_input_grad[2]:
+            db = colsum(dz, into=_grad_sink(ctx.bias_ref()))
+        return dx, dw, db, None
+
+
+def _small_k_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    K, N = weight.shape[1], weight.shape[0]
+    return x.is_cuda and _ext.has_cuda_ext() and K <= 32 and K % 8 != 0 and N % 8 == 0 and weight.dtype == torch.float32
+
+
 def linear_act(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], act: int = ACT_NONE) -> torch.Tensor:
     """Fused ``act(x @ weight.T + bias)``; bf16 tensor-core path on CUDA, torch math elsewhere."""
     if fused_dense_enabled(x):
         lead = x.shape[:-1]
-        y = _LinearAct.apply(x.reshape(-1, x.shape[-1]), weight, bias, act)
+        fn = _LinearSmallK if _small_k_ok(x, weight) else _LinearAct
+        y = fn.apply(x.reshape(-1, x.shape[-1]), weight, bias, act)
         return y.view(*lead, weight.shape[0])
     y = torch.nn.functional.linear(x, weight, bias)
     if act == ACT_RELU:
@@ -434,7 +474,37 @@ def lowrank_cross_stack(x0, Vs, Ws, biases) -> torch.Tensor:
     return _LowRankCrossStack.apply(x0, len(Vs), *Vs, *Ws, *biases)
 
 
+class _LinearOut1(torch.autograd.Function):
+    """Logit layer ``x [M, K] bf16 -> [M, 1] fp32``: one warp per row forward; the backward writes ``dx`` and reduces the weight and
+    bias gradients in one pass over ``x``."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        y = torch.ops.trb200.linear_out1_fwd(x, weight.detach().reshape(-1), None if bias is None else bias.detach())
+        ctx.bias_ref = weakref.ref(bias) if bias is not None else None
+        ctx.save_for_backward(x, weight)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        bias = ctx.bias_ref() if ctx.bias_ref is not None else None
+        w_sink = _grad_sink(weight) if ctx.needs_input_grad[1] else None
+        b_sink = _grad_sink(bias) if bias is not None and ctx.needs_input_grad[2] else None
+        dw = w_sink if w_sink is not None else torch.zeros(weight.shape, dtype=torch.float32, device=x.device)
+        db = None
+        if bias is not None:
+            db = b_sink if b_sink is not None else torch.zeros(1, dtype=torch.float32, device=x.device)
+        dx = torch.ops.trb200.linear_out1_bwd(dy.contiguous().float().reshape(-1), x, weight.detach().reshape(-1), dw.view(-1), db, ctx.needs_input_grad[0])
+        return (dx if ctx.needs_input_grad[0] else None, None if w_sink is not None or not ctx.needs_input_grad[1] else dw,
+                None if bias is None or b_sink is not None or not ctx.needs_input_grad[2] else db)
+
+
 def linear_small_out(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
-    """Final logits layer (``out_features`` tiny, e.g. 1): a CUDA-core dot-product kernel is a
-    better fit than a tensor-core tile; plain ``F.linear`` in fp32 keeps the logits exact."""
+    """Final logits layer in fp32 (``out_features`` tiny, e.g. 1): a CUDA-core dot-product kernel is a better fit than a
+    tensor-core tile; other shapes go through ``F.linear`` in fp32."""
+    if (x.is_cuda and _ext.has_cuda_ext() and x.dim() == 2 and x.dtype == torch.bfloat16 and x.is_contiguous() and weight.shape[0] == 1
+            and weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[1] % 8 == 0 and weight.shape[1] <= 1024
+            and (bias is None or bias.dtype == torch.float32)):
+        return _LinearOut1.apply(x, weight, bias)
     return torch.nn.functional.linear(x.float(), weight, bias)
