@@ -8,11 +8,15 @@
 // accumulators needs to pay off, and the softmax wants the scores in registers.  Probabilities go from the accumulator
 // registers straight into the A operand of the second product; operands that must be read transposed come through ldmatrix.trans.
 //
-// Backward, same CTA shape, two phases over Q, K, V, dO in shared memory and no atomics: (A) a warp owns 16 keys and walks all
-// queries: dV = Pd^T dO, dK = dS^T Q; (B) a warp owns 16 queries and walks all keys: dQ = dS K.  The scores are recomputed in
-// both (7 small products instead of 5) from the saved log-sum-exp.
+// Backward: two kernels of the same CTA shape and no atomics.  `varlen_attn_bwd_kv_kernel` keeps Q and dO of the sequence in shared
+// memory, a warp owns 16 keys and walks all queries: dV = Pd^T dO, dK = dS^T Q (everything held transposed, [key][query]).
+// `varlen_attn_bwd_q_kernel` keeps K and V in shared memory, a warp owns 16 queries and walks all keys: dQ = dS K.  The scores
+// are recomputed in both (7 small products instead of 5) from the saved log-sum-exp; two arrays per kernel instead of four in
+// one kernel lets three CTAs share an SM.
 //
-// Dropout on the probabilities is a hash of (seed, query token, head, key position) recomputed in the backward; no mask is stored.
+// Dropout on the probabilities: 8 bits per element from a hash of (seed, sequence, head, query pair, key pair) - one hash serves a
+// 2 x 2 block, so both the query-major and the key-major kernels hash once per two elements; the keep probability is rounded
+// to a multiple of 1/256 and the rescale factor matches the rounded value.  The backward recomputes the hash; no mask is stored.
 // The reference model pads every sequence to max_len and calls the library's attention
 // (examples/bert4rec/models/bert4rec.py of the reference, nn.TransformerEncoderLayer).
 #include <ATen/ATen.h>
@@ -31,8 +35,8 @@ constexpr int kAttnPad = 8;  // bf16 elements of padding per shared row: 16-byte
 
 struct AttnDrop {
   uint32_t seed_lo, seed_hi;
-  uint32_t keep_below;  // an element is kept iff its 32 hash bits are below this
-  float scale;          // 2^32 / keep_below
+  uint32_t keep_below;  // an element is kept iff its 8 hash bits are below this (1..256)
+  float scale;          // 256 / keep_below
   int on;
 };
 
@@ -44,12 +48,14 @@ __device__ __forceinline__ uint32_t attn_hash32(uint32_t x) {
   x ^= x >> 16;
   return x;
 }
-__device__ __forceinline__ uint32_t attn_row_key(const AttnDrop& d, int64_t tok, int h, int H) {
-  return attn_hash32(uint32_t(tok * H + h) ^ d.seed_lo) + d.seed_hi;
+// per (sequence, head)
+__device__ __forceinline__ uint32_t attn_drop_base(const AttnDrop& d, int64_t tok0, int h, int H) {
+  return attn_hash32(uint32_t(tok0 * H + h) ^ d.seed_lo) + d.seed_hi;
 }
-__device__ __forceinline__ float attn_keep(const AttnDrop& d, uint32_t row_key, int key) {
-  if (!d.on) return 1.f;
-  return attn_hash32(row_key ^ (uint32_t(key) * 0x9E3779B9u)) < d.keep_below ? d.scale : 0.f;
+// 32 bits for the 2 x 2 block (queries 2 qp, 2 qp + 1) x (keys 2 kp, 2 kp + 1); element (q, k) owns byte 2 (q & 1) + (k & 1)
+__device__ __forceinline__ uint32_t attn_block_bits(uint32_t base, int qp, int kp) { return attn_hash32(base ^ ((uint32_t(qp) << 16) | uint32_t(kp))); }
+__device__ __forceinline__ float attn_keep(const AttnDrop& d, uint32_t bits, int q_odd, int k_odd) {
+  return ((bits >> (8 * (2 * q_odd + k_odd))) & 0xffu) < d.keep_below ? d.scale : 0.f;
 }
 
 __device__ __forceinline__ void attn_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -152,6 +158,7 @@ __global__ void __launch_bounds__(32 * WARPS) varlen_attn_fwd_kernel(const __nv_
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t4 = lane & 3;
+  const uint32_t dbase = attn_drop_base(drop, tok0, h, H);
   for (int q0 = warp * 16; q0 < n; q0 += WARPS * 16) {
     const int r0 = q0 + g, r1 = q0 + g + 8;
     uint32_t qa[DH / 16][4];
@@ -164,7 +171,6 @@ __global__ void __launch_bounds__(32 * WARPS) varlen_attn_fwd_kernel(const __nv_
       qa[ks][2] = r0 < n ? attn_ld32(p0 + 8) : 0u;
       qa[ks][3] = r1 < n ? attn_ld32(p1 + 8) : 0u;
     }
-    const uint32_t rk0 = attn_row_key(drop, tok0 + r0, h, H), rk1 = attn_row_key(drop, tok0 + r1, h, H);
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     float o[DH / 8][4];
 #pragma unroll
@@ -206,14 +212,22 @@ __global__ void __launch_bounds__(32 * WARPS) varlen_attn_fwd_kernel(const __nv_
         o[t][3] *= al1;
       }
 #pragma unroll
-      for (int t = 0; t < 4; ++t)
+      for (int t = 0; t < 4; ++t) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const int key = kc + t * 8 + 2 * t4 + (k & 1);
           const float e = exp2f(s[t][k] - (k < 2 ? mn0 : mn1));
           if (k < 2) l0 += e; else l1 += e;
-          s[t][k] = e * attn_keep(drop, k < 2 ? rk0 : rk1, key);
+          s[t][k] = e;
         }
+        if (drop.on) {  // rows r0 and r1 have the parity of g; the two keys of a tile are an aligned pair
+          const int kp = ((kc + t * 8) >> 1) + t4;
+          const uint32_t b0 = attn_block_bits(dbase, r0 >> 1, kp), b1 = attn_block_bits(dbase, r1 >> 1, kp);
+          s[t][0] *= attn_keep(drop, b0, g & 1, 0);
+          s[t][1] *= attn_keep(drop, b0, g & 1, 1);
+          s[t][2] *= attn_keep(drop, b1, g & 1, 0);
+          s[t][3] *= attn_keep(drop, b1, g & 1, 1);
+        }
+      }
       attn_nn<DH>(o, s, Vs, P, kc, lane);
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -233,11 +247,27 @@ __global__ void __launch_bounds__(32 * WARPS) varlen_attn_fwd_kernel(const __nv_
   }
 }
 
+// A fragments of rows r0 + g, r0 + g + 8 of a global row-major array (row pitch ld), zero beyond n
+template <int DH>
+__device__ __forceinline__ void attn_a_frags_global(const __nv_bfloat16* base, int64_t ld, int r0, int n, int g, int t4, uint32_t (&a)[DH / 16][4]) {
+  const int ra = r0 + g, rb = r0 + g + 8;
+#pragma unroll
+  for (int ks = 0; ks < DH / 16; ++ks) {
+    const __nv_bfloat16* pa = base + ra * ld + ks * 16 + 2 * t4;
+    const __nv_bfloat16* pb = base + rb * ld + ks * 16 + 2 * t4;
+    a[ks][0] = ra < n ? attn_ld32(pa) : 0u;
+    a[ks][1] = rb < n ? attn_ld32(pb) : 0u;
+    a[ks][2] = ra < n ? attn_ld32(pa + 8) : 0u;
+    a[ks][3] = rb < n ? attn_ld32(pb + 8) : 0u;
+  }
+}
+
+// dK and dV: Q and dO of the sequence in shared memory; a warp owns 16 keys and walks the queries 32 at a time ([key][query] tiles)
 template <int DH, int WARPS>
-__global__ void __launch_bounds__(32 * WARPS) varlen_attn_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ out,
-                                                                    const __nv_bfloat16* __restrict__ dout, const float* __restrict__ lse2,
-                                                                    const int64_t* __restrict__ offsets, __nv_bfloat16* __restrict__ dqkv, int H, int n_cap,
-                                                                    int np_cap, float scale, float scale_log2, AttnDrop drop, int* __restrict__ err) {
+__global__ void __launch_bounds__(32 * WARPS) varlen_attn_bwd_kv_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ out,
+                                                                       const __nv_bfloat16* __restrict__ dout, const float* __restrict__ lse2,
+                                                                       const int64_t* __restrict__ offsets, __nv_bfloat16* __restrict__ dqkv, int H, int n_cap,
+                                                                       int np_cap, float scale, float scale_log2, AttnDrop drop, int* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char attn_smem[];
   constexpr int P = DH + kAttnPad;
   const int b = blockIdx.x / H, h = blockIdx.x - b * H;
@@ -246,26 +276,21 @@ __global__ void __launch_bounds__(32 * WARPS) varlen_attn_bwd_kernel(const __nv_
   if (n <= 0) return;
   const int D = H * DH;
   const int64_t ld = 3 * int64_t(D);
-  if (n > n_cap) {
+  if (n > n_cap) {  // the tail of a sequence that is longer than the launch was sized for gets zero gradients (k and v here)
     if (threadIdx.x == 0) atomicExch(err, 1);
-    for (int i = threadIdx.x; i < (n - n_cap) * 3 * DH; i += blockDim.x) {
-      const int r = n_cap + i / (3 * DH), c = i % (3 * DH);
-      dqkv[(tok0 + r) * ld + (c / DH) * D + h * DH + (c % DH)] = __float2bfloat16(0.f);
+    for (int i = threadIdx.x; i < (n - n_cap) * 2 * DH; i += blockDim.x) {
+      const int r = n_cap + i / (2 * DH), c = i % (2 * DH);
+      dqkv[(tok0 + r) * ld + (1 + c / DH) * D + h * DH + (c % DH)] = __float2bfloat16(0.f);
     }
     n = n_cap;
   }
   const int np = (n + 31) & ~31;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(attn_smem);
-  __nv_bfloat16* Ks = Qs + np_cap * P;
-  __nv_bfloat16* Vs = Ks + np_cap * P;
-  __nv_bfloat16* Gs = Vs + np_cap * P;  // dO
+  __nv_bfloat16* Gs = Qs + np_cap * P;  // dO
   float* lse_s = reinterpret_cast<float*>(Gs + np_cap * P);
   float* del_s = lse_s + np_cap;
-  uint32_t* rk_s = reinterpret_cast<uint32_t*>(del_s + np_cap);
   const __nv_bfloat16* head = qkv + tok0 * ld + h * DH;
   attn_stage<DH>(head, ld, n, np, Qs, threadIdx.x, blockDim.x);
-  attn_stage<DH>(head + D, ld, n, np, Ks, threadIdx.x, blockDim.x);
-  attn_stage<DH>(head + 2 * D, ld, n, np, Vs, threadIdx.x, blockDim.x);
   attn_stage<DH>(dout + tok0 * D + h * DH, D, n, np, Gs, threadIdx.x, blockDim.x);
   for (int r = threadIdx.x; r < np; r += blockDim.x) {
     float del = 0.f, l = INFINITY;  // padded queries: exp2(s - inf) = 0, nothing flows
@@ -287,22 +312,21 @@ __global__ void __launch_bounds__(32 * WARPS) varlen_attn_bwd_kernel(const __nv_
     }
     del_s[r] = del;
     lse_s[r] = l;
-    rk_s[r] = attn_row_key(drop, tok0 + r, h, H);
   }
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t4 = lane & 3;
-
-  // phase A: a warp owns 16 keys, walks the queries 32 at a time; everything is held transposed ([key][query])
+  const uint32_t dbase = attn_drop_base(drop, tok0, h, H);
   for (int j0 = warp * 16; j0 < n; j0 += WARPS * 16) {
     uint32_t ka[DH / 16][4], va[DH / 16][4];
-    attn_a_frags<DH>(Ks, P, j0, g, t4, ka);
-    attn_a_frags<DH>(Vs, P, j0, g, t4, va);
+    attn_a_frags_global<DH>(head + D, ld, j0, n, g, t4, ka);
+    attn_a_frags_global<DH>(head + 2 * D, ld, j0, n, g, t4, va);
     float dk[DH / 8][4], dv[DH / 8][4];
 #pragma unroll
     for (int t = 0; t < DH / 8; ++t)
 #pragma unroll
       for (int k = 0; k < 4; ++k) dk[t][k] = dv[t][k] = 0.f;
+    const int k0 = j0 + g, k1 = j0 + g + 8;  // both have the parity of g
     for (int qc = 0; qc < np; qc += 32) {
       float st[4][4], dp[4][4];
 #pragma unroll
@@ -312,20 +336,27 @@ __global__ void __launch_bounds__(32 * WARPS) varlen_attn_bwd_kernel(const __nv_
       attn_nt<DH>(st, ka, Qs, P, qc, g, t4);
       attn_nt<DH>(dp, va, Gs, P, qc, g, t4);
 #pragma unroll
-      for (int t = 0; t < 4; ++t)
+      for (int t = 0; t < 4; ++t) {
+        const int q = qc + t * 8 + 2 * t4;  // queries q, q + 1: an aligned pair
+        float f[4] = {1.f, 1.f, 1.f, 1.f};
+        if (drop.on) {
+          const uint32_t b0 = attn_block_bits(dbase, q >> 1, k0 >> 1), b1 = attn_block_bits(dbase, q >> 1, k1 >> 1);
+          f[0] = attn_keep(drop, b0, 0, g & 1);
+          f[1] = attn_keep(drop, b0, 1, g & 1);
+          f[2] = attn_keep(drop, b1, 0, g & 1);
+          f[3] = attn_keep(drop, b1, 1, g & 1);
+        }
+        const float2 ls = *reinterpret_cast<const float2*>(lse_s + q), de = *reinterpret_cast<const float2*>(del_s + q);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const int q = qc + t * 8 + 2 * t4 + (k & 1);
-          const int key = j0 + g + 8 * (k >> 1);
-          const float a = exp2f(st[t][k] * scale_log2 - lse_s[q]);
-          const float f = attn_keep(drop, rk_s[q], key);
-          st[t][k] = a * f;
-          dp[t][k] = a * (f * dp[t][k] - del_s[q]);
+          const float a = exp2f(st[t][k] * scale_log2 - ((k & 1) ? ls.y : ls.x));
+          st[t][k] = a * f[k];
+          dp[t][k] = a * (f[k] * dp[t][k] - ((k & 1) ? de.y : de.x));
         }
+      }
       attn_nn<DH>(dv, st, Gs, P, qc, lane);
       attn_nn<DH>(dk, dp, Qs, P, qc, lane);
     }
-    const int k0 = j0 + g, k1 = j0 + g + 8;
 #pragma unroll
     for (int t = 0; t < DH / 8; ++t) {
       const int col = h * DH + t * 8 + 2 * t4;
@@ -339,15 +370,57 @@ __global__ void __launch_bounds__(32 * WARPS) varlen_attn_bwd_kernel(const __nv_
       }
     }
   }
+}
 
-  // phase B: a warp owns 16 queries, walks the keys 32 at a time
+// dQ: K and V of the sequence in shared memory; a warp owns 16 queries and walks the keys 32 at a time
+template <int DH, int WARPS>
+__global__ void __launch_bounds__(32 * WARPS) varlen_attn_bwd_q_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ out,
+                                                                      const __nv_bfloat16* __restrict__ dout, const float* __restrict__ lse2,
+                                                                      const int64_t* __restrict__ offsets, __nv_bfloat16* __restrict__ dqkv, int H, int n_cap,
+                                                                      int np_cap, float scale, float scale_log2, AttnDrop drop) {
+  extern __shared__ __align__(16) unsigned char attn_smem[];
+  constexpr int P = DH + kAttnPad;
+  const int b = blockIdx.x / H, h = blockIdx.x - b * H;
+  const int64_t tok0 = offsets[b];
+  int n = int(offsets[b + 1] - tok0);
+  if (n <= 0) return;
+  const int D = H * DH;
+  const int64_t ld = 3 * int64_t(D);
+  if (n > n_cap) {
+    for (int i = threadIdx.x; i < (n - n_cap) * DH; i += blockDim.x) dqkv[(tok0 + n_cap + i / DH) * ld + h * DH + (i % DH)] = __float2bfloat16(0.f);
+    n = n_cap;
+  }
+  const int np = (n + 31) & ~31;
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(attn_smem);
+  __nv_bfloat16* Vs = Ks + np_cap * P;
+  const __nv_bfloat16* head = qkv + tok0 * ld + h * DH;
+  attn_stage<DH>(head + D, ld, n, np, Ks, threadIdx.x, blockDim.x);
+  attn_stage<DH>(head + 2 * D, ld, n, np, Vs, threadIdx.x, blockDim.x);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const uint32_t dbase = attn_drop_base(drop, tok0, h, H);
   for (int q0 = warp * 16; q0 < n; q0 += WARPS * 16) {
-    uint32_t qa[DH / 16][4], ga[DH / 16][4];
-    attn_a_frags<DH>(Qs, P, q0, g, t4, qa);
-    attn_a_frags<DH>(Gs, P, q0, g, t4, ga);
+    uint32_t qa[DH / 16][4], ga[DH / 16][4], oa[DH / 16][4];
+    attn_a_frags_global<DH>(head, ld, q0, n, g, t4, qa);
+    attn_a_frags_global<DH>(dout + tok0 * D + h * DH, D, q0, n, g, t4, ga);
+    attn_a_frags_global<DH>(out + tok0 * D + h * DH, D, q0, n, g, t4, oa);
     const int r0 = q0 + g, r1 = q0 + g + 8;
-    const float ls0 = lse_s[r0], ls1 = lse_s[r1], de0 = del_s[r0], de1 = del_s[r1];
-    const uint32_t rk0 = rk_s[r0], rk1 = rk_s[r1];
+    // delta = rowsum(dO * O): this lane's 16 columns of each row, then the four lanes of the row
+    float de0 = 0.f, de1 = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < DH / 16; ++ks)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ga[ks][j]));
+        const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&oa[ks][j]));
+        if (j & 1) de1 += x.x * y.x + x.y * y.y; else de0 += x.x * y.x + x.y * y.y;
+      }
+    de0 += __shfl_xor_sync(0xffffffffu, de0, 1);
+    de0 += __shfl_xor_sync(0xffffffffu, de0, 2);
+    de1 += __shfl_xor_sync(0xffffffffu, de1, 1);
+    de1 += __shfl_xor_sync(0xffffffffu, de1, 2);
+    const float ls0 = r0 < n ? lse2[(tok0 + r0) * H + h] : INFINITY, ls1 = r1 < n ? lse2[(tok0 + r1) * H + h] : INFINITY;
     float dq[DH / 8][4];
 #pragma unroll
     for (int t = 0; t < DH / 8; ++t)
@@ -362,14 +435,23 @@ __global__ void __launch_bounds__(32 * WARPS) varlen_attn_bwd_kernel(const __nv_
       attn_nt<DH>(s, qa, Ks, P, kc, g, t4);
       attn_nt<DH>(dp, ga, Vs, P, kc, g, t4);
 #pragma unroll
-      for (int t = 0; t < 4; ++t)
+      for (int t = 0; t < 4; ++t) {
+        float f[4] = {1.f, 1.f, 1.f, 1.f};
+        if (drop.on) {
+          const int kp = ((kc + t * 8) >> 1) + t4;
+          const uint32_t b0 = attn_block_bits(dbase, r0 >> 1, kp), b1 = attn_block_bits(dbase, r1 >> 1, kp);
+          f[0] = attn_keep(drop, b0, g & 1, 0);
+          f[1] = attn_keep(drop, b0, g & 1, 1);
+          f[2] = attn_keep(drop, b1, g & 1, 0);
+          f[3] = attn_keep(drop, b1, g & 1, 1);
+        }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int key = kc + t * 8 + 2 * t4 + (k & 1);
           const float a = key < n ? exp2f(s[t][k] * scale_log2 - (k < 2 ? ls0 : ls1)) : 0.f;
-          const float f = attn_keep(drop, k < 2 ? rk0 : rk1, key);
-          dp[t][k] = a * (f * dp[t][k] - (k < 2 ? de0 : de1));
+          dp[t][k] = a * (f[k] * dp[t][k] - (k < 2 ? de0 : de1));
         }
+      }
       attn_nn<DH>(dq, dp, Ks, P, kc, lane);
     }
 #pragma unroll
@@ -386,21 +468,21 @@ static AttnDrop make_attn_drop(double p, int64_t seed) {
   d.on = p > 0.0 ? 1 : 0;
   d.seed_lo = uint32_t(uint64_t(seed));
   d.seed_hi = uint32_t(uint64_t(seed) >> 32);
-  const double keep = std::min(4294967295.0, std::max(1.0, std::floor((1.0 - p) * 4294967296.0)));
+  const double keep = std::min(256.0, std::max(1.0, std::floor((1.0 - p) * 256.0 + 0.5)));
   d.keep_below = uint32_t(keep);
-  d.scale = d.on ? float(4294967296.0 / keep) : 1.f;
+  d.scale = d.on ? float(256.0 / keep) : 1.f;
   return d;
 }
 
 constexpr int kAttnDH = 64;
 constexpr int kAttnFwdWarps = 4;
-constexpr int kAttnBwdWarps = 8;
+constexpr int kAttnBwdWarps = 4;
 
 static void attn_check(const at::Tensor& qkv, const at::Tensor& offsets, int64_t H, int64_t max_len) {
   TORCH_CHECK(qkv.is_cuda() && qkv.scalar_type() == at::kBFloat16 && qkv.dim() == 2 && qkv.is_contiguous(), "qkv must be a contiguous bf16 CUDA matrix");
   TORCH_CHECK(offsets.is_cuda() && offsets.scalar_type() == at::kLong && offsets.dim() == 1 && offsets.is_contiguous() && offsets.numel() >= 1);
   TORCH_CHECK(H >= 1 && qkv.size(1) == 3 * H * kAttnDH, "varlen attention: head dimension must be 64");
-  TORCH_CHECK(max_len >= 1 && max_len <= 384, "varlen attention: max_len must be in [1, 384]");
+  TORCH_CHECK(max_len >= 1 && max_len <= 768, "varlen attention: max_len must be in [1, 768]");
 }
 
 std::tuple<at::Tensor, at::Tensor> varlen_attn_fwd(const at::Tensor& qkv, const at::Tensor& offsets, int64_t H, int64_t max_len, double p, int64_t seed,
@@ -438,16 +520,24 @@ at::Tensor varlen_attn_bwd(const at::Tensor& dout, const at::Tensor& qkv, const 
   at::Tensor dqkv = at::empty_like(qkv);
   if (T == 0 || B == 0) return dqkv;
   const int np_cap = (int(max_len) + 31) & ~31;
-  const size_t smem = size_t(4) * np_cap * (kAttnDH + kAttnPad) * sizeof(__nv_bfloat16) + size_t(3) * np_cap * sizeof(float);
-  TORCH_CHECK(smem <= 227 * 1024, "varlen attention backward: max_len ", max_len, " does not fit in shared memory");
-  auto kern = varlen_attn_bwd_kernel<kAttnDH, kAttnBwdWarps>;
-  TRB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  const size_t rows_bytes = size_t(2) * np_cap * (kAttnDH + kAttnPad) * sizeof(__nv_bfloat16);
+  const size_t smem_kv = rows_bytes + size_t(2) * np_cap * sizeof(float);
+  auto kern_kv = varlen_attn_bwd_kv_kernel<kAttnDH, kAttnBwdWarps>;
+  auto kern_q = varlen_attn_bwd_q_kernel<kAttnDH, kAttnBwdWarps>;
+  TRB_CUDA_CHECK(cudaFuncSetAttribute(kern_kv, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_kv)));
+  TRB_CUDA_CHECK(cudaFuncSetAttribute(kern_q, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rows_bytes)));
   const float scale = float(1.0 / std::sqrt(double(kAttnDH)));
-  kern<<<unsigned(B * H), 32 * kAttnBwdWarps, smem, at::cuda::getCurrentCUDAStream()>>>(
-      reinterpret_cast<const __nv_bfloat16*>(qkv.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(out.data_ptr()),
-      reinterpret_cast<const __nv_bfloat16*>(dout.data_ptr()), lse.data_ptr<float>(), offsets.data_ptr<int64_t>(),
-      reinterpret_cast<__nv_bfloat16*>(dqkv.data_ptr()), int(H), int(max_len), np_cap, scale, scale * 1.4426950408889634f, make_attn_drop(p, seed),
-      err.data_ptr<int>());
+  const AttnDrop drop = make_attn_drop(p, seed);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const auto* qp = reinterpret_cast<const __nv_bfloat16*>(qkv.data_ptr());
+  const auto* op = reinterpret_cast<const __nv_bfloat16*>(out.data_ptr());
+  const auto* gp = reinterpret_cast<const __nv_bfloat16*>(dout.data_ptr());
+  auto* dp = reinterpret_cast<__nv_bfloat16*>(dqkv.data_ptr());
+  kern_kv<<<unsigned(B * H), 32 * kAttnBwdWarps, smem_kv, stream>>>(qp, op, gp, lse.data_ptr<float>(), offsets.data_ptr<int64_t>(), dp, int(H), int(max_len), np_cap,
+                                                                   scale, scale * 1.4426950408889634f, drop, err.data_ptr<int>());
+  TRB_CUDA_CHECK(cudaGetLastError());
+  kern_q<<<unsigned(B * H), 32 * kAttnBwdWarps, rows_bytes, stream>>>(qp, op, gp, lse.data_ptr<float>(), offsets.data_ptr<int64_t>(), dp, int(H), int(max_len), np_cap,
+                                                                     scale, scale * 1.4426950408889634f, drop);
   TRB_CUDA_CHECK(cudaGetLastError());
   return dqkv;
 }

@@ -1,14 +1,18 @@
-"""Context and base output dist of the sequence (unpooled) shardings
-(cf. ``torchrec/distributed/sharding/sequence_sharding.py``)."""
+"""What all sequence (unpooled) shardings share: the context that carries the input distribution's routes to the output
+distribution, the output distribution itself (rows travel back along the routes their ids came by) and the lookup factory.
+The per-type modules (``tw_/cw_/rw_/dp_sequence_sharding.py``) only say how ids are routed.
+(cf. ``torchrec/distributed/sharding/sequence_sharding.py`` and the ``*_sequence_sharding.py`` files next to it.)"""
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Optional
+from typing import Any, Dict, List, Optional
 
 import torch
+import torch.distributed as dist
 
-from torchrec_b200.distributed.embedding_sharding import EmbeddingShardingContext
-from torchrec_b200.distributed.embedding_types import KJTList
+from torchrec_b200.distributed.embedding_sharding import BaseEmbeddingDist, EmbeddingShardingContext
+from torchrec_b200.distributed.embedding_types import BaseEmbeddingLookup, KJTList
+from torchrec_b200.distributed.types import Awaitable, CommOp, NoWait, QuantizedCommCodecs
 from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
 from torchrec_b200.streamable import Multistreamable
 
@@ -56,3 +60,43 @@ class InferSequenceShardingContext(Multistreamable):
         for t in (self.unbucketize_permute_tensor, self.bucket_mapping_tensor, self.bucketized_length):
             if t is not None and t.is_cuda:
                 t.record_stream(stream)
+
+
+class SequenceRowsReturn(BaseEmbeddingDist[SequenceShardingContext, torch.Tensor, torch.Tensor]):
+    """Output distribution of every sharded sequence lookup: the rows ``[sum L, D]`` go back to the ranks that sent the ids, along
+    the splits recorded by the input distribution.  ``restore_order`` additionally undoes the row-wise bucketization."""
+
+    def __init__(self, pg: dist.ProcessGroup, features_per_rank: List[int], device: Optional[torch.device] = None,
+                 qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None, restore_order: bool = False) -> None:
+        super().__init__()
+        from torchrec_b200.distributed.dist_data import SequenceEmbeddingsAllToAll
+
+        codecs = (qcomm_codecs_registry or {}).get(CommOp.SEQUENCE_EMBEDDINGS_ALL_TO_ALL.name)
+        self._dist = SequenceEmbeddingsAllToAll(pg, features_per_rank, device, codecs=codecs)
+        self._restore_order = restore_order
+
+    def forward(self, local_embs: torch.Tensor, sharding_ctx: Optional[SequenceShardingContext] = None) -> Awaitable[torch.Tensor]:
+        assert sharding_ctx is not None, "the sequence output distribution needs the routes of the input distribution"
+        c = sharding_ctx
+        return self._dist(local_embs, lengths=c.lengths_after_input_dist, input_splits=c.input_splits, output_splits=c.output_splits,
+                          batch_size_per_rank=c.batch_size_per_rank, sparse_features_recat=c.sparse_features_recat,
+                          unbucketize_permute_tensor=c.unbucketize_permute_tensor if self._restore_order else None)
+
+
+class LocalRows(BaseEmbeddingDist[SequenceShardingContext, torch.Tensor, torch.Tensor]):
+    """Output 'distribution' of a replicated table: the rows are already where they are wanted."""
+
+    def forward(self, local_embs: torch.Tensor, sharding_ctx: Optional[SequenceShardingContext] = None) -> Awaitable[torch.Tensor]:
+        return NoWait(local_embs)
+
+
+class SequenceLookupMixin:
+    """``create_lookup`` of the sequence shardings: the grouped unpooled lookup over this rank's shards."""
+
+    def create_lookup(self, device: Optional[torch.device] = None, fused_params: Optional[Dict[str, Any]] = None, feature_processor=None) -> BaseEmbeddingLookup:
+        from torchrec_b200.distributed.embedding_lookup import GroupedEmbeddingsLookup
+
+        pg = getattr(self, "_pg", None)
+        if pg is None:
+            pg = self._env.process_group
+        return GroupedEmbeddingsLookup(grouped_configs=self._grouped_embedding_configs, pg=pg, device=device if device is not None else self._device)

@@ -1,53 +1,35 @@
-"""Table-wise sharding of unpooled (sequence) embeddings
-(cf. ``torchrec/distributed/sharding/tw_sequence_sharding.py``)."""
+"""Table-wise sharding of unpooled (sequence) embeddings: whole tables live on one rank; ids travel there by a key split and the
+rows come back by the sequence all-to-all (cf. ``torchrec/distributed/sharding/tw_sequence_sharding.py``)."""
 from __future__ import annotations
 
-from typing import Any, Dict, List, Optional
+from typing import Optional
 
 import torch
-import torch.distributed as dist
 
-from torchrec_b200.distributed.dist_data import SequenceEmbeddingsAllToAll
-from torchrec_b200.distributed.embedding_lookup import GroupedEmbeddingsLookup
-from torchrec_b200.distributed.embedding_sharding import BaseEmbeddingDist, BaseSparseFeaturesDist
-from torchrec_b200.distributed.embedding_types import BaseEmbeddingLookup
-from torchrec_b200.distributed.sharding.sequence_sharding import SequenceShardingContext
+from torchrec_b200.distributed.sharding.sequence_sharding import SequenceLookupMixin, SequenceRowsReturn, SequenceShardingContext
 from torchrec_b200.distributed.sharding.tw_sharding import BaseTwEmbeddingSharding, TwSparseFeaturesDist
-from torchrec_b200.distributed.types import Awaitable, CommOp, QuantizedCommCodecs, ShardingType
+from torchrec_b200.distributed.types import ShardingType
 from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
 
 
-class TwSequenceEmbeddingDist(BaseEmbeddingDist[SequenceShardingContext, torch.Tensor, torch.Tensor]):
-    """Rows ``[sum L, D]`` go back to the ranks that sent the ids, along the recorded ``values`` splits."""
+class TwSequenceEmbeddingDist(SequenceRowsReturn):
+    """The rows' way back for table-wise (and column-wise) shards: no bucketization to undo."""
 
-    def __init__(self, pg: dist.ProcessGroup, features_per_rank: List[int], device: Optional[torch.device] = None,
-                 qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None) -> None:
-        super().__init__()
-        self._dist = SequenceEmbeddingsAllToAll(
-            pg, features_per_rank, device,
-            codecs=qcomm_codecs_registry.get(CommOp.SEQUENCE_EMBEDDINGS_ALL_TO_ALL.name, None) if qcomm_codecs_registry else None,
-        )
-
-    def forward(self, local_embs: torch.Tensor, sharding_ctx: Optional[SequenceShardingContext] = None) -> Awaitable[torch.Tensor]:
-        assert sharding_ctx is not None
-        return self._dist(
-            local_embs, lengths=sharding_ctx.lengths_after_input_dist, input_splits=sharding_ctx.input_splits,
-            output_splits=sharding_ctx.output_splits, batch_size_per_rank=sharding_ctx.batch_size_per_rank,
-            sparse_features_recat=sharding_ctx.sparse_features_recat, unbucketize_permute_tensor=None,
-        )
+    def __init__(self, pg, features_per_rank, device=None, qcomm_codecs_registry=None) -> None:
+        super().__init__(pg, features_per_rank, device, qcomm_codecs_registry, restore_order=False)
 
 
-class TwSequenceEmbeddingSharding(BaseTwEmbeddingSharding[SequenceShardingContext, KeyedJaggedTensor, torch.Tensor, torch.Tensor]):
-    sharding_type = ShardingType.TABLE_WISE
+class _KeySplitSequenceRouting(SequenceLookupMixin):
+    """Ids are routed by feature (every rank receives the features of the tables it holds)."""
 
-    def create_input_dist(self, device: Optional[torch.device] = None) -> BaseSparseFeaturesDist[KeyedJaggedTensor]:
+    def create_input_dist(self, device: Optional[torch.device] = None) -> TwSparseFeaturesDist:
         assert self._pg is not None
         return TwSparseFeaturesDist(self._pg, self.features_per_rank())
 
-    def create_lookup(self, device: Optional[torch.device] = None, fused_params: Optional[Dict[str, Any]] = None, feature_processor=None) -> BaseEmbeddingLookup:
-        assert feature_processor is None
-        return GroupedEmbeddingsLookup(grouped_configs=self._grouped_embedding_configs, pg=self._pg, device=device if device is not None else self._device)
-
-    def create_output_dist(self, device: Optional[torch.device] = None) -> BaseEmbeddingDist[SequenceShardingContext, torch.Tensor, torch.Tensor]:
+    def create_output_dist(self, device: Optional[torch.device] = None) -> TwSequenceEmbeddingDist:
         assert self._pg is not None
-        return TwSequenceEmbeddingDist(self._pg, self.features_per_rank(), device if device is not None else self._device, qcomm_codecs_registry=self.qcomm_codecs_registry)
+        return TwSequenceEmbeddingDist(self._pg, self.features_per_rank(), device if device is not None else self._device, self.qcomm_codecs_registry)
+
+
+class TwSequenceEmbeddingSharding(_KeySplitSequenceRouting, BaseTwEmbeddingSharding[SequenceShardingContext, KeyedJaggedTensor, torch.Tensor, torch.Tensor]):
+    sharding_type = ShardingType.TABLE_WISE

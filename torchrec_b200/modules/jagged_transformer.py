@@ -8,7 +8,7 @@ padding position is ever computed.
 * ``dropout + residual add + layer norm`` is one kernel, ``gelu + dropout`` another (``ops.transformer_ops``), with masks recomputed in
   the backward instead of stored;
 * attention runs on the packed tokens too: one CTA per (sequence, head) with the sequence's K and V in shared memory
-  (``ops.transformer_ops.packed_attention``, head dimension 64, sequences up to 384 tokens).  Other shapes pad q, k, v for one
+  (``ops.transformer_ops.packed_attention``, head dimension 64, sequences up to 768 tokens).  Other shapes pad q, k, v for one
   library attention call with the padded keys masked (``ATTENTION_MODE = "padded"``; ``"nested"`` selects the library's
   variable-length kernel where the build has one).
 
@@ -72,7 +72,7 @@ def varlen_attention(qkv: torch.Tensor, offsets: torch.Tensor, num_heads: int, m
     """Self-attention inside every sequence of the packed ``qkv [T, 3 * D]``; returns ``[T, D]``.
 
     ``ATTENTION_MODE = "kernel"`` (default) runs this package's packed-attention kernel where the shape allows (bf16, head
-    dimension 64, ``max_len <= 384``; cost ``sum(len^2)``) and the padded form elsewhere.  ``"padded"`` is one library attention
+    dimension 64, ``max_len <= 768``; cost ``sum(len^2)``) and the padded form elsewhere.  ``"padded"`` is one library attention
     call over ``[B, H, max_len, Dh]`` with the padded keys masked.  ``"nested"`` hands the packed layout to the library's
     variable-length attention through a jagged nested tensor; where the build has no variable-length kernel for the device that
     silently decomposes into one small attention per sequence.  Everything outside the attention stays packed in every mode."""

@@ -108,7 +108,7 @@ def gelu_dropout(z: torch.Tensor, p: float = 0.0, training: bool = True) -> torc
 # attention over packed sequences
 # --------------------------------------------------------------------------------------
 ATTENTION_HEAD_DIM = 64     # the kernel's head dimension
-ATTENTION_MAX_LEN = 384     # longest sequence whose q, k, v and dO fit in one CTA's shared memory in the backward
+ATTENTION_MAX_LEN = 768     # longest sequence whose K and V (or Q and dO) fit in one CTA's shared memory
 _attn_err: dict = {}
 
 
