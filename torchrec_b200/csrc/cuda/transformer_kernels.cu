@@ -223,11 +223,26 @@ __global__ void __launch_bounds__(256) ln_residual_bwd_kernel(const __nv_bfloat1
   }
 }
 
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+// Phi(x) = 0.5 (1 + erf(x / sqrt 2)) and e = exp(-x^2 / 2) from one exponential: erfc by the rational approximation 7.1.26 of
+// Abramowitz & Stegun (absolute error below 1.5e-7, far under the bf16 output's resolution); about a third of the
+// instructions of the library's erff, which made these kernels instruction-bound.
+__device__ __forceinline__ void gelu_parts(float x, float& cdf, float& e) {
+  const float ax = fabsf(x) * 0.70710678118654752f;
+  const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.f));
+  e = exp2f(-0.72134752044448170f * x * x);
+  const float poly = fmaf(fmaf(fmaf(fmaf(1.061405429f, t, -1.453152027f), t, 1.421413741f), t, -0.284496736f), t, 0.254829592f) * t;
+  const float half_erfc = 0.5f * poly * e;
+  cdf = x >= 0.f ? 1.f - half_erfc : half_erfc;
+}
+__device__ __forceinline__ float gelu_f(float x) {
+  float cdf, e;
+  gelu_parts(x, cdf, e);
+  return x * cdf;
+}
 __device__ __forceinline__ float gelu_grad_f(float x) {
-  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+  float cdf, e;
+  gelu_parts(x, cdf, e);
+  return fmaf(x * 0.3989422804014327f, e, cdf);
 }
 
 template <bool kBackward>
@@ -242,10 +257,10 @@ __global__ void __launch_bounds__(256) gelu_dropout_kernel(const __nv_bfloat16* 
     float g[8];
     load8(dh + i * 8, g);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) o[k] = fk[k] != 0.f ? g[k] * fk[k] * gelu_grad_f(zv[k]) : 0.f;
+    for (int k = 0; k < 8; ++k) o[k] = g[k] * fk[k] * gelu_grad_f(zv[k]);
   } else {
 #pragma unroll
-    for (int k = 0; k < 8; ++k) o[k] = fk[k] != 0.f ? gelu_f(zv[k]) * fk[k] : 0.f;
+    for (int k = 0; k < 8; ++k) o[k] = gelu_f(zv[k]) * fk[k];
   }
   store8(out + i * 8, o);
 }

@@ -239,10 +239,48 @@ def bench_engine(B: int, n: int, warm: int) -> None:
         e.peer.check_error()
 
 
+def bench_transformer(B: int, n: int, warm: int) -> None:
+    """Packed attention (forward, backward), the fused layer-norm / GELU kernels and the sampled-softmax cross entropy on BERT4Rec
+    shapes: ``B`` sequences with lengths uniform in [20, 200], 4 heads of 64, hidden 256, feed-forward 1024, 8192 negatives."""
+    from torchrec_b200.ops import transformer_ops as tops
+
+    ops = torch.ops.trb200
+    gen = torch.Generator().manual_seed(0)
+    lengths = torch.randint(20, 201, (B,), generator=gen)
+    offsets = torch.cat([torch.zeros(1, dtype=torch.long), lengths.cumsum(0)]).cuda()
+    T, H, D = int(lengths.sum()), 4, 256
+    pair_flops = 2.0 * float((lengths.double() ** 2).sum()) * 64 * H  # one [len, 64] x [64, len] product per head
+    qkv = torch.randn(T, 3 * D, device="cuda").bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for p in (0.0, 0.1):
+        t = timeit(lambda: ops.varlen_attn_fwd(qkv, offsets, H, 200, p, 7, err), n, warm)
+        print(f"packed attention fwd p={p} T={T}: {t:.3f} ms, {2 * pair_flops / t / 1e9:.0f} TFLOP/s (2 products), {(qkv.numel() + T * D) * 2 / t / 1e6:.0f} GB/s", flush=True)
+        out, lse = ops.varlen_attn_fwd(qkv, offsets, H, 200, p, 7, err)
+        dout = torch.randn_like(out)
+        t = timeit(lambda: ops.varlen_attn_bwd(dout, qkv, out, lse, offsets, H, 200, p, 7, err), n, warm)
+        print(f"packed attention bwd p={p} T={T}: {t:.3f} ms, {7 * pair_flops / t / 1e9:.0f} TFLOP/s (7 products), {(2 * qkv.numel() + 2 * T * D) * 2 / t / 1e6:.0f} GB/s", flush=True)
+    a, r = (torch.randn(T, D, device="cuda").bfloat16() for _ in range(2))
+    w, b = torch.ones(D, device="cuda"), torch.zeros(D, device="cuda")
+    t = timeit(lambda: ops.ln_residual_fwd(a, r, w, b, 0.1, 7, 1e-5), n, warm)
+    print(f"dropout + residual + layer norm fwd [{T}, {D}]: {t:.3f} ms, {4 * T * D * 2 / t / 1e6:.0f} GB/s", flush=True)
+    z = torch.randn(T, 4 * D, device="cuda").bfloat16()
+    t = timeit(lambda: ops.gelu_dropout_fwd(z, 0.1, 7), n, warm)
+    print(f"gelu + dropout fwd [{T}, {4 * D}]: {t:.3f} ms, {2 * z.numel() * 2 / t / 1e6:.0f} GB/s", flush=True)
+    dh = torch.randn_like(z)
+    t = timeit(lambda: ops.gelu_dropout_bwd(dh, z, 0.1, 7), n, warm)
+    print(f"gelu + dropout bwd [{T}, {4 * D}]: {t:.3f} ms, {3 * z.numel() * 2 / t / 1e6:.0f} GB/s", flush=True)
+    P, N = max(8, int(0.15 * T) // 8 * 8), 8192
+    scores = torch.randn(P, N, device="cuda").bfloat16()
+    pos = torch.randn(P, device="cuda")
+    t = timeit(lambda: ops.sampled_ce_fwd_bwd(pos, scores, 1.0 / P), n, warm)
+    print(f"sampled-softmax cross entropy + gradient [{P}, {N}]: {t:.3f} ms, {2 * scores.numel() * 2 / t / 1e6:.0f} GB/s", flush=True)
+    assert tops.attention_error(qkv.device) == 0 and int(err.item()) == 0
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", default="all", choices=["all", "gemm_nt", "gemm_tn", "gemm_cross", "tbe", "tbe_fwd", "tbe_sort", "tbe_bwd",
-                                                       "tbe_uniform", "qtbe", "dense_small", "sparse", "engine"])
+                                                       "tbe_uniform", "qtbe", "dense_small", "sparse", "engine", "transformer"])
     ap.add_argument("--shape", type=str, default="", help="N,K: run the GEMM benchmarks on this one shape only (profiler captures)")
     ap.add_argument("--small", action="store_true", help="profiler-sized case: few launches, a few GB on the device")
     ap.add_argument("--quick", action="store_true", help="full-size operands (larger than L2) but one warm-up and two timed launches per kernel: what a profiler capture runs")
@@ -274,6 +312,8 @@ def main() -> None:
         bench_sparse_kernels(M, n, warm)
     if args.op in ("all", "engine"):
         bench_engine(M // 4, n, warm)
+    if args.op in ("all", "transformer"):
+        bench_transformer(512 if args.small else 4096, n, warm)
     print("gemm status", int(torch.ops.trb200.gemm_error_status()), flush=True)
 
 

@@ -17,7 +17,7 @@ from torchrec_b200.distributed.embedding_sharding import (
 )
 from torchrec_b200.distributed.embedding_types import BaseEmbeddingLookup, ShardedEmbeddingTable
 from torchrec_b200.distributed.sharding.common import C, F, T, W, global_metadata_of, make_sharded_table
-from torchrec_b200.distributed.sharding.tw_sharding import BaseTwEmbeddingSharding, TwPooledEmbeddingDist, TwSparseFeaturesDist
+from torchrec_b200.distributed.sharding.tw_sharding import BaseTwEmbeddingSharding, _KeySplitPooledRouting
 from torchrec_b200.distributed.types import QuantizedCommCodecs, ShardingEnv, ShardingType, ShardMetadata
 from torchrec_b200.ops import sparse_ops as sops
 from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
@@ -72,17 +72,10 @@ class BaseCwEmbeddingSharding(BaseTwEmbeddingSharding[C, F, T, W]):
         self._combined_embedding_names = combined_names
         self._combined_embedding_dims = combined_dims
 
-    def _shard(self, sharding_infos: List[EmbeddingShardingInfo]) -> List[List[ShardedEmbeddingTable]]:
-        tables_per_rank: List[List[ShardedEmbeddingTable]] = [[] for _ in range(self._world_size)]
-        for info in sharding_infos:
-            shards: List[ShardMetadata] = info.param_sharding.sharding_spec.shards
-            gm = global_metadata_of(info)
-            cfg = info.embedding_config
-            rows = cfg.num_embeddings_post_pruning if cfg.num_embeddings_post_pruning is not None else cfg.num_embeddings
-            for i, rank in enumerate(info.param_sharding.ranks):
-                rank = self._remap(rank, ShardingType.COLUMN_WISE)
-                tables_per_rank[rank].append(make_sharded_table(info, shards[i], gm, rows, shards[i].shard_sizes[1]))
-        return tables_per_rank
+    def _placements(self, info: EmbeddingShardingInfo):
+        """One placement per column block of the table."""
+        for rank, shard in zip(info.param_sharding.ranks, info.param_sharding.sharding_spec.shards):
+            yield rank, shard, shard.shard_sizes[1]
 
     def embedding_dims(self) -> List[int]:
         return self._combined_embedding_dims if self._permute_embeddings else self.uncombined_embedding_dims()
@@ -97,27 +90,12 @@ class BaseCwEmbeddingSharding(BaseTwEmbeddingSharding[C, F, T, W]):
         return super().embedding_names()
 
 
-class CwPooledEmbeddingSharding(BaseCwEmbeddingSharding[EmbeddingShardingContext, KeyedJaggedTensor, torch.Tensor, torch.Tensor]):
+class CwPooledEmbeddingSharding(_KeySplitPooledRouting, BaseCwEmbeddingSharding[EmbeddingShardingContext, KeyedJaggedTensor, torch.Tensor, torch.Tensor]):
     sharding_type = ShardingType.COLUMN_WISE
 
-    def create_input_dist(self, device: Optional[torch.device] = None) -> BaseSparseFeaturesDist[KeyedJaggedTensor]:
-        assert self._pg is not None
-        return TwSparseFeaturesDist(self._pg, self.features_per_rank())
-
-    def create_lookup(self, device: Optional[torch.device] = None, fused_params: Optional[Dict[str, Any]] = None, feature_processor=None) -> BaseEmbeddingLookup:
-        return GroupedPooledEmbeddingsLookup(
-            grouped_configs=self._grouped_embedding_configs, pg=self._pg, device=device if device is not None else self._device,
-            feature_processor=feature_processor, sharding_type=ShardingType.COLUMN_WISE,
-        )
-
-    def create_output_dist(self, device: Optional[torch.device] = None) -> BaseEmbeddingDist[EmbeddingShardingContext, torch.Tensor, torch.Tensor]:
-        device = device if device is not None else self._device
-        callbacks: Optional[List[Callable[[torch.Tensor], torch.Tensor]]] = None
-        if self._permute_embeddings and self._embedding_order != list(range(len(self._embedding_order))):
-            assert len(self._embedding_order) == len(self._embedding_dims)
-            callbacks = [PermutePooledEmbeddingsSplit(self._embedding_dims, self._embedding_order, device=device)]
-        assert self._pg is not None
-        return TwPooledEmbeddingDist(
-            pg=self._pg, dim_sum_per_rank=self._dim_sum_per_rank(), emb_dim_per_rank_per_feature=self._emb_dim_per_rank_per_feature(),
-            device=device, callbacks=callbacks, qcomm_codecs_registry=self.qcomm_codecs_registry,
-        )
+    def _output_callbacks(self, device: Optional[torch.device]) -> Optional[List[Callable[[torch.Tensor], torch.Tensor]]]:
+        """Put the column blocks of every table next to each other again when they arrive out of order."""
+        if not self._permute_embeddings or self._embedding_order == list(range(len(self._embedding_order))):
+            return None
+        assert len(self._embedding_order) == len(self._embedding_dims)
+        return [PermutePooledEmbeddingsSplit(self._embedding_dims, self._embedding_order, device=device)]

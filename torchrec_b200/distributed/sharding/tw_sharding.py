@@ -32,18 +32,28 @@ from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
 
 
 class BaseTwEmbeddingSharding(BaseSharding[C, F, T, W]):
+    """Whole-table placement; the column-wise shardings reuse everything and only say where the column blocks go."""
+
+    _shard_type = ShardingType.TABLE_WISE
+
+    def _placements(self, info: EmbeddingShardingInfo):
+        """``(rank, shard metadata, columns)`` of every shard of one table: here the table itself."""
+        yield info.param_sharding.ranks[0], info.param_sharding.sharding_spec.shards[0], info.embedding_config.embedding_dim
+
     def _shard(self, sharding_infos: List[EmbeddingShardingInfo]) -> List[List[ShardedEmbeddingTable]]:
-        tables_per_rank: List[List[ShardedEmbeddingTable]] = [[] for _ in range(self._world_size)]
+        per_rank: List[List[ShardedEmbeddingTable]] = [[] for _ in range(self._world_size)]
         for info in sharding_infos:
-            shards = info.param_sharding.sharding_spec.shards
             cfg = info.embedding_config
-            rows = cfg.num_embeddings_post_pruning if cfg.num_embeddings_post_pruning is not None else cfg.num_embeddings
-            rank = self._remap(info.param_sharding.ranks[0], ShardingType.TABLE_WISE)
-            tables_per_rank[rank].append(make_sharded_table(info, shards[0], global_metadata_of(info), rows, cfg.embedding_dim))
-        return tables_per_rank
+            rows = cfg.num_embeddings if cfg.num_embeddings_post_pruning is None else cfg.num_embeddings_post_pruning
+            whole = global_metadata_of(info)
+            for rank, shard, cols in self._placements(info):
+                per_rank[self._remap(rank, self._shard_type)].append(make_sharded_table(info, shard, whole, rows, cols))
+        return per_rank
 
 
 class TwSparseFeaturesDist(BaseSparseFeaturesDist[KeyedJaggedTensor]):
+    """Ids travel by feature: rank r receives, for the whole global batch, the features of the tables it holds."""
+
     def __init__(self, pg: dist.ProcessGroup, features_per_rank: List[int]) -> None:
         super().__init__()
         self._dist = KJTAllToAll(pg=pg, splits=features_per_rank)
@@ -53,61 +63,57 @@ class TwSparseFeaturesDist(BaseSparseFeaturesDist[KeyedJaggedTensor]):
 
 
 class TwPooledEmbeddingDist(BaseEmbeddingDist[EmbeddingShardingContext, torch.Tensor, torch.Tensor]):
+    """Pooled rows ``[B_global, D_local]`` to ``[B_local, sum D]``.  The exchange module is built on first use: the fixed-batch
+    all-to-all, or the variable-batch one when the first context says that features differ in batch size."""
+
     def __init__(self, pg: dist.ProcessGroup, dim_sum_per_rank: List[int], emb_dim_per_rank_per_feature: List[List[int]],
                  device: Optional[torch.device] = None, callbacks: Optional[List[Callable[[torch.Tensor], torch.Tensor]]] = None,
                  qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None) -> None:
         super().__init__()
-        self._pg = pg
-        self._dim_sum_per_rank = dim_sum_per_rank
-        self._device = device
-        self._callbacks = callbacks
-        self._codecs = qcomm_codecs_registry.get(CommOp.POOLED_EMBEDDINGS_ALL_TO_ALL.name, None) if qcomm_codecs_registry else None
-        self._emb_dim_per_rank_per_feature = emb_dim_per_rank_per_feature
+        codecs = (qcomm_codecs_registry or {}).get(CommOp.POOLED_EMBEDDINGS_ALL_TO_ALL.name)
+        self._build_fixed = lambda: PooledEmbeddingsAllToAll(pg=pg, dim_sum_per_rank=dim_sum_per_rank, device=device, callbacks=callbacks, codecs=codecs)
+        self._build_variable = lambda: VariableBatchPooledEmbeddingsAllToAll(pg=pg, emb_dim_per_rank_per_feature=emb_dim_per_rank_per_feature,
+                                                                             device=device, codecs=codecs)
         self._dist: Optional[PooledEmbeddingsAllToAll] = None
         self._variable_dist: Optional[VariableBatchPooledEmbeddingsAllToAll] = None
 
     def forward(self, local_embs: torch.Tensor, sharding_ctx: Optional[EmbeddingShardingContext] = None) -> Awaitable[torch.Tensor]:
+        if sharding_ctx is not None and sharding_ctx.variable_batch_per_feature:
+            if self._variable_dist is None:
+                self._variable_dist = self._build_variable()
+            return self._variable_dist(local_embs, batch_size_per_rank_per_feature=sharding_ctx.batch_size_per_rank_per_feature,
+                                       batch_size_per_feature_pre_a2a=sharding_ctx.batch_size_per_feature_pre_a2a)
         if self._dist is None:
-            self._create_output_dist_module(sharding_ctx)
+            self._dist = self._build_fixed()
         if sharding_ctx is None:
             return self._dist(local_embs)
-        if sharding_ctx.variable_batch_per_feature:
-            return self._variable_dist(
-                local_embs, batch_size_per_rank_per_feature=sharding_ctx.batch_size_per_rank_per_feature,
-                batch_size_per_feature_pre_a2a=sharding_ctx.batch_size_per_feature_pre_a2a,
-            )
         return self._dist(local_embs, batch_size_per_rank=sharding_ctx.batch_size_per_rank or None)
 
-    def _create_output_dist_module(self, sharding_ctx: Optional[EmbeddingShardingContext] = None) -> None:
-        if sharding_ctx is not None and sharding_ctx.variable_batch_per_feature:
-            self._variable_dist = VariableBatchPooledEmbeddingsAllToAll(
-                pg=self._pg, emb_dim_per_rank_per_feature=self._emb_dim_per_rank_per_feature, device=self._device, codecs=self._codecs,
-            )
-        self._dist = PooledEmbeddingsAllToAll(
-            pg=self._pg, dim_sum_per_rank=self._dim_sum_per_rank, device=self._device, callbacks=self._callbacks, codecs=self._codecs,
-        )
 
+class _KeySplitPooledRouting:
+    """Input distribution, lookup and output distribution of the pooled shardings that route ids by feature (table-wise and the
+    column-wise family); ``_output_callbacks`` lets a sharding post-process the exchanged rows."""
 
-class TwPooledEmbeddingSharding(BaseTwEmbeddingSharding[EmbeddingShardingContext, KeyedJaggedTensor, torch.Tensor, torch.Tensor]):
-    sharding_type = ShardingType.TABLE_WISE
+    def _output_callbacks(self, device: Optional[torch.device]) -> Optional[List[Callable[[torch.Tensor], torch.Tensor]]]:
+        return None
 
-    def create_input_dist(self, device: Optional[torch.device] = None) -> BaseSparseFeaturesDist[KeyedJaggedTensor]:
+    def create_input_dist(self, device: Optional[torch.device] = None) -> TwSparseFeaturesDist:
         assert self._pg is not None
         return TwSparseFeaturesDist(self._pg, self.features_per_rank())
 
     def create_lookup(self, device: Optional[torch.device] = None, fused_params: Optional[Dict[str, Any]] = None, feature_processor=None) -> BaseEmbeddingLookup:
-        lookup = GroupedPooledEmbeddingsLookup(
-            grouped_configs=self._grouped_embedding_configs, pg=self._pg, device=device if device is not None else self._device,
-            feature_processor=feature_processor, sharding_type=ShardingType.TABLE_WISE,
-        )
-        return lookup
+        return GroupedPooledEmbeddingsLookup(grouped_configs=self._grouped_embedding_configs, pg=self._pg, device=device if device is not None else self._device,
+                                             feature_processor=feature_processor, sharding_type=self._shard_type)
 
-    def create_output_dist(self, device: Optional[torch.device] = None) -> BaseEmbeddingDist[EmbeddingShardingContext, torch.Tensor, torch.Tensor]:
+    def create_output_dist(self, device: Optional[torch.device] = None) -> TwPooledEmbeddingDist:
         assert self._pg is not None
-        return TwPooledEmbeddingDist(
-            pg=self._pg, dim_sum_per_rank=self._dim_sum_per_rank(), emb_dim_per_rank_per_feature=self._emb_dim_per_rank_per_feature(),
-            device=device if device is not None else self._device, qcomm_codecs_registry=self.qcomm_codecs_registry,
-        )
+        device = device if device is not None else self._device
+        return TwPooledEmbeddingDist(pg=self._pg, dim_sum_per_rank=self._dim_sum_per_rank(), emb_dim_per_rank_per_feature=self._emb_dim_per_rank_per_feature(),
+                                     device=device, callbacks=self._output_callbacks(device), qcomm_codecs_registry=self.qcomm_codecs_registry)
+
+
+class TwPooledEmbeddingSharding(_KeySplitPooledRouting, BaseTwEmbeddingSharding[EmbeddingShardingContext, KeyedJaggedTensor, torch.Tensor, torch.Tensor]):
+    sharding_type = ShardingType.TABLE_WISE
 
 
 # ---- inference (one process, all devices) ------------------------------------------------------------
