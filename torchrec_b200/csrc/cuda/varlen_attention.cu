@@ -129,7 +129,7 @@ __device__ __forceinline__ void attn_stage(const __nv_bfloat16* src, int64_t ld,
 }
 
 template <int DH, int WARPS>
-__global__ void __launch_bounds__(32 * WARPS) varlen_attn_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int64_t* __restrict__ offsets,
+__global__ void __launch_bounds__(32 * WARPS, 3) varlen_attn_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int64_t* __restrict__ offsets,
                                                                     __nv_bfloat16* __restrict__ out, float* __restrict__ lse2, int H, int n_cap, int np_cap,
                                                                     float scale_log2, AttnDrop drop, int* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char attn_smem[];
@@ -475,8 +475,9 @@ static AttnDrop make_attn_drop(double p, int64_t seed) {
 }
 
 constexpr int kAttnDH = 64;
-constexpr int kAttnFwdWarps = 4;
-constexpr int kAttnBwdWarps = 4;
+constexpr int kAttnFwdWarps = 8;
+constexpr int kAttnBwdWarps = 4;  // dK / dV kernel
+constexpr int kAttnBwdQWarps = 4;
 
 static void attn_check(const at::Tensor& qkv, const at::Tensor& offsets, int64_t H, int64_t max_len) {
   TORCH_CHECK(qkv.is_cuda() && qkv.scalar_type() == at::kBFloat16 && qkv.dim() == 2 && qkv.is_contiguous(), "qkv must be a contiguous bf16 CUDA matrix");
@@ -523,7 +524,7 @@ at::Tensor varlen_attn_bwd(const at::Tensor& dout, const at::Tensor& qkv, const 
   const size_t rows_bytes = size_t(2) * np_cap * (kAttnDH + kAttnPad) * sizeof(__nv_bfloat16);
   const size_t smem_kv = rows_bytes + size_t(2) * np_cap * sizeof(float);
   auto kern_kv = varlen_attn_bwd_kv_kernel<kAttnDH, kAttnBwdWarps>;
-  auto kern_q = varlen_attn_bwd_q_kernel<kAttnDH, kAttnBwdWarps>;
+  auto kern_q = varlen_attn_bwd_q_kernel<kAttnDH, kAttnBwdQWarps>;
   TRB_CUDA_CHECK(cudaFuncSetAttribute(kern_kv, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_kv)));
   TRB_CUDA_CHECK(cudaFuncSetAttribute(kern_q, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rows_bytes)));
   const float scale = float(1.0 / std::sqrt(double(kAttnDH)));
@@ -536,7 +537,7 @@ at::Tensor varlen_attn_bwd(const at::Tensor& dout, const at::Tensor& qkv, const 
   kern_kv<<<unsigned(B * H), 32 * kAttnBwdWarps, smem_kv, stream>>>(qp, op, gp, lse.data_ptr<float>(), offsets.data_ptr<int64_t>(), dp, int(H), int(max_len), np_cap,
                                                                    scale, scale * 1.4426950408889634f, drop, err.data_ptr<int>());
   TRB_CUDA_CHECK(cudaGetLastError());
-  kern_q<<<unsigned(B * H), 32 * kAttnBwdWarps, rows_bytes, stream>>>(qp, op, gp, lse.data_ptr<float>(), offsets.data_ptr<int64_t>(), dp, int(H), int(max_len), np_cap,
+  kern_q<<<unsigned(B * H), 32 * kAttnBwdQWarps, rows_bytes, stream>>>(qp, op, gp, lse.data_ptr<float>(), offsets.data_ptr<int64_t>(), dp, int(H), int(max_len), np_cap,
                                                                      scale, scale * 1.4426950408889634f, drop);
   TRB_CUDA_CHECK(cudaGetLastError());
   return dqkv;

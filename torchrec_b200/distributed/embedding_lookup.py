@@ -235,3 +235,14 @@ def fused_optimizer_of_lookups(lookups: List[nn.Module]) -> KeyedOptimizer:
             if isinstance(m, FusedOptimizerModule):
                 optims.append(m.fused_optimizer)
     return CombinedOptimizer(optims)
+
+
+def __getattr__(name: str):
+    """The inference lookups live in ``infer_embedding_lookup`` (they pull in the quantized kernels); they are reachable from here
+    under the reference's import path."""
+    if name in ("MetaInferGroupedEmbeddingsLookup", "MetaInferGroupedPooledEmbeddingsLookup", "InferGroupedEmbeddingsLookup",
+                "InferGroupedPooledEmbeddingsLookup", "InferCPUGroupedEmbeddingsLookup"):
+        from torchrec_b200.distributed import infer_embedding_lookup
+
+        return getattr(infer_embedding_lookup, name)
+    raise AttributeError(name)
