@@ -153,3 +153,39 @@ def test_itep_unsharded_prunes_and_remaps():
     before = itep.row_util.clone()
     m(batch([9, 5]))
     assert torch.equal(before, itep.row_util)
+
+
+def test_mpzch_opt_in_admission_and_reserved_rows():
+    """With opt-in admission no id claims a reserved slot, an id that was not admitted shares a reserved row of its bucket, an
+    admitted id keeps its own slot afterwards, and about ``opt_in_prob`` percent of new ids are admitted per occurrence."""
+    import torch
+
+    from torchrec_b200.modules.hash_mc_modules import HashZchManagedCollisionModule
+    from torchrec_b200.sparse.jagged_tensor import JaggedTensor
+
+    torch.manual_seed(0)
+    mc = HashZchManagedCollisionModule(zch_size=4000, device=torch.device("cpu"), total_num_buckets=4, max_probe=64, opt_in_prob=30, percent_reserved_slots=10)
+    assert mc.get_reserved_slots_per_bucket() == 100
+    mc.train()
+    ids = torch.arange(1, 1001) * 7919
+    out = mc.remap({"f": JaggedTensor(values=ids, lengths=torch.ones(1000, dtype=torch.long))})["f"].values()
+    ident = mc._hash_zch_identities.data.view(-1)
+    in_bucket = out % 1000
+    claimed = ident[out] == ids
+    assert (in_bucket[claimed] < 900).all() and (in_bucket[~claimed] >= 900).all()
+    assert (ident.view(4, 1000)[:, 900:] == -1).all()  # nobody owns a reserved slot
+    assert 0.2 < claimed.float().mean().item() < 0.4
+    # evaluation: admitted ids find their slot, the others land on the same reserved row as before
+    mc.eval()
+    again = mc.remap({"f": JaggedTensor(values=ids, lengths=torch.ones(1000, dtype=torch.long))})["f"].values()
+    assert torch.equal(again, out)
+    # every further training pass admits more of the remaining ids
+    mc.train()
+    for _ in range(10):
+        out = mc.remap({"f": JaggedTensor(values=ids, lengths=torch.ones(1000, dtype=torch.long))})["f"].values()
+    assert (ident[out] == ids).float().mean().item() > 0.9
+    # sampling off: everything is admitted and nothing is reserved
+    plain = HashZchManagedCollisionModule(zch_size=4000, device=torch.device("cpu"), total_num_buckets=4, max_probe=64)
+    plain.train()
+    o2 = plain.remap({"f": JaggedTensor(values=ids, lengths=torch.ones(1000, dtype=torch.long))})["f"].values()
+    assert (plain._hash_zch_identities.data.view(-1)[o2] == ids).all() and plain.get_reserved_slots_per_bucket() == -1

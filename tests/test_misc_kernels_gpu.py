@@ -161,3 +161,29 @@ def test_dot_interaction_matches_torch(dtype, F, D):
     want.backward(g.float())
     torch.testing.assert_close(dense.grad.float(), d32.grad, rtol=tol, atol=tol * float(d32.grad.abs().max()))
     torch.testing.assert_close(sparse.grad.float(), s32.grad, rtol=tol, atol=tol * float(s32.grad.abs().max()))
+
+
+def test_zch_reserved_slots_and_admission_on_the_device():
+    """Opt-in admission on CUDA: claimed slots lie in front of the reserved block of their bucket, ids that were not admitted share a
+    reserved row, and the read-only pass reproduces the mapping."""
+    from torchrec_b200.ops import sparse_ops as sops
+
+    torch.manual_seed(0)
+    S, buckets, reserved = 8192, 8, 64
+    ident = torch.full((S,), -1, dtype=torch.int64, device="cuda")
+    seg = torch.arange(0, S + 1, S // buckets, device="cuda")
+    ids = (torch.arange(1, 3001, device="cuda") * 104729)
+    admit = torch.rand(3000, device="cuda") < 0.5
+    slots, _ = sops.zch_probe(ids, ident, None, seg, max_probe=64, reserved_slots=reserved, admit=admit)
+    claimed = ident[slots] == ids
+    pos = slots % (S // buckets)
+    assert (pos[claimed] < S // buckets - reserved).all() and (pos[~claimed] >= S // buckets - reserved).all()
+    assert torch.equal(claimed, admit)  # the table has room for every admitted id
+    assert (ident.view(buckets, -1)[:, -reserved:] == -1).all()
+    again, _ = sops.zch_probe(ids, ident, None, seg, max_probe=64, readonly=True, reserved_slots=reserved)
+    assert torch.equal(again, slots)
+    # the host implementation takes the same decisions
+    ident_cpu = torch.full((S,), -1, dtype=torch.int64)
+    slots_cpu, _ = sops.zch_probe(ids.cpu(), ident_cpu, None, seg.cpu(), max_probe=64, reserved_slots=reserved, admit=admit.cpu())
+    assert torch.equal((ident_cpu[slots_cpu] == ids.cpu()), claimed.cpu())
+    assert torch.equal(slots_cpu[~claimed.cpu()], slots.cpu()[~claimed.cpu()])  # shared rows are a pure function of the id

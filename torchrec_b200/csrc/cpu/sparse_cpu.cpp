@@ -182,7 +182,8 @@ at::Tensor jagged_to_padded_dense(const at::Tensor& values, const at::Tensor& of
 // ---- multi-probe zero-collision hash, sequential (the device kernels document the algorithm) -------
 std::tuple<at::Tensor, at::Tensor> zch_probe(const at::Tensor& ids, at::Tensor identities, c10::optional<at::Tensor> metadata, const at::Tensor& segments,
                                              int64_t input_hash_size, int64_t out_offset, int64_t max_probe, bool readonly, bool disable_fallback,
-                                             const c10::optional<at::Tensor>& input_metadata, int64_t eviction_threshold, int64_t eviction_policy) {
+                                             const c10::optional<at::Tensor>& input_metadata, int64_t eviction_threshold, int64_t eviction_policy,
+                                             int64_t reserved_slots) {
   TORCH_CHECK(ids.scalar_type() == at::kLong && identities.scalar_type() == at::kLong && identities.is_contiguous() && segments.scalar_type() == at::kLong);
   at::Tensor ids_c = ids.contiguous(), seg_c = segments.contiguous();
   const int64_t N = ids_c.numel(), S = identities.numel(), nb = seg_c.numel() - 1;
@@ -203,6 +204,7 @@ std::tuple<at::Tensor, at::Tensor> zch_probe(const at::Tensor& ids, at::Tensor i
     const int64_t hi = seg[b + 1] - out_offset;
     if (lo < 0 || hi > S || hi <= lo) return false;
     size = hi - lo;
+    if (reserved_slots > 0 && reserved_slots < size) size -= reserved_slots;  // the reserved block at the end of the bucket is never probed
     start = int64_t(trb::zch_mix(uint64_t(v)) % uint64_t(size));
     return true;
   };
@@ -239,7 +241,9 @@ std::tuple<at::Tensor, at::Tensor> zch_probe(const at::Tensor& ids, at::Tensor i
   if (!disable_fallback)
     for (int64_t i = 0; i < N; ++i) {
       int64_t lo, size, start;
-      if (so[i] < 0 && range(id[i], lo, size, start)) so[i] = lo + start;
+      if (so[i] >= 0 || !range(id[i], lo, size, start)) continue;
+      const int64_t bucket = seg[trb::zch_bucket(id[i], input_hash_size, nb) + 1] - out_offset - lo;
+      so[i] = (reserved_slots > 0 && reserved_slots < bucket) ? lo + size + int64_t(trb::zch_mix(uint64_t(id[i])) % uint64_t(reserved_slots)) : lo + start;
     }
   return {slots, evicted};
 }
@@ -276,6 +280,6 @@ TORCH_LIBRARY(trb200_cpu, m) {
   m.def("block_bucketize(Tensor lengths, Tensor indices, bool bucketize_pos, bool sequence, Tensor block_sizes, int my_size, Tensor? weights, bool keep_orig_idx) -> (Tensor, Tensor, Tensor?, Tensor?, Tensor?)", &trb_cpu::block_bucketize);
   m.def("jagged_to_padded_dense(Tensor values, Tensor offsets, int max_length, float padding_value) -> Tensor", &trb_cpu::jagged_to_padded_dense);
   m.def("zch_probe(Tensor ids, Tensor(a!) identities, Tensor(b!)? metadata, Tensor segments, int input_hash_size, int out_offset, int max_probe, bool readonly, "
-        "bool disable_fallback, Tensor? input_metadata, int eviction_threshold, int eviction_policy) -> (Tensor, Tensor)", &trb_cpu::zch_probe);
+        "bool disable_fallback, Tensor? input_metadata, int eviction_threshold, int eviction_policy, int reserved_slots=0) -> (Tensor, Tensor)", &trb_cpu::zch_probe);
   m.def("itep_remap(Tensor values, Tensor feature_offsets, Tensor feature_buffer, Tensor address_lookup, Tensor(a!) row_util, Tensor buffer_offsets, bool update_util) -> Tensor", &trb_cpu::itep_remap);
 }

@@ -202,6 +202,7 @@ struct ZchArgs {
   int64_t* slots;             // out: local slot, -1 = none
   int64_t* evicted;           // out: local slot whose previous id was evicted by this entry, else -1
   int64_t N, S, num_buckets, input_hash_size, out_offset;
+  int64_t reserved;           // slots at the end of every bucket that are never claimed: the shared rows of ids that were not admitted
   int max_probe, policy, eviction_threshold;
   bool disable_fallback;
 };
@@ -212,6 +213,7 @@ __device__ __forceinline__ bool zch_range(const ZchArgs& a, int64_t id, int64_t&
   const int64_t hi = a.segments[b + 1] - a.out_offset;
   if (lo < 0 || hi > a.S || hi <= lo) return false;  // the bucket is not on this rank
   size = hi - lo;
+  if (a.reserved > 0 && a.reserved < size) size -= a.reserved;  // ids probe (and claim) only the part in front of the reserved block
   start = int64_t(zch_mix(uint64_t(id)) % uint64_t(size));
   return true;
 }
@@ -290,12 +292,16 @@ __global__ void __launch_bounds__(256) zch_fallback_kernel(ZchArgs a) {
   const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= a.N || a.slots[i] >= 0 || a.disable_fallback) return;
   int64_t lo, size, start;
-  if (zch_range(a, a.ids[i], lo, size, start)) a.slots[i] = lo + start;  // shares the row of whoever lives there
+  if (!zch_range(a, a.ids[i], lo, size, start)) return;
+  const int64_t bucket = a.segments[zch_bucket(a.ids[i], a.input_hash_size, a.num_buckets) + 1] - a.out_offset - lo;
+  if (a.reserved > 0 && a.reserved < bucket) a.slots[i] = lo + size + int64_t(zch_mix(uint64_t(a.ids[i])) % uint64_t(a.reserved));  // a reserved row
+  else a.slots[i] = lo + start;  // shares the row of whoever lives there
 }
 
 std::tuple<at::Tensor, at::Tensor> zch_probe(const at::Tensor& ids, at::Tensor identities, c10::optional<at::Tensor> metadata, const at::Tensor& segments,
                                              int64_t input_hash_size, int64_t out_offset, int64_t max_probe, bool readonly, bool disable_fallback,
-                                             const c10::optional<at::Tensor>& input_metadata, int64_t eviction_threshold, int64_t eviction_policy) {
+                                             const c10::optional<at::Tensor>& input_metadata, int64_t eviction_threshold, int64_t eviction_policy,
+                                             int64_t reserved_slots) {
   TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous());
   TORCH_CHECK(identities.is_cuda() && identities.scalar_type() == at::kLong && identities.is_contiguous() && identities.dim() == 1);
   TORCH_CHECK(segments.is_cuda() && segments.scalar_type() == at::kLong && segments.numel() >= 2);
@@ -326,6 +332,7 @@ std::tuple<at::Tensor, at::Tensor> zch_probe(const at::Tensor& ids, at::Tensor i
   a.policy = int(eviction_policy);
   a.eviction_threshold = int(eviction_threshold);
   a.disable_fallback = disable_fallback;
+  a.reserved = std::max<int64_t>(0, reserved_slots);
   const int threads = 256;
   const int blocks = int((a.N + threads - 1) / threads);
   zch_lookup_kernel<<<blocks, threads, 0, stream>>>(a);
@@ -463,7 +470,7 @@ TORCH_LIBRARY_FRAGMENT(trb200, m) {
   m.def("bce_with_logits_fwd_bwd(Tensor logits, Tensor labels, Tensor? weights) -> (Tensor, Tensor)");
   m.def(
       "zch_probe(Tensor ids, Tensor(a!) identities, Tensor(b!)? metadata, Tensor segments, int input_hash_size, int out_offset, int max_probe, bool readonly, "
-      "bool disable_fallback, Tensor? input_metadata, int eviction_threshold, int eviction_policy) -> (Tensor, Tensor)");
+      "bool disable_fallback, Tensor? input_metadata, int eviction_threshold, int eviction_policy, int reserved_slots=0) -> (Tensor, Tensor)");
   m.def("itep_remap(Tensor values, Tensor feature_offsets, Tensor feature_buffer, Tensor address_lookup, Tensor(a!) row_util, Tensor buffer_offsets, bool update_util) -> Tensor");
   m.def("kt_regroup(Tensor[] srcs, int[] dst_widths, Tensor desc, Tensor src_list) -> Tensor[]");
 }

@@ -9,11 +9,13 @@ the same rule the row-wise input distribution uses, so a rank that owns buckets 
 
 Lookup, insertion, eviction and the bucket arithmetic run in one op (``ops.sparse_ops.zch_probe``; device kernels in
 ``csrc/cuda/misc_kernels.cu``).  Counterpart of ``torchrec/modules/hash_mc_modules.py`` (``HashZchManagedCollisionModule`` ``:155``,
-``remap`` ``:469``); the reference's opt-in sampling with reserved slots is not implemented.
+``remap`` ``:469``).  Opt-in admission (``opt_in_prob``, ``percent_reserved_slots``): an id without a slot may claim one only with the
+given probability per occurrence; until then it shares one of the reserved rows at the end of its bucket, which no id can claim.
 """
 from __future__ import annotations
 
 import logging
+import math
 from typing import Any, Dict, Iterator, List, Optional, Tuple
 
 import torch
@@ -62,7 +64,10 @@ class HashZchManagedCollisionModule(ManagedCollisionModule):
             assert zch_size % total_num_buckets == 0, f"pass output_segments when buckets are not uniform ({zch_size=}, {total_num_buckets=})"
             output_segments = [(zch_size // total_num_buckets) * b for b in range(total_num_buckets + 1)]
         super().__init__(device=device if device.type != "meta" else torch.device("cpu"), output_segments=output_segments, skip_state_validation=True)
-        assert opt_in_prob == -1 and percent_reserved_slots == 0, "opt-in sampling with reserved slots is not implemented"
+        assert 0 <= percent_reserved_slots < 100, "percent_reserved_slots must be in [0, 100)"
+        assert opt_in_prob == -1 or 0 <= opt_in_prob <= 100, "opt_in_prob is a percentage (or -1: every id is admitted)"
+        assert opt_in_prob == -1 or percent_reserved_slots > 0, "percent_reserved_slots must be positive when opt_in_prob is set"
+        self._opt_in_prob, self._percent_reserved_slots = int(opt_in_prob), float(percent_reserved_slots)
         self._device = device
         self._zch_size = zch_size
         self._output_segments = list(output_segments)
@@ -153,7 +158,11 @@ class HashZchManagedCollisionModule(ManagedCollisionModule):
         return out + self._output_global_offset
 
     def get_reserved_slots_per_bucket(self) -> int:
-        return -1
+        """With opt-in admission, the number of slots at the end of every bucket that no id may claim (the shared rows of the ids that
+        were not admitted); -1 when admission is off."""
+        if self._opt_in_prob == -1:
+            return -1
+        return math.floor(self._zch_size * self._percent_reserved_slots / 100 / (self._end_bucket - self._start_bucket))
 
     def _dispatch_ids(self, values: torch.Tensor) -> torch.Tensor:
         """Ids as the training ranks saw them: at inference the merged table receives raw ids, while a training rank received the
@@ -175,10 +184,15 @@ class HashZchManagedCollisionModule(ManagedCollisionModule):
             score, threshold = (self._eviction_module(feature) if (self._eviction_module is not None and self.training) else (None, -1))
             ids = values.to(self.device)
             before = identities.clone() if self._scalar_logger is not None else None
+            # opt-in admission: while training, an id that has no slot yet may claim one only if its draw (a percentage) falls below opt_in_prob
+            admit = None
+            if self._opt_in_prob != -1 and self.training:
+                admit = (torch.rand(ids.shape, device=ids.device) * 100).to(torch.int32) < self._opt_in_prob
             slots, evicted = sops.zch_probe(
                 ids, identities, None if metadata is None else metadata.view(-1), segments, input_hash_size=self._input_hash_size,
                 out_offset=self._output_global_offset, max_probe=self._max_probe, readonly=readonly, disable_fallback=self._disable_fallback,
-                input_metadata=score, eviction_threshold=threshold, eviction_policy=get_kernel_from_policy(self._eviction_policy_name) if self.training else sops.ZCH_NO_EVICT)
+                input_metadata=score, eviction_threshold=threshold, eviction_policy=get_kernel_from_policy(self._eviction_policy_name) if self.training else sops.ZCH_NO_EVICT,
+                reserved_slots=max(self.get_reserved_slots_per_bucket(), 0), admit=admit)
             self.table_name_on_device_input_ids_dict[name] = ids
             self.table_name_on_device_remapped_ids_dict[name] = slots
             if self._scalar_logger is not None and before is not None:
@@ -225,4 +239,5 @@ class HashZchManagedCollisionModule(ManagedCollisionModule):
             zch_size=output_id_range[1] - output_id_range[0], device=device or self.device, total_num_buckets=self._buckets, max_probe=self._max_probe,
             input_hash_size=self._input_hash_size, output_segments=self._output_segments, is_inference=self._is_inference, name=self._name,
             tb_logging_frequency=self._tb_logging_frequency, eviction_policy_name=self._eviction_policy_name, eviction_config=self._eviction_config,
-            inference_dispatch_div_train_world_size=self._inference_dispatch_div_train_world_size, start_bucket=start, end_bucket=end, disable_fallback=self._disable_fallback)
+            inference_dispatch_div_train_world_size=self._inference_dispatch_div_train_world_size, start_bucket=start, end_bucket=end, opt_in_prob=self._opt_in_prob, percent_reserved_slots=self._percent_reserved_slots,
+            disable_fallback=self._disable_fallback)

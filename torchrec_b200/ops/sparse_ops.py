@@ -558,16 +558,40 @@ def zch_probe(
     input_metadata: Optional[torch.Tensor] = None,
     eviction_threshold: int = -1,
     eviction_policy: int = ZCH_NO_EVICT,
+    reserved_slots: int = 0,
+    admit: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Multi-probe zero-collision hash: ``ids -> (slot, evicted_slot)`` against the slot table ``identities`` (-1 = empty),
     updated in place unless ``readonly``.  ``segments`` are the global boundaries of the hash buckets, the table covers the slots
     ``[out_offset, out_offset + len(identities))``.  A miss claims an empty slot among the ``max_probe`` slots after its hash
     position inside its bucket, or evicts one whose score in ``metadata`` expired (TTL) / is the oldest (LRU); with no slot free it
     shares the row at its hash position, or gets -1 with ``disable_fallback``.  Duplicate ids are resolved once.
+    Opt-in admission: with ``reserved_slots > 0`` the last ``reserved_slots`` slots of every bucket are never claimed; an id without a slot
+    of its own shares one of them (by hash).  ``admit`` (bool per id) says which ids may claim a slot in this call: the others are
+    only looked up (an id occurring several times is admitted if any occurrence is).
     CUDA: ``misc_kernels.cu`` (lookup and insert launches); CPU: ``csrc/cpu/sparse_cpu.cpp``."""
     ids = ids.to(torch.int64).contiguous()
+    if admit is not None and not readonly and ids.numel() > 0:
+        admit = admit.to(device=ids.device, dtype=torch.bool)
+        if bool(admit.all()):
+            admit = None
+    if admit is not None and not readonly and ids.numel() > 0:
+        # an id with several occurrences must take one path: admitted if any occurrence drew admission
+        uniq, inverse = torch.unique(ids, return_inverse=True)
+        any_admit = torch.zeros(uniq.numel(), dtype=torch.int32, device=ids.device).scatter_reduce_(0, inverse, admit.to(torch.int32), reduce="amax", include_self=True)
+        admit = any_admit.index_select(0, inverse).bool()
+        slots, evicted = torch.empty_like(ids), torch.full_like(ids, -1)
+        common = dict(input_hash_size=input_hash_size, out_offset=out_offset, max_probe=max_probe, disable_fallback=disable_fallback,
+                      eviction_threshold=eviction_threshold, eviction_policy=eviction_policy, reserved_slots=reserved_slots)
+        meta_of = (lambda m: None) if input_metadata is None else (lambda m: input_metadata[m])
+        if bool(admit.any()):
+            slots[admit], evicted[admit] = zch_probe(ids[admit], identities, metadata, segments, readonly=False, input_metadata=meta_of(admit), **common)
+        rest = ~admit
+        slots[rest], _ = zch_probe(ids[rest], identities, metadata, segments, readonly=True, input_metadata=meta_of(rest), **common)
+        return slots, evicted
     args = (identities, metadata, segments.to(device=ids.device, dtype=torch.int64), int(input_hash_size), int(out_offset), int(max_probe), bool(readonly),
-            bool(disable_fallback), None if input_metadata is None else input_metadata.to(torch.int32).contiguous(), int(eviction_threshold), int(eviction_policy))
+            bool(disable_fallback), None if input_metadata is None else input_metadata.to(torch.int32).contiguous(), int(eviction_threshold), int(eviction_policy),
+            int(reserved_slots))
     op = torch.ops.trb200.zch_probe if _kern(ids, "zch_probe") else _ext.cpu_ops().zch_probe
     if readonly or ids.numel() == 0:
         return op(ids, *args)
