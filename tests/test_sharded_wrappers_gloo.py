@@ -351,6 +351,72 @@ def _tower_run(rank, world_size):
             torch.testing.assert_close(dmp.module.tower.interaction.lin.weight, g.tower.interaction.lin.weight, rtol=1e-4, atol=1e-5)
 
 
+def _spread_tower_run(rank, world_size, kind):
+    """A tower whose tables are spread over the ranks (row-wise / table-row-wise / column-wise): pooled rows arrive at the rank that
+    owns the sample, the interaction runs there with replicated parameters, and the whole model matches the unsharded one."""
+    from torchrec_b200.distributed import sharding_plan as sp
+    from torchrec_b200.distributed.embedding_tower_sharding import EmbeddingTowerSharder
+    from torchrec_b200.distributed.model_parallel import DistributedModelParallel
+    from torchrec_b200.distributed.types import ShardingEnv, ShardingPlan
+    from torchrec_b200.modules.embedding_configs import PoolingType
+    from torchrec_b200.modules.embedding_tower import EmbeddingTower
+    from torchrec_b200.optim.apply_optimizer_in_backward import apply_optimizer_in_backward
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    class Model(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.tower = EmbeddingTower(T._make_ebc(PoolingType.SUM), _TowerInteraction(5 * 16))
+            self.head = torch.nn.Linear(4, 1)
+
+        def forward(self, kjt):
+            out = self.tower(kjt)
+            return self.head(out.wait() if hasattr(out, "wait") else out)
+
+    with MultiProcessContext(rank, world_size, "gloo") as ctx:
+        torch.manual_seed(0)
+        B, lr = 6, 0.1
+        g = Model()
+        l = copy.deepcopy(g)
+        apply_optimizer_in_backward(torch.optim.SGD, l.tower.embedding.parameters(), {"lr": lr})
+        sharder = EmbeddingTowerSharder()
+        how = {"row_wise": sp.row_wise(), "table_row_wise": sp.table_row_wise(host_index=0), "column_wise": sp.column_wise(ranks=list(range(world_size)))}[kind]
+        mplan = sp.construct_module_sharding_plan(l.tower.embedding, {f"t{i}": how for i in range(4)}, sharder=sharder._embedding_sharder,
+                                                  world_size=world_size, local_size=world_size, device_type="cpu")
+        dmp = DistributedModelParallel(l, env=ShardingEnv.from_process_group(ctx.pg), device=torch.device("cpu"), plan=ShardingPlan({"tower": mplan}),
+                                       sharders=sp.get_default_sharders() + [sharder])
+        dmp.load_state_dict(copy.deepcopy(g.state_dict()))
+        assert dmp.module.module.tower.owner_rank == -1 if hasattr(dmp.module, "module") else True
+        dense_params = [p for n, p in dmp.named_parameters() if "embedding" not in n]
+        assert len(dense_params) == 4  # interaction and head, both replicated
+        opt = torch.optim.SGD(dense_params, lr=lr)
+        g_opt = torch.optim.SGD(g.parameters(), lr=lr)
+        kjts = [T._make_kjt(B, 100 + r) for r in range(world_size)]
+        keys = kjts[0].keys()
+        vals, lens = [], []
+        for k in keys:
+            for kj in kjts:
+                vals.append(kj[k].values()); lens.append(kj[k].lengths())
+        global_kjt = KeyedJaggedTensor.from_lengths_sync(keys=keys, values=torch.cat(vals), lengths=torch.cat(lens))
+        for step in range(3):
+            g_opt.zero_grad()
+            g_pred = g(global_kjt)
+            g_pred.mean().backward()
+            g_opt.step()
+            opt.zero_grad()
+            l_pred = dmp(kjts[rank])
+            l_pred.mean().backward()  # the data-parallel wrapper averages the gradients of the interaction and the head
+            opt.step()
+            torch.testing.assert_close(l_pred.detach(), g_pred.detach()[rank * B:(rank + 1) * B], rtol=1e-4, atol=1e-5)
+        inner = dmp.module.module if hasattr(dmp.module, "module") else dmp.module
+        torch.testing.assert_close(inner.tower.interaction.lin.weight.detach(), g.tower.interaction.lin.weight.detach(), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("kind", ["row_wise", "table_row_wise", "column_wise"])
+def test_spread_embedding_tower_matches_unsharded(kind):
+    run_multi_process(_spread_tower_run, world_size=2, kind=kind)
+
+
 def test_sharded_embedding_tower_matches_unsharded():
     run_multi_process(_tower_run, world_size=2)
 

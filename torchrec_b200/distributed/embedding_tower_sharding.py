@@ -1,11 +1,15 @@
-"""Sharded embedding towers: the tables of a tower and its interaction module live on one rank.
+"""Sharded embedding towers, in two forms chosen by the plan.
 
-The ids of the tower's features travel to the owning rank (the table-wise input distribution of the embedding module), the
-owner looks the rows up for the *global* batch and runs the interaction on them, and only the interaction's output -- usually
-much narrower than the concatenated embeddings -- is sent back through the pooled all-to-all.  The interaction's parameters are
-therefore trained on the owning rank only and are excluded from the data-parallel wrapper.
-Counterpart of ``torchrec/distributed/embedding_tower_sharding.py`` (``ShardedEmbeddingTower`` ``:95``, collection ``:442``); the
-reference also spreads a tower over the ranks of one host (table-row-wise), which is not built here.
+*One owner* (all tables table-wise on one rank): the ids of the tower's features travel to the owning rank (the table-wise input
+distribution of the embedding module), the owner looks the rows up for the *global* batch and runs the interaction on them, and
+only the interaction's output -- usually much narrower than the concatenated embeddings -- is sent back through the pooled
+all-to-all.  The interaction's parameters are trained on the owning rank only and are excluded from the data-parallel wrapper.
+
+*Spread* (row-wise, table-row-wise, column-wise or table-wise over several ranks): the tables are sharded like any embedding
+collection -- on GPUs through the fused engine over peer memory -- every rank receives the pooled rows of its own samples, and the
+interaction runs data-parallel on them with replicated parameters (the data-parallel wrapper averages their gradients).  On one
+node this is what the reference's table-row-wise tower computes (``torchrec/distributed/embedding_tower_sharding.py:95-440``,
+collection ``:442``); over several nodes the reference additionally confines a tower to one node, which this form does not do.
 """
 from __future__ import annotations
 
@@ -38,19 +42,18 @@ class ShardedEmbeddingTower(ShardedEmbeddingModule):
                  env: ShardingEnv, device: torch.device, module_fqn: Optional[str] = None) -> None:
         super().__init__()
         assert isinstance(module.embedding, EmbeddingBagCollection), "a sharded tower holds an EmbeddingBagCollection"
-        owners = set()
-        for name, ps in table_name_to_parameter_sharding.items():
-            assert ps.sharding_type == ShardingType.TABLE_WISE.value, f"tower table {name} must be table-wise sharded, got {ps.sharding_type}"
-            owners.add(ps.ranks[0])
-        assert len(owners) == 1, f"all tables of a tower must live on one rank, got ranks {sorted(owners)}"
-        self._owner = owners.pop()
+        kinds = {ps.sharding_type for ps in table_name_to_parameter_sharding.values()}
+        owners = {r for ps in table_name_to_parameter_sharding.values() for r in (ps.ranks or [])}
+        assert ShardingType.DATA_PARALLEL.value not in kinds, "tower tables are model-parallel"
+        self._spread = not (kinds == {ShardingType.TABLE_WISE.value} and len(owners) == 1)
+        self._owner = -1 if self._spread else owners.pop()
         self._env, self._device = env, device
         self._rank, self._world = env.rank, env.world_size
         self._pg = env.process_group
-        self._active = self._rank == self._owner
+        self._active = self._spread or self._rank == self._owner
         self.embedding: ShardedEmbeddingBagCollection = embedding_sharder.shard(module.embedding, table_name_to_parameter_sharding, env=env, device=device,
                                                                               module_fqn=(module_fqn + ".embedding") if module_fqn else None)
-        if hasattr(self.embedding, "disable_fused_engine"):
+        if not self._spread and hasattr(self.embedding, "disable_fused_engine"):
             self.embedding.disable_fused_engine()  # the tower consumes the owner-side lookup before any exchange
         self._lookups = self.embedding._lookups
         self.interaction = module.interaction.to(device) if device.type != "meta" else module.interaction
@@ -63,6 +66,8 @@ class ShardedEmbeddingTower(ShardedEmbeddingModule):
 
     def compute(self, ctx, dist_input: KJTList) -> torch.Tensor:
         embs = self.embedding.compute(ctx, dist_input)
+        if self._spread:
+            return embs
         assert len(embs) == 1
         pooled = embs[0]
         if self._active:
@@ -82,10 +87,17 @@ class ShardedEmbeddingTower(ShardedEmbeddingModule):
         return self._out_dim
 
     def output_dist(self, ctx, output: torch.Tensor) -> LazyAwaitable[torch.Tensor]:
+        if self._spread:
+            return _InteractionOnArrival(self.embedding.output_dist(ctx, output), self.interaction)
         O = self._output_dim(output)
         dims = [O if r == self._owner else 0 for r in range(self._world)]
         B = ctx.local_batch
         return _TowerOutput(alltoall_pooled(output.contiguous(), batch_size_per_rank=[B] * self._world, dim_sum_per_rank=dims, group=self._pg))
+
+    def compute_and_output_dist(self, ctx, input: KJTList) -> LazyAwaitable[torch.Tensor]:
+        if self._spread:  # the embedding module's own fused lookup + exchange (the engine's path on GPUs)
+            return _InteractionOnArrival(self.embedding.compute_and_output_dist(ctx, input), self.interaction)
+        return self.output_dist(ctx, self.compute(ctx, input))
 
     def create_context(self):
         ctx = self.embedding.create_context()
@@ -96,16 +108,32 @@ class ShardedEmbeddingTower(ShardedEmbeddingModule):
     def sharded_parameter_names(self, prefix: str = "") -> Iterator[str]:
         p = prefix + "." if prefix else ""
         yield from self.embedding.sharded_parameter_names(p + "embedding")
-        for name, _ in self.interaction.named_parameters():
-            yield f"{p}interaction.{name}"
+        if not self._spread:  # a spread tower's interaction is replicated: the data-parallel wrapper owns its gradients
+            for name, _ in self.interaction.named_parameters():
+                yield f"{p}interaction.{name}"
 
     @property
     def owner_rank(self) -> int:
+        """The rank that holds a one-owner tower; -1 for a spread tower."""
         return self._owner
 
     @property
     def unsharded_module_type(self) -> Type[EmbeddingTower]:
         return EmbeddingTower
+
+
+class _InteractionOnArrival(LazyAwaitable[torch.Tensor]):
+    """The spread form's output: the interaction runs on this rank's pooled rows once the embedding exchange has delivered them."""
+
+    def __init__(self, pooled: Awaitable[KeyedTensor], interaction: nn.Module) -> None:
+        super().__init__()
+        self._pooled, self._interaction = pooled, interaction
+
+    def _wait_impl(self) -> torch.Tensor:
+        kt = self._pooled.wait()
+        out = self._interaction(kt)
+        assert out.dim() == 2 and out.shape[0] == kt.values().shape[0], "the interaction must return [batch, features]"
+        return out
 
 
 class EmbeddingTowerSharder(BaseEmbeddingSharder[EmbeddingTower]):
@@ -130,7 +158,7 @@ class EmbeddingTowerSharder(BaseEmbeddingSharder[EmbeddingTower]):
         return EmbeddingTower
 
     def sharding_types(self, compute_device_type: str) -> List[str]:
-        return [ShardingType.TABLE_WISE.value]
+        return [ShardingType.TABLE_WISE.value, ShardingType.ROW_WISE.value, ShardingType.TABLE_ROW_WISE.value, ShardingType.COLUMN_WISE.value]
 
 
 class ShardedEmbeddingTowerCollection(nn.Module):
