@@ -12,7 +12,8 @@ pytestmark = pytest.mark.gpu
 
 
 def _run(opt, wdtype, pooling, steps=3):
-    specs, ftm, B = [(5000, 128), (40, 64), (100000, 128)], [0, 1, 2, 2], 512
+    specs = [(5000, 128), (40, 64 if pooling != PoolingMode.NONE else 128), (100000, 128)]  # unpooled groups share one width
+    ftm, B = [0, 1, 2, 2], 512
     torch.manual_seed(1)
     tbe = TableBatchedEmbeddingBags(specs, ftm, pooling, wdtype, torch.float32, opt, fused=True, device="cuda")
     tbe.init_embedding_weights_uniform(-0.1, 0.1)
