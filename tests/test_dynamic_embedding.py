@@ -14,7 +14,7 @@ def _lib():
 
 
 def test_id_transformer_assigns_slots_and_reports_new_ids():
-    t = torch.classes.trb_tde.IDTransformer(4, 5)
+    t = torch.classes.trb_tde.IDTransformer(4, 5, "naive")
     gids = torch.tensor([100, 7, 100, 42], dtype=torch.long)
     slots = torch.empty_like(gids)
     r = t.transform(gids, slots, 1)
@@ -28,7 +28,7 @@ def test_id_transformer_assigns_slots_and_reports_new_ids():
 
 
 def test_id_transformer_full_then_evict_and_resume():
-    t = torch.classes.trb_tde.IDTransformer(3, 0)
+    t = torch.classes.trb_tde.IDTransformer(3, 0, "cacheline")
     slots = torch.empty(5, dtype=torch.long)
     gids = torch.tensor([1, 2, 3, 4, 5], dtype=torch.long)
     r = t.transform(gids, slots, 1)
@@ -44,7 +44,7 @@ def test_id_transformer_full_then_evict_and_resume():
 
 
 def test_lru_order_within_equal_frequency():
-    t = torch.classes.trb_tde.IDTransformer(4, 5)
+    t = torch.classes.trb_tde.IDTransformer(4, 5, "naive")
     for time, gid in enumerate([10, 11, 12, 13], start=1):
         t.transform(torch.tensor([gid], dtype=torch.long), torch.empty(1, dtype=torch.long), time)
     assert t.evict(2)[:, 0].tolist() == [10, 11]  # oldest first
@@ -150,3 +150,24 @@ def test_wrapped_dataloader_rewrites_ids_and_saves():
     tl = tde.TensorList([torch.zeros(2)])
     tl.append(torch.ones(3))
     assert len(tl) == 2 and tl[1].numel() == 3
+
+
+def test_cacheline_layout_agrees_with_the_naive_one():
+    """Both table layouts of the native id transformer hand out the same slots for the same stream of ids."""
+    import pytest
+    import torch
+
+    from torchrec_b200.contrib.dynamic_embedding.id_transformer import IDTransformer
+
+    a = IDTransformer(64, transform_config={"type": "naive"})
+    b = IDTransformer(64, transform_config={"type": "cacheline"})
+    g = torch.Generator().manual_seed(0)
+    for step in range(1, 6):
+        ids = torch.randint(0, 40, (30,), generator=g)
+        sa, sb = torch.empty_like(ids), torch.empty_like(ids)
+        ra, rb = a.transform(ids, sa, step), b.transform(ids, sb, step)
+        assert ra.success and rb.success and torch.equal(sa, sb) and torch.equal(ra.ids_to_fetch, rb.ids_to_fetch)
+    assert len(a) == len(b)
+    assert sorted(map(tuple, a.save().tolist())) == sorted(map(tuple, b.save().tolist()))
+    with pytest.raises(Exception):
+        IDTransformer(8, transform_config={"type": "other"})

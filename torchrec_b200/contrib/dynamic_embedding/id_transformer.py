@@ -17,13 +17,15 @@ class TransformResult:
 
 
 class IDTransformer:
-    """``num_embedding`` cache slots for one table; ``eviction_config``: ``{"min_used_freq_power": int}``."""
+    """``num_embedding`` cache slots for one table; ``eviction_config``: ``{"min_used_freq_power": int}``; ``transform_config``:
+    ``{"type": "naive" | "cacheline"}`` selects the table layout of the native transformer (default ``"naive"``)."""
 
     def __init__(self, num_embedding: int, eviction_config: Optional[dict] = None, transform_config: Optional[dict] = None) -> None:
         ensure_native()
         cfg = eviction_config or {}
         self._num_embedding = num_embedding
-        self._impl = torch.classes.trb_tde.IDTransformer(num_embedding, int(cfg.get("min_used_freq_power", 5)))
+        layout = str((transform_config or {}).get("type", "naive"))
+        self._impl = torch.classes.trb_tde.IDTransformer(num_embedding, int(cfg.get("min_used_freq_power", 5)), layout)
 
     def transform(self, global_ids: torch.Tensor, cache_ids: torch.Tensor, time: int) -> TransformResult:
         r = self._impl.transform(global_ids, cache_ids, time)

@@ -30,22 +30,22 @@ static torch::Tensor pairs_to_tensor(const std::vector<std::pair<int64_t, int64_
 
 class IDTransformerWrapper : public torch::CustomClassHolder {
  public:
-  explicit IDTransformerWrapper(int64_t num_embeddings, int64_t min_used_freq_power = 5)
-      : impl_(num_embeddings, uint16_t(min_used_freq_power)) {}
+  explicit IDTransformerWrapper(int64_t num_embeddings, int64_t min_used_freq_power = 5, const std::string& variant = "naive")
+      : impl_(make_id_transformer(variant, num_embeddings, uint16_t(min_used_freq_power))) {}
 
   c10::intrusive_ptr<TransformResult> transform(torch::Tensor global_ids, torch::Tensor cache_ids, int64_t time) {
     TORCH_CHECK(global_ids.scalar_type() == torch::kLong && cache_ids.scalar_type() == torch::kLong);
     TORCH_CHECK(global_ids.is_contiguous() && cache_ids.is_contiguous() && global_ids.numel() == cache_ids.numel());
     TORCH_CHECK(!global_ids.is_cuda() && !cache_ids.is_cuda(), "the id transformer runs on host tensors");
-    auto r = impl_.transform(global_ids.data_ptr<int64_t>(), global_ids.numel(), cache_ids.data_ptr<int64_t>(), uint32_t(time));
+    auto r = impl_->transform(global_ids.data_ptr<int64_t>(), global_ids.numel(), cache_ids.data_ptr<int64_t>(), uint32_t(time));
     return c10::make_intrusive<TransformResult>(r.success, r.num_transformed, pairs_to_tensor(r.fetch));
   }
-  torch::Tensor evict(int64_t num_to_evict) { return pairs_to_tensor(impl_.evict(num_to_evict)); }
-  torch::Tensor save() { return pairs_to_tensor(impl_.save()); }
-  int64_t size() { return impl_.size(); }
+  torch::Tensor evict(int64_t num_to_evict) { return pairs_to_tensor(impl_->evict(num_to_evict)); }
+  torch::Tensor save() { return pairs_to_tensor(impl_->save()); }
+  int64_t size() { return impl_->size(); }
 
  private:
-  IdTransformer impl_;
+  std::unique_ptr<IdTransformerBase> impl_;
 };
 
 }  // namespace tde
@@ -60,7 +60,7 @@ TORCH_LIBRARY(trb_tde, m) {
       .def_readonly("num_transformed", &TransformResult::num_transformed)
       .def_readonly("ids_to_fetch", &TransformResult::ids_to_fetch);
   m.class_<IDTransformerWrapper>("IDTransformer")
-      .def(torch::init<int64_t, int64_t>())
+      .def(torch::init<int64_t, int64_t, const std::string&>())
       .def("transform", &IDTransformerWrapper::transform)
       .def("evict", &IDTransformerWrapper::evict)
       .def("save", &IDTransformerWrapper::save)

@@ -114,5 +114,127 @@ std::vector<std::pair<int64_t, int64_t>> IdTransformer::save() const {
   return out;
 }
 
+// ---- the cache-line layout ------------------------------------------------------------------------------------------------
+CachelineIdTransformer::CachelineIdTransformer(int64_t num_embeddings, uint16_t min_used_freq_power)
+    : num_embeddings_(num_embeddings), strategy_(min_used_freq_power) {
+  if (num_embeddings <= 0) throw std::invalid_argument("num_embeddings must be positive");
+  if (uint64_t(num_embeddings) >= uint64_t(kTombstone)) throw std::invalid_argument("the cache-line layout stores 32-bit slots");
+  size_t lines = 4;
+  while (lines * kWays < size_t(num_embeddings) * 2) lines <<= 1;  // load factor <= 0.5
+  Line blank;
+  for (auto& e : blank.way) e = Entry{0, kEmpty, 0};
+  lines_.assign(lines, blank);
+  line_mask_ = lines - 1;
+  free_slots_.reserve(num_embeddings);
+  for (int64_t s = num_embeddings - 1; s >= 0; --s) free_slots_.push_back(s);
+}
+
+size_t CachelineIdTransformer::probe(int64_t global_id, bool* found) const {
+  size_t line = mix(uint64_t(global_id)) & line_mask_;
+  size_t first_free = SIZE_MAX;
+  for (size_t step = 0; step <= line_mask_; ++step, line = (line + 1) & line_mask_) {
+    const Line& l = lines_[line];
+    bool saw_empty = false;
+    for (int w = 0; w < kWays; ++w) {
+      const Entry& e = l.way[w];
+      if (e.cache_id < kTombstone) {
+        if (e.global_id == global_id) {
+          *found = true;
+          return line * kWays + w;
+        }
+        continue;
+      }
+      if (first_free == SIZE_MAX) first_free = line * kWays + w;
+      if (e.cache_id == kEmpty) saw_empty = true;
+    }
+    if (saw_empty) break;  // an id is never stored past a line that still had a never-used entry
+  }
+  *found = false;
+  return first_free;
+}
+
+void CachelineIdTransformer::rehash() {
+  std::vector<Line> old;
+  old.swap(lines_);
+  Line blank;
+  for (auto& e : blank.way) e = Entry{0, kEmpty, 0};
+  lines_.assign(old.size(), blank);
+  tombstones_ = 0;
+  for (const Line& l : old)
+    for (const Entry& e : l.way) {
+      if (e.cache_id >= kTombstone) continue;
+      bool found;
+      at(probe(e.global_id, &found)) = e;
+    }
+}
+
+TransformOutcome CachelineIdTransformer::transform(const int64_t* global_ids, int64_t n, int64_t* cache_ids, uint32_t time) {
+  strategy_.update_time(time);
+  TransformOutcome res{true, 0, {}};
+  for (int64_t k = 0; k < n; ++k) {
+    const int64_t gid = global_ids[k];
+    bool found;
+    const size_t pos = probe(gid, &found);
+    if (found) {
+      Entry& e = at(pos);
+      LxuRecord r;
+      r.bits = e.record;
+      e.record = strategy_.touched(r).bits;
+      cache_ids[k] = int64_t(e.cache_id);
+    } else {
+      if (free_slots_.empty() || pos == SIZE_MAX) {
+        res.success = false;
+        return res;
+      }
+      const int64_t slot = free_slots_.back();
+      free_slots_.pop_back();
+      if (at(pos).cache_id == kTombstone) --tombstones_;
+      at(pos) = Entry{gid, uint32_t(slot), strategy_.first_seen().bits};
+      ++size_;
+      cache_ids[k] = slot;
+      res.fetch.emplace_back(gid, slot);
+    }
+    ++res.num_transformed;
+  }
+  return res;
+}
+
+std::vector<std::pair<int64_t, int64_t>> CachelineIdTransformer::evict(int64_t num_to_evict) {
+  std::vector<std::pair<int64_t, int64_t>> out;
+  if (num_to_evict <= 0 || size_ == 0) return out;
+  auto picks = strategy_.select_evictions(lines_.size() * kWays, size_t(num_to_evict), [&](size_t i, LxuRecord* r) {
+    const Entry& e = at(i);
+    if (e.cache_id >= kTombstone) return false;
+    r->bits = e.record;
+    return true;
+  });
+  out.reserve(picks.size());
+  for (size_t i : picks) {
+    Entry& e = at(i);
+    out.emplace_back(e.global_id, int64_t(e.cache_id));
+    free_slots_.push_back(int64_t(e.cache_id));
+    e.cache_id = kTombstone;
+    ++tombstones_;
+    --size_;
+  }
+  if (tombstones_ > lines_.size() * kWays / 4) rehash();
+  return out;
+}
+
+std::vector<std::pair<int64_t, int64_t>> CachelineIdTransformer::save() const {
+  std::vector<std::pair<int64_t, int64_t>> out;
+  out.reserve(size_);
+  for (const Line& l : lines_)
+    for (const Entry& e : l.way)
+      if (e.cache_id < kTombstone) out.emplace_back(e.global_id, int64_t(e.cache_id));
+  return out;
+}
+
+std::unique_ptr<IdTransformerBase> make_id_transformer(const std::string& variant, int64_t num_embeddings, uint16_t min_used_freq_power) {
+  if (variant == "naive") return std::make_unique<IdTransformer>(num_embeddings, min_used_freq_power);
+  if (variant == "cacheline") return std::make_unique<CachelineIdTransformer>(num_embeddings, min_used_freq_power);
+  throw std::invalid_argument("unknown id transformer variant '" + variant + "' (naive | cacheline)");
+}
+
 }  // namespace tde
 }  // namespace trb

@@ -41,8 +41,9 @@ static void test_record() {
   CHECK(hot.priority() > newer.priority());  // frequency dominates recency
 }
 
+template <class Table>
 static void test_transformer_basic() {
-  IdTransformer t(4);
+  Table t(4);
   int64_t ids[] = {100, 7, 100, 42};
   int64_t slots[4];
   auto r = t.transform(ids, 4, slots, 1);
@@ -61,8 +62,9 @@ static void test_transformer_basic() {
   CHECK(used.size() == 4);  // every slot is held by exactly one id
 }
 
+template <class Table>
 static void test_transformer_eviction_order() {
-  IdTransformer t(8);
+  Table t(8);
   int64_t slots[8];
   int64_t a[] = {10, 11, 12, 13};
   t.transform(a, 4, slots, 1);
@@ -73,9 +75,10 @@ static void test_transformer_eviction_order() {
   CHECK(gone.count(10) && gone.count(11));
 }
 
+template <class Table>
 static void test_transformer_many_ids() {
   const int64_t cap = 1 << 14;
-  IdTransformer t(cap);
+  Table t(cap);
   std::mt19937_64 rng(3);
   std::vector<int64_t> ids(cap), slots(cap);
   std::set<int64_t> uniq;
@@ -144,9 +147,10 @@ static void test_memory_store() {
   CHECK(threw);
 }
 
-static void bench() {
+template <class Table>
+static void bench(const char* name) {
   const int64_t cap = 1 << 20, batch = 1 << 16;
-  IdTransformer t(cap);
+  Table t(cap);
   std::mt19937_64 rng(1);
   std::vector<int64_t> ids(batch), slots(batch);
   auto t0 = std::chrono::steady_clock::now();
@@ -158,16 +162,35 @@ static void bench() {
     if (!r.success) t.evict(cap / 4);
   }
   const double s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
-  std::printf("BENCH id_transformer: %.1f M ids/s (%lld ids, capacity %lld)\n", total / s / 1e6, (long long)total, (long long)cap);
+  std::printf("BENCH id_transformer %s: %.1f M ids/s (%lld ids, capacity %lld)\n", name, total / s / 1e6, (long long)total, (long long)cap);
 }
 
 int main(int argc, char** argv) {
   test_record();
-  test_transformer_basic();
-  test_transformer_eviction_order();
-  test_transformer_many_ids();
+  test_transformer_basic<IdTransformer>();
+  test_transformer_eviction_order<IdTransformer>();
+  test_transformer_many_ids<IdTransformer>();
+  test_transformer_basic<CachelineIdTransformer>();
+  test_transformer_eviction_order<CachelineIdTransformer>();
+  test_transformer_many_ids<CachelineIdTransformer>();
+  {  // the factory knows both layouts and nothing else
+    auto a = make_id_transformer("naive", 8), b = make_id_transformer("cacheline", 8);
+    int64_t ids[] = {5, 6, 5}, sa[3], sb[3];
+    CHECK(a->transform(ids, 3, sa, 1).fetch.size() == 2 && b->transform(ids, 3, sb, 1).fetch.size() == 2);
+    CHECK(sa[0] == sb[0] && sa[1] == sb[1] && sa[2] == sb[2] && a->capacity() == 8 && b->size() == 2);
+    bool threw = false;
+    try {
+      make_id_transformer("other", 8);
+    } catch (const std::exception&) {
+      threw = true;
+    }
+    CHECK(threw);
+  }
   test_memory_store();
-  if (argc > 1 && std::strcmp(argv[1], "--bench") == 0) bench();
+  if (argc > 1 && std::strcmp(argv[1], "--bench") == 0) {
+    bench<IdTransformer>("naive");
+    bench<CachelineIdTransformer>("cacheline");
+  }
   if (g_failed) {
     std::printf("%d checks failed\n", g_failed);
     return 1;

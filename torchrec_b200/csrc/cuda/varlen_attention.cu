@@ -85,16 +85,23 @@ __device__ __forceinline__ void attn_a_frags(const __nv_bfloat16* base, int pitc
   }
 }
 
-// c[t] (t = 0..3: 8-column tiles n0 + 8 t) += A[16 x DH] * Y[n0 .. n0 + 32)[DH]^T with Y row-major in shared memory
+// c[t] (t = 0..3: 8-column tiles n0 + 8 t) += A[16 x DH] * Y[n0 .. n0 + 32)[DH]^T with Y row-major in shared memory.
+// One ldmatrix.x4 fetches the B fragments of a tile for two k-steps (four 8 x 8 blocks of 16 bytes per row).
 template <int DH>
-__device__ __forceinline__ void attn_nt(float (&c)[4][4], const uint32_t (&a)[DH / 16][4], const __nv_bfloat16* y, int pitch, int n0, int g, int t4) {
+__device__ __forceinline__ void attn_nt(float (&c)[4][4], const uint32_t (&a)[DH / 16][4], const __nv_bfloat16* y, int pitch, int n0, int lane) {
+  static_assert(DH % 32 == 0, "two k-steps per ldmatrix");
 #pragma unroll
-  for (int ks = 0; ks < DH / 16; ++ks)
+  for (int t = 0; t < 4; ++t) {
+    const __nv_bfloat16* row = y + (n0 + t * 8 + (lane & 7)) * pitch + (lane >> 3) * 8;
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const __nv_bfloat16* p = y + (n0 + t * 8 + g) * pitch + ks * 16 + 2 * t4;
-      attn_mma(c[t], a[ks], attn_ld32(p), attn_ld32(p + 8));
+    for (int k2 = 0; k2 < DH / 32; ++k2) {
+      uint32_t b00, b01, b10, b11;
+      const uint32_t addr = uint32_t(__cvta_generic_to_shared(row + k2 * 32));
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(b00), "=r"(b01), "=r"(b10), "=r"(b11) : "r"(addr));
+      attn_mma(c[t], a[2 * k2], b00, b01);
+      attn_mma(c[t], a[2 * k2 + 1], b10, b11);
     }
+  }
 }
 
 // acc[16 x DH] += P[16 x 32] * Y[k0 .. k0 + 32)[DH]; P is given as accumulator-layout values p[t][k] (t: 8-column tiles)
@@ -183,39 +190,46 @@ __global__ void __launch_bounds__(32 * WARPS, 3) varlen_attn_fwd_kernel(const __
       for (int t = 0; t < 4; ++t)
 #pragma unroll
         for (int k = 0; k < 4; ++k) s[t][k] = 0.f;
-      attn_nt<DH>(s, qa, Ks, P, kc, g, t4);
+      attn_nt<DH>(s, qa, Ks, P, kc, lane);
+      if (kc + 32 > n) {  // only the last chunk has keys beyond the sequence
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            if (kc + t * 8 + 2 * t4 + (k & 1) >= n) s[t][k] = -INFINITY;
+      }
+      // running maxima on the raw scores (the softmax scale is positive, so it commutes with max and is folded into the exponent)
       float c0 = -INFINITY, c1 = -INFINITY;
 #pragma unroll
-      for (int t = 0; t < 4; ++t)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int key = kc + t * 8 + 2 * t4 + (k & 1);
-          const float v = key < n ? s[t][k] * scale_log2 : -INFINITY;
-          s[t][k] = v;
-          if (k < 2) c0 = fmaxf(c0, v); else c1 = fmaxf(c1, v);
-        }
+      for (int t = 0; t < 4; ++t) {
+        c0 = fmaxf(c0, fmaxf(s[t][0], s[t][1]));
+        c1 = fmaxf(c1, fmaxf(s[t][2], s[t][3]));
+      }
       c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, 1));
       c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, 2));
       c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, 1));
       c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, 2));
       const float mn0 = fmaxf(m0, c0), mn1 = fmaxf(m1, c1);  // finite: every chunk starts below n
-      const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
-      m0 = mn0;
-      m1 = mn1;
-      l0 *= al0;
-      l1 *= al1;
+      if (__any_sync(0xffffffffu, mn0 != m0 || mn1 != m1)) {  // a maximum moved: bring the running sums to the new reference
+        const float al0 = exp2f((m0 - mn0) * scale_log2), al1 = exp2f((m1 - mn1) * scale_log2);
+        l0 *= al0;
+        l1 *= al1;
 #pragma unroll
-      for (int t = 0; t < DH / 8; ++t) {
-        o[t][0] *= al0;
-        o[t][1] *= al0;
-        o[t][2] *= al1;
-        o[t][3] *= al1;
+        for (int t = 0; t < DH / 8; ++t) {
+          o[t][0] *= al0;
+          o[t][1] *= al0;
+          o[t][2] *= al1;
+          o[t][3] *= al1;
+        }
+        m0 = mn0;
+        m1 = mn1;
       }
+      const float ms0 = m0 * scale_log2, ms1 = m1 * scale_log2;
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const float e = exp2f(s[t][k] - (k < 2 ? mn0 : mn1));
+          const float e = exp2f(fmaf(s[t][k], scale_log2, -(k < 2 ? ms0 : ms1)));
           if (k < 2) l0 += e; else l1 += e;
           s[t][k] = e;
         }
@@ -241,8 +255,8 @@ __global__ void __launch_bounds__(32 * WARPS, 3) varlen_attn_fwd_kernel(const __
       if (r1 < n) *reinterpret_cast<__nv_bfloat162*>(out + (tok0 + r1) * D + h * DH + t * 8 + 2 * t4) = __floats2bfloat162_rn(o[t][2] * i1, o[t][3] * i1);
     }
     if (t4 == 0) {
-      if (r0 < n) lse2[(tok0 + r0) * H + h] = m0 + log2f(l0);
-      if (r1 < n) lse2[(tok0 + r1) * H + h] = m1 + log2f(l1);
+      if (r0 < n) lse2[(tok0 + r0) * H + h] = m0 * scale_log2 + log2f(l0);
+      if (r1 < n) lse2[(tok0 + r1) * H + h] = m1 * scale_log2 + log2f(l1);
     }
   }
 }
@@ -264,7 +278,7 @@ __device__ __forceinline__ void attn_a_frags_global(const __nv_bfloat16* base, i
 
 // dK and dV: Q and dO of the sequence in shared memory; a warp owns 16 keys and walks the queries 32 at a time ([key][query] tiles)
 template <int DH, int WARPS>
-__global__ void __launch_bounds__(32 * WARPS) varlen_attn_bwd_kv_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ out,
+__global__ void __launch_bounds__(32 * WARPS, 3) varlen_attn_bwd_kv_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ out,
                                                                        const __nv_bfloat16* __restrict__ dout, const float* __restrict__ lse2,
                                                                        const int64_t* __restrict__ offsets, __nv_bfloat16* __restrict__ dqkv, int H, int n_cap,
                                                                        int np_cap, float scale, float scale_log2, AttnDrop drop, int* __restrict__ err) {
@@ -333,8 +347,8 @@ __global__ void __launch_bounds__(32 * WARPS) varlen_attn_bwd_kv_kernel(const __
       for (int t = 0; t < 4; ++t)
 #pragma unroll
         for (int k = 0; k < 4; ++k) st[t][k] = dp[t][k] = 0.f;
-      attn_nt<DH>(st, ka, Qs, P, qc, g, t4);
-      attn_nt<DH>(dp, va, Gs, P, qc, g, t4);
+      attn_nt<DH>(st, ka, Qs, P, qc, lane);
+      attn_nt<DH>(dp, va, Gs, P, qc, lane);
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const int q = qc + t * 8 + 2 * t4;  // queries q, q + 1: an aligned pair
@@ -432,8 +446,8 @@ __global__ void __launch_bounds__(32 * WARPS) varlen_attn_bwd_q_kernel(const __n
       for (int t = 0; t < 4; ++t)
 #pragma unroll
         for (int k = 0; k < 4; ++k) s[t][k] = dp[t][k] = 0.f;
-      attn_nt<DH>(s, qa, Ks, P, kc, g, t4);
-      attn_nt<DH>(dp, ga, Vs, P, kc, g, t4);
+      attn_nt<DH>(s, qa, Ks, P, kc, lane);
+      attn_nt<DH>(dp, ga, Vs, P, kc, lane);
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         float f[4] = {1.f, 1.f, 1.f, 1.f};
