@@ -245,6 +245,11 @@ def bench_transformer(B: int, n: int, warm: int) -> None:
     from torchrec_b200.ops import transformer_ops as tops
 
     ops = torch.ops.trb200
+    sink = torch.zeros(1, device="cuda")
+    for chains, per_sm in ((1, 1), (4, 2), (8, 4), (8, 8)):
+        flops = ops.mma_sync_probe(sink, 4096, chains, per_sm)
+        t = timeit(lambda: ops.mma_sync_probe(sink, 4096, chains, per_sm), n, warm)
+        print(f"mma.sync m16n8k16 bf16 issue rate, {chains} independent chains x {8 * per_sm} warps per SM: {flops / t / 1e9:.0f} TFLOP/s", flush=True)
     gen = torch.Generator().manual_seed(0)
     lengths = torch.randint(20, 201, (B,), generator=gen)
     offsets = torch.cat([torch.zeros(1, dtype=torch.long), lengths.cumsum(0)]).cuda()
