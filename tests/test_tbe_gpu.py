@@ -289,3 +289,41 @@ def test_stochastic_rounding_is_unbiased_where_nearest_rounding_stalls():
     expected = steps * 2.0 ** -7 / 16
     assert results[False] == 0.0
     assert abs(results[True] - expected) < 0.1 * expected, (results, expected)
+
+
+@pytest.mark.parametrize("D", [512, 1024])
+@pytest.mark.parametrize("zipf", [False, True])
+def test_wide_rows_against_embedding_bag_and_python_rowwise_adagrad(D, zipf):
+    """Wide rows at a four-digit batch, checked directly against ``torch.nn.functional.embedding_bag`` and a row-wise Adagrad written out
+    in plain torch (state += mean(g^2) per row; w -= lr * g / (sqrt(state) + eps)), two steps so that the state matters."""
+    import torch.nn.functional as F
+
+    lr, eps = 0.05, 1e-8
+    specs, ftm, B = [(3000, D), (500, D)], [0, 1, 0], 2048
+    torch.manual_seed(2)
+    tbe = TableBatchedEmbeddingBags(specs, ftm, PoolingMode.SUM, torch.float32, torch.float32, OptimizerArgs(EmbOptimType.EXACT_ROWWISE_ADAGRAD, lr, eps=eps),
+                                    fused=True, device="cuda")
+    tbe.init_embedding_weights_uniform(-0.1, 0.1)
+    tables = [w.detach().clone() for w in tbe.split_embedding_weights()]
+    state = [torch.zeros(r, device="cuda") for r, _ in specs]
+    for step in range(2):
+        idx, off, _ = _make_inputs(specs, ftm, B, 12, False, 21 + step, zipf=zipf)
+        idx, off = idx.cuda(), off.cuda()
+        out = tbe(idx, off)
+        params = [t.clone().requires_grad_(True) for t in tables]
+        cols = []
+        for f, t in enumerate(ftm):
+            lo, hi = int(off[f * B]), int(off[(f + 1) * B])
+            cols.append(F.embedding_bag(idx[lo:hi], params[t], off[f * B:(f + 1) * B] - lo, mode="sum"))
+        want = torch.cat(cols, dim=1)
+        torch.testing.assert_close(out.detach(), want.detach(), rtol=1e-5, atol=1e-5)
+        g = torch.randn(want.shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(step))
+        out.backward(g)
+        want.backward(g)
+        for t in range(len(specs)):
+            grad = params[t].grad
+            state[t] += grad.pow(2).mean(1)
+            tables[t] = tables[t] - lr * grad / (state[t].sqrt().unsqueeze(1) + eps)  # rows without gradient stay as they are
+        for got, ref in zip(tbe.split_embedding_weights(), tables):
+            torch.testing.assert_close(got.detach(), ref, rtol=1e-4, atol=2e-6)
+    tbe.check_error()
