@@ -150,3 +150,22 @@ def test_itep_remap():
     assert row_util.tolist() == [1, 0, 0, 0, 1, 1, 0, 1, 0, 1]
     out2 = sops.itep_remap(values, feature_offsets, feature_buffer, address_lookup, row_util, buffer_offsets, False)
     assert out2.tolist() == out.tolist() and row_util.sum() == 5
+
+
+def test_jagged_unique_indices_semantics():
+    """Distinct ids per feature (features that share a table are deduplicated together and counted under the last of them), sorted
+    inside a feature, with a reverse index that reproduces the input."""
+    import torch
+
+    from torchrec_b200.ops import sparse_ops as sops
+
+    cumsum = torch.tensor([0, 10, 30])          # two tables: 10 and 20 rows
+    feature_table = torch.tensor([0, 1, 1, 2])   # feature 0 -> table 0, features 1 and 2 -> table 1
+    # B = 2 bags per feature
+    lengths = torch.tensor([2, 1, 0, 3, 2, 0])
+    offsets = torch.cat([torch.zeros(1, dtype=torch.long), lengths.cumsum(0)])
+    ids = torch.tensor([3, 3, 9, 5, 7, 5, 7, 19])
+    out_len, out_off, uniq, rev = sops.jagged_unique_indices(cumsum, feature_table, offsets, ids)
+    assert out_len.tolist() == [2, 0, 3] and out_off.tolist() == [0, 2, 2, 5]
+    assert uniq.tolist() == [3, 9, 5, 7, 19]
+    assert torch.equal(uniq[rev], ids)

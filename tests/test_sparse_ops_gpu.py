@@ -128,3 +128,25 @@ def test_vbe_expand_matches_index_select_and_routes_gradients():
     got.backward(g.cuda())
     want.backward(g)
     torch.testing.assert_close(flat.grad.cpu(), ref_in.grad, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.int64, torch.int32])
+def test_jagged_unique_indices_matches_the_composite(dtype):
+    from torchrec_b200.ops import sparse_ops as sops
+
+    g = torch.Generator().manual_seed(0)
+    F, B = 5, 64
+    table_rows = torch.tensor([1000, 50, 7000])
+    cumsum = torch.cat([torch.zeros(1, dtype=torch.long), table_rows.cumsum(0)])
+    feature_table = torch.tensor([0, 1, 1, 2, 2, 3])  # features 1,2 share table 1; 3,4 share table 2
+    lengths = torch.randint(0, 9, (F * B,), generator=g)
+    lengths[B:B + 5] = 0  # empty bags at a feature's start
+    offsets = torch.cat([torch.zeros(1, dtype=torch.long), lengths.cumsum(0)])
+    rows_of_feature = table_rows[feature_table[:-1]]
+    ids = torch.cat([torch.randint(0, int(rows_of_feature[f]), (int(lengths[f * B:(f + 1) * B].sum()),), generator=g) for f in range(F)]).to(dtype)
+    want = sops.jagged_unique_indices(cumsum, feature_table, offsets, ids)
+    got = sops.jagged_unique_indices(cumsum.cuda(), feature_table.cuda(), offsets.cuda(), ids.cuda())
+    for a, b in zip(got, want):
+        assert a.dtype == b.dtype and torch.equal(a.cpu(), b), (a, b)
+    uniq, rev = got[2], got[3]
+    assert torch.equal(uniq[rev.long()].cpu() , ids)

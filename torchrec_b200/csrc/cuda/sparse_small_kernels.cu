@@ -5,12 +5,18 @@
 //   vbe_expand        variable-batch pooled output -> full batch: every (feature, sample) copies the row that the inverse
 //                     indices name, straight to its output column (replaces one index_select per feature plus a concat)
 //
-// The reference takes the first two from an external operator library and composes the third
-// (torchrec/distributed/embeddingbag.py:385-440).
+//   jagged_unique_indices   per-feature deduplication of ids: linearize (id + base of the feature's table), radix-sort the
+//                     (key, position) pairs, flag the first of every run, scan the flags into ranks, scatter: unique ids, the
+//                     reverse index of every input id, and the number of distinct ids per feature
+//
+// The reference takes the first two and the last from an external operator library and composes the third
+// (torchrec/distributed/embeddingbag.py:385-440, torchrec/distributed/embedding.py:1329-1370).
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
+
+#include <cub/cub.cuh>
 
 #include "common.cuh"
 
@@ -122,15 +128,106 @@ at::Tensor vbe_expand(const at::Tensor& flat, const at::Tensor& desc, const at::
   return out;
 }
 
+// ---- jagged_unique_indices ---------------------------------------------------------------------------------------------
+// last index j in [0, n) with a[j] <= v (a ascending, a[0] <= v)
+__device__ __forceinline__ int64_t last_not_above(const int64_t* __restrict__ a, int64_t n, int64_t v) {
+  int64_t lo = 0, hi = n;
+  while (hi - lo > 1) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (a[mid] <= v) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// key[i] = indices[i] + base[table of the feature of i]; pos[i] = i.  offsets [F * B + 1] bound the bags (feature-major).
+template <typename I>
+__global__ void __launch_bounds__(256) unique_linearize_kernel(const I* __restrict__ indices, const int64_t* __restrict__ offsets, int64_t n_bags, int64_t B,
+                                                               const int64_t* __restrict__ feat_base, int64_t N, int64_t* __restrict__ key,
+                                                               int64_t* __restrict__ pos) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= N) return;
+  const int64_t bag = last_not_above(offsets, n_bags + 1, i);  // offsets[bag] <= i < offsets[bag + 1] (empty bags are skipped by "last")
+  key[i] = int64_t(indices[i]) + feat_base[bag / B];
+  pos[i] = i;
+}
+
+__global__ void __launch_bounds__(256) unique_heads_kernel(const int64_t* __restrict__ key_sorted, int64_t N, int32_t* __restrict__ head) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= N) return;
+  head[i] = (i == 0 || key_sorted[i] != key_sorted[i - 1]) ? 1 : 0;
+}
+
+template <typename I>
+__global__ void __launch_bounds__(256) unique_scatter_kernel(const int64_t* __restrict__ key_sorted, const int64_t* __restrict__ pos_sorted,
+                                                             const int32_t* __restrict__ head, const int64_t* __restrict__ rank, int64_t N,
+                                                             const int64_t* __restrict__ feat_base, int64_t F, I* __restrict__ unique, I* __restrict__ reverse,
+                                                             int64_t* __restrict__ per_feature) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= N) return;
+  const int64_t r = rank[i] - 1;
+  reverse[pos_sorted[i]] = I(r);
+  if (head[i]) {
+    const int64_t f = last_not_above(feat_base, F, key_sorted[i]);
+    unique[r] = I(key_sorted[i] - feat_base[f]);
+    atomicAdd(reinterpret_cast<unsigned long long*>(per_feature + f), 1ull);
+  }
+}
+
+// feat_base [F] ascending: the id base of every feature's table.  Returns (distinct ids per feature [F] int64, unique ids (feature-major,
+// ascending inside a feature), reverse index [N]); one host read for the number of distinct ids.
+std::tuple<at::Tensor, at::Tensor, at::Tensor> jagged_unique_indices(const at::Tensor& feat_base, const at::Tensor& offsets, const at::Tensor& indices,
+                                                                    int64_t key_bits) {
+  TORCH_CHECK(indices.is_cuda() && indices.dim() == 1 && indices.is_contiguous() && (indices.scalar_type() == at::kInt || indices.scalar_type() == at::kLong));
+  TORCH_CHECK(offsets.is_cuda() && offsets.scalar_type() == at::kLong && offsets.is_contiguous() && offsets.numel() >= 1);
+  TORCH_CHECK(feat_base.is_cuda() && feat_base.scalar_type() == at::kLong && feat_base.is_contiguous() && feat_base.numel() >= 1);
+  c10::cuda::CUDAGuard guard(indices.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int64_t N = indices.numel(), F = feat_base.numel(), n_bags = offsets.numel() - 1;
+  TORCH_CHECK(n_bags % F == 0, "offsets must describe the same number of bags for every feature");
+  const auto lopt = indices.options().dtype(at::kLong);
+  at::Tensor per_feature = at::zeros({F}, lopt);
+  if (N == 0) return {per_feature, at::empty({0}, indices.options()), at::empty({0}, indices.options())};
+  at::Tensor key = at::empty({N}, lopt), pos = at::empty({N}, lopt), key_s = at::empty({N}, lopt), pos_s = at::empty({N}, lopt);
+  at::Tensor head = at::empty({N}, indices.options().dtype(at::kInt)), rank = at::empty({N}, lopt);
+  const int64_t blocks = (N + 255) / 256;
+  AT_DISPATCH_INDEX_TYPES(indices.scalar_type(), "jagged_unique_linearize", [&] {
+    unique_linearize_kernel<index_t><<<blocks, 256, 0, stream>>>(indices.data_ptr<index_t>(), offsets.data_ptr<int64_t>(), n_bags, std::max<int64_t>(n_bags / F, 1),
+                                                                feat_base.data_ptr<int64_t>(), N, key.data_ptr<int64_t>(), pos.data_ptr<int64_t>());
+  });
+  const int end_bit = int(std::min<int64_t>(64, std::max<int64_t>(1, key_bits)));
+  size_t bytes = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, bytes, key.data_ptr<int64_t>(), key_s.data_ptr<int64_t>(), pos.data_ptr<int64_t>(), pos_s.data_ptr<int64_t>(), N, 0, end_bit,
+                                  stream);
+  at::Tensor tmp = at::empty({int64_t(bytes)}, indices.options().dtype(at::kByte));
+  cub::DeviceRadixSort::SortPairs(tmp.data_ptr(), bytes, key.data_ptr<int64_t>(), key_s.data_ptr<int64_t>(), pos.data_ptr<int64_t>(), pos_s.data_ptr<int64_t>(), N, 0,
+                                  end_bit, stream);
+  unique_heads_kernel<<<blocks, 256, 0, stream>>>(key_s.data_ptr<int64_t>(), N, head.data_ptr<int32_t>());
+  size_t sbytes = 0;
+  cub::DeviceScan::InclusiveSum(nullptr, sbytes, head.data_ptr<int32_t>(), rank.data_ptr<int64_t>(), N, stream);
+  at::Tensor stmp = at::empty({int64_t(sbytes)}, indices.options().dtype(at::kByte));
+  cub::DeviceScan::InclusiveSum(stmp.data_ptr(), sbytes, head.data_ptr<int32_t>(), rank.data_ptr<int64_t>(), N, stream);
+  at::Tensor unique = at::empty({N}, indices.options()), reverse = at::empty({N}, indices.options());
+  AT_DISPATCH_INDEX_TYPES(indices.scalar_type(), "jagged_unique_scatter", [&] {
+    unique_scatter_kernel<index_t><<<blocks, 256, 0, stream>>>(key_s.data_ptr<int64_t>(), pos_s.data_ptr<int64_t>(), head.data_ptr<int32_t>(), rank.data_ptr<int64_t>(), N,
+                                                              feat_base.data_ptr<int64_t>(), F, unique.data_ptr<index_t>(), reverse.data_ptr<index_t>(),
+                                                              per_feature.data_ptr<int64_t>());
+  });
+  TRB_CUDA_CHECK(cudaGetLastError());
+  const int64_t distinct = rank[N - 1].item<int64_t>();  // the only host read: the output's size
+  return {per_feature, unique.narrow(0, 0, distinct), reverse};
+}
+
 }  // namespace trb
 
 TORCH_LIBRARY_FRAGMENT(trb200, m) {
+  m.def("jagged_unique_indices(Tensor feat_base, Tensor offsets, Tensor indices, int key_bits) -> (Tensor, Tensor, Tensor)");
   m.def("offsets_range(Tensor starts, int total) -> Tensor");
   m.def("segment_sum_csr(int batch, Tensor csr, Tensor values) -> Tensor");
   m.def("vbe_expand(Tensor flat, Tensor desc, Tensor inverse, int out_cols, Tensor(a!) err) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(trb200, CUDA, m) {
+  m.impl("jagged_unique_indices", &trb::jagged_unique_indices);
   m.impl("offsets_range", &trb::offsets_range);
   m.impl("segment_sum_csr", &trb::segment_sum_csr);
   m.impl("vbe_expand", &trb::vbe_expand);

@@ -170,17 +170,8 @@ def _dedup_indices(ctx: EmbeddingCollectionContext, features: KeyedJaggedTensor,
     remember in ``ctx`` how to expand looked-up rows back: rows for the original ids are
     ``unique_rows[reverse_indices]``.  Ids of different features never merge (offset by ``hash_offsets``)."""
     with record_function("## dedup_ec_indices ##"):
-        lpk = features.length_per_key()
-        F = len(lpk)
         values = features.values()
-        feat_of = torch.repeat_interleave(
-            torch.arange(F, device=values.device), torch.tensor(lpk, device=values.device), output_size=int(sum(lpk))
-        )
-        keyed = values.to(torch.int64) + hash_offsets[feat_of]
-        uniq, reverse = torch.unique(keyed, sorted=True, return_inverse=True)
-        # sorted by (feature, id): unique ids stay key-major
-        ufeat = torch.searchsorted(hash_offsets, uniq, right=True) - 1
-        counts = torch.bincount(ufeat, minlength=F)
+        counts, unique_ids, reverse = sops.unique_ids_per_feature(hash_offsets[: len(features.keys())], features.offsets(), values)
         stride = features.stride()
         # spread each feature's unique ids over its `stride` bags: first bags get ceil, rest floor (any split works,
         # the rows are re-expanded by `reverse` and the original lengths afterwards)
@@ -191,7 +182,7 @@ def _dedup_indices(ctx: EmbeddingCollectionContext, features: KeyedJaggedTensor,
         ctx.input_features.append(features)
         ctx.reverse_indices.append(reverse)
         return KeyedJaggedTensor(
-            keys=features.keys(), values=(uniq - hash_offsets[ufeat]).to(values.dtype), lengths=lengths.to(features.lengths().dtype),
+            keys=features.keys(), values=unique_ids, lengths=lengths.to(features.lengths().dtype),
             stride=stride,
         )
 

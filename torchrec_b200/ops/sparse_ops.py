@@ -407,6 +407,44 @@ def jagged_1d_to_dense(values: torch.Tensor, offsets: torch.Tensor, max_sequence
 # --------------------------------------------------------------------------------------
 # dedup
 # --------------------------------------------------------------------------------------
+_key_bits_cache: dict = {}
+
+
+def _key_bits(feat_base: torch.Tensor, indices: torch.Tensor) -> int:
+    """Bits the radix sort has to look at: enough for the largest linearized id.  The bases rarely change, so the one host read
+    this needs is cached per base tensor; the bound on the ids' own width comes from their dtype."""
+    key = (feat_base.data_ptr(), feat_base.numel(), indices.dtype)
+    bits = _key_bits_cache.get(key)
+    if bits is None:
+        top = int(feat_base.max().item()) if feat_base.numel() else 0
+        bits = min(64, max(top.bit_length(), 31 if indices.dtype == torch.int32 else 40) + 1)
+        if len(_key_bits_cache) > 64:
+            _key_bits_cache.clear()
+        _key_bits_cache[key] = bits
+    return bits
+
+
+def unique_ids_per_feature(feat_base: torch.Tensor, offsets: torch.Tensor, indices: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``(distinct ids per feature [F], unique ids, reverse index)`` for ids in feature-major bags; ``feat_base [F]`` (ascending) is the
+    id base of every feature's table: two features with the same base share a table and are deduplicated together (their ids
+    are counted under the last of them).  Unique ids are feature-major and ascending inside a feature;
+    ``unique[reverse[i]] == indices[i]``.  CUDA: sort-based kernels in ``sparse_small_kernels.cu``; elsewhere ``torch.unique``."""
+    F = feat_base.numel()
+    N = indices.numel()
+    base = feat_base.to(torch.int64)
+    if _kern(indices, "jagged_unique_indices") and N > 0:
+        return torch.ops.trb200.jagged_unique_indices(base.contiguous(), offsets.to(torch.int64).contiguous(), indices.contiguous(), _key_bits(base, indices))
+    off = offsets.to(torch.int64)
+    B = max((off.numel() - 1) // max(F, 1), 1)
+    feat = lengths_range(off[1:] - off[:-1], N) // B if N else indices.to(torch.int64)
+    lin = indices.to(torch.int64) + base.index_select(0, feat) if N else indices.to(torch.int64)
+    uniq, reverse = torch.unique(lin, sorted=True, return_inverse=True)
+    ufeat = torch.bucketize(uniq, base, right=True) - 1 if uniq.numel() else uniq
+    counts = torch.bincount(ufeat, minlength=F) if uniq.numel() else torch.zeros(F, dtype=torch.int64, device=indices.device)
+    unique = (uniq - base.index_select(0, ufeat)) if uniq.numel() else uniq
+    return counts, unique.to(indices.dtype), reverse.to(indices.dtype)
+
+
 def jagged_unique_indices(
     hash_size_cumsum: torch.Tensor,
     hash_size_offsets: torch.Tensor,
@@ -421,21 +459,10 @@ def jagged_unique_indices(
     ``unique_indices[output_offsets[f]:output_offsets[f+1]]`` are the sorted distinct ids of
     feature ``f`` and ``unique_indices[reverse_index[i]] == indices[i]``.
     """
-    F = hash_size_offsets.numel() - 1
-    n_bags = offsets.numel() - 1
-    B = n_bags // max(F, 1)
-    off = offsets.to(torch.int64)
-    N = indices.numel()
-    bag = lengths_range(off[1:] - off[:-1], N)
-    feat = bag // max(B, 1)
     base = hash_size_cumsum.to(torch.int64)[hash_size_offsets.to(torch.int64)[:-1]]
-    lin = indices.to(torch.int64) + base.index_select(0, feat) if N else indices.to(torch.int64)
-    uniq, reverse = torch.unique(lin, sorted=True, return_inverse=True)
-    ufeat = torch.bucketize(uniq, base, right=True) - 1 if uniq.numel() else uniq
-    out_len = torch.bincount(ufeat, minlength=F) if uniq.numel() else torch.zeros(F, dtype=torch.int64, device=indices.device)
+    out_len, unique_indices, reverse = unique_ids_per_feature(base, offsets, indices)
     out_off = asynchronous_complete_cumsum(out_len)
-    unique_indices = (uniq - base.index_select(0, ufeat)) if uniq.numel() else uniq
-    return out_len.to(offsets.dtype), out_off.to(offsets.dtype), unique_indices.to(indices.dtype), reverse.to(indices.dtype)
+    return out_len.to(offsets.dtype), out_off.to(offsets.dtype), unique_indices, reverse
 
 
 # --------------------------------------------------------------------------------------
