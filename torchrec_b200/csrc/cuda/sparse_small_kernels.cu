@@ -1,7 +1,7 @@
 // Small sparse-data kernels that the Python layer would otherwise compose from several library launches:
 //
 //   offsets_range     position of every element inside its segment (an arange that restarts at every segment start)
-//   segment_sum_csr   sum of values over [csr[i] * batch, csr[i + 1] * batch): one warp per segment
+//   segment_sum_csr   sum of values over [csr[i] * batch, csr[i + 1] * batch): blocks over (segment, slice), then the slices in order
 //   vbe_expand        variable-batch pooled output -> full batch: every (feature, sample) copies the row that the inverse
 //                     indices name, straight to its output column (replaces one index_select per feature plus a concat)
 //
@@ -35,18 +35,38 @@ __global__ void __launch_bounds__(256) offsets_range_kernel(const T* __restrict_
   out[i] = T(i - int64_t(starts[lo]));
 }
 
+// pass 1: block (segment, slice) sums its slice of the segment in double; pass 2: one thread per segment adds the slices in order
+// (deterministic; integer inputs stay exact up to 2^53, floats get a wider accumulator than their own type)
 template <typename V, typename I>
 __global__ void __launch_bounds__(256) segment_sum_csr_kernel(const I* __restrict__ csr, int64_t batch, const V* __restrict__ values,
-                                                              V* __restrict__ out, int64_t n_seg) {
-  const int lane = threadIdx.x & 31;
-  const int64_t seg = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  if (seg >= n_seg) return;
+                                                              double* __restrict__ partial, int slices) {
+  __shared__ double red[8];
+  const int64_t seg = blockIdx.x;
+  const int sl = blockIdx.y;
   const int64_t lo = int64_t(csr[seg]) * batch, hi = int64_t(csr[seg + 1]) * batch;
-  double acc = 0.0;  // integer inputs stay exact up to 2^53, floats get a wider accumulator than their own type
-  for (int64_t i = lo + lane; i < hi; i += 32) acc += double(values[i]);
+  const int64_t per = (hi - lo + slices - 1) / slices;
+  const int64_t a = lo + sl * per, b = a + per < hi ? a + per : hi;
+  double acc = 0.0;
+  for (int64_t i = a + threadIdx.x; i < b; i += blockDim.x) acc += double(values[i]);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) out[seg] = V(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w];
+    partial[seg * slices + sl] = t;
+  }
+}
+
+template <typename V>
+__global__ void segment_sum_finish_kernel(const double* __restrict__ partial, int slices, V* __restrict__ out, int64_t n_seg) {
+  const int64_t seg = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (seg >= n_seg) return;
+  double t = 0.0;
+  for (int s = 0; s < slices; ++s) t += partial[seg * slices + s];
+  out[seg] = V(t);
 }
 
 // flat: the per-feature outputs [b_f, D_f] back to back; desc (int64 [F, 4]): flat offset, b_f, D_f, output column
@@ -93,12 +113,19 @@ at::Tensor segment_sum_csr(int64_t batch, const at::Tensor& csr, const at::Tenso
   at::Tensor out = at::empty({n_seg}, values.options());
   if (n_seg == 0) return out;
   auto stream = at::cuda::getCurrentCUDAStream();
-  const int64_t blocks = (n_seg * 32 + 255) / 256;
+  // enough (segment, slice) blocks to fill the GPU, but no slice shorter than a few thousand elements
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  const int64_t avg = std::max<int64_t>(values.numel() / n_seg, 1);
+  const int slices = int(std::max<int64_t>(1, std::min<int64_t>({(int64_t(sms) * 4 + n_seg - 1) / n_seg, (avg + 4095) / 4096, int64_t(1024)})));
+  TORCH_CHECK(n_seg <= 2147483647, "too many segments");
+  at::Tensor partial = at::empty({n_seg * slices}, values.options().dtype(at::kDouble));
+  const dim3 grid(static_cast<unsigned>(n_seg), static_cast<unsigned>(slices));
   AT_DISPATCH_ALL_TYPES_AND2(at::kHalf, at::kBFloat16, values.scalar_type(), "segment_sum_csr", [&] {
     if (csr.scalar_type() == at::kLong)
-      segment_sum_csr_kernel<scalar_t, int64_t><<<blocks, 256, 0, stream>>>(csr.data_ptr<int64_t>(), batch, values.data_ptr<scalar_t>(), out.data_ptr<scalar_t>(), n_seg);
+      segment_sum_csr_kernel<scalar_t, int64_t><<<grid, 256, 0, stream>>>(csr.data_ptr<int64_t>(), batch, values.data_ptr<scalar_t>(), partial.data_ptr<double>(), slices);
     else
-      segment_sum_csr_kernel<scalar_t, int32_t><<<blocks, 256, 0, stream>>>(csr.data_ptr<int32_t>(), batch, values.data_ptr<scalar_t>(), out.data_ptr<scalar_t>(), n_seg);
+      segment_sum_csr_kernel<scalar_t, int32_t><<<grid, 256, 0, stream>>>(csr.data_ptr<int32_t>(), batch, values.data_ptr<scalar_t>(), partial.data_ptr<double>(), slices);
+    segment_sum_finish_kernel<scalar_t><<<unsigned((n_seg + 255) / 256), 256, 0, stream>>>(partial.data_ptr<double>(), slices, out.data_ptr<scalar_t>(), n_seg);
   });
   TRB_CUDA_CHECK(cudaGetLastError());
   return out;
@@ -161,7 +188,7 @@ template <typename I>
 __global__ void __launch_bounds__(256) unique_scatter_kernel(const int64_t* __restrict__ key_sorted, const int64_t* __restrict__ pos_sorted,
                                                              const int32_t* __restrict__ head, const int64_t* __restrict__ rank, int64_t N,
                                                              const int64_t* __restrict__ feat_base, int64_t F, I* __restrict__ unique, I* __restrict__ reverse,
-                                                             int64_t* __restrict__ per_feature) {
+                                                             int64_t* __restrict__ unique_key) {
   const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= N) return;
   const int64_t r = rank[i] - 1;
@@ -169,8 +196,28 @@ __global__ void __launch_bounds__(256) unique_scatter_kernel(const int64_t* __re
   if (head[i]) {
     const int64_t f = last_not_above(feat_base, F, key_sorted[i]);
     unique[r] = I(key_sorted[i] - feat_base[f]);
-    atomicAdd(reinterpret_cast<unsigned long long*>(per_feature + f), 1ull);
+    unique_key[r] = key_sorted[i];
   }
+}
+
+// distinct ids per feature from the sorted unique keys: the keys of feature f lie in [base[f], base[f + 1]) (features that share a
+// base: everything is counted under the last of them, the others get 0); one thread per feature, no atomics
+__global__ void unique_count_kernel(const int64_t* __restrict__ unique_key, const int64_t* __restrict__ rank, int64_t N, const int64_t* __restrict__ feat_base,
+                                    int64_t F, int64_t* __restrict__ per_feature) {
+  const int64_t f = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (f >= F) return;
+  const int64_t U = rank[N - 1];
+  auto first_not_below = [&](int64_t v) {
+    int64_t lo = 0, hi = U;
+    while (lo < hi) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (unique_key[mid] < v) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+  };
+  const int64_t begin = first_not_below(feat_base[f]);
+  const int64_t end = (f + 1 < F) ? first_not_below(feat_base[f + 1]) : U;
+  per_feature[f] = end - begin;
 }
 
 // feat_base [F] ascending: the id base of every feature's table.  Returns (distinct ids per feature [F] int64, unique ids (feature-major,
@@ -207,11 +254,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> jagged_unique_indices(const at::T
   at::Tensor stmp = at::empty({int64_t(sbytes)}, indices.options().dtype(at::kByte));
   cub::DeviceScan::InclusiveSum(stmp.data_ptr(), sbytes, head.data_ptr<int32_t>(), rank.data_ptr<int64_t>(), N, stream);
   at::Tensor unique = at::empty({N}, indices.options()), reverse = at::empty({N}, indices.options());
+  at::Tensor unique_key = key;  // the unsorted keys are no longer needed: their buffer takes the sorted distinct keys
   AT_DISPATCH_INDEX_TYPES(indices.scalar_type(), "jagged_unique_scatter", [&] {
     unique_scatter_kernel<index_t><<<blocks, 256, 0, stream>>>(key_s.data_ptr<int64_t>(), pos_s.data_ptr<int64_t>(), head.data_ptr<int32_t>(), rank.data_ptr<int64_t>(), N,
                                                               feat_base.data_ptr<int64_t>(), F, unique.data_ptr<index_t>(), reverse.data_ptr<index_t>(),
-                                                              per_feature.data_ptr<int64_t>());
+                                                              unique_key.data_ptr<int64_t>());
   });
+  unique_count_kernel<<<unsigned((F + 127) / 128), 128, 0, stream>>>(unique_key.data_ptr<int64_t>(), rank.data_ptr<int64_t>(), N, feat_base.data_ptr<int64_t>(), F,
+                                                                    per_feature.data_ptr<int64_t>());
   TRB_CUDA_CHECK(cudaGetLastError());
   const int64_t distinct = rank[N - 1].item<int64_t>();  // the only host read: the output's size
   return {per_feature, unique.narrow(0, 0, distinct), reverse};

@@ -198,6 +198,33 @@ def bench_sparse_kernels(B: int, n: int, warm: int) -> None:
     perm = torch.randperm(F, device="cuda").to(torch.int32)
     t = timeit(lambda: sops.permute_2D_sparse_data(perm, lengths.view(F, B), idx, None, idx.numel()), n, warm)
     print(f"permute 2-D jagged {idx.numel()} ids: {t:.3f} ms, {idx.numel() * 16 / t / 1e6:.0f} GB/s", flush=True)
+    # the small jagged helpers
+    offsets = torch.cat([torch.zeros(1, dtype=torch.int64, device="cuda"), lengths.cumsum(0)])
+    t = timeit(lambda: sops.offsets_range(offsets[:-1], idx.numel()), n, warm)
+    print(f"offsets_range over {idx.numel()} positions: {t:.3f} ms, {idx.numel() * 8 / t / 1e6:.0f} GB/s written", flush=True)
+    csr = torch.arange(0, F * pf + 1, pf, dtype=torch.int64, device="cuda")
+    vals = torch.rand(idx.numel(), device="cuda")
+    t = timeit(lambda: sops.segment_sum_csr(B, csr, vals), n, warm)
+    print(f"segment_sum_csr of {idx.numel()} floats into {F} segments: {t:.3f} ms, {idx.numel() * 4 / t / 1e6:.0f} GB/s", flush=True)
+    base = torch.arange(F, dtype=torch.int64, device="cuda") * rows
+    bound = torch.tensor([F * rows], device="cuda")
+    t = timeit(lambda: sops.unique_ids_per_feature(base, offsets, idx, bound), n, warm)
+    t_lib = timeit(lambda: torch.unique(idx + base.repeat_interleave(B * pf), sorted=True, return_inverse=True), n, warm)
+    print(f"per-feature unique of {idx.numel()} ids (sort + flags + scan + scatter): {t:.3f} ms (torch.unique on pre-linearized keys: {t_lib:.3f} ms)", flush=True)
+    D = 256
+    values = torch.randn(idx.numel() // 4, D, device="cuda").bfloat16()
+    seq_len = torch.randint(20, 201, (values.shape[0] // 110,), device="cuda")
+    seq_len[-1] += values.shape[0] - int(seq_len.sum()) if int(seq_len.sum()) < values.shape[0] else 0
+    seq_off = torch.cat([torch.zeros(1, dtype=torch.int64, device="cuda"), seq_len.cumsum(0)]).clamp(max=values.shape[0])
+    t = timeit(lambda: sops.jagged_to_padded_dense(values, seq_off, 200, 0.0), n, warm)
+    print(f"jagged_to_padded_dense {values.shape[0]} x {D} bf16 rows -> [{seq_len.numel()}, 200, {D}]: {t:.3f} ms, "
+          f"{(values.numel() + seq_len.numel() * 200 * D) * 2 / t / 1e6:.0f} GB/s", flush=True)
+    from torchrec_b200.ops.quant_ops import quantize_rowwise_nbit
+
+    w = torch.randn(4_000_000, 128, device="cuda")
+    for bits in (8, 4):
+        t = timeit(lambda: quantize_rowwise_nbit(w, bits), n, warm)
+        print(f"row-wise int{bits} quantization of [{w.shape[0]}, 128] fp32: {t:.3f} ms, {(w.numel() * 4 + w.shape[0] * (128 * bits // 8 + 4)) / t / 1e6:.0f} GB/s", flush=True)
 
 
 def bench_engine(B: int, n: int, warm: int) -> None:

@@ -171,7 +171,7 @@ def _dedup_indices(ctx: EmbeddingCollectionContext, features: KeyedJaggedTensor,
     ``unique_rows[reverse_indices]``.  Ids of different features never merge (offset by ``hash_offsets``)."""
     with record_function("## dedup_ec_indices ##"):
         values = features.values()
-        counts, unique_ids, reverse = sops.unique_ids_per_feature(hash_offsets[: len(features.keys())], features.offsets(), values)
+        counts, unique_ids, reverse = sops.unique_ids_per_feature(hash_offsets[: len(features.keys())], features.offsets(), values, bound=hash_offsets)
         stride = features.stride()
         # spread each feature's unique ids over its `stride` bags: first bags get ceil, rest floor (any split works,
         # the rows are re-expanded by `reverse` and the original lengths afterwards)

@@ -410,21 +410,24 @@ def jagged_1d_to_dense(values: torch.Tensor, offsets: torch.Tensor, max_sequence
 _key_bits_cache: dict = {}
 
 
-def _key_bits(feat_base: torch.Tensor, indices: torch.Tensor) -> int:
-    """Bits the radix sort has to look at: enough for the largest linearized id.  The bases rarely change, so the one host read
-    this needs is cached per base tensor; the bound on the ids' own width comes from their dtype."""
-    key = (feat_base.data_ptr(), feat_base.numel(), indices.dtype)
+def _key_bits(feat_base: torch.Tensor, indices: torch.Tensor, bound: Optional[torch.Tensor]) -> int:
+    """Bits the radix sort has to look at: enough for the largest linearized id.  ``bound`` (any tensor whose maximum is the total
+    number of rows of all tables) gives it exactly; without it the ids' own width is bounded by their dtype.  The bases rarely
+    change, so the one host read this needs is cached per tensor."""
+    src = feat_base if bound is None else bound
+    key = (src.data_ptr(), src.numel(), indices.dtype, bound is None)
     bits = _key_bits_cache.get(key)
     if bits is None:
-        top = int(feat_base.max().item()) if feat_base.numel() else 0
-        bits = min(64, max(top.bit_length(), 31 if indices.dtype == torch.int32 else 40) + 1)
+        top = int(src.max().item()) if src.numel() else 0
+        bits = top.bit_length() + 1 if bound is not None else min(64, max(top.bit_length(), 31 if indices.dtype == torch.int32 else 40) + 1)
         if len(_key_bits_cache) > 64:
             _key_bits_cache.clear()
         _key_bits_cache[key] = bits
     return bits
 
 
-def unique_ids_per_feature(feat_base: torch.Tensor, offsets: torch.Tensor, indices: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def unique_ids_per_feature(feat_base: torch.Tensor, offsets: torch.Tensor, indices: torch.Tensor,
+                           bound: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """``(distinct ids per feature [F], unique ids, reverse index)`` for ids in feature-major bags; ``feat_base [F]`` (ascending) is the
     id base of every feature's table: two features with the same base share a table and are deduplicated together (their ids
     are counted under the last of them).  Unique ids are feature-major and ascending inside a feature;
@@ -433,7 +436,7 @@ def unique_ids_per_feature(feat_base: torch.Tensor, offsets: torch.Tensor, indic
     N = indices.numel()
     base = feat_base.to(torch.int64)
     if _kern(indices, "jagged_unique_indices") and N > 0:
-        return torch.ops.trb200.jagged_unique_indices(base.contiguous(), offsets.to(torch.int64).contiguous(), indices.contiguous(), _key_bits(base, indices))
+        return torch.ops.trb200.jagged_unique_indices(base.contiguous(), offsets.to(torch.int64).contiguous(), indices.contiguous(), _key_bits(base, indices, bound))
     off = offsets.to(torch.int64)
     B = max((off.numel() - 1) // max(F, 1), 1)
     feat = lengths_range(off[1:] - off[:-1], N) // B if N else indices.to(torch.int64)
@@ -460,7 +463,7 @@ def jagged_unique_indices(
     feature ``f`` and ``unique_indices[reverse_index[i]] == indices[i]``.
     """
     base = hash_size_cumsum.to(torch.int64)[hash_size_offsets.to(torch.int64)[:-1]]
-    out_len, unique_indices, reverse = unique_ids_per_feature(base, offsets, indices)
+    out_len, unique_indices, reverse = unique_ids_per_feature(base, offsets, indices, bound=hash_size_cumsum)
     out_off = asynchronous_complete_cumsum(out_len)
     return out_len.to(offsets.dtype), out_off.to(offsets.dtype), unique_indices, reverse
 
