@@ -11,6 +11,7 @@ from torch import nn
 from torchrec_b200.distributed.embedding_types import BaseQuantEmbeddingSharder
 from torchrec_b200.distributed.quant_embeddingbag import _device_for
 from torchrec_b200.distributed.types import ParameterSharding, ShardingEnv, ShardingType
+from torchrec_b200.distributed.quant_input_dist import ShardedQuantEcInputDist  # noqa: F401  (also the reference's import path for it)
 from torchrec_b200.distributed.quant_state import ShardedQuantEmbeddingModuleState
 from torchrec_b200.quant.embedding_modules import EmbeddingCollection as QuantEmbeddingCollection
 from torchrec_b200.quant.embedding_modules import QuantManagedCollisionEmbeddingCollection
@@ -91,39 +92,31 @@ class ShardedQuantEmbeddingCollection(ShardedQuantEmbeddingModuleState, nn.Modul
         self._rw_out_names: List[str] = [module._name_of[f"{cfg.name}:{f}"] for cfg, _ in self._rw_tables for f in cfg.feature_names]
         self.register_buffer("_rw_block_sizes", torch.tensor([b for cfg, b in self._rw_tables for _ in cfg.feature_names], dtype=torch.int64), persistent=False)
         self._name_of = dict(module._name_of)
+        self._input_dist = ShardedQuantEcInputDist(
+            self._world_size, self._device_type, dict(enumerate(self._feature_names_per_rank)), dict(self._cw_features),
+            {key: int(key.split("_")[0]) for key in self._cw_features}, self._rw_feature_names, self._rw_block_sizes)
         self._init_quant_state("embeddings", {c.name: table_name_to_parameter_sharding[c.name].sharding_type for c in self._configs})
 
     def forward(self, features: KeyedJaggedTensor) -> Dict[str, JaggedTensor]:
-        from torchrec_b200.distributed.embedding_sharding import bucketize_kjt_before_all2all
-
-        keys = features.keys()
+        dist = self._input_dist(features)
         out: Dict[str, JaggedTensor] = {}
-        for rank, (shard, fnames) in enumerate(zip(self._shards, self._feature_names_per_rank)):
-            if not fnames:
-                continue
-            dev = _device_for(rank, self._device_type)
-            local = features.permute([keys.index(f) for f in fnames]).to(dev, non_blocking=True)
-            for k, jt in shard(local).items():
+        for rank, local in dist.table_wise.items():
+            for k, jt in self._shards[rank](local).items():
                 out[k] = jt.to(self._out_device)
-        if self._rw_feature_names:
+        if dist.row_wise:
             F = len(self._rw_feature_names)
-            rw_in = features.permute([keys.index(f) for f in self._rw_feature_names])
-            bucketized, unbucketize = bucketize_kjt_before_all2all(rw_in, num_buckets=self._world_size, block_sizes=self._rw_block_sizes.to(rw_in.values().device), output_permute=True)
+            rw_in = dist.row_wise_request
             rows = []
-            for rank, part in enumerate(bucketized.split([F] * self._world_size)):
-                local = KeyedJaggedTensor(keys=self._rw_feature_names, values=part.values(), lengths=part.lengths(), stride=features.stride())
-                got = self._rw_shards[rank](local.to(_device_for(rank, self._device_type), non_blocking=True))
+            for rank, local in enumerate(dist.row_wise):
+                got = self._rw_shards[rank](local)
                 rows.extend(got[n].values().to(self._out_device, non_blocking=True) for n in self._rw_out_names)
             # bucketized order is (device, feature, sample): undo it to the request's (feature, sample) order
-            ordered = torch.cat(rows).index_select(0, unbucketize.to(self._out_device).long())
+            ordered = torch.cat(rows).index_select(0, dist.unbucketize_permute.to(self._out_device).long())
             lengths = rw_in.lengths().view(F, -1).to(self._out_device)
             ids = rw_in.values().to(self._out_device).split(rw_in.length_per_key()) if self._need_indices else None
             for i, (name, piece) in enumerate(zip(self._rw_out_names, ordered.split(rw_in.length_per_key()))):
                 out[name] = JaggedTensor(values=piece, lengths=lengths[i], weights=ids[i] if ids is not None else None)
-        cw_out: Dict[str, Dict[str, JaggedTensor]] = {}
-        for key, shard in self._cw_shards.items():
-            dev = _device_for(int(key.split("_")[0]), self._device_type)
-            cw_out[key] = shard(features.permute([keys.index(f) for f in self._cw_features[key]]).to(dev, non_blocking=True))
+        cw_out: Dict[str, Dict[str, JaggedTensor]] = {key: self._cw_shards[key](local) for key, local in dist.column_wise.items()}
         for cfg, ranks, width in self._cw_tables:
             per_rank = [cw_out[f"{r}_{width}"] for r in ranks]
             for f in cfg.feature_names:

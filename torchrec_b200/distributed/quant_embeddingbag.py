@@ -17,6 +17,7 @@ from torch import nn
 from torchrec_b200.distributed.embedding_types import BaseQuantEmbeddingSharder
 from torchrec_b200.distributed.types import ParameterSharding, ShardingEnv, ShardingType
 from torchrec_b200.modules.embedding_configs import PoolingType
+from torchrec_b200.distributed.quant_input_dist import ShardedQuantEbcInputDist  # noqa: F401  (also the reference's import path for it)
 from torchrec_b200.distributed.quant_state import ShardedQuantEmbeddingModuleState
 from torchrec_b200.quant.embedding_modules import EmbeddingBagCollection as QuantEmbeddingBagCollection
 from torchrec_b200.quant.embedding_modules import FeatureProcessedEmbeddingBagCollection as QuantFeatureProcessedEmbeddingBagCollection
@@ -127,42 +128,37 @@ class ShardedQuantEmbeddingBagCollection(ShardedQuantEmbeddingModuleState, nn.Mo
                 self._name_table[self._embedding_names[i]] = cfg.name
                 i += 1
 
+        self._input_dist = ShardedQuantEbcInputDist(
+            W, self._device_type, dict(enumerate(self._feature_names_per_rank)), dict(enumerate(self._cw_feature_names_per_rank)), {r: r for r in range(W)},
+            self._rw_feature_names, self._rw_block_sizes)
         self._init_quant_state("embedding_bags", {c.name: table_name_to_parameter_sharding[c.name].sharding_type for c in self._configs})
 
     def _local(self, features: KeyedJaggedTensor, keys: List[str], names: List[str], rank: int) -> KeyedJaggedTensor:
         return features.permute([keys.index(f) for f in names]).to(_device_for(rank, self._device_type), non_blocking=True)
 
     def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
-        from torchrec_b200.distributed.embedding_sharding import bucketize_kjt_before_all2all
-
         keys = features.keys()
         if self._device_type == "cuda" and not self._rw_feature_names:
             return self._forward_direct(features, keys)
+        dist = self._input_dist(features)
         pieces: Dict[str, torch.Tensor] = {}
-        for rank, (shard, fnames) in enumerate(zip(self._shards, self._feature_names_per_rank)):
-            if fnames:
-                for k, v in shard(self._local(features, keys, fnames, rank)).to_dict().items():
-                    pieces[k] = v.to(self._out_device, non_blocking=True)
-        if self._rw_feature_names:
-            rw_in = features.permute([keys.index(f) for f in self._rw_feature_names])
-            bucketized, _ = bucketize_kjt_before_all2all(rw_in, num_buckets=self._world_size, block_sizes=self._rw_block_sizes.to(rw_in.values().device))
-            for rank, part in enumerate(bucketized.split([len(self._rw_feature_names)] * self._world_size)):
-                local = KeyedJaggedTensor(keys=self._rw_feature_names, values=part.values(), weights=part.weights_or_none(), lengths=part.lengths(), stride=features.stride())
-                out = self._rw_shards[rank](local.to(_device_for(rank, self._device_type), non_blocking=True)).to_dict()
-                for k, v in out.items():
-                    v = v.to(self._out_device, non_blocking=True)
-                    pieces[k] = v if k not in pieces or rank == 0 else pieces[k] + v
-            if self._rw_mean_features:
-                lens = rw_in.lengths().view(len(self._rw_feature_names), -1).to(self._out_device)
-                for name in self._embedding_names:
-                    f = name.split("@")[0]
-                    if self._name_kind.get(name) == "rw" and f in self._rw_mean_features:
-                        pieces[name] = pieces[name] / lens[self._rw_feature_names.index(f)].clamp(min=1).unsqueeze(1).to(pieces[name].dtype)
+        for rank, local in dist.table_wise.items():
+            for k, v in self._shards[rank](local).to_dict().items():
+                pieces[k] = v.to(self._out_device, non_blocking=True)
+        for rank, local in enumerate(dist.row_wise):
+            for k, v in self._rw_shards[rank](local).to_dict().items():
+                v = v.to(self._out_device, non_blocking=True)
+                pieces[k] = v if k not in pieces or rank == 0 else pieces[k] + v
+        if dist.row_wise and self._rw_mean_features:
+            lens = dist.row_wise_request.lengths().view(len(self._rw_feature_names), -1).to(self._out_device)
+            for name in self._embedding_names:
+                f = name.split("@")[0]
+                if self._name_kind.get(name) == "rw" and f in self._rw_mean_features:
+                    pieces[name] = pieces[name] / lens[self._rw_feature_names.index(f)].clamp(min=1).unsqueeze(1).to(pieces[name].dtype)
         cw_parts: Dict[str, Dict[int, torch.Tensor]] = {}
-        for rank, (shard, fnames) in enumerate(zip(self._cw_shards, self._cw_feature_names_per_rank)):
-            if fnames:
-                for k, v in shard(self._local(features, keys, fnames, rank)).to_dict().items():
-                    cw_parts.setdefault(k, {})[rank] = v.to(self._out_device, non_blocking=True)
+        for rank, local in dist.column_wise.items():
+            for k, v in self._cw_shards[rank](local).to_dict().items():
+                cw_parts.setdefault(k, {})[rank] = v.to(self._out_device, non_blocking=True)
         for name, by_rank in cw_parts.items():
             pieces[name] = torch.cat([by_rank[r] for r in self._cw_order[self._name_table[name]]], dim=1)
         values = torch.cat([pieces[n] for n in self._embedding_names], dim=1)
