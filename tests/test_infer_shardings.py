@@ -1,0 +1,108 @@
+"""Inference sharding strategies on two virtual devices (host): request -> input distribution -> all-device quantized lookup ->
+output distribution, against plain torch on the dequantized tables."""
+import pytest
+import torch
+
+from torchrec_b200.distributed import sharding_plan as sp
+from torchrec_b200.distributed.embedding_sharding import EmbeddingShardingInfo
+from torchrec_b200.distributed.quant_embeddingbag import QuantEmbeddingBagCollectionSharder
+from torchrec_b200.distributed.types import ShardingEnv
+from torchrec_b200.modules.embedding_configs import DataType, EmbeddingTableConfig, PoolingType
+from torchrec_b200.ops.quant_ops import dequantize_rowwise_nbit, quantize_rowwise_nbit
+from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+W = 2
+TABLES = [("t0", "f0", 40, 16), ("t1", "f1", 30, 16), ("t2", "f2", 50, 16)]
+
+
+def _infos(how, pooled):
+    sharder = QuantEmbeddingBagCollectionSharder()
+    infos = []
+    for i, (name, feat, rows, dim) in enumerate(TABLES):
+        cfg = EmbeddingTableConfig(name=name, embedding_dim=dim, num_embeddings=rows, feature_names=[feat], data_type=DataType.INT8,
+                                   pooling=PoolingType.SUM if pooled else PoolingType.NONE, embedding_names=[feat])
+        gen = {"tw": sp.table_wise(rank=i % W), "rw": sp.row_wise(), "cw": sp.column_wise(ranks=[0, 1])}[how]
+        ps = gen(torch.empty(rows, dim, device="meta"), W, W, "cpu", sharder)
+        infos.append(EmbeddingShardingInfo(embedding_config=cfg, param_sharding=ps, param=torch.empty(rows, dim, device="meta")))
+    return infos
+
+
+def _request(gen, B=6):
+    keys = [f for _, f, _, _ in TABLES]
+    lengths = torch.randint(0, 4, (len(keys) * B,), generator=gen)
+    values = torch.cat([torch.randint(0, rows, (int(lengths[i * B:(i + 1) * B].sum()),), generator=gen) for i, (_, _, rows, _) in enumerate(TABLES)])
+    return KeyedJaggedTensor.from_lengths_sync(keys=keys, values=values, lengths=lengths)
+
+
+def _fill(lookup, gen):
+    """Random quantized rows in every shard; returns the dequantized full tables, assembled from the shards' metadata."""
+    full = {name: torch.zeros(rows, dim) for name, _, rows, dim in TABLES}
+    for per_device in lookup._embedding_lookups_per_rank:
+        for kernel in per_device._emb_modules:
+            for table, buf in zip(kernel.config.embedding_tables, kernel.split_embedding_weights()):
+                w = torch.randn(table.local_rows, table.local_cols, generator=gen)
+                buf.copy_(quantize_rowwise_nbit(w, 8))
+                r0, c0 = table.local_metadata.shard_offsets
+                full[table.name][r0:r0 + table.local_rows, c0:c0 + table.local_cols] = dequantize_rowwise_nbit(buf, table.local_cols, 8)
+    return full
+
+
+def _pooled_oracle(kjt, full):
+    cols = []
+    for (name, feat, _, _) in TABLES:
+        jt = kjt[feat]
+        off = jt.offsets()
+        cols.append(torch.stack([full[name][jt.values()[int(a):int(b)]].sum(0) for a, b in zip(off[:-1], off[1:])]))
+    return cols
+
+
+@pytest.mark.parametrize("how", ["tw", "rw", "cw"])
+def test_pooled_inference_strategies(how):
+    from torchrec_b200.distributed.sharding import cw_sharding, rw_sharding, tw_sharding
+
+    gen = torch.Generator().manual_seed(0)
+    env = ShardingEnv.from_local(world_size=W, rank=0)
+    cpu = torch.device("cpu")
+    cls = {"tw": tw_sharding.InferTwEmbeddingSharding, "rw": rw_sharding.InferRwPooledEmbeddingSharding, "cw": cw_sharding.InferCwPooledEmbeddingSharding}[how]
+    sharding = cls(_infos(how, True), env, cpu, permute_embeddings=True) if how == "cw" else cls(_infos(how, True), env, cpu)
+    idist, lookup, odist = sharding.create_input_dist(cpu), sharding.create_lookup(cpu), sharding.create_output_dist(cpu)
+    full = _fill(lookup, gen)
+    kjt = _request(gen)
+    feats = kjt.permute([kjt.keys().index(f) for f in sharding.feature_names()]) if how != "rw" else kjt
+    out = odist(lookup(idist(feats)))
+    want = dict(zip([t[0] for t in TABLES], _pooled_oracle(kjt, full)))
+    names = sharding.embedding_names()
+    dims = sharding.embedding_dims()
+    assert out.shape == (6, sum(dims))
+    col = 0
+    for name, d in zip(names, dims):
+        table = next(t[0] for t in TABLES if t[1] == name or name.startswith(t[1]))
+        torch.testing.assert_close(out[:, col:col + d].float(), want[table][:, :d] if d == 16 else want[table][:, :d], rtol=1e-3, atol=1e-3)
+        col += d
+
+
+@pytest.mark.parametrize("how", ["tw", "rw"])
+def test_sequence_inference_strategies(how):
+    from torchrec_b200.distributed.sharding import rw_sequence_sharding, tw_sequence_sharding
+
+    gen = torch.Generator().manual_seed(1)
+    env = ShardingEnv.from_local(world_size=W, rank=0)
+    cpu = torch.device("cpu")
+    cls = {"tw": tw_sequence_sharding.InferTwSequenceEmbeddingSharding, "rw": rw_sequence_sharding.InferRwSequenceEmbeddingSharding}[how]
+    sharding = cls(_infos(how, False), env, cpu)
+    idist, lookup, odist = sharding.create_input_dist(cpu), sharding.create_lookup(cpu), sharding.create_output_dist(cpu)
+    full = _fill(lookup, gen)
+    kjt = _request(gen)
+    if how == "tw":
+        feats = kjt.permute([kjt.keys().index(f) for f in sharding.feature_names()])
+        dist_out = idist(feats)
+        rows = odist(lookup(dist_out))
+        for per_device, names, local in zip(rows, sharding.feature_names_per_rank(), dist_out.features):
+            want = torch.cat([full[next(t[0] for t in TABLES if t[1] == f)][local[f].values()] for f in names])
+            torch.testing.assert_close(per_device.float(), want, rtol=1e-3, atol=1e-3)
+    else:
+        dist_out = idist(kjt)
+        rows = torch.cat(odist(lookup(dist_out)))  # (device, feature, sample) order
+        ordered = rows.index_select(0, dist_out.unbucketize_permute_tensor.long())
+        want = torch.cat([full[name][kjt[feat].values()] for name, feat, _, _ in TABLES])
+        torch.testing.assert_close(ordered.float(), want, rtol=1e-3, atol=1e-3)

@@ -13,3 +13,16 @@ from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
 
 class CwSequenceEmbeddingSharding(_KeySplitSequenceRouting, BaseCwEmbeddingSharding[SequenceShardingContext, KeyedJaggedTensor, torch.Tensor, torch.Tensor]):
     sharding_type = ShardingType.COLUMN_WISE
+
+
+_INFER_NAMES = ("InferCwSequenceEmbeddingSharding", "InferCwSequenceEmbeddingDist")
+
+
+def __getattr__(name: str):
+    """The inference strategies live in ``infer_shardings`` (they build on every training strategy); they are reachable from
+    here under the reference's import path."""
+    if name in _INFER_NAMES:
+        from torchrec_b200.distributed.sharding import infer_shardings
+
+        return getattr(infer_shardings, name)
+    raise AttributeError(name)

@@ -99,3 +99,16 @@ class CwPooledEmbeddingSharding(_KeySplitPooledRouting, BaseCwEmbeddingSharding[
             return None
         assert len(self._embedding_order) == len(self._embedding_dims)
         return [PermutePooledEmbeddingsSplit(self._embedding_dims, self._embedding_order, device=device)]
+
+
+_INFER_NAMES = ("InferCwPooledEmbeddingSharding", "InferCwPooledEmbeddingDist", "InferCwPooledEmbeddingDistWithPermute")
+
+
+def __getattr__(name: str):
+    """The inference strategies live in ``infer_shardings`` (they build on every training strategy); they are reachable from
+    here under the reference's import path."""
+    if name in _INFER_NAMES:
+        from torchrec_b200.distributed.sharding import infer_shardings
+
+        return getattr(infer_shardings, name)
+    raise AttributeError(name)

@@ -32,3 +32,16 @@ class RwSequenceEmbeddingSharding(SequenceLookupMixin, BaseRwEmbeddingSharding[S
 
     def create_output_dist(self, device: Optional[torch.device] = None) -> RwSequenceEmbeddingDist:
         return RwSequenceEmbeddingDist(self._pg, self._get_num_features(), device if device is not None else self._device, self.qcomm_codecs_registry)
+
+
+_INFER_NAMES = ("InferRwSequenceEmbeddingDist", "InferRwSequenceEmbeddingSharding")
+
+
+def __getattr__(name: str):
+    """The inference strategies live in ``infer_shardings`` (they build on every training strategy); they are reachable from
+    here under the reference's import path."""
+    if name in _INFER_NAMES:
+        from torchrec_b200.distributed.sharding import infer_shardings
+
+        return getattr(infer_shardings, name)
+    raise AttributeError(name)

@@ -177,3 +177,16 @@ class InferRwPooledEmbeddingDist(BaseEmbeddingDist[NullShardingContext, List[tor
 
     def forward(self, local_embs: List[torch.Tensor], sharding_ctx: Optional[NullShardingContext] = None) -> torch.Tensor:
         return self._dist(local_embs)
+
+
+_INFER_NAMES = ("InferRwSparseFeaturesDist", "InferRwPooledEmbeddingSharding")
+
+
+def __getattr__(name: str):
+    """The inference strategies live in ``infer_shardings`` (they build on every training strategy); they are reachable from
+    here under the reference's import path."""
+    if name in _INFER_NAMES:
+        from torchrec_b200.distributed.sharding import infer_shardings
+
+        return getattr(infer_shardings, name)
+    raise AttributeError(name)

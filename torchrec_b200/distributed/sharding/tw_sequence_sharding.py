@@ -33,3 +33,16 @@ class _KeySplitSequenceRouting(SequenceLookupMixin):
 
 class TwSequenceEmbeddingSharding(_KeySplitSequenceRouting, BaseTwEmbeddingSharding[SequenceShardingContext, KeyedJaggedTensor, torch.Tensor, torch.Tensor]):
     sharding_type = ShardingType.TABLE_WISE
+
+
+_INFER_NAMES = ("InferTwSequenceEmbeddingDist", "InferTwSequenceEmbeddingSharding")
+
+
+def __getattr__(name: str):
+    """The inference strategies live in ``infer_shardings`` (they build on every training strategy); they are reachable from
+    here under the reference's import path."""
+    if name in _INFER_NAMES:
+        from torchrec_b200.distributed.sharding import infer_shardings
+
+        return getattr(infer_shardings, name)
+    raise AttributeError(name)
