@@ -516,3 +516,50 @@ def _as_sharded_like(template, full):
 @pytest.mark.parametrize("kind", ["rw", "cw"])
 def test_single_embedding_bag_sharded(kind):
     run_multi_process(_single_embedding_bag, world_size=2, kind=kind)
+
+
+def _tower_collection_run(rank, world_size):
+    """Two towers in one collection, sharded through the collection sharder: tower 0 on rank 0 (one owner), tower 1 row-wise (spread)."""
+    from torchrec_b200.distributed import sharding_plan as sp
+    from torchrec_b200.distributed.embedding_tower_sharding import EmbeddingTowerCollectionSharder
+    from torchrec_b200.distributed.model_parallel import DistributedModelParallel
+    from torchrec_b200.distributed.types import ShardingEnv, ShardingPlan
+    from torchrec_b200.modules.embedding_configs import EmbeddingBagConfig
+    from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
+    from torchrec_b200.modules.embedding_tower import EmbeddingTower, EmbeddingTowerCollection
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    with MultiProcessContext(rank, world_size, "gloo") as ctx:
+        torch.manual_seed(0)
+        B = 5
+        ebc_a = EmbeddingBagCollection(tables=[EmbeddingBagConfig(name="a0", embedding_dim=8, num_embeddings=40, feature_names=["fa"])])
+        ebc_b = EmbeddingBagCollection(tables=[EmbeddingBagConfig(name="b0", embedding_dim=8, num_embeddings=60, feature_names=["fb"])])
+        g = torch.nn.Module()
+        g.towers = EmbeddingTowerCollection([EmbeddingTower(ebc_a, _TowerInteraction(8)), EmbeddingTower(ebc_b, _TowerInteraction(8))])
+        l = copy.deepcopy(g)
+        sharder = EmbeddingTowerCollectionSharder()
+        inner = sharder._tower_sharder._embedding_sharder
+        plan = {}
+        plan.update(sp.construct_module_sharding_plan(l.towers.towers[0].embedding, {"a0": sp.table_wise(rank=0)}, sharder=inner, world_size=world_size,
+                                                      local_size=world_size, device_type="cpu"))
+        plan.update(sp.construct_module_sharding_plan(l.towers.towers[1].embedding, {"b0": sp.row_wise()}, sharder=inner, world_size=world_size,
+                                                      local_size=world_size, device_type="cpu"))
+        dmp = DistributedModelParallel(l, env=ShardingEnv.from_process_group(ctx.pg), device=torch.device("cpu"), plan=ShardingPlan({"towers": plan}),
+                                       sharders=sp.get_default_sharders() + [sharder])
+        dmp.load_state_dict(copy.deepcopy(g.state_dict()))
+        gen = torch.Generator().manual_seed(5)
+        per_rank = []
+        for r in range(world_size):
+            lens = torch.randint(0, 4, (2 * B,), generator=gen)
+            vals = torch.cat([torch.randint(0, 40, (int(lens[:B].sum()),), generator=gen), torch.randint(0, 60, (int(lens[B:].sum()),), generator=gen)])
+            per_rank.append(KeyedJaggedTensor.from_lengths_sync(keys=["fa", "fb"], values=vals, lengths=lens))
+        want = g.towers(per_rank[rank])
+        inner_module = dmp.module.module if hasattr(dmp.module, "module") else dmp.module
+        got = inner_module.towers(per_rank[rank])
+        assert got.shape == (B, 8)
+        torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
+        assert inner_module.towers.towers[0].owner_rank == 0 and inner_module.towers.towers[1].owner_rank == -1
+
+
+def test_embedding_tower_collection_sharder():
+    run_multi_process(_tower_collection_run, world_size=2)

@@ -175,3 +175,45 @@ class ShardedEmbeddingTowerCollection(nn.Module):
         for tower, (has_f, has_w) in zip(self.towers, self._input_params):
             pending.append(tower(features if has_f else weighted_features))
         return torch.cat([p.wait() for p in pending], dim=1)
+
+
+class EmbeddingTowerCollectionSharder(BaseEmbeddingSharder[EmbeddingTowerCollection]):
+    """Shards a whole ``EmbeddingTowerCollection``: the plan names every table of every tower (table names are unique across the
+    towers), each tower is sharded on its own with the tower sharder."""
+
+    def __init__(self, tower_sharder: Optional[EmbeddingTowerSharder] = None, qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None) -> None:
+        super().__init__(qcomm_codecs_registry=qcomm_codecs_registry)
+        self._tower_sharder = tower_sharder or EmbeddingTowerSharder(qcomm_codecs_registry=self.qcomm_codecs_registry)
+
+    def shard(self, module: EmbeddingTowerCollection, params: Dict[str, ParameterSharding], env: ShardingEnv, device: Optional[torch.device] = None,
+              module_fqn: Optional[str] = None) -> ShardedEmbeddingTowerCollection:
+        device = device if device is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        per_tower = []
+        for tower in module.towers:
+            names = [cfg.name for cfg in tower.embedding.embedding_bag_configs()]
+            missing = [n for n in names if n not in params]
+            assert not missing, f"the plan has no entry for the tower tables {missing}"
+            per_tower.append({n: params[n] for n in names})
+        return ShardedEmbeddingTowerCollection(module, per_tower, self._tower_sharder, env, device)
+
+    @property
+    def fused_params(self) -> Optional[Dict[str, Any]]:
+        return self._tower_sharder.fused_params
+
+    def shardable_parameters(self, module: EmbeddingTowerCollection) -> Dict[str, nn.Parameter]:
+        found: Dict[str, nn.Parameter] = {}
+        for tower in module.towers:
+            for name, p in self._tower_sharder.shardable_parameters(tower).items():
+                assert name not in found, f"table {name} appears in more than one tower"
+                found[name] = p
+        return found
+
+    @property
+    def module_type(self) -> Type[EmbeddingTowerCollection]:
+        return EmbeddingTowerCollection
+
+    def sharding_types(self, compute_device_type: str) -> List[str]:
+        return self._tower_sharder.sharding_types(compute_device_type)
+
+
+TowerLazyAwaitable = _TowerOutput  # the output of a one-owner tower, under the reference's name

@@ -498,3 +498,42 @@ def hash_planner_context_inputs(topology: Topology, batch_size: int, enumerator:
     reserved = storage_reservation.last_reserved_topology
     return hash_function([topology, batch_size, options, reserved, getattr(storage_reservation, "_last_reserved_topology", None),
                           sorted(constraints.items()) if constraints else None])
+
+
+def hash_planner_context_inputs_str(topology: Topology, batch_size: int, enumerator: Enumerator, storage_reservation: StorageReservation,
+                                    constraints: Optional[Dict[str, ParameterConstraints]], hash_function=hash_sha256_str) -> str:
+    """The same fingerprint as ``hash_planner_context_inputs``, as a hex string (what a stored plan carries)."""
+    return hash_planner_context_inputs(topology, batch_size, enumerator, storage_reservation, constraints, hash_function=hash_function)
+
+
+class PlanLoader(abc.ABC):
+    """Source of a plan computed earlier (to skip planning, or as the starting point of the next search).  ``load`` returns the stored
+    sharding options keyed by the hash of the enumerated option they stand for; ``plan_context_hash`` the fingerprint of the inputs
+    the stored plan was computed for, so that a loader can refuse a plan made for another model or topology."""
+
+    @abc.abstractmethod
+    def load(self) -> Optional[Dict[int, "ShardingOption"]]:
+        ...
+
+    @abc.abstractmethod
+    def plan_context_hash(self) -> Optional[str]:
+        ...
+
+
+@dataclass
+class CriticalPathEstimate:
+    """Time of the slowest rank, split into exchange and compute."""
+
+    comms_estimate: float
+    comp_estimate: float
+
+    def total(self) -> float:
+        return self.comms_estimate + self.comp_estimate
+
+
+@dataclass
+class PlanDebugStats:
+    """What a planner reports about itself next to the plan (for logging)."""
+
+    planner_type: str
+    timeout_seconds: Optional[int]

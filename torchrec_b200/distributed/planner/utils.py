@@ -4,7 +4,7 @@ from __future__ import annotations
 import math
 import operator
 from functools import reduce
-from typing import Any, Callable, Iterable, List, Optional, Type, Union
+from typing import Any, Callable, Iterable, List, Optional, Tuple, Type, Union
 
 import torch
 
@@ -87,3 +87,73 @@ class BinarySearchPredicate:
 
     def _mid(self) -> int:
         return self.left + ((self.right - self.left) // 2)
+
+
+def mb_to_bytes(mb: float) -> int:
+    return int(mb * 1024 * 1024)
+
+
+class LuusJaakolaSearch:
+    """Derivative-free minimisation of a scalar function on ``[A, B]`` by a clamped Luus-Jaakola random search: keep the best point
+    ``x``; probe ``y = clamp(x + u)`` with ``u`` uniform in ``[-d, d]``; a probe that is at least as good becomes the new ``x``, and the
+    step ``d`` shrinks by 5 % whenever that happens.  Probes never leave the interval, and a boundary whose cost is already
+    known is not probed again.
+
+    Protocol: ``y = s.next(0.0)`` gives the first point; every further ``s.next(f(y))`` reports the cost of the previous point and
+    returns the next one, or ``None`` after ``max_iterations`` costs; ``s.best()`` is the best ``(x, f(x))`` seen.
+    (``torchrec/distributed/planner/utils.py:177-265`` of the reference.)"""
+
+    def __init__(self, A: float, B: float, max_iterations: int, seed: int = 42, left_cost: Optional[float] = None) -> None:
+        import torch
+
+        self.left, self.right = float(A), float(B)
+        self.max_iterations = max_iterations
+        self.iteration = -1
+        self.gen = torch.Generator().manual_seed(seed)
+        self.d = self.right - self.left
+        self.x = self.uniform(self.left, self.right)
+        self.fx = 0.0
+        self.y = float("nan")
+        self.fleft: Optional[float] = left_cost
+        self.fright: Optional[float] = None
+
+    def uniform(self, A: float, B: float) -> float:
+        import torch
+
+        return A + (B - A) * float(torch.rand(1, generator=self.gen).item())
+
+    def clamp(self, x: float) -> float:
+        return min(max(x, self.left), self.right)
+
+    def shrink_right(self, B: float) -> None:
+        """The caller learned that everything from ``B`` on is infeasible: pull the right end in and treat its cost as infinite."""
+        self.right = float(B)
+        self.fright = float("inf")
+        self.d = self.right - self.left
+        self.x = self.clamp(self.x)
+
+    def next(self, fy: float) -> Optional[float]:
+        self.iteration += 1
+        if self.iteration == 0:
+            return self.x  # the starting point itself is the first probe
+        if self.iteration == 1:
+            self.fx = fy   # ... and this is its cost
+        elif self.iteration == self.max_iterations:
+            return None
+        elif fy <= self.fx:
+            self.x, self.fx = self.y, fy
+            self.d *= 0.95
+        if self.y == self.left:
+            self.fleft = fy
+        elif self.y == self.right:
+            self.fright = fy
+        for _ in range(10_000):  # a boundary with a known cost is skipped; bounded so that a degenerate interval cannot spin
+            y = self.clamp(self.x + self.uniform(-self.d, self.d))
+            if (y == self.left and self.fleft is not None) or (y == self.right and self.fright is not None):
+                continue
+            break
+        self.y = y
+        return y
+
+    def best(self) -> Tuple[float, float]:
+        return self.x, self.fx
