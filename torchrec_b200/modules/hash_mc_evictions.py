@@ -95,15 +95,48 @@ def get_eviction_scorer(policy_name: HashZchEvictionPolicyName, config: HashZchE
     raise ValueError(f"unsupported eviction policy {policy_name}")
 
 
+_SCORED_POLICIES = (HashZchEvictionPolicyName.SINGLE_TTL_EVICTION, HashZchEvictionPolicyName.PER_FEATURE_TTL_EVICTION, HashZchEvictionPolicyName.LRU_EVICTION)
+
+
+class HashZchThresholdEvictionModule(torch.nn.Module):
+    """Policies that score every id (expiry hour or last access) and give the lookup a threshold below which a slot may be taken over:
+    ``forward(feature, device) -> (score per id, threshold)``."""
+
+    def __init__(self, policy_name: HashZchEvictionPolicyName, config: HashZchEvictionConfig) -> None:
+        super().__init__()
+        self._policy_name, self._config = policy_name, config
+        self._eviction_scorer = get_eviction_scorer(policy_name, config)
+
+    def forward(self, feature: JaggedTensor, device: torch.device) -> Tuple[torch.Tensor, int]:
+        return self._eviction_scorer.gen_score(feature, device), self._eviction_scorer.gen_threshold()
+
+
+class HashZchOptEvictionModule(torch.nn.Module):
+    """A policy that needs no per-id score (slots are only claimed while free): ``forward -> (None, -1)``."""
+
+    def __init__(self, policy_name: HashZchEvictionPolicyName) -> None:
+        super().__init__()
+        self._policy_name = policy_name
+
+    def forward(self, feature: JaggedTensor, device: torch.device) -> Tuple[None, int]:
+        return None, -1
+
+
+def get_eviction_module(policy_name: HashZchEvictionPolicyName, config: Optional[HashZchEvictionConfig]) -> torch.nn.Module:
+    if policy_name in _SCORED_POLICIES:
+        assert config is not None, "a scored eviction policy needs its config"
+        return HashZchThresholdEvictionModule(policy_name, config)
+    return HashZchOptEvictionModule(policy_name)
+
+
 class HashZchEvictionModule(torch.nn.Module):
-    """``forward(feature) -> (score per id, threshold)`` of the configured policy."""
+    """``forward(feature) -> (score per id or None, threshold or -1)`` of the configured policy, on the module's device."""
 
     def __init__(self, policy_name: HashZchEvictionPolicyName, device: torch.device, config: Optional[HashZchEvictionConfig]) -> None:
         super().__init__()
-        assert config is not None, "an eviction policy needs its config"
         self._policy_name = policy_name
         self._device = device
-        self._scorer = get_eviction_scorer(policy_name, config)
+        self._eviction_module = get_eviction_module(policy_name, config)
 
     def forward(self, feature: JaggedTensor) -> Tuple[Optional[torch.Tensor], int]:
-        return self._scorer.gen_score(feature, self._device), self._scorer.gen_threshold()
+        return self._eviction_module(feature, self._device)

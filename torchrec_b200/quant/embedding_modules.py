@@ -41,14 +41,41 @@ MODULE_ATTR_CACHE_FEATURES_ORDER: str = "__cache_features_order"
 DEFAULT_ROW_ALIGNMENT = 16
 
 
+# ---- marks that the float modules carry into ``from_float`` ----------------------------------------------------------------
+# A conversion pass (``torch.quantization.convert`` style) reads these attributes from the float module it replaces; the helpers
+# below set them on every submodule of the given types before the conversion runs.
+def for_each_module_of_type_do(module: nn.Module, module_types: List[type], op) -> None:
+    for m in module.modules():
+        if isinstance(m, tuple(module_types)):
+            op(m)
+
+
+def _mark(module: nn.Module, module_types: List[type], attr: str, value) -> None:
+    for_each_module_of_type_do(module, module_types, lambda m: setattr(m, attr, value))
+
+
 def quant_prep_enable_quant_state_dict_split_scale_bias(module: nn.Module) -> None:
+    """The quantized module's state dict lists every table's scale and bias columns as a tensor of their own."""
     setattr(module, MODULE_ATTR_QUANT_STATE_DICT_SPLIT_SCALE_BIAS, True)
 
 
+def quant_prep_enable_quant_state_dict_split_scale_bias_for_types(module: nn.Module, module_types: List[type]) -> None:
+    _mark(module, module_types, MODULE_ATTR_QUANT_STATE_DICT_SPLIT_SCALE_BIAS, True)
+
+
 def quant_prep_enable_register_tbes(module: nn.Module, module_types: List[type]) -> None:
-    for m in module.modules():
-        if type(m) in module_types:
-            setattr(m, MODULE_ATTR_REGISTER_TBES_BOOL, True)
+    """The quantized module registers its lookup kernels as submodules (visible to ``named_modules``)."""
+    _mark(module, module_types, MODULE_ATTR_REGISTER_TBES_BOOL, True)
+
+
+def quant_prep_customize_row_alignment(module: nn.Module, module_types: List[type], row_alignment: int) -> None:
+    """Byte alignment of the quantized rows (the default is 16)."""
+    _mark(module, module_types, MODULE_ATTR_ROW_ALIGNMENT_INT, row_alignment)
+
+
+def quant_prep_enable_cache_features_order(module: nn.Module, module_types: List[type]) -> None:
+    """The quantized module remembers the feature permutation of its first request instead of recomputing it per request."""
+    _mark(module, module_types, MODULE_ATTR_CACHE_FEATURES_ORDER, True)
 
 
 def quantize_state_dict(module: nn.Module, table_name_to_quantized_weights: Dict[str, Tuple[torch.Tensor, Optional[torch.Tensor]]],
