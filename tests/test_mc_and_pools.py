@@ -189,3 +189,20 @@ def test_mpzch_opt_in_admission_and_reserved_rows():
     plain.train()
     o2 = plain.remap({"f": JaggedTensor(values=ids, lengths=torch.ones(1000, dtype=torch.long))})["f"].values()
     assert (plain._hash_zch_identities.data.view(-1)[o2] == ids).all() and plain.get_reserved_slots_per_bucket() == -1
+
+
+def test_inference_tensor_pool_over_virtual_devices():
+    """One process, four row blocks (all on the host here): lookups return the trained pool's rows in the caller's order."""
+    import torch
+
+    from torchrec_b200.distributed.tensor_pool import ShardedInferenceTensorPool
+    from torchrec_b200.distributed.types import ObjectPoolShardingPlan, ObjectPoolShardingType, ShardingEnv
+    from torchrec_b200.modules.tensor_pool import TensorPool
+
+    pool = TensorPool(pool_size=37, dim=6, dtype=torch.float32, device=torch.device("cpu"))
+    pool.update(torch.arange(37), torch.arange(37 * 6, dtype=torch.float32).view(37, 6))
+    sharded = ShardedInferenceTensorPool(ShardingEnv.from_local(world_size=4, rank=0), 37, 6, torch.float32,
+                                         ObjectPoolShardingPlan(sharding_type=ObjectPoolShardingType.ROW_WISE), pool, torch.device("cpu"))
+    assert [p._shard.shape[0] for p in sharded._local_shard_pools] == [10, 10, 10, 7]
+    ids = torch.tensor([36, 0, 9, 10, 29, 30, 5, 36])
+    torch.testing.assert_close(sharded(ids), pool.lookup(ids))

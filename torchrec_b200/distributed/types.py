@@ -591,3 +591,18 @@ class DMPCollectionContext(DMPCollectionConfig):
         self.replica_pg = None
         self.modules_to_sync: List[Tuple[nn.Module, nn.Module]] = []
         self.sharded_module: Optional[Type[nn.Module]] = None
+
+
+def rank_device(device_type: str, rank: int) -> torch.device:
+    """The device of ``rank`` in a job with one device per rank (the host has a single device)."""
+    return torch.device("cpu") if device_type == "cpu" else torch.device(f"{device_type}:{rank}")
+
+
+@dataclass
+class ShardingBucketMetadata:
+    """Bucket layout of a row-wise table that is sharded on bucket boundaries: how many buckets every shard holds, the index of
+    every shard's first bucket, and the rows per bucket."""
+
+    num_buckets_per_shard: List[int]
+    bucket_offsets_per_shard: List[int]
+    bucket_size: int

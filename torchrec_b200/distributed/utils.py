@@ -224,3 +224,70 @@ def modify_input_for_feature_processor(features, feature_processors, is_collecti
         if features.weights_or_none() is None:
             cat_weights = torch.ones(features.values().numel(), dtype=torch.float32, device=features.device())
             features._weights = cat_weights
+
+
+# ---- small helpers of the reference's ``distributed/utils.py`` ---------------------------------------------------------------
+_T = TypeVar("_T")
+
+
+def get_device_type() -> str:
+    return "cuda" if torch.cuda.is_available() else "cpu"
+
+
+def get_class_name(obj: object) -> str:
+    return "None" if obj is None else type(obj).__name__
+
+
+def assert_instance(obj: object, t: Type[_T]) -> _T:
+    assert isinstance(obj, t), f"Got {get_class_name(obj)}"
+    return obj
+
+
+class CopyableMixin(nn.Module):
+    """``module.copy(device)``: a copy of a host-resident module on ``device`` (sharded submodules copy themselves through their own
+    ``copy`` hook, see ``copy_to_device``)."""
+
+    def copy(self, device: torch.device) -> nn.Module:
+        return copy_to_device(self, current_device=torch.device("cpu"), to_device=device)
+
+
+def create_global_tensor_shape_stride_from_metadata(parameter_sharding: ParameterSharding, devices_per_node: Optional[int] = None):
+    """``(shape, stride)`` of the whole table that the shards of ``parameter_sharding`` tile."""
+    shards = parameter_sharding.sharding_spec.shards
+    kind = parameter_sharding.sharding_type
+    rows, cols = shards[0].shard_sizes
+    if kind == ShardingType.COLUMN_WISE.value or kind == ShardingType.TABLE_COLUMN_WISE.value:
+        cols = sum(s.shard_sizes[1] for s in shards)
+    elif kind in (ShardingType.ROW_WISE.value, ShardingType.TABLE_ROW_WISE.value):
+        rows = sum(s.shard_sizes[0] for s in shards)
+    elif kind == ShardingType.GRID_SHARD.value:
+        assert devices_per_node is not None, "grid shards need the node size to tell row shards from column shards"
+        rows, cols = rows * devices_per_node, cols * (len(shards) // devices_per_node)
+    elif kind != ShardingType.TABLE_WISE.value:
+        return torch.Size([0, 0]), (0, 1)
+    return torch.Size([rows, cols]), (cols, 1)
+
+
+def get_bucket_metadata_from_shard_metadata(shards, num_buckets: int):
+    """Bucket layout of a row-wise table cut into ``num_buckets`` equal buckets, every shard holding whole buckets."""
+    from torchrec_b200.distributed.types import ShardingBucketMetadata
+
+    assert len(shards) > 0, "Shards cannot be empty"
+    table_rows = shards[-1].shard_offsets[0] + shards[-1].shard_sizes[0]
+    assert table_rows % num_buckets == 0, f"Table size '{table_rows}' must be divisible by num_buckets '{num_buckets}'"
+    bucket = table_rows // num_buckets
+    meta = ShardingBucketMetadata(num_buckets_per_shard=[], bucket_offsets_per_shard=[], bucket_size=bucket)
+    first = 0
+    for shard in shards:
+        assert len(shard.shard_offsets) == 1 or shard.shard_offsets[1] == 0, "only row-wise shards can be bucketized"
+        assert shard.shard_sizes[0] % bucket == 0, f"Shard size[0] '{shard.shard_sizes[0]}' is not divisible by bucket size '{bucket}'"
+        meta.num_buckets_per_shard.append(shard.shard_sizes[0] // bucket)
+        meta.bucket_offsets_per_shard.append(first)
+        first += shard.shard_sizes[0] // bucket
+    return meta
+
+
+def weights_bytes_in_emb_kernel(emb: nn.Module) -> int:
+    """Bytes of table storage held by one embedding kernel."""
+    w = getattr(emb, "weights", None)
+    return int(w.numel() * w.element_size()) if isinstance(w, torch.Tensor) else sum(int(t.numel() * t.element_size()) for t in emb.split_embedding_weights())
