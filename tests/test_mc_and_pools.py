@@ -206,3 +206,24 @@ def test_inference_tensor_pool_over_virtual_devices():
     assert [p._shard.shape[0] for p in sharded._local_shard_pools] == [10, 10, 10, 7]
     ids = torch.tensor([36, 0, 9, 10, 29, 30, 5, 36])
     torch.testing.assert_close(sharded(ids), pool.lookup(ids))
+
+
+def test_inference_kjt_pool_over_virtual_devices():
+    import torch
+
+    from torchrec_b200.distributed.keyed_jagged_tensor_pool import ShardedInferenceKeyedJaggedTensorPool
+    from torchrec_b200.distributed.types import ObjectPoolShardingPlan, ObjectPoolShardingType, ShardingEnv
+    from torchrec_b200.modules.keyed_jagged_tensor_pool import KeyedJaggedTensorPool
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    caps = {"a": 3, "b": 2}
+    pool = KeyedJaggedTensorPool(pool_size=11, feature_max_lengths=caps, device=torch.device("cpu"))
+    g = torch.Generator().manual_seed(0)
+    la, lb = torch.randint(0, 4, (11,), generator=g), torch.randint(0, 3, (11,), generator=g)
+    vals = torch.randint(0, 100, (int(la.sum() + lb.sum()),), generator=g)
+    pool.update(torch.arange(11), KeyedJaggedTensor.from_lengths_sync(keys=["a", "b"], values=vals, lengths=torch.cat([la, lb])))
+    sharded = ShardedInferenceKeyedJaggedTensorPool(ShardingEnv.from_local(world_size=3, rank=0), 11, caps, torch.int64, False,
+                                                    ObjectPoolShardingPlan(sharding_type=ObjectPoolShardingType.ROW_WISE), pool, torch.device("cpu"))
+    ids = torch.tensor([10, 0, 4, 3, 8, 10])
+    got, want = sharded(ids), pool.lookup(ids)
+    assert got.keys() == want.keys() and torch.equal(got.lengths(), want.lengths()) and torch.equal(got.values(), want.values())
