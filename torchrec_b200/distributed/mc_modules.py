@@ -9,13 +9,14 @@ Counterpart of ``torchrec/distributed/mc_modules.py`` (``ShardedManagedCollision
 from __future__ import annotations
 
 import copy
-from typing import Any, Dict, Iterator, List, Optional, Tuple
+from typing import Any, Dict, Iterator, List, Optional, Tuple, Type
 
 import torch
 import torch.distributed as dist
 from torch import nn
 
-from torchrec_b200.distributed.types import ParameterSharding, ShardedTensor, ShardingEnv, ShardingType
+from torchrec_b200.distributed.embedding_types import BaseEmbeddingSharder
+from torchrec_b200.distributed.types import ParameterSharding, QuantizedCommCodecs, ShardedTensor, ShardingEnv, ShardingType
 from torchrec_b200.modules.mc_modules import ManagedCollisionCollection, ManagedCollisionModule
 from torchrec_b200.sparse.jagged_tensor import JaggedTensor, KeyedJaggedTensor
 
@@ -146,3 +147,26 @@ class ShardedManagedCollisionCollection(nn.Module):
                     state_dict[key] = src.local_shards()[0].tensor
                 elif isinstance(src, torch.Tensor) and src.shape[0] == module._global_rows[table] and src.shape[0] != buf.shape[0]:
                     state_dict[key] = src[off: off + buf.shape[0]]
+
+
+class ManagedCollisionCollectionSharder(BaseEmbeddingSharder[ManagedCollisionCollection]):
+    """Builds the sharded collision collection that sits in front of a sharded embedding module.  It is used by the sharders of
+    the managed-collision embedding collections; a collision collection is not sharded on its own (its slot tables follow the row
+    blocks of the embedding tables they serve).  (``torchrec/distributed/mc_modules.py:843`` of the reference.)"""
+
+    def __init__(self, qcomm_codecs_registry: Optional[Dict[str, QuantizedCommCodecs]] = None) -> None:
+        super().__init__(qcomm_codecs_registry=qcomm_codecs_registry)
+
+    def shard(self, module: ManagedCollisionCollection, params: Dict[str, ParameterSharding], env: ShardingEnv, embedding_shardings: Optional[List[Any]] = None,
+              device: Optional[torch.device] = None, use_index_dedup: bool = False) -> ShardedManagedCollisionCollection:
+        return ShardedManagedCollisionCollection(module, params, env, device if device is not None else torch.device("cpu"))
+
+    def shardable_parameters(self, module: ManagedCollisionCollection) -> Dict[str, nn.Parameter]:
+        raise NotImplementedError("a collision collection is sharded together with its embedding module")
+
+    @property
+    def module_type(self) -> Type[ManagedCollisionCollection]:
+        return ManagedCollisionCollection
+
+    def sharding_types(self, compute_device_type: str) -> List[str]:
+        return [ShardingType.ROW_WISE.value]
