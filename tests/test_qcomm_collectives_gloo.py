@@ -82,3 +82,29 @@ def test_mx4_container_size_and_values():
     # every representable magnitude at block exponent 0 survives exactly; a block is scaled by a power of two
     torch.testing.assert_close(codec.decode(q, ctx)[:32], x[:32], rtol=0, atol=0)
     assert abs(float(codec.decode(q, ctx)[32]) - 96.0) < 1e-6  # 100 -> 6 * 2^4
+
+
+def _functional_forms(rank, world_size):
+    from torchrec_b200.distributed import comm_ops as co
+
+    with MultiProcessContext(rank, world_size, "gloo") as ctx:
+        x = (torch.arange(8, dtype=torch.float32).view(4, 2) + 10 * rank).requires_grad_(True)
+        gathered = co.all_gather_into_tensor(x, 0, ctx.pg)
+        assert gathered.shape == (8, 2) and torch.equal(gathered[4 * rank: 4 * rank + 4].detach(), x.detach())
+        gathered.sum().backward()
+        assert torch.equal(x.grad, torch.full((4, 2), float(world_size)))  # the gradient comes back through a reduce-scatter
+        y = torch.ones(4, 3, requires_grad=True)
+        scattered = co.reduce_scatter_tensor(y, 0, ctx.pg)
+        assert torch.equal(scattered.detach(), torch.full((2, 3), float(world_size)))
+        scattered.sum().backward()
+        assert torch.equal(y.grad, torch.ones(4, 3))
+        pooled = co.all2all_pooled_sync(ctx.pg, co.All2AllPooledInfo([2, 2], [3, 3], None, None), torch.full((4, 3), float(rank + 1)))
+        assert pooled.shape == (2, 6) and torch.equal(pooled[:, :3], torch.ones(2, 3)) and torch.equal(pooled[:, 3:], torch.full((2, 3), 2.0))
+        flat = torch.arange(10, dtype=torch.float32)  # rank 0 keeps feature batches (1, 2) x dims (2, 1) = 4 values, rank 1 gets (2, 2) = 6
+        part = co.reduce_scatter_v_per_feature_pooled(flat, [[1, 2], [2, 2]], [2, 1], ctx.pg).wait()
+        want = flat[:4] * world_size if rank == 0 else flat[4:] * world_size
+        assert torch.equal(part, want)
+
+
+def test_blocking_and_functional_collective_forms():
+    run_multi_process(_functional_forms, world_size=2)

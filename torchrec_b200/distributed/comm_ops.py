@@ -835,3 +835,113 @@ def tensor_alltoall(x: Tensor, in_splits: List[int], out_splits: List[int], grou
     if dist.get_world_size(group) <= 1:
         return x
     return _TensorAllToAll.apply(group, x, in_splits, out_splits)
+
+
+# --------------------------------------------------------------------------------------
+# Blocking forms: the same collectives with the result returned directly.  Code that cannot hold an ``Awaitable`` (a traced or
+# exported region, a debugging session) switches to them with ``set_use_sync_collectives(True)``; they stay differentiable because
+# they run the request / wait functions above back to back.  (``torchrec/distributed/comm_ops.py:1090-1600`` of the reference.)
+# --------------------------------------------------------------------------------------
+def torchrec_use_sync_collectives() -> bool:
+    return get_use_sync_collectives()
+
+
+def pg_name(pg: dist.ProcessGroup) -> str:
+    """The registered name of a process group (what functional collectives take instead of the object)."""
+    return dist._functional_collectives._resolve_group_name(pg, "") if hasattr(dist, "_functional_collectives") else str(pg)
+
+
+def all2all_pooled_sync(pg: dist.ProcessGroup, a2ai: All2AllPooledInfo, input_embeddings: Tensor) -> Tensor:
+    return alltoall_pooled(input_embeddings, a2ai.batch_size_per_rank, a2ai.dim_sum_per_rank, a2ai.dim_sum_per_rank_tensor, a2ai.cumsum_dim_sum_per_rank_tensor,
+                           group=pg, codecs=a2ai.codecs).wait()
+
+
+def variable_batch_all2all_pooled_sync(pg: dist.ProcessGroup, a2ai: VariableBatchAll2AllPooledInfo, input_embeddings: Tensor) -> Tensor:
+    return variable_batch_alltoall_pooled(input_embeddings, a2ai.batch_size_per_rank_per_feature, a2ai.batch_size_per_feature_pre_a2a,
+                                          a2ai.emb_dim_per_rank_per_feature, group=pg, codecs=a2ai.codecs).wait()
+
+
+def all2all_sequence_sync(pg: dist.ProcessGroup, a2ai: All2AllSequenceInfo, sharded_input_embeddings: Tensor) -> Tensor:
+    return alltoall_sequence(sharded_input_embeddings, a2ai.forward_recat_tensor, a2ai.backward_recat_tensor, a2ai.lengths_after_sparse_data_all2all,
+                             a2ai.input_splits, a2ai.output_splits, a2ai.variable_batch_size, group=pg, codecs=a2ai.codecs).wait()
+
+
+def reduce_scatter_sync(pg: dist.ProcessGroup, rsi: ReduceScatterInfo, *inputs: Tensor) -> Tensor:
+    return reduce_scatter_pooled(list(inputs), group=pg, codecs=rsi.codecs).wait()
+
+
+def reduce_scatter_base_sync(pg: dist.ProcessGroup, rsi: ReduceScatterBaseInfo, inputs: Tensor) -> Tensor:
+    return reduce_scatter_base_pooled(inputs, group=pg, codecs=rsi.codecs).wait()
+
+
+def all_gather_base_sync(pg: dist.ProcessGroup, agi: AllGatherBaseInfo, input: Tensor) -> Tensor:
+    return all_gather_base_pooled(input, group=pg, codecs=agi.codecs).wait()
+
+
+def reduce_scatter_v_sync(pg: dist.ProcessGroup, rsi: ReduceScatterVInfo, input: Tensor) -> Tensor:
+    return reduce_scatter_v_pooled(input, list(rsi.input_splits), group=pg, codecs=rsi.codecs).wait()
+
+
+def reduce_scatter_v_per_feature_pooled(input: Tensor, batch_size_per_rank_per_feature: List[List[int]], embedding_dims: List[int],
+                                        group: Optional[dist.ProcessGroup] = None, codecs: Optional[QuantizedCommCodecs] = None) -> Awaitable[Tensor]:
+    """Reduce-scatter of a flat pooled payload whose chunk for rank ``r`` holds, feature after feature, ``batch[r][f] * dim[f]`` values
+    (features differ in batch size)."""
+    if group is None:
+        group = dist.distributed_c10d._get_default_group()
+    if dist.get_world_size(group) <= 1:
+        return NoWait(input)
+    splits = [sum(b * d for b, d in zip(per_feature, embedding_dims)) for per_feature in batch_size_per_rank_per_feature]
+    return reduce_scatter_v_pooled(input.view(-1), splits, group, codecs=codecs)
+
+
+AllToAllSingle = _TensorAllToAll  # differentiable ``all_to_all_single`` over dim 0: ``apply(pg, x, in_splits, out_splits)``
+
+
+class _AllGatherIntoTensor(Function):
+    @staticmethod
+    def forward(ctx, pg, shard: Tensor, gather_dim: int) -> Tensor:
+        world = dist.get_world_size(pg)
+        moved = shard.movedim(gather_dim, 0).contiguous()
+        out = moved.new_empty((world * moved.shape[0],) + tuple(moved.shape[1:]))
+        _all_gather_into_tensor(out, moved, pg, async_op=False)
+        ctx.pg, ctx.dim = pg, gather_dim
+        return out.movedim(0, gather_dim) if gather_dim else out
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        world = dist.get_world_size(ctx.pg)
+        moved = g.movedim(ctx.dim, 0).contiguous()
+        out = moved.new_empty((moved.shape[0] // world,) + tuple(moved.shape[1:]))
+        _reduce_scatter_tensor(out, moved, ctx.pg, async_op=False)
+        return None, (out.movedim(0, ctx.dim) if ctx.dim else out), None
+
+
+class _ReduceScatterTensor(Function):
+    @staticmethod
+    def forward(ctx, pg, x: Tensor, scatter_dim: int) -> Tensor:
+        world = dist.get_world_size(pg)
+        moved = x.movedim(scatter_dim, 0).contiguous()
+        out = moved.new_empty((moved.shape[0] // world,) + tuple(moved.shape[1:]))
+        _reduce_scatter_tensor(out, moved, pg, async_op=False)
+        ctx.pg, ctx.dim = pg, scatter_dim
+        return out.movedim(0, scatter_dim) if scatter_dim else out
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        world = dist.get_world_size(ctx.pg)
+        moved = g.movedim(ctx.dim, 0).contiguous()
+        out = moved.new_empty((world * moved.shape[0],) + tuple(moved.shape[1:]))
+        _all_gather_into_tensor(out, moved, ctx.pg, async_op=False)
+        return None, (out.movedim(0, ctx.dim) if ctx.dim else out), None
+
+
+def all_gather_into_tensor(shard: Tensor, gather_dim: int = 0, group: Optional[dist.ProcessGroup] = None) -> Tensor:
+    """Differentiable all-gather along ``gather_dim`` (backward: reduce-scatter of the gradient)."""
+    group = group if group is not None else dist.distributed_c10d._get_default_group()
+    return shard if dist.get_world_size(group) <= 1 else _AllGatherIntoTensor.apply(group, shard, gather_dim)
+
+
+def reduce_scatter_tensor(input: Tensor, scatter_dim: int = 0, group: Optional[dist.ProcessGroup] = None) -> Tensor:
+    """Differentiable sum reduce-scatter along ``scatter_dim`` (backward: all-gather of the gradient)."""
+    group = group if group is not None else dist.distributed_c10d._get_default_group()
+    return input if dist.get_world_size(group) <= 1 else _ReduceScatterTensor.apply(group, input, scatter_dim)

@@ -55,6 +55,24 @@ class _TbeFusedOptimizer(FusedOptimizer):
             self._emb.set_learning_rate(g["lr"])
 
 
+EmbeddingFusedOptimizer = _TbeFusedOptimizer  # the reference's name for the keyed view of a kernel-side optimizer
+
+
+def convert_optimizer_type_and_kwargs(optimizer_type: Type[torch.optim.Optimizer], optimizer_kwargs: Dict[str, Any]):
+    """``(kernel optimizer, kernel arguments)`` for an optimizer class of torch or of this package (``lr`` becomes
+    ``learning_rate``), or ``None`` when the embedding kernels have no fused form of it."""
+    try:
+        kind = optimizer_type_to_emb_opt_type(optimizer_type)
+    except Exception:
+        return None
+    if kind is None:
+        return None
+    kwargs = dict(optimizer_kwargs)
+    if "lr" in kwargs:
+        kwargs["learning_rate"] = kwargs.pop("lr")
+    return kind, kwargs
+
+
 class _FusedBase(FusedOptimizerModule):
     _container = "embedding_bags"
 
