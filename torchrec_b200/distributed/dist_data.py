@@ -470,6 +470,21 @@ class EmbeddingsAllToOne(nn.Module):
         self._device = torch.device(device_str)
 
 
+class MergePooledEmbeddingsModule(nn.Module):
+    """Brings per-device tensors to one device and concatenates them along ``cat_dim``; a serving runtime can retarget it with
+    ``set_device`` after the model was loaded (``torchrec/distributed/dist_data.py:185`` of the reference)."""
+
+    def __init__(self, device: torch.device) -> None:
+        super().__init__()
+        self._device = device
+
+    def set_device(self, device_str: str) -> None:
+        self._device = torch.device(device_str)
+
+    def forward(self, tensors: List[torch.Tensor], cat_dim: int) -> torch.Tensor:
+        return torch.cat([t.to(self._device, non_blocking=True) for t in tensors], dim=cat_dim)
+
+
 class EmbeddingsAllToOneReduce(nn.Module):
     """Sum per-device partial outputs on ``device`` (row-wise inference)."""
 
