@@ -106,3 +106,18 @@ def test_sequence_inference_strategies(how):
         ordered = rows.index_select(0, dist_out.unbucketize_permute_tensor.long())
         want = torch.cat([full[name][kjt[feat].values()] for name, feat, _, _ in TABLES])
         torch.testing.assert_close(ordered.float(), want, rtol=1e-3, atol=1e-3)
+
+
+def test_strategy_factories_and_device_helpers():
+    from torchrec_b200.distributed.quant_embedding import create_infer_embedding_sharding
+    from torchrec_b200.distributed.quant_embeddingbag import create_infer_embedding_bag_sharding, get_device_from_parameter_sharding, get_device_from_sharding_infos
+    from torchrec_b200.distributed.sharding import infer_shardings as inf
+
+    env = ShardingEnv.from_local(world_size=W, rank=0)
+    infos = _infos("rw", True)
+    assert get_device_from_parameter_sharding(infos[0].param_sharding) == "cpu" and get_device_from_sharding_infos(infos) == "cpu"
+    assert isinstance(create_infer_embedding_bag_sharding("row_wise", infos, env, torch.device("cpu")), inf.InferRwPooledEmbeddingSharding)
+    assert isinstance(create_infer_embedding_bag_sharding("column_wise", _infos("cw", True), env, torch.device("cpu")), inf.InferCwPooledEmbeddingSharding)
+    assert isinstance(create_infer_embedding_sharding("table_wise", _infos("tw", False), env, torch.device("cpu")), inf.InferTwSequenceEmbeddingSharding)
+    with pytest.raises(ValueError):
+        create_infer_embedding_bag_sharding("grid_shard", infos, env)

@@ -11,7 +11,9 @@ from torch import nn
 from torchrec_b200.distributed.embedding_types import BaseQuantEmbeddingSharder
 from torchrec_b200.distributed.quant_embeddingbag import _device_for
 from torchrec_b200.distributed.types import ParameterSharding, ShardingEnv, ShardingType
-from torchrec_b200.distributed.quant_input_dist import ShardedQuantEcInputDist  # noqa: F401  (also the reference's import path for it)
+from torchrec_b200.distributed.quant_input_dist import (  # noqa: F401  (also the reference's import paths for these)
+    ShardedQuantEcInputDist, create_infer_embedding_sharding, get_device_for_first_shard_from_sharding_infos, get_device_from_parameter_sharding, get_device_from_sharding_infos,
+)
 from torchrec_b200.distributed.quant_state import ShardedQuantEmbeddingModuleState
 from torchrec_b200.quant.embedding_modules import EmbeddingCollection as QuantEmbeddingCollection
 from torchrec_b200.quant.embedding_modules import QuantManagedCollisionEmbeddingCollection

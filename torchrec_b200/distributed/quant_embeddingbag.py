@@ -17,7 +17,9 @@ from torch import nn
 from torchrec_b200.distributed.embedding_types import BaseQuantEmbeddingSharder
 from torchrec_b200.distributed.types import ParameterSharding, ShardingEnv, ShardingType
 from torchrec_b200.modules.embedding_configs import PoolingType
-from torchrec_b200.distributed.quant_input_dist import ShardedQuantEbcInputDist  # noqa: F401  (also the reference's import path for it)
+from torchrec_b200.distributed.quant_input_dist import (  # noqa: F401  (also the reference's import paths for these)
+    ShardedQuantEbcInputDist, create_infer_embedding_bag_sharding, flatten_feature_lengths, get_device_for_first_shard_from_sharding_infos, get_device_from_parameter_sharding, get_device_from_sharding_infos,
+)
 from torchrec_b200.distributed.quant_state import ShardedQuantEmbeddingModuleState
 from torchrec_b200.quant.embedding_modules import EmbeddingBagCollection as QuantEmbeddingBagCollection
 from torchrec_b200.quant.embedding_modules import FeatureProcessedEmbeddingBagCollection as QuantFeatureProcessedEmbeddingBagCollection

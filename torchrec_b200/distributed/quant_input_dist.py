@@ -71,3 +71,59 @@ class ShardedQuantEcInputDist(_ShardedQuantInputDist):
     """Sequence collection: looked-up rows come back in (device, feature, sample) order; ``unbucketize_permute`` undoes that."""
 
     _restore_order = True
+
+
+# ---- choosing the inference strategy of a group of tables ---------------------------------------------------------------------
+def get_device_from_parameter_sharding(ps) -> Any:
+    """Device type of a table's shards: one string, or a tuple (one entry per shard) when a row-wise table is spread over device types."""
+    shards = getattr(ps.sharding_spec, "shards", None)
+    if shards is None:
+        raise ValueError("Expected EnumerableShardingSpec as input to the function")
+    kinds = tuple(str(s.placement).split("/")[-1].split(":")[0] for s in shards)
+    if len(set(kinds)) == 1:
+        return kinds[0]
+    assert ps.sharding_type == "row_wise", "Only row_wise sharding supports sharding across multiple device types for a table"
+    return kinds
+
+
+def get_device_from_sharding_infos(emb_shard_infos) -> Any:
+    kinds = {get_device_from_parameter_sharding(info.param_sharding) for info in emb_shard_infos}
+    assert len(kinds) == 1, "All shards should be on the same type of device"
+    return next(iter(kinds))
+
+
+def get_device_for_first_shard_from_sharding_infos(emb_shard_infos) -> str:
+    kind = get_device_from_sharding_infos(emb_shard_infos)
+    return kind[0] if isinstance(kind, tuple) else kind
+
+
+def create_infer_embedding_bag_sharding(sharding_type: str, sharding_infos, env, device: Optional[torch.device] = None):
+    """The pooled inference strategy for ``sharding_type`` (table-wise, row-wise or column-wise)."""
+    from torchrec_b200.distributed.sharding import infer_shardings as inf
+    from torchrec_b200.distributed.types import ShardingType
+
+    if sharding_type == ShardingType.TABLE_WISE.value:
+        return inf.InferTwEmbeddingSharding(sharding_infos, env, device)
+    if sharding_type == ShardingType.ROW_WISE.value:
+        return inf.InferRwPooledEmbeddingSharding(sharding_infos, env, device)
+    if sharding_type == ShardingType.COLUMN_WISE.value:
+        return inf.InferCwPooledEmbeddingSharding(sharding_infos, env, device, permute_embeddings=True)
+    raise ValueError(f"Sharding type not supported {sharding_type}")
+
+
+def create_infer_embedding_sharding(sharding_type: str, sharding_infos, env, device: Optional[torch.device] = None):
+    """The sequence inference strategy for ``sharding_type``."""
+    from torchrec_b200.distributed.sharding import infer_shardings as inf
+    from torchrec_b200.distributed.types import ShardingType
+
+    if sharding_type == ShardingType.TABLE_WISE.value:
+        return inf.InferTwSequenceEmbeddingSharding(sharding_infos, env, device)
+    if sharding_type == ShardingType.ROW_WISE.value:
+        return inf.InferRwSequenceEmbeddingSharding(sharding_infos, env, device)
+    if sharding_type == ShardingType.COLUMN_WISE.value:
+        return inf.InferCwSequenceEmbeddingSharding(sharding_infos, env, device)
+    raise ValueError(f"Sharding type not supported {sharding_type}")
+
+
+def flatten_feature_lengths(features: KeyedJaggedTensor) -> KeyedJaggedTensor:
+    return features.flatten_lengths() if features.lengths().dim() > 1 else features
