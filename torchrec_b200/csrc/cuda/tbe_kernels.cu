@@ -825,21 +825,22 @@ __global__ void __launch_bounds__(256) tbe_bwd_verylong_kernel(BwdParams p) {
   }
 }
 
-// keys: global row id of every id; src: bag id (pooled) or position (unpooled)
-template <typename idx_t>
+// keys: global row id of every id; src: bag id (pooled) or position (unpooled).  kLanes lanes share one bag (32: a warp per bag,
+// for long bags; 8: four bags per warp, for the common bags of a handful of ids, where a whole warp would leave most lanes idle)
+template <typename idx_t, int kLanes>
 __global__ void __launch_bounds__(256) tbe_linearize_kernel(
     const idx_t* __restrict__ indices, const idx_t* __restrict__ offsets, const int64_t* __restrict__ meta, int F, int B,
     int pooled, int64_t* __restrict__ keys, int32_t* __restrict__ src, int32_t* __restrict__ src_feature,
     float* __restrict__ bag_scale, int* err) {
-  const int lane = threadIdx.x & 31;
-  const int64_t bag = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & (kLanes - 1);
+  const int64_t bag = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) / kLanes;
   if (bag >= int64_t(F) * B) return;
   const int f = int(bag / B);
   const int64_t start = offsets[bag], end = offsets[bag + 1];
   const int64_t hoff = meta[M_HASHOFF * F + f];
   const int64_t rows = meta[M_ROWS * F + f];
   if (bag_scale && lane == 0) bag_scale[bag] = end > start ? 1.f / float(end - start) : 0.f;
-  for (int64_t i = start + lane; i < end; i += 32) {
+  for (int64_t i = start + lane; i < end; i += kLanes) {
     int64_t r = int64_t(indices[i]);
     const bool bad = r < 0 || r >= rows;
     if (bad) {
@@ -1064,16 +1065,22 @@ std::vector<at::Tensor> tbe_build_plan(const at::Tensor& meta, const at::Tensor&
       const int64_t seq_blocks = (N + threads - 1) / threads;
       if (i64) tbe_linearize_seq_kernel<int64_t><<<seq_blocks, threads, 0, stream>>>(indices.data_ptr<int64_t>(), offsets.data_ptr<int64_t>(), meta.data_ptr<int64_t>(), F, int(B), keys.data_ptr<int64_t>(), src_ptr, src_feature.data_ptr<int32_t>(), err.data_ptr<int>());
       else tbe_linearize_seq_kernel<int32_t><<<seq_blocks, threads, 0, stream>>>(indices.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), meta.data_ptr<int64_t>(), F, int(B), keys.data_ptr<int64_t>(), src_ptr, src_feature.data_ptr<int32_t>(), err.data_ptr<int>());
-    } else if (i64) {
-      tbe_linearize_kernel<int64_t><<<blocks, threads, 0, stream>>>(
-          indices.data_ptr<int64_t>(), offsets.data_ptr<int64_t>(), meta.data_ptr<int64_t>(), F, int(B), pooled ? 1 : 0,
-          keys.data_ptr<int64_t>(), src_ptr, pooled ? nullptr : src_feature.data_ptr<int32_t>(),
-          bag_scale.defined() ? bag_scale.data_ptr<float>() : nullptr, err.data_ptr<int>());
     } else {
-      tbe_linearize_kernel<int32_t><<<blocks, threads, 0, stream>>>(
-          indices.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), meta.data_ptr<int64_t>(), F, int(B), pooled ? 1 : 0,
-          keys.data_ptr<int64_t>(), src_ptr, pooled ? nullptr : src_feature.data_ptr<int32_t>(),
-          bag_scale.defined() ? bag_scale.data_ptr<float>() : nullptr, err.data_ptr<int>());
+      // short bags (up to 16 ids on average): eight lanes per bag
+      const bool narrow = N <= int64_t(F) * B * 16;
+      const int64_t lin_blocks = narrow ? (int64_t(F) * B * 8 + threads - 1) / threads : blocks;
+      auto launch = [&](auto tag, auto lanes) {
+        using T = decltype(tag);
+        constexpr int kL = decltype(lanes)::value;
+        tbe_linearize_kernel<T, kL><<<lin_blocks, threads, 0, stream>>>(
+            indices.data_ptr<T>(), offsets.data_ptr<T>(), meta.data_ptr<int64_t>(), F, int(B), pooled ? 1 : 0, keys.data_ptr<int64_t>(), src_ptr,
+            pooled ? nullptr : src_feature.data_ptr<int32_t>(), bag_scale.defined() ? bag_scale.data_ptr<float>() : nullptr, err.data_ptr<int>());
+      };
+      if (i64) {
+        if (narrow) launch(int64_t(0), std::integral_constant<int, 8>()); else launch(int64_t(0), std::integral_constant<int, 32>());
+      } else {
+        if (narrow) launch(int32_t(0), std::integral_constant<int, 8>()); else launch(int32_t(0), std::integral_constant<int, 32>());
+      }
     }
     if (padded) {
       if (i64) tbe_count_valid_kernel<int64_t><<<1, 1, 0, stream>>>(offsets.data_ptr<int64_t>(), int64_t(F) * B, n_valid.data_ptr<int64_t>());
