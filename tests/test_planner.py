@@ -229,3 +229,56 @@ def test_local_refinement_never_rates_worse_and_balances_a_skewed_model():
     chosen = EmbeddingShardingPlanner(topology=Topology(world_size=8, local_world_size=8, compute_device="cuda"), batch_size=8192,
                                       proposer=GreedyProposer(), debug=False)
     assert chosen._refine_steps == 0
+
+
+def test_stored_plan_is_reused_and_a_plan_for_other_inputs_is_refused():
+    """A plan stored as {storage_hash: option} comes back as the same placement without a search; the loader's fingerprint of the
+    planner inputs must match (cf. ``torchrec/distributed/planner/tests/test_planners.py`` plan-loader cases)."""
+    import copy
+
+    from torchrec_b200.distributed.planner.planners import EmbeddingPlannerBase, extract_plan
+    from torchrec_b200.distributed.planner.types import PlanLoader
+
+    sharders = [EmbeddingBagCollectionSharder()]
+    first = EmbeddingShardingPlanner(topology=_topo(4), batch_size=256, debug=False)
+    assert isinstance(first, EmbeddingPlannerBase)
+    plan = first.plan(_Model(_tables(4)), sharders)
+    stored = {o.storage_hash(): copy.deepcopy(o) for o in first._best_plan}
+    assert len(stored) == 4
+
+    class _Loader(PlanLoader):
+        def __init__(self, options, fingerprint):
+            self.options, self.fingerprint, self.loads = options, fingerprint, 0
+
+        def load(self):
+            self.loads += 1
+            return self.options
+
+        def plan_context_hash(self):
+            return self.fingerprint
+
+    loader = _Loader(stored, first.hash_planner_context_inputs_str())
+
+    class _NeverProposer(GreedyProposer):
+        def propose(self):
+            raise AssertionError("a stored plan must skip the search")
+
+    again = EmbeddingShardingPlanner(topology=_topo(4), batch_size=256, debug=False, proposer=_NeverProposer(), plan_loader=loader)
+    replayed = again.plan(_Model(_tables(4)), sharders)
+    assert loader.loads == 1
+    for name, ps in plan.plan["sparse"].items():
+        other = replayed.plan["sparse"][name]
+        assert (ps.sharding_type, ps.compute_kernel, ps.ranks) == (other.sharding_type, other.compute_kernel, other.ranks)
+        assert [(s.shard_sizes, s.shard_offsets) for s in ps.sharding_spec.shards] == [(s.shard_sizes, s.shard_offsets) for s in other.sharding_spec.shards]
+
+    other_batch = EmbeddingShardingPlanner(topology=_topo(4), batch_size=512, debug=False, plan_loader=loader)
+    with pytest.raises(PlannerError) as err:
+        other_batch.plan(_Model(_tables(4)), sharders)
+    assert err.value.error_type == PlannerErrorType.PLANNER_INPUT_CONTEXT_MISMATCH
+
+    # a stored plan that lacks a table of the model cannot be used
+    options = EmbeddingEnumerator(topology=_topo(4), batch_size=256).enumerate(_Model(_tables(4)), sharders)
+    partial = dict(list(stored.items())[:3])
+    with pytest.raises(PlannerError) as err:
+        extract_plan(options, partial)
+    assert err.value.error_type == PlannerErrorType.PLAN_LOADING_FAILED

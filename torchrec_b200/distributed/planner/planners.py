@@ -29,6 +29,7 @@ from torchrec_b200.distributed.planner.types import (
     Partitioner,
     Perf,
     PerfModel,
+    PlanLoader,
     PlannerError,
     PlannerErrorType,
     Proposer,
@@ -38,6 +39,7 @@ from torchrec_b200.distributed.planner.types import (
     StorageReservation,
     Topology,
     hash_planner_context_inputs,
+    hash_planner_context_inputs_str,
 )
 from torchrec_b200.distributed.planner.utils import bytes_to_gb, reset_shard_rank, storage_repr_in_gb
 from torchrec_b200.distributed.sharding_plan import get_default_sharders, placement
@@ -98,7 +100,95 @@ def _merge_plans(best_plans: List[ShardingPlan]) -> ShardingPlan:
     return merged
 
 
-class EmbeddingShardingPlanner(ShardingPlanner):
+def extract_plan(search_space: List[ShardingOption], loaded_sharding_options: Dict[int, ShardingOption]) -> List[ShardingOption]:
+    """Rebuild a stored plan on top of a freshly enumerated search space: every stored option (keyed by ``storage_hash``) lends its
+    shards - sizes, offsets, ranks - to the enumerated option with the same key; everything else (tensor, module, input statistics)
+    comes from the enumeration, so a stored plan holds no reference to a model.  Raises ``PLAN_LOADING_FAILED`` when two enumerated
+    options share a key or the stored plan and the model do not name the same tables.
+    Counterpart of ``torchrec/distributed/planner/planners.py:121-197``."""
+    by_key: Dict[int, ShardingOption] = {}
+    for option in search_space:
+        key = option.storage_hash()
+        if key in by_key:
+            raise PlannerError(f"two sharding options of the search space share the storage hash {key}: {by_key[key].fqn}, {option.fqn}",
+                               PlannerErrorType.PLAN_LOADING_FAILED)
+        by_key[key] = option
+    rebuilt: List[ShardingOption] = []
+    for key, stored in loaded_sharding_options.items():
+        option = by_key.get(key)
+        if option is None:
+            continue
+        fresh = copy.deepcopy(option)
+        fresh.shards = copy.deepcopy(stored.shards)
+        rebuilt.append(fresh)
+    tables = {o.fqn for o in search_space}
+    covered = {o.fqn for o in rebuilt}
+    if len(rebuilt) != len(loaded_sharding_options) or covered != tables:
+        missing = sorted(tables - covered)
+        raise PlannerError(
+            f"the stored plan does not fit this model: {len(loaded_sharding_options)} stored options, {len(rebuilt)} matched, "
+            f"tables without a stored option: {missing}", PlannerErrorType.PLAN_LOADING_FAILED)
+    return rebuilt
+
+
+class EmbeddingPlannerBase(ShardingPlanner):
+    """What every embedding planner here shares: the topology (default: the current world), the batch size, the enumerator, the
+    storage reservation, the report sinks, constraints, callbacks and the time limit; ``collective_plan`` (rank 0 plans, everyone
+    receives the result) and the fingerprint of the planner's inputs.  Counterpart of ``torchrec/distributed/planner/planners.py:200-340``."""
+
+    def __init__(
+        self,
+        topology: Optional[Topology] = None,
+        batch_size: Optional[int] = None,
+        enumerator: Optional[Enumerator] = None,
+        storage_reservation: Optional[StorageReservation] = None,
+        stats: Optional[Union[Stats, List[Stats]]] = None,
+        constraints: Optional[Dict[str, ParameterConstraints]] = None,
+        debug: bool = True,
+        callbacks: Optional[List[Callable[[List[ShardingOption]], List[ShardingOption]]]] = None,
+        timeout_seconds: Optional[int] = None,
+        heuristical_storage_reservation_percentage: float = 0.15,
+    ) -> None:
+        if topology is None:
+            world = dist.get_world_size() if dist.is_initialized() else 1
+            topology = Topology(local_world_size=get_local_size(world) if dist.is_initialized() else 1, world_size=world,
+                                compute_device="cuda" if torch.cuda.is_available() else "cpu")
+        self._topology: Topology = topology
+        self._batch_size: int = batch_size if batch_size else BATCH_SIZE
+        self._constraints = constraints
+        self._enumerator: Enumerator = enumerator if enumerator else EmbeddingEnumerator(topology=topology, batch_size=self._batch_size, constraints=constraints)
+        self._storage_reservation: StorageReservation = (
+            storage_reservation if storage_reservation else HeuristicalStorageReservation(percentage=heuristical_storage_reservation_percentage))
+        if stats is not None:
+            self._stats: List[Stats] = [stats] if not isinstance(stats, list) else stats
+        else:
+            from torchrec_b200.distributed.planner.stats import EmbeddingStats
+
+            self._stats = [EmbeddingStats()]
+        self._debug = debug
+        self._callbacks = [] if callbacks is None else callbacks
+        if timeout_seconds is not None:
+            assert timeout_seconds > 0, "Timeout must be positive"
+        self._timeout_seconds = timeout_seconds
+
+    def collective_plan(self, module: nn.Module, sharders: Optional[List[ModuleSharder[nn.Module]]] = None,
+                        pg: Optional[dist.ProcessGroup] = None) -> ShardingPlan:
+        """Plan on rank 0 and broadcast."""
+        if pg is None:
+            assert dist.is_initialized(), "The default process group is not yet initialized. Call torch.distributed.init_process_group first."
+            pg = dist.GroupMember.WORLD
+        if sharders is None:
+            sharders = get_default_sharders()
+        return invoke_on_rank_and_broadcast_result(pg, 0, self.plan, module, sharders)
+
+    def hash_planner_context_inputs(self) -> int:
+        return hash_planner_context_inputs(self._topology, self._batch_size, self._enumerator, self._storage_reservation, self._constraints)
+
+    def hash_planner_context_inputs_str(self) -> str:
+        return hash_planner_context_inputs_str(self._topology, self._batch_size, self._enumerator, self._storage_reservation, self._constraints)
+
+
+class EmbeddingShardingPlanner(EmbeddingPlannerBase):
     """Searches for the sharding plan with the lowest estimated step time that fits in memory.
 
     Args:
@@ -107,6 +197,8 @@ class EmbeddingShardingPlanner(ShardingPlanner):
         enumerator / storage_reservation / proposer / partitioner / performance_model / stats: plug-ins.
         constraints: per-table restrictions and input statistics.
         debug: print the full plan report.
+        plan_loader: source of a plan computed earlier; when it returns one made for the same inputs (fingerprint check), the search
+            is skipped and the stored placement is used.
     """
 
     def __init__(
@@ -124,33 +216,17 @@ class EmbeddingShardingPlanner(ShardingPlanner):
         callbacks: Optional[List[Callable[[List[ShardingOption]], List[ShardingOption]]]] = None,
         timeout_seconds: Optional[int] = None,
         refine_steps: Optional[int] = None,
+        plan_loader: Optional[PlanLoader] = None,
     ) -> None:
-        if topology is None:
-            world = dist.get_world_size() if dist.is_initialized() else 1
-            topology = Topology(local_world_size=get_local_size(world) if dist.is_initialized() else 1, world_size=world,
-                                compute_device="cuda" if torch.cuda.is_available() else "cpu")
-        self._topology: Topology = topology
-        self._batch_size: int = batch_size if batch_size else BATCH_SIZE
-        self._constraints = constraints
-        self._enumerator: Enumerator = enumerator if enumerator else EmbeddingEnumerator(topology=topology, batch_size=self._batch_size, constraints=constraints)
-        self._storage_reservation: StorageReservation = storage_reservation if storage_reservation else HeuristicalStorageReservation(percentage=0.15)
+        super().__init__(topology=topology, batch_size=batch_size, enumerator=enumerator, storage_reservation=storage_reservation, stats=stats,
+                         constraints=constraints, debug=debug, callbacks=callbacks, timeout_seconds=timeout_seconds)
+        topology = self._topology
         self._partitioner: Partitioner = partitioner if partitioner else GreedyPerfPartitioner()
         if proposer:
             self._proposers: List[Proposer] = [proposer] if not isinstance(proposer, list) else proposer
         else:
             self._proposers = [GridSearchProposer(), GreedyProposer(), GreedyProposer(use_depth=False), UniformProposer()]
         self._perf_model: PerfModel = performance_model if performance_model else NoopPerfModel(topology=topology)
-        if stats is not None:
-            self._stats: List[Stats] = [stats] if not isinstance(stats, list) else stats
-        else:
-            from torchrec_b200.distributed.planner.stats import EmbeddingStats
-
-            self._stats = [EmbeddingStats()]
-        self._debug = debug
-        self._callbacks = [] if callbacks is None else callbacks
-        if timeout_seconds is not None:
-            assert timeout_seconds > 0, "Timeout must be positive"
-        self._timeout_seconds = timeout_seconds
         # local search after the proposers (see _refine): on with the default proposers, off when the caller chose the proposers
         self._refine_steps: int = (16 if not proposer else 0) if refine_steps is None else refine_steps
         self._refine_width: int = 2
@@ -158,19 +234,24 @@ class EmbeddingShardingPlanner(ShardingPlanner):
         self._num_proposals: int = 0
         self._num_plans: int = 0
         self._best_plan: Optional[List[ShardingOption]] = None
+        self.plan_loader: Optional[PlanLoader] = plan_loader
 
-    def collective_plan(self, module: nn.Module, sharders: Optional[List[ModuleSharder[nn.Module]]] = None,
-                        pg: Optional[dist.ProcessGroup] = None) -> ShardingPlan:
-        """Plan on rank 0 and broadcast."""
-        if pg is None:
-            assert dist.is_initialized(), "The default process group is not yet initialized. Call torch.distributed.init_process_group first."
-            pg = dist.GroupMember.WORLD
-        if sharders is None:
-            sharders = get_default_sharders()
-        return invoke_on_rank_and_broadcast_result(pg, 0, self.plan, module, sharders)
-
-    def hash_planner_context_inputs(self) -> int:
-        return hash_planner_context_inputs(self._topology, self._batch_size, self._enumerator, self._storage_reservation, self._constraints)
+    def _load_stored_plan(self, options: List[ShardingOption]) -> Optional[List[ShardingOption]]:
+        """The stored placement rebuilt over ``options``; None without a loader or when the loader has nothing.  A plan stored for
+        other inputs (topology, batch size, constraints, ...) is refused."""
+        if self.plan_loader is None:
+            return None
+        stored_for = self.plan_loader.plan_context_hash()
+        current = self.hash_planner_context_inputs_str()
+        if stored_for is not None and stored_for != current:
+            plan_id = getattr(self.plan_loader, "get_plan_id", lambda: None)()
+            raise PlannerError(
+                f"stored plan {plan_id} was computed for other planner inputs (stored {stored_for}, current {current}); it cannot be "
+                "shown to be valid for this model and topology", PlannerErrorType.PLANNER_INPUT_CONTEXT_MISMATCH)
+        stored = self.plan_loader.load()
+        if not stored:
+            return None
+        return extract_plan(options, stored)
 
     def plan(self, module: nn.Module, sharders: Optional[List[ModuleSharder[nn.Module]]] = None) -> ShardingPlan:
         """Search: every proposer suggests complete plans; each new suggestion is placed on devices by the partitioner and
@@ -183,9 +264,12 @@ class EmbeddingShardingPlanner(ShardingPlanner):
         options = self._enumerator.enumerate(module=module, sharders=sharders)
         if not options:
             return ShardingPlan({})
-        for proposer in self._proposers:
+        stored = self._load_stored_plan(options)
+        if stored is not None:
+            search.note_success(stored, 0.0)
+        for proposer in ([] if stored is not None else self._proposers):
             proposer.load(search_space=options, enumerator=self._enumerator)
-        for proposer in self._proposers:
+        for proposer in ([] if stored is not None else self._proposers):
             while not search.out_of_time():
                 proposal = proposer.propose()
                 if not proposal:
@@ -193,7 +277,7 @@ class EmbeddingShardingPlanner(ShardingPlanner):
                 self._try_proposal(search, proposer, proposal, budget)
             if search.out_of_time():
                 break
-        if search.best_plan is not None and self._refine_steps > 0:
+        if stored is None and search.best_plan is not None and self._refine_steps > 0:
             self._refine(search, options, budget)
         if search.best_plan is None:
             raise self._no_plan_error(search, budget)

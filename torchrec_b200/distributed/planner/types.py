@@ -347,6 +347,13 @@ class ShardingOption:
     def __hash__(self) -> int:
         return hash((self.fqn, self.sharding_type, self.compute_kernel, tuple(self.shards), self.cache_params))
 
+    def storage_hash(self) -> int:
+        """Key of this option in a stored plan: stable across processes (no salted ``hash``), and a function only of what the
+        enumerator decides before any placement - table, sharding type, kernel, cache load factor, number of shards
+        (``torchrec/distributed/planner/types.py:641-655``)."""
+        text = f"{self.fqn}|{self.sharding_type}|{self.compute_kernel}|{self.cache_load_factor}|{self.num_shards}"
+        return int.from_bytes(hashlib.blake2b(text.encode("utf-8"), digest_size=7).digest(), "big")
+
     def __deepcopy__(self, memo: Optional[Dict[int, "ShardingOption"]]) -> "ShardingOption":
         clone = object.__new__(type(self))
         clone.__dict__.update({k: (v if k in _NOT_COPIED else deepcopy(v, memo)) for k, v in self.__dict__.items()})
@@ -518,6 +525,10 @@ class PlanLoader(abc.ABC):
     @abc.abstractmethod
     def plan_context_hash(self) -> Optional[str]:
         ...
+
+    def get_plan_id(self) -> Optional[str]:
+        """Name of the stored plan for messages (optional)."""
+        return None
 
 
 @dataclass
