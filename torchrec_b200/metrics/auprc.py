@@ -32,6 +32,20 @@ def compute_auprc(n_tasks: int, predictions: torch.Tensor, labels: torch.Tensor,
     return torch.stack([_compute_auprc_helper(predictions[t], labels[t], weights[t]) for t in range(n_tasks)])
 
 
+def compute_auprc_per_group(n_tasks: int, predictions: torch.Tensor, labels: torch.Tensor, weights: torch.Tensor,
+                            grouping_keys: torch.Tensor) -> torch.Tensor:
+    """Mean over the groups of the per-group AUPRC, per task (``torchrec/metrics/auprc.py:98-141``); a leading placeholder example
+    with key -1 is ignored."""
+    keys = grouping_keys.view(-1)
+    if keys.numel() != 0 and int(keys[0]) == -1:
+        keys, predictions, labels, weights = keys[1:], predictions[:, 1:], labels[:, 1:], weights[:, 1:]
+    groups = torch.unique(keys)
+    if groups.numel() == 0:
+        return torch.zeros(n_tasks, dtype=torch.double, device=predictions.device)
+    return torch.stack([torch.stack([_compute_auprc_helper(predictions[t][keys == g], labels[t][keys == g], weights[t][keys == g]) for g in groups]).mean()
+                        for t in range(n_tasks)])
+
+
 class AUPRCMetricComputation(ListStatesComputation):
     def __init__(self, *args: Any, grouped_auprc: bool = False, **kwargs: Any) -> None:
         self._grouped = grouped_auprc
@@ -44,9 +58,7 @@ class AUPRCMetricComputation(ListStatesComputation):
         if p is None:
             v = torch.zeros(self._n_tasks, dtype=torch.double)
         elif self._grouped:
-            keys = self._cat(GROUPING_KEYS)[0].view(-1)
-            v = torch.stack([torch.stack([_compute_auprc_helper(p[t][keys == g], l[t][keys == g], w[t][keys == g]) for g in torch.unique(keys)]).mean()
-                             for t in range(self._n_tasks)])
+            v = compute_auprc_per_group(self._n_tasks, p, l, w, self._cat(GROUPING_KEYS)[0])
         else:
             v = compute_auprc(self._n_tasks, p, l, w)
         return [MetricComputationReport(name=MetricName.AUPRC, metric_prefix=MetricPrefix.WINDOW, value=v)]

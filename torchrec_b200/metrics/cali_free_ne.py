@@ -2,7 +2,7 @@
 effect of a global mis-calibration (``torchrec/metrics/cali_free_ne.py:65-89``)."""
 from __future__ import annotations
 
-from typing import Any
+from typing import Any, Dict
 
 import torch
 
@@ -20,6 +20,13 @@ def compute_cali_free_ne(ce_sum, weighted_num_samples, pos_labels, neg_labels, w
     return raw / (-pos_labels * torch.log2(mean_pred) - (weighted_num_samples - pos_labels) * torch.log2(1 - mean_pred))
 
 
+def get_cali_free_ne_states(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor, eta: float) -> Dict[str, torch.Tensor]:
+    """The NE states plus the weighted sum of predictions (the mean prediction is what the calibration-free form divides out)."""
+    states = get_ne_states(labels, predictions, weights, eta)
+    states["weighted_sum_predictions"] = (weights * predictions).sum(dim=-1)
+    return states
+
+
 class CaliFreeNEMetricComputation(SumStatesComputation):
     STATES = ("cross_entropy_sum", "weighted_num_samples", "pos_labels", "neg_labels", "weighted_sum_predictions")
 
@@ -29,9 +36,7 @@ class CaliFreeNEMetricComputation(SumStatesComputation):
         self.eta = 1e-12
 
     def _states(self, labels, predictions, weights, **kwargs):
-        s = get_ne_states(labels, predictions, weights, self.eta)
-        s["weighted_sum_predictions"] = (weights * predictions).sum(dim=-1)
-        return s
+        return get_cali_free_ne_states(labels, predictions, weights, self.eta)
 
     def _values(self, s):
         return [(MetricName.CALI_FREE_NE, compute_cali_free_ne(

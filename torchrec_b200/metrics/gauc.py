@@ -36,6 +36,47 @@ def compute_gauc_jagged(predictions: torch.Tensor, labels: torch.Tensor, weights
     return {"auc_sum": (auc * mask).sum(), "num_samples": mask.sum().double()}
 
 
+def to_3d(tensor_2d: torch.Tensor, seq_lengths: torch.Tensor, max_length: int) -> torch.Tensor:
+    """Jagged rows ``[sum(seq_lengths), D]`` to a zero-padded ``[groups, max_length, D]`` block."""
+    lengths = seq_lengths.view(-1).long()
+    groups = lengths.numel()
+    out = tensor_2d.new_zeros((groups, max_length, tensor_2d.shape[1]))
+    gid = torch.repeat_interleave(torch.arange(groups, device=tensor_2d.device), lengths, output_size=tensor_2d.shape[0])
+    start = torch.cumsum(lengths, 0) - lengths
+    pos = torch.arange(tensor_2d.shape[0], device=tensor_2d.device) - start[gid]
+    keep = pos < max_length
+    out[gid[keep], pos[keep]] = tensor_2d[keep]
+    return out
+
+
+def compute_gauc_3d(predictions: torch.Tensor, labels: torch.Tensor, weights: torch.Tensor) -> Dict[str, torch.Tensor]:
+    """Grouped AUC over zero-padded groups, all inputs ``[n_task, n_group, n_sample]``: padding carries weight 0, so it adds nothing
+    to either class; a group counts when it has weight in both classes and its non-zero predictions are not all equal
+    (``torchrec/metrics/gauc.py:24-91``).  Returns per-task ``auc_sum`` and ``num_samples``."""
+    order = torch.argsort(predictions, dim=-1)
+    l = torch.gather(labels, -1, order).double()
+    w = torch.gather(weights, -1, order).double()
+    neg_w = w * (1 - l)
+    numer = (l * w * torch.cumsum(neg_w, dim=-1)).sum(-1)
+    w_pos, w_neg = (l * w).sum(-1), neg_w.sum(-1)
+    auc = numer / (w_pos * w_neg + 1e-10)
+    flat = ((predictions == predictions[..., :1]) | (predictions == 0)).all(dim=-1)
+    counted = (w_pos > 0) & (w_neg > 0) & ~flat
+    return {"auc_sum": (auc * counted).sum(-1), "num_samples": counted.sum(-1)}
+
+
+def get_auc_states(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor, num_candidates: torch.Tensor) -> Dict[str, torch.Tensor]:
+    """Per-task GAUC states from ``[n_task, n_sample]`` inputs whose samples are grouped by ``num_candidates``; computed on the jagged
+    layout (one sort by (group, prediction)), without padding the groups to the longest one."""
+    outs = [compute_gauc_jagged(predictions[t], labels[t], weights[t], num_candidates.view(-1)) for t in range(labels.shape[0])]
+    return {"auc_sum": torch.stack([o["auc_sum"] for o in outs]), "num_samples": torch.stack([o["num_samples"] for o in outs])}
+
+
+def compute_window_auc(auc: torch.Tensor, num_samples: torch.Tensor) -> Dict[str, torch.Tensor]:
+    """Mean AUC over the counted groups; 0.5 when no group counted."""
+    return {"gauc": (auc + 1e-9) / (num_samples + 2e-9), "num_samples": num_samples}
+
+
 class GAUCMetricComputation(SumStatesComputation):
     STATES = ("auc_sum", "num_samples")
 
@@ -45,8 +86,7 @@ class GAUCMetricComputation(SumStatesComputation):
             nc = (kwargs.get("required_inputs") or {}).get("num_candidates")
         if nc is None:
             raise RecMetricException("GAUC needs 'num_candidates' (group sizes)")
-        outs = [compute_gauc_jagged(predictions[t], labels[t], weights[t], nc.view(-1)) for t in range(labels.shape[0])]
-        return {"auc_sum": torch.stack([o["auc_sum"] for o in outs]), "num_samples": torch.stack([o["num_samples"] for o in outs])}
+        return get_auc_states(labels, predictions, weights, nc)
 
     def _values(self, s):
         return [(MetricName.GAUC, safe_div(s["auc_sum"], s["num_samples"])), (MetricName.GAUC_NUM_SAMPLES, s["num_samples"])]

@@ -20,14 +20,31 @@ def compute_threshold_idx(num_true_positives: torch.Tensor, num_false_positives:
     return int(ok[0]) if ok.numel() else THRESHOLD_GRANULARITY - 1
 
 
-def get_pr_states(labels: torch.Tensor, predictions: torch.Tensor, weights: Optional[torch.Tensor]):
+def _sum_over_thresholds(predictions: torch.Tensor, mass: torch.Tensor, above: bool) -> torch.Tensor:
+    """``out[i] = sum(mass[predictions >= t_i])`` (or ``<=``) for the 1000 thresholds, as one [thresholds, samples] comparison."""
     p = predictions.double().view(-1)
-    l = labels.double().view(-1)
-    w = torch.ones_like(p) if weights is None else weights.double().view(-1)
     thr = torch.linspace(0, 1, steps=THRESHOLD_GRANULARITY, dtype=torch.double, device=p.device).unsqueeze(1)
-    above = (p.unsqueeze(0) >= thr).double()
-    below = (p.unsqueeze(0) <= thr).double()
-    return {"true_pos_sum": (above * (w * l)).sum(-1), "false_pos_sum": (above * (w * (1 - l))).sum(-1), "false_neg_sum": (below * (w * l)).sum(-1)}
+    side = (p.unsqueeze(0) >= thr) if above else (p.unsqueeze(0) <= thr)
+    return (side * mass.double().view(1, -1)).sum(-1)
+
+
+def compute_true_pos_sum(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    return _sum_over_thresholds(predictions, weights * labels, above=True)
+
+
+def compute_false_pos_sum(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    return _sum_over_thresholds(predictions, weights * (1 - labels), above=True)
+
+
+def compute_false_neg_sum(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    return _sum_over_thresholds(predictions, weights * labels, above=False)
+
+
+def get_pr_states(labels: torch.Tensor, predictions: torch.Tensor, weights: Optional[torch.Tensor]):
+    if weights is None:
+        weights = torch.ones_like(predictions)
+    return {"true_pos_sum": compute_true_pos_sum(labels, predictions, weights), "false_pos_sum": compute_false_pos_sum(labels, predictions, weights),
+            "false_neg_sum": compute_false_neg_sum(labels, predictions, weights)}
 
 
 class HindsightTargetPRMetricComputation(SumStatesComputation):

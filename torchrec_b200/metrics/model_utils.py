@@ -42,13 +42,31 @@ def parse_model_outputs(label_name: str, prediction_name: str, weight_name: str,
     return labels, predictions, weights
 
 
+def session_ids_to_tensor(session_ids: List[str], device: Optional[torch.device] = None) -> torch.Tensor:
+    """Session names of consecutive examples to run numbers: 1 for the first run of equal names, 2 for the next, ...
+    (``["a", "a", "b", "a"]`` -> ``[1, 1, 2, 3]``); the form the session metrics take their grouping in
+    (``torchrec/metrics/model_utils.py:20-38``)."""
+    runs: List[int] = []
+    current = 0
+    previous: object = object()
+    for name in session_ids:
+        if name != previous:
+            current += 1
+            previous = name
+        runs.append(current)
+    return torch.tensor(runs, device=device)
+
+
 def parse_required_inputs(model_out: Dict[str, torch.Tensor], required_inputs_list: List[str], ndcg_transform_input: bool = False,
                           device: Optional[torch.device] = None) -> Dict[str, torch.Tensor]:
     required_inputs: Dict[str, torch.Tensor] = {}
     for feature in required_inputs_list:
         if feature not in model_out:
             continue
-        t = model_out[feature].squeeze()
+        value = model_out[feature]
+        if ndcg_transform_input and isinstance(value, list):
+            value = model_out[feature] = session_ids_to_tensor(value, device=device)
+        t = value.squeeze()
         assert isinstance(t, torch.Tensor)
         required_inputs[feature] = t.to(device) if device is not None else t
     return required_inputs

@@ -2,7 +2,7 @@
 classes (``torchrec/metrics/multiclass_recall.py:28-81``).  Predictions are ``[n_tasks, n, n_classes]``."""
 from __future__ import annotations
 
-from typing import Any, Tuple
+from typing import Any, Dict, Tuple
 
 import torch
 
@@ -21,6 +21,10 @@ def compute_multiclass_recall_at_k(tp_at_k: torch.Tensor, total_weights: torch.T
     return tp_at_k / total_weights.unsqueeze(-1)
 
 
+def get_multiclass_recall_states(predictions: torch.Tensor, labels: torch.Tensor, weights: torch.Tensor, n_classes: int) -> Dict[str, torch.Tensor]:
+    return {"tp_at_k": compute_true_positives_at_k(predictions, labels, weights, n_classes), "total_weights": weights.double().sum(dim=-1)}
+
+
 class MulticlassRecallMetricComputation(SumStatesComputation):
     STATES = ("tp_at_k", "total_weights")
 
@@ -34,7 +38,7 @@ class MulticlassRecallMetricComputation(SumStatesComputation):
     def _states(self, labels, predictions, weights, **kwargs):
         if predictions.dim() == 2:  # [n, C] for a single task
             predictions = predictions.unsqueeze(0)
-        return {"tp_at_k": compute_true_positives_at_k(predictions, labels, weights, self._n_classes), "total_weights": weights.double().sum(dim=-1)}
+        return get_multiclass_recall_states(predictions, labels, weights, self._n_classes)
 
     def _values(self, s):
         return [(MetricName.MULTICLASS_RECALL, compute_multiclass_recall_at_k(s["tp_at_k"], s["total_weights"]))]

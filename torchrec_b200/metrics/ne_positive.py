@@ -1,7 +1,7 @@
 """Normalized entropy restricted to the positive examples' cross entropy (``torchrec/metrics/ne_positive.py``)."""
 from __future__ import annotations
 
-from typing import Any
+from typing import Any, Dict
 
 import torch
 
@@ -16,6 +16,24 @@ def compute_cross_entropy_positive(labels, predictions, weights, eta):
     return -weights * labels * torch.log2(p)
 
 
+def compute_ne_positive(ce_positive_sum: torch.Tensor, weighted_num_samples: torch.Tensor, pos_labels: torch.Tensor, neg_labels: torch.Tensor,
+                        eta: float, allow_missing_label_with_zero_weight: bool = False) -> torch.Tensor:
+    """Cross entropy of the positives over the entropy of the base rate; ``eta`` for every task when a task has no weight and
+    missing labels are allowed (``torchrec/metrics/ne_positive.py:48-65``)."""
+    if allow_missing_label_with_zero_weight and not bool(weighted_num_samples.all()):
+        return torch.full_like(weighted_num_samples, eta)
+    return ce_positive_sum / base_rate_entropy(pos_labels, neg_labels, weighted_num_samples, eta)
+
+
+def get_ne_positive_states(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor, eta: float) -> Dict[str, torch.Tensor]:
+    return {
+        "cross_entropy_positive_sum": compute_cross_entropy_positive(labels, predictions, weights, eta).sum(dim=-1),
+        "weighted_num_samples": weights.sum(dim=-1),
+        "pos_labels": (weights * labels).sum(dim=-1),
+        "neg_labels": (weights * (1.0 - labels)).sum(dim=-1),
+    }
+
+
 class NEPositiveMetricComputation(SumStatesComputation):
     STATES = ("cross_entropy_positive_sum", "weighted_num_samples", "pos_labels", "neg_labels")
 
@@ -25,19 +43,11 @@ class NEPositiveMetricComputation(SumStatesComputation):
         self.eta = 1e-12
 
     def _states(self, labels, predictions, weights, **kwargs):
-        return {
-            "cross_entropy_positive_sum": compute_cross_entropy_positive(labels, predictions, weights, self.eta).sum(dim=-1),
-            "weighted_num_samples": weights.sum(dim=-1),
-            "pos_labels": (weights * labels).sum(dim=-1),
-            "neg_labels": (weights * (1.0 - labels)).sum(dim=-1),
-        }
+        return get_ne_positive_states(labels, predictions, weights, self.eta)
 
     def _values(self, s):
-        if self._allow_missing and not bool(s["weighted_num_samples"].all()):
-            v = torch.full_like(s["weighted_num_samples"], self.eta)
-        else:
-            v = s["cross_entropy_positive_sum"] / base_rate_entropy(s["pos_labels"], s["neg_labels"], s["weighted_num_samples"], self.eta)
-        return [(MetricName.NE_POSITIVE, v)]
+        return [(MetricName.NE_POSITIVE, compute_ne_positive(s["cross_entropy_positive_sum"], s["weighted_num_samples"], s["pos_labels"],
+                                                             s["neg_labels"], self.eta, self._allow_missing))]
 
 
 class NEPositiveMetric(RecMetric):

@@ -1,7 +1,7 @@
 """Binary precision at a threshold (``torchrec/metrics/precision.py``)."""
 from __future__ import annotations
 
-from typing import Any, Dict
+from typing import Any, Dict, Optional
 
 import torch
 
@@ -14,9 +14,21 @@ def compute_precision(num_true_positives: torch.Tensor, num_false_positives: tor
     return safe_div(num_true_positives, num_true_positives + num_false_positives)
 
 
-def get_precision_states(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor, threshold: float = 0.5) -> Dict[str, torch.Tensor]:
-    pos = (predictions.double() >= threshold).double()
-    return {"true_pos_sum": (weights * pos * labels).sum(dim=-1), "false_pos_sum": (weights * pos * (1 - labels)).sum(dim=-1)}
+def compute_true_pos_sum(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor, threshold: float = 0.5) -> torch.Tensor:
+    """Weight of the positives predicted at or above the threshold, per task."""
+    return (weights * (predictions.double() >= threshold) * labels).sum(dim=-1)
+
+
+def compute_false_pos_sum(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor, threshold: float = 0.5) -> torch.Tensor:
+    """Weight of the negatives predicted at or above the threshold, per task."""
+    return (weights * (predictions.double() >= threshold) * (1 - labels)).sum(dim=-1)
+
+
+def get_precision_states(labels: torch.Tensor, predictions: torch.Tensor, weights: Optional[torch.Tensor], threshold: float = 0.5) -> Dict[str, torch.Tensor]:
+    if weights is None:
+        weights = torch.ones_like(predictions)
+    return {"true_pos_sum": compute_true_pos_sum(labels, predictions, weights, threshold),
+            "false_pos_sum": compute_false_pos_sum(labels, predictions, weights, threshold)}
 
 
 class PrecisionMetricComputation(SumStatesComputation):

@@ -54,6 +54,33 @@ def compute_rauc(n_tasks: int, predictions: torch.Tensor, labels: torch.Tensor, 
     return torch.stack([_compute_rauc_helper(predictions[t], labels[t], weights[t]) for t in range(n_tasks)])
 
 
+def count_reverse_pairs_divide_and_conquer(input: List[float]) -> float:
+    """Fraction of the pairs of ``input`` that are out of order (a later element smaller than an earlier one)."""
+    n = len(input)
+    if n < 2:
+        return 0.0
+    return _count_inversions(torch.as_tensor(input, dtype=torch.double)) / (n * (n - 1) / 2)
+
+
+def _without_padding(keys: torch.Tensor, *per_task: torch.Tensor):
+    """Drop the leading placeholder example (key -1) that an empty state list carries so that a sync never gathers nothing."""
+    if keys.numel() != 0 and int(keys[0]) == -1:
+        return (keys[1:],) + tuple(t[:, 1:] for t in per_task)
+    return (keys,) + per_task
+
+
+def compute_rauc_per_group(n_tasks: int, predictions, labels, weights, grouping_keys: torch.Tensor) -> torch.Tensor:
+    """Mean over the groups of the per-group RAUC, per task; inputs ``[n_tasks, n]`` tensors or lists of such chunks
+    (``torchrec/metrics/rauc.py:151-205``)."""
+    p, l, w = (torch.cat(list(x), dim=-1) if isinstance(x, (list, tuple)) else x for x in (predictions, labels, weights))
+    keys, p, l, w = _without_padding(grouping_keys.view(-1), p, l, w)
+    groups = torch.unique(keys)
+    if groups.numel() == 0:
+        return torch.full((n_tasks,), 0.5, dtype=torch.double)
+    return torch.stack([torch.stack([_compute_rauc_helper(p[t][keys == g], l[t][keys == g], w[t][keys == g]) for g in groups]).mean()
+                        for t in range(n_tasks)])
+
+
 class RAUCMetricComputation(ListStatesComputation):
     def __init__(self, *args: Any, grouped_rauc: bool = False, **kwargs: Any) -> None:
         self._grouped = grouped_rauc
@@ -66,9 +93,7 @@ class RAUCMetricComputation(ListStatesComputation):
         if p is None:
             v = torch.full((self._n_tasks,), 0.5, dtype=torch.double)
         elif self._grouped:
-            keys = self._cat(GROUPING_KEYS)[0].view(-1)
-            v = torch.stack([torch.stack([_compute_rauc_helper(p[t][keys == g], l[t][keys == g], w[t][keys == g]) for g in torch.unique(keys)]).mean()
-                             for t in range(self._n_tasks)])
+            v = compute_rauc_per_group(self._n_tasks, p, l, w, self._cat(GROUPING_KEYS)[0])
         else:
             v = compute_rauc(self._n_tasks, p, l, w)
         return [MetricComputationReport(name=MetricName.RAUC, metric_prefix=MetricPrefix.WINDOW, value=v.to(p.device if p is not None else "cpu"))]

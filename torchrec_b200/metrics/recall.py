@@ -1,7 +1,7 @@
 """Binary recall at a threshold (``torchrec/metrics/recall.py``)."""
 from __future__ import annotations
 
-from typing import Any, Dict
+from typing import Any, Dict, Optional
 
 import torch
 
@@ -14,9 +14,22 @@ def compute_recall(num_true_positives: torch.Tensor, num_false_negitives: torch.
     return safe_div(num_true_positives, num_true_positives + num_false_negitives)
 
 
-def get_recall_states(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor, threshold: float = 0.5) -> Dict[str, torch.Tensor]:
-    pos = (predictions.double() >= threshold).double()
-    return {"true_pos_sum": (weights * pos * labels).sum(dim=-1), "false_neg_sum": (weights * (1 - pos) * labels).sum(dim=-1)}
+def compute_true_pos_sum(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor, threshold: float = 0.5) -> torch.Tensor:
+    """Weight of the positives predicted at or above the threshold, per task."""
+    return (weights * (predictions.double() >= threshold) * labels).sum(dim=-1)
+
+
+def compute_false_neg_sum(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor, threshold: float = 0.5) -> torch.Tensor:
+    """Weight of the positives predicted at or below the threshold, per task (a prediction equal to the threshold counts on both
+    sides, as in ``torchrec/metrics/recall.py:45-52``)."""
+    return (weights * (predictions.double() <= threshold) * labels).sum(dim=-1)
+
+
+def get_recall_states(labels: torch.Tensor, predictions: torch.Tensor, weights: Optional[torch.Tensor], threshold: float = 0.5) -> Dict[str, torch.Tensor]:
+    if weights is None:
+        weights = torch.ones_like(predictions)
+    return {"true_pos_sum": compute_true_pos_sum(labels, predictions, weights, threshold),
+            "false_neg_sum": compute_false_neg_sum(labels, predictions, weights, threshold)}
 
 
 class RecallMetricComputation(SumStatesComputation):

@@ -2,7 +2,7 @@
 (``torchrec/metrics/segmented_ne.py``).  Reported as ``..._segmented_ne_<group>``."""
 from __future__ import annotations
 
-from typing import Any, List, Tuple
+from typing import Any, Dict, List, Tuple
 
 import torch
 
@@ -14,6 +14,24 @@ from torchrec_b200.metrics.rec_metric import MetricComputationReport, RecMetric,
 PREDICTIONS = "predictions"
 LABELS = "labels"
 WEIGHTS = "weights"
+
+
+def compute_ne_helper(ce_sum: torch.Tensor, weighted_num_samples: torch.Tensor, pos_labels: torch.Tensor, neg_labels: torch.Tensor,
+                      eta: float) -> torch.Tensor:
+    """NE of every (task, group) cell at once: cross entropy over the entropy of the cell's base rate."""
+    return compute_ne(ce_sum, weighted_num_samples, pos_labels, neg_labels, eta)
+
+
+def get_segemented_ne_states(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor, grouping_keys: torch.Tensor, eta: float,
+                             num_groups: int) -> Dict[str, torch.Tensor]:
+    """Per-group sums of the four NE states, ``[n_tasks, num_groups]``, as four products with the one-hot matrix of the keys (the
+    reference walks the distinct keys with a mask each, ``torchrec/metrics/segmented_ne.py:105-152``).  Keys outside
+    ``[0, num_groups)`` fall into the nearest group."""
+    keys = grouping_keys.view(-1).long().clamp(0, num_groups - 1)
+    onehot = torch.nn.functional.one_hot(keys, num_groups).double()  # [n, G]
+    ce = compute_cross_entropy(labels, predictions, weights, eta)
+    w, l = weights.double(), labels.double()
+    return {"cross_entropy_sum": ce @ onehot, "weighted_num_samples": w @ onehot, "pos_labels": (w * l) @ onehot, "neg_labels": (w * (1 - l)) @ onehot}
 
 
 class SegmentedNEMetricComputation(SumStatesComputation):
@@ -38,16 +56,12 @@ class SegmentedNEMetricComputation(SumStatesComputation):
             raise RecMetricException(f"Inputs 'predictions' and 'weights' and '{self._grouping_keys}' should not be None for NEMetricComputation update")
         if self._cast_keys_to_int:
             keys = keys.to(torch.int64)
-        keys = keys.view(-1).long().clamp(0, self._num_groups - 1)
-        onehot = torch.nn.functional.one_hot(keys, self._num_groups).double()  # [n, G]
-        ce = compute_cross_entropy(labels, predictions, weights, self.eta)
-        w, l = weights.double(), labels.double()
-        return {"cross_entropy_sum": ce @ onehot, "weighted_num_samples": w @ onehot, "pos_labels": (w * l) @ onehot, "neg_labels": (w * (1 - l)) @ onehot}
+        return get_segemented_ne_states(labels, predictions, weights, keys, self.eta, self._num_groups)
 
     def _compute(self) -> List[MetricComputationReport]:
         reports = []
         for prefix, get in ((MetricPrefix.LIFETIME, lambda n: getattr(self, n)), (MetricPrefix.WINDOW, self.get_window_state)):
-            ne = compute_ne(get("cross_entropy_sum"), get("weighted_num_samples"), get("pos_labels"), get("neg_labels"), self.eta)
+            ne = compute_ne_helper(get("cross_entropy_sum"), get("weighted_num_samples"), get("pos_labels"), get("neg_labels"), self.eta)
             for g in range(self._num_groups):
                 reports.append(MetricComputationReport(name=MetricName.SEGMENTED_NE, metric_prefix=prefix, value=ne[:, g], description="_" + str(g)))
         return reports

@@ -2,6 +2,8 @@
 (``torchrec/metrics/xauc.py:26-68``)."""
 from __future__ import annotations
 
+from typing import Dict
+
 import torch
 
 from torchrec_b200.metrics._sum_states import SumStatesComputation, safe_div
@@ -23,14 +25,23 @@ def compute_weighted_num_pairs(weights: torch.Tensor) -> torch.Tensor:
     return torch.triu(w.unsqueeze(-1) * w.unsqueeze(-2), diagonal=1).sum(dim=(-1, -2))
 
 
+def compute_xauc(error_sum: torch.Tensor, weighted_num_pairs: torch.Tensor) -> torch.Tensor:
+    """Concordant pair weight over total pair weight; 0 where no pair was seen."""
+    return safe_div(error_sum, weighted_num_pairs)
+
+
+def get_xauc_states(labels: torch.Tensor, predictions: torch.Tensor, weights: torch.Tensor) -> Dict[str, torch.Tensor]:
+    return {"error_sum": compute_error_sum(labels, predictions, weights), "weighted_num_pairs": compute_weighted_num_pairs(weights)}
+
+
 class XAUCMetricComputation(SumStatesComputation):
     STATES = ("error_sum", "weighted_num_pairs")
 
     def _states(self, labels, predictions, weights, **kwargs):
-        return {"error_sum": compute_error_sum(labels, predictions, weights), "weighted_num_pairs": compute_weighted_num_pairs(weights)}
+        return get_xauc_states(labels, predictions, weights)
 
     def _values(self, s):
-        return [(MetricName.XAUC, safe_div(s["error_sum"], s["weighted_num_pairs"]))]
+        return [(MetricName.XAUC, compute_xauc(s["error_sum"], s["weighted_num_pairs"]))]
 
 
 class XAUCMetric(RecMetric):
