@@ -227,3 +227,49 @@ def test_inference_kjt_pool_over_virtual_devices():
     ids = torch.tensor([10, 0, 4, 3, 8, 10])
     got, want = sharded(ids), pool.lookup(ids)
     assert got.keys() == want.keys() and torch.equal(got.lengths(), want.lengths()) and torch.equal(got.values(), want.values())
+
+
+def test_small_helpers_of_sparse_and_feature_modules():
+    """``jt_is_equal`` / ``regroup_kts`` / position-weight helpers / ``TrainInputMapper`` / ``apply_mc_method_to_jt_dict``."""
+    from torchrec_b200.modules.feature_processor import PositionWeightedModule
+    from torchrec_b200.modules.feature_processor_ import get_stride_per_key_per_rank, get_weights_list
+    from torchrec_b200.modules.hash_mc_modules import TrainInputMapper
+    from torchrec_b200.modules.mc_modules import apply_mc_method_to_jt_dict
+    from torchrec_b200.sparse.jagged_tensor import JaggedTensor, KeyedJaggedTensor, KeyedTensor, jt_is_equal, regroup_kts
+
+    a = JaggedTensor(values=torch.tensor([1.0, 2.0, 3.0]), lengths=torch.tensor([2, 0, 1]))
+    b = JaggedTensor(values=torch.tensor([1.0, 2.0, 3.0]), offsets=torch.tensor([0, 2, 2, 3]))
+    assert jt_is_equal(a, b) and not jt_is_equal(a, JaggedTensor(values=torch.tensor([1.0, 2.0, 3.0]), lengths=torch.tensor([1, 1, 1])))
+    assert not jt_is_equal(a, "a") and not jt_is_equal(a, JaggedTensor(values=a.values(), lengths=a.lengths(), weights=torch.ones(3)))
+
+    kt1 = KeyedTensor(keys=["x", "y"], length_per_key=[2, 3], values=torch.arange(10.0).view(2, 5))
+    kt2 = KeyedTensor(keys=["z"], length_per_key=[1], values=torch.tensor([[100.0], [200.0]]))
+    got = regroup_kts([kt1, kt2], [["z", "x"], ["y", "x"]])
+    want = KeyedTensor.regroup([kt1, kt2], [["z", "x"], ["y", "x"]])
+    assert all(torch.equal(g, w) for g, w in zip(got, want)) and got[0].tolist() == [[100.0, 0.0, 1.0], [200.0, 5.0, 6.0]]
+
+    kjt = KeyedJaggedTensor(keys=["f0", "f1"], values=torch.arange(6), lengths=torch.tensor([2, 1, 3, 0]))
+    seq = torch.tensor([0, 1, 0, 0, 1, 2])
+    w = get_weights_list(seq, kjt, {"f1": torch.nn.Parameter(torch.tensor([0.5, 0.25, 0.125]))})
+    assert w.tolist() == [1.0, 1.0, 1.0, 0.5, 0.25, 0.125]
+    assert get_stride_per_key_per_rank(kjt) is None
+    vb = KeyedJaggedTensor(keys=["f0", "f1"], values=torch.arange(3), lengths=torch.tensor([1, 1, 1]), stride_per_key_per_rank=[[2], [1]])
+    assert get_stride_per_key_per_rank(vb) == [[2], [1]]
+
+    pw = PositionWeightedModule({"f1": 4})
+    out = pw({"f0": a, "f1": JaggedTensor(values=torch.tensor([7, 8, 9]), lengths=torch.tensor([3]))})
+    assert set(out) == {"f0", "f1"} and out["f0"].weights_or_none() is None and out["f1"].weights().tolist() == [1.0, 1.0, 1.0]
+
+    # ids dealt to 4 chunks of unequal size, modulo rule and block rule
+    sizes, starts = torch.tensor([10, 20, 30, 40]), torch.tensor([0, 10, 30, 60])
+    ids = torch.tensor([0, 5, 6, 7, 103])
+    seen, local, off = TrainInputMapper(0, 4, sizes, starts, inference_dispatch_div_train_world_size=True)(ids)
+    assert seen.tolist() == [0, 1, 1, 1, 25] and local.tolist() == [10, 20, 30, 40, 40] and off.tolist() == [0, 10, 30, 60, 60]
+    seen, local, off = TrainInputMapper(100, 4, sizes, starts)(torch.tensor([0, 24, 25, 99]), output_offset=torch.tensor(10))
+    assert seen.tolist() == [0, 24, 25, 99] and local.tolist() == [10, 10, 20, 40] and off.tolist() == [-10, -10, 0, 50]
+
+    class _Mc(torch.nn.Module):
+        def remap(self, features):
+            return {k: JaggedTensor(values=v.values() + 1, lengths=v.lengths()) for k, v in features.items()}
+
+    assert apply_mc_method_to_jt_dict(_Mc(), "remap", {"f": a})["f"].values().tolist() == [2.0, 3.0, 4.0]

@@ -18,6 +18,13 @@ class BaseFeatureProcessor(nn.Module):
         ...
 
 
+def position_weighted_module_update_features(features: Dict[str, JaggedTensor], weighted_features: Dict[str, JaggedTensor]) -> Dict[str, JaggedTensor]:
+    """``features`` with the entries of ``weighted_features`` put in place of the unweighted ones (features without a position weight
+    pass through)."""
+    features.update(weighted_features)
+    return features
+
+
 class PositionWeightedModule(BaseFeatureProcessor):
     def __init__(self, max_feature_lengths: Dict[str, int], device: Optional[torch.device] = None) -> None:
         super().__init__()
@@ -30,7 +37,7 @@ class PositionWeightedModule(BaseFeatureProcessor):
             jt = features[key]
             seq = offsets_to_range_traceble(jt.offsets(), jt.values())
             out[key] = JaggedTensor(values=jt.values(), lengths=jt.lengths(), offsets=jt.offsets(), weights=torch.gather(pw, 0, seq.long()))
-        return out
+        return position_weighted_module_update_features(features, out)
 
 
 class BaseGroupedFeatureProcessor(nn.Module):

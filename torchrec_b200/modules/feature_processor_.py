@@ -53,6 +53,24 @@ class PositionWeightedModule(FeatureProcessor):
         return JaggedTensor(values=features.values(), weights=weighted, lengths=features.lengths(), offsets=features.offsets())
 
 
+def get_weights_list(cat_seq: torch.Tensor, features: KeyedJaggedTensor, position_weights: Dict[str, nn.Parameter]) -> Optional[torch.Tensor]:
+    """Weight of every id of ``features`` given its position ``cat_seq`` inside its bag: the feature's position weight where the
+    feature has one, 1 elsewhere.  The per-feature form of what ``PositionWeightedModuleCollection.forward`` does in one gather
+    (``torchrec/modules/feature_processor_.py:139-153``)."""
+    pieces = []
+    for key, seq in zip(features.keys(), torch.split(cat_seq, features.length_per_key())):
+        if key in position_weights:
+            pieces.append(torch.gather(position_weights[key], 0, seq.long()))
+        else:
+            pieces.append(torch.ones(seq.shape[0], device=features.values().device))
+    return torch.cat(pieces) if pieces else features.weights_or_none()
+
+
+def get_stride_per_key_per_rank(kjt: KeyedJaggedTensor) -> Optional[List[List[int]]]:
+    """The per-key per-rank batch sizes of a variable-batch KJT, None for a fixed batch."""
+    return kjt.stride_per_key_per_rank() if kjt.variable_stride_per_key() else None
+
+
 class PositionWeightedModuleCollection(FeatureProcessorsCollection):
     def __init__(self, max_feature_lengths: Dict[str, int], device: Optional[torch.device] = None) -> None:
         super().__init__()

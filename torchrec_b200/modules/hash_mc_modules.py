@@ -36,6 +36,43 @@ def create_zch_buffer(size: int, support_evict: bool, device: torch.device) -> T
     return identities, metadata
 
 
+class TrainInputMapper(torch.nn.Module):
+    """Where every id of an inference input would have gone at training time.  At inference the slot tables of all training ranks
+    are merged into one; an id must still be probed inside the chunk of the rank that owned it.  ``forward(values, output_offset)``
+    returns, per id: the id as that rank saw it (divided by, or reduced modulo, the dealing rule when
+    ``inference_dispatch_div_train_world_size``), the size of the owning chunk, and the chunk's first row (minus ``output_offset``).
+    Ids are dealt to ``total_num_buckets`` chunks by ``id % buckets`` when ``input_hash_size`` is 0, else by contiguous blocks of
+    ``ceil(input_hash_size / buckets)`` ids - the rule of the row-wise input distribution.
+    Counterpart of ``torchrec/modules/hash_mc_modules.py:44-147``."""
+
+    def __init__(self, input_hash_size: int, total_num_buckets: int, size_per_rank: torch.Tensor, train_rank_offsets: torch.Tensor,
+                 inference_dispatch_div_train_world_size: bool = False, name: Optional[str] = None) -> None:
+        super().__init__()
+        assert total_num_buckets > 0, f"{total_num_buckets=} must be positive"
+        self._input_hash_size = input_hash_size
+        self._buckets = total_num_buckets
+        self._inference_dispatch_div_train_world_size = inference_dispatch_div_train_world_size
+        self._name = name
+        self.register_buffer("_zch_size_per_training_rank", size_per_rank, persistent=False)
+        self.register_buffer("_train_rank_offsets", train_rank_offsets, persistent=False)
+
+    def forward(self, values: torch.Tensor, output_offset: Optional[torch.Tensor] = None
+                ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+        sizes = self._zch_size_per_training_rank.to(values.device)
+        starts = self._train_rank_offsets.to(values.device)
+        if self._input_hash_size == 0:
+            owner = values % self._buckets
+            seen = values // self._buckets if self._inference_dispatch_div_train_world_size else values
+        else:
+            block = -(-self._input_hash_size // self._buckets)
+            owner = values // block
+            seen = values % block if self._inference_dispatch_div_train_world_size else values
+        offsets = starts.index_select(0, owner)
+        if output_offset is not None:
+            offsets = offsets - output_offset
+        return seen, sizes.index_select(0, owner), offsets
+
+
 class HashZchManagedCollisionModule(ManagedCollisionModule):
     IDENTITY_BUFFER: str = "_hash_zch_identities"
     METADATA_BUFFER: str = "_hash_zch_metadata"

@@ -23,6 +23,12 @@ from torchrec_b200.sparse.jagged_tensor import JaggedTensor, KeyedJaggedTensor
 
 
 @torch.no_grad()
+def apply_mc_method_to_jt_dict(mc_module: nn.Module, method: str, features_dict: Dict[str, JaggedTensor]) -> Dict[str, JaggedTensor]:
+    """Call ``mc_module.<method>(features_dict)`` (``"preprocess"``, ``"profile"``, ``"remap"``): one entry point for the steps a
+    collection runs on every module's features, in the dictionary's order."""
+    return getattr(mc_module, method)(features_dict)
+
+
 def dynamic_threshold_filter(id_counts: torch.Tensor, threshold_skew_multiplier: float = 10.0) -> Tuple[torch.Tensor, torch.Tensor]:
     """Keep ids seen more often than ``multiplier * total / distinct``."""
     num_ids = id_counts.numel()

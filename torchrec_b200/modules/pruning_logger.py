@@ -7,7 +7,11 @@ from contextlib import contextmanager
 from typing import Any, Iterator, Optional
 
 
-class PruningLogDetails:
+class PruningLogBase(object):
+    """Marker base for what a logger yields."""
+
+
+class PruningLogDetails(PruningLogBase):
     """Attribute bag filled inside ``with pruning_logger(...) as details``."""
 
     def __setattr__(self, name: str, value: Any) -> None:

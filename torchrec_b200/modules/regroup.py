@@ -50,6 +50,16 @@ class PermuteMultiEmbedding(nn.Module):
         return list(torch.index_select(cat, 1, self._index).split(self._out_lengths, dim=1))
 
 
+def module_init(module: "KTRegroupAsDict", keyed_tensors: List[KeyedTensor]) -> None:
+    """First-call setup of a ``KTRegroupAsDict``: check that the inputs agree on device and key dimension and build the cached
+    permutation (``torchrec/modules/regroup.py:39-55``)."""
+    assert len(keyed_tensors) > 0, "Empty list provided"
+    assert all(kt.device() == keyed_tensors[0].device() for kt in keyed_tensors), "All inputs should be on the same device."
+    assert all(kt.key_dim() == keyed_tensors[0].key_dim() for kt in keyed_tensors), "All inputs should have the same key_dim"
+    assert keyed_tensors[0].key_dim() == 1, "regrouping needs key_dim 1"
+    module._init_regroup(keyed_tensors)
+
+
 class KTRegroupAsDict(nn.Module):
     """``forward(List[KeyedTensor]) -> {key_i: tensor of groups[i]}`` with the permutation cached after the first call."""
 
@@ -69,7 +79,6 @@ class KTRegroupAsDict(nn.Module):
 
     def forward(self, keyed_tensors: List[KeyedTensor]) -> Dict[str, torch.Tensor]:
         if not self._is_inited:
-            assert all(kt.key_dim() == 1 for kt in keyed_tensors), "regrouping needs key_dim 1"
-            self._init_regroup(keyed_tensors)
+            module_init(self, keyed_tensors)
         values = [kt.values().to(self._emb_dtype) if self._emb_dtype is not None else kt.values() for kt in keyed_tensors]
         return dict(zip(self._keys, self._permute_pooled_embs_impl(values)))

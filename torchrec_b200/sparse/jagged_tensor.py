@@ -838,6 +838,31 @@ pytree.register_pytree_node(
 )
 
 
+def jt_is_equal(jt_1: "JaggedTensor", jt_2: "JaggedTensor") -> bool:
+    """Equality of two jagged tensors: values and weights (close, for floats), and the same bag boundaries whether either side
+    stores them as lengths or as offsets.  Anything that is not a ``JaggedTensor`` compares unequal."""
+    if not isinstance(jt_1, JaggedTensor) or not isinstance(jt_2, JaggedTensor):
+        return False
+    if (jt_1.weights_or_none() is None) != (jt_2.weights_or_none() is None):
+        return False
+    pairs = [(jt_1.values(), jt_2.values()), (jt_1.lengths(), jt_2.lengths())]
+    if jt_1.weights_or_none() is not None:
+        pairs.append((jt_1.weights(), jt_2.weights()))
+    for a, b in pairs:
+        if a.shape != b.shape:
+            return False
+        same = torch.allclose(a, b.to(a.dtype)) if a.is_floating_point() or b.is_floating_point() else torch.equal(a.to(b.dtype), b)
+        if not same:
+            return False
+    return True
+
+
+def regroup_kts(keyed_tensors: List["KeyedTensor"], groups: List[List[str]]) -> List[torch.Tensor]:
+    """``groups[i]`` names the keys (from any of ``keyed_tensors``) whose columns form output ``i``, in that order; one kernel moves
+    every column (``permute_multi_embedding``).  Same result as ``KeyedTensor.regroup``."""
+    return _regroup_keyed_tensors(keyed_tensors, groups)
+
+
 def kjt_is_equal(kjt_1: "KeyedJaggedTensor", kjt_2: "KeyedJaggedTensor") -> bool:
     """Field-by-field equality of two KJTs (keys order included)."""
     if not isinstance(kjt_1, KeyedJaggedTensor) or not isinstance(kjt_2, KeyedJaggedTensor):
