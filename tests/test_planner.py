@@ -282,3 +282,41 @@ def test_stored_plan_is_reused_and_a_plan_for_other_inputs_is_refused():
     with pytest.raises(PlannerError) as err:
         extract_plan(options, partial)
     assert err.value.error_type == PlannerErrorType.PLAN_LOADING_FAILED
+
+
+def test_pipeline_io_cost_offload_stats_and_small_planner_helpers():
+    from torchrec_b200.distributed.planner.partitioners import OrderedDeviceHardware
+    from torchrec_b200.distributed.planner.shard_estimators import EmbeddingOffloadStats, calculate_pipeline_io_cost
+    from torchrec_b200.distributed.planner.stats import round_to_one_sigfig
+    from torchrec_b200.distributed.planner.types import DeviceHardware, Perf, Storage
+    from torchrec_b200.distributed.sharding_plan import placement_helper
+    from torchrec_b200.distributed.types import PipelineType
+
+    assert calculate_pipeline_io_cost(100, 1000, 50, PipelineType.NONE, None) == 1100
+    assert calculate_pipeline_io_cost(100, 1000, 50, PipelineType.TRAIN_SPARSE_DIST, None) == 200
+    assert calculate_pipeline_io_cost(100, 1000, 50, PipelineType.TRAIN_SPARSE_DIST, None, count_ephemeral_storage_cost=True) == 1200
+    assert calculate_pipeline_io_cost(100, 1000, 50, PipelineType.TRAIN_PREFETCH_SPARSE_DIST, None) == 300 + 350
+    assert calculate_pipeline_io_cost(100, 1000, 50, PipelineType.TRAIN_PREFETCH_SPARSE_DIST, 6) == 300 + 100
+    assert calculate_pipeline_io_cost(100, 1000, 50, PipelineType.TRAIN_SPARSE_DIST, None, is_inference=True) == 0
+
+    # 10 bins over 100 rows; 60 % of the lookups reuse within 10 rows, 40 % within 50
+    hist = torch.zeros(10)
+    hist[0], hist[4] = 60.0, 40.0
+    stats = EmbeddingOffloadStats(cacheability=0.3, expected_lookups=77, mrc_hist_counts=hist, height=100)
+    assert stats.expected_lookups == 77 and stats.cacheability == 0.3
+    assert abs(stats.expected_miss_rate(0.05) - 0.4) < 1e-6     # the first bin is reached: its 60 % hit
+    assert abs(stats.expected_miss_rate(0.45) - 0.0) < 1e-6     # bin 4 reached: everything hits
+    assert abs(stats.expected_miss_rate(0.3) - 0.4) < 1e-6
+    assert stats.expected_miss_rate(0.0) == 1.0 and stats.expected_miss_rate(1.0) == 0.0
+    assert float(EmbeddingOffloadStats.estimate_cache_miss_rate(torch.tensor(30.0), torch.zeros(4), torch.linspace(0, 100, 5))) == 0.0
+    assert abs(EmbeddingOffloadStats.estimate_cacheability(hist) - (4 * 0.4) / 10) < 1e-6
+    with pytest.raises(ValueError):
+        EmbeddingOffloadStats(0.0, 0, torch.zeros(2, 2), 10)
+
+    assert round_to_one_sigfig(0.0123) == "0.01" and round_to_one_sigfig(1234) == "1000" and round_to_one_sigfig(0.5) == "0.5"
+    assert placement_helper("cuda", 3, 11) == "rank:11/cuda:3" and placement_helper("cpu", 3, 11) == "rank:0/cpu"
+
+    # equally loaded devices: local rank 0 of host 1 (rank 4) comes before local rank 1 of host 0 (rank 1)
+    mk = lambda rank, perf: OrderedDeviceHardware(DeviceHardware(rank=rank, storage=Storage(hbm=1, ddr=1), perf=Perf(fwd_compute=perf, fwd_comms=0, bwd_compute=0, bwd_comms=0)), 4)
+    order = sorted([mk(1, 1.0), mk(4, 1.0), mk(0, 1.0), mk(5, 0.5)])
+    assert [o.device.rank for o in order] == [5, 0, 4, 1]

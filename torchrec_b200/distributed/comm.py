@@ -18,6 +18,7 @@ logger: logging.Logger = logging.getLogger(__name__)
 
 _INTRA_PG: Optional[dist.ProcessGroup] = None
 _CROSS_PG: Optional[dist.ProcessGroup] = None
+_NODE_GROUP_SIZE_2D: Optional[int] = None  # ranks per node inside a sharding group, set when the 2D node groups are built
 
 
 def _env2int(env_list: List[str], default: int = -1) -> int:
@@ -36,6 +37,14 @@ def get_local_size(world_size: Optional[int] = None) -> int:
         logging.warning("Could not determine LOCAL_WORLD_SIZE from environment, falling back to WORLD_SIZE.")
         local_size = world_size
     return local_size
+
+
+def get_node_group_size(world_size: Optional[int] = None) -> int:
+    """Ranks per node as the sharding group of a 2D-parallel job sees them (recorded by ``intra_and_cross_node_pg_2D``); the plain
+    local size when no 2D groups were built."""
+    if _NODE_GROUP_SIZE_2D is None:
+        return get_local_size(world_size)
+    return _NODE_GROUP_SIZE_2D
 
 
 def get_local_rank(world_size: Optional[int] = None, rank: Optional[int] = None) -> int:
@@ -90,9 +99,10 @@ def intra_and_cross_node_pg(
 
 
 def reset_node_process_groups() -> None:
-    global _INTRA_PG, _CROSS_PG
+    global _INTRA_PG, _CROSS_PG, _NODE_GROUP_SIZE_2D
     _INTRA_PG = None
     _CROSS_PG = None
+    _NODE_GROUP_SIZE_2D = None
 
 
 def intra_and_cross_node_pg_2D(env, device: Optional[torch.device] = None):
@@ -102,6 +112,8 @@ def intra_and_cross_node_pg_2D(env, device: Optional[torch.device] = None):
     sharding_group_size = dist.get_world_size(env.sharding_pg)
     world_size = dist.get_world_size()
     local_size = env.node_group_size if env.node_group_size else get_local_size(world_size)
+    global _NODE_GROUP_SIZE_2D
+    _NODE_GROUP_SIZE_2D = local_size
     num_sharding_groups = world_size // sharding_group_size
     step = 1 if env.use_inter_host_allreduce else num_sharding_groups
     intra_pg = cross_pg = None

@@ -79,6 +79,22 @@ def _group_and_sort_non_uniform_sharding_options(sharding_options: List[Sharding
     return groups
 
 
+@dataclass
+class OrderedDeviceHardware:
+    """A device as the greedy partitioner's heap orders it: least loaded first; among equally loaded devices the lower local rank
+    first, so that consecutive shards spread over the hosts (and their DDR) instead of filling one host
+    (``torchrec/distributed/planner/partitioners.py:158-173``)."""
+
+    device: DeviceHardware
+    local_world_size: int
+
+    def _key(self) -> Tuple[float, int, int]:
+        return (self.device.perf.total, self.device.rank % self.local_world_size, self.device.rank)
+
+    def __lt__(self, other: "OrderedDeviceHardware") -> bool:
+        return self._key() < other._key()
+
+
 class GreedyPerfPartitioner(Partitioner):
     def __init__(self, sort_by: str = SortBy.STORAGE, balance_modules: bool = False) -> None:
         self._sort_by = sort_by
@@ -111,7 +127,7 @@ class GreedyPerfPartitioner(Partitioner):
 
     @staticmethod
     def _establish_minheap(devices: List[DeviceHardware], local_world_size: int) -> List:
-        heap = [(d.perf.total, i, d) for i, d in enumerate(devices)]
+        heap = [OrderedDeviceHardware(d, max(local_world_size, 1)) for d in devices]
         heapq.heapify(heap)
         return heap
 
@@ -122,23 +138,24 @@ class GreedyPerfPartitioner(Partitioner):
                 tmp = []
                 placed = False
                 while minheap_devices:
-                    perf, idx, device = heapq.heappop(minheap_devices)
+                    entry = heapq.heappop(minheap_devices)
+                    device = entry.device
                     storage = cast(Storage, shard.storage)
                     if storage.fits_in(device.storage):
                         shard.rank = device.rank
                         device.storage -= storage
                         device.perf += cast(Perf, shard.perf)
-                        heapq.heappush(minheap_devices, (device.perf.total, idx, device))
+                        heapq.heappush(minheap_devices, entry)
                         placed = True
                         break
-                    tmp.append((perf, idx, device))
+                    tmp.append(entry)
                 for t in tmp:
                     heapq.heappush(minheap_devices, t)
                 if not placed:
                     raise PlannerError(
                         error_type=PlannerErrorType.PARTITION,
                         message=f"Device partition failed. Couldn't find a rank for shard {shard} of table {so.name}, largest device storage: "
-                                f"{max((d.storage for _, _, d in minheap_devices), key=lambda s: s.hbm) if minheap_devices else None}",
+                                f"{max((e.device.storage for e in minheap_devices), key=lambda s: s.hbm) if minheap_devices else None}",
                     )
 
     @classmethod

@@ -296,19 +296,96 @@ class EmbeddingStorageEstimator(ShardEstimator):
             optimizer_class = None
             if hasattr(so.tensor, "_optimizer_classes") and so.tensor._optimizer_classes:
                 optimizer_class = so.tensor._optimizer_classes[0]
-            count_ephemeral = self._run_embedding_at_peak_memory or self._pipeline_type != PipelineType.NONE or True
-            multiplier = {PipelineType.NONE: 1.0, PipelineType.TRAIN_BASE: 1.0, PipelineType.TRAIN_SPARSE_DIST: 2.0, PipelineType.TRAIN_PREFETCH_SPARSE_DIST: 3.0}.get(self._pipeline_type, 1.0)
+            # the lookup's outputs live from forward to backward: they count toward the peak unless the caller says that the
+            # embedding step does not run at the model's memory peak
+            count_ephemeral = True
+            mpp = getattr(so.cache_params, "multipass_prefetch_config", None) if so.cache_params else None
             shard_storages = calculate_shard_storages(
                 sharder=sharder, sharding_type=so.sharding_type, tensor=so.tensor, compute_device=self._topology.compute_device,
                 compute_kernel=so.compute_kernel, shard_sizes=[s.size for s in so.shards], batch_sizes=batch_sizes,
                 world_size=self._topology.world_size, local_world_size=self._topology.local_world_size, input_lengths=so.input_lengths,
                 num_poolings=num_poolings, caching_ratio=caching_ratio if caching_ratio else UVM_CACHING_RATIO, is_pooled=so.is_pooled,
-                input_data_type_size=BIGINT_DTYPE, output_data_type_size=float(so.tensor.element_size()), pipeline_multiplier=multiplier,
+                input_data_type_size=BIGINT_DTYPE, output_data_type_size=float(so.tensor.element_size()), pipeline_type=self._pipeline_type,
+                multipass_prefetch_max_pass=getattr(mpp, "num_passes", None),
                 count_ephemeral_storage_cost=count_ephemeral, is_inference=self._is_inference, optimizer_class=optimizer_class,
                 fused_params=fused_params,
             )
             for shard, storage in zip(so.shards, shard_storages):
                 shard.storage = storage
+
+
+def calculate_pipeline_io_cost(input_size: int, output_size: int, prefetch_size: int, pipeline_type: PipelineType,
+                               multipass_prefetch_max_pass: Optional[int], count_ephemeral_storage_cost: bool = False,
+                               is_inference: bool = False) -> int:
+    """Bytes of id / output buffers that a train pipeline keeps alive at its peak, given the bytes of ONE batch's ids (``input_size``),
+    outputs (``output_size``) and prefetched rows (``prefetch_size``).  A sparse-dist pipeline holds the ids of two batches, the
+    prefetch pipeline three plus the prefetch burst (smaller when the prefetch is split into passes); outputs count only when
+    short-lived buffers are counted; no pipeline: one batch of each; inference: nothing beyond the step itself.
+    Same accounting as ``torchrec/distributed/planner/shard_estimators.py:1087-1127``."""
+    if is_inference:
+        return 0
+    outputs = output_size if count_ephemeral_storage_cost else 0
+    if pipeline_type == PipelineType.TRAIN_SPARSE_DIST:
+        return 2 * input_size + outputs
+    if pipeline_type == PipelineType.TRAIN_PREFETCH_SPARSE_DIST:
+        passes = multipass_prefetch_max_pass or 1
+        return 3 * input_size + int((1 + 6 / passes) * prefetch_size) + outputs
+    return input_size + output_size
+
+
+class EmbeddingOffloadStats(CacheStatistics):
+    """Cache statistics of a table served through a software cache, from a histogram of its LRU miss-ratio curve.
+
+    ``mrc_hist_counts[i]`` is the number of lookups that hit if the cache holds at least ``(i + 1) / n`` of the table's ``height``
+    rows and would miss with less (a histogram of LRU stack distances over ``n`` equal bins).  ``expected_miss_rate(clf)`` is then the
+    share of lookups whose stack distance is not covered by a cache of ``clf * height`` rows.  ``cacheability`` is the area under
+    the miss-ratio curve (0: a tiny cache serves everything, 1: nothing is ever reused); ``expected_lookups`` the expected number of
+    distinct ids per global batch.  Counterpart of ``torchrec/distributed/planner/shard_estimators.py:1660-1774``."""
+
+    def __init__(self, cacheability: float, expected_lookups: int, mrc_hist_counts: torch.Tensor, height: int) -> None:
+        if mrc_hist_counts.dim() != 1:
+            raise ValueError(f"expected 1d tensor, got {mrc_hist_counts.dim()}d")
+        if mrc_hist_counts.numel() == 0:
+            raise ValueError("expected non-empty tensor")
+        self._cacheability = cacheability
+        self._expected_lookups = expected_lookups
+        self.height = height
+        self.hist: torch.Tensor = mrc_hist_counts
+        self.bins: torch.Tensor = torch.linspace(0, height, len(mrc_hist_counts) + 1)
+
+    @property
+    def expected_lookups(self) -> int:
+        return self._expected_lookups
+
+    @property
+    def cacheability(self) -> float:
+        return self._cacheability
+
+    def expected_miss_rate(self, clf: float) -> float:
+        return float(EmbeddingOffloadStats.estimate_cache_miss_rate(torch.tensor(clf * self.height), self.hist, self.bins))
+
+    @staticmethod
+    def estimate_cache_miss_rate(cache_sizes: torch.Tensor, hist: torch.Tensor, bins: torch.Tensor) -> torch.Tensor:
+        """Miss ratio at each of ``cache_sizes`` (rows): 1 - (share of the histogram in the bins that a cache of that size covers
+        completely or reaches into).  A cache of k rows serves stack distances up to k - 1."""
+        total = hist.sum()
+        if float(total) == 0:
+            return torch.zeros_like(cache_sizes, dtype=torch.float32)  # never used: never missed
+        miss_after_bin = 1 - hist.cumsum(0) / total  # miss ratio once the cache reaches bin i
+        sizes = cache_sizes.to(bins.dtype)
+        reached = torch.bucketize(sizes - 1, bins, right=True) - 1  # index of the bin that holds distance k - 1; -1: below the first edge
+        beyond = reached >= hist.numel()
+        out = miss_after_bin[reached.clamp(0, hist.numel() - 1)]
+        out = torch.where(reached < 0, torch.ones_like(out), out)
+        return torch.where(beyond, torch.zeros_like(out), out)
+
+    @staticmethod
+    def estimate_cacheability(hist: torch.Tensor) -> float:
+        """Area under the miss-ratio curve of ``hist``, in [0, 1]."""
+        total = hist.sum()
+        if float(total) == 0:
+            return 0.0
+        return float((1 - hist.cumsum(0) / total).sum() / hist.numel())
 
 
 def _optimizer_multiplier(optimizer_class: Optional[Type[torch.optim.Optimizer]], shape: torch.Size, fused_params: Dict) -> float:
@@ -333,8 +410,9 @@ def _optimizer_multiplier(optimizer_class: Optional[Type[torch.optim.Optimizer]]
 def calculate_shard_storages(
     sharder, sharding_type: str, tensor: torch.Tensor, compute_device: str, compute_kernel: str, shard_sizes: List[List[int]],
     batch_sizes: List[int], world_size: int, local_world_size: int, input_lengths: List[float], num_poolings: List[float],
-    caching_ratio: float, is_pooled: bool, input_data_type_size: float, output_data_type_size: float, pipeline_multiplier: float = 1.0,
+    caching_ratio: float, is_pooled: bool, input_data_type_size: float, output_data_type_size: float, pipeline_type: PipelineType = PipelineType.NONE,
     count_ephemeral_storage_cost: bool = False, is_inference: bool = False, optimizer_class=None, fused_params: Optional[Dict] = None,
+    multipass_prefetch_max_pass: Optional[int] = None,
 ) -> List[Storage]:
     fused_params = fused_params or {}
     tensor_storage = sharder.storage_usage(tensor, compute_device, compute_kernel)
@@ -364,7 +442,10 @@ def calculate_shard_storages(
         else:
             in_sz = batch_inputs_total * world_size * input_data_type_size
             out_sz = batch_outputs_total * world_size * emb_dim * output_data_type_size
-        io = math.ceil((in_sz + out_sz) * pipeline_multiplier) if count_ephemeral_storage_cost else 0
+        io = calculate_pipeline_io_cost(
+            input_size=math.ceil(in_sz), output_size=math.ceil(out_sz), prefetch_size=math.ceil(in_sz) if table_cached else 0,
+            pipeline_type=pipeline_type, multipass_prefetch_max_pass=multipass_prefetch_max_pass,
+            count_ephemeral_storage_cost=count_ephemeral_storage_cost, is_inference=is_inference)
         w_hbm = math.ceil(hbm_storage * frac)
         w_ddr = math.ceil(ddr_storage * frac)
         o_hbm = math.ceil(w_hbm * opt_mult)

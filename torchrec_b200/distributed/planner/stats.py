@@ -177,6 +177,11 @@ def _abbr(sharding_type: str) -> str:
     }.get(sharding_type, sharding_type)
 
 
+def round_to_one_sigfig(x: float) -> str:
+    """``x`` rounded to one significant figure, printed without exponent noise (``0.0123`` -> ``"0.01"``, ``1234`` -> ``"1000"``)."""
+    return f'{float(f"{x:.1g}"):g}'
+
+
 def _format_table(rows: List[List[str]]) -> List[str]:
     widths = [max(len(r[i]) for r in rows) for i in range(len(rows[0]))]
     out = []

@@ -65,6 +65,13 @@ def placement(compute_device: str, rank: int, local_size: int) -> str:
     return f"rank:{rank}/{param_device}"
 
 
+def placement_helper(device_type: str, index: int = 0, rank: int = 0) -> str:
+    """The placement string of a shard: ``rank:<rank>/<device>:<index>``; host memory is always written as rank 0's."""
+    if device_type == "cpu":
+        return f"rank:0/{device_type}"
+    return f"rank:{rank}/{device_type}:{index}"
+
+
 def _rw(hash_size: int, num_devices: int, columns: int, num_buckets: Optional[int] = None):
     shard_sizes: List[List[int]] = []
     if num_buckets:
