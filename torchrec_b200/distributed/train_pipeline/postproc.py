@@ -32,6 +32,20 @@ def _record_stream(obj: Any, stream: torch.Stream, depth: int = 0) -> None:
             _record_stream(v, stream, depth + 1)
 
 
+class NoOpStream:
+    """Context manager that accepts a stream and does nothing: stands in for ``torch.cuda.stream(...)`` where there is no stream to
+    switch to (CPU runs, or a post-processing module that stays on the caller's stream)."""
+
+    def __init__(self, stream: Optional[torch.Stream]) -> None:
+        self._stream = stream
+
+    def __enter__(self) -> "NoOpStream":
+        return self
+
+    def __exit__(self, exc_type, exc_value, traceback) -> None:
+        return None
+
+
 class PipelinedPostproc(torch.nn.Module):
     """Stands in for ``postproc_module`` (found at ``fqn`` in the model).  ``run(batch, context)`` computes the module's output
     from the batch through ``call_args`` once per context; ``forward`` returns the output cached in the current context, or falls

@@ -111,6 +111,35 @@ class PrefetchPipelinedForward(BaseForward[PrefetchTrainPipelineContext]):
         return self._module.compute_and_output_dist(ctx, data)
 
 
+class PrefetchEmbeddingPipelinedForward(PrefetchPipelinedForward):
+    """For a pipeline that prefetches AND runs the lookup of batch N at the end of step N - 1: the pipeline calls
+    ``compute_and_output_dist()`` ahead of time (on the inputs that went through the prefetch stage) and the model's forward then only
+    picks up the awaitable.  Calling the forward first is a usage error
+    (``torchrec/distributed/train_pipeline/runtime_forwards.py:271-328``)."""
+
+    def __init__(self, name: str, args: CallArgs, module: ShardedModule, context: PrefetchTrainPipelineContext, prefetch_stream: Optional[torch.Stream] = None) -> None:
+        super().__init__(name, args, module, context, prefetch_stream)
+        self._compute_and_output_dist_awaitable: Optional[Awaitable] = None
+
+    def compute_and_output_dist(self) -> None:
+        assert self._name in self._context.module_input_post_prefetch, (
+            "PrefetchEmbeddingPipelinedForward has no prefetched input for this module: do not call model.forward() directly")
+        data = self._context.module_input_post_prefetch.pop(self._name)
+        ctx = self._context.module_contexts_post_prefetch.pop(self._name)
+        if self._stream is not None:
+            cur_stream = torch.get_device_module(self._device).current_stream()
+            cur_stream.wait_stream(self._stream)
+            data.record_stream(cur_stream)
+            ctx.record_stream(cur_stream)
+        self._compute_and_output_dist_awaitable = self._module.compute_and_output_dist(ctx, data)
+
+    def __call__(self, *input, **kwargs) -> Awaitable:
+        if self._compute_and_output_dist_awaitable is None:
+            raise Exception("compute_and_output_dist must be called before __call__")
+        out, self._compute_and_output_dist_awaitable = self._compute_and_output_dist_awaitable, None
+        return out
+
+
 class KJTAllToAllForward:
     """Stage 1 of ``KJTAllToAll`` without the collective: the pipelines batch the split exchange of all
     modules into one collective (``FusedKJTListSplitsAwaitable``)."""

@@ -18,6 +18,7 @@ import abc
 import contextlib
 import logging
 from collections import deque
+from dataclasses import dataclass
 from typing import Any, Callable, Deque, Dict, Generic, Iterator, List, Optional, Tuple, Type, Union, cast
 
 import torch
@@ -57,6 +58,18 @@ logger: logging.Logger = logging.getLogger(__name__)
 
 class ModelDetachedException(Exception):
     pass
+
+
+@dataclass
+class TorchCompileConfig:
+    """Compile settings in the shape ``TrainPipelinePT2`` accepts: whole-graph capture, dynamic shapes (None: automatic), backend,
+    and the iteration at which compilation would happen.  No pipeline of this package compiles the model (the hot path is the
+    hand-written kernels); only ``compile_on_iter`` has an effect: it is the iteration at which the pre / post compile hooks run."""
+
+    fullgraph: bool = False
+    dynamic: Optional[bool] = None
+    backend: str = "inductor"
+    compile_on_iter: int = 3
 
 
 class TrainPipeline(abc.ABC, Generic[In, Out]):
@@ -155,18 +168,26 @@ class TrainPipelineBase(TrainPipeline[In, Out]):
 class TrainPipelinePT2(TrainPipelineBase[In, Out]):
     """Kept for API parity: this framework does not use a tracing compiler, so the model runs eagerly
     (CUDA kernels + streams); the class behaves like ``TrainPipelineBase``.  The captured-step counterpart is
-    ``TrainPipelineGraphed``."""
+    ``TrainPipelineGraphed``.  ``pre_compile_fn`` / ``post_compile_fn`` run once, at iteration ``compile_configs.compile_on_iter``
+    (where the counterpart compiles, ``torchrec/distributed/train_pipeline/train_pipelines.py:329-372``)."""
 
-    def __init__(self, model: torch.nn.Module, optimizer: torch.optim.Optimizer, device: torch.device, compile_configs: Optional[Any] = None,
+    def __init__(self, model: torch.nn.Module, optimizer: torch.optim.Optimizer, device: torch.device,
+                 compile_configs: Optional[TorchCompileConfig] = None,
                  pre_compile_fn: Optional[Callable[[torch.nn.Module], None]] = None, post_compile_fn: Optional[Callable[[torch.nn.Module], None]] = None,
                  input_transformer: Optional[Callable[[In], In]] = None) -> None:
         super().__init__(model, optimizer, device)
+        self._compile_configs: TorchCompileConfig = compile_configs or TorchCompileConfig()
+        self._pre_compile_fn = pre_compile_fn
+        self._post_compile_fn = post_compile_fn
         self._input_transformer = input_transformer
-        for hook in (pre_compile_fn, post_compile_fn):
-            if hook is not None:
-                hook(model)
+        self._iter = 0
 
     def progress(self, dataloader_iter: Iterator[In]) -> Out:
+        if self._iter == self._compile_configs.compile_on_iter:
+            for hook in (self._pre_compile_fn, self._post_compile_fn):
+                if hook is not None:
+                    hook(self._model)
+        self._iter += 1
         transform = self._input_transformer
         return super().progress(dataloader_iter if transform is None else map(transform, dataloader_iter))
 

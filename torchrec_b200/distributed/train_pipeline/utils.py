@@ -38,6 +38,11 @@ def _to_device(batch: In, device: torch.device, non_blocking: bool) -> In:
     return cast(In, batch.to(device=device, non_blocking=non_blocking))
 
 
+def get_h2d_func(batch: In, device: torch.device) -> Pipelineable:
+    """The default host-to-device step of a data-loading stage: ``batch.to(device, non_blocking=True)``."""
+    return batch.to(device, non_blocking=True)
+
+
 def _wait_for_batch(batch: In, stream: Optional[torch.Stream]) -> None:
     """Make the current stream wait for ``stream`` and mark ``batch`` as used on the current stream."""
     if stream is None:
