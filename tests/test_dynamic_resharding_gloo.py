@@ -38,7 +38,12 @@ def _worker(rank, world_size):
         torch.testing.assert_close(step(mov), step(ref))
         new = sp.construct_module_sharding_plan(build().ebc, {"t0": sp.table_wise(rank=1), "t1": sp.row_wise(), "t2": sp.table_wise(rank=0), "t3": sp.table_wise(rank=1)},
                                                 sharder=EmbeddingBagCollectionSharder(), world_size=world_size, local_size=world_size, device_type="cpu")
-        mov.reshard("ebc", {k: new[k] for k in ("t0", "t1")})
+        from torchrec_b200.distributed.sharding.dynamic_sharding import output_sharding_plan_delta_single, output_sharding_plans_delta
+
+        volume, delta = output_sharding_plan_delta_single(mov.module.ebc.module_sharding_plan, new, return_data_volume=True)
+        assert set(delta) == {"t0", "t1"} and volume > 0  # t2 and t3 stay where they are
+        assert set(output_sharding_plans_delta({"ebc": mov.module.ebc.module_sharding_plan}, {"ebc": new})["ebc"][1]) == {"t0", "t1"}
+        mov.reshard("ebc", delta)
         assert {k: v.sharding_type for k, v in mov.module.ebc.module_sharding_plan.items()} == {"t0": "table_wise", "t1": "row_wise", "t2": "table_wise", "t3": "table_wise"}
         assert mov.module.ebc.module_sharding_plan["t0"].ranks == [1]
         for _ in range(3):
@@ -49,3 +54,26 @@ def _worker(rank, world_size):
 
 def test_reshard_keeps_training_identical():
     run_multi_process(_worker, world_size=2)
+
+
+def test_plan_update_and_host_offload_helpers():
+    from types import SimpleNamespace
+
+    from torchrec_b200.distributed.sharding.dynamic_sharding import move_sharded_tensors_to_cpu, update_module_sharding_plan
+    from torchrec_b200.distributed.types import ParameterSharding
+
+    old = ParameterSharding(sharding_type="table_wise", compute_kernel="fused", ranks=[0])
+    new = ParameterSharding(sharding_type="table_wise", compute_kernel="fused", ranks=[1])
+    info = SimpleNamespace(embedding_config=SimpleNamespace(name="t0"), param_sharding=old)
+    other = SimpleNamespace(embedding_config=SimpleNamespace(name="t1"), param_sharding=old)
+    module = SimpleNamespace(module_sharding_plan={"t0": old, "t1": old})
+    update_module_sharding_plan(module, {"t0": new}, {"table_wise": [info, other]})
+    assert module.module_sharding_plan["t0"] is new and info.param_sharding is new and other.param_sharding is old
+    try:
+        update_module_sharding_plan(SimpleNamespace(), {"t0": new}, {})
+        raise AssertionError("a module without a plan must be refused")
+    except RuntimeError:
+        pass
+    nested = {"a": [torch.ones(2), ("x", 3)], "b": {"c": 1.5}}
+    out = move_sharded_tensors_to_cpu(nested)
+    assert out["b"]["c"] == 1.5 and out["a"][1] == ("x", 3) and torch.equal(out["a"][0], torch.ones(2))

@@ -200,3 +200,72 @@ def reshard_module(dmp: nn.Module, sharded_module_fqn: str, sharded_module: nn.M
         parent = getattr(parent, p)
     setattr(parent, parts[-1], new)
     return new
+
+
+# ---- helpers around a resharding call ---------------------------------------------------------------------
+def update_module_sharding_plan(module: Any, changed_sharding_params: Dict[str, ParameterSharding],
+                                sharding_type_to_sharding_infos: Dict[str, List[Any]]) -> None:
+    """Write the new ``ParameterSharding`` of every changed table into the module's plan and into the sharding info that describes
+    the table (looked up under the NEW sharding type: a table keeps its sharding type when it moves).
+    Counterpart of ``torchrec/distributed/sharding/dynamic_sharding.py:835-869``."""
+    if not hasattr(module, "module_sharding_plan"):
+        raise RuntimeError("Module does not have a module_sharding_plan attribute")
+    plan = module.module_sharding_plan
+    for name, param in changed_sharding_params.items():
+        plan[name] = param
+        for info in sharding_type_to_sharding_infos.get(param.sharding_type, []):
+            if info.embedding_config.name == name:
+                info.param_sharding = param
+
+
+def output_sharding_plan_delta_single(old_plan: Dict[str, ParameterSharding], new_plan: Dict[str, ParameterSharding],
+                                      return_data_volume: bool = False) -> Tuple[float, Dict[str, ParameterSharding]]:
+    """The tables of one module whose ranks differ between two plans, as the (copied) entries of the new plan - what
+    ``DistributedModelParallel.reshard`` takes - and, on request, the MiB of fp32 weights those tables hold (else 0).  Both plans
+    must name the same tables."""
+    from torchrec_b200.distributed.types import EmbeddingModuleShardingPlan
+
+    assert len(old_plan) == len(new_plan), "old and new plan must cover the same tables"
+    diff = EmbeddingModuleShardingPlan({k: copy.deepcopy(v) for k, v in new_plan.items() if v.ranks != old_plan[k].ranks})
+    volume = 0.0
+    if return_data_volume:
+        for sharding in diff.values():
+            if sharding.sharding_spec is None:
+                continue
+            for shard in sharding.sharding_spec.shards:
+                volume += shard.shard_sizes[0] * shard.shard_sizes[1] * 4 / (1024 * 1024)
+    return volume, diff
+
+
+def output_sharding_plans_delta(old_plan: Dict[str, Dict[str, ParameterSharding]], new_plan: Dict[str, Dict[str, ParameterSharding]],
+                                return_data_volume: bool = False) -> Dict[str, Tuple[float, Dict[str, ParameterSharding]]]:
+    """``output_sharding_plan_delta_single`` for every module of a whole-model plan (``ShardingPlan.plan``)."""
+    out: Dict[str, Tuple[float, Dict[str, ParameterSharding]]] = {}
+    for fqn, plan in old_plan.items():
+        assert fqn in new_plan, f"Found mismatch between old and new plans, key: {fqn} not found in new plan"
+        out[fqn] = output_sharding_plan_delta_single(plan, new_plan[fqn], return_data_volume)
+    return out
+
+
+def move_sharded_tensors_to_cpu(state_dict: Dict[str, Any]) -> Dict[str, Any]:
+    """Move the local shards of every ``ShardedTensor`` inside a (nested) state dict to host memory, in place, and return the
+    dict; other values are untouched.  Keeps a checkpoint-sized copy out of HBM while a resharding rebuilds the module."""
+
+    def walk(item: Any) -> Any:
+        if isinstance(item, ShardedTensor):
+            for shard in item.local_shards():
+                if shard.tensor.device.type != "cpu":
+                    shard.tensor = shard.tensor.cpu()
+            return item
+        if isinstance(item, dict):
+            return {k: walk(v) for k, v in item.items()}
+        if isinstance(item, list):
+            return [walk(v) for v in item]
+        if isinstance(item, tuple):
+            return tuple(walk(v) for v in item)
+        return item
+
+    out = walk(state_dict)
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
+    return out
