@@ -13,6 +13,7 @@ collection ``:442``); over several nodes the reference additionally confines a t
 """
 from __future__ import annotations
 
+from dataclasses import dataclass, field
 from typing import Any, Dict, Iterator, List, Optional, Type
 
 import torch
@@ -26,6 +27,7 @@ from torchrec_b200.distributed.types import Awaitable, LazyAwaitable, NoWait, Pa
 from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
 from torchrec_b200.modules.embedding_tower import EmbeddingTower, EmbeddingTowerCollection
 from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor, KeyedTensor
+from torchrec_b200.streamable import Multistreamable
 
 
 class _TowerOutput(LazyAwaitable[torch.Tensor]):
@@ -161,6 +163,17 @@ class EmbeddingTowerSharder(BaseEmbeddingSharder[EmbeddingTower]):
         return [ShardingType.TABLE_WISE.value, ShardingType.ROW_WISE.value, ShardingType.TABLE_ROW_WISE.value, ShardingType.COLUMN_WISE.value]
 
 
+@dataclass
+class EmbeddingTowerCollectionContext(Multistreamable):
+    """The contexts of the towers of one step of a sharded tower collection, in tower order."""
+
+    embedding_contexts: List[Any] = field(default_factory=list)
+
+    def record_stream(self, stream: torch.Stream) -> None:
+        for ctx in self.embedding_contexts:
+            ctx.record_stream(stream)
+
+
 class ShardedEmbeddingTowerCollection(nn.Module):
     """Every tower sharded on its own; ``forward`` concatenates the tower outputs like the unsharded collection."""
 
@@ -169,6 +182,9 @@ class ShardedEmbeddingTowerCollection(nn.Module):
         super().__init__()
         self.towers = nn.ModuleList([tower_sharder.shard(t, p, env, device, module_fqn=f"towers.{i}") for i, (t, p) in enumerate(zip(module.towers, tower_to_params))])
         self._input_params = module._input_params
+
+    def create_context(self) -> EmbeddingTowerCollectionContext:
+        return EmbeddingTowerCollectionContext(embedding_contexts=[tower.create_context() for tower in self.towers])
 
     def forward(self, features: Optional[KeyedJaggedTensor] = None, weighted_features: Optional[KeyedJaggedTensor] = None) -> torch.Tensor:
         pending = []

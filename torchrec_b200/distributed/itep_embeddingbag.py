@@ -12,7 +12,7 @@ import torch
 from torch import nn
 from torch.nn.parallel import DistributedDataParallel
 
-from torchrec_b200.distributed.embedding import EmbeddingCollectionSharder, ShardedEmbeddingCollection
+from torchrec_b200.distributed.embedding import EmbeddingCollectionContext, EmbeddingCollectionSharder, ShardedEmbeddingCollection
 from torchrec_b200.distributed.embedding_types import BaseEmbeddingSharder, KJTList, ShardedEmbeddingModule
 from torchrec_b200.distributed.embeddingbag import EmbeddingBagCollectionContext, EmbeddingBagCollectionSharder, ShardedEmbeddingBagCollection
 from torchrec_b200.distributed.types import Awaitable, LazyAwaitable, ParameterSharding, QuantizedCommCodecs, ShardingEnv, ShardingType
@@ -35,6 +35,13 @@ SHARDING_TYPE_TO_GROUP: Dict[str, ShardingTypeGroup] = {
 
 
 class ITEPEmbeddingBagCollectionContext(EmbeddingBagCollectionContext):
+    is_reindexed: bool = False
+
+
+class ITEPEmbeddingCollectionContext(EmbeddingCollectionContext):
+    """Context of one step of a sharded ``ITEPEmbeddingCollection``: the sequence collection's context plus whether the ids were
+    already moved to their pruned positions (``torchrec/distributed/itep_embeddingbag.py:311-314``)."""
+
     is_reindexed: bool = False
 
 
@@ -110,8 +117,10 @@ class _ShardedITEPBase(ShardedEmbeddingModule):
         self._iter += 1
         return self._inner.compute_and_output_dist(ctx, input)
 
+    _context_type: Type[Any] = ITEPEmbeddingBagCollectionContext
+
     def create_context(self):
-        ctx = self._inner.create_context()
+        ctx = self._context_type()
         ctx.is_reindexed = False
         return ctx
 
@@ -139,6 +148,7 @@ class ShardedITEPEmbeddingBagCollection(_ShardedITEPBase):
 
 class ShardedITEPEmbeddingCollection(_ShardedITEPBase):
     _INNER_ATTR = "_embedding_collection"
+    _context_type = ITEPEmbeddingCollectionContext
 
     def __init__(self, module: ITEPEmbeddingCollection, table_name_to_parameter_sharding: Dict[str, ParameterSharding], ec_sharder: EmbeddingCollectionSharder,
                  env: ShardingEnv, device: torch.device, module_fqn: Optional[str] = None) -> None:

@@ -8,16 +8,65 @@ import torch
 from torch import nn
 from torch.nn.parallel import DistributedDataParallel
 
-from torchrec_b200.distributed.embedding import EmbeddingCollectionSharder, ShardedEmbeddingCollection
+from torchrec_b200.distributed.embedding import EmbeddingCollectionContext, EmbeddingCollectionSharder, ShardedEmbeddingCollection
 from torchrec_b200.distributed.embedding_types import BaseEmbeddingSharder, KJTList, ShardedEmbeddingModule
-from torchrec_b200.distributed.embeddingbag import EmbeddingBagCollectionSharder, ShardedEmbeddingBagCollection
+from torchrec_b200.distributed.embeddingbag import EmbeddingBagCollectionContext, EmbeddingBagCollectionSharder, ShardedEmbeddingBagCollection
 from torchrec_b200.distributed.mc_modules import ShardedManagedCollisionCollection
 from torchrec_b200.distributed.types import Awaitable, LazyAwaitable, NoWait, ParameterSharding, QuantizedCommCodecs, ShardingEnv, ShardingType
 from torchrec_b200.modules.mc_embedding_modules import ManagedCollisionEmbeddingBagCollection, ManagedCollisionEmbeddingCollection
 from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
 
 
+class _ManagedCollisionFields:
+    """What a managed-collision step adds to the context of the wrapped collection: the remapped ids per sharding (returned to the
+    caller when asked for), the plan for sending them back to the requesting ranks, and the rows evicted in this step."""
+
+    def _init_mc_fields(self, evictions_per_table: Optional[Dict[str, Optional[torch.Tensor]]] = None,
+                        remapped_kjt: Optional[KJTList] = None) -> None:
+        self.evictions_per_table = evictions_per_table
+        self.remapped_kjt = remapped_kjt
+        self.id_return_plan = None
+        self.id_return_keys = None
+
+    def _record_mc_stream(self, stream: torch.Stream) -> None:
+        if self.evictions_per_table:
+            for value in self.evictions_per_table.values():
+                if value is not None and value.is_cuda:
+                    value.record_stream(stream)
+        if self.remapped_kjt is not None:
+            for kjt in (self.remapped_kjt if isinstance(self.remapped_kjt, (list, KJTList)) else [self.remapped_kjt]):
+                kjt.record_stream(stream)
+
+
+class ManagedCollisionEmbeddingBagCollectionContext(EmbeddingBagCollectionContext, _ManagedCollisionFields):
+    """Context of one step of a sharded ``ManagedCollisionEmbeddingBagCollection`` (``torchrec/distributed/mc_embeddingbag.py:36-49``)."""
+
+    def __init__(self, sharding_contexts=None, inverse_indices=None, variable_batch_per_feature: bool = False, divisor=None,
+                 evictions_per_table: Optional[Dict[str, Optional[torch.Tensor]]] = None, remapped_kjt: Optional[KJTList] = None) -> None:
+        super().__init__(sharding_contexts, inverse_indices, variable_batch_per_feature, divisor)
+        self._init_mc_fields(evictions_per_table, remapped_kjt)
+
+    def record_stream(self, stream: torch.Stream) -> None:
+        super().record_stream(stream)
+        self._record_mc_stream(stream)
+
+
+class ManagedCollisionEmbeddingCollectionContext(EmbeddingCollectionContext, _ManagedCollisionFields):
+    """Context of one step of a sharded ``ManagedCollisionEmbeddingCollection`` (``torchrec/distributed/mc_embedding.py:41-64``)."""
+
+    def __init__(self, sharding_contexts=None, input_features=None, reverse_indices=None,
+                 evictions_per_table: Optional[Dict[str, Optional[torch.Tensor]]] = None, remapped_kjt: Optional[KJTList] = None) -> None:
+        super().__init__(sharding_contexts, input_features, reverse_indices)
+        self._init_mc_fields(evictions_per_table, remapped_kjt)
+
+    def record_stream(self, stream: torch.Stream) -> None:
+        super().record_stream(stream)
+        self._record_mc_stream(stream)
+
+
 class BaseShardedManagedCollisionEmbeddingCollection(ShardedEmbeddingModule):
+    _context_type: Type[Any] = ManagedCollisionEmbeddingBagCollectionContext
+
     def __init__(self, module: nn.Module, table_name_to_parameter_sharding: Dict[str, ParameterSharding], e_sharder: BaseEmbeddingSharder, env: ShardingEnv,
                  device: torch.device, module_fqn: Optional[str] = None) -> None:
         super().__init__()
@@ -111,7 +160,8 @@ class BaseShardedManagedCollisionEmbeddingCollection(ShardedEmbeddingModule):
             l, g = self._managed_collision_collection.remap(features)
             local.append(l)
             glob.append(g)
-        self._reset_rows(self._managed_collision_collection.evict())
+        ctx.evictions_per_table = self._managed_collision_collection.evict()
+        self._reset_rows(ctx.evictions_per_table)
         ctx.remapped_kjt = glob
         return KJTList(local)
 
@@ -133,11 +183,7 @@ class BaseShardedManagedCollisionEmbeddingCollection(ShardedEmbeddingModule):
         return lazy, NoWait(ctx.remapped_kjt[0] if len(ctx.remapped_kjt) == 1 else ctx.remapped_kjt)
 
     def create_context(self):
-        ctx = self._embedding_module.create_context()
-        ctx.remapped_kjt = None
-        ctx.id_return_plan = None
-        ctx.id_return_keys = None
-        return ctx
+        return self._context_type()
 
     def sharded_parameter_names(self, prefix: str = "") -> Iterator[str]:
         yield from self._embedding_module.sharded_parameter_names((prefix + "." if prefix else "") + "_embedding_module")
@@ -150,18 +196,25 @@ class BaseShardedManagedCollisionEmbeddingCollection(ShardedEmbeddingModule):
 
 
 class ShardedManagedCollisionEmbeddingBagCollection(BaseShardedManagedCollisionEmbeddingCollection):
+    _context_type = ManagedCollisionEmbeddingBagCollectionContext
+
     @property
     def unsharded_module_type(self) -> Type[ManagedCollisionEmbeddingBagCollection]:
         return ManagedCollisionEmbeddingBagCollection
 
 
 class ShardedManagedCollisionEmbeddingCollection(BaseShardedManagedCollisionEmbeddingCollection):
+    _context_type = ManagedCollisionEmbeddingCollectionContext
+
     @property
     def unsharded_module_type(self) -> Type[ManagedCollisionEmbeddingCollection]:
         return ManagedCollisionEmbeddingCollection
 
 
-class _BaseMCSharder(BaseEmbeddingSharder):
+class BaseManagedCollisionEmbeddingCollectionSharder(BaseEmbeddingSharder):
+    """Sharder of a collection behind managed collision: wraps the sharder of the plain collection (row-wise only, since the owner
+    of an id's row block is also the owner of its slot).  ``torchrec/distributed/mc_embedding_modules.py:336-390``."""
+
     _inner_sharder_type: Type[BaseEmbeddingSharder]
     _sharded_type: Type[BaseShardedManagedCollisionEmbeddingCollection]
 
@@ -184,7 +237,7 @@ class _BaseMCSharder(BaseEmbeddingSharder):
         return [ShardingType.ROW_WISE.value]
 
 
-class ManagedCollisionEmbeddingBagCollectionSharder(_BaseMCSharder):
+class ManagedCollisionEmbeddingBagCollectionSharder(BaseManagedCollisionEmbeddingCollectionSharder):
     _inner_sharder_type = EmbeddingBagCollectionSharder
     _sharded_type = ShardedManagedCollisionEmbeddingBagCollection
 
@@ -193,7 +246,7 @@ class ManagedCollisionEmbeddingBagCollectionSharder(_BaseMCSharder):
         return ManagedCollisionEmbeddingBagCollection
 
 
-class ManagedCollisionEmbeddingCollectionSharder(_BaseMCSharder):
+class ManagedCollisionEmbeddingCollectionSharder(BaseManagedCollisionEmbeddingCollectionSharder):
     _inner_sharder_type = EmbeddingCollectionSharder
     _sharded_type = ShardedManagedCollisionEmbeddingCollection
 
