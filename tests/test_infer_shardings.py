@@ -121,3 +121,28 @@ def test_strategy_factories_and_device_helpers():
     assert isinstance(create_infer_embedding_sharding("table_wise", _infos("tw", False), env, torch.device("cpu")), inf.InferTwSequenceEmbeddingSharding)
     with pytest.raises(ValueError):
         create_infer_embedding_bag_sharding("grid_shard", infos, env)
+
+
+def test_inference_bucketize_reports_the_bucket_of_every_id_and_vbe_padding():
+    import torch
+
+    from torchrec_b200.distributed.embedding import pad_vbe_kjt_lengths
+    from torchrec_b200.distributed.embedding_sharding import bucketize_kjt_inference
+    from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+    kjt = KeyedJaggedTensor(keys=["a", "b"], values=torch.tensor([3, 12, 7, 25, 0, 19, 31, 8]), lengths=torch.tensor([2, 1, 3, 2]))
+    block = torch.tensor([10, 16])  # feature a: 3 buckets of 10 rows; feature b: of 16 rows (the last one partly used)
+    out, permute, mapping = bucketize_kjt_inference(kjt, 3, block, is_sequence=True)
+    want = [0, 1, 0, 1, 0, 1, 1, 0]  # a: 3 -> 0, 12 -> 1, 7 -> 0;  b: 25 -> 1, 0 -> 0, 19 -> 1, 31 -> 1, 8 -> 0
+    assert mapping.tolist() == want
+    assert out.keys() == ["a", "b"] * 3 and int(out.lengths().sum()) == 8
+    # the permutation restores the request order from the bucketized one
+    local = out.values()[permute]
+    assert local.tolist() == [3, 2, 7, 9, 0, 3, 15, 8]
+    plain, none_p, none_m = bucketize_kjt_inference(kjt, 3, block)
+    assert none_p is None and none_m is None and torch.equal(plain.lengths(), out.lengths())
+
+    vb = KeyedJaggedTensor(keys=["a", "b"], values=torch.arange(6), lengths=torch.tensor([1, 2, 3]), stride_per_key_per_rank=[[1], [2]])
+    fixed = pad_vbe_kjt_lengths(vb)
+    assert fixed.stride() == 2 and fixed.lengths().tolist() == [1, 0, 2, 3] and torch.equal(fixed.values(), vb.values())
+    assert fixed.to_dict()["b"].values().tolist() == [1, 2, 3, 4, 5]

@@ -104,6 +104,17 @@ def _functional_forms(rank, world_size):
         part = co.reduce_scatter_v_per_feature_pooled(flat, [[1, 2], [2, 2]], [2, 1], ctx.pg).wait()
         want = flat[:4] * world_size if rank == 0 else flat[4:] * world_size
         assert torch.equal(part, want)
+        # dense rows grouped by destination: rank r sends r + 1 rows to rank 0 and 2 rows to rank 1
+        from torchrec_b200.distributed.dist_data import TensorAllToAll, TensorValuesAllToAll
+
+        rows = torch.arange((rank + 3) * 2, dtype=torch.float32).view(rank + 3, 2) + 100 * rank
+        got = TensorAllToAll(ctx.pg)(rows, torch.tensor([rank + 1, 2])).wait().wait()
+        from_0 = torch.arange(6, dtype=torch.float32).view(3, 2)
+        from_1 = torch.arange(8, dtype=torch.float32).view(4, 2) + 100
+        want = torch.cat([from_0[:1], from_1[:2]]) if rank == 0 else torch.cat([from_0[1:], from_1[2:]])
+        assert torch.equal(got, want)
+        direct = TensorValuesAllToAll(ctx.pg)(rows, [rank + 1, 2], [1, 2] if rank == 0 else [2, 2]).wait()
+        assert torch.equal(direct, want)
 
 
 def test_blocking_and_functional_collective_forms():

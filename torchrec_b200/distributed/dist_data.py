@@ -518,21 +518,75 @@ class SeqEmbeddingsAllToOne(nn.Module):
         self._device = torch.device(device_str)
 
 
+class TensorAllToAllValuesAwaitable(Awaitable[torch.Tensor]):
+    """Rows (or elements) of a dense tensor on their way to the ranks named by the splits; the collective is started in the
+    constructor and ``wait()`` returns the received tensor ``[sum(output_splits), ...]``.  No gradient flows through it (ids and
+    pool rows travel this way; use ``comm_ops.tensor_alltoall`` for a differentiable exchange).
+    Counterpart of ``torchrec/distributed/dist_data.py:1720-1763``."""
+
+    def __init__(self, pg: dist.ProcessGroup, input: torch.Tensor, input_splits: torch.Tensor, output_splits: torch.Tensor, device: torch.device) -> None:
+        super().__init__()
+        self._workers = pg.size()
+        self._work = None
+        if self._workers == 1:
+            self._dist_values = input
+            return
+        out_rows = int(output_splits.sum())
+        self._dist_values = torch.empty((out_rows,) + tuple(input.shape[1:]), device=device, dtype=input.dtype)
+        self._work = dist.all_to_all_single(self._dist_values, input.contiguous(), output_split_sizes=output_splits.tolist(),
+                                            input_split_sizes=input_splits.tolist(), group=pg, async_op=True)
+
+    def _wait_impl(self) -> torch.Tensor:
+        if self._work is not None:
+            self._work.wait()
+        return self._dist_values
+
+
+class TensorAllToAllSplitsAwaitable(Awaitable[TensorAllToAllValuesAwaitable]):
+    """First stage of a dense-tensor all-to-all: every rank tells every other how many rows it will send; ``wait()`` starts the
+    value exchange with the received counts and returns its awaitable (``torchrec/distributed/dist_data.py:1766-1810``)."""
+
+    def __init__(self, pg: dist.ProcessGroup, input: torch.Tensor, splits: torch.Tensor, device: torch.device) -> None:
+        super().__init__()
+        self._workers = pg.size()
+        self._pg, self._device, self._input, self._input_splits = pg, device, input, splits
+        self._work = None
+        if self._workers == 1:
+            self._output_splits = splits
+            return
+        self._output_splits = torch.empty([self._workers], device=device, dtype=splits.dtype)
+        self._work = dist.all_to_all_single(self._output_splits, splits.to(device), group=pg, async_op=True)
+
+    def _wait_impl(self) -> TensorAllToAllValuesAwaitable:
+        if self._work is not None:
+            self._work.wait()
+        return TensorAllToAllValuesAwaitable(self._pg, self._input, self._input_splits, self._output_splits, self._device)
+
+
 class TensorAllToAll(nn.Module):
-    """Row all-to-all of a dense ``[n, D]`` tensor with given splits (object pools)."""
+    """Redistribute a dense ``[n, ...]`` tensor whose rows are grouped by destination rank: ``forward(local_tensor, splits)`` with
+    ``splits[r]`` rows for rank ``r`` returns the two-stage awaitable (counts, then values)."""
 
     def __init__(self, pg: dist.ProcessGroup) -> None:
         super().__init__()
         self._pg = pg
 
-    def forward(self, local_tensor: torch.Tensor, input_splits: List[int], output_splits: List[int]) -> Awaitable[torch.Tensor]:
-        from torchrec_b200.distributed.comm_ops import tensor_alltoall
+    def forward(self, local_tensor: torch.Tensor, splits: torch.Tensor) -> TensorAllToAllSplitsAwaitable:
+        if not isinstance(splits, torch.Tensor):
+            splits = torch.tensor(splits, dtype=torch.int64)
+        return TensorAllToAllSplitsAwaitable(self._pg, local_tensor, splits, local_tensor.device)
 
-        return NoWait(tensor_alltoall(local_tensor, input_splits, output_splits, self._pg))
 
+class TensorValuesAllToAll(nn.Module):
+    """The second stage on its own, for callers that already know both sides' counts."""
 
-class TensorValuesAllToAll(TensorAllToAll):
-    pass
+    def __init__(self, pg: dist.ProcessGroup) -> None:
+        super().__init__()
+        self._pg = pg
+
+    def forward(self, input: torch.Tensor, input_splits: torch.Tensor, output_splits: torch.Tensor) -> TensorAllToAllValuesAwaitable:
+        as_tensor = lambda x: x if isinstance(x, torch.Tensor) else torch.tensor(x, dtype=torch.int64)
+        return TensorAllToAllValuesAwaitable(self._pg, input, as_tensor(input_splits), as_tensor(output_splits), input.device)
 
 
 class JaggedTensorAllToAll(Awaitable):

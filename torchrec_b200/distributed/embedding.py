@@ -116,6 +116,21 @@ def construct_jagged_tensors(embeddings: torch.Tensor, features: KeyedJaggedTens
         return ret
 
 
+def pad_vbe_kjt_lengths(features: KeyedJaggedTensor) -> KeyedJaggedTensor:
+    """A variable-batch KJT as a fixed-batch one: every key's lengths padded with empty bags up to the largest per-key batch size.
+    Values are untouched (the added bags are empty).  ``torchrec/distributed/embedding.py:264-285``."""
+    strides = features.stride_per_key()
+    max_stride = max(strides)
+    lengths = features.lengths()
+    padded = torch.zeros(max_stride * len(strides), device=lengths.device, dtype=lengths.dtype)
+    start = 0
+    for i, stride in enumerate(strides):
+        padded[i * max_stride: i * max_stride + stride] = lengths[start: start + stride]
+        start += stride
+    return KeyedJaggedTensor(keys=features.keys(), values=features.values(), weights=features.weights_or_none(), lengths=padded, stride=max_stride,
+                             length_per_key=features.length_per_key())
+
+
 class EmbeddingCollectionContext(Multistreamable):
     def __init__(self, sharding_contexts: Optional[List[SequenceShardingContext]] = None, input_features: Optional[List[KeyedJaggedTensor]] = None,
                  reverse_indices: Optional[List[torch.Tensor]] = None) -> None:

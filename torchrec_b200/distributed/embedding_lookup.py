@@ -104,6 +104,35 @@ class CommOpGradientScaling(torch.autograd.Function):
         return grad_output, None
 
 
+def fx_wrap_tensor_view2d(x: torch.Tensor, dim0: int, dim1: int) -> torch.Tensor:
+    return x.view(dim0, dim1)
+
+
+def dummy_tensor(sparse_features: KeyedJaggedTensor, dtype: torch.dtype) -> torch.Tensor:
+    """What a pooled lookup without tables returns: ``[batch, 0]``."""
+    return torch.empty([0], dtype=dtype, device=sparse_features.device()).view(sparse_features.stride(), 0)
+
+
+def embeddings_cat_empty_rank_handle(embeddings: List[torch.Tensor], dummy_embs_tensor: torch.Tensor, dim: int = 0) -> torch.Tensor:
+    """Concatenate the outputs of a rank's kernel groups; a rank without tables returns ``dummy_embs_tensor`` (which keeps autograd and
+    the output exchange uniform across ranks), a single group is returned as is."""
+    if len(embeddings) == 0:
+        return dummy_embs_tensor
+    if len(embeddings) == 1:
+        return embeddings[0]
+    return torch.cat(embeddings, dim=dim)
+
+
+def embeddings_cat_empty_rank_handle_inference(embeddings: List[torch.Tensor], dim: int = 0, device: Optional[str] = None,
+                                               dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """The inference form: an empty tensor of the requested dtype on ``device`` when there is nothing to concatenate."""
+    if len(embeddings) == 0:
+        return torch.empty([0], dtype=dtype, device=torch.device(device) if device is not None else None)
+    if len(embeddings) == 1:
+        return embeddings[0]
+    return torch.cat(embeddings, dim=dim)
+
+
 class _GroupedLookupBase(BaseEmbeddingLookup[KeyedJaggedTensor, torch.Tensor]):
     def __init__(self) -> None:
         super().__init__()
@@ -211,7 +240,7 @@ class GroupedPooledEmbeddingsLookup(_GroupedLookupBase):
             return self._dummy_embs_tensor.view(sparse_features.stride(), 0) if sparse_features.stride() else self._dummy_embs_tensor
         parts = [sparse_features] if len(self._emb_modules) == 1 else sparse_features.split(self._feature_splits)
         pooled = [kernel(self._prepare_group_input(cfg, f)) for cfg, kernel, f in zip(self.grouped_configs, self._emb_modules, parts)]
-        return pooled[0] if len(pooled) == 1 else torch.cat(pooled, dim=1)
+        return embeddings_cat_empty_rank_handle(pooled, self._dummy_embs_tensor, dim=1)
 
     def _prepare_group_input(self, config: GroupedEmbeddingConfig, features: KeyedJaggedTensor) -> KeyedJaggedTensor:
         """Feature processors run on the owning rank, after the input dist; learnable per-id weights get their gradient scaled

@@ -107,6 +107,31 @@ def bucketize_kjt_before_all2all(
     )
 
 
+def bucketize_kjt_inference(
+    kjt: KeyedJaggedTensor,
+    num_buckets: int,
+    block_sizes: torch.Tensor,
+    total_num_buckets: Optional[torch.Tensor] = None,
+    bucketize_pos: bool = False,
+    block_bucketize_row_pos: Optional[List[torch.Tensor]] = None,
+    is_sequence: bool = False,
+    keep_original_indices: bool = False,
+) -> Tuple[KeyedJaggedTensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """The row-wise split of a request at inference: like ``bucketize_kjt_before_all2all`` for a fixed batch, and for sequence
+    features also ``bucket_mapping`` - the bucket every input id went to (what a caller needs to route per-id results back without
+    the permutation).  Returns ``(bucketized KJT, unbucketize_permute or None, bucket_mapping or None)``.
+    Counterpart of ``torchrec/distributed/embedding_sharding.py:307-389``."""
+    out, unbucketize_permute = bucketize_kjt_before_all2all(
+        kjt, num_buckets, block_sizes, total_num_blocks=total_num_buckets, output_permute=is_sequence, bucketize_pos=bucketize_pos,
+        block_bucketize_row_pos=block_bucketize_row_pos, keep_original_indices=keep_original_indices)
+    bucket_mapping = None
+    if is_sequence and unbucketize_permute is not None:
+        # position p of the bucketized order lies in bucket b when ends[b - 1] <= p < ends[b]
+        ends = torch.cumsum(out.lengths().view(num_buckets, -1).sum(dim=1), 0)
+        bucket_mapping = torch.searchsorted(ends, unbucketize_permute.to(ends.dtype), right=True).to(unbucketize_permute.dtype)
+    return out, unbucketize_permute, bucket_mapping
+
+
 def _repeat_keys(keys: List[str], n: int) -> List[str]:
     return list(keys) * n
 

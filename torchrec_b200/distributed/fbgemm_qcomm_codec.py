@@ -34,6 +34,15 @@ class CommType(Enum):
         return self.value
 
 
+def comm_type_to_sparse_type(comm_type: CommType) -> "SparseType":
+    """The kernel-side element type of a wire precision.  MX4 (4-bit values with shared block exponents) has no element type of
+    its own in this package's kernels: its payload is carried as packed 4-bit codes."""
+    from torchrec_b200.modules.embedding_configs import SparseType
+
+    return {CommType.FP32: SparseType.FP32, CommType.FP16: SparseType.FP16, CommType.BF16: SparseType.BF16, CommType.FP8: SparseType.FP8,
+            CommType.INT8: SparseType.INT8, CommType.MX4: SparseType.INT4}[comm_type]
+
+
 def comm_type_to_dtype(comm_type: CommType) -> torch.dtype:
     return {
         CommType.FP32: torch.float32, CommType.FP16: torch.float16, CommType.BF16: torch.bfloat16,

@@ -26,6 +26,19 @@ class TensorPoolAwaitable(LazyAwaitable[torch.Tensor]):
         return rows if self._permute is None else rows.index_select(0, self._permute)
 
 
+def index_select_view(output: torch.Tensor, unbucketize_permute: Optional[torch.Tensor], dim: int) -> torch.Tensor:
+    """Rows gathered per block, back in the order of the request: ``output[unbucketize_permute]`` as ``[n, dim]``."""
+    return output[unbucketize_permute].view(-1, dim)
+
+
+def update(shard: torch.nn.Parameter, rank_ids: torch.Tensor, values: torch.Tensor) -> torch.Tensor:
+    """Overwrite rows ``rank_ids`` of one device's block with ``values`` (moved to the block's device); returns an empty tensor so
+    that the call has a tensor result when it is traced."""
+    with torch.no_grad():
+        shard.index_copy_(0, rank_ids.to(shard.device).long(), values.to(shard.device, shard.dtype))
+    return torch.empty(0)
+
+
 class LocalShardPool(nn.Module):
     """The row block one device holds: ``forward(local ids) -> rows``; ``update`` overwrites rows in place."""
 
@@ -38,7 +51,7 @@ class LocalShardPool(nn.Module):
 
     @torch.no_grad()
     def update(self, rank_ids: torch.Tensor, values: torch.Tensor) -> None:
-        self._shard.index_copy_(0, rank_ids.to(self._shard.device).long(), values.to(self._shard.device, self._shard.dtype))
+        update(self._shard, rank_ids, values)
 
 
 class ShardedInferenceTensorPool(nn.Module):
