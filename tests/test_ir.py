@@ -65,3 +65,26 @@ def test_export_round_trip_matches_eager():
     # another batch with a different number of ids
     kjt2 = KeyedJaggedTensor(keys=["f1", "f2", "f3"], values=torch.arange(1, 8), lengths=torch.tensor([1, 1, 2, 1, 1, 1]))
     torch.testing.assert_close(dec(kjt2), m(kjt2))
+
+
+def test_copy_nodes_of_a_graph_module_are_pointed_at_the_serving_device():
+    import torch.fx
+
+    from torchrec_b200.ir import utils as ir_utils
+
+    graph = torch.fx.Graph()
+    x = graph.placeholder("x")
+    copy = graph.call_function(torch.ops.aten._to_copy.default, (x,), {"dtype": torch.float64, "device": torch.device("cpu")})
+    copy.name = "_to_copy"
+    other = graph.call_function(torch.add, (copy, 1))
+    graph.output(other)
+    gm = torch.fx.GraphModule(torch.nn.Module(), graph)
+    ir_utils.move_to_copy_nodes_to_device(gm, torch.device("meta"))
+    node = next(n for n in gm.graph.nodes if n.name == "_to_copy")
+    assert node.kwargs == {"dtype": torch.float64, "device": torch.device("meta")}
+    gm.recompile()
+    assert gm(torch.ones(2)).device.type == "meta"
+    # the eager bodies and the shape-only bodies of the export placeholders are reachable by name
+    out = ir_utils.ir_emb_lookup_impl([torch.ones(1)], 4, [3, 5])
+    assert [tuple(t.shape) for t in out] == [(4, 3), (4, 5)]
+    assert callable(ir_utils.ir_emb_lookup_fake) and callable(ir_utils.ir_kt_regroup_fake) and callable(ir_utils.ir_dynamic_batch_emb_lookup_fake)

@@ -38,7 +38,7 @@ def ir_emb_lookup(tensors: List[Optional[torch.Tensor]], batch_size: int, dims: 
 
 
 @ir_emb_lookup.register_fake
-def _(tensors: List[Optional[torch.Tensor]], batch_size: int, dims: List[int]) -> List[torch.Tensor]:
+def ir_emb_lookup_fake(tensors: List[Optional[torch.Tensor]], batch_size: int, dims: List[int]) -> List[torch.Tensor]:
     dev = get_device(tensors)
     return [torch.empty(batch_size, d, device=dev) for d in dims]
 
@@ -50,7 +50,7 @@ def ir_kt_regroup(tensors: List[Optional[torch.Tensor]], batch_size: int, dims: 
 
 
 @ir_kt_regroup.register_fake
-def _(tensors: List[Optional[torch.Tensor]], batch_size: int, dims: List[int], dtype: torch.dtype = torch.float32) -> List[torch.Tensor]:
+def ir_kt_regroup_fake(tensors: List[Optional[torch.Tensor]], batch_size: int, dims: List[int], dtype: torch.dtype = torch.float32) -> List[torch.Tensor]:
     dev = get_device(tensors)
     return [torch.empty(batch_size, d, device=dev, dtype=dtype) for d in dims]
 
@@ -62,10 +62,25 @@ def ir_dynamic_batch_emb_lookup(tensors: List[Optional[torch.Tensor]], batch_siz
 
 
 @ir_dynamic_batch_emb_lookup.register_fake
-def _(tensors: List[Optional[torch.Tensor]], batch_size: int, dims: List[int]) -> List[torch.Tensor]:
+def ir_dynamic_batch_emb_lookup_fake(tensors: List[Optional[torch.Tensor]], batch_size: int, dims: List[int]) -> List[torch.Tensor]:
     dev = get_device(tensors)
     b = torch.library.get_ctx().new_dynamic_size()  # the batch of a variable-batch KJT is not an input dimension
     return [torch.empty(b, d, device=dev) for d in dims]
+
+
+# the eager bodies under the names the reference gives them (``torchrec/ir/utils.py:54-114``)
+ir_emb_lookup_impl = ir_emb_lookup
+ir_kt_regroup_impl = ir_kt_regroup
+ir_dynamic_batch_emb_lookup_impl = ir_dynamic_batch_emb_lookup
+
+
+def move_to_copy_nodes_to_device(unflattened_module: nn.Module, device: torch.device) -> nn.Module:
+    """Point every ``_to_copy`` node of an unflattened exported module at ``device``: an exported graph carries the devices of the
+    machine it was traced on as literals, and a module traced on the host must copy to the serving GPU instead."""
+    for node in unflattened_module.graph.nodes:
+        if "_to_copy" in node.name:
+            node.kwargs = {k: (device if isinstance(v, torch.device) else v) for k, v in node.kwargs.items()}
+    return unflattened_module
 
 
 def _default_serializer() -> Type[SerializerInterface]:
