@@ -14,6 +14,16 @@ from torchrec_b200.inference import predictor_pb as pb
 from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
 
 
+def create_training_batch(args: argparse.Namespace) -> Any:
+    """One random Criteo-shaped batch (13 dense features, the 26 categorical ones with one id each) of ``args.batch_size`` samples
+    with ids below ``args.num_embedding_features``: what the example client sends (``torchrec/inference/client.py:19-30``)."""
+    from torchrec_b200.datasets.criteo import DEFAULT_CAT_NAMES, DEFAULT_INT_NAMES
+    from torchrec_b200.datasets.random import RandomRecDataset
+
+    return next(iter(RandomRecDataset(keys=DEFAULT_CAT_NAMES, batch_size=args.batch_size, hash_size=args.num_embedding_features, ids_per_feature=1,
+                                      num_dense=len(DEFAULT_INT_NAMES))))
+
+
 def to_bytes(t: torch.Tensor) -> bytes:
     return t.detach().cpu().contiguous().numpy().tobytes()
 
@@ -57,9 +67,14 @@ def main() -> None:  # pragma: no cover
     p.add_argument("--num_id_list_features", type=int, default=26)
     p.add_argument("--num_embeddings", type=int, default=100)
     a = p.parse_args()
+    client = PredictorClient(a.address)
+    if a.num_float_features == 13 and a.num_id_list_features == 26:
+        a.num_embedding_features = a.num_embeddings
+        batch = create_training_batch(a)
+        print(client.predict(create_request(batch.dense_features, batch.sparse_features)))
+        return
     lengths = torch.randint(0, 4, (a.num_id_list_features * a.batch_size,))
     kjt = KeyedJaggedTensor(keys=[f"cat_{i}" for i in range(a.num_id_list_features)], values=torch.randint(0, a.num_embeddings, (int(lengths.sum()),)), lengths=lengths)
-    client = PredictorClient(a.address)
     print(client.predict(create_request(torch.rand(a.batch_size, a.num_float_features), kjt)))
 
 

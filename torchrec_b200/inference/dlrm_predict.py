@@ -16,6 +16,13 @@ from torchrec_b200.modules.embedding_modules import EmbeddingBagCollection
 from torchrec_b200.sparse.jagged_tensor import KeyedJaggedTensor
 
 
+def create_training_batch(args: Any) -> Any:
+    """A random Criteo-shaped batch sized by ``args.batch_size`` / ``args.num_embedding_features`` (sample input for packaging)."""
+    from torchrec_b200.inference.client import create_training_batch as _create
+
+    return _create(args)
+
+
 @dataclass
 class DLRMModelConfig:
     dense_arch_layer_sizes: List[int]
