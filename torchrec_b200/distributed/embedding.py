@@ -116,6 +116,20 @@ def construct_jagged_tensors(embeddings: torch.Tensor, features: KeyedJaggedTens
         return ret
 
 
+def create_sharding_infos_by_sharding_device_group(module, table_name_to_parameter_sharding: Dict[str, ParameterSharding],
+                                                   fused_params: Optional[Dict[str, Any]]) -> Dict[Tuple[str, Any], List[EmbeddingShardingInfo]]:
+    """The sharding infos of a sequence collection keyed by (sharding type, device kind of the table's shards)
+    (``torchrec/distributed/embedding.py:169-262``)."""
+    from torchrec_b200.distributed.quant_input_dist import get_device_from_parameter_sharding
+
+    by_type = ShardedEmbeddingCollection.create_grouped_sharding_infos(module, table_name_to_parameter_sharding, fused_params)
+    out: Dict[Tuple[str, Any], List[EmbeddingShardingInfo]] = {}
+    for sharding_type, infos in by_type.items():
+        for info in infos:
+            out.setdefault((sharding_type, get_device_from_parameter_sharding(info.param_sharding)), []).append(info)
+    return out
+
+
 def pad_vbe_kjt_lengths(features: KeyedJaggedTensor) -> KeyedJaggedTensor:
     """A variable-batch KJT as a fixed-batch one: every key's lengths padded with empty bags up to the largest per-key batch size.
     Values are untouched (the added bags are empty).  ``torchrec/distributed/embedding.py:264-285``."""

@@ -72,6 +72,17 @@ def compute_kernel_to_embedding_location(compute_kernel: EmbeddingComputeKernel)
     return "host"
 
 
+@dataclass
+class DTensorMetadata:
+    """What is needed to present a table's local shards as a ``DTensor``: the device mesh, the placements on it, and the global
+    size and stride."""
+
+    mesh: Optional[Any] = None
+    placements: Optional[Tuple[Any, ...]] = None
+    size: Optional[Tuple[int, ...]] = None
+    stride: Optional[Tuple[int, ...]] = None
+
+
 class KJTList(Multistreamable):
     """One KJT per table group of a sharding."""
 

@@ -877,6 +877,33 @@ def _embedding_names_by_table(tables) -> List[List[str]]:
     return [[f + "@" + cfg.name if shared[f] else f for f in cfg.feature_names] for cfg in tables]
 
 
+def create_sharding_infos_by_sharding_device_group(module, table_name_to_parameter_sharding: Dict[str, ParameterSharding], prefix: str,
+                                                   fused_params: Optional[Dict[str, Any]], suffix: Optional[str] = "weight",
+                                                   ) -> Dict[Tuple[str, Any], List[EmbeddingShardingInfo]]:
+    """The sharding infos of a collection keyed by (sharding type, device kind of the table's shards): a plan may keep some tables
+    on GPUs and some in host memory, and each (type, kind) pair gets its own sharding object.
+    (``torchrec/distributed/embeddingbag.py:185-280``.)"""
+    from torchrec_b200.distributed.quant_input_dist import get_device_from_parameter_sharding
+
+    by_type = ShardedEmbeddingBagCollection.create_grouped_sharding_infos(module, table_name_to_parameter_sharding, prefix, fused_params, suffix)
+    out: Dict[Tuple[str, Any], List[EmbeddingShardingInfo]] = defaultdict(list)
+    for sharding_type, infos in by_type.items():
+        for info in infos:
+            out[(sharding_type, get_device_from_parameter_sharding(info.param_sharding))].append(info)
+    return dict(out)
+
+
+class EmbeddingAwaitable(LazyAwaitable[torch.Tensor]):
+    """The output of a sharded ``nn.EmbeddingBag``: the pooled rows once the exchange finished."""
+
+    def __init__(self, awaitable: Awaitable[torch.Tensor]) -> None:
+        super().__init__()
+        self._awaitable = awaitable
+
+    def _wait_impl(self) -> torch.Tensor:
+        return self._awaitable.wait()
+
+
 class ShardedEmbeddingBag(ShardedEmbeddingModule[KeyedJaggedTensor, torch.Tensor, torch.Tensor, NullShardedModuleContext], FusedOptimizerModule):
     """A single ``nn.EmbeddingBag`` (sum pooling) sharded row-wise, column-wise or data-parallel
     (``torchrec/distributed/embeddingbag.py:2013-2227``).  It is a one-table sharded collection under the hood: the bag's
