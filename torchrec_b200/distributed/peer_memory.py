@@ -98,6 +98,12 @@ class _PeerBase:
     device: torch.device
 
     def _init_common(self, device: torch.device) -> None:
+        if device.type == "cuda":
+            # every method of a peer group launches kernels of the CUDA library: load it here (and fail loudly without it), so that a
+            # group can be the first thing a process builds
+            from torchrec_b200.ops import _ext
+
+            _ext.require_cuda_ext("peer group")
         self.device = device
         self.err = torch.zeros(1, dtype=torch.int32, device=device)
         self.wait_cycles = default_wait_cycles()

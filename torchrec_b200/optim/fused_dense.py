@@ -30,6 +30,10 @@ class FlatParamBuffer:
         dev = self.params[0].device
         assert all(p.device == dev and p.dtype == torch.float32 for p in self.params), "fp32 parameters on one device expected"
         self.device = dev
+        if dev.type == "cuda":
+            from torchrec_b200.ops import _ext
+
+            _ext.require_cuda_ext("fused dense optimizer")  # its one-launch step is a kernel of the CUDA library
         self.offsets: List[int] = []
         total = 0
         for p in self.params:
